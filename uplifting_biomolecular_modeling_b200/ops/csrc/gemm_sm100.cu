@@ -1,0 +1,360 @@
+// Batched bf16 GEMM on tcgen05 tensor cores with TMA-fed operands and TMEM accumulators.
+//
+//   C[b][m][n] = act(alpha * sum_k A[b][m][k] * B[b][n][k] + bias[n]) + R[b][m][n]
+//
+// Two operand layouts:
+//   K-major  ("TN"): A is [batch][M][K], B is [batch][N][K], K contiguous.
+//   MN-major ("NT"): A is [batch][K][M], B is [batch][K][N], M / N contiguous.
+// The triangle-multiplication contraction uses both: with channel-major planes
+// P[c][r][s] = proj(z[r,s,:])[c] the outgoing update is sum_k Pa[c][i][k] Pb[c][j][k]
+// (K-major) and the incoming update is sum_k Pa[c][k][i] Pb[c][k][j] (MN-major), so one
+// projection kernel serves both directions and no transposed copy is ever written.
+// In the reference this contraction is a cuBLAS strided-batched GEMM
+// (common/opt_core/opt_core/kernels/trimul/native/DESIGN.md:21-47).
+//
+// Kernel shape: persistent CTAs (one per SM), 128 x BN output tile, 64-wide K blocks in a
+// multi-stage TMA ring, warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-5 = epilogue.
+// Two TMEM accumulator buffers let the epilogue of tile t overlap the MMAs of tile t+1.
+#include "host_util.h"
+#include "sm100.cuh"
+
+namespace ubm {
+
+struct GemmParams {
+  int M, N, K, batch;
+  void* C;
+  long long ldc, strideC;
+  const float* bias;
+  const __nv_bfloat16* residual;
+  long long ldr, strideR;
+  float alpha;
+  int out_fp32;
+  int act;  // 0 none, 1 silu, 2 sigmoid, 3 gelu (erf), 4 relu
+  KernelStatus* status;
+  int tiles_m, tiles_n, num_tiles;
+};
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 512 /*barriers*/;
+  static constexpr int kTmemCols = (2 * BN <= 32) ? 32 : 2 * BN;  // two accumulator buffers
+};
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  switch (act) {
+    case 1: return siluf_fast(v);
+    case 2: return sigmoidf_fast(v);
+    case 3: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    case 4: return fmaxf(v, 0.0f);
+    default: return v;
+  }
+}
+
+template <int BN, bool MN_MAJOR>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* empty_bar = full_bar + Cfg::kStages;
+  uint64_t* tfull_bar = empty_bar + Cfg::kStages;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const WaitScope ws{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_kb = (p.K + kBK - 1) / kBK;
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+        const int b = t / tiles_per_batch;
+        const int r = t - b * tiles_per_batch;
+        const int nb = r / p.tiles_m;
+        const int mb = r - nb * p.tiles_m;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          mbar_wait(&empty_bar[stage], phase ^ 1u, ws, 1, stage);
+          if (*abort_flag) break;
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + Cfg::kABytes;
+          mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          if (!MN_MAJOR) {
+            tma_load_3d(sa, &tmA, &full_bar[stage], kb * kBK, mb * kBM, b);
+            tma_load_3d(sb, &tmB, &full_bar[stage], kb * kBK, nb * BN, b);
+          } else {
+#pragma unroll
+            for (int h = 0; h < kBM / 64; ++h)
+              tma_load_3d(sa + h * 8192, &tmA, &full_bar[stage], mb * kBM + h * 64, kb * kBK, b);
+#pragma unroll
+            for (int h = 0; h < BN / 64; ++h)
+              tma_load_3d(sb + h * 8192, &tmB, &full_bar[stage], nb * BN + h * 64, kb * kBK, b);
+          }
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (*abort_flag) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(kBM, BN, MN_MAJOR ? 1 : 0, MN_MAJOR ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+        mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, ws, 2, acc);
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          mbar_wait(&full_bar[stage], phase, ws, 3, stage);
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t sb = sa + Cfg::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            uint64_t ad, bd;
+            if (!MN_MAJOR) {
+              ad = umma_smem_desc(sa + k * 32, 16, 1024, kSwizzle128);
+              bd = umma_smem_desc(sb + k * 32, 16, 1024, kSwizzle128);
+            } else {
+              ad = umma_smem_desc(sa + k * 2048, 8192, 1024, kSwizzle128);
+              bd = umma_smem_desc(sb + k * 2048, 8192, 1024, kSwizzle128);
+            }
+            umma_ss(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        umma_commit(&tfull_bar[acc]);  // accumulator complete
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool vec_ok = p.out_fp32 ? ((p.ldc & 3) == 0 && (p.strideC & 3) == 0 &&
+                                      (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)
+                                   : ((p.ldc & 7) == 0 && (p.strideC & 7) == 0 &&
+                                      (reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+      const int b = t / tiles_per_batch;
+      const int r = t - b * tiles_per_batch;
+      const int nb = r / p.tiles_m;
+      const int mb = r - nb * p.tiles_m;
+      mbar_wait(&tfull_bar[acc], acc_phase, ws, 4, acc);
+      tc_fence_after_sync();
+      const int m = mb * kBM + q * 32 + lane;
+      const bool row_ok = m < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int n0 = nb * BN + c * 32;
+        if (n0 >= p.N) break;  // warp-uniform
+        uint32_t v[32];
+        tmem_ld32(tmem_addr(tmem_base, q, acc * BN + c * 32), v);
+        tmem_ld_wait();
+        if (row_ok) {
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) f[j] += __ldg(p.bias + n0 + j);
+          }
+          if (p.act != 0) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = apply_act(f[j], p.act);
+          }
+          if (p.residual != nullptr) {
+            const __nv_bfloat16* rr = p.residual + b * p.strideR + static_cast<long long>(m) * p.ldr + n0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) f[j] += __bfloat162float(rr[j]);
+          }
+          if (p.out_fp32) {
+            float* cp = reinterpret_cast<float*>(p.C) + b * p.strideC + static_cast<long long>(m) * p.ldc + n0;
+            if (vec_ok && n0 + 32 <= p.N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(cp + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + j < p.N) cp[j] = f[j];
+            }
+          } else {
+            __nv_bfloat16* cp =
+                reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.strideC + static_cast<long long>(m) * p.ldc + n0;
+            if (vec_ok && n0 + 32 <= p.N) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 u;
+                u.x = pack_bf16x2(f[j], f[j + 1]);
+                u.y = pack_bf16x2(f[j + 2], f[j + 3]);
+                u.z = pack_bf16x2(f[j + 4], f[j + 5]);
+                u.w = pack_bf16x2(f[j + 6], f[j + 7]);
+                *reinterpret_cast<uint4*>(cp + j) = u;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + j < p.N) cp[j] = __float2bfloat16(f[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int BN, bool MN_MAJOR>
+static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long long lda, long long ldb,
+                       long long strideA, long long strideB, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  GemmParams p = p0;
+  p.tiles_m = (p.M + kBM - 1) / kBM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  p.num_tiles = p.tiles_m * p.tiles_n * p.batch;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!MN_MAJOR) {
+    uint64_t dA[3] = {(uint64_t)p.K, (uint64_t)p.M, (uint64_t)p.batch};
+    uint64_t sA[2] = {(uint64_t)lda * 2, (uint64_t)strideA * 2};
+    uint32_t bA[3] = {kBK, kBM, 1};
+    rc = make_tmap(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dA, sA, bA, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    uint64_t dB[3] = {(uint64_t)p.K, (uint64_t)p.N, (uint64_t)p.batch};
+    uint64_t sB[2] = {(uint64_t)ldb * 2, (uint64_t)strideB * 2};
+    uint32_t bB[3] = {kBK, (uint32_t)BN, 1};
+    rc = make_tmap(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dB, sB, bB, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  } else {
+    uint64_t dA[3] = {(uint64_t)p.M, (uint64_t)p.K, (uint64_t)p.batch};
+    uint64_t sA[2] = {(uint64_t)lda * 2, (uint64_t)strideA * 2};
+    uint32_t bA[3] = {64, kBK, 1};
+    rc = make_tmap(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dA, sA, bA, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    uint64_t dB[3] = {(uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.batch};
+    uint64_t sB[2] = {(uint64_t)ldb * 2, (uint64_t)strideB * 2};
+    uint32_t bB[3] = {64, kBK, 1};
+    rc = make_tmap(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dB, sB, bB, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  }
+  auto kern = gemm_bf16_kernel<BN, MN_MAJOR>;
+  rc = set_smem(kern, Cfg::kSmemBytes);
+  if (rc) return rc;
+  int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  kern<<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, p);
+  UBM_CHECK_LAUNCH("gemm_bf16_kernel");
+  return UBM_OK;
+}
+
+}  // namespace ubm
+
+// C ABI ---------------------------------------------------------------------------------
+// A, B bf16. ld* and stride* in elements. mn_major: 0 = K contiguous, 1 = M/N contiguous.
+// bias: fp32 [N] or null. residual: bf16 with leading dimension ldr / batch stride strideR, or null.
+// status: device pointer to a ubm::KernelStatus (16 bytes) or null.
+extern "C" int ubm_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const void* residual, int M,
+                             int N, int K, int batch, long long lda, long long ldb, long long ldc, long long ldr,
+                             long long strideA, long long strideB, long long strideC, long long strideR, int mn_major,
+                             int out_fp32, int act, float alpha, void* status, void* stream) {
+  using namespace ubm;
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return UBM_ERR_ARGUMENT;
+  if ((lda & 7) || (ldb & 7) || (batch > 1 && ((strideA & 7) || (strideB & 7)))) {
+    fprintf(stderr, "[ubm] gemm: leading dimensions / batch strides must be multiples of 8 elements\n");
+    return UBM_ERR_ARGUMENT;
+  }
+  GemmParams p;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.batch = batch;
+  p.C = C;
+  p.ldc = ldc;
+  p.strideC = strideC;
+  p.bias = static_cast<const float*>(bias);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.ldr = ldr;
+  p.strideR = strideR;
+  p.alpha = alpha;
+  p.out_fp32 = out_fp32;
+  p.act = act;
+  p.status = static_cast<KernelStatus*>(status);
+  if (batch == 1) {
+    if (strideA == 0) strideA = mn_major ? (long long)K * lda : (long long)M * lda;
+    if (strideB == 0) strideB = mn_major ? (long long)K * ldb : (long long)N * ldb;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool wide = N > 128;
+  if (mn_major) {
+    return wide ? launch_gemm<256, true>(A, B, p, lda, ldb, strideA, strideB, st)
+                : launch_gemm<128, true>(A, B, p, lda, ldb, strideA, strideB, st);
+  }
+  return wide ? launch_gemm<256, false>(A, B, p, lda, ldb, strideA, strideB, st)
+              : launch_gemm<128, false>(A, B, p, lda, ldb, strideA, strideB, st);
+}

@@ -1,0 +1,81 @@
+"""Batched bf16 GEMM on the tcgen05 kernel (``csrc/gemm_sm100.cu``).
+
+``gemm_tn`` contracts the last (contiguous) dimension of both operands; ``gemm_nt`` contracts
+the second-to-last dimension (operands stored K x M / K x N).  Both accept an optional leading
+batch dimension.  Replaces the cuBLAS strided-batched call of the reference's triangle
+multiplication (common/opt_core/opt_core/kernels/fpf_trimul_v4/DESIGN.md:21-37).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import native
+
+ACT = {None: 0, "none": 0, "silu": 1, "sigmoid": 2, "gelu": 3, "relu": 4}
+
+
+def _as3(t: torch.Tensor) -> torch.Tensor:
+    return t.unsqueeze(0) if t.dim() == 2 else t
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, mn_major: bool = False, bias: Optional[torch.Tensor] = None,
+         residual: Optional[torch.Tensor] = None, act: Optional[str] = None, alpha: float = 1.0,
+         out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """C = act(alpha * A.B^T + bias) + residual.
+
+    mn_major=False: a [.., M, K], b [.., N, K];  mn_major=True: a [.., K, M], b [.., K, N].
+    The innermost dimension of a and b must be contiguous; other strides are free as long as
+    they are multiples of 8 elements.
+    """
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("gemm expects bf16 operands")
+    squeeze = a.dim() == 2
+    a3, b3 = _as3(a), _as3(b)
+    if a3.stride(-1) != 1 or b3.stride(-1) != 1:
+        raise ValueError("innermost dimension must be contiguous")
+    batch = a3.shape[0]
+    if b3.shape[0] != batch:
+        raise ValueError("batch mismatch")
+    if mn_major:
+        K, M = a3.shape[1], a3.shape[2]
+        N = b3.shape[2]
+        if b3.shape[1] != K:
+            raise ValueError("K mismatch")
+    else:
+        M, K = a3.shape[1], a3.shape[2]
+        N = b3.shape[1]
+        if b3.shape[2] != K:
+            raise ValueError("K mismatch")
+    if out is None:
+        out = torch.empty((batch, M, N), dtype=out_dtype, device=a.device)
+    out3 = _as3(out)
+    if out3.stride(-1) != 1:
+        raise ValueError("output innermost dimension must be contiguous")
+    res3 = None
+    if residual is not None:
+        res3 = _as3(residual)
+        if res3.dtype != torch.bfloat16 or res3.stride(-1) != 1:
+            raise ValueError("residual must be bf16 with contiguous rows")
+    if bias is not None and bias.dtype != torch.float32:
+        bias = bias.float()
+    st = native.status_tensor(a.device)
+    rc = native.lib().ubm_gemm_bf16(
+        native.ptr(a3), native.ptr(b3), native.ptr(out3), native.ptr(bias), native.ptr(res3),
+        M, N, K, batch,
+        a3.stride(1), b3.stride(1), out3.stride(1), 0 if res3 is None else res3.stride(1),
+        a3.stride(0) if batch > 1 else 0, b3.stride(0) if batch > 1 else 0,
+        out3.stride(0) if batch > 1 else 0, 0 if res3 is None or batch == 1 else res3.stride(0),
+        1 if mn_major else 0, 1 if out3.dtype == torch.float32 else 0, ACT[act], float(alpha),
+        native.ptr(st), native.current_stream(a.device))
+    native.check(rc, "ubm_gemm_bf16")
+    return out3[0] if squeeze and out.dim() == 3 else out
+
+
+def gemm_tn(a, b, **kw):
+    return gemm(a, b, mn_major=False, **kw)
+
+
+def gemm_nt(a, b, **kw):
+    return gemm(a, b, mn_major=True, **kw)
