@@ -1,0 +1,57 @@
+"""Fused pair-stack kernels against the plain PyTorch fp32 statements of the same ops."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel_err(out, ref):
+    return ((out.float() - ref.float()).abs().max() / ref.float().abs().max().clamp(min=1e-6)).item()
+
+
+def _rand(shape, g, scale=1.0):
+    return torch.randn(shape, device="cuda", generator=g) * scale
+
+
+@pytest.mark.parametrize("N", [64, 200, 384])
+@pytest.mark.parametrize("hidden", [512, 256])
+def test_transition(N, hidden):
+    from uplifting_biomolecular_modeling_b200.ops import native, pair, reference
+    g = torch.Generator(device="cuda").manual_seed(3)
+    c = 128
+    x = (_rand((N, N, c), g) + 0.3).bfloat16()
+    nw, nb = 1.0 + 0.1 * _rand((c,), g), 0.1 * _rand((c,), g)
+    fc1, fc2 = _rand((hidden, c), g, c ** -0.5), _rand((hidden, c), g, c ** -0.5)
+    fc3 = _rand((c, hidden), g, hidden ** -0.5)
+    w = pair.TransitionPacked.pack(nw, nb, fc1, fc2, fc3)
+    out = pair.transition_fused(x, w, residual=True)
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "transition")
+    ref = reference.transition(x.float(), nw, nb, fc1, fc2, fc3, residual=True)
+    assert _rel_err(out, ref) < 2e-2
+    upd = (out.float() - x.float())
+    upd_ref = ref - x.float()
+    assert ((upd - upd_ref).abs().mean() / upd_ref.abs().mean()).item() < 2e-2
+
+
+@pytest.mark.parametrize("outgoing", [True, False])
+@pytest.mark.parametrize("N", [64, 136, 320])
+def test_trimul(N, outgoing):
+    from uplifting_biomolecular_modeling_b200.ops import native, pair, reference
+    g = torch.Generator(device="cuda").manual_seed(4)
+    c = 128
+    z = (_rand((N, N, c), g) + 0.2).bfloat16()
+    mask = (torch.rand((N, N), device="cuda", generator=g) > 0.1).float()
+    niw, nib = 1.0 + 0.1 * _rand((c,), g), 0.1 * _rand((c,), g)
+    now, nob = 1.0 + 0.1 * _rand((c,), g), 0.1 * _rand((c,), g)
+    p_in, g_in = _rand((2 * c, c), g, c ** -0.5), _rand((2 * c, c), g, c ** -0.5)
+    p_out, g_out = _rand((c, c), g, c ** -0.5), _rand((c, c), g, c ** -0.5)
+    w = pair.TrimulPacked.pack(niw, nib, p_in, g_in, now, nob, p_out, g_out)
+    out = pair.trimul_fused(z, mask, w, outgoing=outgoing, residual=False)
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "trimul")
+    ref = reference.triangle_multiplication(z.float(), mask, niw, nib, p_in, g_in, now, nob, p_out, g_out,
+                                            outgoing=outgoing)
+    err = (out.float() - ref).abs().mean() / ref.abs().mean()
+    assert err.item() < 3e-2, err.item()
+    assert _rel_err(out, ref) < 6e-2

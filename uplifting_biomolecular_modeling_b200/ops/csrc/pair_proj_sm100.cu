@@ -1,0 +1,406 @@
+// Fused LayerNorm -> 512-wide projection of pair rows, with the op-specific epilogue.
+//
+// One kernel, two epilogues:
+//   MODE_TRIMUL   : a = sigmoid(g_a(n)) * p_a(n) * mask, b likewise, n = LN(z_row); written as
+//                   channel-major bf16 planes P[2][c][i][k] (the operands of the triangle
+//                   contraction).  Reference: K1 of common/opt_core/opt_core/kernels/trimul/
+//                   native/DESIGN.md:21-47 and _k1c/_k1t of kernels/fpf_trimul_v4/kernels.py.
+//   MODE_TRIATT   : q | k | v | sigmoid(g) rows (bf16, [row][128]) plus the per-head pair bias
+//                   planes bias[h][j][k]; optionally at the transposed pair index (ending node).
+//                   Reference: the triangle-attention prologue
+//                   (common/opt_core/opt_core/attn/pair_fused.py:1136, N15 triatt_procuda_sm90.cu).
+//
+// LayerNorm is folded into the GEMM: with W' = W * gamma (per input channel),
+//   W.LN(x) = rstd * (W'.x - mu * rowsum(W')) + W.beta,
+// so the raw bf16 row tile that TMA brings in is the A operand as it stands, and the row
+// statistics (computed from the same shared-memory tile while the MMAs run) are applied to the
+// fp32 accumulator in the epilogue.  The 512 x 128 weight matrix stays resident in shared memory
+// for the life of the persistent CTA; only row tiles stream.
+//
+// Warps: 0 = TMA producer, 1 = MMA issuer, 2-5 = epilogue group 0 (output half 0),
+// 6-9 = epilogue group 1 (output half 1).  Each half is one 128 x 256 accumulator in TMEM, so
+// the epilogue of half 0 overlaps the MMAs of half 1 and of the next tile.
+#include "host_util.h"
+#include "sm100.cuh"
+
+namespace ubm {
+
+constexpr int kPPRows = 128;   // rows per tile
+constexpr int kPPC = 128;      // input channels
+constexpr int kPPStages = 2;   // row-tile ring
+constexpr int kPPXBytes = kPPRows * kPPC * 2;        // 32 KB, two k-blocks of [128][64]
+constexpr int kPPWBytes = 512 * kPPC * 2;            // 128 KB, two k-blocks of [512][64]
+constexpr int kPPMaxHeads = 8;
+
+enum { MODE_TRIMUL = 0, MODE_TRIATT = 1 };
+
+struct PairProjParams {
+  long long R;       // number of rows (N * N)
+  int N;             // tokens
+  int Np;            // leading dimension of planes (>= N, multiple of 8)
+  const float* colsum;   // [512]  rowsum(W') per output column
+  const float* colbias;  // [512]  W.beta (+ bias) per output column
+  const float* mask;     // [R] or null (MODE_TRIMUL: multiplies a and b)
+  // MODE_TRIMUL
+  __nv_bfloat16* planes;  // [2][128][N][Np]
+  // MODE_TRIATT
+  __nv_bfloat16* q;  // each [R][128], row index possibly transposed
+  __nv_bfloat16* k;
+  __nv_bfloat16* v;
+  __nv_bfloat16* g;
+  __nv_bfloat16* headbias;   // [H][N][Np]
+  const float* wb;           // [H][128] head-bias weights already multiplied by gamma
+  const float* wb_colsum;    // [H]
+  const float* wb_colbias;   // [H]
+  int H;
+  int transpose_out;
+  float* stats_out;  // optional [R][2] (mu, rstd) of the input rows, or null
+  KernelStatus* status;
+  int num_tiles;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(320, 1)
+pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, PairProjParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sW = smem;                               // 128 KB
+  uint8_t* sX = smem + kPPWBytes;                   // stages * 32 KB
+  float* sColsum = reinterpret_cast<float*>(sX + kPPStages * kPPXBytes);  // 512
+  float* sColbias = sColsum + 512;                                         // 512
+  float* sWb = sColbias + 512;                                             // kPPMaxHeads * 128
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sWb + kPPMaxHeads * 128);
+  uint64_t* x_full = bars;                 // [stages]
+  uint64_t* x_empty = x_full + kPPStages;  // [stages]
+  uint64_t* w_full = x_empty + kPPStages;  // [1]
+  uint64_t* acc_full = w_full + 1;         // [2]
+  uint64_t* acc_empty = acc_full + 2;      // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const WaitScope ws{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kPPStages; ++s) {
+      mbar_init(&x_full[s], 1);
+      mbar_init(&x_empty[s], 1 + 8);  // MMA commit + one arrival per epilogue warp
+    }
+    mbar_init(w_full, 1);
+    for (int h = 0; h < 2; ++h) {
+      mbar_init(&acc_full[h], 1);
+      mbar_init(&acc_empty[h], 4);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmX);
+    tma_prefetch_desc(&tmW);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  // column constants
+  for (int i = threadIdx.x; i < 512; i += blockDim.x) {
+    sColsum[i] = p.colsum[i];
+    sColbias[i] = p.colbias[i];
+  }
+  if (MODE == MODE_TRIATT) {
+    for (int i = threadIdx.x; i < p.H * 128; i += blockDim.x) sWb[i] = p.wb[i];
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      // resident weights: two k-blocks, each 512 rows loaded as two boxes of 256 rows
+      mbar_expect_tx(w_full, kPPWBytes);
+      for (int kb = 0; kb < 2; ++kb)
+        for (int h = 0; h < 2; ++h)
+          tma_load_2d(sW + kb * 65536 + h * 32768, &tmW, w_full, kb * 64, h * 256);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+        mbar_wait(&x_empty[stage], phase ^ 1u, ws, 11, stage);
+        if (*abort_flag) break;
+        uint8_t* dst = sX + stage * kPPXBytes;
+        mbar_expect_tx(&x_full[stage], kPPXBytes);
+        tma_load_2d(dst, &tmX, &x_full[stage], 0, t * kPPRows);
+        tma_load_2d(dst + 16384, &tmX, &x_full[stage], 64, t * kPPRows);
+        if (++stage == kPPStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(128, 256);
+      mbar_wait(w_full, 0, ws, 12);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase = 0;
+      for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+        mbar_wait(&x_full[stage], phase, ws, 13, stage);
+        tc_fence_after_sync();
+        const uint32_t xa = smem_u32(sX + stage * kPPXBytes);
+        const uint32_t wa = smem_u32(sW);
+        for (int h = 0; h < 2; ++h) {
+          mbar_wait(&acc_empty[h], acc_phase ^ 1u, ws, 14, h);
+          tc_fence_after_sync();
+#pragma unroll
+          for (int kb = 0; kb < 2; ++kb) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint64_t ad = umma_smem_desc(xa + kb * 16384 + k * 32, 16, 1024, kSwizzle128);
+              const uint64_t bd = umma_smem_desc(wa + kb * 65536 + h * 32768 + k * 32, 16, 1024, kSwizzle128);
+              umma_ss(tmem_base + h * 256, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+          }
+          umma_commit(&acc_full[h]);
+        }
+        umma_commit(&x_empty[stage]);
+        if (++stage == kPPStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+        acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue groups
+    const int grp = (warp - 2) >> 2;  // 0 or 1: which 256-column half
+    const int q = warp & 3;           // TMEM lane quadrant
+    const int row_in_tile = q * 32 + lane;
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+      const long long r = static_cast<long long>(t) * kPPRows + row_in_tile;
+      const bool row_ok = r < p.R;
+      // ---- row statistics (and head bias) from the shared-memory tile
+      mbar_wait(&x_full[stage], phase, ws, 15, stage);
+      const uint8_t* xs = sX + stage * kPPXBytes;
+      float sum = 0.f, sumsq = 0.f;
+      float hb[kPPMaxHeads / 2];
+#pragma unroll
+      for (int h = 0; h < kPPMaxHeads / 2; ++h) hb[h] = 0.f;
+      const int hpg = (MODE == MODE_TRIATT) ? (p.H + 1) / 2 : 0;  // heads per group
+#pragma unroll 4
+      for (int c16 = 0; c16 < 16; ++c16) {
+        const int kb = c16 >> 3;
+        const uint4 u = *reinterpret_cast<const uint4*>(xs + kb * 16384 + swz128_offset(row_in_tile, c16 & 7));
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+        float e[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          e[2 * j] = bf16_lo(w[j]);
+          e[2 * j + 1] = bf16_hi(w[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          sum += e[j];
+          sumsq += e[j] * e[j];
+        }
+        if (MODE == MODE_TRIATT) {
+#pragma unroll
+          for (int h = 0; h < kPPMaxHeads / 2; ++h) {
+            if (h < hpg) {
+              const float* wrow = sWb + (grp * hpg + h) * 128 + c16 * 8;
+              const float4 w0 = *reinterpret_cast<const float4*>(wrow);
+              const float4 w1 = *reinterpret_cast<const float4*>(wrow + 4);
+              hb[h] += e[0] * w0.x + e[1] * w0.y + e[2] * w0.z + e[3] * w0.w + e[4] * w1.x + e[5] * w1.y +
+                       e[6] * w1.z + e[7] * w1.w;
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&x_empty[stage]);
+      const float mu = sum * (1.0f / kPPC);
+      const float var = fmaxf(sumsq * (1.0f / kPPC) - mu * mu, 0.f);
+      const float rstd = rsqrtf(var + 1e-5f);
+      if (p.stats_out != nullptr && grp == 0 && row_ok) {
+        p.stats_out[2 * r] = mu;
+        p.stats_out[2 * r + 1] = rstd;
+      }
+      // pair index of this row
+      int pi = 0, pk = 0;
+      if (row_ok) {
+        pi = static_cast<int>(r / p.N);
+        pk = static_cast<int>(r - static_cast<long long>(pi) * p.N);
+      }
+      const float mval = (MODE == MODE_TRIMUL && p.mask != nullptr && row_ok) ? p.mask[r] : 1.0f;
+
+      if (MODE == MODE_TRIATT && row_ok) {
+        const int oi = p.transpose_out ? pk : pi;
+        const int ok = p.transpose_out ? pi : pk;
+#pragma unroll
+        for (int h = 0; h < kPPMaxHeads / 2; ++h) {
+          const int head = grp * hpg + h;
+          if (h < hpg && head < p.H) {
+            const float val = rstd * (hb[h] - mu * p.wb_colsum[head]) + p.wb_colbias[head];
+            p.headbias[(static_cast<long long>(head) * p.N + oi) * p.Np + ok] = __float2bfloat16(val);
+          }
+        }
+      }
+
+      // ---- accumulator half of this group
+      mbar_wait(&acc_full[grp], acc_phase, ws, 16, grp);
+      tc_fence_after_sync();
+      const uint32_t tbase = tmem_addr(tmem_base, q, grp * 256);
+      if (MODE == MODE_TRIMUL) {
+        // half = [p (128) | g (128)] of operand `grp`; out[c] = p * sigmoid(g) * mask
+        __nv_bfloat16* plane = p.planes + static_cast<long long>(grp) * 128 * p.N * p.Np;
+        const long long off = static_cast<long long>(pi) * p.Np + pk;
+        const long long cstride = static_cast<long long>(p.N) * p.Np;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128; c0 += 32) {
+          uint32_t pv[32], gv[32];
+          tmem_ld32(tbase + c0, pv);
+          tmem_ld32(tbase + 128 + c0, gv);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int cp = grp * 256 + c0 + j;
+              const int cg = cp + 128;
+              const float pj = rstd * (__uint_as_float(pv[j]) - mu * sColsum[cp]) + sColbias[cp];
+              const float gj = rstd * (__uint_as_float(gv[j]) - mu * sColsum[cg]) + sColbias[cg];
+              const float val = pj * sigmoidf_fast(gj) * mval;
+              plane[(c0 + j) * cstride + off] = __float2bfloat16(val);
+            }
+          }
+        }
+      } else {
+        // half 0 = [q | k], half 1 = [v | g]; rows written at (possibly transposed) pair index
+        const long long orow = p.transpose_out ? (static_cast<long long>(pk) * p.N + pi) : r;
+        __nv_bfloat16* o0 = (grp == 0 ? p.q : p.v) + orow * 128;
+        __nv_bfloat16* o1 = (grp == 0 ? p.k : p.g) + orow * 128;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 256; c0 += 32) {
+          uint32_t av[32];
+          tmem_ld32(tbase + c0, av);
+          tmem_ld_wait();
+          if (row_ok) {
+            const bool gate = (grp == 1) && (c0 >= 128);
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = grp * 256 + c0 + j;
+              float val = rstd * (__uint_as_float(av[j]) - mu * sColsum[col]) + sColbias[col];
+              f[j] = gate ? sigmoidf_fast(val) : val;
+            }
+            __nv_bfloat16* dst = (c0 < 128 ? o0 + c0 : o1 + (c0 - 128));
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 u;
+              u.x = pack_bf16x2(f[j], f[j + 1]);
+              u.y = pack_bf16x2(f[j + 2], f[j + 3]);
+              u.z = pack_bf16x2(f[j + 4], f[j + 5]);
+              u.w = pack_bf16x2(f[j + 6], f[j + 7]);
+              *reinterpret_cast<uint4*>(dst + j) = u;
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[grp]);
+      if (++stage == kPPStages) {
+        stage = 0;
+        phase ^= 1u;
+      }
+      acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+constexpr int kPPSmemBytes = kPPWBytes + kPPStages * kPPXBytes + (512 + 512 + kPPMaxHeads * 128) * 4 + 256 + 1024;
+
+template <int MODE>
+static int launch_pair_proj(const void* x, const void* w, PairProjParams p, cudaStream_t stream) {
+  CUtensorMap tmX, tmW;
+  uint64_t dX[2] = {(uint64_t)kPPC, (uint64_t)p.R};
+  uint64_t sX[1] = {(uint64_t)kPPC * 2};
+  uint32_t bX[2] = {64, kPPRows};
+  int rc = make_tmap(&tmX, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dX, sX, bX, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  uint64_t dW[2] = {(uint64_t)kPPC, 512};
+  uint64_t sW[1] = {(uint64_t)kPPC * 2};
+  uint32_t bW[2] = {64, 256};
+  rc = make_tmap(&tmW, w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dW, sW, bW, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  p.num_tiles = static_cast<int>((p.R + kPPRows - 1) / kPPRows);
+  auto kern = pair_proj_kernel<MODE>;
+  rc = set_smem(kern, kPPSmemBytes);
+  if (rc) return rc;
+  const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  kern<<<grid, 320, kPPSmemBytes, stream>>>(tmX, tmW, p);
+  UBM_CHECK_LAUNCH("pair_proj_kernel");
+  return UBM_OK;
+}
+
+}  // namespace ubm
+
+// z: [N*N][128] bf16.  w: [512][128] bf16 = rows [p_a; g_a; p_b; g_b] each already multiplied by
+// the LayerNorm gamma.  colsum/colbias: fp32 [512].  mask: fp32 [N*N] or null.
+// planes: bf16 [2][128][N][Np] (Np multiple of 8, >= N).
+extern "C" int ubm_trimul_proj(const void* z, const void* w, const void* colsum, const void* colbias, const void* mask,
+                               void* planes, void* stats_out, int N, int Np, void* status, void* stream) {
+  using namespace ubm;
+  if (N <= 0 || Np < N || (Np & 7)) return UBM_ERR_ARGUMENT;
+  PairProjParams p = {};
+  p.R = static_cast<long long>(N) * N;
+  p.N = N;
+  p.Np = Np;
+  p.colsum = static_cast<const float*>(colsum);
+  p.colbias = static_cast<const float*>(colbias);
+  p.mask = static_cast<const float*>(mask);
+  p.planes = static_cast<__nv_bfloat16*>(planes);
+  p.stats_out = static_cast<float*>(stats_out);
+  p.status = static_cast<KernelStatus*>(status);
+  return launch_pair_proj<MODE_TRIMUL>(z, w, p, static_cast<cudaStream_t>(stream));
+}
+
+// w: [512][128] bf16 = rows [q; k; v; g] (gamma folded, q pre-scaled by 1/sqrt(d)).
+// wb: fp32 [H][128] head-bias weights (gamma folded); wb_colsum/wb_colbias fp32 [H].
+// q,k,v,g: bf16 [N*N][128]; headbias: bf16 [H][N][Np].
+extern "C" int ubm_triatt_proj(const void* z, const void* w, const void* colsum, const void* colbias, const void* wb,
+                               const void* wb_colsum, const void* wb_colbias, void* q, void* k, void* v, void* g,
+                               void* headbias, void* stats_out, int N, int Np, int H, int transpose_out, void* status,
+                               void* stream) {
+  using namespace ubm;
+  if (N <= 0 || Np < N || (Np & 7) || H <= 0 || H > kPPMaxHeads) return UBM_ERR_ARGUMENT;
+  PairProjParams p = {};
+  p.R = static_cast<long long>(N) * N;
+  p.N = N;
+  p.Np = Np;
+  p.colsum = static_cast<const float*>(colsum);
+  p.colbias = static_cast<const float*>(colbias);
+  p.q = static_cast<__nv_bfloat16*>(q);
+  p.k = static_cast<__nv_bfloat16*>(k);
+  p.v = static_cast<__nv_bfloat16*>(v);
+  p.g = static_cast<__nv_bfloat16*>(g);
+  p.headbias = static_cast<__nv_bfloat16*>(headbias);
+  p.wb = static_cast<const float*>(wb);
+  p.wb_colsum = static_cast<const float*>(wb_colsum);
+  p.wb_colbias = static_cast<const float*>(wb_colbias);
+  p.H = H;
+  p.transpose_out = transpose_out;
+  p.stats_out = static_cast<float*>(stats_out);
+  p.status = static_cast<KernelStatus*>(status);
+  return launch_pair_proj<MODE_TRIATT>(z, w, p, static_cast<cudaStream_t>(stream));
+}
