@@ -55,3 +55,54 @@ def test_trimul(N, outgoing):
     err = (out.float() - ref).abs().mean() / ref.abs().mean()
     assert err.item() < 3e-2, err.item()
     assert _rel_err(out, ref) < 6e-2
+
+
+@pytest.mark.parametrize("rows,N,H", [(2, 128, 4), (5, 200, 4), (8, 384, 2)])
+def test_attention_core(rows, N, H):
+    """The attention kernel alone: base-2 softmax with shared bias, gate and tail masking."""
+    from uplifting_biomolecular_modeling_b200.ops import native, pair, reference
+    g = torch.Generator(device="cuda").manual_seed(5)
+    D = 32
+    q = _rand((rows, N, H * D), g).bfloat16()
+    k = _rand((rows, N, H * D), g).bfloat16()
+    v = _rand((rows, N, H * D), g).bfloat16()
+    gate = torch.rand((rows, N, H * D), device="cuda", generator=g).bfloat16()
+    Np = (N + 7) // 8 * 8
+    bias = torch.zeros((H, N, Np), device="cuda", dtype=torch.bfloat16)
+    bias[:, :, :N] = _rand((H, N, N), g).bfloat16()
+    out = torch.empty_like(q)
+    qs = (q.float() * (pair.LOG2E / D ** 0.5)).bfloat16()
+    bs = (bias.float() * pair.LOG2E).bfloat16()
+    pair.attention_d32(qs, k, v, bs, gate, out, rows, N, N, H, ldb=Np)
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "attention")
+    qh = qs.float().view(rows, N, H, D).transpose(1, 2) / pair.LOG2E
+    kh = k.float().view(rows, N, H, D).transpose(1, 2)
+    vh = v.float().view(rows, N, H, D).transpose(1, 2)
+    ref = reference.attention_with_bias(qh, kh, vh, bs.float()[None, :, :, :N] / pair.LOG2E, scale=1.0)
+    ref = ref.transpose(1, 2).reshape(rows, N, H * D) * gate.float()
+    err = (out.float() - ref).abs().max().item()
+    assert err < 3e-2, err
+
+
+@pytest.mark.parametrize("starting", [True, False])
+@pytest.mark.parametrize("N", [64, 200])
+def test_triangle_attention(N, starting):
+    from uplifting_biomolecular_modeling_b200.ops import native, pair, reference
+    g = torch.Generator(device="cuda").manual_seed(6)
+    c, H = 128, 4
+    z = (_rand((N, N, c), g) + 0.2).bfloat16()
+    ln_w, ln_b = 1.0 + 0.1 * _rand((c,), g), 0.1 * _rand((c,), g)
+    w_bias = _rand((H, c), g, c ** -0.5)
+    w_q, w_k, w_v, w_g = [_rand((c, c), g, c ** -0.5) for _ in range(4)]
+    b_g = 0.1 * _rand((c,), g)
+    w_o, b_o = _rand((c, c), g, c ** -0.5), 0.1 * _rand((c,), g)
+    w = pair.TriattPacked.pack(ln_w, ln_b, w_bias, w_q, w_k, w_v, w_g, b_g, w_o, b_o, H)
+    out = pair.triangle_attention_fused(z, w, starting=starting, residual=False)
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "triangle attention")
+    ref = reference.triangle_attention(z.float(), None, ln_w, ln_b, w_bias, w_q, w_k, w_v, w_g, b_g, w_o, b_o, H,
+                                       starting=starting)
+    err = (out.float() - ref).abs().mean() / ref.abs().mean()
+    assert err.item() < 3e-2, err.item()
+    assert _rel_err(out, ref) < 6e-2

@@ -1,0 +1,410 @@
+// Attention with a pair bias shared over rows, on tcgen05 / TMEM / TMA (head dimension 32).
+//
+//   O[r, q, h, :] = softmax_k( Q[r,q,h,:] . K[r,k,h,:] + bias[h, q, k] ) V[r,k,h,:]   (* gate)
+//
+// r is the "row" of a triangle attention (all rows share the bias of a head), a diffusion
+// sample of the token transformer, or a batch entry of single attention with pair bias.  Q is
+// pre-scaled by log2(e)/sqrt(d) and the bias by log2(e), so the softmax runs in base 2.
+//
+// CTA = one query tile (128) x one head x TWO rows.  The two rows share every bias tile that TMA
+// brings in (the reason the reference's kernels process several rows per CTA:
+// common/opt_core/opt_core/kernels/triattn/triattn_native/DESIGN.md:41-59) and their softmax
+// warpgroups ping-pong on the one tensor core.  Per 128-key tile and row:
+//   MMA warp  : S = Q K^T            (TMEM, 128 columns per row)
+//   softmax WG: S -> registers, S freed at once (the next QK^T overlaps the exponentials),
+//               + bias, running max / sum, P (bf16) -> shared memory
+//   MMA warp  : O += P V             (TMEM, 32 columns per row; V is an MN-major B operand)
+// O is rescaled in TMEM only when a running maximum moved.  No TMA multicast is used: the bias
+// tile is loaded once per CTA and reused by both rows from shared memory.
+//
+// Persistent CTAs walk (head, query tile, row pair) with the row pair fastest, so CTAs that
+// run together read the same bias tiles from L2.
+#include "host_util.h"
+#include "sm100.cuh"
+
+namespace ubm {
+
+constexpr int kAD = 32;                         // head dimension
+constexpr int kATile = 128;                     // queries per CTA, keys per step
+constexpr int kAQBytes = kATile * kAD * 2;      // 8 KB
+constexpr int kAKVBytes = kATile * kAD * 2;     // 8 KB
+constexpr int kABiasBytes = kATile * kATile * 2;  // 32 KB (two halves of 64 keys)
+constexpr int kAStageBytes = 4 * kAKVBytes + kABiasBytes;  // K0 V0 K1 V1 bias = 64 KB
+constexpr int kAPBytes = kATile * kATile * 2;   // 32 KB per row
+constexpr int kAStages = 2;
+constexpr float kNegBig = -1.0e30f;
+
+struct AttnParams {
+  int rows, Nq, Nk, H;
+  const __nv_bfloat16* gate;  // [rows][Nq][H*32] or null
+  __nv_bfloat16* out;         // [rows][Nq][H*32], or transposed [Nq][rows][H*32]
+  int transpose_out;
+  int has_bias;
+  KernelStatus* status;
+  int n_qt, n_kt, n_rp, num_items;
+};
+
+__global__ void __launch_bounds__(384, 1)
+attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmB, AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                              // 2 x 8 KB
+  uint8_t* sSt = sQ + 2 * kAQBytes;                // stages x 64 KB
+  uint8_t* sP = sSt + kAStages * kAStageBytes;     // 2 x 32 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kAPBytes);
+  uint64_t* q_full = bars;             // [1]
+  uint64_t* q_empty = q_full + 1;      // [1] commit
+  uint64_t* kv_full = q_empty + 1;     // [stages]
+  uint64_t* kv_empty = kv_full + kAStages;   // [stages] commit + 8 warps
+  uint64_t* s_full = kv_empty + kAStages;    // [2] commit
+  uint64_t* s_empty = s_full + 2;      // [2] 4 warps
+  uint64_t* p_full = s_empty + 2;      // [2] 4 warps
+  uint64_t* pv_done = p_full + 2;      // [2] commit
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const WaitScope ws{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
+    for (int s = 0; s < kAStages; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1 + 8);
+    }
+    for (int r = 0; r < 2; ++r) {
+      mbar_init(&s_full[r], 1);
+      mbar_init(&s_empty[r], 4);
+      mbar_init(&p_full[r], 4);
+      mbar_init(&pv_done[r], 1);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base;         // S[r] at r * 128
+  const uint32_t tO = tmem_base + 256;   // O[r] at r * 32
+  const int T = p.n_kt;
+
+  // Register split: warps 0-3 (producer, MMA issuer, two idle warps) give registers up, the two
+  // softmax warpgroups (warps 4-7 and 8-11) take them: 128 * 40 + 256 * 232 <= 65536.
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t item_cnt = 0, gk = 0;
+      for (int item = blockIdx.x; item < p.num_items; item += gridDim.x, ++item_cnt) {
+        const int rp = item % p.n_rp;
+        const int tmp = item / p.n_rp;
+        const int qt = tmp % p.n_qt;
+        const int h = tmp / p.n_qt;
+        const int r0 = rp * 2;
+        mbar_wait(q_empty, (item_cnt & 1u) ^ 1u, ws, 51);
+        if (*abort_flag) break;
+        mbar_expect_tx(q_full, 2 * kAQBytes);
+        tma_load_3d(sQ, &tmQ, q_full, h * kAD, qt * kATile, r0);
+        tma_load_3d(sQ + kAQBytes, &tmQ, q_full, h * kAD, qt * kATile, r0 + 1);
+        for (int j = 0; j < T; ++j, ++gk) {
+          const int s = gk & 1;
+          mbar_wait(&kv_empty[s], ((gk >> 1) & 1u) ^ 1u, ws, 52, s);
+          if (*abort_flag) break;
+          uint8_t* st = sSt + s * kAStageBytes;
+          mbar_expect_tx(&kv_full[s], p.has_bias ? kAStageBytes : 4 * kAKVBytes);
+          tma_load_3d(st, &tmK, &kv_full[s], h * kAD, j * kATile, r0);
+          tma_load_3d(st + kAKVBytes, &tmV, &kv_full[s], h * kAD, j * kATile, r0);
+          tma_load_3d(st + 2 * kAKVBytes, &tmK, &kv_full[s], h * kAD, j * kATile, r0 + 1);
+          tma_load_3d(st + 3 * kAKVBytes, &tmV, &kv_full[s], h * kAD, j * kATile, r0 + 1);
+          if (p.has_bias) {
+            tma_load_3d(st + 4 * kAKVBytes, &tmB, &kv_full[s], j * kATile, qt * kATile, h);
+            tma_load_3d(st + 4 * kAKVBytes + 16384, &tmB, &kv_full[s], j * kATile + 64, qt * kATile, h);
+          }
+        }
+        if (*abort_flag) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, kAD, 0, 1);  // B = V is MN-major
+      uint32_t item_cnt = 0, gk = 0;
+      auto issue_qk = [&](int r, uint32_t g) {
+        const uint32_t st = smem_u32(sSt + (g & 1) * kAStageBytes);
+        const uint32_t qa = smem_u32(sQ + r * kAQBytes);
+        const uint32_t ka = st + r * 2 * kAKVBytes;
+#pragma unroll
+        for (int k = 0; k < kAD / 16; ++k) {
+          const uint64_t ad = umma_smem_desc(qa + k * 32, 16, 512, kSwizzle64);
+          const uint64_t bd = umma_smem_desc(ka + k * 32, 16, 512, kSwizzle64);
+          umma_ss(tS + r * 128, ad, bd, idesc_qk, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[r]);
+      };
+      for (int item = blockIdx.x; item < p.num_items; item += gridDim.x, ++item_cnt) {
+        mbar_wait(q_full, item_cnt & 1u, ws, 53);
+        mbar_wait(&kv_full[gk & 1], (gk >> 1) & 1u, ws, 54, 0);
+        tc_fence_after_sync();
+        for (int r = 0; r < 2; ++r) {
+          mbar_wait(&s_empty[r], (gk & 1u) ^ 1u, ws, 55, r);
+          tc_fence_after_sync();
+          issue_qk(r, gk);
+        }
+        for (int j = 0; j < T; ++j) {
+          const uint32_t g = gk + j;
+          if (j + 1 < T) {
+            mbar_wait(&kv_full[(g + 1) & 1], ((g + 1) >> 1) & 1u, ws, 56, 1);
+            tc_fence_after_sync();
+            for (int r = 0; r < 2; ++r) {
+              mbar_wait(&s_empty[r], ((g + 1) & 1u) ^ 1u, ws, 57, r);
+              tc_fence_after_sync();
+              issue_qk(r, g + 1);
+            }
+          }
+          const uint32_t st = smem_u32(sSt + (g & 1) * kAStageBytes);
+          for (int r = 0; r < 2; ++r) {
+            mbar_wait(&p_full[r], g & 1u, ws, 58, r);
+            tc_fence_after_sync();
+            const uint32_t pa = smem_u32(sP + r * kAPBytes);
+            const uint32_t va = st + (r * 2 + 1) * kAKVBytes;
+#pragma unroll
+            for (int k = 0; k < kATile / 16; ++k) {
+              // P: K-major, two k-blocks of 64 keys; V: MN-major, 16 keys = 1024 bytes
+              const uint64_t ad = umma_smem_desc(pa + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024, kSwizzle128);
+              const uint64_t bd = umma_smem_desc(va + k * 1024, 16, 512, kSwizzle64);
+              umma_ss(tO + r * kAD, ad, bd, idesc_pv, (j | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(&pv_done[r]);
+          }
+          umma_commit(&kv_empty[g & 1]);
+        }
+        umma_commit(q_empty);
+        gk += T;
+      }
+    }
+  }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    // ------------------------------------------------------------------ softmax warpgroups
+    const int r_in = (warp - 4) >> 2;  // which of the two rows
+    const int quad = warp & 3;
+    const int qrow = quad * 32 + lane;
+    uint32_t gk = 0;
+    for (int item = blockIdx.x; item < p.num_items; item += gridDim.x) {
+      const int rp = item % p.n_rp;
+      const int tmp = item / p.n_rp;
+      const int qt = tmp % p.n_qt;
+      const int h = tmp / p.n_qt;
+      const int r = rp * 2 + r_in;
+      const int qi = qt * kATile + qrow;
+      float m = kNegBig, l = 0.f;
+      for (int j = 0; j < T; ++j) {
+        const uint32_t g = gk + j;
+        mbar_wait(&s_full[r_in], g & 1u, ws, 59, r_in);
+        tc_fence_after_sync();
+        float t[128];
+        {
+          uint32_t* tu = reinterpret_cast<uint32_t*>(t);
+          const uint32_t ta = tmem_addr(tS, quad, r_in * 128);
+          tmem_ld32(ta, *reinterpret_cast<uint32_t(*)[32]>(tu));
+          tmem_ld32(ta + 32, *reinterpret_cast<uint32_t(*)[32]>(tu + 32));
+          tmem_ld32(ta + 64, *reinterpret_cast<uint32_t(*)[32]>(tu + 64));
+          tmem_ld32(ta + 96, *reinterpret_cast<uint32_t(*)[32]>(tu + 96));
+          tmem_ld_wait();
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_empty[r_in]);
+
+        mbar_wait(&kv_full[g & 1], (g >> 1) & 1u, ws, 60, r_in);
+        if (p.has_bias) {
+          const uint8_t* bs = sSt + (g & 1) * kAStageBytes + 4 * kAKVBytes;
+#pragma unroll
+          for (int c16 = 0; c16 < 16; ++c16) {
+            const uint4 u = *reinterpret_cast<const uint4*>(bs + (c16 >> 3) * 16384 + swz128_offset(qrow, c16 & 7));
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              t[c16 * 8 + 2 * e] += bf16_lo(w[e]);
+              t[c16 * 8 + 2 * e + 1] += bf16_hi(w[e]);
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&kv_empty[g & 1]);
+        if (j == T - 1) {
+          const int valid = p.Nk - j * kATile;
+          if (valid < kATile) {
+#pragma unroll
+            for (int k = 0; k < 128; ++k)
+              if (k >= valid) t[k] = kNegBig;
+          }
+        }
+        float mt = t[0];
+#pragma unroll
+        for (int k = 1; k < 128; ++k) mt = fmaxf(mt, t[k]);
+        const float m_new = fmaxf(m, mt);
+        const float alpha = fast_exp2(m - m_new);
+        float psum = 0.f;
+        uint32_t pk[64];
+#pragma unroll
+        for (int k = 0; k < 128; k += 2) {
+          const float p0 = fast_exp2(t[k] - m_new);
+          const float p1 = fast_exp2(t[k + 1] - m_new);
+          psum += p0 + p1;
+          pk[k >> 1] = pack_bf16x2(p0, p1);
+        }
+        l = l * alpha + psum;
+        m = m_new;
+
+        // previous P.V of this row must be complete: P buffer free, O stable
+        mbar_wait(&pv_done[r_in], (g & 1u) ^ 1u, ws, 61, r_in);
+        tc_fence_after_sync();
+        if (j > 0 && __any_sync(0xffffffffu, alpha < 1.0f)) {
+          uint32_t ov[32];
+          const uint32_t oa = tmem_addr(tO, quad, r_in * kAD);
+          tmem_ld32(oa, ov);
+          tmem_ld_wait();
+#pragma unroll
+          for (int d = 0; d < 32; ++d) ov[d] = __float_as_uint(__uint_as_float(ov[d]) * alpha);
+          tmem_st32(oa, ov);
+          tmem_st_wait();
+        }
+        uint8_t* ps = sP + r_in * kAPBytes;
+#pragma unroll
+        for (int c16 = 0; c16 < 16; ++c16) {
+          const uint4 u = make_uint4(pk[c16 * 4], pk[c16 * 4 + 1], pk[c16 * 4 + 2], pk[c16 * 4 + 3]);
+          *reinterpret_cast<uint4*>(ps + (c16 >> 3) * 16384 + swz128_offset(qrow, c16 & 7)) = u;
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[r_in]);
+      }
+      // ---- epilogue of this (row, head, query tile)
+      mbar_wait(&pv_done[r_in], (gk + T - 1) & 1u, ws, 62, r_in);
+      tc_fence_after_sync();
+      {
+        uint32_t ov[32];
+        tmem_ld32(tmem_addr(tO, quad, r_in * kAD), ov);
+        tmem_ld_wait();
+        if (r < p.rows && qi < p.Nq) {
+          const float inv = 1.0f / l;
+          const long long in_row = static_cast<long long>(r) * p.Nq + qi;
+          const long long out_row = p.transpose_out ? (static_cast<long long>(qi) * p.rows + r) : in_row;
+          float f[32];
+#pragma unroll
+          for (int d = 0; d < 32; ++d) f[d] = __uint_as_float(ov[d]) * inv;
+          if (p.gate != nullptr) {
+            const uint4* gp = reinterpret_cast<const uint4*>(p.gate + in_row * (p.H * kAD) + h * kAD);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const uint4 u = __ldg(gp + c);
+              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                f[c * 8 + 2 * e] *= bf16_lo(w[e]);
+                f[c * 8 + 2 * e + 1] *= bf16_hi(w[e]);
+              }
+            }
+          }
+          uint4* op = reinterpret_cast<uint4*>(p.out + out_row * (p.H * kAD) + h * kAD);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint4 u;
+            u.x = pack_bf16x2(f[c * 8], f[c * 8 + 1]);
+            u.y = pack_bf16x2(f[c * 8 + 2], f[c * 8 + 3]);
+            u.z = pack_bf16x2(f[c * 8 + 4], f[c * 8 + 5]);
+            u.w = pack_bf16x2(f[c * 8 + 6], f[c * 8 + 7]);
+            op[c] = u;
+          }
+        }
+      }
+      tc_fence_before_sync();
+      gk += T;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+constexpr int kASmemBytes = 2 * kAQBytes + kAStages * kAStageBytes + 2 * kAPBytes + 256 + 1024;
+
+}  // namespace ubm
+
+// q, k, v, gate, out: bf16 [rows][N*][H*32] (innermost contiguous; row strides given in elements).
+// bias: bf16 [H][Nq][ldb] (ldb multiple of 8) or null.  q must carry the factor log2(e)/sqrt(32) and
+// bias the factor log2(e).  transpose_out writes out[q][r] instead of out[r][q].
+extern "C" int ubm_attention_d32(const void* q, const void* k, const void* v, const void* bias, const void* gate,
+                                 void* out, int rows, int Nq, int Nk, int H, long long ldb, int transpose_out,
+                                 void* status, void* stream) {
+  using namespace ubm;
+  if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0) return UBM_ERR_ARGUMENT;
+  if (bias != nullptr && (ldb < Nk || (ldb & 7))) return UBM_ERR_ARGUMENT;
+  const uint64_t hd = (uint64_t)H * kAD;
+  CUtensorMap tmQ, tmK, tmV, tmB;
+  {
+    uint64_t d[3] = {hd, (uint64_t)Nq, (uint64_t)rows};
+    uint64_t s[2] = {hd * 2, hd * 2 * (uint64_t)Nq};
+    uint32_t b[3] = {kAD, kATile, 1};
+    int rc = make_tmap(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d, s, b, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc) return rc;
+  }
+  {
+    uint64_t d[3] = {hd, (uint64_t)Nk, (uint64_t)rows};
+    uint64_t s[2] = {hd * 2, hd * 2 * (uint64_t)Nk};
+    uint32_t b[3] = {kAD, kATile, 1};
+    int rc = make_tmap(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d, s, b, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc) return rc;
+    rc = make_tmap(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d, s, b, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc) return rc;
+  }
+  if (bias != nullptr) {
+    uint64_t d[3] = {(uint64_t)Nk, (uint64_t)Nq, (uint64_t)H};
+    uint64_t s[2] = {(uint64_t)ldb * 2, (uint64_t)ldb * 2 * (uint64_t)Nq};
+    uint32_t b[3] = {64, kATile, 1};
+    int rc = make_tmap(&tmB, bias, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d, s, b, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  } else {
+    tmB = tmQ;
+  }
+  AttnParams p = {};
+  p.rows = rows;
+  p.Nq = Nq;
+  p.Nk = Nk;
+  p.H = H;
+  p.gate = static_cast<const __nv_bfloat16*>(gate);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.transpose_out = transpose_out;
+  p.has_bias = bias != nullptr ? 1 : 0;
+  p.status = static_cast<KernelStatus*>(status);
+  p.n_qt = (Nq + kATile - 1) / kATile;
+  p.n_kt = (Nk + kATile - 1) / kATile;
+  p.n_rp = (rows + 1) / 2;
+  p.num_items = p.n_qt * p.n_rp * H;
+  int rc = set_smem(attention_kernel, kASmemBytes);
+  if (rc) return rc;
+  const int grid = p.num_items < sm_count() ? p.num_items : sm_count();
+  attention_kernel<<<grid, 384, kASmemBytes, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmB, p);
+  UBM_CHECK_LAUNCH("attention_kernel");
+  return UBM_OK;
+}

@@ -144,3 +144,87 @@ def trimul_fused(z: torch.Tensor, mask: Optional[torch.Tensor], w: TrimulPacked,
                                      native.ptr(st), stream)
     native.check(rc, "ubm_trimul_out")
     return out
+
+
+# ------------------------------------------------------------------------------------------
+native.declare("ubm_attention_d32", [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_ll, c_int, c_void_p, c_void_p])
+
+LOG2E = 1.4426950408889634
+
+
+@dataclass
+class TriattPacked:
+    w: torch.Tensor          # bf16 [512, 128] rows [q * log2e/sqrt(d); k; v; g], gamma folded
+    colsum: torch.Tensor     # fp32 [512]
+    colbias: torch.Tensor
+    wb: torch.Tensor         # fp32 [H, 128] head-bias weights * gamma * log2e
+    wb_colsum: torch.Tensor  # fp32 [H]
+    wb_colbias: torch.Tensor
+    wo: torch.Tensor         # bf16 [128, 128]
+    bo: Optional[torch.Tensor]
+    heads: int
+
+    @classmethod
+    def pack(cls, ln_w, ln_b, w_bias, w_q, w_k, w_v, w_g, b_g, w_o, b_o, heads: int) -> "TriattPacked":
+        c = w_q.shape[1]
+        if c != 128 or w_q.shape[0] != 128 or heads * 32 != 128:
+            raise ValueError("fused triangle attention supports c_z = 128 and 4 heads of 32")
+        qs = LOG2E / (32 ** 0.5)
+        wq, sq, bq = fold_ln_linear(w_q, ln_w, ln_b, scale=qs)
+        wk, sk, bk = fold_ln_linear(w_k, ln_w, ln_b)
+        wv, sv, bv = fold_ln_linear(w_v, ln_w, ln_b)
+        wg, sg, bg = fold_ln_linear(w_g, ln_w, ln_b, bias=b_g)
+        w = torch.cat([wq, wk, wv, wg], 0).contiguous()
+        colsum = torch.cat([sq, sk, sv, sg]).contiguous()
+        colbias = torch.cat([bq, bk, bv, bg]).contiguous()
+        gam = torch.ones(c, device=w_q.device) if ln_w is None else ln_w.detach().float()
+        wb = (w_bias.detach().float() * gam[None, :] * LOG2E).contiguous()
+        wb_colsum = wb.sum(1).contiguous()
+        wb_colbias = torch.zeros(heads, device=w_q.device)
+        if ln_b is not None:
+            wb_colbias = (w_bias.detach().float() @ ln_b.detach().float()) * LOG2E
+        return cls(w, colsum, colbias, wb, wb_colsum, wb_colbias.contiguous(),
+                   w_o.detach().to(torch.bfloat16).contiguous(),
+                   None if b_o is None else b_o.detach().float().contiguous(), heads)
+
+
+def attention_d32(q, k, v, bias, gate, out, rows: int, Nq: int, Nk: int, H: int, ldb: int = 0,
+                  transpose_out: bool = False):
+    """Raw launch of the tcgen05 attention kernel (see csrc/attention_sm100.cu for the layout)."""
+    st = native.status_tensor(q.device)
+    rc = native.lib().ubm_attention_d32(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(bias),
+                                        native.ptr(gate), native.ptr(out), rows, Nq, Nk, H, ldb,
+                                        1 if transpose_out else 0, native.ptr(st), native.current_stream(q.device))
+    native.check(rc, "ubm_attention_d32")
+    return out
+
+
+def triangle_attention_fused(z: torch.Tensor, w: TriattPacked, starting: bool, residual: bool = True,
+                             out: Optional[torch.Tensor] = None, workspace: Optional[dict] = None) -> torch.Tensor:
+    """z: bf16 [N, N, 128] contiguous (no padding mask).  Three launches: projection (LN folded,
+    q|k|v|gate rows + head bias planes, written at the transposed pair index for the ending
+    node) -> attention -> output projection with residual."""
+    if z.dtype != torch.bfloat16 or z.dim() != 3 or z.shape[-1] != 128 or not z.is_contiguous():
+        raise ValueError("triangle_attention_fused expects a contiguous bf16 [N, N, 128] tensor")
+    N = z.shape[0]
+    Np = ceil_to(N, 8)
+    dev = z.device
+    ws = workspace if workspace is not None else {}
+    key = ("triatt", N, dev)
+    if key not in ws:
+        ws[key] = (torch.empty((5, N * N, 128), dtype=torch.bfloat16, device=dev),
+                   torch.zeros((w.heads, N, Np), dtype=torch.bfloat16, device=dev))
+    qkvgo, hb = ws[key]
+    q, k, v, g, og = qkvgo[0], qkvgo[1], qkvgo[2], qkvgo[3], qkvgo[4]
+    st = native.status_tensor(dev)
+    stream = native.current_stream(dev)
+    rc = native.lib().ubm_triatt_proj(native.ptr(z), native.ptr(w.w), native.ptr(w.colsum), native.ptr(w.colbias),
+                                      native.ptr(w.wb), native.ptr(w.wb_colsum), native.ptr(w.wb_colbias),
+                                      native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(g), native.ptr(hb), 0,
+                                      N, Np, w.heads, 0 if starting else 1, native.ptr(st), stream)
+    native.check(rc, "ubm_triatt_proj")
+    attention_d32(q, k, v, hb, g, og, rows=N, Nq=N, Nk=N, H=w.heads, ldb=Np, transpose_out=not starting)
+    z2 = z.view(N * N, 128)
+    out = torch.empty_like(z) if out is None else out
+    _gemm.gemm(og, w.wo, bias=w.bo, residual=z2 if residual else None, out=out.view(N * N, 128))
+    return out
