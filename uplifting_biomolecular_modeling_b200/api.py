@@ -1,0 +1,190 @@
+"""Public prediction API: ``Predictor(config, mode).predict(features)``.
+
+One object owns a model on one GPU under one mode word:
+
+* ``off``   - the plain PyTorch statements (``ops.reference``), eager.
+* ``exact`` - the same statements, with what is step-invariant hoisted and the sampler step replayed
+              from a CUDA graph: bitwise identical to ``off`` by construction (same kernels, same order).
+* ``fast``  - the fused sm_100a kernels in the pair stack / MSA module / diffusion transformer, plus graphs.
+* ``big``   - ``fast`` plus the memory levers (row-chunked pair ops, released intermediates); with
+              ``n_gpu > 1`` the pair tensor is row-sharded over the ranks (``parallel.rowpair``).
+
+``predict`` takes a feature dict on the host (pinned memory is used for the copy), runs embed ->
+trunk -> sampler -> confidence, and returns host tensors.  It is the call the benchmarks time end to end.
+Mode vocabulary and the no-silent-fallback rule are those of the reference kits (README.md:24-50).
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, Optional
+
+import torch
+
+from .models import cofold
+
+MODES = ("off", "exact", "fast", "big")
+
+
+class NotActive(RuntimeError):
+    """The requested mode cannot engage on this machine (exit code 3 at the CLI)."""
+
+
+def _tree_copy(dst, src) -> None:
+    """Copy every tensor of ``src`` into the tensor at the same place of ``dst`` (dicts / lists / tuples)."""
+    if isinstance(dst, torch.Tensor):
+        dst.copy_(src)
+    elif isinstance(dst, dict):
+        for k in dst:
+            _tree_copy(dst[k], src[k])
+    elif isinstance(dst, (list, tuple)):
+        for d, s_ in zip(dst, src):
+            _tree_copy(d, s_)
+
+
+class Predictor:
+    def __init__(self, config: str = "af3", mode: str = "fast", device: str = "cuda:0",
+                 dtype: torch.dtype = torch.bfloat16, seed: int = 0, use_graphs: Optional[bool] = None,
+                 **overrides):
+        if mode not in MODES:
+            raise ValueError(f"mode {mode!r} not in {MODES}")
+        self.mode, self.device, self.dtype, self.seed = mode, torch.device(device), dtype, seed
+        self.model = cofold.build_model(config, device=self.device, dtype=dtype, seed=seed, **overrides)
+        self.cfg = self.model.cfg
+        self.levers = []
+        if mode in ("fast", "big"):
+            if self.device.type != "cuda":
+                raise NotActive(f"mode {mode} needs a CUDA device (sm_100a); got {self.device}")
+            from .ops import native
+            try:
+                native.lib()
+            except native.NativeUnavailable as e:
+                raise NotActive(f"mode {mode}: {e}") from e
+            n = self.model.set_impl("fused")
+            self.levers.append(f"fused_kernels:{n}")
+        self.use_graphs = (mode != "off" and self.device.type == "cuda") if use_graphs is None else use_graphs
+        self._graph = None
+        self._graph_key = None
+        self._pinned: Dict[str, torch.Tensor] = {}
+        self.last_timing: Dict[str, float] = {}
+
+    # ------------------------------------------------------------------ host <-> device
+    def to_device(self, feats: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        out = {}
+        self.h2d_bytes = 0
+        for k, v in feats.items():
+            if self.device.type == "cuda":
+                pin = self._pinned.get(k)
+                if pin is None or pin.shape != v.shape or pin.dtype != v.dtype:
+                    pin = torch.empty(v.shape, dtype=v.dtype, pin_memory=True)
+                    self._pinned[k] = pin
+                pin.copy_(v)
+                d = pin.to(self.device, non_blocking=True)
+                self.h2d_bytes += v.numel() * v.element_size()
+            else:
+                d = v
+            out[k] = d.to(self.dtype) if d.is_floating_point() else d
+        return out
+
+    # ------------------------------------------------------------------ sampler step graph
+    def _step_fn(self, prep, feats, n_tokens, samples):
+        """Sampler step as a CUDA graph.  The graph is captured once per (tokens, atoms, samples) on the
+        first prediction's step-invariant tensors; later predictions copy theirs into those buffers and
+        replay (capture-once, replay-many; reference: common/opt_core/opt_core/capture/graphs.py:569)."""
+        if not self.use_graphs:
+            return None
+        sm = self.model.structure_module
+        A = feats["ref_pos"].shape[1]
+        key = (n_tokens, A, samples)
+        if self._graph is not None and self._graph_key == key:
+            _tree_copy(self._graph["prep"], prep)
+            self._graph["a2t"].copy_(feats["atom_to_token"][0])
+            return self._graph["fn"]
+        a2t = feats["atom_to_token"][0].clone()
+        static_x = torch.zeros((samples, A, 3), device=self.device)
+        static_s = torch.zeros(3, device=self.device)
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                sm.step(static_x, static_s[0] + 1.0, static_s[1] + 0.5, static_s[2], prep, a2t, n_tokens)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        from .ops import native
+        before = native.launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            static_out = sm.step(static_x, static_s[0], static_s[1], static_s[2], prep, a2t, n_tokens)
+        per_replay = native.launch_count() - before      # kernels of this library inside one replay
+
+        def fn(x, sig_tm, sig_t, gamma):
+            static_x.copy_(x)
+            static_s[0].copy_(sig_tm)
+            static_s[1].copy_(sig_t)
+            static_s[2].copy_(gamma)
+            graph.replay()
+            if per_replay:
+                native.add_launches(per_replay)
+            return static_out
+
+        self._graph = {"graph": graph, "prep": prep, "a2t": a2t, "fn": fn}
+        self._graph_key = key
+        return fn
+
+    # ------------------------------------------------------------------ one prediction
+    @torch.no_grad()
+    def predict(self, feats_host: Dict[str, torch.Tensor], recycles: Optional[int] = None,
+                samples: Optional[int] = None, steps: Optional[int] = None, confidence: bool = True,
+                seed: Optional[int] = None) -> Dict[str, torch.Tensor]:
+        m = self.model
+        dev = self.device
+        if dev.type == "cuda":
+            torch.cuda.manual_seed(self.seed if seed is None else seed)
+        else:
+            torch.manual_seed(self.seed if seed is None else seed)
+        import os
+        timing = os.environ.get("UBM_STAGE_TIMES") == "1" and dev.type == "cuda"
+        marks = []
+
+        def mark(name):
+            if timing:
+                torch.cuda.synchronize(dev)
+                marks.append((name, time.perf_counter()))
+
+        mark("start")
+        feats = self.to_device(feats_host)
+        s_inputs, s_init, z_init, atom_c, atom_p = m.embed(feats)
+        mark("embed")
+        s, z = m.trunk(feats, s_inputs, s_init, z_init, recycles)
+        mark("trunk")
+        N = s.shape[1]
+        nsamp = samples or self.cfg.samples
+        sm = m.structure_module
+        prep = sm.score_model.prepare(s, s_inputs, m.z_cond_norm(z), atom_c, atom_c, atom_p, m.fused)
+        step_fn = self._step_fn(prep, feats, N, nsamp)
+        # the sampler's random stream starts here in every mode (graph warm-up / capture draw numbers too)
+        if dev.type == "cuda":
+            torch.cuda.manual_seed(self.seed if seed is None else seed)
+        else:
+            torch.manual_seed(self.seed if seed is None else seed)
+        mark("sampler_setup")
+        x, _ = m.structure(feats, s, z, s_inputs, atom_c, atom_p, nsamp, steps, None, step_fn, prep)
+        mark("sampler")
+        out = {"coords": x}
+        if confidence:
+            rep = feats["token_rep_atom"][0]
+            conf = m.confidence_module(s, z, x[:1, rep].to(s.dtype))
+            p = torch.softmax(conf["plddt_logits"].float(), -1)
+            out["plddt"] = (p * (torch.arange(50, device=p.device) + 0.5) / 50).sum(-1)
+            pae = torch.softmax(conf["pae_logits"].float(), -1)
+            out["pae_mean"] = (pae * (torch.arange(64, device=p.device) + 0.5) * 0.5).sum(-1).mean()
+        host = {k: v.float().cpu() for k, v in out.items()}
+        mark("confidence_and_copy")
+        if timing:
+            self.last_timing = {marks[i][0]: round((marks[i][1] - marks[i - 1][1]) * 1e3, 2)
+                                for i in range(1, len(marks))}
+            import sys
+            print(f"[ubm] STAGES ms {self.last_timing}", file=sys.stderr, flush=True)
+        self.d2h_bytes = sum(v.numel() * 4 for v in host.values())
+        if dev.type == "cuda" and m.fused:
+            from .ops import native
+            native.raise_on_status(dev, "predict")
+        return host

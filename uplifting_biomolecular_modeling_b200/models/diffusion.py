@@ -1,0 +1,357 @@
+"""Diffusion module (AF3 / Boltz-2 family) and its sampler.
+
+Structure and names follow Boltz-2 (boltz2/stock/src/boltz/model/modules/diffusionv2.py:38-115
+``single_conditioner, atom_attention_encoder, s_to_a_linear, token_transformer, a_norm,
+atom_attention_decoder``; transformersv2.py:17-227 ``DiffusionTransformerLayer`` = ``adaln,
+pair_bias_attn, output_projection, transition``; windows of 32 queries x 128 keys,
+diffusionv2.py:44-56).  The sampler is the EDM roll-out of ``AtomDiffusion.sample``
+(diffusionv2.py:295-396): per step a random rigid augmentation, noise injection, one denoiser
+call over all samples, an Euler update.
+
+What is step-invariant is computed once per prediction and reused by all steps: the pair biases of
+the 24 token-transformer layers, the atom-pair biases of the 6 atom layers, and every
+conditioning projection of s (the reference's ``apb_hoist`` / ``atom_hoist`` / ``dit_hoist``
+levers, common/opt_core/opt_core/of3_sampler/atom_hoist.py, of3_trunk/apb_hoist.py).
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops import reference as R
+from .pairformer import AttentionPairBias, _Switchable
+
+
+class AdaLN(nn.Module):
+    def __init__(self, dim: int, dim_s: int):
+        super().__init__()
+        self.a_norm = nn.LayerNorm(dim, elementwise_affine=False)
+        self.s_norm = nn.LayerNorm(dim_s, bias=False)
+        self.s_scale = nn.Linear(dim_s, dim)
+        self.s_bias = nn.Linear(dim_s, dim, bias=False)
+
+    def cond(self, s):
+        sn = self.s_norm(s)
+        return self.s_scale(sn), self.s_bias(sn)
+
+    def forward(self, a, s=None, cond=None, fused: bool = False):
+        scale, shift = self.cond(s) if cond is None else cond
+        if fused and a.is_cuda and a.dtype == torch.bfloat16:
+            from ..ops import rows
+            return rows.adaln_rows(a.contiguous(), scale.contiguous(), shift.contiguous())
+        return torch.sigmoid(scale) * self.a_norm(a) + shift
+
+
+class ConditionedTransitionBlock(nn.Module):
+    def __init__(self, dim: int, dim_s: int, expansion: int = 2):
+        super().__init__()
+        self.adaln = AdaLN(dim, dim_s)
+        hidden = dim * expansion
+        self.swish_gated = nn.Linear(dim, 2 * hidden, bias=False)
+        self.a_to_b = nn.Linear(dim, hidden, bias=False)
+        self.b_to_a = nn.Linear(hidden, dim, bias=False)
+        self.output_projection = nn.Linear(dim_s, dim)
+        nn.init.constant_(self.output_projection.bias, -2.0)
+
+    def forward(self, a, s=None, cond=None, gate=None, fused: bool = False):
+        x = self.adaln(a, s, cond, fused)
+        sg = self.swish_gated(x)
+        u, g = sg.chunk(2, dim=-1)
+        b = F.silu(u) * g * self.a_to_b(x)
+        gate = self.output_projection(s) if gate is None else gate
+        return torch.sigmoid(gate) * self.b_to_a(b)
+
+
+class DiffusionTransformerLayer(_Switchable):
+    def __init__(self, dim: int = 768, dim_s: int = 768, heads: int = 16):
+        super().__init__()
+        self.adaln = AdaLN(dim, dim_s)
+        self.pair_bias_attn = AttentionPairBias(dim, 128, heads, compute_pair_bias=False)
+        self.output_projection_linear = nn.Linear(dim_s, dim)
+        nn.init.constant_(self.output_projection_linear.bias, -2.0)
+        self.transition = ConditionedTransitionBlock(dim, dim_s)
+        self.dim, self.heads = dim, heads
+
+    def hoist(self, s):
+        """Everything that depends only on the conditioning s (same for every layer call of a step)."""
+        return {"adaln": self.adaln.cond(s), "gate": self.output_projection_linear(s),
+                "t_adaln": self.transition.adaln.cond(s), "t_gate": self.transition.output_projection(s)}
+
+    def forward(self, a, s, bias, mask=None, multiplicity: int = 1, hoisted: Optional[dict] = None,
+                window: Optional[tuple] = None):
+        fused = self.impl == "fused"
+        h = hoisted if hoisted is not None else self.hoist(s)
+        b = self.adaln(a, None, h["adaln"], fused)
+        if window is None:
+            b = self.pair_bias_attn(b, None, mask, bias=bias, multiplicity=multiplicity)
+        else:
+            b = _window_attention(self.pair_bias_attn, b, bias, window)
+        a = a + torch.sigmoid(h["gate"]) * b
+        a = a + self.transition(a, None, h["t_adaln"], h["t_gate"], fused)
+        return a
+
+
+def _window_attention(attn: AttentionPairBias, x, bias, window):
+    """Atom attention in (wq, wk) windows; bias: [B, H, nw, wq, wk]."""
+    wq, wk = window
+    B, A, _ = x.shape
+    H, D = attn.heads, attn.head_dim
+    q = attn.proj_q(x).view(B, A, H, D).transpose(1, 2)
+    k = attn.proj_k(x).view(B, A, H, D).transpose(1, 2)
+    v = attn.proj_v(x).view(B, A, H, D).transpose(1, 2)
+    g = torch.sigmoid(attn.proj_g(x))
+    bb = bias
+    if bb is not None and bb.shape[0] != B:
+        bb = bb.repeat_interleave(B // bb.shape[0], 0)
+    o = R.window_attention(q, k, v, bb, wq, wk)
+    o = o.transpose(1, 2).reshape(B, A, H * D)
+    return attn.proj_o(g * o)
+
+
+class DiffusionTransformer(nn.Module):
+    def __init__(self, depth: int, dim: int, dim_s: int, heads: int):
+        super().__init__()
+        self.layers = nn.ModuleList([DiffusionTransformerLayer(dim, dim_s, heads) for _ in range(depth)])
+
+    def forward(self, a, s, biases, mask=None, multiplicity=1, hoisted=None, window=None):
+        for i, layer in enumerate(self.layers):
+            a = layer(a, s, biases[i], mask, multiplicity, None if hoisted is None else hoisted[i], window)
+        return a
+
+
+class FourierEmbedding(nn.Module):
+    def __init__(self, dim: int = 256):
+        super().__init__()
+        self.proj = nn.Linear(1, dim)
+        for p in self.proj.parameters():
+            p.requires_grad_(False)
+        nn.init.normal_(self.proj.weight)
+        nn.init.normal_(self.proj.bias)
+
+    def forward(self, t):
+        x = F.linear(t.float().unsqueeze(-1), self.proj.weight.float(), self.proj.bias.float())
+        return torch.cos(2 * math.pi * x)
+
+
+class SingleConditioning(nn.Module):
+    def __init__(self, c_s: int = 384, c_s_inputs: int = 384, dim_fourier: int = 256, sigma_data: float = 16.0):
+        super().__init__()
+        from .pairformer import Transition
+        d = c_s + c_s_inputs
+        self.sigma_data = sigma_data
+        self.norm_single = nn.LayerNorm(d)
+        self.single_embed = nn.Linear(d, 2 * c_s)
+        self.fourier_embed = FourierEmbedding(dim_fourier)
+        self.norm_fourier = nn.LayerNorm(dim_fourier)
+        self.fourier_to_single = nn.Linear(dim_fourier, 2 * c_s, bias=False)
+        self.transitions = nn.ModuleList([Transition(2 * c_s, 4 * c_s) for _ in range(2)])
+
+    def static_part(self, s_trunk, s_inputs):
+        return self.single_embed(self.norm_single(torch.cat([s_trunk, s_inputs], dim=-1)))
+
+    def forward(self, times, static):
+        """times: [B] (c_noise); static: [1, N, 2c_s] from :meth:`static_part`."""
+        f = self.fourier_to_single(self.norm_fourier(self.fourier_embed(times).to(static.dtype)))
+        s = static + f[:, None, :]
+        for t in self.transitions:
+            s = s + t(s)
+        return s
+
+
+_SEG_CACHE: dict = {}
+
+
+def segment_mean(t: torch.Tensor, atom_to_token: torch.Tensor, n_tokens: int) -> torch.Tensor:
+    """Mean of atom rows per token, deterministic (no atomics): atoms of a token are gathered through
+    a padded [N, M] index table built once per atom layout.  t: [B, A, C] -> [B, N, C].
+    Reference kernel with the same job: _seg_reduce_kernel (common/opt_core/opt_core/kernels/dtk_kernels.py)."""
+    key = (atom_to_token.data_ptr(), atom_to_token.shape[0], n_tokens, str(t.device))
+    tab = _SEG_CACHE.get(key)
+    if tab is None:
+        a2t = atom_to_token.detach().cpu()
+        counts = torch.bincount(a2t, minlength=n_tokens)
+        M = int(counts.max().item())
+        order = torch.argsort(a2t, stable=True)
+        starts = torch.cumsum(counts, 0) - counts
+        idx = starts[:, None] + torch.arange(M)[None, :]
+        valid = torch.arange(M)[None, :] < counts[:, None]
+        idx = order[idx.clamp(max=a2t.shape[0] - 1)]
+        tab = (idx.to(t.device), valid.to(t.device), counts.clamp(min=1).to(t.device))
+        if len(_SEG_CACHE) > 64:
+            _SEG_CACHE.clear()
+        _SEG_CACHE[key] = tab
+    idx, valid, counts = tab
+    g = t[:, idx]                                              # [B, N, M, C]
+    g = g * valid[None, :, :, None].to(t.dtype)
+    return (g.float().sum(2) / counts[None, :, None].float()).to(t.dtype)
+
+
+class AtomEncoderDecoderBase(nn.Module):
+    def __init__(self, c_atom: int, c_token: int, depth: int, heads: int):
+        super().__init__()
+        self.c_atom = c_atom
+        self.atom_transformer = DiffusionTransformer(depth, c_atom, c_atom, heads)
+
+
+class AtomAttentionEncoder(AtomEncoderDecoderBase):
+    def __init__(self, c_atom: int = 128, c_token: int = 768, depth: int = 3, heads: int = 4, structure: bool = True):
+        super().__init__(c_atom, c_token, depth, heads)
+        self.structure = structure
+        if structure:
+            self.r_to_q_trans = nn.Linear(3, c_atom, bias=False)
+        self.atom_to_token_trans = nn.Sequential(nn.Linear(c_atom, c_token, bias=False), nn.ReLU())
+
+    def forward(self, q0, c, biases, r, atom_to_token, n_tokens, hoisted=None, window=(32, 128)):
+        """q0, c: [1, A, c_atom]; r: [B, A, 3]; atom_to_token: [A] long.  Returns (a [B, N, c_token], q, c)."""
+        B = r.shape[0]
+        q = q0.expand(B, -1, -1)
+        if self.structure:
+            q = q + self.r_to_q_trans(r.to(q0.dtype))
+        q = self.atom_transformer(q, c, biases, hoisted=hoisted, window=window)
+        t = self.atom_to_token_trans(q)
+        a = segment_mean(t, atom_to_token, n_tokens)
+        return a, q
+
+
+class AtomAttentionDecoder(AtomEncoderDecoderBase):
+    def __init__(self, c_atom: int = 128, c_token: int = 768, depth: int = 3, heads: int = 4):
+        super().__init__(c_atom, c_token, depth, heads)
+        self.a_to_q_trans = nn.Linear(c_token, c_atom, bias=False)
+        self.atom_feat_to_atom_pos_update = nn.Sequential(nn.LayerNorm(c_atom), nn.Linear(c_atom, 3, bias=False))
+
+    def forward(self, a, q, c, biases, atom_to_token, hoisted=None, window=(32, 128)):
+        q = q + self.a_to_q_trans(a)[:, atom_to_token]
+        q = self.atom_transformer(q, c, biases, hoisted=hoisted, window=window)
+        return self.atom_feat_to_atom_pos_update(q)
+
+
+class DiffusionModule(nn.Module):
+    """Denoiser network: atoms -> tokens -> 24-block token transformer -> atoms."""
+
+    def __init__(self, c_s: int = 384, c_z: int = 128, c_atom: int = 128, c_atompair: int = 16,
+                 token_depth: int = 24, token_heads: int = 16, atom_depth: int = 3, atom_heads: int = 4,
+                 wq: int = 32, wk: int = 128, sigma_data: float = 16.0):
+        super().__init__()
+        self.c_token = 2 * c_s
+        self.window = (wq, wk)
+        self.sigma_data = sigma_data
+        self.single_conditioner = SingleConditioning(c_s, c_s, sigma_data=sigma_data)
+        self.atom_attention_encoder = AtomAttentionEncoder(c_atom, self.c_token, atom_depth, atom_heads)
+        self.s_to_a_linear = nn.Sequential(nn.LayerNorm(2 * c_s), nn.Linear(2 * c_s, self.c_token, bias=False))
+        self.token_transformer = DiffusionTransformer(token_depth, self.c_token, 2 * c_s, token_heads)
+        self.a_norm = nn.LayerNorm(self.c_token)
+        self.atom_attention_decoder = AtomAttentionDecoder(c_atom, self.c_token, atom_depth, atom_heads)
+        # producers of the step-invariant biases
+        self.token_pair_bias = nn.ModuleList(
+            [nn.Sequential(nn.LayerNorm(c_z), nn.Linear(c_z, token_heads, bias=False)) for _ in range(token_depth)])
+        self.atom_enc_pair_bias = nn.ModuleList(
+            [nn.Sequential(nn.LayerNorm(c_atompair), nn.Linear(c_atompair, atom_heads, bias=False))
+             for _ in range(atom_depth)])
+        self.atom_dec_pair_bias = nn.ModuleList(
+            [nn.Sequential(nn.LayerNorm(c_atompair), nn.Linear(c_atompair, atom_heads, bias=False))
+             for _ in range(atom_depth)])
+
+    # ---- once per prediction
+    def prepare(self, s_trunk, s_inputs, z_cond, atom_q, atom_c, atom_pair, fused: bool = False) -> Dict:
+        """Step-invariant tensors.  z_cond: [1, N, N, c_z]; atom_pair: [1, nw, wq, wk, c_atompair]."""
+        if fused and z_cond.is_cuda and z_cond.dtype == torch.bfloat16 and z_cond.shape[-1] == 128:
+            from ..ops import rows
+            tb = [rows.pair_head_bias(z_cond[0].contiguous(), m[0].weight, m[0].bias, m[1].weight).unsqueeze(0)
+                  for m in self.token_pair_bias]
+        else:
+            tb = [m(z_cond).permute(0, 3, 1, 2) for m in self.token_pair_bias]
+        eb = [m(atom_pair).permute(0, 4, 1, 2, 3) for m in self.atom_enc_pair_bias]
+        db = [m(atom_pair).permute(0, 4, 1, 2, 3) for m in self.atom_dec_pair_bias]
+        enc_h = [l.hoist(atom_c) for l in self.atom_attention_encoder.atom_transformer.layers]
+        dec_h = [l.hoist(atom_c) for l in self.atom_attention_decoder.atom_transformer.layers]
+        return {"token_bias": tb, "enc_bias": eb, "dec_bias": db, "enc_hoist": enc_h, "dec_hoist": dec_h,
+                "s_static": self.single_conditioner.static_part(s_trunk, s_inputs), "atom_q": atom_q,
+                "atom_c": atom_c}
+
+    # ---- once per step
+    def forward(self, r_noisy, times, prep: Dict, atom_to_token, n_tokens: int):
+        """r_noisy: [B, A, 3] (already scaled by c_in); times: [B] = c_noise.  Returns r_update [B, A, 3]."""
+        B = r_noisy.shape[0]
+        r_noisy = r_noisy.to(prep["atom_q"].dtype)
+        s = self.single_conditioner(times, prep["s_static"])                       # [B, N, 2c_s]
+        a, q = self.atom_attention_encoder(prep["atom_q"], prep["atom_c"], prep["enc_bias"], r_noisy,
+                                           atom_to_token, n_tokens, prep["enc_hoist"], self.window)
+        a = a + self.s_to_a_linear(s)
+        a = self.token_transformer(a, s, prep["token_bias"], None, multiplicity=B)
+        a = self.a_norm(a)
+        return self.atom_attention_decoder(a, q, prep["atom_c"], prep["dec_bias"], atom_to_token,
+                                           prep["dec_hoist"], self.window)
+
+
+def edm_schedule(num_steps: int, sigma_min=0.0004, sigma_max=160.0, sigma_data=16.0, rho=7.0, device=None):
+    inv = 1.0 / rho
+    steps = torch.arange(num_steps, device=device, dtype=torch.float32)
+    sig = sigma_data * (sigma_max ** inv + steps / (num_steps - 1) * (sigma_min ** inv - sigma_max ** inv)) ** rho
+    return F.pad(sig, (0, 1), value=0.0)
+
+
+def random_rigid(batch: int, device, generator=None, s_trans: float = 1.0):
+    """Uniform random rotations (from normalised quaternions) and Gaussian translations."""
+    qd = torch.randn((batch, 4), device=device, generator=generator)
+    qd = qd / qd.norm(dim=-1, keepdim=True)
+    w, x, y, z = qd.unbind(-1)
+    Rm = torch.stack([1 - 2 * (y * y + z * z), 2 * (x * y - z * w), 2 * (x * z + y * w),
+                      2 * (x * y + z * w), 1 - 2 * (x * x + z * z), 2 * (y * z - x * w),
+                      2 * (x * z - y * w), 2 * (y * z + x * w), 1 - 2 * (x * x + y * y)], -1).view(batch, 3, 3)
+    t = torch.randn((batch, 1, 3), device=device, generator=generator) * s_trans
+    return Rm, t
+
+
+class AtomDiffusion(nn.Module):
+    """EDM preconditioning + sampler around :class:`DiffusionModule`."""
+
+    def __init__(self, score_model: DiffusionModule, num_steps: int = 200, gamma_0: float = 0.8,
+                 gamma_min: float = 1.0, noise_scale: float = 1.003, step_scale: float = 1.5):
+        super().__init__()
+        self.score_model = score_model
+        self.num_steps, self.gamma_0, self.gamma_min = num_steps, gamma_0, gamma_min
+        self.noise_scale, self.step_scale = noise_scale, step_scale
+        self.sigma_data = score_model.sigma_data
+
+    def denoise(self, x_noisy, sigma, prep, atom_to_token, n_tokens):
+        """Preconditioned network output D(x; sigma).  sigma: [B]."""
+        sd = self.sigma_data
+        s2 = sigma[:, None, None]
+        c_in = 1.0 / torch.sqrt(s2 ** 2 + sd ** 2)
+        c_skip = sd ** 2 / (s2 ** 2 + sd ** 2)
+        c_out = s2 * sd / torch.sqrt(s2 ** 2 + sd ** 2)
+        c_noise = torch.log(sigma / sd) * 0.25
+        upd = self.score_model(x_noisy * c_in, c_noise, prep, atom_to_token, n_tokens)
+        return c_skip * x_noisy + c_out * upd.float()
+
+    def step(self, x, sigma_tm, sigma_t, gamma, prep, atom_to_token, n_tokens, generator=None):
+        """One sampler step for all samples.  x: [B, A, 3] fp32."""
+        B = x.shape[0]
+        x = x - x.mean(dim=1, keepdim=True)
+        Rm, t = random_rigid(B, x.device, generator)
+        x = torch.einsum("bij,baj->bai", Rm, x) + t
+        t_hat = sigma_tm * (1.0 + gamma)
+        eps = self.noise_scale * torch.sqrt(torch.clamp(t_hat ** 2 - sigma_tm ** 2, min=0.0)) * \
+            torch.randn(x.shape, device=x.device, generator=generator)
+        x_noisy = x + eps
+        den = self.denoise(x_noisy, t_hat.expand(B), prep, atom_to_token, n_tokens)
+        d = (x_noisy - den) / t_hat
+        return x_noisy + self.step_scale * (sigma_t - t_hat) * d
+
+    @torch.no_grad()
+    def sample(self, prep, atom_to_token, n_tokens: int, n_atoms: int, multiplicity: int = 1, num_steps=None,
+               generator=None, step_fn=None):
+        """Roll the sampler out; ``step_fn`` (a captured CUDA graph wrapper) may replace :meth:`step`."""
+        dev = prep["atom_q"].device
+        steps = num_steps or self.num_steps
+        sig = edm_schedule(steps, sigma_data=self.sigma_data, device=dev)
+        gammas = torch.where(sig > self.gamma_min, torch.full_like(sig, self.gamma_0), torch.zeros_like(sig))
+        x = sig[0] * torch.randn((multiplicity, n_atoms, 3), device=dev, generator=generator)
+        fn = step_fn or (lambda x_, a_, b_, g_: self.step(x_, a_, b_, g_, prep, atom_to_token, n_tokens, generator))
+        for i in range(steps):
+            x = fn(x, sig[i], sig[i + 1], gammas[i + 1])
+        return x

@@ -1,0 +1,275 @@
+"""Pairformer stack (AF3 / Boltz-2 family) with the upstream parameter names.
+
+Module and parameter names follow Boltz-2 so its checkpoints load unchanged
+(boltz2/stock/src/boltz/model/layers/pairformer.py:41-62 ``pre_norm_s, attention, tri_mul_out,
+tri_mul_in, tri_att_start, tri_att_end, transition_s, transition_z``; triangular_mult.py:49-54;
+transition.py; attentionv2.py; triangular_attention/attention.py:44-50).  Every module has two
+forwards: the plain statement (``ops.reference``, the ``off`` path and the CPU oracle) and the
+fused sm_100a path (``ops.pair``) that a mode's levers switch on per module through
+:func:`set_impl`.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops import reference as R
+
+IMPLS = ("reference", "fused")
+
+
+class _Switchable(nn.Module):
+    """A module with a per-instance implementation word and a lazily packed weight cache."""
+
+    impl: str = "reference"
+
+    def __init__(self):
+        super().__init__()
+        self.impl = "reference"
+        self._packed = None
+        self._workspace: Optional[dict] = None
+
+    def set_impl(self, impl: str, workspace: Optional[dict] = None):
+        if impl not in IMPLS:
+            raise ValueError(f"impl {impl!r} not in {IMPLS}")
+        self.impl = impl
+        self._packed = None
+        self._workspace = workspace
+
+    def _fusable(self, z: torch.Tensor) -> bool:
+        return (self.impl == "fused" and z.is_cuda and z.dtype == torch.bfloat16 and z.shape[-1] == 128)
+
+
+class Transition(_Switchable):
+    """SwiGLU transition: ``fc3(silu(fc1 n) * fc2 n)``, n = LN(x)."""
+
+    def __init__(self, dim: int, hidden: Optional[int] = None, out_dim: Optional[int] = None):
+        super().__init__()
+        hidden = hidden or 4 * dim
+        out_dim = out_dim or dim
+        self.norm = nn.LayerNorm(dim, eps=1e-5)
+        self.fc1 = nn.Linear(dim, hidden, bias=False)
+        self.fc2 = nn.Linear(dim, hidden, bias=False)
+        self.fc3 = nn.Linear(hidden, out_dim, bias=False)
+        self.dim, self.hidden, self.out_dim = dim, hidden, out_dim
+
+    def forward(self, x: torch.Tensor, residual: bool = False) -> torch.Tensor:
+        if self._fusable(x) and self.dim == 128 and self.out_dim == 128 and self.hidden % 64 == 0 \
+                and self.hidden <= 1024:
+            from ..ops import pair
+            if self._packed is None:
+                self._packed = pair.TransitionPacked.pack(self.norm.weight, self.norm.bias, self.fc1.weight,
+                                                          self.fc2.weight, self.fc3.weight)
+            return pair.transition_fused(x.contiguous(), self._packed, residual=residual)
+        return R.transition(x, self.norm.weight, self.norm.bias, self.fc1.weight, self.fc2.weight, self.fc3.weight,
+                            residual=residual)
+
+
+class TriangleMultiplication(_Switchable):
+    def __init__(self, dim: int = 128, outgoing: bool = True):
+        super().__init__()
+        self.outgoing = outgoing
+        self.norm_in = nn.LayerNorm(dim, eps=1e-5)
+        self.p_in = nn.Linear(dim, 2 * dim, bias=False)
+        self.g_in = nn.Linear(dim, 2 * dim, bias=False)
+        self.norm_out = nn.LayerNorm(dim)
+        self.p_out = nn.Linear(dim, dim, bias=False)
+        self.g_out = nn.Linear(dim, dim, bias=False)
+
+    def forward(self, z: torch.Tensor, mask: Optional[torch.Tensor], residual: bool = False) -> torch.Tensor:
+        if self._fusable(z) and z.shape[0] == 1:
+            from ..ops import pair
+            if self._packed is None:
+                self._packed = pair.TrimulPacked.pack(self.norm_in.weight, self.norm_in.bias, self.p_in.weight,
+                                                      self.g_in.weight, self.norm_out.weight, self.norm_out.bias,
+                                                      self.p_out.weight, self.g_out.weight)
+            m = None if mask is None else mask[0]
+            out = pair.trimul_fused(z[0].contiguous(), m, self._packed, self.outgoing, residual=residual,
+                                    workspace=self._workspace)
+            return out.unsqueeze(0)
+        return R.triangle_multiplication(z, mask, self.norm_in.weight, self.norm_in.bias, self.p_in.weight,
+                                         self.g_in.weight, self.norm_out.weight, self.norm_out.bias,
+                                         self.p_out.weight, self.g_out.weight, outgoing=self.outgoing,
+                                         residual=residual)
+
+
+class TriangleMultiplicationOutgoing(TriangleMultiplication):
+    def __init__(self, dim: int = 128):
+        super().__init__(dim, outgoing=True)
+
+
+class TriangleMultiplicationIncoming(TriangleMultiplication):
+    def __init__(self, dim: int = 128):
+        super().__init__(dim, outgoing=False)
+
+
+class _MHA(nn.Module):
+    """Parameter holder with the OpenFold attention names used by Boltz-2's triangle attention."""
+
+    def __init__(self, c_in: int, c_hidden: int, heads: int):
+        super().__init__()
+        self.linear_q = nn.Linear(c_in, c_hidden * heads, bias=False)
+        self.linear_k = nn.Linear(c_in, c_hidden * heads, bias=False)
+        self.linear_v = nn.Linear(c_in, c_hidden * heads, bias=False)
+        self.linear_o = nn.Linear(c_hidden * heads, c_in)
+        self.linear_g = nn.Linear(c_in, c_hidden * heads)
+
+
+class TriangleAttention(_Switchable):
+    def __init__(self, c_in: int = 128, c_hidden: int = 32, heads: int = 4, starting: bool = True):
+        super().__init__()
+        self.starting, self.heads, self.c_hidden = starting, heads, c_hidden
+        self.layer_norm = nn.LayerNorm(c_in)
+        self.linear = nn.Linear(c_in, heads, bias=False)
+        self.mha = _MHA(c_in, c_hidden, heads)
+
+    def forward(self, z: torch.Tensor, mask: Optional[torch.Tensor] = None, residual: bool = False) -> torch.Tensor:
+        m = self.mha
+        if self._fusable(z) and z.shape[0] == 1 and mask is None and self.heads == 4 and self.c_hidden == 32:
+            from ..ops import pair
+            if self._packed is None:
+                self._packed = pair.TriattPacked.pack(self.layer_norm.weight, self.layer_norm.bias,
+                                                      self.linear.weight, m.linear_q.weight, m.linear_k.weight,
+                                                      m.linear_v.weight, m.linear_g.weight, m.linear_g.bias,
+                                                      m.linear_o.weight, m.linear_o.bias, self.heads)
+            out = pair.triangle_attention_fused(z[0].contiguous(), self._packed, self.starting, residual=residual,
+                                                workspace=self._workspace)
+            return out.unsqueeze(0)
+        outs = [R.triangle_attention(z[b], None if mask is None else mask[b], self.layer_norm.weight,
+                                     self.layer_norm.bias, self.linear.weight, m.linear_q.weight, m.linear_k.weight,
+                                     m.linear_v.weight, m.linear_g.weight, m.linear_g.bias, m.linear_o.weight,
+                                     m.linear_o.bias, self.heads, starting=self.starting, residual=residual)
+                for b in range(z.shape[0])]
+        return torch.stack(outs, 0)
+
+
+class TriangleAttentionStartingNode(TriangleAttention):
+    def __init__(self, c_in=128, c_hidden=32, heads=4):
+        super().__init__(c_in, c_hidden, heads, starting=True)
+
+
+class TriangleAttentionEndingNode(TriangleAttention):
+    def __init__(self, c_in=128, c_hidden=32, heads=4):
+        super().__init__(c_in, c_hidden, heads, starting=False)
+
+
+class AttentionPairBias(_Switchable):
+    """Single-representation attention with a bias projected from the pair tensor."""
+
+    def __init__(self, c_s: int = 384, c_z: int = 128, heads: int = 16, compute_pair_bias: bool = True):
+        super().__init__()
+        self.c_s, self.heads = c_s, heads
+        self.head_dim = c_s // heads
+        self.proj_q = nn.Linear(c_s, c_s)
+        self.proj_k = nn.Linear(c_s, c_s, bias=False)
+        self.proj_v = nn.Linear(c_s, c_s, bias=False)
+        self.proj_g = nn.Linear(c_s, c_s, bias=False)
+        self.compute_pair_bias = compute_pair_bias
+        if compute_pair_bias:
+            self.proj_z = nn.Sequential(nn.LayerNorm(c_z), nn.Linear(c_z, heads, bias=False))
+        self.proj_o = nn.Linear(c_s, c_s, bias=False)
+
+    def pair_bias(self, z: torch.Tensor) -> torch.Tensor:
+        """[B, H, N, N] bias from the pair tensor."""
+        if self._fusable(z) and z.shape[0] == 1:
+            from ..ops import rows
+            return rows.pair_head_bias(z[0], self.proj_z[0].weight, self.proj_z[0].bias,
+                                       self.proj_z[1].weight).unsqueeze(0)
+        return self.proj_z[1](self.proj_z[0](z)).permute(0, 3, 1, 2)
+
+    def forward(self, s: torch.Tensor, z: Optional[torch.Tensor], mask: Optional[torch.Tensor],
+                bias: Optional[torch.Tensor] = None, k_in: Optional[torch.Tensor] = None,
+                multiplicity: int = 1) -> torch.Tensor:
+        """s: [B*mult, N, c_s] already normalised by the caller; bias (if given) replaces proj_z(z)."""
+        B, N, _ = s.shape
+        kin = s if k_in is None else k_in
+        if bias is None:
+            bias = self.pair_bias(z)
+        H, D = self.heads, self.head_dim
+        q = self.proj_q(s).view(B, N, H, D).transpose(1, 2)
+        k = self.proj_k(kin).view(B, kin.shape[1], H, D).transpose(1, 2)
+        v = self.proj_v(kin).view(B, kin.shape[1], H, D).transpose(1, 2)
+        g = torch.sigmoid(self.proj_g(s))
+        b = bias[..., : kin.shape[1]].float()
+        if multiplicity > 1:
+            b = b.repeat_interleave(multiplicity, 0)
+        if mask is not None:
+            mm = mask if multiplicity == 1 else mask.repeat_interleave(multiplicity, 0)
+            b = b + ((1.0 - mm.float()) * -1e6)[:, None, None, :]
+        o = R.attention_with_bias(q, k, v, b)
+        o = o.transpose(1, 2).reshape(B, N, H * D)
+        return self.proj_o(g * o)
+
+
+class PairformerLayer(nn.Module):
+    def __init__(self, c_s: int = 384, c_z: int = 128, heads: int = 16, pair_heads: int = 4, no_seq: bool = False,
+                 transition_n: int = 4):
+        super().__init__()
+        self.no_seq = no_seq
+        if not no_seq:
+            self.pre_norm_s = nn.LayerNorm(c_s)
+            self.attention = AttentionPairBias(c_s, c_z, heads)
+            self.transition_s = Transition(c_s, c_s * transition_n)
+        self.tri_mul_out = TriangleMultiplicationOutgoing(c_z)
+        self.tri_mul_in = TriangleMultiplicationIncoming(c_z)
+        self.tri_att_start = TriangleAttentionStartingNode(c_z, c_z // pair_heads, pair_heads)
+        self.tri_att_end = TriangleAttentionEndingNode(c_z, c_z // pair_heads, pair_heads)
+        self.transition_z = Transition(c_z, c_z * transition_n)
+
+    def pair_update(self, z: torch.Tensor, pair_mask: Optional[torch.Tensor]) -> torch.Tensor:
+        z = self.tri_mul_out(z, pair_mask, residual=True)
+        z = self.tri_mul_in(z, pair_mask, residual=True)
+        z = self.tri_att_start(z, pair_mask, residual=True)
+        z = self.tri_att_end(z, pair_mask, residual=True)
+        z = self.transition_z(z, residual=True)
+        return z
+
+    def forward(self, s: Optional[torch.Tensor], z: torch.Tensor, mask: Optional[torch.Tensor],
+                pair_mask: Optional[torch.Tensor]):
+        z = self.pair_update(z, pair_mask)
+        if self.no_seq:
+            return s, z
+        # single track in fp32, as upstream (pairformer.py:103-111)
+        s32 = s.float()
+        sn = F.layer_norm(s32, (s32.shape[-1],), self.pre_norm_s.weight.float(), self.pre_norm_s.bias.float())
+        with torch.autocast(device_type=s.device.type, enabled=False):
+            upd = _run_fp32(self.attention, sn, z, mask)
+        s32 = s32 + upd
+        s32 = s32 + _run_fp32(self.transition_s, s32)
+        return s32.to(s.dtype), z
+
+
+def _run_fp32(module: nn.Module, x: torch.Tensor, *args):
+    """Run a module whose parameters may be bf16 on an fp32 activation (weights up-cast on the fly)."""
+    p = next(module.parameters())
+    if p.dtype == torch.float32:
+        return module(x, *args)
+    return module(x.to(p.dtype), *args).float()
+
+
+class PairformerModule(nn.Module):
+    def __init__(self, c_s: int = 384, c_z: int = 128, num_blocks: int = 48, heads: int = 16, pair_heads: int = 4,
+                 no_seq: bool = False):
+        super().__init__()
+        self.layers = nn.ModuleList([PairformerLayer(c_s, c_z, heads, pair_heads, no_seq) for _ in range(num_blocks)])
+
+    def forward(self, s, z, mask=None, pair_mask=None):
+        for layer in self.layers:
+            s, z = layer(s, z, mask, pair_mask)
+        return s, z
+
+
+def set_impl(module: nn.Module, impl: str, kinds=None, workspace: Optional[dict] = None) -> int:
+    """Switch every :class:`_Switchable` below ``module`` (optionally only the given classes).
+    All switched modules share one scratch workspace, so the pair stack's intermediates are
+    allocated once per size.  Returns the number of modules switched."""
+    ws = {} if workspace is None else workspace
+    n = 0
+    for m in module.modules():
+        if isinstance(m, _Switchable) and (kinds is None or isinstance(m, tuple(kinds))):
+            m.set_impl(impl, ws)
+            n += 1
+    return n

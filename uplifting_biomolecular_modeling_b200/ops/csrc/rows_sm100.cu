@@ -1,0 +1,304 @@
+// Row kernels: memory-bound elementwise / normalisation work that has no GEMM to hide in.
+//
+//   ubm_layernorm_rows   LayerNorm over the last dimension, one warp per row, 16-byte accesses
+//                        (reference rows: fastln / exactln, common/opt_core/opt_core/kernels/ln/DESIGN.md:5-37)
+//   ubm_pair_head_bias   bias[h][i][j] = Linear_{c->H}(LN(z[i][j])) as channel-major bf16 planes
+//                        (the proj_z of attention with pair bias; reference: _pf_bias_kernel,
+//                        common/opt_core/opt_core/kernels/apb/fpf_apb)
+//   ubm_adaln_rows       sigmoid(scale[r]) * LN_noaffine(a[r]) + shift[r]   (DiT AdaLN)
+//   ubm_gate_residual    out = res + sigmoid(gate) * x
+//   ubm_swiglu_rows      out = silu(a) * b for a | b halves of one row
+// Reference for the last three: _ln_mod_kernel / _gate_res_kernel / _swiglu_kernel in
+// common/opt_core/opt_core/kernels/dtk_kernels.py.
+#include "host_util.h"
+#include "sm100.cuh"
+
+namespace ubm {
+
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+
+// One warp per row, two passes over registers-free data (row re-read from L1/L2 on pass two is
+// avoided by keeping up to 32 values per lane in registers; wider rows fall back to re-reading).
+template <typename TI, typename TO, int MAXPL>
+__global__ void __launch_bounds__(256) layernorm_rows_kernel(const TI* __restrict__ x, const float* __restrict__ gamma,
+                                                             const float* __restrict__ beta, TO* __restrict__ out,
+                                                             long long R, int C, float eps) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (long long r = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); r < R;
+       r += static_cast<long long>(gridDim.x) * warps_per_block) {
+    const TI* xr = x + r * C;
+    float v[MAXPL];
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXPL; ++i) {
+      const int c = lane + i * 32;
+      v[i] = c < C ? to_f<TI>(xr[c]) : 0.f;
+      sum += v[i];
+    }
+    sum = warp_sum(sum);
+    const float mu = sum / C;
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXPL; ++i) {
+      const int c = lane + i * 32;
+      const float d = c < C ? v[i] - mu : 0.f;
+      sq += d * d;
+    }
+    sq = warp_sum(sq);
+    const float rstd = rsqrtf(sq / C + eps);
+    TO* orow = out + r * C;
+#pragma unroll
+    for (int i = 0; i < MAXPL; ++i) {
+      const int c = lane + i * 32;
+      if (c < C) {
+        float y = (v[i] - mu) * rstd;
+        if (gamma != nullptr) y *= gamma[c];
+        if (beta != nullptr) y += beta[c];
+        orow[c] = from_f<TO>(y);
+      }
+    }
+  }
+}
+
+// z rows [R][128] bf16 -> planes out[h][i][j] (bf16, leading dimension Np), LN folded:
+//   out = scale_out * (rstd * (w[h] . x - mu * colsum[h]) + colbias[h])
+// One thread per row; weights in shared memory (broadcast reads).
+template <int H>
+__global__ void __launch_bounds__(128) pair_head_bias_kernel(const __nv_bfloat16* __restrict__ z,
+                                                             const float* __restrict__ w,
+                                                             const float* __restrict__ colsum,
+                                                             const float* __restrict__ colbias,
+                                                             __nv_bfloat16* __restrict__ out, int N, int Np,
+                                                             int transpose_out) {
+  __shared__ float sw[H * 128];
+  for (int i = threadIdx.x; i < H * 128; i += blockDim.x) sw[i] = w[i];
+  __syncthreads();
+  const long long R = static_cast<long long>(N) * N;
+  for (long long r = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; r < R;
+       r += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(z + r * 128);
+    float acc[H];
+#pragma unroll
+    for (int h = 0; h < H; ++h) acc[h] = 0.f;
+    float sum = 0.f, sumsq = 0.f;
+#pragma unroll 4
+    for (int c16 = 0; c16 < 16; ++c16) {
+      const uint4 u = __ldg(xr + c16);
+      const uint32_t ww[4] = {u.x, u.y, u.z, u.w};
+      float e[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        e[2 * j] = bf16_lo(ww[j]);
+        e[2 * j + 1] = bf16_hi(ww[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        sum += e[j];
+        sumsq += e[j] * e[j];
+      }
+#pragma unroll
+      for (int h = 0; h < H; ++h) {
+        const float4 w0 = *reinterpret_cast<const float4*>(&sw[h * 128 + c16 * 8]);
+        const float4 w1 = *reinterpret_cast<const float4*>(&sw[h * 128 + c16 * 8 + 4]);
+        acc[h] += e[0] * w0.x + e[1] * w0.y + e[2] * w0.z + e[3] * w0.w + e[4] * w1.x + e[5] * w1.y +
+                  e[6] * w1.z + e[7] * w1.w;
+      }
+    }
+    const float mu = sum * (1.f / 128.f);
+    const float rstd = rsqrtf(fmaxf(sumsq * (1.f / 128.f) - mu * mu, 0.f) + 1e-5f);
+    const int i = static_cast<int>(r / N);
+    const int j = static_cast<int>(r - static_cast<long long>(i) * N);
+    const long long off = transpose_out ? (static_cast<long long>(j) * Np + i) : (static_cast<long long>(i) * Np + j);
+#pragma unroll
+    for (int h = 0; h < H; ++h) {
+      const float val = rstd * (acc[h] - mu * colsum[h]) + colbias[h];
+      out[static_cast<long long>(h) * N * Np + off] = __float2bfloat16(val);
+    }
+  }
+}
+
+// a: [R][C] (bf16), scale/shift: [Rs][C] (bf16) with Rs = R / rows_per_cond (conditioning shared by
+// `rows_per_cond`... no: one conditioning row per activation row).  out = sigmoid(scale)*LN(a)+shift.
+__global__ void __launch_bounds__(256) adaln_rows_kernel(const __nv_bfloat16* __restrict__ a,
+                                                         const __nv_bfloat16* __restrict__ scale,
+                                                         const __nv_bfloat16* __restrict__ shift,
+                                                         __nv_bfloat16* __restrict__ out, long long R, int C,
+                                                         long long cond_rows, float eps) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (long long r = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); r < R;
+       r += static_cast<long long>(gridDim.x) * warps_per_block) {
+    const __nv_bfloat16* ar = a + r * C;
+    const long long rc = r % cond_rows;
+    float sum = 0.f, sumsq = 0.f;
+    for (int c = lane * 2; c < C; c += 64) {
+      const __nv_bfloat162 p = *reinterpret_cast<const __nv_bfloat162*>(ar + c);
+      const float x0 = __low2float(p), x1 = __high2float(p);
+      sum += x0 + x1;
+      sumsq += x0 * x0 + x1 * x1;
+    }
+    sum = warp_sum(sum);
+    sumsq = warp_sum(sumsq);
+    const float mu = sum / C;
+    const float rstd = rsqrtf(fmaxf(sumsq / C - mu * mu, 0.f) + eps);
+    for (int c = lane * 2; c < C; c += 64) {
+      const __nv_bfloat162 p = *reinterpret_cast<const __nv_bfloat162*>(ar + c);
+      const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162*>(scale + rc * C + c);
+      const __nv_bfloat162 sh = *reinterpret_cast<const __nv_bfloat162*>(shift + rc * C + c);
+      const float y0 = sigmoidf_fast(__low2float(sc)) * ((__low2float(p) - mu) * rstd) + __low2float(sh);
+      const float y1 = sigmoidf_fast(__high2float(sc)) * ((__high2float(p) - mu) * rstd) + __high2float(sh);
+      *reinterpret_cast<__nv_bfloat162*>(out + r * C + c) = __floats2bfloat162_rn(y0, y1);
+    }
+  }
+}
+
+// out = res + sigmoid(gate[r % cond_rows]) * x   (res may be null)
+__global__ void __launch_bounds__(256) gate_residual_kernel(const __nv_bfloat16* __restrict__ x,
+                                                            const __nv_bfloat16* __restrict__ gate,
+                                                            const __nv_bfloat16* __restrict__ res,
+                                                            __nv_bfloat16* __restrict__ out, long long n2, int C2,
+                                                            long long cond_rows) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n2;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / C2;
+    const int c = static_cast<int>(i - r * C2);
+    const long long gi = (r % cond_rows) * C2 + c;
+    const __nv_bfloat162 xv = reinterpret_cast<const __nv_bfloat162*>(x)[i];
+    const __nv_bfloat162 gv = reinterpret_cast<const __nv_bfloat162*>(gate)[gi];
+    float y0 = sigmoidf_fast(__low2float(gv)) * __low2float(xv);
+    float y1 = sigmoidf_fast(__high2float(gv)) * __high2float(xv);
+    if (res != nullptr) {
+      const __nv_bfloat162 rv = reinterpret_cast<const __nv_bfloat162*>(res)[i];
+      y0 += __low2float(rv);
+      y1 += __high2float(rv);
+    }
+    reinterpret_cast<__nv_bfloat162*>(out)[i] = __floats2bfloat162_rn(y0, y1);
+  }
+}
+
+// ab: [R][2*Hd] -> out [R][Hd] = silu(ab[:, :Hd]) * ab[:, Hd:]
+__global__ void __launch_bounds__(256) swiglu_rows_kernel(const __nv_bfloat16* __restrict__ ab,
+                                                          __nv_bfloat16* __restrict__ out, long long R, int Hd) {
+  const int h2 = Hd >> 1;
+  const long long n2 = R * h2;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n2;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / h2;
+    const int c = static_cast<int>(i - r * h2);
+    const __nv_bfloat162 av = reinterpret_cast<const __nv_bfloat162*>(ab + r * 2 * Hd)[c];
+    const __nv_bfloat162 bv = reinterpret_cast<const __nv_bfloat162*>(ab + r * 2 * Hd + Hd)[c];
+    reinterpret_cast<__nv_bfloat162*>(out + r * Hd)[c] =
+        __floats2bfloat162_rn(siluf_fast(__low2float(av)) * __low2float(bv),
+                              siluf_fast(__high2float(av)) * __high2float(bv));
+  }
+}
+
+static inline int grid_for(long long work, int per_block) {
+  long long b = (work + per_block - 1) / per_block;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return static_cast<int>(b);
+}
+
+}  // namespace ubm
+
+// in_dtype / out_dtype: 0 = bf16, 1 = fp32.  gamma / beta: fp32 [C] or null.  C <= 1024.
+extern "C" int ubm_layernorm_rows(const void* x, const void* gamma, const void* beta, void* out, long long R, int C,
+                                  float eps, int in_dtype, int out_dtype, void* stream) {
+  using namespace ubm;
+  if (R <= 0 || C <= 0 || C > 1024) return UBM_ERR_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(R, 8);
+  const float* g = static_cast<const float*>(gamma);
+  const float* b = static_cast<const float*>(beta);
+#define UBM_LN_LAUNCH(TI, TO, MP)                                                                          \
+  layernorm_rows_kernel<TI, TO, MP><<<grid, 256, 0, st>>>(static_cast<const TI*>(x), g, b, static_cast<TO*>(out), R, \
+                                                          C, eps)
+#define UBM_LN_BY_WIDTH(TI, TO)      \
+  do {                               \
+    if (C <= 128) {                  \
+      UBM_LN_LAUNCH(TI, TO, 4);      \
+    } else if (C <= 256) {           \
+      UBM_LN_LAUNCH(TI, TO, 8);      \
+    } else if (C <= 512) {           \
+      UBM_LN_LAUNCH(TI, TO, 16);     \
+    } else {                         \
+      UBM_LN_LAUNCH(TI, TO, 32);     \
+    }                                \
+  } while (0)
+  if (in_dtype == 0 && out_dtype == 0) UBM_LN_BY_WIDTH(__nv_bfloat16, __nv_bfloat16);
+  else if (in_dtype == 0 && out_dtype == 1) UBM_LN_BY_WIDTH(__nv_bfloat16, float);
+  else if (in_dtype == 1 && out_dtype == 0) UBM_LN_BY_WIDTH(float, __nv_bfloat16);
+  else UBM_LN_BY_WIDTH(float, float);
+#undef UBM_LN_BY_WIDTH
+#undef UBM_LN_LAUNCH
+  UBM_CHECK_LAUNCH("layernorm_rows_kernel");
+  return UBM_OK;
+}
+
+extern "C" int ubm_pair_head_bias(const void* z, const void* w, const void* colsum, const void* colbias, void* out,
+                                  int N, int Np, int H, int transpose_out, void* stream) {
+  using namespace ubm;
+  if (N <= 0 || Np < N) return UBM_ERR_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(static_cast<long long>(N) * N, 128);
+  const __nv_bfloat16* zz = static_cast<const __nv_bfloat16*>(z);
+  const float* ww = static_cast<const float*>(w);
+  const float* cs = static_cast<const float*>(colsum);
+  const float* cb = static_cast<const float*>(colbias);
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
+  switch (H) {
+    case 4: pair_head_bias_kernel<4><<<grid, 128, 0, st>>>(zz, ww, cs, cb, o, N, Np, transpose_out); break;
+    case 8: pair_head_bias_kernel<8><<<grid, 128, 0, st>>>(zz, ww, cs, cb, o, N, Np, transpose_out); break;
+    case 16: pair_head_bias_kernel<16><<<grid, 128, 0, st>>>(zz, ww, cs, cb, o, N, Np, transpose_out); break;
+    case 32: pair_head_bias_kernel<32><<<grid, 128, 0, st>>>(zz, ww, cs, cb, o, N, Np, transpose_out); break;
+    default: return UBM_ERR_ARGUMENT;
+  }
+  UBM_CHECK_LAUNCH("pair_head_bias_kernel");
+  return UBM_OK;
+}
+
+extern "C" int ubm_adaln_rows(const void* a, const void* scale, const void* shift, void* out, long long R, int C,
+                              long long cond_rows, float eps, void* stream) {
+  using namespace ubm;
+  if (R <= 0 || C <= 0 || (C & 1) || cond_rows <= 0) return UBM_ERR_ARGUMENT;
+  adaln_rows_kernel<<<grid_for(R, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(scale),
+      static_cast<const __nv_bfloat16*>(shift), static_cast<__nv_bfloat16*>(out), R, C, cond_rows, eps);
+  UBM_CHECK_LAUNCH("adaln_rows_kernel");
+  return UBM_OK;
+}
+
+extern "C" int ubm_gate_residual(const void* x, const void* gate, const void* res, void* out, long long R, int C,
+                                 long long cond_rows, void* stream) {
+  using namespace ubm;
+  if (R <= 0 || C <= 0 || (C & 1) || cond_rows <= 0) return UBM_ERR_ARGUMENT;
+  const long long n2 = R * (C / 2);
+  gate_residual_kernel<<<grid_for(n2, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gate),
+      static_cast<const __nv_bfloat16*>(res), static_cast<__nv_bfloat16*>(out), n2, C / 2, cond_rows);
+  UBM_CHECK_LAUNCH("gate_residual_kernel");
+  return UBM_OK;
+}
+
+extern "C" int ubm_swiglu_rows(const void* ab, void* out, long long R, int Hd, void* stream) {
+  using namespace ubm;
+  if (R <= 0 || Hd <= 0 || (Hd & 1)) return UBM_ERR_ARGUMENT;
+  swiglu_rows_kernel<<<grid_for(R * (Hd / 2), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(ab), static_cast<__nv_bfloat16*>(out), R, Hd);
+  UBM_CHECK_LAUNCH("swiglu_rows_kernel");
+  return UBM_OK;
+}

@@ -25,7 +25,7 @@ class KernelFault(RuntimeError):
 
 
 _LOCK = threading.Lock()
-_LIB: Optional[ctypes.CDLL] = None
+_LIB = None
 
 c_void_p = ctypes.c_void_p
 c_int = ctypes.c_int
@@ -51,13 +51,11 @@ def library_path() -> Path:
 def declare(name: str, argtypes) -> None:
     """Register the signature of an exported symbol (used by op modules beside their kernels)."""
     _SIGNATURES[name] = list(argtypes)
-    if _LIB is not None and hasattr(_LIB, name):
-        fn = getattr(_LIB, name)
-        fn.argtypes = _SIGNATURES[name]
-        fn.restype = c_int
+    if _LIB is not None:
+        _LIB._cache.pop(name, None)
 
 
-def lib(build_if_missing: bool = False) -> ctypes.CDLL:
+def lib(build_if_missing: bool = False):
     global _LIB
     if _LIB is not None:
         return _LIB
@@ -80,8 +78,61 @@ def lib(build_if_missing: bool = False) -> ctypes.CDLL:
                 fn = getattr(handle, name)
                 fn.argtypes = argtypes
                 fn.restype = c_int
-        _LIB = handle
-        return handle
+        _LIB = _LibProxy(handle)
+        return _LIB
+
+
+class _LibProxy:
+    """Attribute access returns counted callables; unknown symbols raise AttributeError as ctypes does."""
+
+    def __init__(self, handle):
+        self._handle = handle
+        self._cache = {}
+
+    def __getattr__(self, name):
+        c = self._cache.get(name)
+        if c is None:
+            fn = getattr(self._handle, name)
+            if name in _SIGNATURES:
+                fn.argtypes = _SIGNATURES[name]
+                fn.restype = c_int
+            c = _Counted(fn, name)
+            self._cache[name] = c
+        return c
+
+
+class _Counted:
+    """Callable proxy of an exported symbol that counts launches (one call = one or more kernels)."""
+
+    __slots__ = ("fn", "name")
+
+    def __init__(self, fn, name):
+        self.fn, self.name = fn, name
+
+    def __call__(self, *a):
+        _COUNTS[self.name] = _COUNTS.get(self.name, 0) + 1
+        return self.fn(*a)
+
+
+_COUNTS: dict = {}
+
+
+def launch_count() -> int:
+    """Entry-point calls since the last reset (each is one kernel launch of this library)."""
+    return sum(_COUNTS.values())
+
+
+def add_launches(n: int, name: str = "graph_replay") -> None:
+    """Account for kernels of this library launched by a CUDA-graph replay (n per replay)."""
+    _COUNTS[name] = _COUNTS.get(name, 0) + int(n)
+
+
+def launch_counts() -> dict:
+    return dict(_COUNTS)
+
+
+def reset_launch_count() -> None:
+    _COUNTS.clear()
 
 
 def available() -> bool:

@@ -1,0 +1,98 @@
+"""Python face of the row kernels (``csrc/rows_sm100.cu``): LayerNorm rows, pair -> head-bias
+planes, AdaLN, gated residual, SwiGLU.  Each wrapper has the same signature as its plain
+statement in :mod:`ops.reference` where one exists."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import native
+from .native import c_float, c_int, c_ll, c_void_p
+
+native.declare("ubm_layernorm_rows", [c_void_p] * 4 + [c_ll, c_int, c_float, c_int, c_int, c_void_p])
+native.declare("ubm_pair_head_bias", [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_void_p])
+native.declare("ubm_adaln_rows", [c_void_p] * 4 + [c_ll, c_int, c_ll, c_float, c_void_p])
+native.declare("ubm_gate_residual", [c_void_p] * 4 + [c_ll, c_int, c_ll, c_void_p])
+native.declare("ubm_swiglu_rows", [c_void_p] * 2 + [c_ll, c_int, c_void_p])
+
+_DT = {torch.bfloat16: 0, torch.float32: 1}
+
+
+def layernorm_rows(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+                   eps: float = 1e-5, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    if x.dtype not in _DT or not x.is_contiguous():
+        raise ValueError("layernorm_rows expects contiguous bf16 / fp32 input")
+    C = x.shape[-1]
+    R = x.numel() // C
+    out_dtype = out_dtype or x.dtype
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    w = None if weight is None else weight.detach().float().contiguous()
+    b = None if bias is None else bias.detach().float().contiguous()
+    rc = native.lib().ubm_layernorm_rows(native.ptr(x), native.ptr(w), native.ptr(b), native.ptr(out), R, C,
+                                         float(eps), _DT[x.dtype], _DT[out_dtype], native.current_stream(x.device))
+    native.check(rc, "ubm_layernorm_rows")
+    return out
+
+
+_HB_CACHE = {}
+
+
+def pair_head_bias(z: torch.Tensor, ln_w, ln_b, w, scale: float = 1.0, transpose: bool = False,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """z: bf16 [N, N, 128]; w: [H, 128].  Returns bf16 [H, N, N] (a view of planes padded to a
+    multiple of 8 columns) with ``scale * Linear(LN(z))`` laid out head-major."""
+    N = z.shape[0]
+    H = w.shape[0]
+    Np = (N + 7) // 8 * 8
+    key = (w.data_ptr(), w._version, None if ln_w is None else ln_w._version, float(scale))
+    packed = _HB_CACHE.get(key)
+    if packed is None:
+        gam = torch.ones(128, device=z.device) if ln_w is None else ln_w.detach().float()
+        wf = (w.detach().float() * gam[None, :] * scale).contiguous()
+        colsum = wf.sum(1).contiguous()
+        colbias = torch.zeros(H, device=z.device) if ln_b is None else \
+            ((w.detach().float() @ ln_b.detach().float()) * scale).contiguous()
+        packed = (wf, colsum, colbias)
+        if len(_HB_CACHE) > 4096:
+            _HB_CACHE.clear()
+        _HB_CACHE[key] = packed
+    wf, colsum, colbias = packed
+    if out is None:
+        out = torch.zeros((H, N, Np), dtype=torch.bfloat16, device=z.device) if Np != N else \
+            torch.empty((H, N, Np), dtype=torch.bfloat16, device=z.device)
+    rc = native.lib().ubm_pair_head_bias(native.ptr(z), native.ptr(wf), native.ptr(colsum), native.ptr(colbias),
+                                         native.ptr(out), N, Np, H, 1 if transpose else 0,
+                                         native.current_stream(z.device))
+    native.check(rc, "ubm_pair_head_bias")
+    return out[:, :, :N]
+
+
+def adaln_rows(a: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """sigmoid(scale) * LN_noaffine(a) + shift; scale/shift rows are reused cyclically over a's rows."""
+    C = a.shape[-1]
+    R = a.numel() // C
+    out = torch.empty_like(a)
+    rc = native.lib().ubm_adaln_rows(native.ptr(a), native.ptr(scale), native.ptr(shift), native.ptr(out), R, C,
+                                     scale.numel() // C, float(eps), native.current_stream(a.device))
+    native.check(rc, "ubm_adaln_rows")
+    return out
+
+
+def gate_residual(x: torch.Tensor, gate: torch.Tensor, res: Optional[torch.Tensor]) -> torch.Tensor:
+    C = x.shape[-1]
+    R = x.numel() // C
+    out = torch.empty_like(x)
+    rc = native.lib().ubm_gate_residual(native.ptr(x), native.ptr(gate), native.ptr(res), native.ptr(out), R, C,
+                                        gate.numel() // C, native.current_stream(x.device))
+    native.check(rc, "ubm_gate_residual")
+    return out
+
+
+def swiglu_rows(ab: torch.Tensor) -> torch.Tensor:
+    Hd = ab.shape[-1] // 2
+    R = ab.numel() // (2 * Hd)
+    out = torch.empty(ab.shape[:-1] + (Hd,), dtype=ab.dtype, device=ab.device)
+    rc = native.lib().ubm_swiglu_rows(native.ptr(ab), native.ptr(out), R, Hd, native.current_stream(ab.device))
+    native.check(rc, "ubm_swiglu_rows")
+    return out
