@@ -33,6 +33,8 @@ def _tree_copy(dst, src) -> None:
     """Copy every tensor of ``src`` into the tensor at the same place of ``dst`` (dicts / lists / tuples)."""
     if isinstance(dst, torch.Tensor):
         dst.copy_(src)
+    elif hasattr(dst, "view") and isinstance(getattr(dst, "view"), torch.Tensor) and not isinstance(dst, dict):
+        dst.view.copy_(src.view)              # models.pairformer.BiasPlanes
     elif isinstance(dst, dict):
         for k in dst:
             _tree_copy(dst[k], src[k])
@@ -71,6 +73,7 @@ class Predictor:
     def to_device(self, feats: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
         out = {}
         self.h2d_bytes = 0
+        no_padding = bool(feats["token_mask"].min() > 0) if "token_mask" in feats else False
         for k, v in feats.items():
             if self.device.type == "cuda":
                 pin = self._pinned.get(k)
@@ -83,6 +86,7 @@ class Predictor:
             else:
                 d = v
             out[k] = d.to(self.dtype) if d.is_floating_point() else d
+        out["no_padding"] = no_padding
         return out
 
     # ------------------------------------------------------------------ sampler step graph

@@ -213,11 +213,13 @@ class CofoldModel(nn.Module):
         z = torch.zeros_like(z_init)
         n = cfg.recycles if recycles is None else recycles
         tmask = feats["token_mask"]
+        # without padding tokens the single-track attention needs no key mask (and may run fused)
+        smask = None if feats.get("no_padding") is True else tmask
         for _ in range(n + 1):
             s = s_init + self.s_recycle(self.s_norm(s))
             z = z_init + self.z_recycle(self.z_norm(z))
             z = self.msa_module(z, s_inputs, feats["msa_feat"], feats["msa_mask"], tmask, None)
-            s, z = self.pairformer_module(s, z, tmask, None)
+            s, z = self.pairformer_module(s, z, smask, None)
         return s, z
 
     def structure(self, feats, s, z, s_inputs, atom_c, atom_p, samples=None, steps=None, generator=None,

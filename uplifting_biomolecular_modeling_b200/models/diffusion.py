@@ -81,10 +81,38 @@ class DiffusionTransformerLayer(_Switchable):
         return {"adaln": self.adaln.cond(s), "gate": self.output_projection_linear(s),
                 "t_adaln": self.transition.adaln.cond(s), "t_gate": self.transition.output_projection(s)}
 
+    def _fused_token_layer(self, a, h, bias):
+        """Token-transformer layer on the fused path: AdaLN rows -> q|k|v and gate projections (tcgen05
+        GEMM) -> attention with the hoisted pair-bias planes shared by all samples -> output projection ->
+        gated residual; then the conditioned SwiGLU transition the same way."""
+        from ..ops import gemm, pair, rows
+        B, N, C = a.shape
+        attn = self.pair_bias_attn
+        b = rows.adaln_rows(a.contiguous(), h["adaln"][0].contiguous(), h["adaln"][1].contiguous())
+        o = attn._fused_forward(b, bias)
+        a = rows.gate_residual(o.contiguous(), h["gate"].contiguous(), a)
+        tr = self.transition
+        if self._packed is None:
+            self._packed = (tr.swish_gated.weight.to(torch.bfloat16).contiguous(),
+                            tr.a_to_b.weight.to(torch.bfloat16).contiguous(),
+                            tr.b_to_a.weight.to(torch.bfloat16).contiguous())
+        w_sg, w_ab, w_ba = self._packed
+        x = rows.adaln_rows(a, h["t_adaln"][0].contiguous(), h["t_adaln"][1].contiguous()).view(B * N, C)
+        u = rows.swiglu_rows(gemm.gemm(x, w_sg))
+        u = u * gemm.gemm(x, w_ab)
+        y = gemm.gemm(u, w_ba).view(B, N, C)
+        return rows.gate_residual(y, h["t_gate"].contiguous(), a)
+
     def forward(self, a, s, bias, mask=None, multiplicity: int = 1, hoisted: Optional[dict] = None,
                 window: Optional[tuple] = None):
         fused = self.impl == "fused"
         h = hoisted if hoisted is not None else self.hoist(s)
+        from .pairformer import BiasPlanes
+        if fused and window is None and mask is None and isinstance(bias, BiasPlanes) and a.is_cuda \
+                and a.dtype == torch.bfloat16:
+            return self._fused_token_layer(a, h, bias)
+        if isinstance(bias, BiasPlanes):
+            bias = bias.dense()
         b = self.adaln(a, None, h["adaln"], fused)
         if window is None:
             b = self.pair_bias_attn(b, None, mask, bias=bias, multiplicity=multiplicity)
@@ -260,7 +288,9 @@ class DiffusionModule(nn.Module):
         """Step-invariant tensors.  z_cond: [1, N, N, c_z]; atom_pair: [1, nw, wq, wk, c_atompair]."""
         if fused and z_cond.is_cuda and z_cond.dtype == torch.bfloat16 and z_cond.shape[-1] == 128:
             from ..ops import rows
-            tb = [rows.pair_head_bias(z_cond[0].contiguous(), m[0].weight, m[0].bias, m[1].weight).unsqueeze(0)
+            from .pairformer import BiasPlanes
+            zc = z_cond[0].contiguous()
+            tb = [BiasPlanes(rows.pair_head_bias(zc, m[0].weight, m[0].bias, m[1].weight, scale=BiasPlanes.LOG2E))
                   for m in self.token_pair_bias]
         else:
             tb = [m(z_cond).permute(0, 3, 1, 2) for m in self.token_pair_bias]
@@ -281,7 +311,8 @@ class DiffusionModule(nn.Module):
         a, q = self.atom_attention_encoder(prep["atom_q"], prep["atom_c"], prep["enc_bias"], r_noisy,
                                            atom_to_token, n_tokens, prep["enc_hoist"], self.window)
         a = a + self.s_to_a_linear(s)
-        a = self.token_transformer(a, s, prep["token_bias"], None, multiplicity=B)
+        hoisted = [l.hoist(s) for l in self.token_transformer.layers]
+        a = self.token_transformer(a, s, prep["token_bias"], None, multiplicity=B, hoisted=hoisted)
         a = self.a_norm(a)
         return self.atom_attention_decoder(a, q, prep["atom_c"], prep["dec_bias"], atom_to_token,
                                            prep["dec_hoist"], self.window)

@@ -156,6 +156,20 @@ class TriangleAttentionEndingNode(TriangleAttention):
         super().__init__(c_in, c_hidden, heads, starting=False)
 
 
+class BiasPlanes:
+    """Pair bias laid out for the attention kernel: bf16 planes [H, N, ld] (ld a multiple of 8) that
+    already carry the factor log2(e).  ``dense()`` gives the plain [1, H, N, N] bias back."""
+
+    LOG2E = 1.4426950408889634
+
+    def __init__(self, view: torch.Tensor):
+        self.view = view                      # [H, N, N] view with stride(1) = ld
+        self.ld = view.stride(1)
+
+    def dense(self) -> torch.Tensor:
+        return (self.view.float() / self.LOG2E).unsqueeze(0)
+
+
 class AttentionPairBias(_Switchable):
     """Single-representation attention with a bias projected from the pair tensor."""
 
@@ -172,13 +186,21 @@ class AttentionPairBias(_Switchable):
             self.proj_z = nn.Sequential(nn.LayerNorm(c_z), nn.Linear(c_z, heads, bias=False))
         self.proj_o = nn.Linear(c_s, c_s, bias=False)
 
-    def pair_bias(self, z: torch.Tensor) -> torch.Tensor:
-        """[B, H, N, N] bias from the pair tensor."""
+    def pair_bias(self, z: torch.Tensor):
+        """[B, H, N, N] bias from the pair tensor (a :class:`BiasPlanes` on the fused path)."""
         if self._fusable(z) and z.shape[0] == 1:
             from ..ops import rows
-            return rows.pair_head_bias(z[0], self.proj_z[0].weight, self.proj_z[0].bias,
-                                       self.proj_z[1].weight).unsqueeze(0)
+            return BiasPlanes(rows.pair_head_bias(z[0].contiguous(), self.proj_z[0].weight, self.proj_z[0].bias,
+                                                  self.proj_z[1].weight, scale=BiasPlanes.LOG2E))
         return self.proj_z[1](self.proj_z[0](z)).permute(0, 3, 1, 2)
+
+    def _fused_forward(self, s: torch.Tensor, planes: "BiasPlanes") -> torch.Tensor:
+        from ..ops import pair
+        if self._packed is None:
+            self._packed = pair.ApbPacked.pack(self.proj_q.weight, self.proj_q.bias, self.proj_k.weight,
+                                               self.proj_v.weight, self.proj_g.weight, self.proj_o.weight,
+                                               self.heads)
+        return pair.apb_fused(s.to(torch.bfloat16).contiguous(), self._packed, planes.view, planes.ld)
 
     def forward(self, s: torch.Tensor, z: Optional[torch.Tensor], mask: Optional[torch.Tensor],
                 bias: Optional[torch.Tensor] = None, k_in: Optional[torch.Tensor] = None,
@@ -188,6 +210,10 @@ class AttentionPairBias(_Switchable):
         kin = s if k_in is None else k_in
         if bias is None:
             bias = self.pair_bias(z)
+        if isinstance(bias, BiasPlanes):
+            if self.impl == "fused" and mask is None and k_in is None and s.is_cuda:
+                return self._fused_forward(s, bias).to(s.dtype)
+            bias = bias.dense()
         H, D = self.heads, self.head_dim
         q = self.proj_q(s).view(B, N, H, D).transpose(1, 2)
         k = self.proj_k(kin).view(B, kin.shape[1], H, D).transpose(1, 2)

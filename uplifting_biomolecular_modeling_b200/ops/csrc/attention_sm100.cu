@@ -24,15 +24,24 @@
 
 namespace ubm {
 
-constexpr int kAD = 32;                         // head dimension
-constexpr int kATile = 128;                     // queries per CTA, keys per step
-constexpr int kAQBytes = kATile * kAD * 2;      // 8 KB
-constexpr int kAKVBytes = kATile * kAD * 2;     // 8 KB
-constexpr int kABiasBytes = kATile * kATile * 2;  // 32 KB (two halves of 64 keys)
-constexpr int kAStageBytes = 4 * kAKVBytes + kABiasBytes;  // K0 V0 K1 V1 bias = 64 KB
-constexpr int kAPBytes = kATile * kATile * 2;   // 32 KB per row
+constexpr int kATile = 128;  // queries per CTA
 constexpr int kAStages = 2;
 constexpr float kNegBig = -1.0e30f;
+
+// D = head dimension (32 or 64), TK = keys per step (128 for D = 32, 64 for D = 64 so that two rows,
+// two stages and the P tiles still fit in shared memory).
+template <int D, int TK>
+struct AttnCfg {
+  static constexpr int kQBytes = kATile * D * 2;
+  static constexpr int kKVBytes = TK * D * 2;
+  static constexpr int kBiasBytes = kATile * TK * 2;
+  static constexpr int kStageBytes = 4 * kKVBytes + kBiasBytes;  // K0 V0 K1 V1 bias
+  static constexpr int kPBytes = kATile * TK * 2;
+  static constexpr int kSmemBytes = 2 * kQBytes + kAStages * kStageBytes + 2 * kPBytes + 256 + 1024;
+  static constexpr uint64_t kSwz = (D == 32) ? kSwizzle64 : kSwizzle128;  // operand rows are D * 2 bytes
+  static constexpr uint32_t kSbo = (D == 32) ? 512 : 1024;               // 8 rows of D * 2 bytes
+  static constexpr uint32_t kVStep = 16 * D * 2;                         // 16 keys of V
+};
 
 struct AttnParams {
   int rows, Nq, Nk, H;
@@ -44,12 +53,19 @@ struct AttnParams {
   int n_qt, n_kt, n_rp, num_items;
 };
 
+template <int D, int TK>
 __global__ void __launch_bounds__(384, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmB, AttnParams p) {
+  using Cfg = AttnCfg<D, TK>;
+  constexpr int kAD = D;
+  constexpr int kAQBytes = Cfg::kQBytes;
+  constexpr int kAKVBytes = Cfg::kKVBytes;
+  constexpr int kAStageBytes = Cfg::kStageBytes;
+  constexpr int kAPBytes = Cfg::kPBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;                              // 2 x 8 KB
+  uint8_t* sQ = smem;                              // 2 x Q tile
   uint8_t* sSt = sQ + 2 * kAQBytes;                // stages x 64 KB
   uint8_t* sP = sSt + kAStages * kAStageBytes;     // 2 x 32 KB
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kAPBytes);
@@ -97,7 +113,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base;         // S[r] at r * 128
-  const uint32_t tO = tmem_base + 256;   // O[r] at r * 32
+  const uint32_t tO = tmem_base + 256;   // O[r] at r * D
   const int T = p.n_kt;
 
   // Register split: warps 0-3 (producer, MMA issuer, two idle warps) give registers up, the two
@@ -125,13 +141,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (*abort_flag) break;
           uint8_t* st = sSt + s * kAStageBytes;
           mbar_expect_tx(&kv_full[s], p.has_bias ? kAStageBytes : 4 * kAKVBytes);
-          tma_load_3d(st, &tmK, &kv_full[s], h * kAD, j * kATile, r0);
-          tma_load_3d(st + kAKVBytes, &tmV, &kv_full[s], h * kAD, j * kATile, r0);
-          tma_load_3d(st + 2 * kAKVBytes, &tmK, &kv_full[s], h * kAD, j * kATile, r0 + 1);
-          tma_load_3d(st + 3 * kAKVBytes, &tmV, &kv_full[s], h * kAD, j * kATile, r0 + 1);
+          tma_load_3d(st, &tmK, &kv_full[s], h * kAD, j * TK, r0);
+          tma_load_3d(st + kAKVBytes, &tmV, &kv_full[s], h * kAD, j * TK, r0);
+          tma_load_3d(st + 2 * kAKVBytes, &tmK, &kv_full[s], h * kAD, j * TK, r0 + 1);
+          tma_load_3d(st + 3 * kAKVBytes, &tmV, &kv_full[s], h * kAD, j * TK, r0 + 1);
           if (p.has_bias) {
-            tma_load_3d(st + 4 * kAKVBytes, &tmB, &kv_full[s], j * kATile, qt * kATile, h);
-            tma_load_3d(st + 4 * kAKVBytes + 16384, &tmB, &kv_full[s], j * kATile + 64, qt * kATile, h);
+#pragma unroll
+            for (int hb = 0; hb < TK / 64; ++hb)
+              tma_load_3d(st + 4 * kAKVBytes + hb * 16384, &tmB, &kv_full[s], j * TK + hb * 64, qt * kATile, h);
           }
         }
         if (*abort_flag) break;
@@ -140,7 +157,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, TK, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, kAD, 0, 1);  // B = V is MN-major
       uint32_t item_cnt = 0, gk = 0;
       auto issue_qk = [&](int r, uint32_t g) {
@@ -149,8 +166,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t ka = st + r * 2 * kAKVBytes;
 #pragma unroll
         for (int k = 0; k < kAD / 16; ++k) {
-          const uint64_t ad = umma_smem_desc(qa + k * 32, 16, 512, kSwizzle64);
-          const uint64_t bd = umma_smem_desc(ka + k * 32, 16, 512, kSwizzle64);
+          const uint64_t ad = umma_smem_desc(qa + k * 32, 16, Cfg::kSbo, Cfg::kSwz);
+          const uint64_t bd = umma_smem_desc(ka + k * 32, 16, Cfg::kSbo, Cfg::kSwz);
           umma_ss(tS + r * 128, ad, bd, idesc_qk, k != 0 ? 1u : 0u);
         }
         umma_commit(&s_full[r]);
@@ -182,10 +199,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const uint32_t pa = smem_u32(sP + r * kAPBytes);
             const uint32_t va = st + (r * 2 + 1) * kAKVBytes;
 #pragma unroll
-            for (int k = 0; k < kATile / 16; ++k) {
-              // P: K-major, two k-blocks of 64 keys; V: MN-major, 16 keys = 1024 bytes
+            for (int k = 0; k < TK / 16; ++k) {
+              // P: K-major, k-blocks of 64 keys; V: MN-major, a step of 16 keys
               const uint64_t ad = umma_smem_desc(pa + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024, kSwizzle128);
-              const uint64_t bd = umma_smem_desc(va + k * 1024, 16, 512, kSwizzle64);
+              const uint64_t bd = umma_smem_desc(va + k * Cfg::kVStep, 16, Cfg::kSbo, Cfg::kSwz);
               umma_ss(tO + r * kAD, ad, bd, idesc_pv, (j | k) != 0 ? 1u : 0u);
             }
             umma_commit(&pv_done[r]);
@@ -216,14 +233,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t g = gk + j;
         mbar_wait(&s_full[r_in], g & 1u, ws, 59, r_in);
         tc_fence_after_sync();
-        float t[128];
+        float t[TK];
         {
           uint32_t* tu = reinterpret_cast<uint32_t*>(t);
           const uint32_t ta = tmem_addr(tS, quad, r_in * 128);
-          tmem_ld32(ta, *reinterpret_cast<uint32_t(*)[32]>(tu));
-          tmem_ld32(ta + 32, *reinterpret_cast<uint32_t(*)[32]>(tu + 32));
-          tmem_ld32(ta + 64, *reinterpret_cast<uint32_t(*)[32]>(tu + 64));
-          tmem_ld32(ta + 96, *reinterpret_cast<uint32_t(*)[32]>(tu + 96));
+#pragma unroll
+          for (int c = 0; c < TK / 32; ++c) tmem_ld32(ta + c * 32, *reinterpret_cast<uint32_t(*)[32]>(tu + c * 32));
           tmem_ld_wait();
         }
         tc_fence_before_sync();
@@ -234,7 +249,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (p.has_bias) {
           const uint8_t* bs = sSt + (g & 1) * kAStageBytes + 4 * kAKVBytes;
 #pragma unroll
-          for (int c16 = 0; c16 < 16; ++c16) {
+          for (int c16 = 0; c16 < TK / 8; ++c16) {
             const uint4 u = *reinterpret_cast<const uint4*>(bs + (c16 >> 3) * 16384 + swz128_offset(qrow, c16 & 7));
             const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
@@ -247,22 +262,22 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&kv_empty[g & 1]);
         if (j == T - 1) {
-          const int valid = p.Nk - j * kATile;
-          if (valid < kATile) {
+          const int valid = p.Nk - j * TK;
+          if (valid < TK) {
 #pragma unroll
-            for (int k = 0; k < 128; ++k)
+            for (int k = 0; k < TK; ++k)
               if (k >= valid) t[k] = kNegBig;
           }
         }
         float mt = t[0];
 #pragma unroll
-        for (int k = 1; k < 128; ++k) mt = fmaxf(mt, t[k]);
+        for (int k = 1; k < TK; ++k) mt = fmaxf(mt, t[k]);
         const float m_new = fmaxf(m, mt);
         const float alpha = fast_exp2(m - m_new);
         float psum = 0.f;
-        uint32_t pk[64];
+        uint32_t pk[TK / 2];
 #pragma unroll
-        for (int k = 0; k < 128; k += 2) {
+        for (int k = 0; k < TK; k += 2) {
           const float p0 = fast_exp2(t[k] - m_new);
           const float p1 = fast_exp2(t[k + 1] - m_new);
           psum += p0 + p1;
@@ -275,18 +290,21 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_wait(&pv_done[r_in], (g & 1u) ^ 1u, ws, 61, r_in);
         tc_fence_after_sync();
         if (j > 0 && __any_sync(0xffffffffu, alpha < 1.0f)) {
-          uint32_t ov[32];
           const uint32_t oa = tmem_addr(tO, quad, r_in * kAD);
-          tmem_ld32(oa, ov);
-          tmem_ld_wait();
 #pragma unroll
-          for (int d = 0; d < 32; ++d) ov[d] = __float_as_uint(__uint_as_float(ov[d]) * alpha);
-          tmem_st32(oa, ov);
+          for (int dc = 0; dc < kAD / 32; ++dc) {
+            uint32_t ov[32];
+            tmem_ld32(oa + dc * 32, ov);
+            tmem_ld_wait();
+#pragma unroll
+            for (int d = 0; d < 32; ++d) ov[d] = __float_as_uint(__uint_as_float(ov[d]) * alpha);
+            tmem_st32(oa + dc * 32, ov);
+          }
           tmem_st_wait();
         }
         uint8_t* ps = sP + r_in * kAPBytes;
 #pragma unroll
-        for (int c16 = 0; c16 < 16; ++c16) {
+        for (int c16 = 0; c16 < TK / 8; ++c16) {
           const uint4 u = make_uint4(pk[c16 * 4], pk[c16 * 4 + 1], pk[c16 * 4 + 2], pk[c16 * 4 + 3]);
           *reinterpret_cast<uint4*>(ps + (c16 >> 3) * 16384 + swz128_offset(qrow, c16 & 7)) = u;
         }
@@ -299,38 +317,42 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_wait(&pv_done[r_in], (gk + T - 1) & 1u, ws, 62, r_in);
       tc_fence_after_sync();
       {
-        uint32_t ov[32];
-        tmem_ld32(tmem_addr(tO, quad, r_in * kAD), ov);
-        tmem_ld_wait();
-        if (r < p.rows && qi < p.Nq) {
-          const float inv = 1.0f / l;
-          const long long in_row = static_cast<long long>(r) * p.Nq + qi;
-          const long long out_row = p.transpose_out ? (static_cast<long long>(qi) * p.rows + r) : in_row;
-          float f[32];
+        const bool ok = r < p.rows && qi < p.Nq;
+        const float inv = 1.0f / l;
+        const long long in_row = static_cast<long long>(r) * p.Nq + qi;
+        const long long out_row = p.transpose_out ? (static_cast<long long>(qi) * p.rows + r) : in_row;
 #pragma unroll
-          for (int d = 0; d < 32; ++d) f[d] = __uint_as_float(ov[d]) * inv;
-          if (p.gate != nullptr) {
-            const uint4* gp = reinterpret_cast<const uint4*>(p.gate + in_row * (p.H * kAD) + h * kAD);
+        for (int dc = 0; dc < kAD / 32; ++dc) {
+          uint32_t ov[32];
+          tmem_ld32(tmem_addr(tO, quad, r_in * kAD + dc * 32), ov);
+          tmem_ld_wait();
+          if (ok) {
+            float f[32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const uint4 u = __ldg(gp + c);
-              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+            for (int d = 0; d < 32; ++d) f[d] = __uint_as_float(ov[d]) * inv;
+            if (p.gate != nullptr) {
+              const uint4* gp = reinterpret_cast<const uint4*>(p.gate + in_row * (p.H * kAD) + h * kAD + dc * 32);
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                f[c * 8 + 2 * e] *= bf16_lo(w[e]);
-                f[c * 8 + 2 * e + 1] *= bf16_hi(w[e]);
+              for (int c = 0; c < 4; ++c) {
+                const uint4 u = __ldg(gp + c);
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  f[c * 8 + 2 * e] *= bf16_lo(w[e]);
+                  f[c * 8 + 2 * e + 1] *= bf16_hi(w[e]);
+                }
               }
             }
-          }
-          uint4* op = reinterpret_cast<uint4*>(p.out + out_row * (p.H * kAD) + h * kAD);
+            uint4* op = reinterpret_cast<uint4*>(p.out + out_row * (p.H * kAD) + h * kAD + dc * 32);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint4 u;
-            u.x = pack_bf16x2(f[c * 8], f[c * 8 + 1]);
-            u.y = pack_bf16x2(f[c * 8 + 2], f[c * 8 + 3]);
-            u.z = pack_bf16x2(f[c * 8 + 4], f[c * 8 + 5]);
-            u.w = pack_bf16x2(f[c * 8 + 6], f[c * 8 + 7]);
-            op[c] = u;
+            for (int c = 0; c < 4; ++c) {
+              uint4 u;
+              u.x = pack_bf16x2(f[c * 8], f[c * 8 + 1]);
+              u.y = pack_bf16x2(f[c * 8 + 2], f[c * 8 + 3]);
+              u.z = pack_bf16x2(f[c * 8 + 4], f[c * 8 + 5]);
+              u.w = pack_bf16x2(f[c * 8 + 6], f[c * 8 + 7]);
+              op[c] = u;
+            }
           }
         }
       }
@@ -347,35 +369,30 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-constexpr int kASmemBytes = 2 * kAQBytes + kAStages * kAStageBytes + 2 * kAPBytes + 256 + 1024;
-
-}  // namespace ubm
-
-// q, k, v, gate, out: bf16 [rows][N*][H*32] (innermost contiguous; row strides given in elements).
-// bias: bf16 [H][Nq][ldb] (ldb multiple of 8) or null.  q must carry the factor log2(e)/sqrt(32) and
-// bias the factor log2(e).  transpose_out writes out[q][r] instead of out[r][q].
-extern "C" int ubm_attention_d32(const void* q, const void* k, const void* v, const void* bias, const void* gate,
-                                 void* out, int rows, int Nq, int Nk, int H, long long ldb, int transpose_out,
-                                 void* status, void* stream) {
-  using namespace ubm;
-  if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0) return UBM_ERR_ARGUMENT;
-  if (bias != nullptr && (ldb < Nk || (ldb & 7))) return UBM_ERR_ARGUMENT;
-  const uint64_t hd = (uint64_t)H * kAD;
+template <int D, int TK>
+static int launch_attention(const void* q, const void* k, const void* v, const void* bias, const void* gate, void* out,
+                            int rows, int Nq, int Nk, int H, long long ldb, long long ld_in, int transpose_out,
+                            void* status, void* stream) {
+  using Cfg = AttnCfg<D, TK>;
+  const uint64_t hd = (uint64_t)H * D;
+  const uint64_t ldi = ld_in > 0 ? (uint64_t)ld_in : hd;  // row stride of q / k / v in elements
+  if (ldi < hd || (ldi & 7)) return UBM_ERR_ARGUMENT;
+  const CUtensorMapSwizzle swz = (D == 32) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
   CUtensorMap tmQ, tmK, tmV, tmB;
   {
     uint64_t d[3] = {hd, (uint64_t)Nq, (uint64_t)rows};
-    uint64_t s[2] = {hd * 2, hd * 2 * (uint64_t)Nq};
-    uint32_t b[3] = {kAD, kATile, 1};
-    int rc = make_tmap(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d, s, b, CU_TENSOR_MAP_SWIZZLE_64B);
+    uint64_t s[2] = {ldi * 2, ldi * 2 * (uint64_t)Nq};
+    uint32_t b[3] = {(uint32_t)D, kATile, 1};
+    int rc = make_tmap(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d, s, b, swz);
     if (rc) return rc;
   }
   {
     uint64_t d[3] = {hd, (uint64_t)Nk, (uint64_t)rows};
-    uint64_t s[2] = {hd * 2, hd * 2 * (uint64_t)Nk};
-    uint32_t b[3] = {kAD, kATile, 1};
-    int rc = make_tmap(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d, s, b, CU_TENSOR_MAP_SWIZZLE_64B);
+    uint64_t s[2] = {ldi * 2, ldi * 2 * (uint64_t)Nk};
+    uint32_t b[3] = {(uint32_t)D, (uint32_t)TK, 1};
+    int rc = make_tmap(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d, s, b, swz);
     if (rc) return rc;
-    rc = make_tmap(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d, s, b, CU_TENSOR_MAP_SWIZZLE_64B);
+    rc = make_tmap(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d, s, b, swz);
     if (rc) return rc;
   }
   if (bias != nullptr) {
@@ -398,13 +415,38 @@ extern "C" int ubm_attention_d32(const void* q, const void* k, const void* v, co
   p.has_bias = bias != nullptr ? 1 : 0;
   p.status = static_cast<KernelStatus*>(status);
   p.n_qt = (Nq + kATile - 1) / kATile;
-  p.n_kt = (Nk + kATile - 1) / kATile;
+  p.n_kt = (Nk + TK - 1) / TK;
   p.n_rp = (rows + 1) / 2;
   p.num_items = p.n_qt * p.n_rp * H;
-  int rc = set_smem(attention_kernel, kASmemBytes);
+  auto kern = attention_kernel<D, TK>;
+  int rc = set_smem(kern, Cfg::kSmemBytes);
   if (rc) return rc;
   const int grid = p.num_items < sm_count() ? p.num_items : sm_count();
-  attention_kernel<<<grid, 384, kASmemBytes, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmB, p);
+  kern<<<grid, 384, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmB, p);
   UBM_CHECK_LAUNCH("attention_kernel");
   return UBM_OK;
+}
+
+}  // namespace ubm
+
+// q, k, v, gate, out: bf16 [rows][N*][H*D] (innermost contiguous).  bias: bf16 [H][Nq][ldb] (ldb multiple
+// of 8) or null.  q must carry the factor log2(e)/sqrt(d) and bias the factor log2(e).  transpose_out
+// writes out[q][r] instead of out[r][q].  ld_in: row stride of q / k / v in elements (0 = H*D), so the
+// three may be column slices of one projection output.  D = 32 (ubm_attention_d32) or 64 (ubm_attention_d64).
+extern "C" int ubm_attention_d32(const void* q, const void* k, const void* v, const void* bias, const void* gate,
+                                 void* out, int rows, int Nq, int Nk, int H, long long ldb, long long ld_in,
+                                 int transpose_out, void* status, void* stream) {
+  if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0) return ubm::UBM_ERR_ARGUMENT;
+  if (bias != nullptr && (ldb < Nk || (ldb & 7))) return ubm::UBM_ERR_ARGUMENT;
+  return ubm::launch_attention<32, 128>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
+                                        status, stream);
+}
+
+extern "C" int ubm_attention_d64(const void* q, const void* k, const void* v, const void* bias, const void* gate,
+                                 void* out, int rows, int Nq, int Nk, int H, long long ldb, long long ld_in,
+                                 int transpose_out, void* status, void* stream) {
+  if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0) return ubm::UBM_ERR_ARGUMENT;
+  if (bias != nullptr && (ldb < Nk || (ldb & 7))) return ubm::UBM_ERR_ARGUMENT;
+  return ubm::launch_attention<64, 64>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
+                                       status, stream);
 }

@@ -147,7 +147,8 @@ def trimul_fused(z: torch.Tensor, mask: Optional[torch.Tensor], w: TrimulPacked,
 
 
 # ------------------------------------------------------------------------------------------
-native.declare("ubm_attention_d32", [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_ll, c_int, c_void_p, c_void_p])
+native.declare("ubm_attention_d32", [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_ll, c_ll, c_int, c_void_p, c_void_p])
+native.declare("ubm_attention_d64", [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_ll, c_ll, c_int, c_void_p, c_void_p])
 
 LOG2E = 1.4426950408889634
 
@@ -188,15 +189,72 @@ class TriattPacked:
                    None if b_o is None else b_o.detach().float().contiguous(), heads)
 
 
-def attention_d32(q, k, v, bias, gate, out, rows: int, Nq: int, Nk: int, H: int, ldb: int = 0,
-                  transpose_out: bool = False):
-    """Raw launch of the tcgen05 attention kernel (see csrc/attention_sm100.cu for the layout)."""
+def attention(q, k, v, bias, gate, out, rows: int, Nq: int, Nk: int, H: int, D: int = 32, ldb: int = 0,
+              ld_in: int = 0, transpose_out: bool = False):
+    """Raw launch of the tcgen05 attention kernel (see csrc/attention_sm100.cu for the layout).
+    D is the (padded) head dimension, 32 or 64; ld_in the row stride of q / k / v in elements."""
     st = native.status_tensor(q.device)
-    rc = native.lib().ubm_attention_d32(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(bias),
-                                        native.ptr(gate), native.ptr(out), rows, Nq, Nk, H, ldb,
-                                        1 if transpose_out else 0, native.ptr(st), native.current_stream(q.device))
-    native.check(rc, "ubm_attention_d32")
+    fn = native.lib().ubm_attention_d32 if D == 32 else native.lib().ubm_attention_d64
+    if D not in (32, 64):
+        raise ValueError("attention kernel supports head dimensions 32 and 64 (pad smaller heads)")
+    rc = fn(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(bias), native.ptr(gate), native.ptr(out), rows,
+            Nq, Nk, H, ldb, ld_in, 1 if transpose_out else 0, native.ptr(st), native.current_stream(q.device))
+    native.check(rc, f"ubm_attention_d{D}")
     return out
+
+
+def attention_d32(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb: int = 0, transpose_out: bool = False):
+    return attention(q, k, v, bias, gate, out, rows, Nq, Nk, H, 32, ldb, 0, transpose_out)
+
+
+@dataclass
+class ApbPacked:
+    """Weights of attention-with-pair-bias for the fused path: heads padded to the kernel's head
+    dimension (zero rows / columns), q scaled by log2(e)/sqrt(d), q|k|v stacked into one projection."""
+    wqkv: torch.Tensor      # bf16 [3*H*Dp, c]
+    bqkv: torch.Tensor      # fp32 [3*H*Dp]
+    wg: torch.Tensor        # bf16 [H*Dp, c]
+    wo: torch.Tensor        # bf16 [c, H*Dp]
+    H: int
+    Dp: int
+
+    @classmethod
+    def pack(cls, w_q, b_q, w_k, w_v, w_g, w_o, heads: int) -> "ApbPacked":
+        c_out, c = w_q.shape
+        D = c_out // heads
+        Dp = 32 if D <= 32 else 64
+        if D > 64:
+            raise ValueError("head dimension above 64 is not supported by the attention kernel")
+
+        def pad_rows(W, scale=1.0):
+            Wp = torch.zeros((heads, Dp, W.shape[1]), dtype=torch.float32, device=W.device)
+            Wp[:, :D] = W.detach().float().view(heads, D, -1) * scale
+            return Wp.view(heads * Dp, -1)
+
+        qs = LOG2E / (D ** 0.5)
+        wqkv = torch.cat([pad_rows(w_q, qs), pad_rows(w_k), pad_rows(w_v)], 0).to(torch.bfloat16).contiguous()
+        bq = torch.zeros((heads, Dp), device=w_q.device)
+        if b_q is not None:
+            bq[:, :D] = b_q.detach().float().view(heads, D) * qs
+        bqkv = torch.cat([bq.view(-1), torch.zeros(2 * heads * Dp, device=w_q.device)]).contiguous()
+        wg = pad_rows(w_g).to(torch.bfloat16).contiguous()
+        wo = torch.zeros((w_o.shape[0], heads, Dp), dtype=torch.float32, device=w_o.device)
+        wo[:, :, :D] = w_o.detach().float().view(w_o.shape[0], heads, D)
+        return cls(wqkv, bqkv, wg, wo.view(w_o.shape[0], heads * Dp).to(torch.bfloat16).contiguous(), heads, Dp)
+
+
+def apb_fused(x: torch.Tensor, w: ApbPacked, bias_planes: torch.Tensor, ldb: int) -> torch.Tensor:
+    """Gated attention with pair bias on rows x: bf16 [B, N, c]; bias_planes: bf16 [H, N, ldb] holding
+    log2(e) * bias (shared by the B rows).  Returns proj_o(sigmoid(proj_g x) * attention) as [B, N, c]."""
+    B, N, c = x.shape
+    HD = w.H * w.Dp
+    x2 = x.reshape(B * N, c)
+    qkv = _gemm.gemm(x2, w.wqkv, bias=w.bqkv)
+    g = _gemm.gemm(x2, w.wg, act="sigmoid")
+    o = torch.empty((B * N, HD), dtype=torch.bfloat16, device=x.device)
+    attention(qkv[:, :HD], qkv[:, HD:2 * HD], qkv[:, 2 * HD:], bias_planes, g, o, rows=B, Nq=N, Nk=N, H=w.H,
+              D=w.Dp, ldb=ldb, ld_in=3 * HD)
+    return _gemm.gemm(o, w.wo).view(B, N, -1)
 
 
 def triangle_attention_fused(z: torch.Tensor, w: TriattPacked, starting: bool, residual: bool = True,

@@ -3,6 +3,7 @@ planes, AdaLN, gated residual, SwiGLU.  Each wrapper has the same signature as i
 statement in :mod:`ops.reference` where one exists."""
 from __future__ import annotations
 
+import weakref
 from typing import Optional
 
 import torch
@@ -45,8 +46,10 @@ def pair_head_bias(z: torch.Tensor, ln_w, ln_b, w, scale: float = 1.0, transpose
     N = z.shape[0]
     H = w.shape[0]
     Np = (N + 7) // 8 * 8
-    key = (w.data_ptr(), w._version, None if ln_w is None else ln_w._version, float(scale))
-    packed = _HB_CACHE.get(key)
+    # the cache entry is tied to the live weight tensor object (a freed tensor's address may be reused)
+    key = (id(w), w._version, None if ln_w is None else ln_w._version, float(scale), str(z.device))
+    entry = _HB_CACHE.get(key)
+    packed = entry[1] if entry is not None and entry[0]() is w else None
     if packed is None:
         gam = torch.ones(128, device=z.device) if ln_w is None else ln_w.detach().float()
         wf = (w.detach().float() * gam[None, :] * scale).contiguous()
@@ -56,7 +59,7 @@ def pair_head_bias(z: torch.Tensor, ln_w, ln_b, w, scale: float = 1.0, transpose
         packed = (wf, colsum, colbias)
         if len(_HB_CACHE) > 4096:
             _HB_CACHE.clear()
-        _HB_CACHE[key] = packed
+        _HB_CACHE[key] = (weakref.ref(w), packed)
     wf, colsum, colbias = packed
     if out is None:
         out = torch.zeros((H, N, Np), dtype=torch.bfloat16, device=z.device) if Np != N else \
