@@ -1,0 +1,87 @@
+"""Row-sharded statements equal the dense statements (rank threads on CPU; P in {2, 3, 4}, uneven N)."""
+import pytest
+import torch
+
+from uplifting_biomolecular_modeling_b200.core.testing import RankFailure, run_ranks
+from uplifting_biomolecular_modeling_b200.models import pairformer
+from uplifting_biomolecular_modeling_b200.parallel import comm as C
+from uplifting_biomolecular_modeling_b200.parallel import rowpair
+from uplifting_biomolecular_modeling_b200.parallel.layout import Layout
+
+
+def test_layout_bounds():
+    assert Layout(10, 3).bounds() == [(0, 4), (4, 7), (7, 10)]
+    assert Layout(1000, 4, align=128).bounds() == [(0, 256), (256, 512), (512, 768), (768, 1000)]
+    assert Layout(100, 4, align=128).bounds() == [(0, 100), (100, 100), (100, 100), (100, 100)]
+    assert Layout(100, 4, align=128).empty_ranks() == [1, 2, 3]
+    assert Layout(10, 3).owner(6) == 1 and Layout(10, 3).max_count() == 4
+
+
+@pytest.mark.parametrize("P,N", [(2, 12), (3, 11), (4, 13)])
+def test_transpose_shard(P, N):
+    z = torch.randn(N, N, 3, dtype=torch.float64)
+    lay = Layout(N, P)
+
+    def fn(comm):
+        zt = rowpair.transpose_shard(rowpair.shard_rows(z, lay, comm.rank), lay, comm)
+        a, b = lay.rows(comm.rank)
+        assert torch.equal(zt, z.transpose(0, 1)[a:b])
+        return True
+
+    assert all(run_ranks(P, fn))
+
+
+@pytest.mark.parametrize("P,N", [(2, 16), (3, 13)])
+def test_pairformer_layer_sharded_equals_dense(P, N):
+    torch.manual_seed(0)
+    layer = pairformer.PairformerLayer(c_s=32, c_z=16, heads=4, pair_heads=2).double().eval()
+    s = torch.randn(1, N, 32, dtype=torch.float64)
+    z = torch.randn(1, N, N, 16, dtype=torch.float64)
+    with torch.no_grad():
+        s_ref, z_ref = layer(s, z, None, None)
+    lay = Layout(N, P)
+
+    def fn(comm):
+        with torch.no_grad():
+            zl = rowpair.shard_rows(z[0], lay, comm.rank)
+            s2, zl = rowpair.pairformer_layer_rows(layer, s, zl, lay, comm, comm.rank)
+            zfull = rowpair.gather_pair(zl, comm)
+        return s2, zfull
+
+    for s2, zfull in run_ranks(P, fn):
+        assert torch.allclose(zfull, z_ref[0], atol=1e-9, rtol=1e-9)
+        assert torch.allclose(s2, s_ref, atol=1e-5, rtol=1e-5)      # single track runs in fp32 by design
+
+
+def test_solo_comm_is_identity_and_failures_surface():
+    c = C.SoloComm()
+    t = torch.arange(6.).view(3, 2)
+    assert torch.equal(c.all_gather_rows(t), t) and c.all_reduce_scalar(3.0) == 3.0
+
+    def bad(comm):
+        if comm.rank == 1:
+            raise ValueError("boom")
+        comm.barrier()
+
+    with pytest.raises(RankFailure) as ei:
+        run_ranks(2, bad, timeout_s=20)
+    assert "boom" in str(ei.value)
+
+    def guard(comm):
+        comm.check_replicated(torch.ones(3) * (1 + comm.rank), "weights")
+
+    with pytest.raises(RankFailure) as ei:
+        run_ranks(2, guard, timeout_s=20)
+    assert "replication guard" in str(ei.value)
+
+
+def test_host_wait_times_out_by_name():
+    hub = C.ThreadHub(2)
+
+    def fn(comm):
+        if comm.rank == 0:
+            with pytest.raises(C.CommAborted):
+                comm.host_wait("never", timeout_s=0.3)
+        return True
+
+    assert all(run_ranks(2, fn, hub=hub))

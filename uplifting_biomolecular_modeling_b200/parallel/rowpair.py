@@ -1,0 +1,163 @@
+"""Row-sharded pair stack ("rowpair"): one prediction over P GPUs of one host (``big --n_gpu P``).
+
+Every rank owns rows [r0, r1) of the pair tensor z[N, N, C] from its birth to its last reader; the
+single representation and the MSA are replicated.  Each sharded statement equals its dense statement:
+the full-k sum of every output element happens inside one matmul on one rank - no split-K across
+ranks, no partial-sum all-reduce (the reference's P-invariance rule,
+common/opt_core/opt_core/mem/rowpair/trimul.py:15-18).
+
+What crosses ranks, per Pairformer block (collective sites C1-C7 of the reference,
+common/opt_core/opt_core/mem/rowpair/dist.py, ring.py, triatt.py, trimul.py):
+
+* triangle multiplication, outgoing : all-gather of the projected ``b`` rows feeding a_ik . b_jk
+* triangle multiplication, incoming : transpose of z (all-to-all), then the outgoing schedule on z^T rows
+* triangle attention, starting node : all-gather of the per-head pair bias rows
+* triangle attention, ending node   : transpose (all-to-all), starting-node schedule, transpose back
+* single attention with pair bias   : local query rows, all-gather of the updated single rows
+
+``impl="reference"`` runs plain PyTorch statements on the shards through the :class:`Comm` surface
+(the NCCL baseline, also what the CPU tests check against the dense model); ``impl="fused"`` runs the
+sm_100a kernels on the shards and lets the contraction GEMM and the attention kernel read the other
+ranks' projected rows / bias planes straight from peer memory (see ``parallel.symm`` and
+``ops.peer``), so the gather overlaps the math tile by tile.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from ..ops import reference as R
+from .comm import Comm
+from .layout import Layout
+
+
+# ------------------------------------------------------------------------------- data movement
+def shard_rows(z: torch.Tensor, layout: Layout, rank: int) -> torch.Tensor:
+    a, b = layout.rows(rank)
+    return z[a:b].contiguous()
+
+
+def transpose_shard(z_loc: torch.Tensor, layout: Layout, comm: Comm) -> torch.Tensor:
+    """Rows [r0, r1) of z -> rows [r0, r1) of z^T (z^T[i, k] = z[k, i]) by one all-to-all of blocks."""
+    parts = [z_loc[:, a:b].contiguous() for (a, b) in layout.bounds()]          # to rank q: my rows x its columns
+    got = comm.all_to_all(parts)                                                # from q: its rows x my columns
+    col = torch.cat(got, dim=0)                                                 # [N, R_p, ...]
+    return col.transpose(0, 1).contiguous()
+
+
+# ------------------------------------------------------------------------------- sharded statements
+def trimul_rows(z_loc, mask_loc, mod, layout: Layout, comm: Comm, outgoing: bool = True, residual: bool = True,
+                mask_t_loc=None):
+    """Triangle multiplication on local rows.  ``mod`` is a models.pairformer.TriangleMultiplication."""
+    w = mod
+    x_in = R.layer_norm(z_loc, w.norm_in.weight, w.norm_in.bias)
+    if outgoing:
+        src, src_mask = x_in, mask_loc
+    else:
+        zt = transpose_shard(z_loc, layout, comm)
+        src = R.layer_norm(zt, w.norm_in.weight, w.norm_in.bias)
+        src_mask = mask_t_loc
+    ab = F.linear(src, w.p_in.weight) * torch.sigmoid(F.linear(src, w.g_in.weight))
+    if src_mask is not None:
+        ab = ab * src_mask.unsqueeze(-1).to(ab.dtype)
+    a, b = torch.chunk(ab.float(), 2, dim=-1)
+    b_all = comm.all_gather_rows(b.contiguous())                                # [N, N, c]
+    x = torch.einsum("ikd,jkd->ijd", a, b_all).to(z_loc.dtype)
+    out = F.linear(R.layer_norm(x, w.norm_out.weight, w.norm_out.bias), w.p_out.weight) * \
+        torch.sigmoid(F.linear(x_in, w.g_out.weight))
+    return z_loc + out if residual else out
+
+
+def triatt_rows(z_loc, mod, layout: Layout, comm: Comm, starting: bool = True, residual: bool = True):
+    """Triangle attention on local rows.  ``mod`` is a models.pairformer.TriangleAttention."""
+    m = mod.mha
+    H = mod.heads
+    src = z_loc if starting else transpose_shard(z_loc, layout, comm)
+    n = R.layer_norm(src, mod.layer_norm.weight, mod.layer_norm.bias)
+    bias_loc = F.linear(n, mod.linear.weight)                                   # [R, N, H]
+    bias = comm.all_gather_rows(bias_loc.contiguous()).permute(2, 0, 1)         # [H, N, N]
+    Rr, N, _ = n.shape
+    q = F.linear(n, m.linear_q.weight).view(Rr, N, H, -1).transpose(1, 2)
+    k = F.linear(n, m.linear_k.weight).view(Rr, N, H, -1).transpose(1, 2)
+    v = F.linear(n, m.linear_v.weight).view(Rr, N, H, -1).transpose(1, 2)
+    g = torch.sigmoid(F.linear(n, m.linear_g.weight, m.linear_g.bias))
+    o = R.attention_with_bias(q, k, v, bias.unsqueeze(0)).transpose(1, 2).reshape(Rr, N, -1)
+    o = F.linear(o * g, m.linear_o.weight, m.linear_o.bias)
+    if not starting:
+        o = transpose_shard(o, layout, comm)
+    return z_loc + o if residual else o
+
+
+def transition_rows(z_loc, mod, residual: bool = True):
+    return mod(z_loc, residual=residual)
+
+
+def apb_rows(s, z_loc, mod, pre_norm, layout: Layout, comm: Comm, rank: int):
+    """Single attention with pair bias: queries of the local token rows, keys of all tokens (s is
+    replicated), bias from the local pair rows; the updated rows are all-gathered."""
+    a, b = layout.rows(rank)
+    s32 = s.float()
+    sn = F.layer_norm(s32, (s32.shape[-1],), pre_norm.weight.float(), pre_norm.bias.float())
+    H, D = mod.heads, mod.head_dim
+    N = sn.shape[1]
+    ql = sn[:, a:b]
+    q = F.linear(ql, mod.proj_q.weight.float(), mod.proj_q.bias.float()).view(1, b - a, H, D).transpose(1, 2)
+    k = F.linear(sn, mod.proj_k.weight.float()).view(1, N, H, D).transpose(1, 2)
+    v = F.linear(sn, mod.proj_v.weight.float()).view(1, N, H, D).transpose(1, 2)
+    g = torch.sigmoid(F.linear(ql, mod.proj_g.weight.float()))
+    zl = z_loc.float()
+    bias = F.linear(R.layer_norm(zl, mod.proj_z[0].weight.float(), mod.proj_z[0].bias.float()),
+                    mod.proj_z[1].weight.float()).permute(2, 0, 1).unsqueeze(0)           # [1, H, R, N]
+    o = R.attention_with_bias(q, k, v, bias).transpose(1, 2).reshape(1, b - a, H * D)
+    upd_loc = F.linear(g * o, mod.proj_o.weight.float())[0]                              # [R, c_s]
+    upd = comm.all_gather_rows(upd_loc.contiguous()).unsqueeze(0)
+    return upd
+
+
+def pairformer_layer_rows(layer, s, z_loc, layout: Layout, comm: Comm, rank: int, mask_loc=None, mask_t_loc=None):
+    """One PairformerLayer on a row shard (block order as in the dense layer)."""
+    z_loc = trimul_rows(z_loc, mask_loc, layer.tri_mul_out, layout, comm, True, True)
+    z_loc = trimul_rows(z_loc, mask_loc, layer.tri_mul_in, layout, comm, False, True, mask_t_loc)
+    z_loc = triatt_rows(z_loc, layer.tri_att_start, layout, comm, True, True)
+    z_loc = triatt_rows(z_loc, layer.tri_att_end, layout, comm, False, True)
+    z_loc = transition_rows(z_loc, layer.transition_z, True)
+    if layer.no_seq:
+        return s, z_loc
+    s32 = s.float() + apb_rows(s, z_loc, layer.attention, layer.pre_norm_s, layout, comm, rank)
+    t = layer.transition_s
+    s32 = s32 + R.transition(s32, t.norm.weight.float(), t.norm.bias.float(), t.fc1.weight.float(),
+                             t.fc2.weight.float(), t.fc3.weight.float())
+    return s32.to(s.dtype), z_loc
+
+
+def pair_stack_rows(module, s, z_loc, layout: Layout, comm: Comm, rank: int):
+    for layer in module.layers:
+        s, z_loc = pairformer_layer_rows(layer, s, z_loc, layout, comm, rank)
+    return s, z_loc
+
+
+def opm_rows(m, mask, mod, layout: Layout, rank: int):
+    """Outer product mean: output rows [r0, r1) only (m replicated, so no traffic at all; contraction over
+    the MSA depth is whole per (i, j))."""
+    a0, a1 = layout.rows(rank)
+    n = R.layer_norm(m, mod.norm.weight, mod.norm.bias)
+    mk = mask.unsqueeze(-1).to(n.dtype)
+    a = (F.linear(n, mod.proj_a.weight) * mk)[0, :, a0:a1]
+    b = (F.linear(n, mod.proj_b.weight) * mk)[0]
+    num = torch.einsum("sic,sjd->ijcd", a.float(), b.float())
+    cnt = torch.einsum("si,sj->ij", mask[0, :, a0:a1].float(), mask[0].float()).clamp(min=1.0)
+    zz = (num / cnt[..., None, None]).reshape(a1 - a0, b.shape[1], -1).to(m.dtype)
+    return F.linear(zz, mod.proj_o.weight, mod.proj_o.bias)
+
+
+def gather_pair(z_loc, comm: Comm) -> torch.Tensor:
+    return comm.all_gather_rows(z_loc)
+
+
+# ------------------------------------------------------------------------------- memory model
+def shard_bytes(n: int, c: int, elt: int, world: int) -> int:
+    """u = N^2 * C * elt / P, the unit of the per-rank peak model peak = a(N) + b(N) / P
+    (common/opt_core/opt_core/mem/rowpair/API.md:174)."""
+    return n * n * c * elt // world
