@@ -51,12 +51,43 @@ struct AttnParams {
   int has_bias;
   KernelStatus* status;
   int n_qt, n_kt, n_rp, num_items;
+  // peer mode: the bias rows (queries) are row shards owned by several GPUs; query tiles are enumerated
+  // shard by shard and each tile's bias comes through that GPU's tensor map
+  int npeers;
+  int peer_tile0[9];
+  int peer_row0[8];
+  int peer_rows[8];
 };
 
-template <int D, int TK>
+constexpr int kAMaxPeers = 8;
+struct BiasPeerMaps {
+  CUtensorMap m[kAMaxPeers];
+};
+
+// query tile -> (shard, first global query, query limit, row offset inside the shard)
+__device__ __forceinline__ void decode_qtile(const AttnParams& p, int qt, int& q, int& q_base, int& q_limit,
+                                             int& local_row) {
+  if (p.npeers == 0) {
+    q = 0;
+    q_base = qt * kATile;
+    q_limit = p.Nq;
+    local_row = q_base;
+    return;
+  }
+  q = 0;
+#pragma unroll
+  for (int i = 1; i < kAMaxPeers; ++i)
+    if (i < p.npeers && qt >= p.peer_tile0[i]) q = i;
+  local_row = (qt - p.peer_tile0[q]) * kATile;
+  q_base = p.peer_row0[q] + local_row;
+  q_limit = p.peer_row0[q] + p.peer_rows[q];
+}
+
+template <int D, int TK, bool PEER>
 __global__ void __launch_bounds__(384, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmB, AttnParams p) {
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ BiasPeerMaps peers, AttnParams p) {
   using Cfg = AttnCfg<D, TK>;
   constexpr int kAD = D;
   constexpr int kAQBytes = Cfg::kQBytes;
@@ -132,9 +163,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int r0 = rp * 2;
         mbar_wait(q_empty, (item_cnt & 1u) ^ 1u, ws, 51);
         if (*abort_flag) break;
+        int pq, q_base, q_limit, lrow;
+        decode_qtile(p, qt, pq, q_base, q_limit, lrow);
         mbar_expect_tx(q_full, 2 * kAQBytes);
-        tma_load_3d(sQ, &tmQ, q_full, h * kAD, qt * kATile, r0);
-        tma_load_3d(sQ + kAQBytes, &tmQ, q_full, h * kAD, qt * kATile, r0 + 1);
+        tma_load_3d(sQ, &tmQ, q_full, h * kAD, q_base, r0);
+        tma_load_3d(sQ + kAQBytes, &tmQ, q_full, h * kAD, q_base, r0 + 1);
         for (int j = 0; j < T; ++j, ++gk) {
           const int s = gk & 1;
           mbar_wait(&kv_empty[s], ((gk >> 1) & 1u) ^ 1u, ws, 52, s);
@@ -147,8 +180,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tma_load_3d(st + 3 * kAKVBytes, &tmV, &kv_full[s], h * kAD, j * TK, r0 + 1);
           if (p.has_bias) {
 #pragma unroll
-            for (int hb = 0; hb < TK / 64; ++hb)
-              tma_load_3d(st + 4 * kAKVBytes + hb * 16384, &tmB, &kv_full[s], j * TK + hb * 64, qt * kATile, h);
+            for (int hb = 0; hb < TK / 64; ++hb) {
+              // peer mode: the bias rows of this query tile live on GPU pq (plain TMA load, no multicast)
+              const CUtensorMap* bm = PEER ? &peers.m[pq] : &tmB;
+              tma_load_3d(st + 4 * kAKVBytes + hb * 16384, bm, &kv_full[s], j * TK + hb * 64, lrow, h);
+            }
           }
         }
         if (*abort_flag) break;
@@ -227,7 +263,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int qt = tmp % p.n_qt;
       const int h = tmp / p.n_qt;
       const int r = rp * 2 + r_in;
-      const int qi = qt * kATile + qrow;
+      int pq, q_base, q_limit, lrow;
+      decode_qtile(p, qt, pq, q_base, q_limit, lrow);
+      const int qi = q_base + qrow;
       float m = kNegBig, l = 0.f;
       for (int j = 0; j < T; ++j) {
         const uint32_t g = gk + j;
@@ -317,7 +355,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_wait(&pv_done[r_in], (gk + T - 1) & 1u, ws, 62, r_in);
       tc_fence_after_sync();
       {
-        const bool ok = r < p.rows && qi < p.Nq;
+        const bool ok = r < p.rows && qi < q_limit;
         const float inv = 1.0f / l;
         const long long in_row = static_cast<long long>(r) * p.Nq + qi;
         const long long out_row = p.transpose_out ? (static_cast<long long>(qi) * p.rows + r) : in_row;
@@ -372,7 +410,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 template <int D, int TK>
 static int launch_attention(const void* q, const void* k, const void* v, const void* bias, const void* gate, void* out,
                             int rows, int Nq, int Nk, int H, long long ldb, long long ld_in, int transpose_out,
-                            void* status, void* stream) {
+                            void* status, void* stream, int npeers = 0, const void* const* bias_ptrs = nullptr,
+                            const int* peer_rows = nullptr, long long peer_head_stride = 0) {
   using Cfg = AttnCfg<D, TK>;
   const uint64_t hd = (uint64_t)H * D;
   const uint64_t ldi = ld_in > 0 ? (uint64_t)ld_in : hd;  // row stride of q / k / v in elements
@@ -417,12 +456,45 @@ static int launch_attention(const void* q, const void* k, const void* v, const v
   p.n_qt = (Nq + kATile - 1) / kATile;
   p.n_kt = (Nk + TK - 1) / TK;
   p.n_rp = (rows + 1) / 2;
+  BiasPeerMaps maps;
+  for (int i = 0; i < kAMaxPeers; ++i) maps.m[i] = tmQ;
+  if (npeers > 0) {
+    if (npeers > kAMaxPeers || bias_ptrs == nullptr || peer_rows == nullptr) return UBM_ERR_ARGUMENT;
+    p.npeers = npeers;
+    p.has_bias = 1;
+    int row = 0, tile = 0;
+    for (int i = 0; i < npeers; ++i) {
+      p.peer_tile0[i] = tile;
+      p.peer_row0[i] = row;
+      p.peer_rows[i] = peer_rows[i];
+      if (peer_rows[i] > 0) {
+        uint64_t d[3] = {(uint64_t)Nk, (uint64_t)peer_rows[i], (uint64_t)H};
+        uint64_t s[2] = {(uint64_t)ldb * 2, (uint64_t)peer_head_stride * 2};
+        uint32_t b[3] = {64, kATile, 1};
+        int rc = make_tmap(&maps.m[i], bias_ptrs[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d, s, b,
+                           CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+      }
+      row += peer_rows[i];
+      tile += (peer_rows[i] + kATile - 1) / kATile;
+    }
+    p.peer_tile0[npeers] = tile;
+    if (row != Nq) return UBM_ERR_ARGUMENT;
+    p.n_qt = tile;
+  }
   p.num_items = p.n_qt * p.n_rp * H;
-  auto kern = attention_kernel<D, TK>;
-  int rc = set_smem(kern, Cfg::kSmemBytes);
-  if (rc) return rc;
   const int grid = p.num_items < sm_count() ? p.num_items : sm_count();
-  kern<<<grid, 384, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmB, p);
+  if (npeers > 0) {
+    auto kern = attention_kernel<D, TK, true>;
+    int rc = set_smem(kern, Cfg::kSmemBytes);
+    if (rc) return rc;
+    kern<<<grid, 384, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmB, maps, p);
+  } else {
+    auto kern = attention_kernel<D, TK, false>;
+    int rc = set_smem(kern, Cfg::kSmemBytes);
+    if (rc) return rc;
+    kern<<<grid, 384, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmB, maps, p);
+  }
   UBM_CHECK_LAUNCH("attention_kernel");
   return UBM_OK;
 }
@@ -449,4 +521,19 @@ extern "C" int ubm_attention_d64(const void* q, const void* k, const void* v, co
   if (bias != nullptr && (ldb < Nk || (ldb & 7))) return ubm::UBM_ERR_ARGUMENT;
   return ubm::launch_attention<64, 64>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
                                        status, stream);
+}
+
+// Pair-bias all-gather fused into the attention kernel (head dimension 32): the bias planes are row
+// shards, shard i = bf16 [H][peer_rows[i]][ldb] in GPU i's memory with head stride peer_head_stride
+// (elements).  Query tiles are enumerated shard by shard and every CTA reads the bias tiles it needs
+// from the owner with ordinary TMA loads (no cluster multicast) while its tensor-core work proceeds; the
+// gathered [H][N][N] bias never exists in local memory.  sum(peer_rows) must equal Nq.
+extern "C" int ubm_attention_d32_peer_bias(const void* q, const void* k, const void* v, const void* const* bias_ptrs,
+                                           const int* peer_rows, int npeers, long long peer_head_stride,
+                                           const void* gate, void* out, int rows, int Nq, int Nk, int H, long long ldb,
+                                           long long ld_in, void* status, void* stream) {
+  if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0 || npeers <= 0) return ubm::UBM_ERR_ARGUMENT;
+  if (ldb < Nk || (ldb & 7) || (peer_head_stride & 7)) return ubm::UBM_ERR_ARGUMENT;
+  return ubm::launch_attention<32, 128>(q, k, v, nullptr, gate, out, rows, Nq, Nk, H, ldb, ld_in, 0, status, stream,
+                                        npeers, bias_ptrs, peer_rows, peer_head_stride);
 }

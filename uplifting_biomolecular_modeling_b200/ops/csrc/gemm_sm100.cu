@@ -32,7 +32,38 @@ struct GemmParams {
   int act;  // 0 none, 1 silu, 2 sigmoid, 3 gelu (erf), 4 relu
   KernelStatus* status;
   int tiles_m, tiles_n, num_tiles;
+  // peer mode: the N dimension is the concatenation of row shards owned by several GPUs; n-tiles are
+  // enumerated shard by shard and each shard's B rows are read through that GPU's tensor map
+  int npeers;
+  int peer_tile0[9];   // first n-tile of each shard (prefix sums), [npeers] = tiles_n
+  int peer_col0[8];    // global column (= row of the gathered operand) where the shard starts
+  int peer_cols[8];    // rows in the shard
 };
+
+constexpr int kMaxPeers = 8;
+struct PeerMaps {
+  CUtensorMap m[kMaxPeers];
+};
+
+// n-tile -> (shard, first global column, column limit, row offset inside the shard)
+template <int BN>
+__device__ __forceinline__ void decode_ntile(const GemmParams& p, int nb, int& q, int& n_base, int& n_limit,
+                                             int& local_row) {
+  if (p.npeers == 0) {
+    q = 0;
+    n_base = nb * BN;
+    n_limit = p.N;
+    local_row = n_base;
+    return;
+  }
+  q = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxPeers; ++i)
+    if (i < p.npeers && nb >= p.peer_tile0[i]) q = i;
+  local_row = (nb - p.peer_tile0[q]) * BN;
+  n_base = p.peer_col0[q] + local_row;
+  n_limit = p.peer_col0[q] + p.peer_cols[q];
+}
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
@@ -57,9 +88,10 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   }
 }
 
-template <int BN, bool MN_MAJOR>
+template <int BN, bool MN_MAJOR, bool PEER>
 __global__ void __launch_bounds__(192, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ PeerMaps peers, GemmParams p) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -118,7 +150,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
           if (!MN_MAJOR) {
             tma_load_3d(sa, &tmA, &full_bar[stage], kb * kBK, mb * kBM, b);
-            tma_load_3d(sb, &tmB, &full_bar[stage], kb * kBK, nb * BN, b);
+            if (PEER) {
+              // B rows of this n-tile live on GPU q: plain (non-multicast) TMA load from its memory
+              int q, n_base, n_limit, lrow;
+              decode_ntile<BN>(p, nb, q, n_base, n_limit, lrow);
+              tma_load_3d(sb, &peers.m[q], &full_bar[stage], kb * kBK, lrow, b);
+            } else {
+              tma_load_3d(sb, &tmB, &full_bar[stage], kb * kBK, nb * BN, b);
+            }
           } else {
 #pragma unroll
             for (int h = 0; h < kBM / 64; ++h)
@@ -195,10 +234,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after_sync();
       const int m = mb * kBM + q * 32 + lane;
       const bool row_ok = m < p.M;
+      int pq, n_base, n_limit, lrow;
+      decode_ntile<BN>(p, nb, pq, n_base, n_limit, lrow);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
-        const int n0 = nb * BN + c * 32;
-        if (n0 >= p.N) break;  // warp-uniform
+        const int n0 = n_base + c * 32;
+        if (n0 >= n_limit) break;  // warp-uniform
         uint32_t v[32];
         tmem_ld32(tmem_addr(tmem_base, q, acc * BN + c * 32), v);
         tmem_ld_wait();
@@ -209,7 +250,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (p.bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (n0 + j < p.N) f[j] += __ldg(p.bias + n0 + j);
+              if (n0 + j < n_limit) f[j] += __ldg(p.bias + n0 + j);
           }
           if (p.act != 0) {
 #pragma unroll
@@ -219,23 +260,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const __nv_bfloat16* rr = p.residual + b * p.strideR + static_cast<long long>(m) * p.ldr + n0;
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (n0 + j < p.N) f[j] += __bfloat162float(rr[j]);
+              if (n0 + j < n_limit) f[j] += __bfloat162float(rr[j]);
           }
           if (p.out_fp32) {
             float* cp = reinterpret_cast<float*>(p.C) + b * p.strideC + static_cast<long long>(m) * p.ldc + n0;
-            if (vec_ok && n0 + 32 <= p.N) {
+            if (vec_ok && n0 + 32 <= n_limit) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4)
                 *reinterpret_cast<float4*>(cp + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (n0 + j < p.N) cp[j] = f[j];
+                if (n0 + j < n_limit) cp[j] = f[j];
             }
           } else {
             __nv_bfloat16* cp =
                 reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.strideC + static_cast<long long>(m) * p.ldc + n0;
-            if (vec_ok && n0 + 32 <= p.N) {
+            if (vec_ok && n0 + 32 <= n_limit) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
                 uint4 u;
@@ -248,7 +289,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (n0 + j < p.N) cp[j] = __float2bfloat16(f[j]);
+                if (n0 + j < n_limit) cp[j] = __float2bfloat16(f[j]);
             }
           }
         }
@@ -276,6 +317,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
                        long long strideA, long long strideB, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   GemmParams p = p0;
+  p.npeers = 0;
   p.tiles_m = (p.M + kBM - 1) / kBM;
   p.tiles_n = (p.N + BN - 1) / BN;
   p.num_tiles = p.tiles_m * p.tiles_n * p.batch;
@@ -304,11 +346,13 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
     rc = make_tmap(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dB, sB, bB, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   }
-  auto kern = gemm_bf16_kernel<BN, MN_MAJOR>;
+  auto kern = gemm_bf16_kernel<BN, MN_MAJOR, false>;
   rc = set_smem(kern, Cfg::kSmemBytes);
   if (rc) return rc;
   int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  kern<<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, p);
+  PeerMaps none;
+  none.m[0] = tmB;
+  kern<<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, none, p);
   UBM_CHECK_LAUNCH("gemm_bf16_kernel");
   return UBM_OK;
 }
@@ -357,4 +401,76 @@ extern "C" int ubm_gemm_bf16(const void* A, const void* B, void* C, const void* 
   }
   return wide ? launch_gemm<256, false>(A, B, p, lda, ldb, strideA, strideB, st)
               : launch_gemm<128, false>(A, B, p, lda, ldb, strideA, strideB, st);
+}
+
+// All-gather fused into the GEMM: C[b][m][col0_q + n] = sum_k A[b][m][k] * B_q[b][n][k] where B_q is the
+// row shard that GPU q holds (a pointer into its memory, mapped into this process).  Each CTA reads the
+// B tiles it needs straight from the owner with ordinary TMA loads (no cluster multicast), so the
+// transfer over NVLink overlaps the tensor-core work of the other pipeline stages; nothing is gathered
+// into a local buffer first.  The caller orders this launch after the owners have finished writing
+// their shards (a stream-ordered barrier over the symmetric buffers).
+//   B_ptrs[q]   bf16 [batch][rows_q][K] with leading dimension ldb and batch stride strideB (elements)
+//   rows[q]     number of rows of shard q;  the output has sum(rows) columns, shard q starting at the
+//               running sum.  K contiguous (K-major) only.
+extern "C" int ubm_gemm_bf16_allgather_b(const void* A, const void* const* B_ptrs, const int* rows, int npeers,
+                                         void* C, int M, int K, int batch, long long lda, long long ldb,
+                                         long long ldc, long long strideA, long long strideB, long long strideC,
+                                         int out_fp32, float alpha, void* status, void* stream) {
+  using namespace ubm;
+  constexpr int BN = 256;
+  using Cfg = GemmCfg<BN>;
+  if (npeers < 1 || npeers > kMaxPeers || M <= 0 || K <= 0 || batch <= 0) return UBM_ERR_ARGUMENT;
+  if ((lda & 7) || (ldb & 7) || (strideA & 7) || (strideB & 7)) return UBM_ERR_ARGUMENT;
+  GemmParams p = {};
+  p.M = M;
+  p.K = K;
+  p.batch = batch;
+  p.C = C;
+  p.ldc = ldc;
+  p.strideC = strideC;
+  p.alpha = alpha;
+  p.out_fp32 = out_fp32;
+  p.status = static_cast<KernelStatus*>(status);
+  p.npeers = npeers;
+  PeerMaps maps;
+  int col = 0, tile = 0;
+  CUtensorMap tmA;
+  {
+    uint64_t dA[3] = {(uint64_t)K, (uint64_t)M, (uint64_t)batch};
+    uint64_t sA[2] = {(uint64_t)lda * 2, (uint64_t)strideA * 2};
+    uint32_t bA[3] = {kBK, kBM, 1};
+    int rc = make_tmap(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dA, sA, bA, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  }
+  for (int q = 0; q < npeers; ++q) {
+    p.peer_tile0[q] = tile;
+    p.peer_col0[q] = col;
+    p.peer_cols[q] = rows[q];
+    if (rows[q] > 0) {
+      uint64_t dB[3] = {(uint64_t)K, (uint64_t)rows[q], (uint64_t)batch};
+      uint64_t sB[2] = {(uint64_t)ldb * 2, (uint64_t)strideB * 2};
+      uint32_t bB[3] = {kBK, (uint32_t)BN, 1};
+      int rc = make_tmap(&maps.m[q], B_ptrs[q], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dB, sB, bB,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc) return rc;
+    } else {
+      maps.m[q] = tmA;
+    }
+    col += rows[q];
+    tile += (rows[q] + BN - 1) / BN;
+  }
+  for (int q = npeers; q < kMaxPeers; ++q) maps.m[q] = tmA;
+  p.peer_tile0[npeers] = tile;
+  p.N = col;
+  p.tiles_m = (M + kBM - 1) / kBM;
+  p.tiles_n = tile;
+  p.num_tiles = p.tiles_m * p.tiles_n * batch;
+  if (p.num_tiles == 0) return UBM_OK;
+  auto kern = gemm_bf16_kernel<BN, false, true>;
+  int rc = set_smem(kern, Cfg::kSmemBytes);
+  if (rc) return rc;
+  const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  kern<<<grid, 192, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmA, tmA, maps, p);
+  UBM_CHECK_LAUNCH("gemm_bf16_kernel<peer>");
+  return UBM_OK;
 }

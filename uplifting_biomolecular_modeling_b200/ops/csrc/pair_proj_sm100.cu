@@ -35,20 +35,22 @@ constexpr int kPPMaxHeads = 8;
 enum { MODE_TRIMUL = 0, MODE_TRIATT = 1 };
 
 struct PairProjParams {
-  long long R;       // number of rows (N * N)
-  int N;             // tokens
+  long long R;       // number of pair rows (rows * N)
+  int rows;          // first pair index extent (N for a whole pair tensor, fewer for a row shard)
+  int plane_rows;    // rows the output planes are allocated for (>= rows; equal-sized symmetric buffers)
+  int N;             // tokens (second pair index extent)
   int Np;            // leading dimension of planes (>= N, multiple of 8)
   const float* colsum;   // [512]  rowsum(W') per output column
   const float* colbias;  // [512]  W.beta (+ bias) per output column
   const float* mask;     // [R] or null (MODE_TRIMUL: multiplies a and b)
   // MODE_TRIMUL
-  __nv_bfloat16* planes;  // [2][128][N][Np]
+  __nv_bfloat16* planes;  // [2][128][rows][Np]
   // MODE_TRIATT
   __nv_bfloat16* q;  // each [R][128], row index possibly transposed
   __nv_bfloat16* k;
   __nv_bfloat16* v;
   __nv_bfloat16* g;
-  __nv_bfloat16* headbias;   // [H][N][Np]
+  __nv_bfloat16* headbias;   // [H][rows][Np]
   const float* wb;           // [H][128] head-bias weights already multiplied by gamma
   const float* wb_colsum;    // [H]
   const float* wb_colbias;   // [H]
@@ -245,7 +247,7 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           const int head = grp * hpg + h;
           if (h < hpg && head < p.H) {
             const float val = rstd * (hb[h] - mu * p.wb_colsum[head]) + p.wb_colbias[head];
-            p.headbias[(static_cast<long long>(head) * p.N + oi) * p.Np + ok] = __float2bfloat16(val);
+            p.headbias[(static_cast<long long>(head) * p.plane_rows + oi) * p.Np + ok] = __float2bfloat16(val);
           }
         }
       }
@@ -256,9 +258,9 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       const uint32_t tbase = tmem_addr(tmem_base, q, grp * 256);
       if (MODE == MODE_TRIMUL) {
         // half = [p (128) | g (128)] of operand `grp`; out[c] = p * sigmoid(g) * mask
-        __nv_bfloat16* plane = p.planes + static_cast<long long>(grp) * 128 * p.N * p.Np;
+        __nv_bfloat16* plane = p.planes + static_cast<long long>(grp) * 128 * p.plane_rows * p.Np;
         const long long off = static_cast<long long>(pi) * p.Np + pk;
-        const long long cstride = static_cast<long long>(p.N) * p.Np;
+        const long long cstride = static_cast<long long>(p.plane_rows) * p.Np;
 #pragma unroll 1
         for (int c0 = 0; c0 < 128; c0 += 32) {
           uint32_t pv[32], gv[32];
@@ -358,12 +360,15 @@ static int launch_pair_proj(const void* x, const void* w, PairProjParams p, cuda
 // z: [N*N][128] bf16.  w: [512][128] bf16 = rows [p_a; g_a; p_b; g_b] each already multiplied by
 // the LayerNorm gamma.  colsum/colbias: fp32 [512].  mask: fp32 [N*N] or null.
 // planes: bf16 [2][128][N][Np] (Np multiple of 8, >= N).
-extern "C" int ubm_trimul_proj(const void* z, const void* w, const void* colsum, const void* colbias, const void* mask,
-                               void* planes, void* stats_out, int N, int Np, void* status, void* stream) {
+extern "C" int ubm_trimul_proj_rows(const void* z, const void* w, const void* colsum, const void* colbias,
+                                    const void* mask, void* planes, void* stats_out, int rows, int plane_rows, int N,
+                                    int Np, void* status, void* stream) {
   using namespace ubm;
-  if (N <= 0 || Np < N || (Np & 7)) return UBM_ERR_ARGUMENT;
+  if (N <= 0 || rows <= 0 || plane_rows < rows || Np < N || (Np & 7)) return UBM_ERR_ARGUMENT;
   PairProjParams p = {};
-  p.R = static_cast<long long>(N) * N;
+  p.R = static_cast<long long>(rows) * N;
+  p.rows = rows;
+  p.plane_rows = plane_rows;
   p.N = N;
   p.Np = Np;
   p.colsum = static_cast<const float*>(colsum);
@@ -375,17 +380,26 @@ extern "C" int ubm_trimul_proj(const void* z, const void* w, const void* colsum,
   return launch_pair_proj<MODE_TRIMUL>(z, w, p, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int ubm_trimul_proj(const void* z, const void* w, const void* colsum, const void* colbias, const void* mask,
+                               void* planes, void* stats_out, int N, int Np, void* status, void* stream) {
+  return ubm_trimul_proj_rows(z, w, colsum, colbias, mask, planes, stats_out, N, N, N, Np, status, stream);
+}
+
 // w: [512][128] bf16 = rows [q; k; v; g] (gamma folded, q pre-scaled by 1/sqrt(d)).
 // wb: fp32 [H][128] head-bias weights (gamma folded); wb_colsum/wb_colbias fp32 [H].
 // q,k,v,g: bf16 [N*N][128]; headbias: bf16 [H][N][Np].
-extern "C" int ubm_triatt_proj(const void* z, const void* w, const void* colsum, const void* colbias, const void* wb,
-                               const void* wb_colsum, const void* wb_colbias, void* q, void* k, void* v, void* g,
-                               void* headbias, void* stats_out, int N, int Np, int H, int transpose_out, void* status,
-                               void* stream) {
+extern "C" int ubm_triatt_proj_rows(const void* z, const void* w, const void* colsum, const void* colbias,
+                                    const void* wb, const void* wb_colsum, const void* wb_colbias, void* q, void* k,
+                                    void* v, void* g, void* headbias, void* stats_out, int rows, int plane_rows, int N,
+                                    int Np, int H, int transpose_out, void* status, void* stream) {
   using namespace ubm;
-  if (N <= 0 || Np < N || (Np & 7) || H <= 0 || H > kPPMaxHeads) return UBM_ERR_ARGUMENT;
+  if (N <= 0 || rows <= 0 || plane_rows < rows || Np < N || (Np & 7) || H <= 0 || H > kPPMaxHeads)
+    return UBM_ERR_ARGUMENT;
+  if (transpose_out && rows != N) return UBM_ERR_ARGUMENT;  // the transposed write needs the whole square
   PairProjParams p = {};
-  p.R = static_cast<long long>(N) * N;
+  p.R = static_cast<long long>(rows) * N;
+  p.rows = rows;
+  p.plane_rows = plane_rows;
   p.N = N;
   p.Np = Np;
   p.colsum = static_cast<const float*>(colsum);
@@ -403,4 +417,12 @@ extern "C" int ubm_triatt_proj(const void* z, const void* w, const void* colsum,
   p.stats_out = static_cast<float*>(stats_out);
   p.status = static_cast<KernelStatus*>(status);
   return launch_pair_proj<MODE_TRIATT>(z, w, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ubm_triatt_proj(const void* z, const void* w, const void* colsum, const void* colbias, const void* wb,
+                               const void* wb_colsum, const void* wb_colbias, void* q, void* k, void* v, void* g,
+                               void* headbias, void* stats_out, int N, int Np, int H, int transpose_out, void* status,
+                               void* stream) {
+  return ubm_triatt_proj_rows(z, w, colsum, colbias, wb, wb_colsum, wb_colbias, q, k, v, g, headbias, stats_out, N, N,
+                              N, Np, H, transpose_out, status, stream);
 }

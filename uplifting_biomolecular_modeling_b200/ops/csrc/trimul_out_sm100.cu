@@ -23,7 +23,7 @@ constexpr int kTOTileBytes = 128 * 128 * 2;  // 32 KB per operand tile
 constexpr int kTOStageBytes = 2 * kTOTileBytes;
 
 struct TrimulOutParams {
-  int N, Np;
+  int rows, N, Np;   // rows = first pair index extent (N, or fewer for a row shard)
   const float* o_colsum;   // [128] rowsum(Wo')
   const float* o_colbias;  // [128] Wo.beta_out
   const float* g_colsum;   // [128]
@@ -302,21 +302,21 @@ constexpr int kTOSmemBytes = 2 * kTOTileBytes + kTOStages * kTOStageBytes + (512
 // x: bf16 planes [128][N][Np]; z: bf16 [N*N][128]; wo, wg: bf16 [128][128] (gamma folded);
 // *_colsum / *_colbias: fp32 [128]; out: bf16 [N*N][128] (may alias z only when add_residual == 0
 // is not required: each row is read from shared memory before it is written).
-extern "C" int ubm_trimul_out(const void* x, const void* z, const void* wo, const void* wg, const void* o_colsum,
-                              const void* o_colbias, const void* g_colsum, const void* g_colbias, void* out, int N,
-                              int Np, int add_residual, void* status, void* stream) {
+extern "C" int ubm_trimul_out_rows(const void* x, const void* z, const void* wo, const void* wg, const void* o_colsum,
+                                   const void* o_colbias, const void* g_colsum, const void* g_colbias, void* out,
+                                   int rows, int N, int Np, int add_residual, void* status, void* stream) {
   using namespace ubm;
-  if (N <= 0 || Np < N || (Np & 7)) return UBM_ERR_ARGUMENT;
+  if (N <= 0 || rows <= 0 || Np < N || (Np & 7)) return UBM_ERR_ARGUMENT;
   CUtensorMap tmX, tmZ, tmWo, tmWg;
   {
-    uint64_t d[3] = {(uint64_t)N, (uint64_t)N, 128};
-    uint64_t s[2] = {(uint64_t)Np * 2, (uint64_t)N * Np * 2};
+    uint64_t d[3] = {(uint64_t)N, (uint64_t)rows, 128};
+    uint64_t s[2] = {(uint64_t)Np * 2, (uint64_t)rows * Np * 2};
     uint32_t b[3] = {64, 1, 64};
     int rc = make_tmap(&tmX, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d, s, b, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   }
   {
-    uint64_t d[2] = {128, (uint64_t)N * N};
+    uint64_t d[2] = {128, (uint64_t)rows * N};
     uint64_t s[1] = {256};
     uint32_t b[2] = {64, 128};
     int rc = make_tmap(&tmZ, z, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d, s, b, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -332,6 +332,7 @@ extern "C" int ubm_trimul_out(const void* x, const void* z, const void* wo, cons
     if (rc) return rc;
   }
   TrimulOutParams p = {};
+  p.rows = rows;
   p.N = N;
   p.Np = Np;
   p.o_colsum = static_cast<const float*>(o_colsum);
@@ -343,11 +344,18 @@ extern "C" int ubm_trimul_out(const void* x, const void* z, const void* wo, cons
   p.add_residual = add_residual;
   p.status = static_cast<KernelStatus*>(status);
   p.tiles_per_i = (N + 127) / 128;
-  p.num_tiles = p.tiles_per_i * N;
+  p.num_tiles = p.tiles_per_i * rows;
   int rc = set_smem(trimul_out_kernel, kTOSmemBytes);
   if (rc) return rc;
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
   trimul_out_kernel<<<grid, 320, kTOSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmX, tmZ, tmWo, tmWg, p);
   UBM_CHECK_LAUNCH("trimul_out_kernel");
   return UBM_OK;
+}
+
+extern "C" int ubm_trimul_out(const void* x, const void* z, const void* wo, const void* wg, const void* o_colsum,
+                              const void* o_colbias, const void* g_colsum, const void* g_colbias, void* out, int N,
+                              int Np, int add_residual, void* status, void* stream) {
+  return ubm_trimul_out_rows(x, z, wo, wg, o_colsum, o_colbias, g_colsum, g_colbias, out, N, N, Np, add_residual,
+                             status, stream);
 }

@@ -1,0 +1,54 @@
+"""Python face of the kernels that read other GPUs' memory themselves (collective fused with compute):
+the all-gather -> triangle contraction GEMM and the attention kernel with its pair-bias all-gather."""
+from __future__ import annotations
+
+import ctypes
+from typing import Sequence
+
+import torch
+
+from . import native
+from .native import c_float, c_int, c_ll, c_void_p
+
+native.declare("ubm_gemm_bf16_allgather_b",
+               [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll,
+                c_int, c_float, c_void_p, c_void_p])
+native.declare("ubm_attention_d32_peer_bias",
+               [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_ll, c_void_p, c_void_p, c_int, c_int, c_int,
+                c_int, c_ll, c_ll, c_void_p, c_void_p])
+native.declare("ubm_trimul_proj_rows", [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+native.declare("ubm_triatt_proj_rows", [c_void_p] * 13 + [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+native.declare("ubm_trimul_out_rows", [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+
+
+def _ptrs(ptrs: Sequence[int]):
+    return (ctypes.c_void_p * len(ptrs))(*[ctypes.c_void_p(int(p)) for p in ptrs])
+
+
+def _ints(vals: Sequence[int]):
+    return (ctypes.c_int * len(vals))(*[int(v) for v in vals])
+
+
+def gemm_allgather_b(a: torch.Tensor, b_ptrs: Sequence[int], rows: Sequence[int], out: torch.Tensor, K: int,
+                     ldb: int, stride_b: int, alpha: float = 1.0) -> torch.Tensor:
+    """out[c][m][col0_q + n] = sum_k a[c][m][k] * B_q[c][n][k]; B_q = bf16 [batch][rows[q]][K] at b_ptrs[q]
+    (possibly on another GPU) with leading dimension ldb and batch stride stride_b (elements)."""
+    batch, M = a.shape[0], a.shape[1]
+    st = native.status_tensor(a.device)
+    rc = native.lib().ubm_gemm_bf16_allgather_b(native.ptr(a), _ptrs(b_ptrs), _ints(rows), len(rows), native.ptr(out),
+                                                M, K, batch, a.stride(1), ldb, out.stride(1), a.stride(0), stride_b,
+                                                out.stride(0), 1 if out.dtype == torch.float32 else 0, float(alpha),
+                                                native.ptr(st), native.current_stream(a.device))
+    native.check(rc, "ubm_gemm_bf16_allgather_b")
+    return out
+
+
+def attention_peer_bias(q, k, v, bias_ptrs: Sequence[int], peer_rows: Sequence[int], head_stride: int, gate, out,
+                        rows: int, N: int, H: int, ldb: int):
+    st = native.status_tensor(q.device)
+    rc = native.lib().ubm_attention_d32_peer_bias(native.ptr(q), native.ptr(k), native.ptr(v), _ptrs(bias_ptrs),
+                                                  _ints(peer_rows), len(peer_rows), head_stride, native.ptr(gate),
+                                                  native.ptr(out), rows, N, N, H, ldb, 0, native.ptr(st),
+                                                  native.current_stream(q.device))
+    native.check(rc, "ubm_attention_d32_peer_bias")
+    return out

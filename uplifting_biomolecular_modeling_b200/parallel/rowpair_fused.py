@@ -1,0 +1,144 @@
+"""Row-sharded pair stack on the sm_100a kernels, with the gathers fused into the compute kernels.
+
+Per rank: rows [r0, r1) of z (bf16 [R, N, 128]).  Buffers that peers read live in symmetric memory:
+the projected triangle-multiplication operands (``planes``) and the per-head triangle-attention bias
+(``headbias``).  The schedule of one Pairformer block:
+
+  trimul outgoing : projection (local rows) -> barrier -> contraction GEMM whose B tiles are TMA-loaded from
+                    the owners' planes (all-gather fused into the GEMM) -> barrier -> output stage (local)
+  trimul incoming : z^T rows by all-to-all, then the same three kernels on z^T, output stage on z
+  triatt starting : projection (q|k|v|gate rows + bias planes) -> barrier -> attention whose bias tiles
+                    are TMA-loaded from the owners' planes (bias all-gather fused) -> barrier -> output GEMM
+  triatt ending   : the starting-node schedule on z^T rows, update transposed back by all-to-all
+  transition      : local
+
+The barriers are stream-ordered kernels with bounded waits (``parallel.symm``).  The two transposes use
+the process group's all-to-all.  Same statements as ``parallel.rowpair`` (which is the NCCL-only
+baseline of every step).  Reference schedule: common/opt_core/opt_core/mem/rowpair/pairstack.py:195-251.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..ops import gemm as _gemm
+from ..ops import native, pair, peer
+from .comm import Comm
+from .layout import Layout
+from .rowpair import transpose_shard
+from .symm import SymmHeap
+
+
+class FusedRowPair:
+    def __init__(self, layout: Layout, comm: Comm, heap: SymmHeap, heads: int = 4):
+        self.layout, self.comm, self.heap = layout, comm, heap
+        self.rank, self.world = comm.rank, comm.world
+        self.N = layout.n
+        self.Np = pair.ceil_to(self.N, 8)
+        self.rows = layout.count(self.rank)
+        self.counts = [b - a for a, b in layout.bounds()]
+        self.Rmax = max(max(self.counts), 1)
+        dev = heap.device
+        self.H = heads
+        self.planes = heap.alloc((2, 128, self.Rmax, self.Np), torch.bfloat16)
+        self.headbias = heap.alloc((heads, self.Rmax, self.Np), torch.bfloat16)
+        self.planes.local.zero_()
+        self.headbias.local.zero_()
+        self.x = torch.empty((128, self.Rmax, self.Np), dtype=torch.bfloat16, device=dev)
+        self.qkvgo = torch.empty((5, self.Rmax * self.N, 128), dtype=torch.bfloat16, device=dev)
+        self.dev = dev
+        heap.barrier()
+
+    # ------------------------------------------------------------------ triangle multiplication
+    def trimul_(self, z_loc: torch.Tensor, w: pair.TrimulPacked, outgoing: bool) -> torch.Tensor:
+        R, N, Np, Rmax = self.rows, self.N, self.Np, self.Rmax
+        st = native.status_tensor(self.dev)
+        stream = native.current_stream(self.dev)
+        src = z_loc if outgoing else transpose_shard(z_loc, self.layout, self.comm)
+        lib = native.lib()
+        if R > 0:
+            rc = lib.ubm_trimul_proj_rows(native.ptr(src), native.ptr(w.w_in), native.ptr(w.in_colsum),
+                                          native.ptr(w.in_colbias), 0, native.ptr(self.planes.local), 0, R, Rmax, N, Np,
+                                          native.ptr(st), stream)
+            native.check(rc, "ubm_trimul_proj_rows")
+        self.heap.barrier()                      # every owner's b rows are written and visible
+        if R > 0:
+            b_off = 128 * Rmax * Np * 2          # byte offset of plane b inside each rank's buffer
+            a_loc = self.planes.local[0][:, :R, :N]
+            xv = self.x.view(-1)[: 128 * R * Np].view(128, R, Np)     # [128][rows][Np], what the output stage expects
+            peer.gemm_allgather_b(a_loc, [self.planes.ptr(q, b_off) for q in range(self.world)], self.counts,
+                                  xv[:, :, :N], K=N, ldb=Np, stride_b=Rmax * Np)
+        self.heap.barrier()                      # nobody still reads my planes when I overwrite them
+        if R > 0:
+            out = torch.empty_like(z_loc)
+            rc = lib.ubm_trimul_out_rows(native.ptr(self.x), native.ptr(z_loc), native.ptr(w.wo), native.ptr(w.wg),
+                                         native.ptr(w.o_colsum), native.ptr(w.o_colbias), native.ptr(w.g_colsum),
+                                         native.ptr(w.g_colbias), native.ptr(out), R, N, Np, 1, native.ptr(st), stream)
+            native.check(rc, "ubm_trimul_out_rows")
+            return out
+        return z_loc
+
+    # ------------------------------------------------------------------ triangle attention
+    def triatt_(self, z_loc: torch.Tensor, w: pair.TriattPacked, starting: bool) -> torch.Tensor:
+        R, N, Np, Rmax, H = self.rows, self.N, self.Np, self.Rmax, self.H
+        st = native.status_tensor(self.dev)
+        stream = native.current_stream(self.dev)
+        src = z_loc if starting else transpose_shard(z_loc, self.layout, self.comm)
+        q, k, v, g, og = (self.qkvgo[i][: R * N] for i in range(5))
+        lib = native.lib()
+        if R > 0:
+            rc = lib.ubm_triatt_proj_rows(native.ptr(src), native.ptr(w.w), native.ptr(w.colsum), native.ptr(w.colbias),
+                                          native.ptr(w.wb), native.ptr(w.wb_colsum), native.ptr(w.wb_colbias),
+                                          native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(g),
+                                          native.ptr(self.headbias.local), 0, R, Rmax, N, Np, H, 0, native.ptr(st),
+                                          stream)
+            native.check(rc, "ubm_triatt_proj_rows")
+        self.heap.barrier()
+        if R > 0:
+            peer.attention_peer_bias(q, k, v, [self.headbias.ptr(p) for p in range(self.world)], self.counts,
+                                     Rmax * Np, g, og, rows=R, N=N, H=H, ldb=Np)
+        self.heap.barrier()
+        src2 = src.view(R * N, 128)
+        if starting:
+            out = torch.empty_like(z_loc)
+            if R > 0:
+                _gemm.gemm(og, w.wo, bias=w.bo, residual=z_loc.view(R * N, 128), out=out.view(R * N, 128))
+            return out
+        upd_t = torch.empty_like(src)
+        if R > 0:
+            _gemm.gemm(og, w.wo, bias=w.bo, out=upd_t.view(R * N, 128))
+        upd = transpose_shard(upd_t, self.layout, self.comm)
+        return z_loc + upd
+
+    # ------------------------------------------------------------------ one Pairformer block (pair part)
+    def pair_block_(self, layer, z_loc: torch.Tensor) -> torch.Tensor:
+        def packed(mod, maker):
+            if mod._packed is None:
+                mod._packed = maker()
+            return mod._packed
+
+        tmo, tmi, tas, tae, tr = (layer.tri_mul_out, layer.tri_mul_in, layer.tri_att_start, layer.tri_att_end,
+                                  layer.transition_z)
+        w_tmo = packed(tmo, lambda: pair.TrimulPacked.pack(tmo.norm_in.weight, tmo.norm_in.bias, tmo.p_in.weight,
+                                                           tmo.g_in.weight, tmo.norm_out.weight, tmo.norm_out.bias,
+                                                           tmo.p_out.weight, tmo.g_out.weight))
+        w_tmi = packed(tmi, lambda: pair.TrimulPacked.pack(tmi.norm_in.weight, tmi.norm_in.bias, tmi.p_in.weight,
+                                                           tmi.g_in.weight, tmi.norm_out.weight, tmi.norm_out.bias,
+                                                           tmi.p_out.weight, tmi.g_out.weight))
+
+        def tri(m):
+            a = m.mha
+            return pair.TriattPacked.pack(m.layer_norm.weight, m.layer_norm.bias, m.linear.weight, a.linear_q.weight,
+                                          a.linear_k.weight, a.linear_v.weight, a.linear_g.weight, a.linear_g.bias,
+                                          a.linear_o.weight, a.linear_o.bias, m.heads)
+        w_tas, w_tae = packed(tas, lambda: tri(tas)), packed(tae, lambda: tri(tae))
+        w_tr = packed(tr, lambda: pair.TransitionPacked.pack(tr.norm.weight, tr.norm.bias, tr.fc1.weight,
+                                                             tr.fc2.weight, tr.fc3.weight))
+        z_loc = self.trimul_(z_loc, w_tmo, True)
+        z_loc = self.trimul_(z_loc, w_tmi, False)
+        z_loc = self.triatt_(z_loc, w_tas, True)
+        z_loc = self.triatt_(z_loc, w_tae, False)
+        if self.rows > 0:
+            z_loc = pair.transition_fused(z_loc.contiguous(), w_tr, residual=True)
+        return z_loc
