@@ -1,0 +1,33 @@
+"""StripedHyena-2 decoder on CPU: decode steps reproduce the prefill, FFT convolution equals the FIR."""
+import torch
+
+from uplifting_biomolecular_modeling_b200.models import evo2
+
+
+def test_layer_pattern_of_the_7b_shape():
+    cfg = evo2.CONFIGS["evo2_7b"]
+    kinds = [cfg.layer_kind(i) for i in range(cfg.n_layers)]
+    assert kinds.count("attn") == 5 and kinds[3] == "attn" and kinds[31] == "attn"
+    assert kinds[:3] == ["hcs", "hcm", "hcl"] and kinds.count("hcs") == 9
+
+
+def test_fft_conv_equals_fir():
+    torch.manual_seed(0)
+    x = torch.randn(2, 50, 6, dtype=torch.float64)
+    h = torch.randn(6, 9, dtype=torch.float64)
+    assert torch.allclose(evo2.fft_causal_conv(x, h), evo2.causal_fir(x, h), atol=1e-5)
+
+
+def test_decode_steps_match_prefill():
+    m = evo2.build("evo2_tiny", dtype=torch.float64)
+    toks = torch.randint(0, 512, (1, 24))
+    full = m.forward(toks)
+    states = [dict() for _ in m.blocks]
+    pre = m.forward(toks[:, :16], states)
+    assert torch.allclose(pre, full[:, :16], atol=2e-4)     # long filters run as fp32 FFT convolutions
+    for t in range(16, 24):
+        lg = m.step(toks[:, t:t + 1], states)
+        assert torch.allclose(lg[:, 0], full[:, t], atol=2e-4), t
+    out = m.generate(toks[:, :8], 5)
+    assert out.shape == (1, 5)
+    assert torch.isfinite(m.score(toks)).all()

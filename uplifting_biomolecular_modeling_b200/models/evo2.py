@@ -1,0 +1,320 @@
+"""Evo2-shaped genomic language model: a StripedHyena-2 decoder (gated short / medium / long
+convolution operators interleaved with multi-head attention, SwiGLU MLPs, byte vocabulary).
+
+Shape facts follow the reference's stock configuration (evo2/stock/src/evo2/configs/evo2-7b-1m.yml:
+hidden 4096, 32 layers, attention at layers 3/10/17/24/31 with 32 heads, the remaining layers cycling
+short (7-tap FIR), medium (128-tap FIR) and long (implicit, pole/residue) Hyena operators, vocabulary
+512) and the benchmark configuration (SwiGLU width 11008).  Each Hyena operator is
+``out( x2 * conv(x1 * v) )`` after a 3-tap depthwise FIR on the 3d-wide input projection (the reference's
+kernels for the same pieces: evo2/opt/evo2_opt/kit/base.py:55 ``_fir3_kernel``, :160 ``_hcs7_kernel_s``,
+:219/:242 FFT-convolution epilogues, gen/hyenafuse for the decode-step state update).
+
+Prefill runs the medium / long operators as FFT convolutions; decoding keeps per-layer state (FIR
+tails, pole states, attention KV cache) and advances one token per step.  Tensor parallelism shards
+the channel dimension of every operator: column-parallel input projections, row-parallel output
+projections, with the two collectives fused into the GEMMs (``parallel.tp``).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, replace
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+@dataclass(frozen=True)
+class Evo2Config:
+    name: str = "evo2_7b"
+    d_model: int = 4096
+    n_layers: int = 32
+    n_heads: int = 32
+    ffn: int = 11008
+    vocab: int = 512
+    attn_layers: Tuple[int, ...] = (3, 10, 17, 24, 31)
+    short_len: int = 7
+    medium_len: int = 128
+    state_dim: int = 16            # poles per channel of the long operator
+    fir_len: int = 3               # depthwise FIR on the input projection
+    rope_base: float = 10000.0
+    eps: float = 1e-6
+
+    def layer_kind(self, i: int) -> str:
+        if i in self.attn_layers:
+            return "attn"
+        k = [j for j in range(self.n_layers) if j not in self.attn_layers].index(i) % 3
+        return ("hcs", "hcm", "hcl")[k]
+
+
+CONFIGS: Dict[str, Evo2Config] = {
+    "evo2_7b": Evo2Config(),
+    "evo2_1b": Evo2Config(name="evo2_1b", d_model=1920, n_layers=25, n_heads=15, ffn=5120,
+                          attn_layers=(3, 10, 17, 24)),
+    "evo2_tiny": Evo2Config(name="evo2_tiny", d_model=128, n_layers=4, n_heads=4, ffn=256, attn_layers=(3,),
+                            medium_len=16, state_dim=4),
+}
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, d: int, eps: float = 1e-6):
+        super().__init__()
+        self.scale = nn.Parameter(torch.ones(d))
+        self.eps = eps
+
+    def forward(self, x):
+        x32 = x.float()
+        y = x32 * torch.rsqrt(x32.pow(2).mean(-1, keepdim=True) + self.eps)
+        return (y * self.scale.float()).to(x.dtype)
+
+
+def causal_fir(x: torch.Tensor, h: torch.Tensor, tail: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Depthwise causal FIR.  x: [B, L, C]; h: [C, K] (h[:, 0] multiplies the current sample); tail: the
+    K-1 samples before x ([B, K-1, C]) or None for zeros."""
+    B, L, C = x.shape
+    K = h.shape[1]
+    pad = x.new_zeros((B, K - 1, C)) if tail is None else tail.to(x.dtype)
+    xp = torch.cat([pad, x], dim=1).transpose(1, 2)                      # [B, C, L+K-1]
+    w = h.flip(1).unsqueeze(1).to(x.dtype)                                # conv1d correlates: flip for convolution
+    return F.conv1d(xp, w, groups=C).transpose(1, 2)
+
+
+def fft_causal_conv(x: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+    """Depthwise causal convolution with a filter as long as the sequence.  x: [B, L, C]; h: [C, Lh]."""
+    B, L, C = x.shape
+    n = 1 << (L + h.shape[1] - 1).bit_length()
+    X = torch.fft.rfft(x.float().transpose(1, 2), n=n)
+    Hf = torch.fft.rfft(h.float(), n=n)
+    y = torch.fft.irfft(X * Hf.unsqueeze(0), n=n)[..., :L]
+    return y.transpose(1, 2).to(x.dtype)
+
+
+class HyenaOperator(nn.Module):
+    """Gated convolution operator; ``kind`` in {hcs, hcm, hcl}."""
+
+    def __init__(self, cfg: Evo2Config, kind: str):
+        super().__init__()
+        d = cfg.d_model
+        self.kind, self.d, self.cfg = kind, d, cfg
+        self.in_proj = nn.Linear(d, 3 * d, bias=False)
+        self.fir = nn.Parameter(torch.randn(3 * d, cfg.fir_len) * 0.3)
+        if kind == "hcs":
+            self.h = nn.Parameter(torch.randn(d, cfg.short_len) * 0.2)
+        elif kind == "hcm":
+            self.h = nn.Parameter(torch.randn(d, cfg.medium_len) * (1.0 / math.sqrt(cfg.medium_len)))
+        else:
+            self.log_poles = nn.Parameter(torch.log(torch.rand(d, cfg.state_dim) * 0.5 + 0.45))
+            self.residues = nn.Parameter(torch.randn(d, cfg.state_dim) * (1.0 / cfg.state_dim))
+        self.D = nn.Parameter(torch.ones(d))
+        self.out_proj = nn.Linear(d, d, bias=True)
+
+    # ---- filters
+    def long_filter(self, L: int) -> torch.Tensor:
+        t = torch.arange(L, device=self.residues.device, dtype=torch.float32)
+        lam = torch.exp(self.log_poles.float())                                   # in (0, 1)
+        return torch.einsum("cs,cst->ct", self.residues.float(), lam.unsqueeze(-1) ** t)
+
+    def inner(self, u: torch.Tensor, state: Optional[dict]) -> torch.Tensor:
+        """conv(u) + D*u for the operator's filter.  u: [B, L, d]."""
+        if self.kind in ("hcs", "hcm"):
+            tail = None if state is None else state.get("inner_tail")
+            if self.kind == "hcm" and u.shape[1] > 4 * self.h.shape[1] and tail is None:
+                y = fft_causal_conv(u, self.h)
+            else:
+                y = causal_fir(u, self.h, tail)
+        else:
+            y = fft_causal_conv(u, self.long_filter(u.shape[1]))
+        return y + u * self.D.to(u.dtype)
+
+    def forward(self, x: torch.Tensor, state: Optional[dict] = None, linear=None) -> torch.Tensor:
+        """Prefill form.  When ``state`` is a dict it is filled with what decoding needs."""
+        lin = linear or (lambda m, t: m(t))
+        z = lin(self.in_proj, x)
+        zf = causal_fir(z, self.fir)
+        x1, x2, v = zf.chunk(3, dim=-1)
+        u = x1 * v
+        y = self.inner(u, None)
+        if state is not None:
+            K = self.cfg.fir_len
+            state["fir_tail"] = _last(z, K - 1)
+            if self.kind in ("hcs", "hcm"):
+                state["inner_tail"] = _last(u, self.h.shape[1] - 1)
+            else:
+                lam = torch.exp(self.log_poles.float())                           # [d, S]
+                L = u.shape[1]
+                w = lam.unsqueeze(0) ** torch.arange(L - 1, -1, -1, device=u.device, dtype=torch.float32).view(L, 1, 1)
+                state["poles"] = torch.einsum("bld,lds->bds", u.float(), w)       # sum_t lam^(L-1-t) u_t
+        return lin(self.out_proj, x2 * y)
+
+    def step(self, x: torch.Tensor, state: dict, linear=None) -> torch.Tensor:
+        """One token.  x: [B, 1, d]."""
+        lin = linear or (lambda m, t: m(t))
+        z = lin(self.in_proj, x)
+        zf = causal_fir(z, self.fir, state["fir_tail"])
+        state["fir_tail"] = torch.cat([state["fir_tail"], z], 1)[:, 1:]
+        x1, x2, v = zf.chunk(3, dim=-1)
+        u = x1 * v
+        if self.kind in ("hcs", "hcm"):
+            y = causal_fir(u, self.h, state["inner_tail"]) + u * self.D.to(u.dtype)
+            state["inner_tail"] = torch.cat([state["inner_tail"], u], 1)[:, 1:]
+        else:
+            lam = torch.exp(self.log_poles.float())
+            s = state["poles"] * lam.unsqueeze(0) + u[:, 0].float().unsqueeze(-1)     # [B, d, S]
+            state["poles"] = s
+            y = (s * self.residues.float().unsqueeze(0)).sum(-1).unsqueeze(1).to(u.dtype) + u * self.D.to(u.dtype)
+        return lin(self.out_proj, x2 * y)
+
+
+def _last(t: torch.Tensor, n: int) -> torch.Tensor:
+    B, L, C = t.shape
+    if n <= 0:
+        return t.new_zeros((B, 0, C))
+    if L >= n:
+        return t[:, L - n:].clone()
+    return torch.cat([t.new_zeros((B, n - L, C)), t], 1)
+
+
+def rope(x: torch.Tensor, pos: torch.Tensor, base: float) -> torch.Tensor:
+    """x: [B, L, H, D]; pos: [L]."""
+    D = x.shape[-1]
+    inv = 1.0 / (base ** (torch.arange(0, D, 2, device=x.device, dtype=torch.float32) / D))
+    ang = pos.float().unsqueeze(-1) * inv                                  # [L, D/2]
+    cos, sin = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
+    x1, x2 = x.float()[..., 0::2], x.float()[..., 1::2]
+    out = torch.stack([x1 * cos - x2 * sin, x1 * sin + x2 * cos], dim=-1).flatten(-2)
+    return out.to(x.dtype)
+
+
+class AttentionOperator(nn.Module):
+    def __init__(self, cfg: Evo2Config):
+        super().__init__()
+        self.cfg = cfg
+        d = cfg.d_model
+        self.qkv = nn.Linear(d, 3 * d, bias=False)
+        self.out_proj = nn.Linear(d, d, bias=True)
+
+    def _qkv(self, x, pos, lin):
+        B, L, d = x.shape
+        H = self.cfg.n_heads
+        q, k, v = lin(self.qkv, x).view(B, L, 3, H, d // H).unbind(2)
+        return rope(q, pos, self.cfg.rope_base), rope(k, pos, self.cfg.rope_base), v
+
+    def forward(self, x, state: Optional[dict] = None, linear=None):
+        lin = linear or (lambda m, t: m(t))
+        B, L, d = x.shape
+        pos = torch.arange(L, device=x.device)
+        q, k, v = self._qkv(x, pos, lin)
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
+        if state is not None:
+            state["k"], state["v"] = k, v
+        return lin(self.out_proj, o.transpose(1, 2).reshape(B, L, d))
+
+    def step(self, x, state: dict, linear=None):
+        lin = linear or (lambda m, t: m(t))
+        B, _, d = x.shape
+        pos = torch.tensor([state["k"].shape[1]], device=x.device)
+        q, k, v = self._qkv(x, pos, lin)
+        state["k"] = torch.cat([state["k"], k], 1)
+        state["v"] = torch.cat([state["v"], v], 1)
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), state["k"].transpose(1, 2), state["v"].transpose(1, 2))
+        return lin(self.out_proj, o.transpose(1, 2).reshape(B, 1, d))
+
+
+class SwiGLU(nn.Module):
+    def __init__(self, d: int, ffn: int):
+        super().__init__()
+        self.l1 = nn.Linear(d, ffn, bias=False)     # gate
+        self.l2 = nn.Linear(d, ffn, bias=False)     # up
+        self.l3 = nn.Linear(ffn, d, bias=False)     # down
+
+    def forward(self, x, linear=None):
+        lin = linear or (lambda m, t: m(t))
+        return lin(self.l3, F.silu(lin(self.l1, x)) * lin(self.l2, x))
+
+
+class Block(nn.Module):
+    def __init__(self, cfg: Evo2Config, kind: str):
+        super().__init__()
+        self.kind = kind
+        self.pre_norm = RMSNorm(cfg.d_model, cfg.eps)
+        self.mixer = AttentionOperator(cfg) if kind == "attn" else HyenaOperator(cfg, kind)
+        self.post_norm = RMSNorm(cfg.d_model, cfg.eps)
+        self.mlp = SwiGLU(cfg.d_model, cfg.ffn)
+
+    def forward(self, x, state=None, linear=None):
+        x = x + self.mixer(self.pre_norm(x), state, linear)
+        return x + self.mlp(self.post_norm(x), linear)
+
+    def step(self, x, state, linear=None):
+        x = x + self.mixer.step(self.pre_norm(x), state, linear)
+        return x + self.mlp(self.post_norm(x), linear)
+
+
+class StripedHyena2(nn.Module):
+    def __init__(self, cfg: Evo2Config):
+        super().__init__()
+        self.cfg = cfg
+        self.embedding = nn.Embedding(cfg.vocab, cfg.d_model)
+        self.blocks = nn.ModuleList([Block(cfg, cfg.layer_kind(i)) for i in range(cfg.n_layers)])
+        self.norm = RMSNorm(cfg.d_model, cfg.eps)
+        self.linear = None          # optional callable (module, x) -> y replacing nn.Linear calls (fused / TP GEMMs)
+
+    def logits(self, x):
+        return F.linear(self.norm(x), self.embedding.weight)
+
+    @torch.no_grad()
+    def forward(self, tokens: torch.Tensor, states: Optional[List[dict]] = None) -> torch.Tensor:
+        """tokens: [B, L] -> logits [B, L, vocab].  ``states`` (a list of dicts, one per block) is filled for decoding."""
+        x = self.embedding(tokens)
+        for i, blk in enumerate(self.blocks):
+            x = blk(x, None if states is None else states[i], self.linear)
+        return self.logits(x)
+
+    @torch.no_grad()
+    def step(self, token: torch.Tensor, states: List[dict]) -> torch.Tensor:
+        x = self.embedding(token)
+        for i, blk in enumerate(self.blocks):
+            x = blk.step(x, states[i], self.linear)
+        return self.logits(x)
+
+    @torch.no_grad()
+    def generate(self, tokens: torch.Tensor, max_new_tokens: int) -> torch.Tensor:
+        """Greedy decoding: prefill, then ``max_new_tokens`` single-token steps."""
+        states = [dict() for _ in self.blocks]
+        logits = self.forward(tokens, states)
+        nxt = logits[:, -1:].argmax(-1)
+        out = [nxt]
+        for _ in range(max_new_tokens - 1):
+            logits = self.step(nxt, states)
+            nxt = logits[:, -1:].argmax(-1)
+            out.append(nxt)
+        return torch.cat(out, 1)
+
+    @torch.no_grad()
+    def score(self, tokens: torch.Tensor) -> torch.Tensor:
+        """Mean log-likelihood per sequence (the kit's ``score`` verb)."""
+        lp = torch.log_softmax(self.forward(tokens).float(), -1)
+        tgt = tokens[:, 1:]
+        return lp[:, :-1].gather(-1, tgt.unsqueeze(-1)).squeeze(-1).mean(-1)
+
+
+BYTE_LUT = {c: i for i, c in enumerate("ACGTN")}
+
+
+def tokenize(seq: str, device="cpu") -> torch.Tensor:
+    """Byte tokenizer (vocabulary 512; DNA letters map to their byte values)."""
+    return torch.tensor([[min(ord(c), 511) for c in seq]], dtype=torch.long, device=device)
+
+
+def build(config: str = "evo2_7b", device="cpu", dtype=torch.float32, seed: int = 0, **overrides) -> StripedHyena2:
+    cfg = CONFIGS[config]
+    if overrides:
+        cfg = replace(cfg, **overrides)
+    torch.manual_seed(seed)
+    with torch.device(device):
+        m = StripedHyena2(cfg)
+    m = m.to(dtype=dtype).eval()
+    for p in m.parameters():
+        p.requires_grad_(False)
+    return m

@@ -307,20 +307,35 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               if (k >= valid) t[k] = kNegBig;
           }
         }
-        float mt = t[0];
+        // four independent chains each for the maximum and the sum: a single chain of TK dependent
+        // operations would leave the two warps per scheduler waiting on instruction latency
+        float mx[4] = {t[0], t[1], t[2], t[3]};
 #pragma unroll
-        for (int k = 1; k < TK; ++k) mt = fmaxf(mt, t[k]);
+        for (int k = 4; k < TK; k += 4) {
+          mx[0] = fmaxf(mx[0], t[k]);
+          mx[1] = fmaxf(mx[1], t[k + 1]);
+          mx[2] = fmaxf(mx[2], t[k + 2]);
+          mx[3] = fmaxf(mx[3], t[k + 3]);
+        }
+        const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
         const float m_new = fmaxf(m, mt);
         const float alpha = fast_exp2(m - m_new);
-        float psum = 0.f;
+        float ps[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t pk[TK / 2];
 #pragma unroll
-        for (int k = 0; k < TK; k += 2) {
+        for (int k = 0; k < TK; k += 4) {
           const float p0 = fast_exp2(t[k] - m_new);
           const float p1 = fast_exp2(t[k + 1] - m_new);
-          psum += p0 + p1;
+          const float p2 = fast_exp2(t[k + 2] - m_new);
+          const float p3 = fast_exp2(t[k + 3] - m_new);
+          ps[0] += p0;
+          ps[1] += p1;
+          ps[2] += p2;
+          ps[3] += p3;
           pk[k >> 1] = pack_bf16x2(p0, p1);
+          pk[(k >> 1) + 1] = pack_bf16x2(p2, p3);
         }
+        const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
         l = l * alpha + psum;
         m = m_new;
 
