@@ -320,7 +320,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
         const float m_new = fmaxf(m, mt);
         const float alpha = fast_exp2(m - m_new);
-        float ps[4] = {0.f, 0.f, 0.f, 0.f};
+        float psv[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t pk[TK / 2];
 #pragma unroll
         for (int k = 0; k < TK; k += 4) {
@@ -328,14 +328,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           const float p1 = fast_exp2(t[k + 1] - m_new);
           const float p2 = fast_exp2(t[k + 2] - m_new);
           const float p3 = fast_exp2(t[k + 3] - m_new);
-          ps[0] += p0;
-          ps[1] += p1;
-          ps[2] += p2;
-          ps[3] += p3;
+          psv[0] += p0;
+          psv[1] += p1;
+          psv[2] += p2;
+          psv[3] += p3;
           pk[k >> 1] = pack_bf16x2(p0, p1);
           pk[(k >> 1) + 1] = pack_bf16x2(p2, p3);
         }
-        const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
+        const float psum = (psv[0] + psv[1]) + (psv[2] + psv[3]);
         l = l * alpha + psum;
         m = m_new;
 
