@@ -1,0 +1,141 @@
+"""Run one kernel of the library on a named case, timed with CUDA events (and small enough for ncu).
+
+    python benchmarks/kernel_cases.py <case> [--n N] [--iters K] [--warmup W]
+
+Cases: ``attention`` (triangle-attention core, H=4 x D=32, rows = N), ``attention_d64`` (token attention,
+16 heads x 64, 5 samples), ``trimul_proj``, ``trimul_gemm``, ``trimul_out``, ``triatt_proj``, ``transition``,
+``out_gemm`` (the [N*N,128] x [128,128] output projection with residual), ``trimul`` (three launches),
+``triatt`` (three launches).  Inputs are larger than L2 for N >= 768.  Prints one line per case with the
+mean time, the algorithmic bytes and FLOPs, and the fractions of the measured peaks in MEASURED_PEAKS.json
+(fallback 6.65 TB/s, 1.59 PFLOP/s when the file is absent).
+"""
+import argparse
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import torch
+
+from uplifting_biomolecular_modeling_b200.ops import gemm, native, pair
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "measured"
+    return 6.65e12, 1.59e15, "fallback"
+
+
+def timeit(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    ts = []
+    for _ in range(iters):
+        flush.zero_()                       # write a buffer larger than L2 between timed launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case")
+    ap.add_argument("--n", type=int, default=768)
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args()
+    N, c = a.n, 128
+    dev = "cuda"
+    torch.manual_seed(0)
+    r = lambda *s: torch.randn(*s, device=dev) * 0.08  # noqa: E731
+    ones, zeros = torch.ones(c, device=dev), torch.zeros(c, device=dev)
+    z = torch.randn(N, N, c, device=dev).bfloat16()
+    Np = pair.ceil_to(N, 8)
+    st = native.status_tensor(dev)
+    stream = native.current_stream(dev)
+    lib = native.lib()
+    byts = flops = 0
+    if a.case in ("attention", "attention_d64"):
+        if a.case == "attention":
+            rows, H, D = N, 4, 32
+        else:
+            rows, H, D = 5, 16, 64
+        q = torch.randn(rows, N, H * D, device=dev).bfloat16()
+        k, v, g = torch.randn_like(q), torch.randn_like(q), torch.rand_like(q)
+        bias = torch.randn(H, N, Np, device=dev).bfloat16()
+        out = torch.empty_like(q)
+        fn = lambda: pair.attention(q, k, v, bias, g, out, rows, N, N, H, D, ldb=Np)  # noqa: E731
+        byts = 5 * q.numel() * 2 + bias.numel() * 2
+        flops = 4.0 * rows * H * N * N * D
+    elif a.case in ("trimul_proj", "trimul_gemm", "trimul_out", "trimul"):
+        w = pair.TrimulPacked.pack(ones, zeros, r(256, c), r(256, c), ones, zeros, r(c, c), r(c, c))
+        planes = torch.empty((2, 128, N, Np), dtype=torch.bfloat16, device=dev)
+        x = torch.empty((128, N, Np), dtype=torch.bfloat16, device=dev)
+        out = torch.empty_like(z)
+        f1 = lambda: lib.ubm_trimul_proj(native.ptr(z), native.ptr(w.w_in), native.ptr(w.in_colsum),  # noqa: E731
+                                         native.ptr(w.in_colbias), 0, native.ptr(planes), 0, N, Np, native.ptr(st),
+                                         stream)
+        f2 = lambda: gemm.gemm(planes[0][:, :, :N], planes[1][:, :, :N], out=x[:, :, :N])  # noqa: E731
+        f3 = lambda: lib.ubm_trimul_out(native.ptr(x), native.ptr(z), native.ptr(w.wo), native.ptr(w.wg),  # noqa: E731
+                                        native.ptr(w.o_colsum), native.ptr(w.o_colbias), native.ptr(w.g_colsum),
+                                        native.ptr(w.g_colbias), native.ptr(out), N, Np, 1, native.ptr(st), stream)
+        f1(); f2()
+        zb = z.numel() * 2
+        if a.case == "trimul_proj":
+            fn, byts, flops = f1, 3 * zb, 2.0 * N * N * 128 * 512
+        elif a.case == "trimul_gemm":
+            fn, byts, flops = f2, 3 * zb, 2.0 * 128 * N ** 3
+        elif a.case == "trimul_out":
+            fn, byts, flops = f3, 3 * zb, 2.0 * N * N * 128 * 256
+        else:
+            fn = lambda: (f1(), f2(), f3())  # noqa: E731
+            byts, flops = 9 * zb, 2.0 * 128 * N ** 3 + 2.0 * N * N * 128 * 768
+    elif a.case in ("triatt_proj", "triatt"):
+        w = pair.TriattPacked.pack(ones, zeros, r(4, c), r(c, c), r(c, c), r(c, c), r(c, c), r(c), r(c, c), r(c), 4)
+        ws = {}
+        out = torch.empty_like(z)
+        if a.case == "triatt":
+            fn = lambda: pair.triangle_attention_fused(z, w, True, out=out, workspace=ws)  # noqa: E731
+            byts, flops = 11 * z.numel() * 2, 4.0 * N * 4 * N * N * 32 + 2.0 * N * N * 128 * 640
+        else:
+            bufs = torch.empty((4, N * N, 128), dtype=torch.bfloat16, device=dev)
+            hb = torch.zeros((4, N, Np), dtype=torch.bfloat16, device=dev)
+            fn = lambda: lib.ubm_triatt_proj(native.ptr(z), native.ptr(w.w), native.ptr(w.colsum),  # noqa: E731
+                                             native.ptr(w.colbias), native.ptr(w.wb), native.ptr(w.wb_colsum),
+                                             native.ptr(w.wb_colbias), native.ptr(bufs[0]), native.ptr(bufs[1]),
+                                             native.ptr(bufs[2]), native.ptr(bufs[3]), native.ptr(hb), 0, N, Np, 4, 0,
+                                             native.ptr(st), stream)
+            byts, flops = 5 * z.numel() * 2, 2.0 * N * N * 128 * 512
+    elif a.case == "transition":
+        w = pair.TransitionPacked.pack(ones, zeros, r(512, c), r(512, c), r(c, 512))
+        out = torch.empty_like(z)
+        fn = lambda: pair.transition_fused(z, w, out=out)  # noqa: E731
+        byts, flops = 2 * z.numel() * 2, 2.0 * N * N * (128 * 1024 + 512 * 128)
+    elif a.case == "out_gemm":
+        og = torch.randn(N * N, c, device=dev).bfloat16()
+        wo = r(c, c).bfloat16()
+        out = torch.empty_like(og)
+        fn = lambda: gemm.gemm(og, wo, bias=zeros, residual=z.view(N * N, c), out=out)  # noqa: E731
+        byts, flops = 3 * og.numel() * 2, 2.0 * N * N * c * c
+    else:
+        raise SystemExit(f"unknown case {a.case}")
+    ms = timeit(fn, a.iters, a.warmup)
+    native.raise_on_status(dev, a.case)
+    bw, fl, src = peaks()
+    print(f"CASE {a.case} N={N} ms={ms:.4f} GB/s={byts / ms / 1e6:.0f} ({byts / ms / 1e-3 / bw:.3f} of {src} HBM) "
+          f"TFLOP/s={flops / ms / 1e9:.0f} ({flops / ms / 1e-3 / fl:.3f} of {src} bf16)", flush=True)
+
+
+if __name__ == "__main__":
+    main()

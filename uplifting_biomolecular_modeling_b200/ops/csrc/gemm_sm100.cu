@@ -258,9 +258,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           if (p.residual != nullptr) {
             const __nv_bfloat16* rr = p.residual + b * p.strideR + static_cast<long long>(m) * p.ldr + n0;
+            if (n0 + 32 <= n_limit && (p.ldr & 7) == 0 && (p.strideR & 7) == 0 &&
+                (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (n0 + j < n_limit) f[j] += __bfloat162float(rr[j]);
+              for (int j8 = 0; j8 < 4; ++j8) {
+                const uint4 u = __ldg(reinterpret_cast<const uint4*>(rr) + j8);
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  f[j8 * 8 + 2 * e] += bf16_lo(w[e]);
+                  f[j8 * 8 + 2 * e + 1] += bf16_hi(w[e]);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + j < n_limit) f[j] += __bfloat162float(rr[j]);
+            }
           }
           if (p.out_fp32) {
             float* cp = reinterpret_cast<float*>(p.C) + b * p.strideC + static_cast<long long>(m) * p.ldc + n0;
