@@ -31,7 +31,13 @@ from .symm import SymmHeap
 
 
 class FusedRowPair:
-    def __init__(self, layout: Layout, comm: Comm, heap: SymmHeap, heads: int = 4):
+    def __init__(self, layout: Layout, comm: Comm, heap: SymmHeap, heads: int = 4, gather: str = "peer"):
+        """``gather="peer"``: the GEMM / attention kernels read the owners' shards themselves (fused);
+        ``gather="nccl"``: the shards are first all-gathered into local buffers with NCCL and the same
+        kernels run on the gathered copy - the NCCL-only baseline of the same schedule."""
+        if gather not in ("peer", "nccl"):
+            raise ValueError("gather must be 'peer' or 'nccl'")
+        self.gather = gather
         self.layout, self.comm, self.heap = layout, comm, heap
         self.rank, self.world = comm.rank, comm.world
         self.N = layout.n
@@ -62,14 +68,23 @@ class FusedRowPair:
                                           native.ptr(w.in_colbias), 0, native.ptr(self.planes.local), 0, R, Rmax, N, Np,
                                           native.ptr(st), stream)
             native.check(rc, "ubm_trimul_proj_rows")
-        self.heap.barrier()                      # every owner's b rows are written and visible
-        if R > 0:
-            b_off = 128 * Rmax * Np * 2          # byte offset of plane b inside each rank's buffer
-            a_loc = self.planes.local[0][:, :R, :N]
-            xv = self.x.view(-1)[: 128 * R * Np].view(128, R, Np)     # [128][rows][Np], what the output stage expects
-            peer.gemm_allgather_b(a_loc, [self.planes.ptr(q, b_off) for q in range(self.world)], self.counts,
-                                  xv[:, :, :N], K=N, ldb=Np, stride_b=Rmax * Np)
-        self.heap.barrier()                      # nobody still reads my planes when I overwrite them
+        xv = self.x.view(-1)[: 128 * max(R, 1) * Np].view(128, max(R, 1), Np)   # [128][rows][Np] for the output stage
+        a_loc = self.planes.local[0][:, :R, :N]
+        if self.gather == "peer":
+            self.heap.barrier()                  # every owner's b rows are written and visible
+            if R > 0:
+                b_off = 128 * Rmax * Np * 2      # byte offset of plane b inside each rank's buffer
+                peer.gemm_allgather_b(a_loc, [self.planes.ptr(q, b_off) for q in range(self.world)], self.counts,
+                                      xv[:, :, :N], K=N, ldb=Np, stride_b=Rmax * Np)
+            self.heap.barrier()                  # nobody still reads my planes when I overwrite them
+        else:
+            import torch.distributed as dist
+            if not hasattr(self, "_b_all"):
+                self._b_all = torch.empty((self.world, 128, Rmax, Np), dtype=torch.bfloat16, device=self.dev)
+            dist.all_gather_into_tensor(self._b_all, self.planes.local[1].contiguous())
+            if R > 0:
+                b_full = torch.cat([self._b_all[q][:, :self.counts[q], :N] for q in range(self.world)], dim=1)
+                _gemm.gemm(a_loc, b_full, out=xv[:, :, :N])
         if R > 0:
             out = torch.empty_like(z_loc)
             rc = lib.ubm_trimul_out_rows(native.ptr(self.x), native.ptr(z_loc), native.ptr(w.wo), native.ptr(w.wg),
@@ -94,11 +109,20 @@ class FusedRowPair:
                                           native.ptr(self.headbias.local), 0, R, Rmax, N, Np, H, 0, native.ptr(st),
                                           stream)
             native.check(rc, "ubm_triatt_proj_rows")
-        self.heap.barrier()
-        if R > 0:
-            peer.attention_peer_bias(q, k, v, [self.headbias.ptr(p) for p in range(self.world)], self.counts,
-                                     Rmax * Np, g, og, rows=R, N=N, H=H, ldb=Np)
-        self.heap.barrier()
+        if self.gather == "peer":
+            self.heap.barrier()
+            if R > 0:
+                peer.attention_peer_bias(q, k, v, [self.headbias.ptr(p) for p in range(self.world)], self.counts,
+                                         Rmax * Np, g, og, rows=R, N=N, H=H, ldb=Np)
+            self.heap.barrier()
+        else:
+            import torch.distributed as dist
+            if not hasattr(self, "_hb_all"):
+                self._hb_all = torch.empty((self.world, H, Rmax, Np), dtype=torch.bfloat16, device=self.dev)
+            dist.all_gather_into_tensor(self._hb_all, self.headbias.local)
+            if R > 0:
+                hb_full = torch.cat([self._hb_all[p][:, :self.counts[p]] for p in range(self.world)], dim=1).contiguous()
+                pair.attention(q, k, v, hb_full, g, og, rows=R, Nq=N, Nk=N, H=H, D=32, ldb=Np)
         src2 = src.view(R * N, 128)
         if starting:
             out = torch.empty_like(z_loc)
