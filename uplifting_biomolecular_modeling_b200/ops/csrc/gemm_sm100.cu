@@ -38,6 +38,12 @@ struct GemmParams {
   int peer_tile0[9];   // first n-tile of each shard (prefix sums), [npeers] = tiles_n
   int peer_col0[8];    // global column (= row of the gathered operand) where the shard starts
   int peer_cols[8];    // rows in the shard
+  // gather-once mode: the last `copy_ctas` CTAs pull the remote shards into a local buffer, tile block by
+  // tile block, and publish one flag per (batch, n-tile); compute CTAs read remote shards from that copy
+  int my_rank;
+  int copy_ctas;
+  uint32_t* ready;     // [batch * tiles_n] flags, value >= epoch means "this B block is local now"
+  uint32_t epoch;
 };
 
 constexpr int kMaxPeers = 8;
@@ -88,10 +94,35 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   }
 }
 
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Order of n-tiles in gather-once mode: shards are visited starting with this rank's own (no copy
+// needed), then rank+1, rank+2, ... so that the ranks pull from different owners at the same time.
+template <int BN>
+__device__ __forceinline__ void decode_ntile_rot(const GemmParams& p, int nb_rot, int& q, int& n_base, int& n_limit,
+                                                 int& local_row, int& nb_plain) {
+  int acc = 0;
+  q = p.my_rank;
+  for (int i = 0; i < p.npeers; ++i) {
+    const int qq = (p.my_rank + i) % p.npeers;
+    const int nt = p.peer_tile0[qq + 1] - p.peer_tile0[qq];
+    if (nb_rot < acc + nt) {
+      q = qq;
+      break;
+    }
+    acc += nt;
+  }
+  const int lb = nb_rot - acc;
+  local_row = lb * BN;
+  n_base = p.peer_col0[q] + local_row;
+  n_limit = p.peer_col0[q] + p.peer_cols[q];
+  nb_plain = p.peer_tile0[q] + lb;
+}
+
 template <int BN, bool MN_MAJOR, bool PEER>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ PeerMaps peers, GemmParams p) {
+                 const __grid_constant__ PeerMaps peers, const __grid_constant__ PeerMaps gathered, GemmParams p) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -131,17 +162,95 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int num_kb = (p.K + kBK - 1) / kBK;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
+  const int compute_ctas = PEER ? static_cast<int>(gridDim.x) - p.copy_ctas : static_cast<int>(gridDim.x);
+  const bool gather_once = PEER && p.copy_ctas > 0;
+  // copy CTAs take the lowest block indices so that they are resident before any compute CTA can wait on them
+  const int cta_id = PEER ? static_cast<int>(blockIdx.x) - p.copy_ctas : static_cast<int>(blockIdx.x);
+
+  if (PEER && cta_id < 0) {
+    // ---------------------------------------------------------------- copy role (gather-once mode)
+    // One thread streams remote B blocks [BN rows x 64 k] through the shared-memory ring: TMA load from the
+    // owner's memory (plain, no multicast), TMA store into the local gathered buffer; when all k-blocks of an
+    // n-tile are local, its flag is published.  Every remote byte crosses NVLink exactly once.
+    if (threadIdx.x == 0) {
+      constexpr int kSlots = Cfg::kStages * Cfg::kStageBytes / Cfg::kBBytes;   // 32 KB slots in the ring
+      static_assert(kSlots <= 2 * Cfg::kStages, "ring barriers");
+      uint64_t* slot_bar = full_bar;   // full_bar and empty_bar are contiguous: 2 * kStages barriers of count 1
+      const int cid = static_cast<int>(blockIdx.x);
+      const int own_tiles = p.peer_tile0[p.my_rank + 1] - p.peer_tile0[p.my_rank];
+      const int remote_tiles = p.tiles_n - own_tiles;
+      const long long chunks = static_cast<long long>(p.batch) * remote_tiles;
+      long long base_it = 0;
+      for (long long ch = cid; ch < chunks && !*abort_flag; ch += p.copy_ctas) {
+        const int b = static_cast<int>(ch / remote_tiles);
+        const int nb_rot = own_tiles + static_cast<int>(ch - static_cast<long long>(b) * remote_tiles);
+        int q, n_base, n_limit, lrow, nb_plain;
+        decode_ntile_rot<BN>(p, nb_rot, q, n_base, n_limit, lrow, nb_plain);
+        int kb_load = 0;
+        for (int kb_store = 0; kb_store < num_kb; ++kb_store) {
+          while (kb_load < num_kb && kb_load < kb_store + (kSlots - 1)) {
+            const long long it = base_it + kb_load;
+            const int sl = static_cast<int>(it % kSlots);
+            if (it >= kSlots) tma_store_wait_read<0>();   // whatever last used this slot has been read out
+            mbar_expect_tx(&slot_bar[sl], Cfg::kBBytes);
+            tma_load_3d(smem + sl * Cfg::kBBytes, &peers.m[q], &slot_bar[sl], kb_load * kBK, lrow, b);
+            ++kb_load;
+          }
+          const long long it = base_it + kb_store;
+          const int sl = static_cast<int>(it % kSlots);
+          mbar_wait(&slot_bar[sl], static_cast<uint32_t>((it / kSlots) & 1), ws, 5, sl);
+          if (*abort_flag) break;
+          tma_store_3d(&gathered.m[q], smem + sl * Cfg::kBBytes, kb_store * kBK, lrow, b);
+          tma_store_commit();
+        }
+        base_it += num_kb;
+        tma_store_wait_all<0>();     // the block is in local memory
+        fence_proxy_async_all();
+        __threadfence();
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ready + static_cast<long long>(b) * p.tiles_n +
+                                                                 nb_plain),
+                     "r"(p.epoch)
+                     : "memory");
+      }
+      tma_store_wait_all<0>();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+      tc_fence_after_sync();
+      tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+    return;
+  }
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+      for (int t = cta_id; t < p.num_tiles; t += compute_ctas) {
         const int b = t / tiles_per_batch;
         const int r = t - b * tiles_per_batch;
         const int nb = r / p.tiles_m;
         const int mb = r - nb * p.tiles_m;
+        int gq = 0, g_base = 0, g_limit = 0, g_lrow = 0, g_plain = 0;
+        if (gather_once) {
+          decode_ntile_rot<BN>(p, nb, gq, g_base, g_limit, g_lrow, g_plain);
+          if (gq != p.my_rank) {
+            // wait (bounded) until the copy CTAs have brought this B block into local memory
+            const uint32_t* flag = p.ready + static_cast<long long>(b) * p.tiles_n + g_plain;
+            const unsigned long long t0 = globaltimer_ns();
+            while (ld_acquire_gpu(flag) < p.epoch) {
+              if (*abort_flag) break;
+              if (globaltimer_ns() - t0 > kPeerLimitNs) {
+                report_failure(ws, kErrPeerTimeout, 6, static_cast<unsigned int>(g_plain));
+                break;
+              }
+              __nanosleep(200);
+            }
+            fence_proxy_async_all();
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           mbar_wait(&empty_bar[stage], phase ^ 1u, ws, 1, stage);
           if (*abort_flag) break;
@@ -150,7 +259,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
           if (!MN_MAJOR) {
             tma_load_3d(sa, &tmA, &full_bar[stage], kb * kBK, mb * kBM, b);
-            if (PEER) {
+            if (PEER && gather_once) {
+              // own shard straight from the local planes, remote shards from the gathered local copy
+              const CUtensorMap* bm = (gq == p.my_rank) ? &peers.m[gq] : &gathered.m[gq];
+              tma_load_3d(sb, bm, &full_bar[stage], kb * kBK, g_lrow, b);
+            } else if (PEER) {
               // B rows of this n-tile live on GPU q: plain (non-multicast) TMA load from its memory
               int q, n_base, n_limit, lrow;
               decode_ntile<BN>(p, nb, q, n_base, n_limit, lrow);
@@ -182,7 +295,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
-      for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+      for (int t = cta_id; t < p.num_tiles; t += compute_ctas) {
         mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, ws, 2, acc);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
@@ -225,7 +338,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                       (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)
                                    : ((p.ldc & 7) == 0 && (p.strideC & 7) == 0 &&
                                       (reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
-    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+    for (int t = cta_id; t < p.num_tiles; t += compute_ctas) {
       const int b = t / tiles_per_batch;
       const int r = t - b * tiles_per_batch;
       const int nb = r / p.tiles_m;
@@ -235,7 +348,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int m = mb * kBM + q * 32 + lane;
       const bool row_ok = m < p.M;
       int pq, n_base, n_limit, lrow;
-      decode_ntile<BN>(p, nb, pq, n_base, n_limit, lrow);
+      if (gather_once) {
+        int plain;
+        decode_ntile_rot<BN>(p, nb, pq, n_base, n_limit, lrow, plain);
+      } else {
+        decode_ntile<BN>(p, nb, pq, n_base, n_limit, lrow);
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int n0 = n_base + c * 32;
@@ -366,7 +484,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
   PeerMaps none;
   none.m[0] = tmB;
-  kern<<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, none, p);
+  kern<<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, none, none, p);
   UBM_CHECK_LAUNCH("gemm_bf16_kernel");
   return UBM_OK;
 }
@@ -426,10 +544,17 @@ extern "C" int ubm_gemm_bf16(const void* A, const void* B, void* C, const void* 
 //   B_ptrs[q]   bf16 [batch][rows_q][K] with leading dimension ldb and batch stride strideB (elements)
 //   rows[q]     number of rows of shard q;  the output has sum(rows) columns, shard q starting at the
 //               running sum.  K contiguous (K-major) only.
+// Gather-once mode (gathered != null, copy_ctas > 0): the last copy_ctas CTAs of the grid copy every remote
+// shard block into `gathered` ([batch][sum(rows)][K], leading dimension ldg, batch stride strideG) exactly once
+// and publish per-block flags in ready_flags ([batch * n_tiles] uint32, zero at first use; epoch grows by one per
+// call); compute CTAs start with the local shard and wait (bounded) for the flag of a remote block before
+// loading it from the local copy.  Without it every CTA re-reads remote tiles over NVLink for each m-tile.
 extern "C" int ubm_gemm_bf16_allgather_b(const void* A, const void* const* B_ptrs, const int* rows, int npeers,
                                          void* C, int M, int K, int batch, long long lda, long long ldb,
                                          long long ldc, long long strideA, long long strideB, long long strideC,
-                                         int out_fp32, float alpha, void* status, void* stream) {
+                                         int out_fp32, float alpha, int my_rank, int copy_ctas, void* gathered,
+                                         long long ldg, long long strideG, void* ready_flags, unsigned int epoch,
+                                         void* status, void* stream) {
   using namespace ubm;
   constexpr int BN = 256;
   using Cfg = GemmCfg<BN>;
@@ -446,7 +571,13 @@ extern "C" int ubm_gemm_bf16_allgather_b(const void* A, const void* const* B_ptr
   p.out_fp32 = out_fp32;
   p.status = static_cast<KernelStatus*>(status);
   p.npeers = npeers;
-  PeerMaps maps;
+  p.my_rank = my_rank;
+  p.copy_ctas = (gathered != nullptr && ready_flags != nullptr && npeers > 1) ? copy_ctas : 0;
+  p.ready = static_cast<uint32_t*>(ready_flags);
+  p.epoch = epoch;
+  if (my_rank < 0 || my_rank >= npeers) return UBM_ERR_ARGUMENT;
+  if (p.copy_ctas > 0 && ((ldg & 7) || (strideG & 7))) return UBM_ERR_ARGUMENT;
+  PeerMaps maps, gmaps;
   int col = 0, tile = 0;
   CUtensorMap tmA;
   {
@@ -467,13 +598,26 @@ extern "C" int ubm_gemm_bf16_allgather_b(const void* A, const void* const* B_ptr
       int rc = make_tmap(&maps.m[q], B_ptrs[q], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dB, sB, bB,
                          CU_TENSOR_MAP_SWIZZLE_128B);
       if (rc) return rc;
+      gmaps.m[q] = maps.m[q];
+      if (p.copy_ctas > 0) {
+        // shard q inside the local gathered buffer [batch][sum(rows)][K]: clipped to the shard's own rows
+        uint64_t sG[2] = {(uint64_t)ldg * 2, (uint64_t)strideG * 2};
+        const __nv_bfloat16* gbase = static_cast<const __nv_bfloat16*>(gathered) + static_cast<long long>(col) * ldg;
+        rc = make_tmap(&gmaps.m[q], gbase, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dB, sG, bB,
+                       CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+      }
     } else {
       maps.m[q] = tmA;
+      gmaps.m[q] = tmA;
     }
     col += rows[q];
     tile += (rows[q] + BN - 1) / BN;
   }
-  for (int q = npeers; q < kMaxPeers; ++q) maps.m[q] = tmA;
+  for (int q = npeers; q < kMaxPeers; ++q) {
+    maps.m[q] = tmA;
+    gmaps.m[q] = tmA;
+  }
   p.peer_tile0[npeers] = tile;
   p.N = col;
   p.tiles_m = (M + kBM - 1) / kBM;
@@ -483,8 +627,14 @@ extern "C" int ubm_gemm_bf16_allgather_b(const void* A, const void* const* B_ptr
   auto kern = gemm_bf16_kernel<BN, false, true>;
   int rc = set_smem(kern, Cfg::kSmemBytes);
   if (rc) return rc;
-  const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  kern<<<grid, 192, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmA, tmA, maps, p);
+  int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  if (p.copy_ctas > 0) {
+    // compute CTAs + copy CTAs must all be resident at once (one CTA per SM): never more than the SM count
+    if (p.copy_ctas >= sm_count()) return UBM_ERR_ARGUMENT;
+    const int compute = sm_count() - p.copy_ctas;
+    grid = (p.num_tiles < compute ? p.num_tiles : compute) + p.copy_ctas;
+  }
+  kern<<<grid, 192, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmA, tmA, maps, gmaps, p);
   UBM_CHECK_LAUNCH("gemm_bf16_kernel<peer>");
   return UBM_OK;
 }

@@ -12,7 +12,7 @@ from .native import c_float, c_int, c_ll, c_void_p
 
 native.declare("ubm_gemm_bf16_allgather_b",
                [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll,
-                c_int, c_float, c_void_p, c_void_p])
+                c_int, c_float, c_int, c_int, c_void_p, c_ll, c_ll, c_void_p, ctypes.c_uint, c_void_p, c_void_p])
 native.declare("ubm_attention_d32_peer_bias",
                [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_ll, c_void_p, c_void_p, c_int, c_int, c_int,
                 c_int, c_ll, c_ll, c_void_p, c_void_p])
@@ -29,15 +29,34 @@ def _ints(vals: Sequence[int]):
     return (ctypes.c_int * len(vals))(*[int(v) for v in vals])
 
 
+class GatherState:
+    """Per-buffer state of the gather-once mode: the local gathered copy, its ready flags and the epoch."""
+
+    def __init__(self, batch: int, total_rows: int, ld: int, device, copy_ctas: int = 16):
+        self.buf = torch.empty((batch, total_rows, ld), dtype=torch.bfloat16, device=device)
+        self.flags = torch.zeros(batch * ((total_rows + 255) // 256 + 8), dtype=torch.int32, device=device)
+        self.epoch = 0
+        self.copy_ctas = copy_ctas
+
+
 def gemm_allgather_b(a: torch.Tensor, b_ptrs: Sequence[int], rows: Sequence[int], out: torch.Tensor, K: int,
-                     ldb: int, stride_b: int, alpha: float = 1.0) -> torch.Tensor:
+                     ldb: int, stride_b: int, alpha: float = 1.0, my_rank: int = 0,
+                     gather: "GatherState | None" = None) -> torch.Tensor:
     """out[c][m][col0_q + n] = sum_k a[c][m][k] * B_q[c][n][k]; B_q = bf16 [batch][rows[q]][K] at b_ptrs[q]
-    (possibly on another GPU) with leading dimension ldb and batch stride stride_b (elements)."""
+    (possibly on another GPU) with leading dimension ldb and batch stride stride_b (elements).  With a
+    :class:`GatherState` the kernel's copy CTAs bring each remote block into local memory once."""
     batch, M = a.shape[0], a.shape[1]
     st = native.status_tensor(a.device)
+    if gather is not None:
+        gather.epoch += 1
+        g_args = (gather.copy_ctas, native.ptr(gather.buf), gather.buf.stride(1), gather.buf.stride(0),
+                  native.ptr(gather.flags), gather.epoch)
+    else:
+        g_args = (0, 0, 0, 0, 0, 0)
     rc = native.lib().ubm_gemm_bf16_allgather_b(native.ptr(a), _ptrs(b_ptrs), _ints(rows), len(rows), native.ptr(out),
                                                 M, K, batch, a.stride(1), ldb, out.stride(1), a.stride(0), stride_b,
                                                 out.stride(0), 1 if out.dtype == torch.float32 else 0, float(alpha),
+                                                my_rank, *g_args,
                                                 native.ptr(st), native.current_stream(a.device))
     native.check(rc, "ubm_gemm_bf16_allgather_b")
     return out

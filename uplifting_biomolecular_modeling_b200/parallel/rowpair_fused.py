@@ -33,10 +33,11 @@ from .symm import SymmHeap
 class FusedRowPair:
     def __init__(self, layout: Layout, comm: Comm, heap: SymmHeap, heads: int = 4, gather: str = "peer"):
         """``gather="peer"``: the GEMM / attention kernels read the owners' shards themselves (fused);
+        ``gather="peer_direct"``: as "peer" but the GEMM re-reads remote tiles per m-tile instead of copying them once;
         ``gather="nccl"``: the shards are first all-gathered into local buffers with NCCL and the same
         kernels run on the gathered copy - the NCCL-only baseline of the same schedule."""
-        if gather not in ("peer", "nccl"):
-            raise ValueError("gather must be 'peer' or 'nccl'")
+        if gather not in ("peer", "peer_direct", "nccl"):
+            raise ValueError("gather must be 'peer', 'peer_direct' or 'nccl'")
         self.gather = gather
         self.layout, self.comm, self.heap = layout, comm, heap
         self.rank, self.world = comm.rank, comm.world
@@ -70,12 +71,17 @@ class FusedRowPair:
             native.check(rc, "ubm_trimul_proj_rows")
         xv = self.x.view(-1)[: 128 * max(R, 1) * Np].view(128, max(R, 1), Np)   # [128][rows][Np] for the output stage
         a_loc = self.planes.local[0][:, :R, :N]
-        if self.gather == "peer":
+        if self.gather in ("peer", "peer_direct"):
             self.heap.barrier()                  # every owner's b rows are written and visible
             if R > 0:
                 b_off = 128 * Rmax * Np * 2      # byte offset of plane b inside each rank's buffer
+                gs = None
+                if self.gather == "peer" and self.world > 1:
+                    if not hasattr(self, "_gather_b"):
+                        self._gather_b = peer.GatherState(128, N, Np, self.dev)
+                    gs = self._gather_b
                 peer.gemm_allgather_b(a_loc, [self.planes.ptr(q, b_off) for q in range(self.world)], self.counts,
-                                      xv[:, :, :N], K=N, ldb=Np, stride_b=Rmax * Np)
+                                      xv[:, :, :N], K=N, ldb=Np, stride_b=Rmax * Np, my_rank=self.rank, gather=gs)
             self.heap.barrier()                  # nobody still reads my planes when I overwrite them
         else:
             import torch.distributed as dist
@@ -109,7 +115,9 @@ class FusedRowPair:
                                           native.ptr(self.headbias.local), 0, R, Rmax, N, Np, H, 0, native.ptr(st),
                                           stream)
             native.check(rc, "ubm_triatt_proj_rows")
-        if self.gather == "peer":
+        # the bias tiles are reused by every row pair: reading them in-kernel from the owner crosses NVLink once
+        # per reuse, so only the "peer_direct" mode does that; otherwise the planes are gathered once
+        if self.gather == "peer_direct":
             self.heap.barrier()
             if R > 0:
                 peer.attention_peer_bias(q, k, v, [self.headbias.ptr(p) for p in range(self.world)], self.counts,
