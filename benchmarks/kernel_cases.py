@@ -54,8 +54,10 @@ def main():
     ap.add_argument("--n", type=int, default=768)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--attn-variant", type=int, default=0, help="0 = by shape, 1 = two rows per CTA")
     a = ap.parse_args()
     N, c = a.n, 128
+    pair.set_attention_variant(a.attn_variant)
     dev = "cuda"
     torch.manual_seed(0)
     r = lambda *s: torch.randn(*s, device=dev) * 0.08  # noqa: E731

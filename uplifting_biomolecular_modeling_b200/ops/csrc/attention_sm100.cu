@@ -17,27 +17,41 @@
 // O is rescaled in TMEM only when a running maximum moved.  No TMA multicast is used: the bias
 // tile is loaded once per CTA and reused by both rows from shared memory.
 //
-// Persistent CTAs walk (head, query tile, row pair) with the row pair fastest, so CTAs that
-// run together read the same bias tiles from L2.
+// Persistent CTAs walk (head, row group, query tile) with the query tile fastest: CTAs that run together
+// work on the same rows, so each K / V tile comes from HBM once and is re-read from L2 by the other query
+// tiles; the bias planes of a head (a few MB) stay in L2 throughout.
 #include "host_util.h"
 #include "sm100.cuh"
 
 namespace ubm {
 
+
 constexpr int kATile = 128;  // queries per CTA
-constexpr int kAStages = 2;
 constexpr float kNegBig = -1.0e30f;
 
 // D = head dimension (32 or 64), TK = keys per step (128 for D = 32, 64 for D = 64 so that two rows,
 // two stages and the P tiles still fit in shared memory).
-template <int D, int TK>
+// R2 = rows per CTA (softmax warpgroups sharing each bias tile): 2, or 4 with TK = 64 - four warps per
+// scheduler hide the TMEM-load -> bias -> max -> exp latency chain that two cannot.
+template <int D, int TK, int R2>
 struct AttnCfg {
   static constexpr int kQBytes = kATile * D * 2;
   static constexpr int kKVBytes = TK * D * 2;
   static constexpr int kBiasBytes = kATile * TK * 2;
-  static constexpr int kStageBytes = 4 * kKVBytes + kBiasBytes;  // K0 V0 K1 V1 bias
+  static constexpr int kStageBytes = 2 * R2 * kKVBytes + kBiasBytes;  // {K, V} per row, then the bias tile
   static constexpr int kPBytes = kATile * TK * 2;
-  static constexpr int kSmemBytes = 2 * kQBytes + kAStages * kStageBytes + 2 * kPBytes + 256 + 1024;
+  // As many stages as fit: the loop is bound by the latency of the tile loads unless they are issued
+  // several tiles ahead (with two stages every tile waited a full TMA round trip).
+  static constexpr int kStages = (224 * 1024 - R2 * kQBytes - R2 * kPBytes) / kStageBytes;
+  static_assert(kStages >= 2 && kStages <= 8, "stage count");
+  static constexpr int kSmemBytes = R2 * kQBytes + kStages * kStageBytes + R2 * kPBytes + 512 + 1024;
+  static constexpr int kThreads = 128 + R2 * 128;
+  // setmaxnreg moves registers inside the pool the CTA was launched with (threads x compiled registers):
+  //   R2 = 2: 384 x 168 = 64512 = 128 x 56 + 256 x 224;   R2 = 4: 640 x 96 = 61440 >= 128 x 56 + 512 x 104.
+  // An increase that does not fit that pool would wait forever, so these pairs are checked below.
+  static constexpr int kLaunchRegs = (R2 == 2) ? 168 : 96;
+  static constexpr int kSoftmaxRegs = (R2 == 2) ? 224 : 104;
+  static_assert(128 * 56 + R2 * 128 * kSoftmaxRegs <= kThreads * kLaunchRegs, "setmaxnreg budget");
   static constexpr uint64_t kSwz = (D == 32) ? kSwizzle64 : kSwizzle128;  // operand rows are D * 2 bytes
   static constexpr uint32_t kSbo = (D == 32) ? 512 : 1024;               // 8 rows of D * 2 bytes
   static constexpr uint32_t kVStep = 16 * D * 2;                         // 16 keys of V
@@ -83,32 +97,33 @@ __device__ __forceinline__ void decode_qtile(const AttnParams& p, int qt, int& q
   q_limit = p.peer_row0[q] + p.peer_rows[q];
 }
 
-template <int D, int TK, bool PEER>
-__global__ void __launch_bounds__(384, 1)
+template <int D, int TK, int R2, bool PEER>
+__global__ void __launch_bounds__(128 + R2 * 128, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ BiasPeerMaps peers, AttnParams p) {
-  using Cfg = AttnCfg<D, TK>;
+  using Cfg = AttnCfg<D, TK, R2>;
   constexpr int kAD = D;
   constexpr int kAQBytes = Cfg::kQBytes;
   constexpr int kAKVBytes = Cfg::kKVBytes;
   constexpr int kAStageBytes = Cfg::kStageBytes;
   constexpr int kAPBytes = Cfg::kPBytes;
+  constexpr int kAStages = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;                              // 2 x Q tile
-  uint8_t* sSt = sQ + 2 * kAQBytes;                // stages x 64 KB
-  uint8_t* sP = sSt + kAStages * kAStageBytes;     // 2 x 32 KB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kAPBytes);
+  uint8_t* sQ = smem;                              // R2 x Q tile
+  uint8_t* sSt = sQ + R2 * kAQBytes;               // stages
+  uint8_t* sP = sSt + kAStages * kAStageBytes;     // R2 x P tile
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + R2 * kAPBytes);
   uint64_t* q_full = bars;             // [1]
   uint64_t* q_empty = q_full + 1;      // [1] commit
   uint64_t* kv_full = q_empty + 1;     // [stages]
   uint64_t* kv_empty = kv_full + kAStages;   // [stages] commit + 8 warps
-  uint64_t* s_full = kv_empty + kAStages;    // [2] commit
-  uint64_t* s_empty = s_full + 2;      // [2] 4 warps
-  uint64_t* p_full = s_empty + 2;      // [2] 4 warps
-  uint64_t* pv_done = p_full + 2;      // [2] commit
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+  uint64_t* s_full = kv_empty + kAStages;    // [R2] commit
+  uint64_t* s_empty = s_full + R2;     // [R2] 4 warps
+  uint64_t* p_full = s_empty + R2;     // [R2] 4 warps
+  uint64_t* pv_done = p_full + R2;     // [R2] commit
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + R2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -121,9 +136,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(q_empty, 1);
     for (int s = 0; s < kAStages; ++s) {
       mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1 + 8);
+      mbar_init(&kv_empty[s], 1 + 4 * R2);
     }
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < R2; ++r) {
       mbar_init(&s_full[r], 1);
       mbar_init(&s_empty[r], 4);
       mbar_init(&p_full[r], 4);
@@ -143,47 +158,48 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base;         // S[r] at r * 128
+  const uint32_t tS = tmem_base;         // S[r] at r * TK
   const uint32_t tO = tmem_base + 256;   // O[r] at r * D
   const int T = p.n_kt;
 
-  // Register split: warps 0-3 (producer, MMA issuer, two idle warps) give registers up, the two
-  // softmax warpgroups (warps 4-7 and 8-11) take them: 128 * 40 + 256 * 232 <= 65536.
+  // Register split: warps 0-3 (producer, MMA issuer, two idle warps) give registers up, the softmax
+  // warpgroups take them (budget checked in AttnCfg and again on the host before launch).
   if (warp < 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t item_cnt = 0, gk = 0;
       for (int item = blockIdx.x; item < p.num_items; item += gridDim.x, ++item_cnt) {
-        const int rp = item % p.n_rp;
-        const int tmp = item / p.n_rp;
-        const int qt = tmp % p.n_qt;
-        const int h = tmp / p.n_qt;
-        const int r0 = rp * 2;
+        const int qt = item % p.n_qt;
+        const int tmp = item / p.n_qt;
+        const int rp = tmp % p.n_rp;
+        const int h = tmp / p.n_rp;
+        const int r0 = rp * R2;
         mbar_wait(q_empty, (item_cnt & 1u) ^ 1u, ws, 51);
         if (*abort_flag) break;
         int pq, q_base, q_limit, lrow;
         decode_qtile(p, qt, pq, q_base, q_limit, lrow);
-        mbar_expect_tx(q_full, 2 * kAQBytes);
-        tma_load_3d(sQ, &tmQ, q_full, h * kAD, q_base, r0);
-        tma_load_3d(sQ + kAQBytes, &tmQ, q_full, h * kAD, q_base, r0 + 1);
+        mbar_expect_tx(q_full, R2 * kAQBytes);
+#pragma unroll
+        for (int rr = 0; rr < R2; ++rr) tma_load_3d(sQ + rr * kAQBytes, &tmQ, q_full, h * kAD, q_base, r0 + rr);
         for (int j = 0; j < T; ++j, ++gk) {
-          const int s = gk & 1;
-          mbar_wait(&kv_empty[s], ((gk >> 1) & 1u) ^ 1u, ws, 52, s);
+          const int s = gk % kAStages;
+          mbar_wait(&kv_empty[s], ((gk / kAStages) & 1u) ^ 1u, ws, 52, s);
           if (*abort_flag) break;
           uint8_t* st = sSt + s * kAStageBytes;
-          mbar_expect_tx(&kv_full[s], p.has_bias ? kAStageBytes : 4 * kAKVBytes);
-          tma_load_3d(st, &tmK, &kv_full[s], h * kAD, j * TK, r0);
-          tma_load_3d(st + kAKVBytes, &tmV, &kv_full[s], h * kAD, j * TK, r0);
-          tma_load_3d(st + 2 * kAKVBytes, &tmK, &kv_full[s], h * kAD, j * TK, r0 + 1);
-          tma_load_3d(st + 3 * kAKVBytes, &tmV, &kv_full[s], h * kAD, j * TK, r0 + 1);
+          mbar_expect_tx(&kv_full[s], p.has_bias ? kAStageBytes : 2 * R2 * kAKVBytes);
+#pragma unroll
+          for (int rr = 0; rr < R2; ++rr) {
+            tma_load_3d(st + (2 * rr) * kAKVBytes, &tmK, &kv_full[s], h * kAD, j * TK, r0 + rr);
+            tma_load_3d(st + (2 * rr + 1) * kAKVBytes, &tmV, &kv_full[s], h * kAD, j * TK, r0 + rr);
+          }
           if (p.has_bias) {
 #pragma unroll
             for (int hb = 0; hb < TK / 64; ++hb) {
               // peer mode: the bias rows of this query tile live on GPU pq (plain TMA load, no multicast)
               const CUtensorMap* bm = PEER ? &peers.m[pq] : &tmB;
-              tma_load_3d(st + 4 * kAKVBytes + hb * 16384, bm, &kv_full[s], j * TK + hb * 64, lrow, h);
+              tma_load_3d(st + 2 * R2 * kAKVBytes + hb * 16384, bm, &kv_full[s], j * TK + hb * 64, lrow, h);
             }
           }
         }
@@ -197,22 +213,22 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, kAD, 0, 1);  // B = V is MN-major
       uint32_t item_cnt = 0, gk = 0;
       auto issue_qk = [&](int r, uint32_t g) {
-        const uint32_t st = smem_u32(sSt + (g & 1) * kAStageBytes);
+        const uint32_t st = smem_u32(sSt + (g % kAStages) * kAStageBytes);
         const uint32_t qa = smem_u32(sQ + r * kAQBytes);
         const uint32_t ka = st + r * 2 * kAKVBytes;
 #pragma unroll
         for (int k = 0; k < kAD / 16; ++k) {
           const uint64_t ad = umma_smem_desc(qa + k * 32, 16, Cfg::kSbo, Cfg::kSwz);
           const uint64_t bd = umma_smem_desc(ka + k * 32, 16, Cfg::kSbo, Cfg::kSwz);
-          umma_ss(tS + r * 128, ad, bd, idesc_qk, k != 0 ? 1u : 0u);
+          umma_ss(tS + r * TK, ad, bd, idesc_qk, k != 0 ? 1u : 0u);
         }
         umma_commit(&s_full[r]);
       };
       for (int item = blockIdx.x; item < p.num_items; item += gridDim.x, ++item_cnt) {
         mbar_wait(q_full, item_cnt & 1u, ws, 53);
-        mbar_wait(&kv_full[gk & 1], (gk >> 1) & 1u, ws, 54, 0);
+        mbar_wait(&kv_full[gk % kAStages], (gk / kAStages) & 1u, ws, 54, 0);
         tc_fence_after_sync();
-        for (int r = 0; r < 2; ++r) {
+        for (int r = 0; r < R2; ++r) {
           mbar_wait(&s_empty[r], (gk & 1u) ^ 1u, ws, 55, r);
           tc_fence_after_sync();
           issue_qk(r, gk);
@@ -220,16 +236,16 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int j = 0; j < T; ++j) {
           const uint32_t g = gk + j;
           if (j + 1 < T) {
-            mbar_wait(&kv_full[(g + 1) & 1], ((g + 1) >> 1) & 1u, ws, 56, 1);
+            mbar_wait(&kv_full[(g + 1) % kAStages], ((g + 1) / kAStages) & 1u, ws, 56, 1);
             tc_fence_after_sync();
-            for (int r = 0; r < 2; ++r) {
+            for (int r = 0; r < R2; ++r) {
               mbar_wait(&s_empty[r], ((g + 1) & 1u) ^ 1u, ws, 57, r);
               tc_fence_after_sync();
               issue_qk(r, g + 1);
             }
           }
-          const uint32_t st = smem_u32(sSt + (g & 1) * kAStageBytes);
-          for (int r = 0; r < 2; ++r) {
+          const uint32_t st = smem_u32(sSt + (g % kAStages) * kAStageBytes);
+          for (int r = 0; r < R2; ++r) {
             mbar_wait(&p_full[r], g & 1u, ws, 58, r);
             tc_fence_after_sync();
             const uint32_t pa = smem_u32(sP + r * kAPBytes);
@@ -243,7 +259,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             umma_commit(&pv_done[r]);
           }
-          umma_commit(&kv_empty[g & 1]);
+          umma_commit(&kv_empty[g % kAStages]);
         }
         umma_commit(q_empty);
         gk += T;
@@ -251,18 +267,22 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    if (R2 == 2) {
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    } else {
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+    }
     // ------------------------------------------------------------------ softmax warpgroups
-    const int r_in = (warp - 4) >> 2;  // which of the two rows
+    const int r_in = (warp - 4) >> 2;  // which of the R2 rows
     const int quad = warp & 3;
     const int qrow = quad * 32 + lane;
     uint32_t gk = 0;
     for (int item = blockIdx.x; item < p.num_items; item += gridDim.x) {
-      const int rp = item % p.n_rp;
-      const int tmp = item / p.n_rp;
-      const int qt = tmp % p.n_qt;
-      const int h = tmp / p.n_qt;
-      const int r = rp * 2 + r_in;
+      const int qt = item % p.n_qt;
+      const int tmp = item / p.n_qt;
+      const int rp = tmp % p.n_rp;
+      const int h = tmp / p.n_rp;
+      const int r = rp * R2 + r_in;
       int pq, q_base, q_limit, lrow;
       decode_qtile(p, qt, pq, q_base, q_limit, lrow);
       const int qi = q_base + qrow;
@@ -274,7 +294,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         float t[TK];
         {
           uint32_t* tu = reinterpret_cast<uint32_t*>(t);
-          const uint32_t ta = tmem_addr(tS, quad, r_in * 128);
+          const uint32_t ta = tmem_addr(tS, quad, r_in * TK);
 #pragma unroll
           for (int c = 0; c < TK / 32; ++c) tmem_ld32(ta + c * 32, *reinterpret_cast<uint32_t(*)[32]>(tu + c * 32));
           tmem_ld_wait();
@@ -283,9 +303,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_empty[r_in]);
 
-        mbar_wait(&kv_full[g & 1], (g >> 1) & 1u, ws, 60, r_in);
+        mbar_wait(&kv_full[g % kAStages], (g / kAStages) & 1u, ws, 60, r_in);
         if (p.has_bias) {
-          const uint8_t* bs = sSt + (g & 1) * kAStageBytes + 4 * kAKVBytes;
+          const uint8_t* bs = sSt + (g % kAStages) * kAStageBytes + 2 * R2 * kAKVBytes;
 #pragma unroll
           for (int c16 = 0; c16 < TK / 8; ++c16) {
             const uint4 u = *reinterpret_cast<const uint4*>(bs + (c16 >> 3) * 16384 + swz128_offset(qrow, c16 & 7));
@@ -298,7 +318,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&kv_empty[g & 1]);
+        if (lane == 0) mbar_arrive(&kv_empty[g % kAStages]);
         if (j == T - 1) {
           const int valid = p.Nk - j * TK;
           if (valid < TK) {
@@ -422,12 +442,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-template <int D, int TK>
+template <int D, int TK, int R2>
 static int launch_attention(const void* q, const void* k, const void* v, const void* bias, const void* gate, void* out,
                             int rows, int Nq, int Nk, int H, long long ldb, long long ld_in, int transpose_out,
                             void* status, void* stream, int npeers = 0, const void* const* bias_ptrs = nullptr,
                             const int* peer_rows = nullptr, long long peer_head_stride = 0) {
-  using Cfg = AttnCfg<D, TK>;
+  using Cfg = AttnCfg<D, TK, R2>;
   const uint64_t hd = (uint64_t)H * D;
   const uint64_t ldi = ld_in > 0 ? (uint64_t)ld_in : hd;  // row stride of q / k / v in elements
   if (ldi < hd || (ldi & 7)) return UBM_ERR_ARGUMENT;
@@ -470,7 +490,7 @@ static int launch_attention(const void* q, const void* k, const void* v, const v
   p.status = static_cast<KernelStatus*>(status);
   p.n_qt = (Nq + kATile - 1) / kATile;
   p.n_kt = (Nk + TK - 1) / TK;
-  p.n_rp = (rows + 1) / 2;
+  p.n_rp = (rows + R2 - 1) / R2;
   BiasPeerMaps maps;
   for (int i = 0; i < kAMaxPeers; ++i) maps.m[i] = tmQ;
   if (npeers > 0) {
@@ -499,22 +519,38 @@ static int launch_attention(const void* q, const void* k, const void* v, const v
   }
   p.num_items = p.n_qt * p.n_rp * H;
   const int grid = p.num_items < sm_count() ? p.num_items : sm_count();
+  {
+    // the in-kernel register re-split must fit the pool this build was compiled with, or it would never return
+    cudaFuncAttributes fa;
+    cudaError_t e = npeers > 0 ? cudaFuncGetAttributes(&fa, attention_kernel<D, TK, R2, true>)
+                               : cudaFuncGetAttributes(&fa, attention_kernel<D, TK, R2, false>);
+    if (e != cudaSuccess || 128 * 56 + R2 * 128 * Cfg::kSoftmaxRegs > Cfg::kThreads * fa.numRegs) {
+      fprintf(stderr, "[ubm] attention: register budget check failed (numRegs=%d)\n", e == cudaSuccess ? fa.numRegs : -1);
+      return UBM_ERR_LAUNCH;
+    }
+  }
   if (npeers > 0) {
-    auto kern = attention_kernel<D, TK, true>;
+    auto kern = attention_kernel<D, TK, R2, true>;
     int rc = set_smem(kern, Cfg::kSmemBytes);
     if (rc) return rc;
-    kern<<<grid, 384, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmB, maps, p);
+    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmB, maps, p);
   } else {
-    auto kern = attention_kernel<D, TK, false>;
+    auto kern = attention_kernel<D, TK, R2, false>;
     int rc = set_smem(kern, Cfg::kSmemBytes);
     if (rc) return rc;
-    kern<<<grid, 384, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmB, maps, p);
+    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmB, maps, p);
   }
   UBM_CHECK_LAUNCH("attention_kernel");
   return UBM_OK;
 }
 
 }  // namespace ubm
+
+static int g_attn_variant = 0;
+extern "C" int ubm_attention_set_variant(int v) {
+  g_attn_variant = v & 0xff;  // 0 / 1 = 128-key steps, two rows per CTA; 2 = four rows per CTA; 3 = 64-key steps
+  return 0;
+}
 
 // q, k, v, gate, out: bf16 [rows][N*][H*D] (innermost contiguous).  bias: bf16 [H][Nq][ldb] (ldb multiple
 // of 8) or null.  q must carry the factor log2(e)/sqrt(d) and bias the factor log2(e).  transpose_out
@@ -525,8 +561,14 @@ extern "C" int ubm_attention_d32(const void* q, const void* k, const void* v, co
                                  int transpose_out, void* status, void* stream) {
   if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0) return ubm::UBM_ERR_ARGUMENT;
   if (bias != nullptr && (ldb < Nk || (ldb & 7))) return ubm::UBM_ERR_ARGUMENT;
-  return ubm::launch_attention<32, 128>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
-                                        status, stream);
+  if (g_attn_variant == 2 && rows >= 3)
+    return ubm::launch_attention<32, 64, 4>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
+                                            status, stream);
+  if (g_attn_variant == 3)
+    return ubm::launch_attention<32, 64, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
+                                            status, stream);
+  return ubm::launch_attention<32, 128, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
+                                           status, stream);
 }
 
 extern "C" int ubm_attention_d64(const void* q, const void* k, const void* v, const void* bias, const void* gate,
@@ -534,8 +576,8 @@ extern "C" int ubm_attention_d64(const void* q, const void* k, const void* v, co
                                  int transpose_out, void* status, void* stream) {
   if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0) return ubm::UBM_ERR_ARGUMENT;
   if (bias != nullptr && (ldb < Nk || (ldb & 7))) return ubm::UBM_ERR_ARGUMENT;
-  return ubm::launch_attention<64, 64>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
-                                       status, stream);
+  return ubm::launch_attention<64, 64, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
+                                          status, stream);
 }
 
 // Pair-bias all-gather fused into the attention kernel (head dimension 32): the bias planes are row
@@ -549,6 +591,6 @@ extern "C" int ubm_attention_d32_peer_bias(const void* q, const void* k, const v
                                            long long ld_in, void* status, void* stream) {
   if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0 || npeers <= 0) return ubm::UBM_ERR_ARGUMENT;
   if (ldb < Nk || (ldb & 7) || (peer_head_stride & 7)) return ubm::UBM_ERR_ARGUMENT;
-  return ubm::launch_attention<32, 128>(q, k, v, nullptr, gate, out, rows, Nq, Nk, H, ldb, ld_in, 0, status, stream,
-                                        npeers, bias_ptrs, peer_rows, peer_head_stride);
+  return ubm::launch_attention<32, 128, 2>(q, k, v, nullptr, gate, out, rows, Nq, Nk, H, ldb, ld_in, 0, status,
+                                           stream, npeers, bias_ptrs, peer_rows, peer_head_stride);
 }

@@ -150,7 +150,15 @@ def trimul_fused(z: torch.Tensor, mask: Optional[torch.Tensor], w: TrimulPacked,
 native.declare("ubm_attention_d32", [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_ll, c_ll, c_int, c_void_p, c_void_p])
 native.declare("ubm_attention_d64", [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_ll, c_ll, c_int, c_void_p, c_void_p])
 
+native.declare("ubm_attention_set_variant", [c_int])
+
 LOG2E = 1.4426950408889634
+
+
+def set_attention_variant(v: int) -> None:
+    """0 = choose by shape (four rows per CTA with 64-key steps when there are at least three rows),
+    1 = always two rows per CTA with 128-key steps."""
+    native.lib().ubm_attention_set_variant(int(v))
 
 
 @dataclass
