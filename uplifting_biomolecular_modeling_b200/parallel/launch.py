@@ -93,6 +93,7 @@ def run_rank_processes(world: int, argv: Sequence[str], cpu: bool = False, run_t
     """Run ``argv`` as ``world`` rank processes.  Returns the exit codes (all zero) or raises RankFailed."""
     port = free_port()
     log_dir = log_dir or tempfile.mkdtemp(prefix="rowpair_logs_")
+    os.makedirs(log_dir, exist_ok=True)
     procs: List[subprocess.Popen] = []
     logs: List[str] = []
     try:

@@ -1,0 +1,100 @@
+"""Rank worker of a row-sharded prediction (``pred --mode big --n_gpu P``).
+
+Every rank builds the same model (same seed), rank 0 builds the features and broadcasts them, all ranks
+check that replicated inputs agree, then the trunk runs with the pair tensor row-sharded: embedding
+and MSA module replicated, the Pairformer stack through :class:`parallel.rowpair_fused.FusedRowPair`
+on GPUs (plain sharded statements on CPU / gloo).  Rank 0 gathers the pair tensor for the heads and
+writes the outputs; each rank prints its SCHEDULE and MEMSTATS lines.
+Reference: common/opt_core/opt_core/mem/rowpair/trunk.py:1131, evidence.py:163,187.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import torch
+
+from ..core import det, report
+from ..models import cofold
+from . import launch, rowpair
+from .ckpt import TrunkCheckpointer, feature_digest
+from .layout import Layout
+
+TAG = "rowpair"
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="tiny")
+    ap.add_argument("--tokens", type=int, default=64)
+    ap.add_argument("--msa_depth", type=int, default=1)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--recycles", type=int, default=None)
+    ap.add_argument("--out_dir", default=None)
+    ap.add_argument("--gather", default="peer")
+    a = ap.parse_args(argv)
+    comm = launch.init_from_env()
+    cuda = comm.backend == "nccl"
+    dev = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")
+    dtype = torch.bfloat16 if cuda else torch.float32
+    model = cofold.build_model(a.config, device=dev, dtype=dtype, seed=a.seed)
+    comm.check_replicated(next(model.parameters()).float(), "model weights")
+    feats = cofold.synthetic_features(a.tokens, a.msa_depth, model.cfg, device=dev, dtype=dtype, seed=a.seed,
+                                      chains=cofold.chains_for(a.config, a.tokens))
+    comm.check_replicated(feats["token_feat"].float(), "features")
+    N = a.tokens
+    lay = Layout(N, comm.world, align=128 if cuda else 1)
+    r0, r1 = lay.rows(comm.rank)
+    report.emit(report.line(TAG, "SCHEDULE", ("rank", comm.rank), ("rows", f"{r0}:{r1}"), ("world", comm.world),
+                            ("backend", comm.backend), ("gather", a.gather if cuda else "none")))
+    t0 = time.time()
+    with torch.no_grad():
+        s_inputs, s_init, z_init, atom_c, atom_p = model.embed(feats)
+        recycles = model.cfg.recycles if a.recycles is None else a.recycles
+        fused = None
+        if cuda:
+            from .rowpair_fused import FusedRowPair
+            from .symm import SymmHeap
+            fused = FusedRowPair(lay, comm, SymmHeap(device=dev), gather=a.gather)
+        ck = TrunkCheckpointer.from_env(comm.rank, comm.world, det.numerics_signature(det.Policy()))
+        fd = feature_digest({k: v for k, v in feats.items() if isinstance(v, torch.Tensor)}) if ck else ""
+        s = torch.zeros_like(s_init)
+        z_loc = torch.zeros_like(z_init[0, r0:r1])
+        for cyc in range(recycles + 1):
+            s = s_init + model.s_recycle(model.s_norm(s))
+            z_loc = z_init[0, r0:r1] + model.z_recycle(model.z_norm(z_loc))
+            for bi, layer in enumerate(model.pairformer_module.layers):
+                if fused is not None:
+                    z_loc = fused.pair_block_(layer, z_loc.contiguous())
+                    s32 = s.float() + rowpair.apb_rows(s, z_loc, layer.attention, layer.pre_norm_s, lay, comm, comm.rank)
+                    s = (s32 + layer.transition_s(s32.to(s.dtype)).float()).to(s.dtype)
+                else:
+                    s, z_loc = rowpair.pairformer_layer_rows(layer, s, z_loc, lay, comm, comm.rank)
+            if ck is not None:
+                ck.save(cyc, z_loc, (r0, r1), fd, {"s": s}, comm.barrier)
+        z = rowpair.gather_pair(z_loc.contiguous(), comm)
+        dist = model.distogram_module(z.unsqueeze(0))
+    if cuda:
+        torch.cuda.synchronize()
+        from ..ops import native
+        native.raise_on_status(dev, "sharded trunk")
+        peak = torch.cuda.max_memory_allocated(dev)
+    else:
+        peak = 0
+    report.emit(report.line(TAG, "MEMSTATS", ("rank", comm.rank), ("peak_bytes", peak),
+                            ("seconds", round(time.time() - t0, 3))))
+    if comm.rank == 0 and a.out_dir:
+        os.makedirs(a.out_dir, exist_ok=True)
+        torch.save({"s": s.float().cpu(), "distogram_logits_mean": float(dist.float().mean())},
+                   os.path.join(a.out_dir, "trunk.pt"))
+        with open(os.path.join(a.out_dir, "sharding.json"), "w") as f:
+            json.dump({"n_gpu": comm.world, "sharding": "rowpair", "bounds": lay.bounds()}, f)
+    comm.barrier()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
