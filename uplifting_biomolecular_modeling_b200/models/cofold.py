@@ -67,12 +67,17 @@ class RelativePositionEncoding(nn.Module):
         self.linear_layer = nn.Linear(bins, c_z, bias=False)
         self.bins = bins
 
-    def forward(self, residue_index, chain_id, entity_id=None):
+    def rows(self, residue_index, chain_id, r0: int, r1: int):
+        return self.forward(residue_index, chain_id, rows=(r0, r1))
+
+    def forward(self, residue_index, chain_id, entity_id=None, rows=None):
         r_max, s_max = 32, 2
-        same_chain = chain_id[:, :, None] == chain_id[:, None, :]
-        d = residue_index[:, :, None] - residue_index[:, None, :]
+        a0, a1 = (0, residue_index.shape[1]) if rows is None else rows
+        chain_q, res_q = chain_id[:, a0:a1], residue_index[:, a0:a1]
+        same_chain = chain_q[:, :, None] == chain_id[:, None, :]
+        d = res_q[:, :, None] - residue_index[:, None, :]
         d_res = torch.where(same_chain, torch.clamp(d + r_max, 0, 2 * r_max), torch.full_like(d, 2 * r_max + 1))
-        d_chain = torch.clamp(chain_id[:, :, None] - chain_id[:, None, :] + s_max, 0, 2 * s_max)
+        d_chain = torch.clamp(chain_q[:, :, None] - chain_id[:, None, :] + s_max, 0, 2 * s_max)
         d_chain = torch.where(same_chain, torch.full_like(d_chain, 2 * s_max + 1), d_chain)
         n_res, n_chain = 2 * r_max + 2, 2 * s_max + 2
         w = self.linear_layer.weight                                           # [c_z, bins]
@@ -206,6 +211,15 @@ class CofoldModel(nn.Module):
         z_init = z_init + self.rel_pos(feats["residue_index"], feats["chain_id"]).to(z_init.dtype)
         z_init = z_init + self.token_bonds(feats["token_bonds"].to(z_init.dtype))
         return s_inputs, s_init, z_init, atom_c, atom_p
+
+    def z_init_rows(self, feats, s_inputs, r0: int, r1: int):
+        """Rows [r0, r1) of the initial pair tensor without building the whole [N, N, c_z] tensor."""
+        z = self.z_init_1(s_inputs)[:, r0:r1, None] + self.z_init_2(s_inputs)[:, None, :]
+        ri, ci = feats["residue_index"], feats["chain_id"]
+        rel = self.rel_pos.rows(ri, ci, r0, r1) if hasattr(self.rel_pos, "rows") else \
+            self.rel_pos(ri, ci)[:, r0:r1]
+        z = z + rel.to(z.dtype)
+        return z + self.token_bonds(feats["token_bonds"][:, r0:r1].to(z.dtype))
 
     def trunk(self, feats, s_inputs, s_init, z_init, recycles: Optional[int] = None):
         cfg = self.cfg

@@ -152,6 +152,36 @@ def opm_rows(m, mask, mod, layout: Layout, rank: int):
     return F.linear(zz, mod.proj_o.weight, mod.proj_o.bias)
 
 
+def pwa_rows(m, z_loc, mod, layout: Layout, comm: Comm, rank: int):
+    """Pair-weighted averaging with local query rows: the softmax over j of the bias of rows [r0, r1) is whole
+    on this rank; the averaged rows are all-gathered to update the replicated MSA representation."""
+    a0, a1 = layout.rows(rank)
+    mn = R.layer_norm(m, mod.norm_m.weight, mod.norm_m.bias)
+    zn = R.layer_norm(z_loc, mod.norm_z.weight, mod.norm_z.bias)
+    B, S, N, _ = mn.shape
+    H, c = mod.heads, mod.c_h
+    v = F.linear(mn, mod.proj_m.weight).view(B, S, N, H, c)[0]                       # [S, N, H, c]
+    w = torch.softmax(F.linear(zn, mod.proj_z.weight).permute(2, 0, 1).float(), dim=-1)   # [H, R, N]
+    o = torch.einsum("hij,sjhd->sihd", w, v.float()).to(m.dtype)                       # [S, R, H, c]
+    g = torch.sigmoid(F.linear(mn[0, :, a0:a1], mod.proj_g.weight))                   # [S, R, H*c]
+    upd_loc = F.linear(g * o.reshape(S, a1 - a0, H * c), mod.proj_o.weight)            # [S, R, c_m]
+    upd = comm.all_gather_rows(upd_loc.transpose(0, 1).contiguous()).transpose(0, 1)   # [S, N, c_m]
+    return upd.unsqueeze(0)
+
+
+def msa_layer_rows(layer, z_loc, m, msa_mask, layout: Layout, comm: Comm, rank: int, pair_block=None):
+    """One MSA block on a row shard: m replicated, z rows local.  ``pair_block(layer, z_loc)`` may replace the
+    plain sharded pair update (the fused GPU path)."""
+    m = m + pwa_rows(m, z_loc, layer.pair_weighted_averaging, layout, comm, rank)
+    m = m + layer.msa_transition(m)
+    z_loc = z_loc + opm_rows(m, msa_mask, layer.outer_product_mean, layout, rank).to(z_loc.dtype)
+    if pair_block is not None:
+        z_loc = pair_block(layer.pairformer_layer, z_loc.contiguous())
+    else:
+        _, z_loc = pairformer_layer_rows(layer.pairformer_layer, None, z_loc, layout, comm, rank)
+    return z_loc, m
+
+
 def gather_pair(z_loc, comm: Comm) -> torch.Tensor:
     return comm.all_gather_rows(z_loc)
 

@@ -35,12 +35,15 @@ def main(argv=None) -> int:
     ap.add_argument("--recycles", type=int, default=None)
     ap.add_argument("--out_dir", default=None)
     ap.add_argument("--gather", default="peer")
+    ap.add_argument("--blocks", type=int, default=None, help="override the number of Pairformer blocks")
+    ap.add_argument("--json", action="store_true", help="rank 0 prints one BIGMODE json line (device-timed)")
     a = ap.parse_args(argv)
     comm = launch.init_from_env()
     cuda = comm.backend == "nccl"
     dev = torch.device("cuda", torch.cuda.current_device()) if cuda else torch.device("cpu")
     dtype = torch.bfloat16 if cuda else torch.float32
-    model = cofold.build_model(a.config, device=dev, dtype=dtype, seed=a.seed)
+    over = {} if a.blocks is None else {"pairformer_blocks": a.blocks}
+    model = cofold.build_model(a.config, device=dev, dtype=dtype, seed=a.seed, **over)
     comm.check_replicated(next(model.parameters()).float(), "model weights")
     feats = cofold.synthetic_features(a.tokens, a.msa_depth, model.cfg, device=dev, dtype=dtype, seed=a.seed,
                                       chains=cofold.chains_for(a.config, a.tokens))
@@ -51,8 +54,15 @@ def main(argv=None) -> int:
     report.emit(report.line(TAG, "SCHEDULE", ("rank", comm.rank), ("rows", f"{r0}:{r1}"), ("world", comm.world),
                             ("backend", comm.backend), ("gather", a.gather if cuda else "none")))
     t0 = time.time()
+    if cuda:
+        torch.cuda.reset_peak_memory_stats(dev)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        comm.barrier()
+        ev0.record()
     with torch.no_grad():
-        s_inputs, s_init, z_init, atom_c, atom_p = model.embed(feats)
+        s_inputs, atom_c, atom_p = model.input_embedder(feats)
+        s_init = model.s_init(s_inputs)
+        z_init_loc = model.z_init_rows(feats, s_inputs, r0, r1)[0]          # only this rank's rows ever exist
         recycles = model.cfg.recycles if a.recycles is None else a.recycles
         fused = None
         if cuda:
@@ -62,10 +72,16 @@ def main(argv=None) -> int:
         ck = TrunkCheckpointer.from_env(comm.rank, comm.world, det.numerics_signature(det.Policy()))
         fd = feature_digest({k: v for k, v in feats.items() if isinstance(v, torch.Tensor)}) if ck else ""
         s = torch.zeros_like(s_init)
-        z_loc = torch.zeros_like(z_init[0, r0:r1])
+        z_loc = torch.zeros_like(z_init_loc)
+        msa = model.msa_module
         for cyc in range(recycles + 1):
             s = s_init + model.s_recycle(model.s_norm(s))
-            z_loc = z_init[0, r0:r1] + model.z_recycle(model.z_norm(z_loc))
+            z_loc = z_init_loc + model.z_recycle(model.z_norm(z_loc))
+            m = msa.msa_proj(feats["msa_feat"].to(dtype)) + msa.s_proj(s_inputs.to(dtype)).unsqueeze(1)
+            for ml in msa.layers:
+                z_loc, m = rowpair.msa_layer_rows(ml, z_loc, m, feats["msa_mask"], lay, comm, comm.rank,
+                                                  None if fused is None else fused.pair_block_)
+            del m
             for bi, layer in enumerate(model.pairformer_module.layers):
                 if fused is not None:
                     z_loc = fused.pair_block_(layer, z_loc.contiguous())
@@ -75,10 +91,18 @@ def main(argv=None) -> int:
                     s, z_loc = rowpair.pairformer_layer_rows(layer, s, z_loc, lay, comm, comm.rank)
             if ck is not None:
                 ck.save(cyc, z_loc, (r0, r1), fd, {"s": s}, comm.barrier)
-        z = rowpair.gather_pair(z_loc.contiguous(), comm)
-        dist = model.distogram_module(z.unsqueeze(0))
+        # distogram on the local rows (z + z^T needs the transposed rows: one all-to-all)
+        zt = rowpair.transpose_shard(z_loc.contiguous(), lay, comm)
+        dist = model.distogram_module.distogram(z_loc + zt)
+        dist_mean = comm.all_reduce_scalar(float(dist.float().sum()), "sum") / float(N * N * dist.shape[-1])
+    ms = None
     if cuda:
+        ev1.record()
         torch.cuda.synchronize()
+        tms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+        import torch.distributed as tdist
+        tdist.all_reduce(tms, op=tdist.ReduceOp.MAX)
+        ms = float(tms.item())
         from ..ops import native
         native.raise_on_status(dev, "sharded trunk")
         peak = torch.cuda.max_memory_allocated(dev)
@@ -86,9 +110,16 @@ def main(argv=None) -> int:
         peak = 0
     report.emit(report.line(TAG, "MEMSTATS", ("rank", comm.rank), ("peak_bytes", peak),
                             ("seconds", round(time.time() - t0, 3))))
+    peaks = comm.all_gather(torch.tensor([float(peak)], device=dev))
+    if a.json and comm.rank == 0:
+        print("BIGMODE " + json.dumps({"n_gpus": comm.world, "tokens": N, "blocks": len(model.pairformer_module.layers),
+                                       "msa_blocks": len(model.msa_module.layers), "trunk_passes": recycles + 1,
+                                       "gather": a.gather if cuda else "none", "latency_ms_max_over_ranks": ms,
+                                       "peak_gb_per_gpu_max": round(max(float(p.item()) for p in peaks) / 2 ** 30, 3),
+                                       "mean_distogram_logit": dist_mean}), flush=True)
     if comm.rank == 0 and a.out_dir:
         os.makedirs(a.out_dir, exist_ok=True)
-        torch.save({"s": s.float().cpu(), "distogram_logits_mean": float(dist.float().mean())},
+        torch.save({"s": s.float().cpu(), "distogram_logits_mean": dist_mean},
                    os.path.join(a.out_dir, "trunk.pt"))
         with open(os.path.join(a.out_dir, "sharding.json"), "w") as f:
             json.dump({"n_gpu": comm.world, "sharding": "rowpair", "bounds": lay.bounds()}, f)
