@@ -146,10 +146,15 @@ def opm_rows(m, mask, mod, layout: Layout, rank: int):
     mk = mask.unsqueeze(-1).to(n.dtype)
     a = (F.linear(n, mod.proj_a.weight) * mk)[0, :, a0:a1]
     b = (F.linear(n, mod.proj_b.weight) * mk)[0]
-    num = torch.einsum("sic,sjd->ijcd", a.float(), b.float())
     cnt = torch.einsum("si,sj->ij", mask[0, :, a0:a1].float(), mask[0].float()).clamp(min=1.0)
-    zz = (num / cnt[..., None, None]).reshape(a1 - a0, b.shape[1], -1).to(m.dtype)
-    return F.linear(zz, mod.proj_o.weight, mod.proj_o.bias)
+    out = []
+    step = max(1, min(a1 - a0, (1 << 28) // max(1, b.shape[1] * a.shape[-1] * b.shape[-1])))   # <= 1 GiB fp32 per block
+    for i0 in range(0, a1 - a0, step):
+        i1 = min(a1 - a0, i0 + step)
+        num = torch.einsum("sic,sjd->ijcd", a[:, i0:i1].float(), b.float())
+        zz = (num / cnt[i0:i1, :, None, None]).reshape(i1 - i0, b.shape[1], -1).to(m.dtype)
+        out.append(F.linear(zz, mod.proj_o.weight, mod.proj_o.bias))
+    return torch.cat(out, 0) if out else a.new_zeros((0, b.shape[1], mod.proj_o.weight.shape[0]))
 
 
 def pwa_rows(m, z_loc, mod, layout: Layout, comm: Comm, rank: int):
