@@ -151,3 +151,22 @@ def test_row_kernels():
     assert torch.allclose(rows.swiglu_rows(ab).float(), ref, atol=3e-2, rtol=3e-2)
     ref = a.float() + torch.sigmoid(sc.float()) * sh.float()
     assert torch.allclose(rows.gate_residual(sh, sc, a).float(), ref, atol=5e-2, rtol=3e-2)
+
+
+def test_window_attention_matches_reference():
+    from uplifting_biomolecular_modeling_b200.models import diffusion, pairformer
+    from uplifting_biomolecular_modeling_b200.ops import pair
+    torch.manual_seed(9)
+    B, A, c, H = 3, 320, 128, 4
+    attn = pairformer.AttentionPairBias(c, 128, H, compute_pair_bias=False).cuda().eval()
+    x = torch.randn(B, A, c, device="cuda")
+    bias = torch.randn(1, H, A // 32, 32, 128, device="cuda")
+    with torch.no_grad():
+        ref = diffusion._window_attention(attn, x, bias, (32, 128))
+        ab = attn.to(torch.bfloat16)
+        w = pair.ApbPacked.pack(ab.proj_q.weight, ab.proj_q.bias, ab.proj_k.weight, ab.proj_v.weight, ab.proj_g.weight,
+                                ab.proj_o.weight, H)
+        out = pair.window_attention_fused(x.bfloat16(), w, diffusion.WindowBias(bias).data)
+    torch.cuda.synchronize()
+    err = ((out.float() - ref).abs().mean() / ref.abs().mean()).item()
+    assert err < 4e-2, err

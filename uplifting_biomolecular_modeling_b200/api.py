@@ -35,6 +35,8 @@ def _tree_copy(dst, src) -> None:
         dst.copy_(src)
     elif hasattr(dst, "view") and isinstance(getattr(dst, "view"), torch.Tensor) and not isinstance(dst, dict):
         dst.view.copy_(src.view)              # models.pairformer.BiasPlanes
+    elif hasattr(dst, "data") and isinstance(getattr(dst, "data"), torch.Tensor) and not isinstance(dst, dict):
+        dst.data.copy_(src.data)              # models.diffusion.WindowBias
     elif isinstance(dst, dict):
         for k in dst:
             _tree_copy(dst[k], src[k])

@@ -66,6 +66,19 @@ class ConditionedTransitionBlock(nn.Module):
         return torch.sigmoid(gate) * self.b_to_a(b)
 
 
+class WindowBias:
+    """Atom-pair bias of one atom-transformer layer laid out for the window-attention kernel: bf16
+    [1, H, windows, 32, 128] that already carries the factor log2(e)."""
+
+    LOG2E = 1.4426950408889634
+
+    def __init__(self, dense: torch.Tensor):
+        self.data = (dense.float() * self.LOG2E).to(torch.bfloat16).contiguous()
+
+    def dense(self) -> torch.Tensor:
+        return self.data.float() / self.LOG2E
+
+
 class DiffusionTransformerLayer(_Switchable):
     def __init__(self, dim: int = 768, dim_s: int = 768, heads: int = 16):
         super().__init__()
@@ -89,7 +102,14 @@ class DiffusionTransformerLayer(_Switchable):
         B, N, C = a.shape
         attn = self.pair_bias_attn
         b = rows.adaln_rows(a.contiguous(), h["adaln"][0].contiguous(), h["adaln"][1].contiguous())
-        o = attn._fused_forward(b, bias)
+        if isinstance(bias, WindowBias):
+            if attn._packed is None:
+                attn._packed = pair.ApbPacked.pack(attn.proj_q.weight, attn.proj_q.bias, attn.proj_k.weight,
+                                                   attn.proj_v.weight, attn.proj_g.weight, attn.proj_o.weight,
+                                                   attn.heads)
+            o = pair.window_attention_fused(b, attn._packed, bias.data)
+        else:
+            o = attn._fused_forward(b, bias)
         a = rows.gate_residual(o.contiguous(), h["gate"].contiguous(), a)
         tr = self.transition
         if self._packed is None:
@@ -108,9 +128,12 @@ class DiffusionTransformerLayer(_Switchable):
         fused = self.impl == "fused"
         h = hoisted if hoisted is not None else self.hoist(s)
         from .pairformer import BiasPlanes
-        if fused and window is None and mask is None and isinstance(bias, BiasPlanes) and a.is_cuda \
-                and a.dtype == torch.bfloat16:
+        if fused and mask is None and a.is_cuda and a.dtype == torch.bfloat16 and \
+                ((window is None and isinstance(bias, BiasPlanes)) or
+                 (window == (32, 128) and isinstance(bias, WindowBias) and self.pair_bias_attn.head_dim == 32)):
             return self._fused_token_layer(a, h, bias)
+        if isinstance(bias, WindowBias):
+            bias = bias.dense()
         if isinstance(bias, BiasPlanes):
             bias = bias.dense()
         b = self.adaln(a, None, h["adaln"], fused)
@@ -128,6 +151,8 @@ def _window_attention(attn: AttentionPairBias, x, bias, window):
     wq, wk = window
     B, A, _ = x.shape
     H, D = attn.heads, attn.head_dim
+    if isinstance(bias, WindowBias):
+        bias = bias.dense().to(x.dtype)
     q = attn.proj_q(x).view(B, A, H, D).transpose(1, 2)
     k = attn.proj_k(x).view(B, A, H, D).transpose(1, 2)
     v = attn.proj_v(x).view(B, A, H, D).transpose(1, 2)
@@ -296,6 +321,9 @@ class DiffusionModule(nn.Module):
             tb = [m(z_cond).permute(0, 3, 1, 2) for m in self.token_pair_bias]
         eb = [m(atom_pair).permute(0, 4, 1, 2, 3) for m in self.atom_enc_pair_bias]
         db = [m(atom_pair).permute(0, 4, 1, 2, 3) for m in self.atom_dec_pair_bias]
+        if fused and atom_pair.is_cuda and self.window == (32, 128):
+            eb = [WindowBias(x) for x in eb]
+            db = [WindowBias(x) for x in db]
         enc_h = [l.hoist(atom_c) for l in self.atom_attention_encoder.atom_transformer.layers]
         dec_h = [l.hoist(atom_c) for l in self.atom_attention_decoder.atom_transformer.layers]
         return {"token_bias": tb, "enc_bias": eb, "dec_bias": db, "enc_hoist": enc_h, "dec_hoist": dec_h,

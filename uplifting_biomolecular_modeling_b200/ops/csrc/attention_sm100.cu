@@ -97,6 +97,19 @@ __device__ __forceinline__ void decode_qtile(const AttnParams& p, int qt, int& q
   q_limit = p.peer_row0[q] + p.peer_rows[q];
 }
 
+// Optional timeline (build with -DUBM_ATTN_TIMELINE): CTA 0 stamps clock64 at fixed points of its first
+// tiles into a global buffer [3 roles][kTlTiles][8 events]; used to see which role waits for which.
+#ifdef UBM_ATTN_TIMELINE
+constexpr int kTlTiles = 48;
+__device__ long long g_attn_timeline[3 * kTlTiles * 8];
+#define ATT_STAMP(role, tile, ev)                                                        \
+  do {                                                                                   \
+    if (blockIdx.x == 0 && (tile) < kTlTiles) g_attn_timeline[((role) * kTlTiles + (tile)) * 8 + (ev)] = clock64(); \
+  } while (0)
+#else
+#define ATT_STAMP(role, tile, ev) do { } while (0)
+#endif
+
 template <int D, int TK, int R2, bool PEER>
 __global__ void __launch_bounds__(128 + R2 * 128, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -237,16 +250,19 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           const uint32_t g = gk + j;
           if (j + 1 < T) {
             mbar_wait(&kv_full[(g + 1) % kAStages], ((g + 1) / kAStages) & 1u, ws, 56, 1);
+            ATT_STAMP(0, g, 0);
             tc_fence_after_sync();
             for (int r = 0; r < R2; ++r) {
               mbar_wait(&s_empty[r], ((g + 1) & 1u) ^ 1u, ws, 57, r);
               tc_fence_after_sync();
               issue_qk(r, g + 1);
+              ATT_STAMP(0, g, 1 + r);
             }
           }
           const uint32_t st = smem_u32(sSt + (g % kAStages) * kAStageBytes);
           for (int r = 0; r < R2; ++r) {
             mbar_wait(&p_full[r], g & 1u, ws, 58, r);
+            ATT_STAMP(0, g, 3 + 2 * r);
             tc_fence_after_sync();
             const uint32_t pa = smem_u32(sP + r * kAPBytes);
             const uint32_t va = st + (r * 2 + 1) * kAKVBytes;
@@ -258,6 +274,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               umma_ss(tO + r * kAD, ad, bd, idesc_pv, (j | k) != 0 ? 1u : 0u);
             }
             umma_commit(&pv_done[r]);
+            ATT_STAMP(0, g, 4 + 2 * r);
           }
           umma_commit(&kv_empty[g % kAStages]);
         }
@@ -290,6 +307,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int j = 0; j < T; ++j) {
         const uint32_t g = gk + j;
         mbar_wait(&s_full[r_in], g & 1u, ws, 59, r_in);
+        if (quad == 0 && lane == 0) ATT_STAMP(1 + r_in, g, 0);
         tc_fence_after_sync();
         float t[TK];
         {
@@ -299,11 +317,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           for (int c = 0; c < TK / 32; ++c) tmem_ld32(ta + c * 32, *reinterpret_cast<uint32_t(*)[32]>(tu + c * 32));
           tmem_ld_wait();
         }
+        if (quad == 0 && lane == 0) ATT_STAMP(1 + r_in, g, 1);
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_empty[r_in]);
 
         mbar_wait(&kv_full[g % kAStages], (g / kAStages) & 1u, ws, 60, r_in);
+        if (quad == 0 && lane == 0) ATT_STAMP(1 + r_in, g, 2);
         if (p.has_bias) {
           const uint8_t* bs = sSt + (g % kAStages) * kAStageBytes + 2 * R2 * kAKVBytes;
 #pragma unroll
@@ -340,6 +360,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
         const float m_new = fmaxf(m, mt);
         const float alpha = fast_exp2(m - m_new);
+        if (quad == 0 && lane == 0) ATT_STAMP(1 + r_in, g, 3);
         float psv[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t pk[TK / 2];
 #pragma unroll
@@ -358,9 +379,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const float psum = (psv[0] + psv[1]) + (psv[2] + psv[3]);
         l = l * alpha + psum;
         m = m_new;
+        if (quad == 0 && lane == 0) ATT_STAMP(1 + r_in, g, 4);
 
         // previous P.V of this row must be complete: P buffer free, O stable
         mbar_wait(&pv_done[r_in], (g & 1u) ^ 1u, ws, 61, r_in);
+        if (quad == 0 && lane == 0) ATT_STAMP(1 + r_in, g, 5);
         tc_fence_after_sync();
         if (j > 0 && __any_sync(0xffffffffu, alpha < 1.0f)) {
           const uint32_t oa = tmem_addr(tO, quad, r_in * kAD);
@@ -385,6 +408,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[r_in]);
+        if (quad == 0 && lane == 0) ATT_STAMP(1 + r_in, g, 6);
       }
       // ---- epilogue of this (row, head, query tile)
       mbar_wait(&pv_done[r_in], (gk + T - 1) & 1u, ws, 62, r_in);
@@ -547,6 +571,12 @@ static int launch_attention(const void* q, const void* k, const void* v, const v
 }  // namespace ubm
 
 static int g_attn_variant = 0;
+#ifdef UBM_ATTN_TIMELINE
+extern "C" int ubm_attention_read_timeline(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, ubm::g_attn_timeline, sizeof(long long) * 3 * ubm::kTlTiles * 8);
+}
+#endif
+
 extern "C" int ubm_attention_set_variant(int v) {
   g_attn_variant = v & 0xff;  // 0 / 1 = 128-key steps, two rows per CTA; 2 = four rows per CTA; 3 = 64-key steps
   return 0;

@@ -294,3 +294,25 @@ def triangle_attention_fused(z: torch.Tensor, w: TriattPacked, starting: bool, r
     out = torch.empty_like(z) if out is None else out
     _gemm.gemm(og, w.wo, bias=w.bo, residual=z2 if residual else None, out=out.view(N * N, 128))
     return out
+
+
+# ------------------------------------------------------------------------------------------
+native.declare("ubm_window_attention", [c_void_p] * 6 + [c_int, c_int, c_int, c_ll, c_int, c_void_p])
+
+
+def window_attention_fused(x: torch.Tensor, w: ApbPacked, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """Gated atom attention in 32 x 128 windows.  x: bf16 [B, A, c] (A a multiple of 32); w: packed projections with
+    4 x 32 heads; bias: bf16 [1 or B, H, A/32, 32, 128] already multiplied by log2(e).  Returns [B, A, c]."""
+    B, A, c = x.shape
+    if w.Dp != 32:
+        raise ValueError("window attention supports head dimension 32")
+    HD = w.H * 32
+    x2 = x.reshape(B * A, c)
+    qkv = _gemm.gemm(x2, w.wqkv, bias=w.bqkv)
+    g = _gemm.gemm(x2, w.wg, act="sigmoid")
+    o = torch.empty((B * A, HD), dtype=torch.bfloat16, device=x.device)
+    rc = native.lib().ubm_window_attention(native.ptr(qkv), native.ptr(qkv) + HD * 2, native.ptr(qkv) + 2 * HD * 2,
+                                           native.ptr(bias), native.ptr(g), native.ptr(o), B, A, w.H, 3 * HD,
+                                           1 if bias is None else bias.shape[0], native.current_stream(x.device))
+    native.check(rc, "ubm_window_attention")
+    return _gemm.gemm(o, w.wo).view(B, A, -1)

@@ -167,10 +167,34 @@ class FusedRowPair:
         w_tas, w_tae = packed(tas, lambda: tri(tas)), packed(tae, lambda: tri(tae))
         w_tr = packed(tr, lambda: pair.TransitionPacked.pack(tr.norm.weight, tr.norm.bias, tr.fc1.weight,
                                                              tr.fc2.weight, tr.fc3.weight))
+        import os
+        timing = os.environ.get("ROWPAIR_PAIRSTACK_TIMES") == "1"
+        marks = []
+
+        def mark(name):
+            if timing:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                marks.append((name, e))
+
+        mark("start")
         z_loc = self.trimul_(z_loc, w_tmo, True)
+        mark("trimul_out")
         z_loc = self.trimul_(z_loc, w_tmi, False)
+        mark("trimul_in")
         z_loc = self.triatt_(z_loc, w_tas, True)
+        mark("triatt_start")
         z_loc = self.triatt_(z_loc, w_tae, False)
+        mark("triatt_end")
         if self.rows > 0:
             z_loc = pair.transition_fused(z_loc.contiguous(), w_tr, residual=True)
+        mark("transition")
+        if timing:
+            torch.cuda.synchronize()
+            self.block_count = getattr(self, "block_count", 0) + 1
+            if self.rank == 0 and self.block_count % 8 == 0:
+                from ..core import report
+                report.emit(report.line("rowpair", "BLOCKTIMES", ("block", self.block_count),
+                                        *[(marks[i][0], round(marks[i - 1][1].elapsed_time(marks[i][1]), 2))
+                                          for i in range(1, len(marks))]))
         return z_loc
