@@ -335,7 +335,9 @@ class DiffusionModule(nn.Module):
         """r_noisy: [B, A, 3] (already scaled by c_in); times: [B] = c_noise.  Returns r_update [B, A, 3]."""
         B = r_noisy.shape[0]
         r_noisy = r_noisy.to(prep["atom_q"].dtype)
-        s = self.single_conditioner(times, prep["s_static"])                       # [B, N, 2c_s]
+        # every sample of a step sees the same noise level, so the conditioning (and everything hoisted from
+        # it) is computed for one row and broadcast over the samples
+        s = self.single_conditioner(times[:1], prep["s_static"])                   # [1, N, 2c_s]
         a, q = self.atom_attention_encoder(prep["atom_q"], prep["atom_c"], prep["enc_bias"], r_noisy,
                                            atom_to_token, n_tokens, prep["enc_hoist"], self.window)
         a = a + self.s_to_a_linear(s)
