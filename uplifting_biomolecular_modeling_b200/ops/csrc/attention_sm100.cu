@@ -33,7 +33,10 @@ constexpr float kNegBig = -1.0e30f;
 // two stages and the P tiles still fit in shared memory).
 // R2 = rows per CTA (softmax warpgroups sharing each bias tile): 2, or 4 with TK = 64 - four warps per
 // scheduler hide the TMEM-load -> bias -> max -> exp latency chain that two cannot.
-template <int D, int TK, int R2>
+// TP = the probability tile stays in tensor memory (the P.V product takes its A operand from TMEM) and the pair
+// bias is added by the tensor cores (S = I . bias^T + Q K^T with an identity A operand in TMEM): the softmax
+// threads then neither read the bias from shared memory nor write P to it.
+template <int D, int TK, int R2, bool TP = false>
 struct AttnCfg {
   static constexpr int kQBytes = kATile * D * 2;
   static constexpr int kKVBytes = TK * D * 2;
@@ -42,9 +45,14 @@ struct AttnCfg {
   static constexpr int kPBytes = kATile * TK * 2;
   // As many stages as fit: the loop is bound by the latency of the tile loads unless they are issued
   // several tiles ahead (with two stages every tile waited a full TMA round trip).
-  static constexpr int kStages = (224 * 1024 - R2 * kQBytes - R2 * kPBytes) / kStageBytes;
+  static constexpr int kPSmem = TP ? 0 : R2 * kPBytes;
+  static constexpr int kStages = (224 * 1024 - R2 * kQBytes - kPSmem) / kStageBytes;
   static_assert(kStages >= 2 && kStages <= 8, "stage count");
-  static constexpr int kSmemBytes = R2 * kQBytes + kStages * kStageBytes + R2 * kPBytes + 512 + 1024;
+  static constexpr int kSmemBytes = R2 * kQBytes + kStages * kStageBytes + kPSmem + 512 + 1024;
+  // tensor memory map (512 columns): S[r] at r*TK, O[r] at 256 + r*D, then (TP) P[r] and the identity
+  static constexpr int kTmemP = 256 + R2 * D;             // P[r] at kTmemP + r * TK / 2 (two bf16 per column)
+  static constexpr int kTmemI = kTmemP + R2 * TK / 2;     // identity: 64 columns (128 x 128 bf16)
+  static_assert(!TP || (R2 * TK <= 256 && kTmemI + 64 <= 512), "tensor memory budget");
   static constexpr int kThreads = 128 + R2 * 128;
   // setmaxnreg moves registers inside the pool the CTA was launched with (threads x compiled registers):
   //   R2 = 2: 384 x 168 = 64512 = 128 x 56 + 256 x 224;   R2 = 4: 640 x 96 = 61440 >= 128 x 56 + 512 x 104.
@@ -110,12 +118,12 @@ __device__ long long g_attn_timeline[3 * kTlTiles * 8];
 #define ATT_STAMP(role, tile, ev) do { } while (0)
 #endif
 
-template <int D, int TK, int R2, bool PEER>
+template <int D, int TK, int R2, bool PEER, bool TP>
 __global__ void __launch_bounds__(128 + R2 * 128, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ BiasPeerMaps peers, AttnParams p) {
-  using Cfg = AttnCfg<D, TK, R2>;
+  using Cfg = AttnCfg<D, TK, R2, TP>;
   constexpr int kAD = D;
   constexpr int kAQBytes = Cfg::kQBytes;
   constexpr int kAKVBytes = Cfg::kKVBytes;
@@ -127,7 +135,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sQ = smem;                              // R2 x Q tile
   uint8_t* sSt = sQ + R2 * kAQBytes;               // stages
   uint8_t* sP = sSt + kAStages * kAStageBytes;     // R2 x P tile
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + R2 * kAPBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + (TP ? 0 : R2 * kAPBytes));   // no P tiles in smem when TP
   uint64_t* q_full = bars;             // [1]
   uint64_t* q_empty = q_full + 1;      // [1] commit
   uint64_t* kv_full = q_empty + 1;     // [stages]
@@ -149,7 +157,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(q_empty, 1);
     for (int s = 0; s < kAStages; ++s) {
       mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1 + 4 * R2);
+      mbar_init(&kv_empty[s], TP ? 1 : 1 + 4 * R2);
     }
     for (int r = 0; r < R2; ++r) {
       mbar_init(&s_full[r], 1);
@@ -173,7 +181,29 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base;         // S[r] at r * TK
   const uint32_t tO = tmem_base + 256;   // O[r] at r * D
+  const uint32_t tP = tmem_base + Cfg::kTmemP;
+  const uint32_t tI = tmem_base + Cfg::kTmemI;
   const int T = p.n_kt;
+  if (TP) {
+    // identity A operand: lane q holds 128 bf16, element q is 1.0 (two bf16 per 32-bit column)
+    if (warp >= 4 && warp < 8) {
+      const int qrow0 = (warp & 3) * 32 + lane;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t iv[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int col = half * 32 + c;
+          iv[c] = (col == (qrow0 >> 1)) ? ((qrow0 & 1) ? 0x3F800000u : 0x00003F80u) : 0u;
+        }
+        tmem_st32(tmem_addr(tI, warp & 3, half * 32), iv);
+      }
+      tmem_st_wait();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+  }
 
   // Register split: warps 0-3 (producer, MMA issuer, two idle warps) give registers up, the softmax
   // warpgroups take them (budget checked in AttnCfg and again on the host before launch).
@@ -224,16 +254,27 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, TK, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, kAD, 0, 1);  // B = V is MN-major
+      constexpr uint32_t idesc_bias = umma_idesc_bf16(128, TK, 0, 1);  // B = bias tile, keys contiguous (MN-major)
       uint32_t item_cnt = 0, gk = 0;
       auto issue_qk = [&](int r, uint32_t g) {
         const uint32_t st = smem_u32(sSt + (g % kAStages) * kAStageBytes);
         const uint32_t qa = smem_u32(sQ + r * kAQBytes);
         const uint32_t ka = st + r * 2 * kAKVBytes;
+        const bool with_bias = TP && p.has_bias;
+        if (with_bias) {
+          // S = I . bias^T: the 128 x TK bias tile sits in shared memory as TK/64 boxes of [128 q][64 k]
+          const uint32_t ba = st + 2 * R2 * kAKVBytes;
+#pragma unroll
+          for (int k = 0; k < kATile / 16; ++k) {
+            const uint64_t bd = umma_smem_desc(ba + k * 2048, 16384, 1024, kSwizzle128);
+            umma_ts(tS + r * TK, tI + k * 8, bd, idesc_bias, k != 0 ? 1u : 0u);
+          }
+        }
 #pragma unroll
         for (int k = 0; k < kAD / 16; ++k) {
           const uint64_t ad = umma_smem_desc(qa + k * 32, 16, Cfg::kSbo, Cfg::kSwz);
           const uint64_t bd = umma_smem_desc(ka + k * 32, 16, Cfg::kSbo, Cfg::kSwz);
-          umma_ss(tS + r * TK, ad, bd, idesc_qk, k != 0 ? 1u : 0u);
+          umma_ss(tS + r * TK, ad, bd, idesc_qk, (with_bias || k != 0) ? 1u : 0u);
         }
         umma_commit(&s_full[r]);
       };
@@ -269,9 +310,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
             for (int k = 0; k < TK / 16; ++k) {
               // P: K-major, k-blocks of 64 keys; V: MN-major, a step of 16 keys
-              const uint64_t ad = umma_smem_desc(pa + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024, kSwizzle128);
               const uint64_t bd = umma_smem_desc(va + k * Cfg::kVStep, 16, Cfg::kSbo, Cfg::kSwz);
-              umma_ss(tO + r * kAD, ad, bd, idesc_pv, (j | k) != 0 ? 1u : 0u);
+              if (TP) {
+                umma_ts(tO + r * kAD, tP + r * (TK / 2) + k * 8, bd, idesc_pv, (j | k) != 0 ? 1u : 0u);
+              } else {
+                const uint64_t ad = umma_smem_desc(pa + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024, kSwizzle128);
+                umma_ss(tO + r * kAD, ad, bd, idesc_pv, (j | k) != 0 ? 1u : 0u);
+              }
             }
             umma_commit(&pv_done[r]);
             ATT_STAMP(0, g, 4 + 2 * r);
@@ -322,9 +367,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&s_empty[r_in]);
 
-        mbar_wait(&kv_full[g % kAStages], (g / kAStages) & 1u, ws, 60, r_in);
+        if (!TP) mbar_wait(&kv_full[g % kAStages], (g / kAStages) & 1u, ws, 60, r_in);
         if (quad == 0 && lane == 0) ATT_STAMP(1 + r_in, g, 2);
-        if (p.has_bias) {
+        if (!TP && p.has_bias) {
           const uint8_t* bs = sSt + (g % kAStages) * kAStageBytes + 2 * R2 * kAKVBytes;
 #pragma unroll
           for (int c16 = 0; c16 < TK / 8; ++c16) {
@@ -337,8 +382,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
           }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&kv_empty[g % kAStages]);
+        if (!TP) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&kv_empty[g % kAStages]);
+        }
         if (j == T - 1) {
           const int valid = p.Nk - j * TK;
           if (valid < TK) {
@@ -351,11 +398,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // operations would leave the two warps per scheduler waiting on instruction latency
         float mx[4] = {t[0], t[1], t[2], t[3]};
 #pragma unroll
-        for (int k = 4; k < TK; k += 4) {
-          mx[0] = fmaxf(mx[0], t[k]);
-          mx[1] = fmaxf(mx[1], t[k + 1]);
-          mx[2] = fmaxf(mx[2], t[k + 2]);
-          mx[3] = fmaxf(mx[3], t[k + 3]);
+        for (int k = 4; k + 8 <= TK + 4; k += 8) {     // four chains, two new values per step (3-input max)
+          mx[0] = max3f(mx[0], t[k], t[k + 4 < TK ? k + 4 : k]);
+          mx[1] = max3f(mx[1], t[k + 1], t[k + 5 < TK ? k + 5 : k + 1]);
+          mx[2] = max3f(mx[2], t[k + 2], t[k + 6 < TK ? k + 6 : k + 2]);
+          mx[3] = max3f(mx[3], t[k + 3], t[k + 7 < TK ? k + 7 : k + 3]);
         }
         const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
         const float m_new = fmaxf(m, mt);
@@ -398,13 +445,21 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
           tmem_st_wait();
         }
-        uint8_t* ps = sP + r_in * kAPBytes;
+        if (TP) {
+          // P stays in tensor memory: this thread's lane, TK/2 columns of packed bf16 pairs
+          const uint32_t pa_t = tmem_addr(tP, quad, r_in * (TK / 2));
 #pragma unroll
-        for (int c16 = 0; c16 < TK / 8; ++c16) {
-          const uint4 u = make_uint4(pk[c16 * 4], pk[c16 * 4 + 1], pk[c16 * 4 + 2], pk[c16 * 4 + 3]);
-          *reinterpret_cast<uint4*>(ps + (c16 >> 3) * 16384 + swz128_offset(qrow, c16 & 7)) = u;
+          for (int c = 0; c < TK / 64; ++c) tmem_st32(pa_t + c * 32, *reinterpret_cast<uint32_t(*)[32]>(pk + c * 32));
+          tmem_st_wait();
+        } else {
+          uint8_t* ps = sP + r_in * kAPBytes;
+#pragma unroll
+          for (int c16 = 0; c16 < TK / 8; ++c16) {
+            const uint4 u = make_uint4(pk[c16 * 4], pk[c16 * 4 + 1], pk[c16 * 4 + 2], pk[c16 * 4 + 3]);
+            *reinterpret_cast<uint4*>(ps + (c16 >> 3) * 16384 + swz128_offset(qrow, c16 & 7)) = u;
+          }
+          fence_proxy_async_smem();
         }
-        fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[r_in]);
@@ -466,12 +521,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-template <int D, int TK, int R2>
+template <int D, int TK, int R2, bool TP = false>
 static int launch_attention(const void* q, const void* k, const void* v, const void* bias, const void* gate, void* out,
                             int rows, int Nq, int Nk, int H, long long ldb, long long ld_in, int transpose_out,
                             void* status, void* stream, int npeers = 0, const void* const* bias_ptrs = nullptr,
                             const int* peer_rows = nullptr, long long peer_head_stride = 0) {
-  using Cfg = AttnCfg<D, TK, R2>;
+  using Cfg = AttnCfg<D, TK, R2, TP>;
   const uint64_t hd = (uint64_t)H * D;
   const uint64_t ldi = ld_in > 0 ? (uint64_t)ld_in : hd;  // row stride of q / k / v in elements
   if (ldi < hd || (ldi & 7)) return UBM_ERR_ARGUMENT;
@@ -546,20 +601,20 @@ static int launch_attention(const void* q, const void* k, const void* v, const v
   {
     // the in-kernel register re-split must fit the pool this build was compiled with, or it would never return
     cudaFuncAttributes fa;
-    cudaError_t e = npeers > 0 ? cudaFuncGetAttributes(&fa, attention_kernel<D, TK, R2, true>)
-                               : cudaFuncGetAttributes(&fa, attention_kernel<D, TK, R2, false>);
+    cudaError_t e = npeers > 0 ? cudaFuncGetAttributes(&fa, attention_kernel<D, TK, R2, true, TP>)
+                               : cudaFuncGetAttributes(&fa, attention_kernel<D, TK, R2, false, TP>);
     if (e != cudaSuccess || 128 * 56 + R2 * 128 * Cfg::kSoftmaxRegs > Cfg::kThreads * fa.numRegs) {
       fprintf(stderr, "[ubm] attention: register budget check failed (numRegs=%d)\n", e == cudaSuccess ? fa.numRegs : -1);
       return UBM_ERR_LAUNCH;
     }
   }
   if (npeers > 0) {
-    auto kern = attention_kernel<D, TK, R2, true>;
+    auto kern = attention_kernel<D, TK, R2, true, TP>;
     int rc = set_smem(kern, Cfg::kSmemBytes);
     if (rc) return rc;
     kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmB, maps, p);
   } else {
-    auto kern = attention_kernel<D, TK, R2, false>;
+    auto kern = attention_kernel<D, TK, R2, false, TP>;
     int rc = set_smem(kern, Cfg::kSmemBytes);
     if (rc) return rc;
     kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmB, maps, p);
@@ -578,7 +633,8 @@ extern "C" int ubm_attention_read_timeline(long long* host_out) {
 #endif
 
 extern "C" int ubm_attention_set_variant(int v) {
-  g_attn_variant = v & 0xff;  // 0 / 1 = 128-key steps, two rows per CTA; 2 = four rows per CTA; 3 = 64-key steps
+  g_attn_variant = v & 0xff;  // 0 = P and bias through tensor memory; 1 = P and bias through shared memory;
+                              // 2 = four rows per CTA; 3 = 64-key steps
   return 0;
 }
 
@@ -597,8 +653,11 @@ extern "C" int ubm_attention_d32(const void* q, const void* k, const void* v, co
   if (g_attn_variant == 3)
     return ubm::launch_attention<32, 64, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
                                             status, stream);
-  return ubm::launch_attention<32, 128, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
-                                           status, stream);
+  if (g_attn_variant == 1)
+    return ubm::launch_attention<32, 128, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
+                                             status, stream);
+  return ubm::launch_attention<32, 128, 2, true>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in,
+                                                 transpose_out, status, stream);
 }
 
 extern "C" int ubm_attention_d64(const void* q, const void* k, const void* v, const void* bias, const void* gate,

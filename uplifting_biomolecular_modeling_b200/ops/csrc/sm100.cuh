@@ -417,6 +417,13 @@ __device__ __forceinline__ float fast_rcp(float x) {
 __device__ __forceinline__ float sigmoidf_fast(float x) { return fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * x)); }
 __device__ __forceinline__ float siluf_fast(float x) { return x * sigmoidf_fast(x); }
 
+// three-input maximum (one instruction on sm_100)
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
