@@ -154,10 +154,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
+    mbar_init(q_empty, 2);   // the two S issuers
     for (int s = 0; s < kAStages; ++s) {
       mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], TP ? 1 : 1 + 4 * R2);
+      mbar_init(&kv_empty[s], TP ? 3 : 3 + 4 * R2);   // two S issuers, the P.V issuer (+ the softmax warps)
     }
     for (int r = 0; r < R2; ++r) {
       mbar_init(&s_full[r], 1);
@@ -249,81 +249,104 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (*abort_flag) break;
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+  } else if (warp >= 1 && warp <= 3) {
+    // ------------------------------------------------------------------ MMA issuers
+    // Issuing one tcgen05.mma costs its thread on the order of a hundred cycles and a key tile needs
+    // 18 per row, so the work is spread over three single-thread issuers:
+    //   warps 1, 2 : S = I.bias^T + Q K^T for the rows r with r % 2 == warp - 1
+    //   warp 3     : O += P V for all rows
+    // The whole warp runs the loop with warp-uniform operands; one elected lane issues the tcgen05 instructions.
+    const bool leader = elect_one();
+    if (warp <= 2) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, TK, 0, 0);
-      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, kAD, 0, 1);  // B = V is MN-major
       constexpr uint32_t idesc_bias = umma_idesc_bf16(128, TK, 0, 1);  // B = bias tile, keys contiguous (MN-major)
+      const int r_first = warp - 1;
       uint32_t item_cnt = 0, gk = 0;
       auto issue_qk = [&](int r, uint32_t g) {
         const uint32_t st = smem_u32(sSt + (g % kAStages) * kAStageBytes);
         const uint32_t qa = smem_u32(sQ + r * kAQBytes);
         const uint32_t ka = st + r * 2 * kAKVBytes;
         const bool with_bias = TP && p.has_bias;
-        if (with_bias) {
-          // S = I . bias^T: the 128 x TK bias tile sits in shared memory as TK/64 boxes of [128 q][64 k]
-          const uint32_t ba = st + 2 * R2 * kAKVBytes;
+        const uint64_t bd0 = umma_smem_desc(st + 2 * R2 * kAKVBytes, 16384, 1024, kSwizzle128);
+        const uint64_t ad0 = umma_smem_desc(qa, 16, Cfg::kSbo, Cfg::kSwz);
+        const uint64_t kd0 = umma_smem_desc(ka, 16, Cfg::kSbo, Cfg::kSwz);
+        if (leader) {
+          if (with_bias) {
+            // S = I . bias^T: the 128 x TK bias tile sits in shared memory as TK/64 boxes of [128 q][64 k]
 #pragma unroll
-          for (int k = 0; k < kATile / 16; ++k) {
-            const uint64_t bd = umma_smem_desc(ba + k * 2048, 16384, 1024, kSwizzle128);
-            umma_ts(tS + r * TK, tI + k * 8, bd, idesc_bias, k != 0 ? 1u : 0u);
+            for (int k = 0; k < kATile / 16; ++k)
+              umma_ts(tS + r * TK, tI + k * 8, bd0 + static_cast<uint64_t>(k * (2048 >> 4)), idesc_bias,
+                      k != 0 ? 1u : 0u);
           }
-        }
 #pragma unroll
-        for (int k = 0; k < kAD / 16; ++k) {
-          const uint64_t ad = umma_smem_desc(qa + k * 32, 16, Cfg::kSbo, Cfg::kSwz);
-          const uint64_t bd = umma_smem_desc(ka + k * 32, 16, Cfg::kSbo, Cfg::kSwz);
-          umma_ss(tS + r * TK, ad, bd, idesc_qk, (with_bias || k != 0) ? 1u : 0u);
+          for (int k = 0; k < kAD / 16; ++k)
+            umma_ss(tS + r * TK, ad0 + static_cast<uint64_t>(k * 2), kd0 + static_cast<uint64_t>(k * 2), idesc_qk,
+                    (with_bias || k != 0) ? 1u : 0u);
+          umma_commit(&s_full[r]);
         }
-        umma_commit(&s_full[r]);
+        __syncwarp();
       };
       for (int item = blockIdx.x; item < p.num_items; item += gridDim.x, ++item_cnt) {
         mbar_wait(q_full, item_cnt & 1u, ws, 53);
         mbar_wait(&kv_full[gk % kAStages], (gk / kAStages) & 1u, ws, 54, 0);
         tc_fence_after_sync();
-        for (int r = 0; r < R2; ++r) {
+        for (int r = r_first; r < R2; r += 2) {
           mbar_wait(&s_empty[r], (gk & 1u) ^ 1u, ws, 55, r);
           tc_fence_after_sync();
           issue_qk(r, gk);
         }
         for (int j = 0; j < T; ++j) {
           const uint32_t g = gk + j;
+          if (leader) umma_commit(&kv_empty[g % kAStages]);   // K and bias of tile g: free when the MMAs so far end
           if (j + 1 < T) {
             mbar_wait(&kv_full[(g + 1) % kAStages], ((g + 1) / kAStages) & 1u, ws, 56, 1);
             ATT_STAMP(0, g, 0);
             tc_fence_after_sync();
-            for (int r = 0; r < R2; ++r) {
+            for (int r = r_first; r < R2; r += 2) {
               mbar_wait(&s_empty[r], ((g + 1) & 1u) ^ 1u, ws, 57, r);
               tc_fence_after_sync();
               issue_qk(r, g + 1);
               ATT_STAMP(0, g, 1 + r);
             }
           }
+        }
+        if (leader) umma_commit(q_empty);
+        gk += T;
+      }
+    } else {
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, kAD, 0, 1);  // B = V is MN-major
+      uint32_t gk = 0;
+      for (int item = blockIdx.x; item < p.num_items; item += gridDim.x) {
+        for (int j = 0; j < T; ++j) {
+          const uint32_t g = gk + j;
+          mbar_wait(&kv_full[g % kAStages], (g / kAStages) & 1u, ws, 54, 2);
           const uint32_t st = smem_u32(sSt + (g % kAStages) * kAStageBytes);
           for (int r = 0; r < R2; ++r) {
             mbar_wait(&p_full[r], g & 1u, ws, 58, r);
             ATT_STAMP(0, g, 3 + 2 * r);
             tc_fence_after_sync();
             const uint32_t pa = smem_u32(sP + r * kAPBytes);
-            const uint32_t va = st + (r * 2 + 1) * kAKVBytes;
+            const uint64_t vd0 = umma_smem_desc(st + (r * 2 + 1) * kAKVBytes, 16, Cfg::kSbo, Cfg::kSwz);
+            const uint64_t pd0 = umma_smem_desc(pa, 16, 1024, kSwizzle128);
+            if (leader) {
 #pragma unroll
-            for (int k = 0; k < TK / 16; ++k) {
-              // P: K-major, k-blocks of 64 keys; V: MN-major, a step of 16 keys
-              const uint64_t bd = umma_smem_desc(va + k * Cfg::kVStep, 16, Cfg::kSbo, Cfg::kSwz);
-              if (TP) {
-                umma_ts(tO + r * kAD, tP + r * (TK / 2) + k * 8, bd, idesc_pv, (j | k) != 0 ? 1u : 0u);
-              } else {
-                const uint64_t ad = umma_smem_desc(pa + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024, kSwizzle128);
-                umma_ss(tO + r * kAD, ad, bd, idesc_pv, (j | k) != 0 ? 1u : 0u);
+              for (int k = 0; k < TK / 16; ++k) {
+                // P: K-major (TMEM, or shared-memory k-blocks of 64 keys); V: MN-major, a step of 16 keys
+                const uint64_t bd = vd0 + static_cast<uint64_t>(k * (Cfg::kVStep >> 4));
+                if (TP) {
+                  umma_ts(tO + r * kAD, tP + r * (TK / 2) + k * 8, bd, idesc_pv, (j | k) != 0 ? 1u : 0u);
+                } else {
+                  umma_ss(tO + r * kAD, pd0 + static_cast<uint64_t>((k >> 2) * (16384 >> 4) + (k & 3) * 2), bd,
+                          idesc_pv, (j | k) != 0 ? 1u : 0u);
+                }
               }
+              umma_commit(&pv_done[r]);
             }
-            umma_commit(&pv_done[r]);
+            __syncwarp();
             ATT_STAMP(0, g, 4 + 2 * r);
           }
-          umma_commit(&kv_empty[g % kAStages]);
+          if (leader) umma_commit(&kv_empty[g % kAStages]);   // V of tile g
         }
-        umma_commit(q_empty);
         gk += T;
       }
     }
