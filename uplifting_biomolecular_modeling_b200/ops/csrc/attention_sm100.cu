@@ -688,8 +688,11 @@ extern "C" int ubm_attention_d64(const void* q, const void* k, const void* v, co
                                  int transpose_out, void* status, void* stream) {
   if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0) return ubm::UBM_ERR_ARGUMENT;
   if (bias != nullptr && (ldb < Nk || (ldb & 7))) return ubm::UBM_ERR_ARGUMENT;
-  return ubm::launch_attention<64, 64, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
-                                          status, stream);
+  if (g_attn_variant == 1)
+    return ubm::launch_attention<64, 64, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
+                                            status, stream);
+  return ubm::launch_attention<64, 64, 2, true>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
+                                                status, stream);
 }
 
 // Pair-bias all-gather fused into the attention kernel (head dimension 32): the bias planes are row
