@@ -506,28 +506,18 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
             for (int d = 0; d < 32; ++d) f[d] = __uint_as_float(ov[d]) * inv;
             if (p.gate != nullptr) {
-              const uint4* gp = reinterpret_cast<const uint4*>(p.gate + in_row * (p.H * kAD) + h * kAD + dc * 32);
+              const __nv_bfloat16* gp = p.gate + in_row * (p.H * kAD) + h * kAD + dc * 32;
 #pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                const uint4 u = __ldg(gp + c);
-                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+              for (int c = 0; c < 2; ++c) {
+                float e[16];
+                ld_bf16x16(gp + c * 16, e);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  f[c * 8 + 2 * e] *= bf16_lo(w[e]);
-                  f[c * 8 + 2 * e + 1] *= bf16_hi(w[e]);
-                }
+                for (int d = 0; d < 16; ++d) f[c * 16 + d] *= e[d];
               }
             }
-            uint4* op = reinterpret_cast<uint4*>(p.out + out_row * (p.H * kAD) + h * kAD + dc * 32);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              uint4 u;
-              u.x = pack_bf16x2(f[c * 8], f[c * 8 + 1]);
-              u.y = pack_bf16x2(f[c * 8 + 2], f[c * 8 + 3]);
-              u.z = pack_bf16x2(f[c * 8 + 4], f[c * 8 + 5]);
-              u.w = pack_bf16x2(f[c * 8 + 6], f[c * 8 + 7]);
-              op[c] = u;
-            }
+            __nv_bfloat16* op = p.out + out_row * (p.H * kAD) + h * kAD + dc * 32;
+            st_bf16x16(op, f);
+            st_bf16x16(op + 16, f + 16);
           }
         }
       }

@@ -289,7 +289,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // the whole warp runs the loop (warp-uniform operands), one elected lane issues the tcgen05 instructions
+    const bool leader = elect_one();
+    {
       constexpr uint32_t idesc = umma_idesc_bf16(kBM, BN, MN_MAJOR ? 1 : 0, MN_MAJOR ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
@@ -304,25 +306,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
           const uint32_t sb = sa + Cfg::kABytes;
+          const uint64_t ad0 = MN_MAJOR ? umma_smem_desc(sa, 8192, 1024, kSwizzle128)
+                                        : umma_smem_desc(sa, 16, 1024, kSwizzle128);
+          const uint64_t bd0 = MN_MAJOR ? umma_smem_desc(sb, 8192, 1024, kSwizzle128)
+                                        : umma_smem_desc(sb, 16, 1024, kSwizzle128);
+          constexpr uint64_t kStep = MN_MAJOR ? (2048 >> 4) : (32 >> 4);
+          if (leader) {
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) {
-            uint64_t ad, bd;
-            if (!MN_MAJOR) {
-              ad = umma_smem_desc(sa + k * 32, 16, 1024, kSwizzle128);
-              bd = umma_smem_desc(sb + k * 32, 16, 1024, kSwizzle128);
-            } else {
-              ad = umma_smem_desc(sa + k * 2048, 8192, 1024, kSwizzle128);
-              bd = umma_smem_desc(sb + k * 2048, 8192, 1024, kSwizzle128);
-            }
-            umma_ss(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < kBK / 16; ++k)
+              umma_ss(d_tmem, ad0 + k * kStep, bd0 + k * kStep, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
           }
-          umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
+          __syncwarp();
           if (++stage == Cfg::kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        umma_commit(&tfull_bar[acc]);  // accumulator complete
+        if (leader) umma_commit(&tfull_bar[acc]);  // accumulator complete
+        __syncwarp();
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1u;
@@ -376,7 +378,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           if (p.residual != nullptr) {
             const __nv_bfloat16* rr = p.residual + b * p.strideR + static_cast<long long>(m) * p.ldr + n0;
-            if (n0 + 32 <= n_limit && (p.ldr & 7) == 0 && (p.strideR & 7) == 0 &&
+            if (n0 + 32 <= n_limit && (reinterpret_cast<uintptr_t>(rr) & 31) == 0) {
+#pragma unroll
+              for (int c = 0; c < 2; ++c) {
+                float e[16];
+                ld_bf16x16(rr + c * 16, e);
+#pragma unroll
+                for (int d = 0; d < 16; ++d) f[c * 16 + d] += e[d];
+              }
+            } else if (n0 + 32 <= n_limit && (p.ldr & 7) == 0 && (p.strideR & 7) == 0 &&
                 (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0) {
 #pragma unroll
               for (int j8 = 0; j8 < 4; ++j8) {
@@ -396,7 +406,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           if (p.out_fp32) {
             float* cp = reinterpret_cast<float*>(p.C) + b * p.strideC + static_cast<long long>(m) * p.ldc + n0;
-            if (vec_ok && n0 + 32 <= n_limit) {
+            if (n0 + 32 <= n_limit && (reinterpret_cast<uintptr_t>(cp) & 31) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8)
+                st_global_256(cp + j,
+                              make_uint4(__float_as_uint(f[j]), __float_as_uint(f[j + 1]), __float_as_uint(f[j + 2]),
+                                         __float_as_uint(f[j + 3])),
+                              make_uint4(__float_as_uint(f[j + 4]), __float_as_uint(f[j + 5]),
+                                         __float_as_uint(f[j + 6]), __float_as_uint(f[j + 7])));
+            } else if (vec_ok && n0 + 32 <= n_limit) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4)
                 *reinterpret_cast<float4*>(cp + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
@@ -408,7 +426,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           } else {
             __nv_bfloat16* cp =
                 reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.strideC + static_cast<long long>(m) * p.ldc + n0;
-            if (vec_ok && n0 + 32 <= n_limit) {
+            if (n0 + 32 <= n_limit && (reinterpret_cast<uintptr_t>(cp) & 31) == 0) {
+              st_bf16x16(cp, f);
+              st_bf16x16(cp + 16, f + 16);
+            } else if (vec_ok && n0 + 32 <= n_limit) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
                 uint4 u;

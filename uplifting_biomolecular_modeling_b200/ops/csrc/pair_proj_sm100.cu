@@ -1,14 +1,10 @@
 // Fused LayerNorm -> 512-wide projection of pair rows, with the op-specific epilogue.
 //
-// One kernel, two epilogues:
-//   MODE_TRIMUL   : a = sigmoid(g_a(n)) * p_a(n) * mask, b likewise, n = LN(z_row); written as
-//                   channel-major bf16 planes P[2][c][i][k] (the operands of the triangle
-//                   contraction).  Reference: K1 of common/opt_core/opt_core/kernels/trimul/
-//                   native/DESIGN.md:21-47 and _k1c/_k1t of kernels/fpf_trimul_v4/kernels.py.
-//   MODE_TRIATT   : q | k | v | sigmoid(g) rows (bf16, [row][128]) plus the per-head pair bias
-//                   planes bias[h][j][k]; optionally at the transposed pair index (ending node).
-//                   Reference: the triangle-attention prologue
-//                   (common/opt_core/opt_core/attn/pair_fused.py:1136, N15 triatt_procuda_sm90.cu).
+// Epilogue (MODE_TRIATT): q | k | v | sigmoid(g) rows (bf16, [row][128]) plus the per-head pair bias
+// planes bias[h][j][k]; optionally at the transposed pair index (ending node).  Reference: the
+// triangle-attention prologue (common/opt_core/opt_core/attn/pair_fused.py:1136, N15
+// triatt_procuda_sm90.cu).  (The triangle-multiplication projection, whose planes want the transposed
+// accumulator orientation, is a kernel of its own in trimul_proj_sm100.cu.)
 //
 // LayerNorm is folded into the GEMM: with W' = W * gamma (per input channel),
 //   W.LN(x) = rstd * (W'.x - mu * rowsum(W')) + W.beta,
@@ -42,10 +38,6 @@ struct PairProjParams {
   int Np;            // leading dimension of planes (>= N, multiple of 8)
   const float* colsum;   // [512]  rowsum(W') per output column
   const float* colbias;  // [512]  W.beta (+ bias) per output column
-  const float* mask;     // [R] or null (MODE_TRIMUL: multiplies a and b)
-  // MODE_TRIMUL
-  __nv_bfloat16* planes;  // [2][128][rows][Np]
-  // MODE_TRIATT
   __nv_bfloat16* q;  // each [R][128], row index possibly transposed
   __nv_bfloat16* k;
   __nv_bfloat16* v;
@@ -140,8 +132,9 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (warp-uniform loop, elected lane issues)
+    const bool leader = elect_one();
+    {
       constexpr uint32_t idesc = umma_idesc_bf16(128, 256);
       mbar_wait(w_full, 0, ws, 12);
       int stage = 0;
@@ -155,18 +148,22 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         for (int h = 0; h < 2; ++h) {
           mbar_wait(&acc_empty[h], acc_phase ^ 1u, ws, 14, h);
           tc_fence_after_sync();
+          const uint64_t ad0 = umma_smem_desc(xa, 16, 1024, kSwizzle128);
+          const uint64_t bd0 = umma_smem_desc(wa + h * 32768, 16, 1024, kSwizzle128);
+          if (leader) {
 #pragma unroll
-          for (int kb = 0; kb < 2; ++kb) {
+            for (int kb = 0; kb < 2; ++kb) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const uint64_t ad = umma_smem_desc(xa + kb * 16384 + k * 32, 16, 1024, kSwizzle128);
-              const uint64_t bd = umma_smem_desc(wa + kb * 65536 + h * 32768 + k * 32, 16, 1024, kSwizzle128);
-              umma_ss(tmem_base + h * 256, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+              for (int k = 0; k < 4; ++k)
+                umma_ss(tmem_base + h * 256, ad0 + static_cast<uint64_t>(kb * (16384 >> 4) + k * 2),
+                        bd0 + static_cast<uint64_t>(kb * (65536 >> 4) + k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
             }
+            umma_commit(&acc_full[h]);
           }
-          umma_commit(&acc_full[h]);
+          __syncwarp();
         }
-        umma_commit(&x_empty[stage]);
+        if (leader) umma_commit(&x_empty[stage]);
+        __syncwarp();
         if (++stage == kPPStages) {
           stage = 0;
           phase ^= 1u;
@@ -237,7 +234,6 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         pi = static_cast<int>(r / p.N);
         pk = static_cast<int>(r - static_cast<long long>(pi) * p.N);
       }
-      const float mval = (MODE == MODE_TRIMUL && p.mask != nullptr && row_ok) ? p.mask[r] : 1.0f;
 
       if (MODE == MODE_TRIATT && row_ok) {
         const int oi = p.transpose_out ? pk : pi;
@@ -256,30 +252,7 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       mbar_wait(&acc_full[grp], acc_phase, ws, 16, grp);
       tc_fence_after_sync();
       const uint32_t tbase = tmem_addr(tmem_base, q, grp * 256);
-      if (MODE == MODE_TRIMUL) {
-        // half = [p (128) | g (128)] of operand `grp`; out[c] = p * sigmoid(g) * mask
-        __nv_bfloat16* plane = p.planes + static_cast<long long>(grp) * 128 * p.plane_rows * p.Np;
-        const long long off = static_cast<long long>(pi) * p.Np + pk;
-        const long long cstride = static_cast<long long>(p.plane_rows) * p.Np;
-#pragma unroll 1
-        for (int c0 = 0; c0 < 128; c0 += 32) {
-          uint32_t pv[32], gv[32];
-          tmem_ld32(tbase + c0, pv);
-          tmem_ld32(tbase + 128 + c0, gv);
-          tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int cp = grp * 256 + c0 + j;
-              const int cg = cp + 128;
-              const float pj = rstd * (__uint_as_float(pv[j]) - mu * sColsum[cp]) + sColbias[cp];
-              const float gj = rstd * (__uint_as_float(gv[j]) - mu * sColsum[cg]) + sColbias[cg];
-              const float val = pj * sigmoidf_fast(gj) * mval;
-              plane[(c0 + j) * cstride + off] = __float2bfloat16(val);
-            }
-          }
-        }
-      } else {
+      {
         // half 0 = [q | k], half 1 = [v | g]; rows written at (possibly transposed) pair index
         const long long orow = p.transpose_out ? (static_cast<long long>(pk) * p.N + pi) : r;
         __nv_bfloat16* o0 = (grp == 0 ? p.q : p.v) + orow * 128;
@@ -299,15 +272,8 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
               f[j] = gate ? sigmoidf_fast(val) : val;
             }
             __nv_bfloat16* dst = (c0 < 128 ? o0 + c0 : o1 + (c0 - 128));
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 u;
-              u.x = pack_bf16x2(f[j], f[j + 1]);
-              u.y = pack_bf16x2(f[j + 2], f[j + 3]);
-              u.z = pack_bf16x2(f[j + 4], f[j + 5]);
-              u.w = pack_bf16x2(f[j + 6], f[j + 7]);
-              *reinterpret_cast<uint4*>(dst + j) = u;
-            }
+            st_bf16x16(dst, f);
+            st_bf16x16(dst + 16, f + 16);
           }
         }
       }
@@ -356,34 +322,6 @@ static int launch_pair_proj(const void* x, const void* w, PairProjParams p, cuda
 }
 
 }  // namespace ubm
-
-// z: [N*N][128] bf16.  w: [512][128] bf16 = rows [p_a; g_a; p_b; g_b] each already multiplied by
-// the LayerNorm gamma.  colsum/colbias: fp32 [512].  mask: fp32 [N*N] or null.
-// planes: bf16 [2][128][N][Np] (Np multiple of 8, >= N).
-extern "C" int ubm_trimul_proj_rows(const void* z, const void* w, const void* colsum, const void* colbias,
-                                    const void* mask, void* planes, void* stats_out, int rows, int plane_rows, int N,
-                                    int Np, void* status, void* stream) {
-  using namespace ubm;
-  if (N <= 0 || rows <= 0 || plane_rows < rows || Np < N || (Np & 7)) return UBM_ERR_ARGUMENT;
-  PairProjParams p = {};
-  p.R = static_cast<long long>(rows) * N;
-  p.rows = rows;
-  p.plane_rows = plane_rows;
-  p.N = N;
-  p.Np = Np;
-  p.colsum = static_cast<const float*>(colsum);
-  p.colbias = static_cast<const float*>(colbias);
-  p.mask = static_cast<const float*>(mask);
-  p.planes = static_cast<__nv_bfloat16*>(planes);
-  p.stats_out = static_cast<float*>(stats_out);
-  p.status = static_cast<KernelStatus*>(status);
-  return launch_pair_proj<MODE_TRIMUL>(z, w, p, static_cast<cudaStream_t>(stream));
-}
-
-extern "C" int ubm_trimul_proj(const void* z, const void* w, const void* colsum, const void* colbias, const void* mask,
-                               void* planes, void* stats_out, int N, int Np, void* status, void* stream) {
-  return ubm_trimul_proj_rows(z, w, colsum, colbias, mask, planes, stats_out, N, N, N, Np, status, stream);
-}
 
 // w: [512][128] bf16 = rows [q; k; v; g] (gamma folded, q pre-scaled by 1/sqrt(d)).
 // wb: fp32 [H][128] head-bias weights (gamma folded); wb_colsum/wb_colbias fp32 [H].

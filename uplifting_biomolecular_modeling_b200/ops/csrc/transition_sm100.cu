@@ -53,15 +53,17 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   uint64_t* bars = reinterpret_cast<uint64_t*>(sColbias + 2 * kTRMaxHidden);
   uint64_t* x_full = bars;            // [2]
   uint64_t* x_empty = x_full + 2;     // [2] 8 arrivals
-  uint64_t* w_full = x_empty + 2;     // [2]
-  uint64_t* w_empty = w_full + 2;     // [2] commit
-  uint64_t* ab_full = w_empty + 2;    // [2] commit
+  uint64_t* w_full = x_empty + 2;     // [2] first-GEMM weights (a|b rows) landed
+  uint64_t* w_empty = w_full + 2;     // [2] commit after the first GEMM: its slot refills while SwiGLU runs
+  uint64_t* wo_full = w_empty + 2;    // [2] second-GEMM weights landed
+  uint64_t* wo_empty = wo_full + 2;   // [2] commit after the second GEMM
+  uint64_t* ab_full = wo_empty + 2;   // [2] commit
   uint64_t* ab_empty = ab_full + 2;   // [2] 4 arrivals
   uint64_t* h_full = ab_empty + 2;    // [2] 4 arrivals
   uint64_t* h_empty = h_full + 2;     // [2] commit
   uint64_t* y_full = h_empty + 2;     // [1] commit
   uint64_t* y_empty = y_full + 1;     // [1] 8 arrivals
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(y_empty + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(y_empty + 1);   // 22 barriers before it: 176 of the 256 bytes
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -76,6 +78,8 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       mbar_init(&x_empty[s], 8);
       mbar_init(&w_full[s], 1);
       mbar_init(&w_empty[s], 1);
+      mbar_init(&wo_full[s], 1);
+      mbar_init(&wo_empty[s], 1);
       mbar_init(&ab_full[s], 1);
       mbar_init(&ab_empty[s], 4);
       mbar_init(&h_full[s], 4);
@@ -115,6 +119,15 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         tma_load_2d(sX + xs * kTRXBytes, &tmX, &x_full[xs], 0, tile * 128);
         tma_load_2d(sX + xs * kTRXBytes + 16384, &tmX, &x_full[xs], 64, tile * 128);
       };
+      // The second-GEMM weights of chunk g are requested one chunk late (after the first-GEMM weights of
+      // chunk g + 1): their slot frees only when the second GEMM of chunk g - 2 has run, which follows a
+      // SwiGLU pass, and waiting for it here must not hold back the first-GEMM weights.
+      auto load_wo = [&](uint32_t gc, int hc) {
+        const int s = gc & 1;
+        mbar_wait(&wo_empty[s], ((gc >> 1) & 1u) ^ 1u, ws, 42, s);
+        mbar_expect_tx(&wo_full[s], kTRWoBytes);
+        tma_load_2d(sW + s * kTRWStage + kTRWabBytes, &tmWo, &wo_full[s], hc * 64, 0);
+      };
       if (blockIdx.x < p.num_tiles) load_x(blockIdx.x, xt++);
       for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
         for (int h = 0; h < nch; ++h, ++g) {
@@ -122,10 +135,11 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           mbar_wait(&w_empty[s], ((g >> 1) & 1u) ^ 1u, ws, 32, s);
           if (*abort_flag) break;
           uint8_t* dst = sW + s * kTRWStage;
-          mbar_expect_tx(&w_full[s], kTRWStage);
+          mbar_expect_tx(&w_full[s], kTRWabBytes);
           tma_load_2d(dst, &tmWab, &w_full[s], 0, h * 128);
           tma_load_2d(dst + 16384, &tmWab, &w_full[s], 64, h * 128);
-          tma_load_2d(dst + kTRWabBytes, &tmWo, &w_full[s], h * 64, 0);
+          if (g > 0) load_wo(g - 1, h == 0 ? nch - 1 : h - 1);
+          if (*abort_flag) break;
           if (h == 1 || nch == 1) {
             const int tn = t + gridDim.x;
             if (tn < p.num_tiles) load_x(tn, xt++);
@@ -133,10 +147,12 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         }
         if (*abort_flag) break;
       }
+      if (g > 0 && !*abort_flag) load_wo(g - 1, nch - 1);
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (warp-uniform loop, elected lane issues)
+    const bool leader = elect_one();
+    {
       constexpr uint32_t idesc = umma_idesc_bf16(128, 128);
       uint32_t g = 0;   // chunks whose GEMM1 has been issued
       uint32_t g2 = 0;  // chunks whose GEMM2 has been issued
@@ -144,19 +160,23 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       uint32_t tile_cnt = 0;
       auto gemm2 = [&](uint32_t c, bool first_of_tile) {
         const int b = c & 1;
+        mbar_wait(&wo_full[b], (c >> 1) & 1u, ws, 43, b);
         mbar_wait(&h_full[b], (c >> 1) & 1u, ws, 33, b);
         if (first_of_tile) mbar_wait(y_empty, (tile_cnt & 1u) ^ 1u, ws, 34);
         tc_fence_after_sync();
         const uint32_t ha = smem_u32(sH + b * kTRHBytes);
         const uint32_t wo = smem_u32(sW + b * kTRWStage + kTRWabBytes);
+        const uint64_t ad0 = umma_smem_desc(ha, 16, 1024, kSwizzle128);
+        const uint64_t bd0 = umma_smem_desc(wo, 16, 1024, kSwizzle128);
+        if (leader) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const uint64_t ad = umma_smem_desc(ha + k * 32, 16, 1024, kSwizzle128);
-          const uint64_t bd = umma_smem_desc(wo + k * 32, 16, 1024, kSwizzle128);
-          umma_ss(tY, ad, bd, idesc, (first_of_tile && k == 0) ? 0u : 1u);
+          for (int k = 0; k < 4; ++k)
+            umma_ss(tY, ad0 + static_cast<uint64_t>(k * 2), bd0 + static_cast<uint64_t>(k * 2), idesc,
+                    (first_of_tile && k == 0) ? 0u : 1u);
+          umma_commit(&h_empty[b]);
+          umma_commit(&wo_empty[b]);
         }
-        umma_commit(&h_empty[b]);
-        umma_commit(&w_empty[b]);
+        __syncwarp();
       };
       for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++xt, ++tile_cnt) {
         const int xs = xt & 1;
@@ -168,16 +188,20 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
           mbar_wait(&ab_empty[b], ((g >> 1) & 1u) ^ 1u, ws, 37, b);
           tc_fence_after_sync();
           const uint32_t wa = smem_u32(sW + b * kTRWStage);
+          const uint64_t ad0 = umma_smem_desc(xa, 16, 1024, kSwizzle128);
+          const uint64_t bd0 = umma_smem_desc(wa, 16, 1024, kSwizzle128);
+          if (leader) {
 #pragma unroll
-          for (int kb = 0; kb < 2; ++kb) {
+            for (int kb = 0; kb < 2; ++kb) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const uint64_t ad = umma_smem_desc(xa + kb * 16384 + k * 32, 16, 1024, kSwizzle128);
-              const uint64_t bd = umma_smem_desc(wa + kb * 16384 + k * 32, 16, 1024, kSwizzle128);
-              umma_ss(tAB + b * 128, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+              for (int k = 0; k < 4; ++k)
+                umma_ss(tAB + b * 128, ad0 + static_cast<uint64_t>(kb * (16384 >> 4) + k * 2),
+                        bd0 + static_cast<uint64_t>(kb * (16384 >> 4) + k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
             }
+            umma_commit(&w_empty[b]);
+            umma_commit(&ab_full[b]);
           }
-          umma_commit(&ab_full[b]);
+          __syncwarp();
           if (h >= 1) {
             gemm2(g2, h == 1);
             ++g2;
@@ -185,7 +209,8 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         }
         gemm2(g2, nch == 1);
         ++g2;
-        umma_commit(y_full);
+        if (leader) umma_commit(y_full);
+        __syncwarp();
       }
     }
   } else {
@@ -294,15 +319,8 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         }
         if (row_ok) {
           __nv_bfloat16* dst = p.out + r * 128 + grp * 64 + c0;
-#pragma unroll
-          for (int m = 0; m < 32; m += 8) {
-            uint4 u;
-            u.x = pack_bf16x2(f[m], f[m + 1]);
-            u.y = pack_bf16x2(f[m + 2], f[m + 3]);
-            u.z = pack_bf16x2(f[m + 4], f[m + 5]);
-            u.w = pack_bf16x2(f[m + 6], f[m + 7]);
-            *reinterpret_cast<uint4*>(dst + m) = u;
-          }
+          st_bf16x16(dst, f);
+          st_bf16x16(dst + 16, f + 16);
         }
       }
       tc_fence_before_sync();

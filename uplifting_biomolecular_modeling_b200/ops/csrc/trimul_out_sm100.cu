@@ -121,7 +121,8 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    const bool leader = elect_one();   // warp-uniform loop, the elected lane issues the tcgen05 instructions
+    {
       constexpr uint32_t idesc_o = umma_idesc_bf16(128, 128, /*a_mn=*/1, /*b_mn=*/0);
       constexpr uint32_t idesc_g = umma_idesc_bf16(128, 128, 0, 0);
       mbar_wait(w_full, 0, ws, 22);
@@ -138,26 +139,29 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         const uint32_t wo = smem_u32(sWo), wg = smem_u32(sWg);
         const uint32_t dO = tmem_base + acc * 256;
         const uint32_t dG = dO + 128;
+        const uint64_t xd0 = umma_smem_desc(sx, 8192, 1024, kSwizzle128);
+        const uint64_t wod0 = umma_smem_desc(wo, 16, 1024, kSwizzle128);
+        const uint64_t zd0 = umma_smem_desc(sz, 16, 1024, kSwizzle128);
+        const uint64_t wgd0 = umma_smem_desc(wg, 16, 1024, kSwizzle128);
+        if (leader) {
 #pragma unroll
-        for (int kb = 0; kb < 2; ++kb) {
+          for (int kb = 0; kb < 2; ++kb) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t ad = umma_smem_desc(sx + kb * 16384 + k * 2048, 8192, 1024, kSwizzle128);
-            const uint64_t bd = umma_smem_desc(wo + kb * 16384 + k * 32, 16, 1024, kSwizzle128);
-            umma_ss(dO, ad, bd, idesc_o, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < 4; ++k)
+              umma_ss(dO, xd0 + static_cast<uint64_t>(kb * (16384 >> 4) + k * (2048 >> 4)),
+                      wod0 + static_cast<uint64_t>(kb * (16384 >> 4) + k * 2), idesc_o, (kb | k) != 0 ? 1u : 0u);
           }
-        }
 #pragma unroll
-        for (int kb = 0; kb < 2; ++kb) {
+          for (int kb = 0; kb < 2; ++kb) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t ad = umma_smem_desc(sz + kb * 16384 + k * 32, 16, 1024, kSwizzle128);
-            const uint64_t bd = umma_smem_desc(wg + kb * 16384 + k * 32, 16, 1024, kSwizzle128);
-            umma_ss(dG, ad, bd, idesc_g, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < 4; ++k)
+              umma_ss(dG, zd0 + static_cast<uint64_t>(kb * (16384 >> 4) + k * 2),
+                      wgd0 + static_cast<uint64_t>(kb * (16384 >> 4) + k * 2), idesc_g, (kb | k) != 0 ? 1u : 0u);
           }
+          umma_commit(&acc_full[acc]);
+          umma_commit(&empty[stage]);
         }
-        umma_commit(&acc_full[acc]);
-        umma_commit(&empty[stage]);
+        __syncwarp();
         if (++stage == kTOStages) {
           stage = 0;
           phase ^= 1u;
@@ -259,15 +263,8 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             }
           }
           __nv_bfloat16* dst = p.out + r * 128 + grp * 64 + c0;
-#pragma unroll
-          for (int m = 0; m < 32; m += 8) {
-            uint4 u;
-            u.x = pack_bf16x2(f[m], f[m + 1]);
-            u.y = pack_bf16x2(f[m + 2], f[m + 3]);
-            u.z = pack_bf16x2(f[m + 4], f[m + 5]);
-            u.w = pack_bf16x2(f[m + 6], f[m + 7]);
-            *reinterpret_cast<uint4*>(dst + m) = u;
-          }
+          st_bf16x16(dst, f);
+          st_bf16x16(dst + 16, f + 16);
         }
       }
       tc_fence_before_sync();
