@@ -47,3 +47,38 @@ def test_gemm_epilogue_bias_residual_act():
     ref = torch.nn.functional.silu(0.5 * (a.float() @ b.float().T) + bias) + res.float()
     assert out.dtype == torch.bfloat16
     assert torch.allclose(out.float(), ref, atol=6e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(1000, 128, 128), (384, 96, 256), (257, 128, 64)])
+def test_gemm_residual_tiles_by_tma(M, N, K):
+    """N <= 128 takes the 128-wide tile whose residual arrives through the shared-memory ring."""
+    from uplifting_biomolecular_modeling_b200.ops import gemm, native
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    b = (torch.randn(N, K, device="cuda", generator=g) * K ** -0.5).bfloat16()
+    bias = torch.randn(N, device="cuda", generator=g)
+    res = torch.randn(M, N, device="cuda", generator=g).bfloat16()
+    out = gemm.gemm(a, b, bias=bias, residual=res)
+    inplace = res.clone()
+    gemm.gemm(a, b, bias=bias, residual=inplace, out=inplace)      # output over the residual
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "gemm")
+    ref = a.float() @ b.float().T + bias + res.float()
+    assert torch.allclose(out.float(), ref, atol=4e-2, rtol=2e-2)
+    assert torch.equal(out, inplace)
+
+
+def test_gemm_blocked_output_is_the_permuted_product():
+    """c_blocked writes [(i, c), (j, d)] products as [(i, j), (c, d)] rows."""
+    from uplifting_biomolecular_modeling_b200.ops import gemm, native
+    g = torch.Generator(device="cuda").manual_seed(4)
+    I, J, c, S = 6, 40, 32, 72
+    a = torch.randn(I * c, S, device="cuda", generator=g).bfloat16()
+    b = torch.randn(J * c, S, device="cuda", generator=g).bfloat16()
+    out = torch.zeros(I * J, c * c, device="cuda", dtype=torch.bfloat16)
+    gemm.gemm(a, b, alpha=0.25, out=out, c_blocked=(J * c * c, c, c * c))
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "gemm")
+    ref = 0.25 * (a.float() @ b.float().T)                                  # [(i, c), (j, d)]
+    ref = ref.view(I, c, J, c).permute(0, 2, 1, 3).reshape(I * J, c * c)
+    assert torch.allclose(out.float(), ref, atol=5e-2, rtol=2e-2)

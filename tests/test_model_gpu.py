@@ -54,3 +54,27 @@ def test_exact_is_bitwise_off():
     b = exact.predict(feats)
     assert torch.equal(a["coords"], b["coords"])
     assert torch.equal(a["plddt"], b["plddt"])
+
+
+@pytest.mark.parametrize("full", [True, False])
+def test_outer_product_mean_fused_vs_reference(full):
+    from uplifting_biomolecular_modeling_b200.models import msa
+    from uplifting_biomolecular_modeling_b200.ops import native
+    torch.manual_seed(1)
+    S, N = 40, 200
+    opm = msa.OuterProductMean().cuda().eval()
+    m = torch.randn(1, S, N, 64, device="cuda")
+    mask = torch.ones(1, S, N, device="cuda")
+    if not full:
+        mask = (torch.rand(1, S, N, device="cuda") > 0.2).float()
+    with torch.no_grad():
+        ref = opm(m, mask)
+        ob = opm.to(torch.bfloat16)
+        ob.impl = "fused"
+        ob.row_block = 64
+        ob.full_mask = full
+        out = ob(m.bfloat16(), mask)
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "outer product mean")
+    err = ((out.float() - ref).abs().mean() / ref.abs().mean()).item()
+    assert err < 3e-2, err

@@ -76,6 +76,7 @@ class Predictor:
         out = {}
         self.h2d_bytes = 0
         no_padding = bool(feats["token_mask"].min() > 0) if "token_mask" in feats else False
+        msa_full = bool(feats["msa_mask"].min() > 0) if "msa_mask" in feats else False
         for k, v in feats.items():
             if self.device.type == "cuda":
                 pin = self._pinned.get(k)
@@ -89,6 +90,7 @@ class Predictor:
                 d = v
             out[k] = d.to(self.dtype) if d.is_floating_point() else d
         out["no_padding"] = no_padding
+        out["msa_full"] = msa_full      # host-side facts about the masks: they select mask-free kernels
         return out
 
     # ------------------------------------------------------------------ sampler step graph

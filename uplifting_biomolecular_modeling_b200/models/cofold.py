@@ -229,6 +229,8 @@ class CofoldModel(nn.Module):
         tmask = feats["token_mask"]
         # without padding tokens the single-track attention needs no key mask (and may run fused)
         smask = None if feats.get("no_padding") is True else tmask
+        for layer in self.msa_module.layers:
+            layer.outer_product_mean.full_mask = feats.get("msa_full") is True
         for _ in range(n + 1):
             s = s_init + self.s_recycle(self.s_norm(s))
             z = z_init + self.z_recycle(self.z_norm(z))

@@ -30,6 +30,7 @@ class OuterProductMean(_Switchable):
         self.proj_b = nn.Linear(c_in, c_hidden, bias=False)
         self.proj_o = nn.Linear(c_hidden * c_hidden, c_out)
         self.row_block = 128
+        self.full_mask = False      # set by the caller when the MSA mask is known (on the host) to be all ones
 
     def forward(self, m: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
         if not (self.impl == "fused" and m.is_cuda and m.dtype == torch.bfloat16 and m.shape[0] == 1):
@@ -47,17 +48,34 @@ class OuterProductMean(_Switchable):
         bt = torch.zeros((N * c, Sp), dtype=torch.bfloat16, device=m.device)
         at[:, :S] = a.permute(1, 2, 0).reshape(N * c, S)
         bt[:, :S] = b.permute(1, 2, 0).reshape(N * c, S)
-        cnt = torch.einsum("si,sj->ij", mask[0].float(), mask[0].float()).clamp(min=1.0)
         wo = self.proj_o.weight.to(torch.bfloat16).contiguous()
         bo = self.proj_o.bias.float()
         out = torch.empty((N, N, wo.shape[0]), dtype=torch.bfloat16, device=m.device)
+        # The mean over sequences: the first GEMM carries 1/S; where sequences are masked the per-pair count
+        # differs from S and the (linear) output projection is rescaled by S / count afterwards, on 128
+        # channels instead of c*c.
+        scale = None
+        if not self.full_mask:
+            cnt = torch.einsum("si,sj->ij", mask[0].float(), mask[0].float()).clamp(min=1.0)
+            scale = (float(S) / cnt).unsqueeze(-1)
         rb = self.row_block
+        blocked = c == 32 and (N * c) % 32 == 0
+        t2 = torch.empty((rb * N, c * c), dtype=torch.bfloat16, device=m.device)
         for i0 in range(0, N, rb):
             i1 = min(N, i0 + rb)
-            t = gemm.gemm(at[i0 * c:i1 * c], bt)                       # [(i,c), (j,d)]
-            t = t.view(i1 - i0, c, N, c).permute(0, 2, 1, 3).reshape((i1 - i0) * N, c * c)
-            t = (t.float() / cnt[i0:i1].reshape(-1, 1)).to(torch.bfloat16)
-            gemm.gemm(t, wo, bias=bo, out=out[i0:i1].view((i1 - i0) * N, -1))
+            nr = (i1 - i0) * N
+            if blocked:
+                # product [(i, c), (j, d)] stored straight into [(i, j), (c, d)] by the kernel's epilogue
+                gemm.gemm(at[i0 * c:i1 * c], bt, alpha=1.0 / S, out=t2, c_blocked=(N * c * c, c, c * c))
+                t = t2[:nr]
+            else:
+                t = gemm.gemm(at[i0 * c:i1 * c], bt, alpha=1.0 / S)
+                t = t.view(i1 - i0, c, N, c).permute(0, 2, 1, 3).reshape(nr, c * c)
+            if scale is None:
+                gemm.gemm(t, wo, bias=bo, out=out[i0:i1].view(nr, -1))
+            else:
+                o = gemm.gemm(t, wo).view(i1 - i0, N, -1)
+                out[i0:i1] = (o.float() * scale[i0:i1] + bo).to(torch.bfloat16)
         return out.unsqueeze(0)
 
 

@@ -30,6 +30,11 @@ struct GemmParams {
   float alpha;
   int out_fp32;
   int act;  // 0 none, 1 silu, 2 sigmoid, 3 gelu (erf), 4 relu
+  int res_tma;  // residual tiles arrive by TMA (tensor map in the auxiliary map slot 0)
+  // blocked output (cblk_col != 0): element (m, n) goes to (m / 32) * cblk_hi + (m % 32) * cblk_lo +
+  // (n / 32) * cblk_col + n % 32.  With m = (i, c) and n = (j, d), c, d < 32, this writes the outer-product
+  // layout [(i, j)][(c, d)] directly, so no permuted copy of the product is made.
+  long long cblk_hi, cblk_lo, cblk_col;
   KernelStatus* status;
   int tiles_m, tiles_n, num_tiles;
   // peer mode: the N dimension is the concatenation of row shards owned by several GPUs; n-tiles are
@@ -79,8 +84,13 @@ struct GemmCfg {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 512 /*barriers*/;
+  // BN = 128 gives up one operand stage for a two-slot ring of residual tiles (128 x 128 bf16 each) that the
+  // producer fills by TMA, so the epilogue never waits on a global load
+  static constexpr bool kResTma = (BN == 128);
+  static constexpr int kStages = (BN == 256) ? 4 : 5;
+  static constexpr int kResSlotBytes = kBM * 128 * 2;
+  static constexpr int kResBytes = kResTma ? 2 * kResSlotBytes : 0;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kResBytes + 1024 /*align*/ + 512 /*barriers*/;
   static constexpr int kTmemCols = (2 * BN <= 32) ? 32 : 2 * BN;  // two accumulator buffers
 };
 
@@ -126,11 +136,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint8_t* sRes = smem + Cfg::kStages * Cfg::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sRes + Cfg::kResBytes);
   uint64_t* empty_bar = full_bar + Cfg::kStages;
   uint64_t* tfull_bar = empty_bar + Cfg::kStages;
   uint64_t* tempty_bar = tfull_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* rfull_bar = tempty_bar + 2;
+  uint64_t* rempty_bar = rfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(rempty_bar + 2);
+  const bool res_tma = Cfg::kResTma && !PEER && p.res_tma != 0;
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -146,6 +160,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
       mbar_init(&tempty_bar[a], 4);
+      mbar_init(&rfull_bar[a], 1);
+      mbar_init(&rempty_bar[a], 4);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -228,11 +244,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int t = cta_id; t < p.num_tiles; t += compute_ctas) {
+      uint32_t lt = 0;   // tiles this CTA has started
+      for (int t = cta_id; t < p.num_tiles; t += compute_ctas, ++lt) {
         const int b = t / tiles_per_batch;
         const int r = t - b * tiles_per_batch;
         const int nb = r / p.tiles_m;
         const int mb = r - nb * p.tiles_m;
+        if (res_tma) {
+          // residual tile of this output tile; its slot was released by the epilogue two tiles ago
+          const int rs = lt & 1;
+          mbar_wait(&rempty_bar[rs], ((lt >> 1) & 1u) ^ 1u, ws, 7, rs);
+          if (*abort_flag) break;
+          mbar_expect_tx(&rfull_bar[rs], Cfg::kResSlotBytes);
+          tma_load_3d(sRes + rs * Cfg::kResSlotBytes, &gathered.m[0], &rfull_bar[rs], nb * BN, mb * kBM, b);
+          tma_load_3d(sRes + rs * Cfg::kResSlotBytes + 16384, &gathered.m[0], &rfull_bar[rs], nb * BN + 64,
+                      mb * kBM, b);
+        }
         int gq = 0, g_base = 0, g_limit = 0, g_lrow = 0, g_plain = 0;
         if (gather_once) {
           decode_ntile_rot<BN>(p, nb, gq, g_base, g_limit, g_lrow, g_plain);
@@ -340,11 +367,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                       (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)
                                    : ((p.ldc & 7) == 0 && (p.strideC & 7) == 0 &&
                                       (reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
-    for (int t = cta_id; t < p.num_tiles; t += compute_ctas) {
+    uint32_t lt = 0;
+    for (int t = cta_id; t < p.num_tiles; t += compute_ctas, ++lt) {
       const int b = t / tiles_per_batch;
       const int r = t - b * tiles_per_batch;
       const int nb = r / p.tiles_m;
       const int mb = r - nb * p.tiles_m;
+      const uint8_t* rsm = sRes + (lt & 1) * Cfg::kResSlotBytes;
+      if (res_tma) mbar_wait(&rfull_bar[lt & 1], (lt >> 1) & 1u, ws, 8, lt & 1);
       mbar_wait(&tfull_bar[acc], acc_phase, ws, 4, acc);
       tc_fence_after_sync();
       const int m = mb * kBM + q * 32 + lane;
@@ -356,27 +386,55 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       } else {
         decode_ntile<BN>(p, nb, pq, n_base, n_limit, lrow);
       }
-#pragma unroll 1
+      // 32-column chunks; the TMEM load of chunk c + 1 is in flight while chunk c is processed
+      const int nchunks = min(BN / 32, (n_limit - n_base + 31) / 32);   // warp-uniform
+      uint32_t vbuf[2][32];
+      if (nchunks > 0) tmem_ld32(tmem_addr(tmem_base, q, acc * BN), vbuf[0]);
+#pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
         const int n0 = n_base + c * 32;
-        if (n0 >= n_limit) break;  // warp-uniform
-        uint32_t v[32];
-        tmem_ld32(tmem_addr(tmem_base, q, acc * BN + c * 32), v);
+        if (c >= nchunks) break;
         tmem_ld_wait();
+        if (c + 1 < nchunks) tmem_ld32(tmem_addr(tmem_base, q, acc * BN + (c + 1) * 32), vbuf[(c + 1) & 1]);
+        const uint32_t* v = vbuf[c & 1];
         if (row_ok) {
           float f[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
           if (p.bias != nullptr) {
+            if (n0 + 32 <= n_limit && (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (n0 + j < n_limit) f[j] += __ldg(p.bias + n0 + j);
+              for (int j = 0; j < 32; j += 4) {
+                const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + n0 + j));
+                f[j] += bv.x;
+                f[j + 1] += bv.y;
+                f[j + 2] += bv.z;
+                f[j + 3] += bv.w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + j < n_limit) f[j] += __ldg(p.bias + n0 + j);
+            }
           }
           if (p.act != 0) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] = apply_act(f[j], p.act);
           }
-          if (p.residual != nullptr) {
+          if (res_tma) {
+            // 32 columns = four 16-byte units of tile row q*32+lane in the swizzled 64-column block c/2
+#pragma unroll
+            for (int j8 = 0; j8 < 4; ++j8) {
+              const uint4 u = *reinterpret_cast<const uint4*>(rsm + (c >> 1) * 16384 +
+                                                              swz128_offset(q * 32 + lane, (c & 1) * 4 + j8));
+              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                f[j8 * 8 + 2 * e] += bf16_lo(w[e]);
+                f[j8 * 8 + 2 * e + 1] += bf16_hi(w[e]);
+              }
+            }
+          } else if (p.residual != nullptr) {
             const __nv_bfloat16* rr = p.residual + b * p.strideR + static_cast<long long>(m) * p.ldr + n0;
             if (n0 + 32 <= n_limit && (reinterpret_cast<uintptr_t>(rr) & 31) == 0) {
 #pragma unroll
@@ -404,8 +462,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (n0 + j < n_limit) f[j] += __bfloat162float(rr[j]);
             }
           }
+          const long long c_off =
+              p.cblk_col != 0 ? (static_cast<long long>(m >> 5) * p.cblk_hi + static_cast<long long>(m & 31) * p.cblk_lo +
+                                 static_cast<long long>(n0 >> 5) * p.cblk_col)
+                              : static_cast<long long>(m) * p.ldc + n0;
           if (p.out_fp32) {
-            float* cp = reinterpret_cast<float*>(p.C) + b * p.strideC + static_cast<long long>(m) * p.ldc + n0;
+            float* cp = reinterpret_cast<float*>(p.C) + b * p.strideC + c_off;
             if (n0 + 32 <= n_limit && (reinterpret_cast<uintptr_t>(cp) & 31) == 0) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8)
@@ -424,8 +486,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (n0 + j < n_limit) cp[j] = f[j];
             }
           } else {
-            __nv_bfloat16* cp =
-                reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.strideC + static_cast<long long>(m) * p.ldc + n0;
+            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.strideC + c_off;
             if (n0 + 32 <= n_limit && (reinterpret_cast<uintptr_t>(cp) & 31) == 0) {
               st_bf16x16(cp, f);
               st_bf16x16(cp + 16, f + 16);
@@ -449,7 +510,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (lane == 0) {
+        mbar_arrive(&tempty_bar[acc]);
+        if (res_tma) mbar_arrive(&rempty_bar[lt & 1]);
+      }
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1u;
@@ -503,9 +567,23 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   rc = set_smem(kern, Cfg::kSmemBytes);
   if (rc) return rc;
   int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  PeerMaps none;
+  PeerMaps none, aux;
   none.m[0] = tmB;
-  kern<<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, none, none, p);
+  aux.m[0] = tmB;
+  p.res_tma = 0;
+  if (Cfg::kResTma && p.residual != nullptr && (p.ldr & 7) == 0 && (p.batch == 1 || (p.strideR & 7) == 0) &&
+      (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0) {
+    // residual [batch][M][N] as a tensor map: 64-column x 128-row boxes in the 128-byte swizzle
+    const long long sr = p.batch == 1 ? (long long)p.M * p.ldr : p.strideR;
+    uint64_t dR[3] = {(uint64_t)p.N, (uint64_t)p.M, (uint64_t)p.batch};
+    uint64_t sR[2] = {(uint64_t)p.ldr * 2, (uint64_t)sr * 2};
+    uint32_t bR[3] = {64, kBM, 1};
+    rc = make_tmap(&aux.m[0], p.residual, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dR, sR, bR,
+                   CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    p.res_tma = 1;
+  }
+  kern<<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, none, aux, p);
   UBM_CHECK_LAUNCH("gemm_bf16_kernel");
   return UBM_OK;
 }
@@ -516,12 +594,16 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
 // A, B bf16. ld* and stride* in elements. mn_major: 0 = K contiguous, 1 = M/N contiguous.
 // bias: fp32 [N] or null. residual: bf16 with leading dimension ldr / batch stride strideR, or null.
 // status: device pointer to a ubm::KernelStatus (16 bytes) or null.
-extern "C" int ubm_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const void* residual, int M,
-                             int N, int K, int batch, long long lda, long long ldb, long long ldc, long long ldr,
-                             long long strideA, long long strideB, long long strideC, long long strideR, int mn_major,
-                             int out_fp32, int act, float alpha, void* status, void* stream) {
+// cblk_*: blocked output addressing (see GemmParams); all zero for the plain [M][N] layout.  The blocked form
+// needs N to be a multiple of 32.
+extern "C" int ubm_gemm_bf16_ex(const void* A, const void* B, void* C, const void* bias, const void* residual, int M,
+                                int N, int K, int batch, long long lda, long long ldb, long long ldc, long long ldr,
+                                long long strideA, long long strideB, long long strideC, long long strideR,
+                                int mn_major, int out_fp32, int act, float alpha, long long cblk_hi,
+                                long long cblk_lo, long long cblk_col, void* status, void* stream) {
   using namespace ubm;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return UBM_ERR_ARGUMENT;
+  if (cblk_col != 0 && ((N & 31) || residual != nullptr)) return UBM_ERR_ARGUMENT;
   if ((lda & 7) || (ldb & 7) || (batch > 1 && ((strideA & 7) || (strideB & 7)))) {
     fprintf(stderr, "[ubm] gemm: leading dimensions / batch strides must be multiples of 8 elements\n");
     return UBM_ERR_ARGUMENT;
@@ -541,6 +623,9 @@ extern "C" int ubm_gemm_bf16(const void* A, const void* B, void* C, const void* 
   p.alpha = alpha;
   p.out_fp32 = out_fp32;
   p.act = act;
+  p.cblk_hi = cblk_hi;
+  p.cblk_lo = cblk_lo;
+  p.cblk_col = cblk_col;
   p.status = static_cast<KernelStatus*>(status);
   if (batch == 1) {
     if (strideA == 0) strideA = mn_major ? (long long)K * lda : (long long)M * lda;
@@ -554,6 +639,14 @@ extern "C" int ubm_gemm_bf16(const void* A, const void* B, void* C, const void* 
   }
   return wide ? launch_gemm<256, false>(A, B, p, lda, ldb, strideA, strideB, st)
               : launch_gemm<128, false>(A, B, p, lda, ldb, strideA, strideB, st);
+}
+
+extern "C" int ubm_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const void* residual, int M,
+                             int N, int K, int batch, long long lda, long long ldb, long long ldc, long long ldr,
+                             long long strideA, long long strideB, long long strideC, long long strideR, int mn_major,
+                             int out_fp32, int act, float alpha, void* status, void* stream) {
+  return ubm_gemm_bf16_ex(A, B, C, bias, residual, M, N, K, batch, lda, ldb, ldc, ldr, strideA, strideB, strideC,
+                          strideR, mn_major, out_fp32, act, alpha, 0, 0, 0, status, stream);
 }
 
 // All-gather fused into the GEMM: C[b][m][col0_q + n] = sum_k A[b][m][k] * B_q[b][n][k] where B_q is the

@@ -22,8 +22,13 @@ def _as3(t: torch.Tensor) -> torch.Tensor:
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, mn_major: bool = False, bias: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, act: Optional[str] = None, alpha: float = 1.0,
-         out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+         out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
+         c_blocked: Optional[tuple] = None) -> torch.Tensor:
     """C = act(alpha * A.B^T + bias) + residual.
+
+    ``c_blocked=(hi, lo, col)`` (with ``out`` given, N a multiple of 32, batch 1) stores element (m, n) at
+    ``out.data_ptr + (m // 32) * hi + (m % 32) * lo + (n // 32) * col + n % 32`` elements: the product of two
+    [(token, channel)] operands lands as [(i, j)][(c, d)] without a permuted copy.
 
     mn_major=False: a [.., M, K], b [.., N, K];  mn_major=True: a [.., K, M], b [.., K, N].
     The innermost dimension of a and b must be contiguous; other strides are free as long as
@@ -48,11 +53,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, mn_major: bool = False, bias: Opti
         N = b3.shape[1]
         if b3.shape[2] != K:
             raise ValueError("K mismatch")
-    if out is None:
-        out = torch.empty((batch, M, N), dtype=out_dtype, device=a.device)
-    out3 = _as3(out)
-    if out3.stride(-1) != 1:
-        raise ValueError("output innermost dimension must be contiguous")
+    if c_blocked is not None:
+        if out is None or batch != 1 or N % 32 or residual is not None:
+            raise ValueError("c_blocked needs an output tensor, batch 1, N % 32 == 0 and no residual")
+        out3 = out
+    else:
+        if out is None:
+            out = torch.empty((batch, M, N), dtype=out_dtype, device=a.device)
+        out3 = _as3(out)
+        if out3.stride(-1) != 1:
+            raise ValueError("output innermost dimension must be contiguous")
     res3 = None
     if residual is not None:
         res3 = _as3(residual)
@@ -61,15 +71,20 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, mn_major: bool = False, bias: Opti
     if bias is not None and bias.dtype != torch.float32:
         bias = bias.float()
     st = native.status_tensor(a.device)
-    rc = native.lib().ubm_gemm_bf16(
+    cb = c_blocked if c_blocked is not None else (0, 0, 0)
+    rc = native.lib().ubm_gemm_bf16_ex(
         native.ptr(a3), native.ptr(b3), native.ptr(out3), native.ptr(bias), native.ptr(res3),
         M, N, K, batch,
-        a3.stride(1), b3.stride(1), out3.stride(1), 0 if res3 is None else res3.stride(1),
+        a3.stride(1), b3.stride(1), 0 if c_blocked is not None else out3.stride(1),
+        0 if res3 is None else res3.stride(1),
         a3.stride(0) if batch > 1 else 0, b3.stride(0) if batch > 1 else 0,
-        out3.stride(0) if batch > 1 else 0, 0 if res3 is None or batch == 1 else res3.stride(0),
+        out3.stride(0) if batch > 1 and c_blocked is None else 0,
+        0 if res3 is None or batch == 1 else res3.stride(0),
         1 if mn_major else 0, 1 if out3.dtype == torch.float32 else 0, ACT[act], float(alpha),
-        native.ptr(st), native.current_stream(a.device))
-    native.check(rc, "ubm_gemm_bf16")
+        int(cb[0]), int(cb[1]), int(cb[2]), native.ptr(st), native.current_stream(a.device))
+    native.check(rc, "ubm_gemm_bf16_ex")
+    if c_blocked is not None:
+        return out
     return out3[0] if squeeze and out.dim() == 3 else out
 
 
