@@ -5,7 +5,8 @@
 Cases: ``attention`` (triangle-attention core, H=4 x D=32, rows = N), ``attention_d64`` (token attention,
 16 heads x 64, 5 samples), ``trimul_proj``, ``trimul_gemm``, ``trimul_out``, ``triatt_proj``, ``transition``,
 ``out_gemm`` (the [N*N,128] x [128,128] output projection with residual), ``trimul`` (three launches),
-``triatt`` (three launches).  Inputs are larger than L2 for N >= 768.  Prints one line per case with the
+``triatt`` (three launches), ``gemm_rows`` (--m --k --nn: a row GEMM with bias), ``window_attention`` (--m atoms,
+5 samples, 4 heads x 32).  Inputs are larger than L2 for N >= 768.  Prints one line per case with the
 mean time, the algorithmic bytes and FLOPs, and the fractions of the measured peaks in MEASURED_PEAKS.json
 (fallback 6.65 TB/s, 1.59 PFLOP/s when the file is absent).
 """
@@ -55,6 +56,9 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--attn-variant", type=int, default=0, help="0 = by shape, 1 = two rows per CTA")
+    ap.add_argument("--m", type=int, default=7680, help="rows of the gemm_rows case / atoms of window_attention")
+    ap.add_argument("--k", type=int, default=768)
+    ap.add_argument("--nn", type=int, default=3072)
     a = ap.parse_args()
     N, c = a.n, 128
     pair.set_attention_variant(a.attn_variant)
@@ -130,6 +134,33 @@ def main():
         out = torch.empty_like(og)
         fn = lambda: gemm.gemm(og, wo, bias=zeros, residual=z.view(N * N, c), out=out)  # noqa: E731
         byts, flops = 3 * og.numel() * 2, 2.0 * N * N * c * c
+    elif a.case == "gemm_rows":
+        # plain row GEMM with bias, the shape family of the diffusion transformer: [m, k] x [nn, k]^T
+        M, K, NN = a.m, a.k, a.nn
+        x = torch.randn(M, K, device=dev).bfloat16()
+        wt = r(NN, K).bfloat16()
+        bvec = torch.zeros(NN, device=dev)
+        out = torch.empty((M, NN), dtype=torch.bfloat16, device=dev)
+        fn = lambda: gemm.gemm(x, wt, bias=bvec, out=out)  # noqa: E731
+        byts, flops = (x.numel() + wt.numel() + out.numel()) * 2, 2.0 * M * K * NN
+    elif a.case == "window_attention":
+        B, A, H = 5, a.m // 32 * 32, 4
+        xw = torch.randn(B * A, 3 * H * 32, device=dev).bfloat16()
+        bias = torch.randn(1, H, A // 32, 32, 128, device=dev).bfloat16()
+        gate = torch.rand(B * A, H * 32, device=dev).bfloat16()
+        out = torch.empty_like(gate)
+        native.declare("ubm_window_attention", [native.c_void_p] * 6 + [native.c_int, native.c_int, native.c_int,
+                                                                       native.c_ll, native.c_int, native.c_void_p])
+        if a.attn_variant == 1:       # CUDA-core kernel, one window per CTA
+            fn = lambda: lib.ubm_window_attention(native.ptr(xw), native.ptr(xw) + H * 64,  # noqa: E731
+                                                  native.ptr(xw) + H * 128, native.ptr(bias), native.ptr(gate),
+                                                  native.ptr(out), B, A, H, 3 * H * 32, 1, stream)
+        else:                         # tcgen05 kernel, four windows per CTA
+            fn = lambda: lib.ubm_window_attention_tc(native.ptr(xw), native.ptr(xw) + H * 64,  # noqa: E731
+                                                     native.ptr(xw) + H * 128, native.ptr(bias), native.ptr(gate),
+                                                     native.ptr(out), B, A, H, 3 * H * 32, 1, native.ptr(st), stream)
+        byts = (xw.numel() + bias.numel() + 2 * gate.numel()) * 2
+        flops = 4.0 * B * A * H * 128 * 32
     else:
         raise SystemExit(f"unknown case {a.case}")
     ms = timeit(fn, a.iters, a.warmup)

@@ -153,11 +153,14 @@ def test_row_kernels():
     assert torch.allclose(rows.gate_residual(sh, sc, a).float(), ref, atol=5e-2, rtol=3e-2)
 
 
-def test_window_attention_matches_reference():
+@pytest.mark.parametrize("kernel", ["tc", "simt"])
+@pytest.mark.parametrize("A", [320, 96, 800])
+def test_window_attention_matches_reference(A, kernel, monkeypatch):
     from uplifting_biomolecular_modeling_b200.models import diffusion, pairformer
-    from uplifting_biomolecular_modeling_b200.ops import pair
+    from uplifting_biomolecular_modeling_b200.ops import native, pair
+    monkeypatch.setattr(pair, "WINDOW_KERNEL", kernel)
     torch.manual_seed(9)
-    B, A, c, H = 3, 320, 128, 4
+    B, c, H = 3, 128, 4
     attn = pairformer.AttentionPairBias(c, 128, H, compute_pair_bias=False).cuda().eval()
     x = torch.randn(B, A, c, device="cuda")
     bias = torch.randn(1, H, A // 32, 32, 128, device="cuda")
@@ -168,5 +171,6 @@ def test_window_attention_matches_reference():
                                 ab.proj_o.weight, H)
         out = pair.window_attention_fused(x.bfloat16(), w, diffusion.WindowBias(bias).data)
     torch.cuda.synchronize()
+    native.raise_on_status("cuda", "window attention")
     err = ((out.float() - ref).abs().mean() / ref.abs().mean()).item()
     assert err < 4e-2, err

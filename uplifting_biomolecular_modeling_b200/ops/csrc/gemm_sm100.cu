@@ -388,15 +388,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       // 32-column chunks; the TMEM load of chunk c + 1 is in flight while chunk c is processed
       const int nchunks = min(BN / 32, (n_limit - n_base + 31) / 32);   // warp-uniform
-      uint32_t vbuf[2][32];
-      if (nchunks > 0) tmem_ld32(tmem_addr(tmem_base, q, acc * BN), vbuf[0]);
-#pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
+      // (the chunk body appears twice, not BN/32 times: unrolled over all chunks it outgrew the instruction cache)
+      auto process = [&](const uint32_t (&v)[32], const int c) {
         const int n0 = n_base + c * 32;
-        if (c >= nchunks) break;
-        tmem_ld_wait();
-        if (c + 1 < nchunks) tmem_ld32(tmem_addr(tmem_base, q, acc * BN + (c + 1) * 32), vbuf[(c + 1) & 1]);
-        const uint32_t* v = vbuf[c & 1];
         if (row_ok) {
           float f[32];
 #pragma unroll
@@ -506,6 +500,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (n0 + j < n_limit) cp[j] = __float2bfloat16(f[j]);
             }
           }
+        }
+      };
+      uint32_t va[32], vb[32];
+      if (nchunks > 0) tmem_ld32(tmem_addr(tmem_base, q, acc * BN), va);
+#pragma unroll 1
+      for (int c = 0; c < nchunks; c += 2) {
+        tmem_ld_wait();
+        if (c + 1 < nchunks) tmem_ld32(tmem_addr(tmem_base, q, acc * BN + (c + 1) * 32), vb);
+        process(va, c);
+        if (c + 1 < nchunks) {
+          tmem_ld_wait();
+          if (c + 2 < nchunks) tmem_ld32(tmem_addr(tmem_base, q, acc * BN + (c + 2) * 32), va);
+          process(vb, c + 1);
         }
       }
       tc_fence_before_sync();

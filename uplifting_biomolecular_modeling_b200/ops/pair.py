@@ -298,6 +298,9 @@ def triangle_attention_fused(z: torch.Tensor, w: TriattPacked, starting: bool, r
 
 # ------------------------------------------------------------------------------------------
 native.declare("ubm_window_attention", [c_void_p] * 6 + [c_int, c_int, c_int, c_ll, c_int, c_void_p])
+native.declare("ubm_window_attention_tc", [c_void_p] * 6 + [c_int, c_int, c_int, c_ll, c_int, c_void_p, c_void_p])
+
+WINDOW_KERNEL = "tc"     # "tc": tcgen05 kernel (four windows per CTA); "simt": CUDA-core kernel (one window per CTA)
 
 
 def window_attention_fused(x: torch.Tensor, w: ApbPacked, bias: Optional[torch.Tensor]) -> torch.Tensor:
@@ -311,8 +314,18 @@ def window_attention_fused(x: torch.Tensor, w: ApbPacked, bias: Optional[torch.T
     qkv = _gemm.gemm(x2, w.wqkv, bias=w.bqkv)
     g = _gemm.gemm(x2, w.wg, act="sigmoid")
     o = torch.empty((B * A, HD), dtype=torch.bfloat16, device=x.device)
-    rc = native.lib().ubm_window_attention(native.ptr(qkv), native.ptr(qkv) + HD * 2, native.ptr(qkv) + 2 * HD * 2,
-                                           native.ptr(bias), native.ptr(g), native.ptr(o), B, A, w.H, 3 * HD,
-                                           1 if bias is None else bias.shape[0], native.current_stream(x.device))
-    native.check(rc, "ubm_window_attention")
+    if WINDOW_KERNEL == "tc":
+        rc = native.lib().ubm_window_attention_tc(native.ptr(qkv), native.ptr(qkv) + HD * 2,
+                                                  native.ptr(qkv) + 2 * HD * 2, native.ptr(bias), native.ptr(g),
+                                                  native.ptr(o), B, A, w.H, 3 * HD,
+                                                  1 if bias is None else bias.shape[0],
+                                                  native.ptr(native.status_tensor(x.device)),
+                                                  native.current_stream(x.device))
+        native.check(rc, "ubm_window_attention_tc")
+    else:
+        rc = native.lib().ubm_window_attention(native.ptr(qkv), native.ptr(qkv) + HD * 2,
+                                               native.ptr(qkv) + 2 * HD * 2, native.ptr(bias), native.ptr(g),
+                                               native.ptr(o), B, A, w.H, 3 * HD,
+                                               1 if bias is None else bias.shape[0], native.current_stream(x.device))
+        native.check(rc, "ubm_window_attention")
     return _gemm.gemm(o, w.wo).view(B, A, -1)
