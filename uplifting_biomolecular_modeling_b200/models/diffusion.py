@@ -91,37 +91,60 @@ class DiffusionTransformerLayer(_Switchable):
 
     def hoist(self, s):
         """Everything that depends only on the conditioning s (same for every layer call of a step)."""
-        return {"adaln": self.adaln.cond(s), "gate": self.output_projection_linear(s),
-                "t_adaln": self.transition.adaln.cond(s), "t_gate": self.transition.output_projection(s)}
+        gate, t_gate = self.output_projection_linear(s), self.transition.output_projection(s)
+        return {"adaln": self.adaln.cond(s), "gate": gate, "t_adaln": self.transition.adaln.cond(s),
+                "t_gate": t_gate, "gate_sig": torch.sigmoid(gate), "t_gate_sig": torch.sigmoid(t_gate)}
+
+    def cond_weights(self):
+        """Rows of the batched conditioning GEMMs of this layer: (W [4C, dim_s], b [4C]) for
+        scale | shift | transition scale | transition shift on the affine-free normalised s (the LayerNorm weight
+        of each AdaLN is folded into its columns), and (W [2C, dim_s], b [2C]) for the two output gates on s."""
+        def fold(ad):
+            g = ad.s_norm.weight.detach().float()
+            return (ad.s_scale.weight.detach().float() * g[None, :], ad.s_scale.bias.detach().float(),
+                    ad.s_bias.weight.detach().float() * g[None, :])
+        ws, bs, wb = fold(self.adaln)
+        tws, tbs, twb = fold(self.transition.adaln)
+        zc = torch.zeros_like(bs)
+        w1 = torch.cat([ws, wb, tws, twb], 0)
+        b1 = torch.cat([bs, zc, tbs, zc], 0)
+        w2 = torch.cat([self.output_projection_linear.weight.detach().float(),
+                        self.transition.output_projection.weight.detach().float()], 0)
+        b2 = torch.cat([self.output_projection_linear.bias.detach().float(),
+                        self.transition.output_projection.bias.detach().float()], 0)
+        return w1, b1, w2, b2
 
     def _fused_token_layer(self, a, h, bias):
         """Token-transformer layer on the fused path: AdaLN rows -> q|k|v and gate projections (tcgen05
-        GEMM) -> attention with the hoisted pair-bias planes shared by all samples -> output projection ->
-        gated residual; then the conditioned SwiGLU transition the same way."""
+        GEMM) -> attention with the hoisted pair-bias planes shared by all samples -> output projection whose
+        epilogue applies the conditioning gate and the residual; then the conditioned SwiGLU transition the same
+        way (one GEMM for swish_gated and a_to_b, a three-way row kernel, an output GEMM with gate and residual)."""
         from ..ops import gemm, pair, rows
         B, N, C = a.shape
         attn = self.pair_bias_attn
-        b = rows.adaln_rows(a.contiguous(), h["adaln"][0].contiguous(), h["adaln"][1].contiguous())
+        a = a.contiguous()
+        a2 = a.view(B * N, C)
+        gate, t_gate = h["gate_sig"], h["t_gate_sig"]
+        gate = gate.reshape(-1, C) if gate.dim() == 3 else gate
+        t_gate = t_gate.reshape(-1, C) if t_gate.dim() == 3 else t_gate
+        b = rows.adaln_rows(a, h["adaln"][0], h["adaln"][1])
         if isinstance(bias, WindowBias):
             if attn._packed is None:
                 attn._packed = pair.ApbPacked.pack(attn.proj_q.weight, attn.proj_q.bias, attn.proj_k.weight,
                                                    attn.proj_v.weight, attn.proj_g.weight, attn.proj_o.weight,
                                                    attn.heads)
-            o = pair.window_attention_fused(b, attn._packed, bias.data)
+            a = pair.window_attention_fused(b, attn._packed, bias.data, out_gate=gate, out_residual=a2)
         else:
-            o = attn._fused_forward(b, bias)
-        a = rows.gate_residual(o.contiguous(), h["gate"].contiguous(), a)
+            a = attn._fused_forward(b, bias, out_gate=gate, out_residual=a2)
+        a2 = a.view(B * N, C)
         tr = self.transition
         if self._packed is None:
-            self._packed = (tr.swish_gated.weight.to(torch.bfloat16).contiguous(),
-                            tr.a_to_b.weight.to(torch.bfloat16).contiguous(),
+            self._packed = (torch.cat([tr.swish_gated.weight, tr.a_to_b.weight], 0).to(torch.bfloat16).contiguous(),
                             tr.b_to_a.weight.to(torch.bfloat16).contiguous())
-        w_sg, w_ab, w_ba = self._packed
-        x = rows.adaln_rows(a, h["t_adaln"][0].contiguous(), h["t_adaln"][1].contiguous()).view(B * N, C)
-        u = rows.swiglu_rows(gemm.gemm(x, w_sg))
-        u = u * gemm.gemm(x, w_ab)
-        y = gemm.gemm(u, w_ba).view(B, N, C)
-        return rows.gate_residual(y, h["t_gate"].contiguous(), a)
+        w_in, w_ba = self._packed
+        x = rows.adaln_rows(a, h["t_adaln"][0], h["t_adaln"][1]).view(B * N, C)
+        u = rows.swiglu3_rows(gemm.gemm(x, w_in))
+        return gemm.gemm(u, w_ba, gate=t_gate, residual=a2).view(B, N, C)
 
     def forward(self, a, s, bias, mask=None, multiplicity: int = 1, hoisted: Optional[dict] = None,
                 window: Optional[tuple] = None):
@@ -169,6 +192,38 @@ class DiffusionTransformer(nn.Module):
     def __init__(self, depth: int, dim: int, dim_s: int, heads: int):
         super().__init__()
         self.layers = nn.ModuleList([DiffusionTransformerLayer(dim, dim_s, heads) for _ in range(depth)])
+        self._cond_packed = None
+
+    def hoist_all(self, s):
+        """Conditioning of every layer from two GEMMs (fused path): the affine-free normalised s against the
+        stacked AdaLN weights of all layers, and s against the stacked gate weights with the sigmoid in the
+        epilogue.  Per-layer entries are column slices of the two outputs.  s: [1, N, dim_s] bf16 on the GPU."""
+        from ..ops import gemm
+        C = self.layers[0].dim
+        if self._cond_packed is None:
+            parts = [l.cond_weights() for l in self.layers]
+            self._cond_packed = (torch.cat([p[0] for p in parts], 0).to(torch.bfloat16).contiguous(),
+                                 torch.cat([p[1] for p in parts], 0).contiguous(),
+                                 torch.cat([p[2] for p in parts], 0).to(torch.bfloat16).contiguous(),
+                                 torch.cat([p[3] for p in parts], 0).contiguous())
+        w1, b1, w2, b2 = self._cond_packed
+        s2 = s.reshape(-1, s.shape[-1])
+        sn = F.layer_norm(s2.float(), (s2.shape[-1],)).to(torch.bfloat16)
+        cond = gemm.gemm(sn, w1, bias=b1)                                   # [N, L * 4C]
+        gates = gemm.gemm(s2.to(torch.bfloat16).contiguous(), w2, bias=b2, act="sigmoid")   # [N, L * 2C]
+        out = []
+        for i in range(len(self.layers)):
+            c0, g0 = i * 4 * C, i * 2 * C
+            out.append({"adaln": (cond[:, c0:c0 + C], cond[:, c0 + C:c0 + 2 * C]),
+                        "t_adaln": (cond[:, c0 + 2 * C:c0 + 3 * C], cond[:, c0 + 3 * C:c0 + 4 * C]),
+                        "gate_sig": gates[:, g0:g0 + C], "t_gate_sig": gates[:, g0 + C:g0 + 2 * C],
+                        "gate": None, "t_gate": None})
+        return out
+
+    def can_hoist_all(self, s, biases) -> bool:
+        from .pairformer import BiasPlanes
+        return (s.is_cuda and s.dtype == torch.bfloat16 and all(l.impl == "fused" for l in self.layers)
+                and all(isinstance(b, BiasPlanes) for b in biases) and self.layers[0].dim % 8 == 0)
 
     def forward(self, a, s, biases, mask=None, multiplicity=1, hoisted=None, window=None):
         for i, layer in enumerate(self.layers):
@@ -341,7 +396,8 @@ class DiffusionModule(nn.Module):
         a, q = self.atom_attention_encoder(prep["atom_q"], prep["atom_c"], prep["enc_bias"], r_noisy,
                                            atom_to_token, n_tokens, prep["enc_hoist"], self.window)
         a = a + self.s_to_a_linear(s)
-        hoisted = [l.hoist(s) for l in self.token_transformer.layers]
+        tt = self.token_transformer
+        hoisted = tt.hoist_all(s) if tt.can_hoist_all(s, prep["token_bias"]) else [l.hoist(s) for l in tt.layers]
         a = self.token_transformer(a, s, prep["token_bias"], None, multiplicity=B, hoisted=hoisted)
         a = self.a_norm(a)
         return self.atom_attention_decoder(a, q, prep["atom_c"], prep["dec_bias"], atom_to_token,

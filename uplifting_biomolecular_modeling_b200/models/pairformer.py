@@ -194,13 +194,14 @@ class AttentionPairBias(_Switchable):
                                                   self.proj_z[1].weight, scale=BiasPlanes.LOG2E))
         return self.proj_z[1](self.proj_z[0](z)).permute(0, 3, 1, 2)
 
-    def _fused_forward(self, s: torch.Tensor, planes: "BiasPlanes") -> torch.Tensor:
+    def _fused_forward(self, s: torch.Tensor, planes: "BiasPlanes", out_gate=None, out_residual=None) -> torch.Tensor:
         from ..ops import pair
         if self._packed is None:
             self._packed = pair.ApbPacked.pack(self.proj_q.weight, self.proj_q.bias, self.proj_k.weight,
                                                self.proj_v.weight, self.proj_g.weight, self.proj_o.weight,
                                                self.heads)
-        return pair.apb_fused(s.to(torch.bfloat16).contiguous(), self._packed, planes.view, planes.ld)
+        return pair.apb_fused(s.to(torch.bfloat16).contiguous(), self._packed, planes.view, planes.ld,
+                              out_gate=out_gate, out_residual=out_residual)
 
     def forward(self, s: torch.Tensor, z: Optional[torch.Tensor], mask: Optional[torch.Tensor],
                 bias: Optional[torch.Tensor] = None, k_in: Optional[torch.Tensor] = None,

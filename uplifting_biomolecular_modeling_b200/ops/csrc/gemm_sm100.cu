@@ -35,6 +35,11 @@ struct GemmParams {
   // (n / 32) * cblk_col + n % 32.  With m = (i, c) and n = (j, d), c, d < 32, this writes the outer-product
   // layout [(i, j)][(c, d)] directly, so no permuted copy of the product is made.
   long long cblk_hi, cblk_lo, cblk_col;
+  // multiplicative gate applied after the activation and before the residual: bf16 [gate_rows][ld_gate],
+  // row m uses gate row m % gate_rows (conditioning shared by several samples); values are used as they are
+  const __nv_bfloat16* gate;
+  long long ld_gate;
+  int gate_rows;
   KernelStatus* status;
   int tiles_m, tiles_n, num_tiles;
   // peer mode: the N dimension is the concatenation of row shards owned by several GPUs; n-tiles are
@@ -415,6 +420,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] = apply_act(f[j], p.act);
           }
+          if (p.gate != nullptr) {
+            const __nv_bfloat16* gr = p.gate + static_cast<long long>(m % p.gate_rows) * p.ld_gate + n0;
+            if (n0 + 32 <= n_limit && (reinterpret_cast<uintptr_t>(gr) & 31) == 0) {
+#pragma unroll
+              for (int c2 = 0; c2 < 2; ++c2) {
+                float e[16];
+                ld_bf16x16(gr + c2 * 16, e);
+#pragma unroll
+                for (int d = 0; d < 16; ++d) f[c2 * 16 + d] *= e[d];
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + j < n_limit) f[j] *= __bfloat162float(gr[j]);
+            }
+          }
           if (res_tma) {
             // 32 columns = four 16-byte units of tile row q*32+lane in the swizzled 64-column block c/2
 #pragma unroll
@@ -602,12 +623,14 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
 // bias: fp32 [N] or null. residual: bf16 with leading dimension ldr / batch stride strideR, or null.
 // status: device pointer to a ubm::KernelStatus (16 bytes) or null.
 // cblk_*: blocked output addressing (see GemmParams); all zero for the plain [M][N] layout.  The blocked form
-// needs N to be a multiple of 32.
+// needs N to be a multiple of 32.  gate: optional bf16 [gate_rows][ld_gate] multiplied in before the residual
+// (C = act(alpha A.B^T + bias) * gate[m % gate_rows] + residual).
 extern "C" int ubm_gemm_bf16_ex(const void* A, const void* B, void* C, const void* bias, const void* residual, int M,
                                 int N, int K, int batch, long long lda, long long ldb, long long ldc, long long ldr,
                                 long long strideA, long long strideB, long long strideC, long long strideR,
                                 int mn_major, int out_fp32, int act, float alpha, long long cblk_hi,
-                                long long cblk_lo, long long cblk_col, void* status, void* stream) {
+                                long long cblk_lo, long long cblk_col, const void* gate, long long ld_gate,
+                                int gate_rows, void* status, void* stream) {
   using namespace ubm;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return UBM_ERR_ARGUMENT;
   if (cblk_col != 0 && ((N & 31) || residual != nullptr)) return UBM_ERR_ARGUMENT;
@@ -633,6 +656,9 @@ extern "C" int ubm_gemm_bf16_ex(const void* A, const void* B, void* C, const voi
   p.cblk_hi = cblk_hi;
   p.cblk_lo = cblk_lo;
   p.cblk_col = cblk_col;
+  p.gate = static_cast<const __nv_bfloat16*>(gate);
+  p.ld_gate = ld_gate;
+  p.gate_rows = gate_rows > 0 ? gate_rows : 1;
   p.status = static_cast<KernelStatus*>(status);
   if (batch == 1) {
     if (strideA == 0) strideA = mn_major ? (long long)K * lda : (long long)M * lda;
@@ -653,7 +679,7 @@ extern "C" int ubm_gemm_bf16(const void* A, const void* B, void* C, const void* 
                              long long strideA, long long strideB, long long strideC, long long strideR, int mn_major,
                              int out_fp32, int act, float alpha, void* status, void* stream) {
   return ubm_gemm_bf16_ex(A, B, C, bias, residual, M, N, K, batch, lda, ldb, ldc, ldr, strideA, strideB, strideC,
-                          strideR, mn_major, out_fp32, act, alpha, 0, 0, 0, status, stream);
+                          strideR, mn_major, out_fp32, act, alpha, 0, 0, 0, nullptr, 0, 0, status, stream);
 }
 
 // All-gather fused into the GEMM: C[b][m][col0_q + n] = sum_k A[b][m][k] * B_q[b][n][k] where B_q is the

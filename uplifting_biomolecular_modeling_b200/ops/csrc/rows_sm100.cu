@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(256) adaln_rows_kernel(const __nv_bfloat16* __
                                                          const __nv_bfloat16* __restrict__ scale,
                                                          const __nv_bfloat16* __restrict__ shift,
                                                          __nv_bfloat16* __restrict__ out, long long R, int C,
-                                                         long long cond_rows, float eps) {
+                                                         long long cond_rows, long long ld_cond, float eps) {
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   for (long long r = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); r < R;
@@ -155,11 +155,67 @@ __global__ void __launch_bounds__(256) adaln_rows_kernel(const __nv_bfloat16* __
     const float rstd = rsqrtf(fmaxf(sumsq / C - mu * mu, 0.f) + eps);
     for (int c = lane * 2; c < C; c += 64) {
       const __nv_bfloat162 p = *reinterpret_cast<const __nv_bfloat162*>(ar + c);
-      const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162*>(scale + rc * C + c);
-      const __nv_bfloat162 sh = *reinterpret_cast<const __nv_bfloat162*>(shift + rc * C + c);
+      const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162*>(scale + rc * ld_cond + c);
+      const __nv_bfloat162 sh = *reinterpret_cast<const __nv_bfloat162*>(shift + rc * ld_cond + c);
       const float y0 = sigmoidf_fast(__low2float(sc)) * ((__low2float(p) - mu) * rstd) + __low2float(sh);
       const float y1 = sigmoidf_fast(__high2float(sc)) * ((__high2float(p) - mu) * rstd) + __high2float(sh);
       *reinterpret_cast<__nv_bfloat162*>(out + r * C + c) = __floats2bfloat162_rn(y0, y1);
+    }
+  }
+}
+
+// The same with 16-byte accesses: a warp per row, the row (up to 1024 channels: four 8-channel chunks per
+// lane) stays in registers between the statistics and the output pass, so it is read once.
+template <int CHUNKS>
+__global__ void __launch_bounds__(256) adaln_rows_vec_kernel(const __nv_bfloat16* __restrict__ a,
+                                                             const __nv_bfloat16* __restrict__ scale,
+                                                             const __nv_bfloat16* __restrict__ shift,
+                                                             __nv_bfloat16* __restrict__ out, long long R, int C,
+                                                             long long cond_rows, long long ld_cond, float eps) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (long long r = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); r < R;
+       r += static_cast<long long>(gridDim.x) * warps_per_block) {
+    const __nv_bfloat16* ar = a + r * C;
+    const long long rc = r % cond_rows;
+    float x[CHUNKS][8];
+    float sum = 0.f, sumsq = 0.f;
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < C) {
+        const uint4 u = *reinterpret_cast<const uint4*>(ar + c);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          x[k][2 * j] = bf16_lo(w[j]);
+          x[k][2 * j + 1] = bf16_hi(w[j]);
+          sum += x[k][2 * j] + x[k][2 * j + 1];
+          sumsq += x[k][2 * j] * x[k][2 * j] + x[k][2 * j + 1] * x[k][2 * j + 1];
+        }
+      }
+    }
+    sum = warp_sum(sum);
+    sumsq = warp_sum(sumsq);
+    const float mu = sum / C;
+    const float rstd = rsqrtf(fmaxf(sumsq / C - mu * mu, 0.f) + eps);
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < C) {
+        const uint4 us = __ldg(reinterpret_cast<const uint4*>(scale + rc * ld_cond + c));
+        const uint4 uh = __ldg(reinterpret_cast<const uint4*>(shift + rc * ld_cond + c));
+        const uint32_t ws[4] = {us.x, us.y, us.z, us.w};
+        const uint32_t wh[4] = {uh.x, uh.y, uh.z, uh.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float y0 = sigmoidf_fast(bf16_lo(ws[j])) * ((x[k][2 * j] - mu) * rstd) + bf16_lo(wh[j]);
+          const float y1 = sigmoidf_fast(bf16_hi(ws[j])) * ((x[k][2 * j + 1] - mu) * rstd) + bf16_hi(wh[j]);
+          o[j] = pack_bf16x2(y0, y1);
+        }
+        *reinterpret_cast<uint4*>(out + r * C + c) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
     }
   }
 }
@@ -169,12 +225,12 @@ __global__ void __launch_bounds__(256) gate_residual_kernel(const __nv_bfloat16*
                                                             const __nv_bfloat16* __restrict__ gate,
                                                             const __nv_bfloat16* __restrict__ res,
                                                             __nv_bfloat16* __restrict__ out, long long n2, int C2,
-                                                            long long cond_rows) {
+                                                            long long cond_rows, long long ld_gate2) {
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n2;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long r = i / C2;
     const int c = static_cast<int>(i - r * C2);
-    const long long gi = (r % cond_rows) * C2 + c;
+    const long long gi = (r % cond_rows) * ld_gate2 + c;
     const __nv_bfloat162 xv = reinterpret_cast<const __nv_bfloat162*>(x)[i];
     const __nv_bfloat162 gv = reinterpret_cast<const __nv_bfloat162*>(gate)[gi];
     float y0 = sigmoidf_fast(__low2float(gv)) * __low2float(xv);
@@ -202,6 +258,29 @@ __global__ void __launch_bounds__(256) swiglu_rows_kernel(const __nv_bfloat16* _
     reinterpret_cast<__nv_bfloat162*>(out + r * Hd)[c] =
         __floats2bfloat162_rn(siluf_fast(__low2float(av)) * __low2float(bv),
                               siluf_fast(__high2float(av)) * __high2float(bv));
+  }
+}
+
+// x: [R][3*Hd] = [u | g | w] -> out [R][Hd] = silu(u) * g * w   (16-byte accesses; Hd a multiple of 8)
+__global__ void __launch_bounds__(256) swiglu3_rows_kernel(const __nv_bfloat16* __restrict__ x,
+                                                           __nv_bfloat16* __restrict__ out, long long R, int Hd) {
+  const int h8 = Hd >> 3;
+  const long long n8 = R * h8;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / h8;
+    const int c = static_cast<int>(i - r * h8) * 8;
+    const __nv_bfloat16* row = x + r * 3 * Hd;
+    const uint4 uu = *reinterpret_cast<const uint4*>(row + c);
+    const uint4 ug = *reinterpret_cast<const uint4*>(row + Hd + c);
+    const uint4 uw = *reinterpret_cast<const uint4*>(row + 2 * Hd + c);
+    const uint32_t a[4] = {uu.x, uu.y, uu.z, uu.w}, g[4] = {ug.x, ug.y, ug.z, ug.w}, w[4] = {uw.x, uw.y, uw.z, uw.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      o[j] = pack_bf16x2(siluf_fast(bf16_lo(a[j])) * bf16_lo(g[j]) * bf16_lo(w[j]),
+                         siluf_fast(bf16_hi(a[j])) * bf16_hi(g[j]) * bf16_hi(w[j]));
+    *reinterpret_cast<uint4*>(out + r * Hd + c) = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
@@ -271,26 +350,55 @@ extern "C" int ubm_pair_head_bias(const void* z, const void* w, const void* cols
   return UBM_OK;
 }
 
+// scale / shift: bf16 rows of leading dimension ld_cond (elements), reused cyclically every cond_rows rows.
 extern "C" int ubm_adaln_rows(const void* a, const void* scale, const void* shift, void* out, long long R, int C,
-                              long long cond_rows, float eps, void* stream) {
+                              long long cond_rows, long long ld_cond, float eps, void* stream) {
   using namespace ubm;
-  if (R <= 0 || C <= 0 || (C & 1) || cond_rows <= 0) return UBM_ERR_ARGUMENT;
-  adaln_rows_kernel<<<grid_for(R, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(scale),
-      static_cast<const __nv_bfloat16*>(shift), static_cast<__nv_bfloat16*>(out), R, C, cond_rows, eps);
+  if (R <= 0 || C <= 0 || (C & 1) || cond_rows <= 0 || ld_cond < C) return UBM_ERR_ARGUMENT;
+  const __nv_bfloat16* aa = static_cast<const __nv_bfloat16*>(a);
+  const __nv_bfloat16* sc = static_cast<const __nv_bfloat16*>(scale);
+  const __nv_bfloat16* sh = static_cast<const __nv_bfloat16*>(shift);
+  __nv_bfloat16* oo = static_cast<__nv_bfloat16*>(out);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool vec = (C % 8) == 0 && C <= 1024 && (ld_cond % 8) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(scale) |
+                     reinterpret_cast<uintptr_t>(shift) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  const int grid = grid_for(R, 8);
+  if (vec && C <= 256) {
+    adaln_rows_vec_kernel<1><<<grid, 256, 0, st>>>(aa, sc, sh, oo, R, C, cond_rows, ld_cond, eps);
+  } else if (vec && C <= 512) {
+    adaln_rows_vec_kernel<2><<<grid, 256, 0, st>>>(aa, sc, sh, oo, R, C, cond_rows, ld_cond, eps);
+  } else if (vec && C <= 768) {
+    adaln_rows_vec_kernel<3><<<grid, 256, 0, st>>>(aa, sc, sh, oo, R, C, cond_rows, ld_cond, eps);
+  } else if (vec) {
+    adaln_rows_vec_kernel<4><<<grid, 256, 0, st>>>(aa, sc, sh, oo, R, C, cond_rows, ld_cond, eps);
+  } else {
+    adaln_rows_kernel<<<grid, 256, 0, st>>>(aa, sc, sh, oo, R, C, cond_rows, ld_cond, eps);
+  }
   UBM_CHECK_LAUNCH("adaln_rows_kernel");
   return UBM_OK;
 }
 
 extern "C" int ubm_gate_residual(const void* x, const void* gate, const void* res, void* out, long long R, int C,
-                                 long long cond_rows, void* stream) {
+                                 long long cond_rows, long long ld_gate, void* stream) {
   using namespace ubm;
-  if (R <= 0 || C <= 0 || (C & 1) || cond_rows <= 0) return UBM_ERR_ARGUMENT;
+  if (R <= 0 || C <= 0 || (C & 1) || cond_rows <= 0 || ld_gate < C || (ld_gate & 1)) return UBM_ERR_ARGUMENT;
   const long long n2 = R * (C / 2);
   gate_residual_kernel<<<grid_for(n2, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gate),
-      static_cast<const __nv_bfloat16*>(res), static_cast<__nv_bfloat16*>(out), n2, C / 2, cond_rows);
+      static_cast<const __nv_bfloat16*>(res), static_cast<__nv_bfloat16*>(out), n2, C / 2, cond_rows, ld_gate / 2);
   UBM_CHECK_LAUNCH("gate_residual_kernel");
+  return UBM_OK;
+}
+
+extern "C" int ubm_swiglu3_rows(const void* x, void* out, long long R, int Hd, void* stream) {
+  using namespace ubm;
+  if (R <= 0 || Hd <= 0 || (Hd & 7) ||
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15))
+    return UBM_ERR_ARGUMENT;
+  swiglu3_rows_kernel<<<grid_for(R * (Hd / 8), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), R, Hd);
+  UBM_CHECK_LAUNCH("swiglu3_rows_kernel");
   return UBM_OK;
 }
 

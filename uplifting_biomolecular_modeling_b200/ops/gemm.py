@@ -23,8 +23,11 @@ def _as3(t: torch.Tensor) -> torch.Tensor:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, mn_major: bool = False, bias: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, act: Optional[str] = None, alpha: float = 1.0,
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
-         c_blocked: Optional[tuple] = None) -> torch.Tensor:
-    """C = act(alpha * A.B^T + bias) + residual.
+         c_blocked: Optional[tuple] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C = act(alpha * A.B^T + bias) * gate + residual.
+
+    ``gate`` (bf16 [rows, N], rows dividing M, row stride free): row m is multiplied by gate row m % rows -
+    a conditioning gate shared by the samples stacked along M.
 
     ``c_blocked=(hi, lo, col)`` (with ``out`` given, N a multiple of 32, batch 1) stores element (m, n) at
     ``out.data_ptr + (m // 32) * hi + (m % 32) * lo + (n // 32) * col + n % 32`` elements: the product of two
@@ -71,6 +74,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, mn_major: bool = False, bias: Opti
     if bias is not None and bias.dtype != torch.float32:
         bias = bias.float()
     st = native.status_tensor(a.device)
+    if gate is not None:
+        if gate.dtype != torch.bfloat16 or gate.dim() != 2 or gate.shape[1] != N or gate.stride(1) != 1 or batch != 1:
+            raise ValueError("gate must be bf16 [rows, N] with contiguous rows (batch 1)")
     cb = c_blocked if c_blocked is not None else (0, 0, 0)
     rc = native.lib().ubm_gemm_bf16_ex(
         native.ptr(a3), native.ptr(b3), native.ptr(out3), native.ptr(bias), native.ptr(res3),
@@ -81,7 +87,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, mn_major: bool = False, bias: Opti
         out3.stride(0) if batch > 1 and c_blocked is None else 0,
         0 if res3 is None or batch == 1 else res3.stride(0),
         1 if mn_major else 0, 1 if out3.dtype == torch.float32 else 0, ACT[act], float(alpha),
-        int(cb[0]), int(cb[1]), int(cb[2]), native.ptr(st), native.current_stream(a.device))
+        int(cb[0]), int(cb[1]), int(cb[2]), native.ptr(gate), 0 if gate is None else gate.stride(0),
+        0 if gate is None else gate.shape[0], native.ptr(st), native.current_stream(a.device))
     native.check(rc, "ubm_gemm_bf16_ex")
     if c_blocked is not None:
         return out

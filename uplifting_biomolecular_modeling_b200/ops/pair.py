@@ -251,9 +251,12 @@ class ApbPacked:
         return cls(wqkv, bqkv, wg, wo.view(w_o.shape[0], heads * Dp).to(torch.bfloat16).contiguous(), heads, Dp)
 
 
-def apb_fused(x: torch.Tensor, w: ApbPacked, bias_planes: torch.Tensor, ldb: int) -> torch.Tensor:
+def apb_fused(x: torch.Tensor, w: ApbPacked, bias_planes: torch.Tensor, ldb: int,
+              out_gate: Optional[torch.Tensor] = None, out_residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Gated attention with pair bias on rows x: bf16 [B, N, c]; bias_planes: bf16 [H, N, ldb] holding
-    log2(e) * bias (shared by the B rows).  Returns proj_o(sigmoid(proj_g x) * attention) as [B, N, c]."""
+    log2(e) * bias (shared by the B rows).  Returns proj_o(sigmoid(proj_g x) * attention) as [B, N, c];
+    with ``out_gate`` ([N, c], shared by the B rows) and ``out_residual`` ([B*N, c]) the output projection's
+    epilogue returns residual + gate * projection."""
     B, N, c = x.shape
     HD = w.H * w.Dp
     x2 = x.reshape(B * N, c)
@@ -262,7 +265,7 @@ def apb_fused(x: torch.Tensor, w: ApbPacked, bias_planes: torch.Tensor, ldb: int
     o = torch.empty((B * N, HD), dtype=torch.bfloat16, device=x.device)
     attention(qkv[:, :HD], qkv[:, HD:2 * HD], qkv[:, 2 * HD:], bias_planes, g, o, rows=B, Nq=N, Nk=N, H=w.H,
               D=w.Dp, ldb=ldb, ld_in=3 * HD)
-    return _gemm.gemm(o, w.wo).view(B, N, -1)
+    return _gemm.gemm(o, w.wo, gate=out_gate, residual=out_residual).view(B, N, -1)
 
 
 def triangle_attention_fused(z: torch.Tensor, w: TriattPacked, starting: bool, residual: bool = True,
@@ -303,7 +306,9 @@ native.declare("ubm_window_attention_tc", [c_void_p] * 6 + [c_int, c_int, c_int,
 WINDOW_KERNEL = "tc"     # "tc": tcgen05 kernel (four windows per CTA); "simt": CUDA-core kernel (one window per CTA)
 
 
-def window_attention_fused(x: torch.Tensor, w: ApbPacked, bias: Optional[torch.Tensor]) -> torch.Tensor:
+def window_attention_fused(x: torch.Tensor, w: ApbPacked, bias: Optional[torch.Tensor],
+                           out_gate: Optional[torch.Tensor] = None,
+                           out_residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Gated atom attention in 32 x 128 windows.  x: bf16 [B, A, c] (A a multiple of 32); w: packed projections with
     4 x 32 heads; bias: bf16 [1 or B, H, A/32, 32, 128] already multiplied by log2(e).  Returns [B, A, c]."""
     B, A, c = x.shape
@@ -328,4 +333,4 @@ def window_attention_fused(x: torch.Tensor, w: ApbPacked, bias: Optional[torch.T
                                                native.ptr(o), B, A, w.H, 3 * HD,
                                                1 if bias is None else bias.shape[0], native.current_stream(x.device))
         native.check(rc, "ubm_window_attention")
-    return _gemm.gemm(o, w.wo).view(B, A, -1)
+    return _gemm.gemm(o, w.wo, gate=out_gate, residual=out_residual).view(B, A, -1)

@@ -13,9 +13,10 @@ from .native import c_float, c_int, c_ll, c_void_p
 
 native.declare("ubm_layernorm_rows", [c_void_p] * 4 + [c_ll, c_int, c_float, c_int, c_int, c_void_p])
 native.declare("ubm_pair_head_bias", [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_void_p])
-native.declare("ubm_adaln_rows", [c_void_p] * 4 + [c_ll, c_int, c_ll, c_float, c_void_p])
-native.declare("ubm_gate_residual", [c_void_p] * 4 + [c_ll, c_int, c_ll, c_void_p])
+native.declare("ubm_adaln_rows", [c_void_p] * 4 + [c_ll, c_int, c_ll, c_ll, c_float, c_void_p])
+native.declare("ubm_gate_residual", [c_void_p] * 4 + [c_ll, c_int, c_ll, c_ll, c_void_p])
 native.declare("ubm_swiglu_rows", [c_void_p] * 2 + [c_ll, c_int, c_void_p])
+native.declare("ubm_swiglu3_rows", [c_void_p] * 2 + [c_ll, c_int, c_void_p])
 
 _DT = {torch.bfloat16: 0, torch.float32: 1}
 
@@ -71,24 +72,48 @@ def pair_head_bias(z: torch.Tensor, ln_w, ln_b, w, scale: float = 1.0, transpose
     return out[:, :, :N]
 
 
+def _cond2d(t: torch.Tensor, C: int) -> torch.Tensor:
+    """Conditioning rows as a 2-D view [rows, C] whose rows may be strided (a column slice of a wider buffer)."""
+    t2 = t.reshape(-1, C) if t.is_contiguous() else t.squeeze(0) if t.dim() == 3 and t.shape[0] == 1 else t
+    if t2.dim() != 2 or t2.shape[1] != C or t2.stride(1) != 1:
+        t2 = t.reshape(-1, C).contiguous()
+    return t2
+
+
 def adaln_rows(a: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
-    """sigmoid(scale) * LN_noaffine(a) + shift; scale/shift rows are reused cyclically over a's rows."""
+    """sigmoid(scale) * LN_noaffine(a) + shift; scale/shift rows are reused cyclically over a's rows and may be
+    column slices of one wider buffer (equal row strides)."""
     C = a.shape[-1]
     R = a.numel() // C
     out = torch.empty_like(a)
-    rc = native.lib().ubm_adaln_rows(native.ptr(a), native.ptr(scale), native.ptr(shift), native.ptr(out), R, C,
-                                     scale.numel() // C, float(eps), native.current_stream(a.device))
+    sc, sh = _cond2d(scale, C), _cond2d(shift, C)
+    if sc.stride(0) != sh.stride(0) or sc.shape[0] != sh.shape[0]:
+        sc, sh = sc.contiguous(), sh.contiguous()
+    rc = native.lib().ubm_adaln_rows(native.ptr(a), native.ptr(sc), native.ptr(sh), native.ptr(out), R, C,
+                                     sc.shape[0], sc.stride(0), float(eps), native.current_stream(a.device))
     native.check(rc, "ubm_adaln_rows")
     return out
 
 
 def gate_residual(x: torch.Tensor, gate: torch.Tensor, res: Optional[torch.Tensor]) -> torch.Tensor:
+    """res + sigmoid(gate) * x; gate rows reused cyclically, possibly a column slice of a wider buffer."""
     C = x.shape[-1]
     R = x.numel() // C
     out = torch.empty_like(x)
-    rc = native.lib().ubm_gate_residual(native.ptr(x), native.ptr(gate), native.ptr(res), native.ptr(out), R, C,
-                                        gate.numel() // C, native.current_stream(x.device))
+    g = _cond2d(gate, C)
+    rc = native.lib().ubm_gate_residual(native.ptr(x), native.ptr(g), native.ptr(res), native.ptr(out), R, C,
+                                        g.shape[0], g.stride(0), native.current_stream(x.device))
     native.check(rc, "ubm_gate_residual")
+    return out
+
+
+def swiglu3_rows(x: torch.Tensor) -> torch.Tensor:
+    """x: [.., 3*Hd] = [u | g | w] -> silu(u) * g * w."""
+    Hd = x.shape[-1] // 3
+    R = x.numel() // (3 * Hd)
+    out = torch.empty(x.shape[:-1] + (Hd,), dtype=x.dtype, device=x.device)
+    rc = native.lib().ubm_swiglu3_rows(native.ptr(x), native.ptr(out), R, Hd, native.current_stream(x.device))
+    native.check(rc, "ubm_swiglu3_rows")
     return out
 
 
