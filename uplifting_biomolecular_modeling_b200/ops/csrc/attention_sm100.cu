@@ -28,6 +28,10 @@ namespace ubm {
 
 constexpr int kATile = 128;  // queries per CTA
 constexpr float kNegBig = -1.0e30f;
+#ifndef UBM_ATTN_POLY_EXP
+#define UBM_ATTN_POLY_EXP 1
+#endif
+constexpr bool kPolyExp = UBM_ATTN_POLY_EXP != 0;   // a quarter of the softmax exponentials as a polynomial
 
 // D = head dimension (32 or 64), TK = keys per step (128 for D = 32, 64 for D = 64 so that two rows,
 // two stages and the P tiles still fit in shared memory).
@@ -431,22 +435,25 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const float m_new = fmaxf(m, mt);
         const float alpha = fast_exp2(m - m_new);
         if (quad == 0 && lane == 0) ATT_STAMP(1 + r_in, g, 3);
-        float psv[4] = {0.f, 0.f, 0.f, 0.f};
+        // differences and partial sums as packed two-wide fp32 operations: one issue slot per two values
+        float2 ps01 = make_float2(0.f, 0.f), ps23 = make_float2(0.f, 0.f);
+        const float2 neg_m = make_float2(-m_new, -m_new);
         uint32_t pk[TK / 2];
 #pragma unroll
         for (int k = 0; k < TK; k += 4) {
-          const float p0 = fast_exp2(t[k] - m_new);
-          const float p1 = fast_exp2(t[k + 1] - m_new);
-          const float p2 = fast_exp2(t[k + 2] - m_new);
-          const float p3 = fast_exp2(t[k + 3] - m_new);
-          psv[0] += p0;
-          psv[1] += p1;
-          psv[2] += p2;
-          psv[3] += p3;
-          pk[k >> 1] = pack_bf16x2(p0, p1);
-          pk[(k >> 1) + 1] = pack_bf16x2(p2, p3);
+          const float2 d01 = __fadd2_rn(make_float2(t[k], t[k + 1]), neg_m);
+          const float2 d23 = __fadd2_rn(make_float2(t[k + 2], t[k + 3]), neg_m);
+          float2 e01, e23;
+          e01.x = fast_exp2(d01.x);
+          e01.y = fast_exp2(d01.y);
+          e23.x = fast_exp2(d23.x);
+          e23.y = (kPolyExp && D == 64) ? poly_exp2(d23.y) : fast_exp2(d23.y);
+          ps01 = __fadd2_rn(ps01, e01);
+          ps23 = __fadd2_rn(ps23, e23);
+          pk[k >> 1] = pack_bf16x2(e01.x, e01.y);
+          pk[(k >> 1) + 1] = pack_bf16x2(e23.x, e23.y);
         }
-        const float psum = (psv[0] + psv[1]) + (psv[2] + psv[3]);
+        const float psum = (ps01.x + ps01.y) + (ps23.x + ps23.y);
         l = l * alpha + psum;
         m = m_new;
         if (quad == 0 && lane == 0) ATT_STAMP(1 + r_in, g, 4);

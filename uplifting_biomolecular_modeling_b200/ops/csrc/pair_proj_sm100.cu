@@ -53,6 +53,19 @@ struct PairProjParams {
   int num_tiles;
 };
 
+// Optional timeline (build with -DUBM_PP_TIMELINE): CTA 0 stamps clock64 at fixed points of its first tiles
+// into a global buffer [4 roles][kPPTlTiles][8 events] (roles: producer, MMA issuer, epilogue group 0, 1).
+#ifdef UBM_PP_TIMELINE
+constexpr int kPPTlTiles = 32;
+__device__ long long g_pp_timeline[4 * kPPTlTiles * 8];
+#define PP_STAMP(role, tile, ev)                                                                              \
+  do {                                                                                                        \
+    if (blockIdx.x == 0 && (tile) < kPPTlTiles) g_pp_timeline[((role) * kPPTlTiles + (tile)) * 8 + (ev)] = clock64(); \
+  } while (0)
+#else
+#define PP_STAMP(role, tile, ev) do { } while (0)
+#endif
+
 template <int MODE>
 __global__ void __launch_bounds__(320, 1)
 pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, PairProjParams p) {
@@ -118,8 +131,11 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           tma_load_2d(sW + kb * 65536 + h * 32768, &tmW, w_full, kb * 64, h * 256);
       int stage = 0;
       uint32_t phase = 0;
-      for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+      int lt = 0;
+      for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++lt) {
+        PP_STAMP(0, lt, 0);
         mbar_wait(&x_empty[stage], phase ^ 1u, ws, 11, stage);
+        PP_STAMP(0, lt, 1);
         if (*abort_flag) break;
         uint8_t* dst = sX + stage * kPPXBytes;
         mbar_expect_tx(&x_full[stage], kPPXBytes);
@@ -140,13 +156,17 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       uint32_t acc_phase = 0;
-      for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+      int lt = 0;
+      for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++lt) {
+        if (lane == 0) PP_STAMP(1, lt, 0);
         mbar_wait(&x_full[stage], phase, ws, 13, stage);
+        if (lane == 0) PP_STAMP(1, lt, 1);
         tc_fence_after_sync();
         const uint32_t xa = smem_u32(sX + stage * kPPXBytes);
         const uint32_t wa = smem_u32(sW);
         for (int h = 0; h < 2; ++h) {
           mbar_wait(&acc_empty[h], acc_phase ^ 1u, ws, 14, h);
+          if (lane == 0) PP_STAMP(1, lt, 2 + 2 * h);
           tc_fence_after_sync();
           const uint64_t ad0 = umma_smem_desc(xa, 16, 1024, kSwizzle128);
           const uint64_t bd0 = umma_smem_desc(wa + h * 32768, 16, 1024, kSwizzle128);
@@ -161,6 +181,7 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             umma_commit(&acc_full[h]);
           }
           __syncwarp();
+          if (lane == 0) PP_STAMP(1, lt, 3 + 2 * h);
         }
         if (leader) umma_commit(&x_empty[stage]);
         __syncwarp();
@@ -179,11 +200,14 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     int stage = 0;
     uint32_t phase = 0;
     uint32_t acc_phase = 0;
-    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+    int lt = 0;
+    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++lt) {
       const long long r = static_cast<long long>(t) * kPPRows + row_in_tile;
       const bool row_ok = r < p.R;
       // ---- row statistics (and head bias) from the shared-memory tile
+      if (q == 0 && lane == 0) PP_STAMP(2 + grp, lt, 0);
       mbar_wait(&x_full[stage], phase, ws, 15, stage);
+      if (q == 0 && lane == 0) PP_STAMP(2 + grp, lt, 1);
       const uint8_t* xs = sX + stage * kPPXBytes;
       float sum = 0.f, sumsq = 0.f;
       float hb[kPPMaxHeads / 2];
@@ -249,7 +273,9 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       }
 
       // ---- accumulator half of this group
+      if (q == 0 && lane == 0) PP_STAMP(2 + grp, lt, 2);
       mbar_wait(&acc_full[grp], acc_phase, ws, 16, grp);
+      if (q == 0 && lane == 0) PP_STAMP(2 + grp, lt, 3);
       tc_fence_after_sync();
       const uint32_t tbase = tmem_addr(tmem_base, q, grp * 256);
       {
@@ -257,26 +283,38 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         const long long orow = p.transpose_out ? (static_cast<long long>(pk) * p.N + pi) : r;
         __nv_bfloat16* o0 = (grp == 0 ? p.q : p.v) + orow * 128;
         __nv_bfloat16* o1 = (grp == 0 ? p.k : p.g) + orow * 128;
-#pragma unroll 1
-        for (int c0 = 0; c0 < 256; c0 += 32) {
-          uint32_t av[32];
-          tmem_ld32(tbase + c0, av);
-          tmem_ld_wait();
-          if (row_ok) {
-            const bool gate = (grp == 1) && (c0 >= 128);
-            float f[32];
+        const float2 a2 = make_float2(rstd, rstd);
+        const float2 b2 = make_float2(-mu * rstd, -mu * rstd);
+        // 32-column chunks, the tensor-memory load of the next chunk in flight while this one is processed;
+        // the chunk body exists twice (ping-pong registers), not eight times
+        auto chunk = [&](const uint32_t (&av)[32], const int c0) {
+          if (!row_ok) return;
+          if (q == 0 && lane == 0 && c0 == 32) PP_STAMP(2 + grp, lt, 5);
+          float f[32];
+          ln_fold32(av, a2, b2, sColsum + grp * 256 + c0, sColbias + grp * 256 + c0, f);
+          if (grp == 1 && c0 >= 128) {      // gate columns (warp-uniform)
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int col = grp * 256 + c0 + j;
-              float val = rstd * (__uint_as_float(av[j]) - mu * sColsum[col]) + sColbias[col];
-              f[j] = gate ? sigmoidf_fast(val) : val;
-            }
-            __nv_bfloat16* dst = (c0 < 128 ? o0 + c0 : o1 + (c0 - 128));
-            st_bf16x16(dst, f);
-            st_bf16x16(dst + 16, f + 16);
+            for (int j = 0; j < 32; ++j) f[j] = sigmoidf_fast(f[j]);
           }
+          if (q == 0 && lane == 0 && c0 == 32) PP_STAMP(2 + grp, lt, 6);
+          __nv_bfloat16* dst = (c0 < 128 ? o0 + c0 : o1 + (c0 - 128));
+          st_bf16x16(dst, f);
+          st_bf16x16(dst + 16, f + 16);
+          if (q == 0 && lane == 0 && c0 == 32) PP_STAMP(2 + grp, lt, 7);
+        };
+        uint32_t va[32], vb[32];
+        tmem_ld32(tbase, va);
+#pragma unroll 1
+        for (int c0 = 0; c0 < 256; c0 += 64) {
+          tmem_ld_wait();
+          tmem_ld32(tbase + c0 + 32, vb);
+          chunk(va, c0);
+          tmem_ld_wait();
+          if (c0 + 64 < 256) tmem_ld32(tbase + c0 + 64, va);
+          chunk(vb, c0 + 32);
         }
       }
+      if (q == 0 && lane == 0) PP_STAMP(2 + grp, lt, 4);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[grp]);
@@ -356,6 +394,12 @@ extern "C" int ubm_triatt_proj_rows(const void* z, const void* w, const void* co
   p.status = static_cast<KernelStatus*>(status);
   return launch_pair_proj<MODE_TRIATT>(z, w, p, static_cast<cudaStream_t>(stream));
 }
+
+#ifdef UBM_PP_TIMELINE
+extern "C" int ubm_pair_proj_read_timeline(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, ubm::g_pp_timeline, sizeof(ubm::g_pp_timeline)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 extern "C" int ubm_triatt_proj(const void* z, const void* w, const void* colsum, const void* colbias, const void* wb,
                                const void* wb_colsum, const void* wb_colbias, void* q, void* k, void* v, void* g,

@@ -476,6 +476,46 @@ __device__ __forceinline__ void ld_bf16x16(const __nv_bfloat16* src, float* e) {
   }
 }
 
+// LayerNorm folded into a GEMM, applied to two adjacent accumulator columns in two packed instructions:
+//   out = rstd * (acc - mu * colsum) + colbias = acc * a + (b * colsum + colbias),  a = rstd, b = -mu * rstd
+__device__ __forceinline__ float2 ln_fold2(uint32_t acc0, uint32_t acc1, float2 a2, float2 b2, float cs0, float cs1,
+                                           float cb0, float cb1) {
+  return __ffma2_rn(make_float2(__uint_as_float(acc0), __uint_as_float(acc1)), a2,
+                    __ffma2_rn(b2, make_float2(cs0, cs1), make_float2(cb0, cb1)));
+}
+// 32 accumulator columns at once; cs / cb point at 16-byte aligned shared-memory constants of those columns
+__device__ __forceinline__ void ln_fold32(const uint32_t (&acc)[32], float2 a2, float2 b2, const float* cs,
+                                          const float* cb, float (&out)[32]) {
+  const float4* cs4 = reinterpret_cast<const float4*>(cs);
+  const float4* cb4 = reinterpret_cast<const float4*>(cb);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float4 s4 = cs4[j], b4 = cb4[j];
+    const float2 v01 = ln_fold2(acc[4 * j], acc[4 * j + 1], a2, b2, s4.x, s4.y, b4.x, b4.y);
+    const float2 v23 = ln_fold2(acc[4 * j + 2], acc[4 * j + 3], a2, b2, s4.z, s4.w, b4.z, b4.w);
+    out[4 * j] = v01.x;
+    out[4 * j + 1] = v01.y;
+    out[4 * j + 2] = v23.x;
+    out[4 * j + 3] = v23.y;
+  }
+}
+
+// 2^x for x <= 0 on the FMA and ALU pipes (no special-function instruction): split x into a rounded integer n
+// (magic-number add; the integer lands in the low mantissa bits) and f = x - n in [-0.5, 0.5], evaluate a
+// degree-3 polynomial of 2^f (largest relative error 7.5e-5, far inside bf16 resolution) and add n to the
+// exponent field.  Measured in the attention softmax: it pays for head dimension 64 (one exponential in four
+// moved off the special-function unit: 0.128 -> 0.115 ms together with packed adds) and costs time for head
+// dimension 32, whose loop is short of issue slots rather than of special-function throughput.
+__device__ __forceinline__ float poly_exp2(float x) {
+  x = fmaxf(x, -125.0f);
+  const float t = x + 12582912.0f;
+  const float f = x - (t - 12582912.0f);
+  float p = fmaf(f, 0.0551716685f, 0.2426111251f);
+  p = fmaf(p, f, 0.6932609677f);
+  p = fmaf(p, f, 0.9999280572f);
+  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
+}
+
 // three-input maximum (one instruction on sm_100)
 __device__ __forceinline__ float max3f(float a, float b, float c) {
   float r;

@@ -242,6 +242,8 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
       const float mu = sum * (1.f / kTRC);
       const float var = fmaxf(sumsq * (1.f / kTRC) - mu * mu, 0.f);
       const float rstd = rsqrtf(var + 1e-5f);
+      const float2 a2 = make_float2(rstd, rstd);
+      const float2 b2 = make_float2(-mu * rstd, -mu * rstd);
 
       for (int h = 0; h < nch; ++h, ++g) {
         const int b = g & 1;
@@ -264,17 +266,14 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(&ab_empty[b]);
           }
+          float fa[32], fb[32];
+          ln_fold32(av, a2, b2, cs + half * 32, cb + half * 32, fa);
+          ln_fold32(bv, a2, b2, cs + 64 + half * 32, cb + 64 + half * 32, fb);
 #pragma unroll
           for (int m = 0; m < 32; m += 2) {
-            float hv[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int col = half * 32 + m + e;
-              const float a = rstd * (__uint_as_float(av[m + e]) - mu * cs[col]) + cb[col];
-              const float bb = rstd * (__uint_as_float(bv[m + e]) - mu * cs[64 + col]) + cb[64 + col];
-              hv[e] = siluf_fast(a) * bb;
-            }
-            packed[half * 16 + (m >> 1)] = pack_bf16x2(hv[0], hv[1]);
+            const float2 hv = __fmul2_rn(make_float2(siluf_fast(fa[m]), siluf_fast(fa[m + 1])),
+                                         make_float2(fb[m], fb[m + 1]));
+            packed[half * 16 + (m >> 1)] = pack_bf16x2(hv.x, hv.y);
           }
         }
         mbar_wait(&h_empty[b], ph ^ 1u, ws, 40, b);

@@ -239,13 +239,17 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         tmem_ld32(tG + c0, gv);
         tmem_ld_wait();
         if (row_ok) {
-          float f[32];
+          float f[32], fg[32];
+          const int cb0 = grp * 64 + c0;
+          ln_fold32(ov, make_float2(rsx, rsx), make_float2(-mux * rsx, -mux * rsx), sConst + cb0, sConst + 128 + cb0, f);
+          ln_fold32(gv, make_float2(rsz, rsz), make_float2(-muz * rsz, -muz * rsz), sConst + 256 + cb0,
+                    sConst + 384 + cb0, fg);
 #pragma unroll
-          for (int m = 0; m < 32; ++m) {
-            const int c = grp * 64 + c0 + m;
-            const float o = rsx * (__uint_as_float(ov[m]) - mux * sConst[c]) + sConst[128 + c];
-            const float g = rsz * (__uint_as_float(gv[m]) - muz * sConst[256 + c]) + sConst[384 + c];
-            f[m] = o * sigmoidf_fast(g);
+          for (int m = 0; m < 32; m += 2) {
+            const float2 v = __fmul2_rn(make_float2(f[m], f[m + 1]),
+                                        make_float2(sigmoidf_fast(fg[m]), sigmoidf_fast(fg[m + 1])));
+            f[m] = v.x;
+            f[m + 1] = v.y;
           }
           if (p.add_residual) {
             // residual from the z tile in shared memory: channels grp*64 + c0 .. +31

@@ -161,6 +161,8 @@ trimul_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     const int ch = q * 32 + lane;     // output channel of this thread; also the tile row it takes statistics of
     const float cs_v = p.colsum[grp * 256 + ch], cb_v = p.colbias[grp * 256 + ch];
     const float cs_g = p.colsum[grp * 256 + 128 + ch], cb_g = p.colbias[grp * 256 + 128 + ch];
+    const float2 csv2 = make_float2(cs_v, cs_v), cbv2 = make_float2(cb_v, cb_v);
+    const float2 csg2 = make_float2(cs_g, cs_g), cbg2 = make_float2(cb_g, cb_g);
     int stage = 0;
     uint32_t phase = 0;
     uint32_t acc_phase = 0;
@@ -235,11 +237,19 @@ trimul_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           const float nmv[4] = {nm.x, nm.y, nm.z, nm.w};
           const float mkv[4] = {mk.x, mk.y, mk.z, mk.w};
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
+          for (int e = 0; e < 4; e += 2) {
+            // two adjacent s at a time in packed fp32 instructions
             const int si = j4 * 4 + e;
-            const float val = fmaf(__uint_as_float(v[si]), rsv[e], fmaf(nmv[e], cs_v, cb_v));
-            const float gt = fmaf(__uint_as_float(g[si]), rsv[e], fmaf(nmv[e], cs_g, cb_g));
-            o[si] = val * (mkv[e] * sigmoidf_fast(gt));
+            const float2 rs2 = make_float2(rsv[e], rsv[e + 1]);
+            const float2 nm2 = make_float2(nmv[e], nmv[e + 1]);
+            const float2 val = __ffma2_rn(make_float2(__uint_as_float(v[si]), __uint_as_float(v[si + 1])), rs2,
+                                          __ffma2_rn(nm2, csv2, cbv2));
+            const float2 gt = __ffma2_rn(make_float2(__uint_as_float(g[si]), __uint_as_float(g[si + 1])), rs2,
+                                         __ffma2_rn(nm2, csg2, cbg2));
+            const float2 sg = make_float2(mkv[e] * sigmoidf_fast(gt.x), mkv[e + 1] * sigmoidf_fast(gt.y));
+            const float2 ov = __fmul2_rn(val, sg);
+            o[si] = ov.x;
+            o[si + 1] = ov.y;
           }
         }
         uint4 u[2];
