@@ -174,3 +174,22 @@ def test_window_attention_matches_reference(A, kernel, monkeypatch):
     native.raise_on_status("cuda", "window attention")
     err = ((out.float() - ref).abs().mean() / ref.abs().mean()).item()
     assert err < 4e-2, err
+
+
+def test_segment_mean_and_gather_rows():
+    from uplifting_biomolecular_modeling_b200.models import diffusion
+    from uplifting_biomolecular_modeling_b200.ops import rows
+    g = torch.Generator(device="cuda").manual_seed(11)
+    B, N, C = 3, 37, 768
+    counts = torch.randint(1, 9, (N,), generator=torch.Generator().manual_seed(1))
+    a2t = torch.repeat_interleave(torch.arange(N), counts).cuda()
+    A = a2t.shape[0]
+    t = torch.randn(B, A, C, device="cuda", generator=g).bfloat16()
+    ref = diffusion.segment_mean(t, a2t, N, fused=False)
+    out = diffusion.segment_mean(t, a2t, N, fused=True)
+    assert torch.allclose(out.float(), ref.float(), atol=2e-2, rtol=2e-2)
+    a = torch.randn(B, N, 128, device="cuda", generator=g).bfloat16()
+    q = torch.randn(B, A, 128, device="cuda", generator=g).bfloat16()
+    got = rows.gather_rows_add(q, a, a2t.to(torch.int32))
+    assert torch.equal(got, q + a[:, a2t])
+    assert torch.equal(rows.gather_rows_add(None, a, a2t.to(torch.int32)), a[:, a2t])

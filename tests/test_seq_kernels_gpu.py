@@ -1,0 +1,124 @@
+"""Row / sequence kernels of the LM and genomics families against plain fp32 PyTorch statements."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(out, ref, tol=2e-2):
+    err = (out.float() - ref.float()).abs().max().item()
+    scale = max(ref.float().abs().max().item(), 1.0)
+    assert err <= tol * scale, (err, scale)
+
+
+@pytest.mark.parametrize("C", [256, 4096, 8192])
+def test_rmsnorm(C):
+    from uplifting_biomolecular_modeling_b200.ops import reference as R, seq
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(37, C, device="cuda", generator=g).bfloat16()
+    sc = 1 + 0.1 * torch.randn(C, device="cuda", generator=g)
+    _close(seq.rmsnorm_rows(x, sc), R.rmsnorm_rows(x, sc))
+
+
+@pytest.mark.parametrize("K,tail", [(3, False), (3, True), (4, True)])
+def test_fir_gate3(K, tail):
+    from uplifting_biomolecular_modeling_b200.ops import reference as R, seq
+    g = torch.Generator(device="cuda").manual_seed(1)
+    B, L, d = 2, 77, 64
+    z = torch.randn(B, L, 3 * d, device="cuda", generator=g).bfloat16()
+    h = torch.randn(3 * d, K, device="cuda", generator=g) * 0.4
+    t = torch.randn(B, K - 1, 3 * d, device="cuda", generator=g).bfloat16() if tail else None
+    u, x2 = seq.fir_gate3(z, seq.taps_major(h), t)
+    ur, x2r = R.fir_gate3(z, h, t)
+    _close(u, ur)
+    _close(x2, x2r)
+
+
+@pytest.mark.parametrize("K,tail", [(7, False), (7, True), (40, False), (40, True)])
+def test_fir_inner_gate(K, tail):
+    from uplifting_biomolecular_modeling_b200.ops import reference as R, seq
+    g = torch.Generator(device="cuda").manual_seed(2)
+    B, L, d = 2, 90, 128
+    u = torch.randn(B, L, d, device="cuda", generator=g).bfloat16()
+    x2 = torch.randn(B, L, d, device="cuda", generator=g).bfloat16()
+    h = torch.randn(d, K, device="cuda", generator=g) * K ** -0.5
+    D = torch.randn(d, device="cuda", generator=g)
+    t = torch.randn(B, K - 1, d, device="cuda", generator=g).bfloat16() if tail else None
+    _close(seq.fir_inner_gate(u, seq.taps_major(h), D, x2, t), R.fir_inner_gate(u, h, D, x2, t), 3e-2)
+
+
+def test_fftconv_epilogue_and_pole_step():
+    from uplifting_biomolecular_modeling_b200.ops import reference as R, seq
+    g = torch.Generator(device="cuda").manual_seed(3)
+    B, L, d, n, S = 2, 70, 96, 128, 8
+    y = torch.randn(B, d, n, device="cuda", generator=g)
+    u = torch.randn(B, L, d, device="cuda", generator=g).bfloat16()
+    x2 = torch.randn(B, L, d, device="cuda", generator=g).bfloat16()
+    D = torch.randn(d, device="cuda", generator=g)
+    _close(seq.fftconv_epilogue(y, u, D, x2), R.fftconv_epilogue(y, u, D, x2), 3e-2)
+    state = torch.randn(B, d, S, device="cuda", generator=g)
+    lam = torch.rand(d, S, device="cuda", generator=g) * 0.5 + 0.45
+    res = torch.randn(d, S, device="cuda", generator=g) / S
+    u1, g1 = u[:, 0].contiguous(), x2[:, 0].contiguous()
+    ref, sref = R.pole_step(state.clone(), lam, res, u1, D, g1)
+    out = seq.pole_step(state, lam, res, u1, D, g1)
+    _close(out, ref, 3e-2)
+    _close(state, sref, 1e-5)
+
+
+def test_elementwise_sets():
+    from uplifting_biomolecular_modeling_b200.ops import reference as R, seq
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(33, 512, device="cuda", generator=g).bfloat16()
+    a = torch.randn(33, 512, device="cuda", generator=g).bfloat16()
+    b = torch.randn(33, 512, device="cuda", generator=g).bfloat16()
+    v0 = torch.randn(512, device="cuda", generator=g)
+    v1 = torch.randn(512, device="cuda", generator=g)
+    _close(seq.gelu_new(x), R.gelu_new(x))
+    _close(seq.residual_add2(x, a, b), x.float() + a.float() + b.float())
+    _close(seq.bias_residual(x, v0, a), x.float() + v0 + a.float())
+    _close(seq.scale_shift_gelu(x, v0, v1), torch.nn.functional.gelu(x.float() * v0 + v1))
+    _close(seq.silu_mul(x, a), torch.nn.functional.silu(x.float()) * a.float())
+    _close(seq.add2_softmax_rows(x, a, b), torch.softmax(x.float() + a.float() + b.float(), -1), 1e-5)
+    xs = torch.randn(2, 40, 64, device="cuda", generator=g).bfloat16()
+    ws = torch.randn(2, 40, 64, device="cuda", generator=g).bfloat16()
+    for mode in ("max", "mean", "softmax"):
+        _close(seq.pool2(xs, mode, ws), R.pool2(xs, mode, ws))
+    out, s = seq.residual_ln(x, a, 1 + 0.1 * v0, v1, return_sum=True)
+    _close(out, R.residual_ln(x, a, 1 + 0.1 * v0, v1), 3e-2)
+    assert torch.equal(s, (x.float() + a.float()).bfloat16())
+
+
+def test_rotary_split_qkv():
+    from uplifting_biomolecular_modeling_b200.ops import reference as R, seq
+    g = torch.Generator(device="cuda").manual_seed(5)
+    T, H, Dh, rot = 50, 4, 64, 32
+    qkv = torch.randn(T, 3 * H * Dh, device="cuda", generator=g).bfloat16()
+    pos = torch.arange(T, device="cuda")
+    q, k, v = seq.rotary_split_qkv(qkv, pos, H, rot)
+    qr, kr, vr = R.rotary_split_qkv(qkv, pos, H, rot)
+    _close(q, qr)
+    _close(k, kr)
+    assert torch.equal(v.float(), vr)
+
+
+def test_evo2_fused_matches_plain_statements():
+    """Prefill logits and greedy decoding of the kernel path against the plain statements (bf16 weights)."""
+    from uplifting_biomolecular_modeling_b200.models import evo2
+    from uplifting_biomolecular_modeling_b200.ops import native
+    m = evo2.build("evo2_tiny", device="cuda", dtype=torch.bfloat16, seed=3)
+    tok = torch.randint(0, m.cfg.vocab, (2, 96), device="cuda")
+    ref = m(tok).float()
+    ref_states = [dict() for _ in m.blocks]
+    m(tok, ref_states)
+    ref_step = m.step(tok[:, -1:], ref_states).float()
+    assert m.set_impl("fused") > 0
+    out = m(tok).float()
+    states = [dict() for _ in m.blocks]
+    m(tok, states)
+    out_step = m.step(tok[:, -1:], states).float()
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "evo2")
+    scale = ref.abs().max().item()
+    assert (out - ref).abs().max().item() < 6e-2 * scale
+    assert (out_step - ref_step).abs().max().item() < 6e-2 * scale

@@ -104,9 +104,12 @@ class Predictor:
         A = feats["ref_pos"].shape[1]
         key = (n_tokens, A, samples)
         if self._graph is not None and self._graph_key == key:
-            _tree_copy(self._graph["prep"], prep)
-            self._graph["a2t"].copy_(feats["atom_to_token"][0])
-            return self._graph["fn"]
+            from .models import diffusion
+            # the captured step reads the atom -> token tables of its static a2t tensor: rewrite them in place
+            if diffusion.refresh_segment_tables(self._graph["a2t"], feats["atom_to_token"][0], n_tokens):
+                _tree_copy(self._graph["prep"], prep)
+                return self._graph["fn"]
+            self._graph = None          # a token with more atoms than any before: tables change shape, recapture
         a2t = feats["atom_to_token"][0].clone()
         static_x = torch.zeros((samples, A, 3), device=self.device)
         static_s = torch.zeros(3, device=self.device)

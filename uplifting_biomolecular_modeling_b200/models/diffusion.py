@@ -271,28 +271,75 @@ class SingleConditioning(nn.Module):
 
 
 _SEG_CACHE: dict = {}
+_WEIGHT_CACHE: dict = {}
 
 
-def segment_mean(t: torch.Tensor, atom_to_token: torch.Tensor, n_tokens: int) -> torch.Tensor:
-    """Mean of atom rows per token, deterministic (no atomics): atoms of a token are gathered through
-    a padded [N, M] index table built once per atom layout.  t: [B, A, C] -> [B, N, C].
-    Reference kernel with the same job: _seg_reduce_kernel (common/opt_core/opt_core/kernels/dtk_kernels.py)."""
+def _bf16_weight(lin: nn.Linear) -> torch.Tensor:
+    """Contiguous bf16 copy of a bias-free Linear's weight for the GEMM kernel (refreshed when the weight changes)."""
+    ent = _WEIGHT_CACHE.get(id(lin))
+    if ent is None or ent[0] is not lin.weight or ent[1] != lin.weight._version:
+        ent = (lin.weight, lin.weight._version, lin.weight.detach().to(torch.bfloat16).contiguous())
+        _WEIGHT_CACHE[id(lin)] = ent
+    return ent[2]
+
+
+
+def build_segment_tables(atom_to_token: torch.Tensor, n_tokens: int, device) -> tuple:
+    """Index tables of one atom layout: padded gather table [N, M], validity and counts for the plain statement,
+    an int32 table (-1 = no atom) and an int32 atom -> token map for the kernels."""
+    a2t = atom_to_token.detach().cpu()
+    counts = torch.bincount(a2t, minlength=n_tokens)
+    M = int(counts.max().item())
+    order = torch.argsort(a2t, stable=True)
+    starts = torch.cumsum(counts, 0) - counts
+    idx = starts[:, None] + torch.arange(M)[None, :]
+    valid = torch.arange(M)[None, :] < counts[:, None]
+    idx = order[idx.clamp(max=a2t.shape[0] - 1)]
+    table = torch.where(valid, idx, torch.full_like(idx, -1)).to(torch.int32).contiguous()
+    return (idx.to(device), valid.to(device), counts.clamp(min=1).to(device), table.to(device),
+            a2t.to(torch.int32).contiguous().to(device))
+
+
+def _segment_tables(t: torch.Tensor, atom_to_token: torch.Tensor, n_tokens: int):
+    """Tables of :func:`build_segment_tables`, built once per ``atom_to_token`` tensor.  A caller that rewrites that
+    tensor in place (a captured graph's static input) refreshes the cached tables itself: see
+    :func:`refresh_segment_tables`."""
     key = (atom_to_token.data_ptr(), atom_to_token.shape[0], n_tokens, str(t.device))
     tab = _SEG_CACHE.get(key)
     if tab is None:
-        a2t = atom_to_token.detach().cpu()
-        counts = torch.bincount(a2t, minlength=n_tokens)
-        M = int(counts.max().item())
-        order = torch.argsort(a2t, stable=True)
-        starts = torch.cumsum(counts, 0) - counts
-        idx = starts[:, None] + torch.arange(M)[None, :]
-        valid = torch.arange(M)[None, :] < counts[:, None]
-        idx = order[idx.clamp(max=a2t.shape[0] - 1)]
-        tab = (idx.to(t.device), valid.to(t.device), counts.clamp(min=1).to(t.device))
+        tab = build_segment_tables(atom_to_token, n_tokens, t.device)
         if len(_SEG_CACHE) > 64:
             _SEG_CACHE.clear()
         _SEG_CACHE[key] = tab
-    idx, valid, counts = tab
+    return tab
+
+
+def refresh_segment_tables(static_a2t: torch.Tensor, new_a2t: torch.Tensor, n_tokens: int) -> bool:
+    """Rewrite, in place, the cached tables of ``static_a2t`` for a new atom layout (and ``static_a2t`` itself).
+    Returns False when the new layout needs tables of another shape (more atoms in some token): the caller must
+    then drop whatever captured the old tensors."""
+    key = (static_a2t.data_ptr(), static_a2t.shape[0], n_tokens, str(static_a2t.device))
+    old = _SEG_CACHE.get(key)
+    new = build_segment_tables(new_a2t, n_tokens, static_a2t.device)
+    if old is not None and any(o.shape != n.shape for o, n in zip(old, new)):
+        return False
+    static_a2t.copy_(new_a2t)
+    if old is None:
+        _SEG_CACHE[key] = new
+    else:
+        for o, n in zip(old, new):
+            o.copy_(n)
+    return True
+
+
+def segment_mean(t: torch.Tensor, atom_to_token: torch.Tensor, n_tokens: int, fused: bool = False) -> torch.Tensor:
+    """Mean of atom rows per token, deterministic (no atomics): atoms of a token are gathered through
+    a padded [N, M] index table built once per atom layout.  t: [B, A, C] -> [B, N, C].
+    Reference kernel with the same job: _seg_reduce_kernel (common/opt_core/opt_core/kernels/dtk_kernels.py)."""
+    idx, valid, counts, table, _ = _segment_tables(t, atom_to_token, n_tokens)
+    if fused and t.is_cuda and t.dtype == torch.bfloat16 and t.shape[-1] % 8 == 0:
+        from ..ops import rows
+        return rows.segment_mean(t, table, n_tokens)
     g = t[:, idx]                                              # [B, N, M, C]
     g = g * valid[None, :, :, None].to(t.dtype)
     return (g.float().sum(2) / counts[None, :, None].float()).to(t.dtype)
@@ -320,8 +367,14 @@ class AtomAttentionEncoder(AtomEncoderDecoderBase):
         if self.structure:
             q = q + self.r_to_q_trans(r.to(q0.dtype))
         q = self.atom_transformer(q, c, biases, hoisted=hoisted, window=window)
-        t = self.atom_to_token_trans(q)
-        a = segment_mean(t, atom_to_token, n_tokens)
+        fused = self.atom_transformer.layers[0].impl == "fused" and q.is_cuda and q.dtype == torch.bfloat16
+        if fused:
+            from ..ops import gemm
+            lin = self.atom_to_token_trans[0]
+            t = gemm.gemm(q.reshape(-1, q.shape[-1]), _bf16_weight(lin), act="relu").view(B, q.shape[1], -1)
+        else:
+            t = self.atom_to_token_trans(q)
+        a = segment_mean(t, atom_to_token, n_tokens, fused=fused)
         return a, q
 
 
@@ -332,7 +385,14 @@ class AtomAttentionDecoder(AtomEncoderDecoderBase):
         self.atom_feat_to_atom_pos_update = nn.Sequential(nn.LayerNorm(c_atom), nn.Linear(c_atom, 3, bias=False))
 
     def forward(self, a, q, c, biases, atom_to_token, hoisted=None, window=(32, 128)):
-        q = q + self.a_to_q_trans(a)[:, atom_to_token]
+        if self.atom_transformer.layers[0].impl == "fused" and q.is_cuda and q.dtype == torch.bfloat16:
+            from ..ops import gemm, rows
+            B, N, _ = a.shape
+            aq = gemm.gemm(a.reshape(B * N, -1), _bf16_weight(self.a_to_q_trans)).view(B, N, -1)
+            a2t32 = _segment_tables(q, atom_to_token, N)[4]
+            q = rows.gather_rows_add(q, aq, a2t32)
+        else:
+            q = q + self.a_to_q_trans(a)[:, atom_to_token]
         q = self.atom_transformer(q, c, biases, hoisted=hoisted, window=window)
         return self.atom_feat_to_atom_pos_update(q)
 

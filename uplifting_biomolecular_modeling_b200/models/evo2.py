@@ -57,13 +57,22 @@ CONFIGS: Dict[str, Evo2Config] = {
 }
 
 
+def _fusable(mod, x: torch.Tensor) -> bool:
+    """The kernel path serves bf16 activations on the GPU whose channel count is a multiple of 8."""
+    return getattr(mod, "impl", "torch") == "fused" and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0
+
+
 class RMSNorm(nn.Module):
     def __init__(self, d: int, eps: float = 1e-6):
         super().__init__()
         self.scale = nn.Parameter(torch.ones(d))
         self.eps = eps
+        self.impl = "torch"
 
     def forward(self, x):
+        if _fusable(self, x):
+            from ..ops import seq
+            return seq.rmsnorm_rows(x, self.scale, self.eps)
         x32 = x.float()
         y = x32 * torch.rsqrt(x32.pow(2).mean(-1, keepdim=True) + self.eps)
         return (y * self.scale.float()).to(x.dtype)
@@ -108,6 +117,8 @@ class HyenaOperator(nn.Module):
             self.residues = nn.Parameter(torch.randn(d, cfg.state_dim) * (1.0 / cfg.state_dim))
         self.D = nn.Parameter(torch.ones(d))
         self.out_proj = nn.Linear(d, d, bias=True)
+        self.impl = "torch"
+        self._taps = None           # tap-major fp32 copies of the filters for the kernels
 
     # ---- filters
     def long_filter(self, L: int) -> torch.Tensor:
@@ -127,14 +138,42 @@ class HyenaOperator(nn.Module):
             y = fft_causal_conv(u, self.long_filter(u.shape[1]))
         return y + u * self.D.to(u.dtype)
 
+    def _kernel_taps(self):
+        if self._taps is None:
+            from ..ops import seq
+            self._taps = (seq.taps_major(self.fir), None if self.kind == "hcl" else seq.taps_major(self.h))
+        return self._taps
+
+    def _fused_inner(self, u, x2, tail):
+        """x2 * (conv(u) + D u) with the gate folded into the convolution's epilogue."""
+        from ..ops import seq
+        if self.kind in ("hcs", "hcm"):
+            if self.kind == "hcm" and u.shape[1] > 4 * self.h.shape[1] and tail is None:
+                h = self.h
+            else:
+                return seq.fir_inner_gate(u, self._kernel_taps()[1], self.D, x2, tail)
+        else:
+            h = self.long_filter(u.shape[1])
+        L = u.shape[1]
+        n = 1 << (L + h.shape[1] - 1).bit_length()
+        X = torch.fft.rfft(u.float().transpose(1, 2), n=n)
+        y = torch.fft.irfft(X * torch.fft.rfft(h.float(), n=n).unsqueeze(0), n=n)        # [B, d, n] fp32
+        return seq.fftconv_epilogue(y, u, self.D, x2)
+
     def forward(self, x: torch.Tensor, state: Optional[dict] = None, linear=None) -> torch.Tensor:
         """Prefill form.  When ``state`` is a dict it is filled with what decoding needs."""
         lin = linear or (lambda m, t: m(t))
         z = lin(self.in_proj, x)
-        zf = causal_fir(z, self.fir)
-        x1, x2, v = zf.chunk(3, dim=-1)
-        u = x1 * v
-        y = self.inner(u, None)
+        fused = _fusable(self, z) and self.cfg.fir_len <= 4
+        if fused:
+            from ..ops import seq
+            u, x2 = seq.fir_gate3(z, self._kernel_taps()[0])
+            gated = self._fused_inner(u, x2, None)
+        else:
+            zf = causal_fir(z, self.fir)
+            x1, x2, v = zf.chunk(3, dim=-1)
+            u = x1 * v
+            gated = x2 * self.inner(u, None)
         if state is not None:
             K = self.cfg.fir_len
             state["fir_tail"] = _last(z, K - 1)
@@ -145,12 +184,25 @@ class HyenaOperator(nn.Module):
                 L = u.shape[1]
                 w = lam.unsqueeze(0) ** torch.arange(L - 1, -1, -1, device=u.device, dtype=torch.float32).view(L, 1, 1)
                 state["poles"] = torch.einsum("bld,lds->bds", u.float(), w)       # sum_t lam^(L-1-t) u_t
-        return lin(self.out_proj, x2 * y)
+        return lin(self.out_proj, gated)
 
     def step(self, x: torch.Tensor, state: dict, linear=None) -> torch.Tensor:
         """One token.  x: [B, 1, d]."""
         lin = linear or (lambda m, t: m(t))
         z = lin(self.in_proj, x)
+        if _fusable(self, z) and self.cfg.fir_len <= 4:
+            from ..ops import seq
+            u, x2 = seq.fir_gate3(z, self._kernel_taps()[0], state["fir_tail"])
+            state["fir_tail"] = torch.cat([state["fir_tail"], z], 1)[:, 1:]
+            if self.kind in ("hcs", "hcm"):
+                gated = seq.fir_inner_gate(u, self._kernel_taps()[1], self.D, x2, state["inner_tail"])
+                state["inner_tail"] = torch.cat([state["inner_tail"], u], 1)[:, 1:]
+            else:
+                st = state["poles"].float().contiguous()
+                gated = seq.pole_step(st, torch.exp(self.log_poles.float()), self.residues, u[:, 0], self.D,
+                                      x2[:, 0]).unsqueeze(1)
+                state["poles"] = st
+            return lin(self.out_proj, gated)
         zf = causal_fir(z, self.fir, state["fir_tail"])
         state["fir_tail"] = torch.cat([state["fir_tail"], z], 1)[:, 1:]
         x1, x2, v = zf.chunk(3, dim=-1)
@@ -227,10 +279,15 @@ class SwiGLU(nn.Module):
         self.l1 = nn.Linear(d, ffn, bias=False)     # gate
         self.l2 = nn.Linear(d, ffn, bias=False)     # up
         self.l3 = nn.Linear(ffn, d, bias=False)     # down
+        self.impl = "torch"
 
     def forward(self, x, linear=None):
         lin = linear or (lambda m, t: m(t))
-        return lin(self.l3, F.silu(lin(self.l1, x)) * lin(self.l2, x))
+        g, up = lin(self.l1, x), lin(self.l2, x)
+        if _fusable(self, g):
+            from ..ops import seq
+            return lin(self.l3, seq.silu_mul(g, up))
+        return lin(self.l3, F.silu(g) * up)
 
 
 class Block(nn.Module):
@@ -259,6 +316,18 @@ class StripedHyena2(nn.Module):
         self.blocks = nn.ModuleList([Block(cfg, cfg.layer_kind(i)) for i in range(cfg.n_layers)])
         self.norm = RMSNorm(cfg.d_model, cfg.eps)
         self.linear = None          # optional callable (module, x) -> y replacing nn.Linear calls (fused / TP GEMMs)
+
+    def set_impl(self, impl: str) -> int:
+        """``fused``: RMSNorm, the FIR / gate stages, the convolution epilogues, the decode state step and SwiGLU
+        run as kernels and every nn.Linear goes through the tcgen05 GEMM; ``torch``: the plain statements.
+        Returns the number of modules switched."""
+        n = 0
+        for m in self.modules():
+            if hasattr(m, "impl"):
+                m.impl = impl
+                n += 1
+        self.linear = fused_linear if impl == "fused" else None
+        return n
 
     def logits(self, x):
         return F.linear(self.norm(x), self.embedding.weight)
@@ -300,6 +369,27 @@ class StripedHyena2(nn.Module):
 
 
 BYTE_LUT = {c: i for i, c in enumerate("ACGTN")}
+
+
+_W_CACHE: dict = {}
+
+
+def fused_linear(module: nn.Linear, x: torch.Tensor) -> torch.Tensor:
+    """nn.Linear on the tcgen05 GEMM for bf16 GPU activations (weights cached as contiguous bf16); anything
+    else takes the module's own forward."""
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0):
+        return module(x)
+    from ..ops import gemm
+    key = id(module)
+    ent = _W_CACHE.get(key)
+    if ent is None or ent[0] is not module.weight or ent[1] != module.weight._version:
+        ent = (module.weight, module.weight._version, module.weight.detach().to(torch.bfloat16).contiguous(),
+               None if module.bias is None else module.bias.detach().float().contiguous())
+        _W_CACHE[key] = ent
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    return gemm.gemm(x2, ent[2], bias=ent[3]).view(*x.shape[:-1], ent[2].shape[0])
 
 
 def tokenize(seq: str, device="cpu") -> torch.Tensor:

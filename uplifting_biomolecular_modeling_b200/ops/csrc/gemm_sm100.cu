@@ -40,6 +40,12 @@ struct GemmParams {
   const __nv_bfloat16* gate;
   long long ld_gate;
   int gate_rows;
+  // Row-scattered output (the data movement of a reduce-scatter done by the epilogue): output row m belongs to
+  // GPU m / c_peer_rows and is stored, with plain peer stores, into that GPU's buffer c_peer[q] at row
+  // m % c_peer_rows (leading dimension ldc).  Each GPU passes the address of ITS slot in every peer's slot array,
+  // so the partial products of the ranks never overlap; the owner adds the slots afterwards in rank order.
+  void* c_peer[8];
+  int c_peer_rows;
   KernelStatus* status;
   int tiles_m, tiles_n, num_tiles;
   // peer mode: the N dimension is the concatenation of row shards owned by several GPUs; n-tiles are
@@ -477,12 +483,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (n0 + j < n_limit) f[j] += __bfloat162float(rr[j]);
             }
           }
+          char* c_base = reinterpret_cast<char*>(p.C);
+          long long m_out = m;
+          if (p.c_peer_rows > 0) {
+            const int owner = m / p.c_peer_rows;
+            c_base = reinterpret_cast<char*>(p.c_peer[owner]);
+            m_out = m - owner * p.c_peer_rows;
+          }
           const long long c_off =
               p.cblk_col != 0 ? (static_cast<long long>(m >> 5) * p.cblk_hi + static_cast<long long>(m & 31) * p.cblk_lo +
                                  static_cast<long long>(n0 >> 5) * p.cblk_col)
-                              : static_cast<long long>(m) * p.ldc + n0;
+                              : m_out * p.ldc + n0;
           if (p.out_fp32) {
-            float* cp = reinterpret_cast<float*>(p.C) + b * p.strideC + c_off;
+            float* cp = reinterpret_cast<float*>(c_base) + b * p.strideC + c_off;
             if (n0 + 32 <= n_limit && (reinterpret_cast<uintptr_t>(cp) & 31) == 0) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8)
@@ -501,7 +514,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (n0 + j < n_limit) cp[j] = f[j];
             }
           } else {
-            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.strideC + c_off;
+            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(c_base) + b * p.strideC + c_off;
             if (n0 + 32 <= n_limit && (reinterpret_cast<uintptr_t>(cp) & 31) == 0) {
               st_bf16x16(cp, f);
               st_bf16x16(cp + 16, f + 16);
@@ -659,6 +672,7 @@ extern "C" int ubm_gemm_bf16_ex(const void* A, const void* B, void* C, const voi
   p.gate = static_cast<const __nv_bfloat16*>(gate);
   p.ld_gate = ld_gate;
   p.gate_rows = gate_rows > 0 ? gate_rows : 1;
+  p.c_peer_rows = 0;
   p.status = static_cast<KernelStatus*>(status);
   if (batch == 1) {
     if (strideA == 0) strideA = mn_major ? (long long)K * lda : (long long)M * lda;
@@ -680,6 +694,36 @@ extern "C" int ubm_gemm_bf16(const void* A, const void* B, void* C, const void* 
                              int out_fp32, int act, float alpha, void* status, void* stream) {
   return ubm_gemm_bf16_ex(A, B, C, bias, residual, M, N, K, batch, lda, ldb, ldc, ldr, strideA, strideB, strideC,
                           strideR, mn_major, out_fp32, act, alpha, 0, 0, 0, nullptr, 0, 0, status, stream);
+}
+
+// GEMM whose epilogue scatters output rows to their owners: the transfer half of a reduce-scatter fused into the
+// compute.  C_ptrs[q] = address, in GPU q's memory (mapped here), of the slot this GPU writes: bf16 (or fp32)
+// [rows_per_rank][N] with leading dimension ldc.  Output row m goes to C_ptrs[m / rows_per_rank].  K-major only,
+// batch 1.  The owners add their slots afterwards (ubm_sum_slots) behind a barrier that orders the stores.
+extern "C" int ubm_gemm_bf16_scatter_rows(const void* A, const void* B, void* const* C_ptrs, int npeers,
+                                          int rows_per_rank, int M, int N, int K, long long lda, long long ldb,
+                                          long long ldc, int out_fp32, float alpha, void* status, void* stream) {
+  using namespace ubm;
+  if (npeers < 1 || npeers > 8 || M <= 0 || N <= 0 || K <= 0 || rows_per_rank <= 0) return UBM_ERR_ARGUMENT;
+  if (static_cast<long long>(rows_per_rank) * npeers < M) return UBM_ERR_ARGUMENT;
+  if ((lda & 7) || (ldb & 7)) return UBM_ERR_ARGUMENT;
+  GemmParams p = {};
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.batch = 1;
+  p.C = C_ptrs[0];
+  p.ldc = ldc;
+  p.alpha = alpha;
+  p.out_fp32 = out_fp32;
+  p.gate_rows = 1;
+  p.status = static_cast<KernelStatus*>(status);
+  for (int q = 0; q < 8; ++q) p.c_peer[q] = C_ptrs[q < npeers ? q : 0];
+  p.c_peer_rows = rows_per_rank;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long strideA = static_cast<long long>(M) * lda, strideB = static_cast<long long>(N) * ldb;
+  return N > 128 ? launch_gemm<256, false>(A, B, p, lda, ldb, strideA, strideB, st)
+                 : launch_gemm<128, false>(A, B, p, lda, ldb, strideA, strideB, st);
 }
 
 // All-gather fused into the GEMM: C[b][m][col0_q + n] = sum_k A[b][m][k] * B_q[b][n][k] where B_q is the

@@ -66,3 +66,64 @@ extern "C" int ubm_set_flag(void* flags, int index, unsigned int value, void* st
   UBM_CHECK_LAUNCH("set_flag_kernel");
   return ubm::UBM_OK;
 }
+
+
+// Sum of the slots a reduce-scatter's senders wrote: out[r][c] = sum over p (in rank order) of slots[p][r][c].
+// bf16 slots, fp32 accumulation, bf16 (or fp32) output; 16-byte accesses; optional bias [C] and residual [R][C].
+namespace ubm {
+__global__ void __launch_bounds__(256) sum_slots_kernel(const __nv_bfloat16* __restrict__ slots, long long slot_stride,
+                                                        int P, const float* __restrict__ bias,
+                                                        const __nv_bfloat16* __restrict__ residual,
+                                                        __nv_bfloat16* __restrict__ out, long long R, int C) {
+  const int c8 = C / 8;
+  const long long total = R * c8;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % c8) * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int p = 0; p < P; ++p) {
+      const uint4 u = *reinterpret_cast<const uint4*>(slots + p * slot_stride + i * 8);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += bf16_lo(w[j]);
+        acc[2 * j + 1] += bf16_hi(w[j]);
+      }
+    }
+    if (bias != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += bias[c + j];
+    }
+    if (residual != nullptr) {
+      const uint4 u = *reinterpret_cast<const uint4*>(residual + i * 8);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += bf16_lo(w[j]);
+        acc[2 * j + 1] += bf16_hi(w[j]);
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + i * 8) = o;
+  }
+}
+}  // namespace ubm
+
+// slots: bf16 [P][R][C] contiguous per slot, slot_stride in elements (this GPU's own memory).
+extern "C" int ubm_sum_slots(const void* slots, long long slot_stride, int P, const void* bias, const void* residual,
+                             void* out, long long R, int C, void* stream) {
+  using namespace ubm;
+  if (P < 1 || R <= 0 || C <= 0 || (C & 7) || (slot_stride & 7)) return UBM_ERR_ARGUMENT;
+  long long blocks = (R * (C / 8) + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count()) * 32;
+  if (blocks > cap) blocks = cap;
+  sum_slots_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(slots), slot_stride, P, static_cast<const float*>(bias),
+      static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(out), R, C);
+  UBM_CHECK_LAUNCH("sum_slots_kernel");
+  return UBM_OK;
+}

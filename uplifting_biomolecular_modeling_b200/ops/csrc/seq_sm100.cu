@@ -1,0 +1,777 @@
+// Row and sequence kernels for the language-model and genomics families (StripedHyena-2 / Evo2, ProGen2, ESM-C,
+// Enformer-style towers).  All are memory bound: bf16 (or fp32) rows in, fp32 arithmetic, 16-byte accesses, one
+// pass over the data, the neighbouring elementwise steps folded in.
+//
+//   rmsnorm_rows          y = x * rsqrt(mean(x^2) + eps) * scale                       (Evo2 pre/post norm)
+//   fir_gate3             zf = causal_fir3..8(z) over [B, L, 3d]; u = zf_1 * zf_3, x2 = zf_2   (Hyena input stage)
+//   fir_inner_gate        out = x2 * (causal_fir(u, h) + D * u)                         (hcs / hcm operators)
+//   fftconv_epilogue      out = x2 * (y[b][c][l] + D * u) with y channel-major fp32     (after the inverse FFT)
+//   pole_step             s = s * lam + u; out = x2 * (sum_s s * res + D * u)           (hcl decode step)
+//   gelu_new, residual_add2, bias_residual, scale_shift_gelu, rotary_split_qkv, add2_softmax_rows, pool2,
+//   residual_ln           exact-order elementwise sets of the LM / genomics kits
+//
+// Reference kernels with the same boundaries: the evo2 Triton set (FIR, RMSNorm tail, FFT-conv epilogue,
+// decode-step state), progen2 kits/v0_ew/kernels.cu:37-209 (gelu_new, rotary_split_qkv, residual_add2),
+// esmc kits/residual_ln/kernels.cu:28-127, enformer kits/v0_2/enformer_xattn.cu:24-99 (add2 softmax) and
+// enformer_fastkit.py:96-157 (bn_gelu, pool, bias_residual).
+#include "host_util.h"
+#include "sm100.cuh"
+
+namespace ubm {
+
+static inline int seq_grid(long long work, int per_block) {
+  long long b = (work + per_block - 1) / per_block;
+  const long long cap = static_cast<long long>(sm_count()) * 32;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return static_cast<int>(b);
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&e)[8]) {
+  e[0] = bf16_lo(u.x); e[1] = bf16_hi(u.x); e[2] = bf16_lo(u.y); e[3] = bf16_hi(u.y);
+  e[4] = bf16_lo(u.z); e[5] = bf16_hi(u.z); e[6] = bf16_lo(u.w); e[7] = bf16_hi(u.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&e)[8]) {
+  return make_uint4(pack_bf16x2(e[0], e[1]), pack_bf16x2(e[2], e[3]), pack_bf16x2(e[4], e[5]),
+                    pack_bf16x2(e[6], e[7]));
+}
+
+// ------------------------------------------------------------------------------------------ RMSNorm
+// one warp per row, the row read once (kept in registers for C <= 8192: up to 32 chunks of 8 per lane)
+template <int CHUNKS>
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x,
+                                                           const float* __restrict__ scale,
+                                                           __nv_bfloat16* __restrict__ out, long long R, int C,
+                                                           float eps) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  for (long long r = static_cast<long long>(blockIdx.x) * wpb + (threadIdx.x >> 5); r < R;
+       r += static_cast<long long>(gridDim.x) * wpb) {
+    float v[CHUNKS][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < C) {
+        unpack8(*reinterpret_cast<const uint4*>(x + r * C + c), v[k]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[k][j] * v[k][j];
+      }
+    }
+    ss = warp_sum(ss);
+    const float rs = rsqrtf(ss / C + eps);
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < C) {
+        const float4 s0 = __ldg(reinterpret_cast<const float4*>(scale + c));
+        const float4 s1 = __ldg(reinterpret_cast<const float4*>(scale + c + 4));
+        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = v[k][j] * rs * sc[j];
+        *reinterpret_cast<uint4*>(out + r * C + c) = pack8(o);
+      }
+    }
+  }
+}
+
+// rows wider than 4096 channels: two passes over the row (the second one hits L1/L2)
+__global__ void __launch_bounds__(256) rmsnorm_rows_wide_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                const float* __restrict__ scale,
+                                                                __nv_bfloat16* __restrict__ out, long long R, int C,
+                                                                float eps) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  for (long long r = static_cast<long long>(blockIdx.x) * wpb + (threadIdx.x >> 5); r < R;
+       r += static_cast<long long>(gridDim.x) * wpb) {
+    float ss = 0.f;
+    for (int c = lane * 8; c < C; c += 256) {
+      float v[8];
+      unpack8(*reinterpret_cast<const uint4*>(x + r * C + c), v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+    }
+    ss = warp_sum(ss);
+    const float rs = rsqrtf(ss / C + eps);
+    for (int c = lane * 8; c < C; c += 256) {
+      float v[8], o[8];
+      unpack8(*reinterpret_cast<const uint4*>(x + r * C + c), v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = v[j] * rs * scale[c + j];
+      *reinterpret_cast<uint4*>(out + r * C + c) = pack8(o);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------ causal FIR
+// Depthwise causal FIR over [B][L][C] with taps ht[k][c] (k = 0 multiplies the current sample).  A thread owns 8
+// channels and walks TL consecutive positions with the K-1 previous samples in registers, so each input element
+// is read once (plus K-1 per run of TL).  tail: [B][K-1][C] samples before position 0, or null (zeros).
+template <int K>
+struct FirWindow {
+  float h[K][8];
+  float w[K - 1][8];   // w[j] = sample at distance j+1 behind the current one
+  __device__ __forceinline__ void load_taps(const float* __restrict__ ht, int C, int c) {
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(ht + static_cast<long long>(k) * C + c));
+      const float4 b = __ldg(reinterpret_cast<const float4*>(ht + static_cast<long long>(k) * C + c + 4));
+      h[k][0] = a.x; h[k][1] = a.y; h[k][2] = a.z; h[k][3] = a.w;
+      h[k][4] = b.x; h[k][5] = b.y; h[k][6] = b.z; h[k][7] = b.w;
+    }
+  }
+  __device__ __forceinline__ void prime(const __nv_bfloat16* __restrict__ xb, const __nv_bfloat16* __restrict__ tb,
+                                        int l0, int C, int c) {
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) {
+      const int l = l0 - 1 - j;
+      if (l >= 0) {
+        unpack8(*reinterpret_cast<const uint4*>(xb + static_cast<long long>(l) * C + c), w[j]);
+      } else if (tb != nullptr) {
+        unpack8(*reinterpret_cast<const uint4*>(tb + static_cast<long long>(K - 1 + l) * C + c), w[j]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) w[j][e] = 0.f;
+      }
+    }
+  }
+  __device__ __forceinline__ void step(const float (&cur)[8], float (&y)[8]) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float a = h[0][e] * cur[e];
+#pragma unroll
+      for (int j = 0; j < K - 1; ++j) a = fmaf(h[j + 1][e], w[j][e], a);
+      y[e] = a;
+    }
+#pragma unroll
+    for (int j = K - 2; j > 0; --j)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) w[j][e] = w[j - 1][e];
+    if (K > 1) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) w[0][e] = cur[e];
+    }
+  }
+};
+
+constexpr int kFirTL = 32;   // positions per thread run
+
+// Hyena input stage: z [B][L][3d] -> zf = fir(z) per channel; u = zf[0:d] * zf[2d:3d], x2 = zf[d:2d].
+template <int K>
+__global__ void __launch_bounds__(128) fir_gate3_kernel(const __nv_bfloat16* __restrict__ z,
+                                                        const float* __restrict__ ht,     // [K][3d]
+                                                        const __nv_bfloat16* __restrict__ tail,  // [B][K-1][3d] or null
+                                                        __nv_bfloat16* __restrict__ u, __nv_bfloat16* __restrict__ x2,
+                                                        int B, int L, int d) {
+  const int c8 = d / 8;
+  const int runs = (L + kFirTL - 1) / kFirTL;
+  const long long total = static_cast<long long>(B) * runs * c8;
+  const int C = 3 * d;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int cc = static_cast<int>(i % c8) * 8;
+    const long long br = i / c8;
+    const int run = static_cast<int>(br % runs);
+    const int b = static_cast<int>(br / runs);
+    const __nv_bfloat16* zb = z + static_cast<long long>(b) * L * C;
+    const __nv_bfloat16* tb = tail == nullptr ? nullptr : tail + static_cast<long long>(b) * (K - 1) * C;
+    FirWindow<K> f1, f2, f3;
+    f1.load_taps(ht, C, cc);
+    f2.load_taps(ht, C, d + cc);
+    f3.load_taps(ht, C, 2 * d + cc);
+    const int l0 = run * kFirTL;
+    f1.prime(zb, tb, l0, C, cc);
+    f2.prime(zb, tb, l0, C, d + cc);
+    f3.prime(zb, tb, l0, C, 2 * d + cc);
+    const int l1 = min(L, l0 + kFirTL);
+    for (int l = l0; l < l1; ++l) {
+      float a[8], bb[8], cv[8], y1[8], y2[8], y3[8];
+      const __nv_bfloat16* row = zb + static_cast<long long>(l) * C;
+      unpack8(*reinterpret_cast<const uint4*>(row + cc), a);
+      unpack8(*reinterpret_cast<const uint4*>(row + d + cc), bb);
+      unpack8(*reinterpret_cast<const uint4*>(row + 2 * d + cc), cv);
+      f1.step(a, y1);
+      f2.step(bb, y2);
+      f3.step(cv, y3);
+      // the plain statement rounds zf to the activation type before the gate product
+      float uo[8], xo[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        uo[e] = __bfloat162float(__float2bfloat16(y1[e])) * __bfloat162float(__float2bfloat16(y3[e]));
+        xo[e] = y2[e];
+      }
+      const long long o = (static_cast<long long>(b) * L + l) * d + cc;
+      *reinterpret_cast<uint4*>(u + o) = pack8(uo);
+      *reinterpret_cast<uint4*>(x2 + o) = pack8(xo);
+    }
+  }
+}
+
+// Inner operator of hcs / hcm: out = x2 * (fir(u, h) + D * u).  Short filters keep the window in registers;
+// longer ones (the 128-tap medium filter) re-read the inputs through L1/L2 (generic kernel below).
+template <int K>
+__global__ void __launch_bounds__(128) fir_inner_gate_kernel(const __nv_bfloat16* __restrict__ u,
+                                                             const float* __restrict__ ht,   // [K][d]
+                                                             const float* __restrict__ D,
+                                                             const __nv_bfloat16* __restrict__ x2,   // or null
+                                                             const __nv_bfloat16* __restrict__ tail, // [B][K-1][d]
+                                                             __nv_bfloat16* __restrict__ out, int B, int L, int d) {
+  const int c8 = d / 8;
+  const int runs = (L + kFirTL - 1) / kFirTL;
+  const long long total = static_cast<long long>(B) * runs * c8;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int cc = static_cast<int>(i % c8) * 8;
+    const long long br = i / c8;
+    const int run = static_cast<int>(br % runs);
+    const int b = static_cast<int>(br / runs);
+    const __nv_bfloat16* ub = u + static_cast<long long>(b) * L * d;
+    const __nv_bfloat16* tb = tail == nullptr ? nullptr : tail + static_cast<long long>(b) * (K - 1) * d;
+    FirWindow<K> f;
+    f.load_taps(ht, d, cc);
+    const int l0 = run * kFirTL;
+    f.prime(ub, tb, l0, d, cc);
+    const float4 d0 = __ldg(reinterpret_cast<const float4*>(D + cc));
+    const float4 d1 = __ldg(reinterpret_cast<const float4*>(D + cc + 4));
+    const float dv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+    const int l1 = min(L, l0 + kFirTL);
+    for (int l = l0; l < l1; ++l) {
+      float cur[8], y[8], g[8];
+      const long long o = (static_cast<long long>(b) * L + l) * d + cc;
+      unpack8(*reinterpret_cast<const uint4*>(u + o), cur);
+      f.step(cur, y);
+      if (x2 != nullptr) {
+        unpack8(*reinterpret_cast<const uint4*>(x2 + o), g);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) g[e] = 1.f;
+      }
+      float r[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float conv = __bfloat162float(__float2bfloat16(y[e]));     // the plain statement's bf16 conv output
+        r[e] = g[e] * __bfloat162float(__float2bfloat16(conv + cur[e] * dv[e]));
+      }
+      *reinterpret_cast<uint4*>(out + o) = pack8(r);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128) fir_inner_gate_long_kernel(const __nv_bfloat16* __restrict__ u,
+                                                                  const float* __restrict__ ht, int K,
+                                                                  const float* __restrict__ D,
+                                                                  const __nv_bfloat16* __restrict__ x2,
+                                                                  const __nv_bfloat16* __restrict__ tail,
+                                                                  __nv_bfloat16* __restrict__ out, int B, int L,
+                                                                  int d) {
+  const int c8 = d / 8;
+  const long long total = static_cast<long long>(B) * L * c8;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int cc = static_cast<int>(i % c8) * 8;
+    const long long bl = i / c8;
+    const int l = static_cast<int>(bl % L);
+    const int b = static_cast<int>(bl / L);
+    const __nv_bfloat16* ub = u + static_cast<long long>(b) * L * d;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float cur[8];
+    for (int k = 0; k < K; ++k) {
+      const int ls = l - k;
+      float xv[8];
+      if (ls >= 0) {
+        unpack8(*reinterpret_cast<const uint4*>(ub + static_cast<long long>(ls) * d + cc), xv);
+      } else if (tail != nullptr) {
+        unpack8(*reinterpret_cast<const uint4*>(tail + (static_cast<long long>(b) * (K - 1) + (K - 1 + ls)) * d + cc),
+                xv);
+      } else {
+        break;   // everything further back is zero
+      }
+      if (k == 0) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) cur[e] = xv[e];
+      }
+      const float4 h0 = __ldg(reinterpret_cast<const float4*>(ht + static_cast<long long>(k) * d + cc));
+      const float4 h1 = __ldg(reinterpret_cast<const float4*>(ht + static_cast<long long>(k) * d + cc + 4));
+      const float hv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = fmaf(hv[e], xv[e], acc[e]);
+    }
+    const long long o = (static_cast<long long>(b) * L + l) * d + cc;
+    float g[8];
+    if (x2 != nullptr) {
+      unpack8(*reinterpret_cast<const uint4*>(x2 + o), g);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) g[e] = 1.f;
+    }
+    const float4 d0 = __ldg(reinterpret_cast<const float4*>(D + cc));
+    const float4 d1 = __ldg(reinterpret_cast<const float4*>(D + cc + 4));
+    const float dv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+    float r[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float conv = __bfloat162float(__float2bfloat16(acc[e]));
+      r[e] = g[e] * __bfloat162float(__float2bfloat16(conv + cur[e] * dv[e]));
+    }
+    *reinterpret_cast<uint4*>(out + o) = pack8(r);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ FFT-conv epilogue
+// y: fp32 [B][d][n] (channel-major, the inverse FFT's layout; first L of n samples used), u, x2: bf16 [B][L][d].
+// out[b][l][c] = x2 * (bf16(y[b][c][l]) + D[c] * u).  A 32 x 32 tile goes through shared memory so that both the
+// fp32 reads (along l) and the bf16 accesses (along c) are coalesced.
+__global__ void __launch_bounds__(256) fftconv_epilogue_kernel(const float* __restrict__ y, int n,
+                                                               const __nv_bfloat16* __restrict__ u,
+                                                               const float* __restrict__ D,
+                                                               const __nv_bfloat16* __restrict__ x2,
+                                                               __nv_bfloat16* __restrict__ out, int B, int L, int d) {
+  __shared__ float tile[32][33];
+  const int tl = (L + 31) / 32, tc = (d + 31) / 32;
+  const long long tiles = static_cast<long long>(B) * tl * tc;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 8 rows of 32
+  for (long long t = blockIdx.x; t < tiles; t += gridDim.x) {
+    const int ct = static_cast<int>(t % tc);
+    const int lt = static_cast<int>((t / tc) % tl);
+    const int b = static_cast<int>(t / (static_cast<long long>(tc) * tl));
+    const int l0 = lt * 32, c0 = ct * 32;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = c0 + ty + k * 8, l = l0 + tx;
+      tile[ty + k * 8][tx] = (c < d && l < L) ? y[(static_cast<long long>(b) * d + c) * n + l] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int l = l0 + ty + k * 8, c = c0 + tx;
+      if (l < L && c < d) {
+        const long long o = (static_cast<long long>(b) * L + l) * d + c;
+        const float conv = __bfloat162float(__float2bfloat16(tile[tx][ty + k * 8]));
+        const float yy = __bfloat162float(__float2bfloat16(conv + __bfloat162float(u[o]) * D[c]));
+        const float g = x2 == nullptr ? 1.f : __bfloat162float(x2[o]);
+        out[o] = __float2bfloat16(g * yy);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------------------------------ hcl decode step
+// state [B][d][S] fp32 (updated in place), lam / res [d][S] fp32, u / x2 / out [B][d] bf16.
+__global__ void __launch_bounds__(256) pole_step_kernel(float* __restrict__ state, const float* __restrict__ lam,
+                                                        const float* __restrict__ res,
+                                                        const __nv_bfloat16* __restrict__ u,
+                                                        const float* __restrict__ D,
+                                                        const __nv_bfloat16* __restrict__ x2,
+                                                        __nv_bfloat16* __restrict__ out, int B, int d, int S) {
+  const long long total = static_cast<long long>(B) * d;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % d);
+    const float uv = __bfloat162float(u[i]);
+    float* s = state + i * S;
+    float acc = 0.f;
+    for (int k = 0; k < S; ++k) {
+      const float v = s[k] * lam[static_cast<long long>(c) * S + k] + uv;
+      s[k] = v;
+      acc += v * res[static_cast<long long>(c) * S + k];
+    }
+    const float yy = __bfloat162float(__float2bfloat16(acc)) + uv * D[c];
+    const float g = x2 == nullptr ? 1.f : __bfloat162float(x2[i]);
+    out[i] = __float2bfloat16(g * __bfloat162float(__float2bfloat16(yy)));
+  }
+}
+
+// ------------------------------------------------------------------------------------------ elementwise sets
+enum { EW_GELU_NEW = 0, EW_ADD2 = 1, EW_BIAS_RESIDUAL = 2, EW_SCALE_SHIFT_GELU = 3, EW_SILU_MUL = 4 };
+
+__device__ __forceinline__ float gelu_new_f(float x) {
+  // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), the "gelu_new" of GPT-J / ProGen2
+  const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(inner));
+}
+__device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+
+// x, a, b: bf16 [R][C]; v0 / v1: fp32 [C] per-channel vectors.  C a multiple of 8.
+//   GELU_NEW:          out = gelu_new(x)
+//   ADD2:              out = x + a + b                      (residual_add2; b may be null)
+//   BIAS_RESIDUAL:     out = x + v0[c] + a                  (a may be null)
+//   SCALE_SHIFT_GELU:  out = gelu_erf(x * v0[c] + v1[c])    (folded batch norm + GELU)
+//   SILU_MUL:          out = silu(x) * a
+template <int OP>
+__global__ void __launch_bounds__(256) ew_kernel(const __nv_bfloat16* __restrict__ x,
+                                                 const __nv_bfloat16* __restrict__ a,
+                                                 const __nv_bfloat16* __restrict__ b, const float* __restrict__ v0,
+                                                 const float* __restrict__ v1, __nv_bfloat16* __restrict__ out,
+                                                 long long R, int C) {
+  const int c8 = C / 8;
+  const long long total = R * c8;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % c8) * 8;
+    float xv[8], av[8], bv[8], o[8];
+    unpack8(reinterpret_cast<const uint4*>(x)[i], xv);
+    if (a != nullptr) unpack8(reinterpret_cast<const uint4*>(a)[i], av);
+    if (b != nullptr) unpack8(reinterpret_cast<const uint4*>(b)[i], bv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      if (OP == EW_GELU_NEW) {
+        o[e] = gelu_new_f(xv[e]);
+      } else if (OP == EW_ADD2) {
+        o[e] = xv[e] + (a != nullptr ? av[e] : 0.f) + (b != nullptr ? bv[e] : 0.f);
+      } else if (OP == EW_BIAS_RESIDUAL) {
+        o[e] = xv[e] + v0[c + e] + (a != nullptr ? av[e] : 0.f);
+      } else if (OP == EW_SCALE_SHIFT_GELU) {
+        o[e] = gelu_erf_f(fmaf(xv[e], v0[c + e], v1[c + e]));
+      } else {
+        o[e] = (xv[e] / (1.0f + __expf(-xv[e]))) * av[e];
+      }
+    }
+    reinterpret_cast<uint4*>(out)[i] = pack8(o);
+  }
+}
+
+// rotary_split_qkv: qkv [T][3][H][Dh] bf16 (one fused projection row per token) -> q, k with rotary applied to
+// the first `rot` dims of each head (GPT-J interleaved pairs), v copied; outputs [T][H][Dh].  pos: int32 [T].
+__global__ void __launch_bounds__(256) rotary_split_qkv_kernel(const __nv_bfloat16* __restrict__ qkv,
+                                                               const int* __restrict__ pos,
+                                                               __nv_bfloat16* __restrict__ q,
+                                                               __nv_bfloat16* __restrict__ k,
+                                                               __nv_bfloat16* __restrict__ v, long long T, int H,
+                                                               int Dh, int rot, float base) {
+  const int half = Dh / 2;
+  const long long total = T * H * half;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int p = static_cast<int>(i % half);
+    const long long th = i / half;
+    const int h = static_cast<int>(th % H);
+    const long long t = th / H;
+    const long long src = (t * 3 * H + h) * Dh + 2 * p;
+    const long long dst = (t * H + h) * Dh + 2 * p;
+    const long long hs = static_cast<long long>(H) * Dh;
+    float q0 = __bfloat162float(qkv[src]), q1 = __bfloat162float(qkv[src + 1]);
+    float k0 = __bfloat162float(qkv[src + hs]), k1 = __bfloat162float(qkv[src + hs + 1]);
+    if (2 * p < rot) {
+      const float inv = powf(base, -static_cast<float>(2 * p) / static_cast<float>(rot));
+      float sn, cs;
+      sincosf(static_cast<float>(pos[t]) * inv, &sn, &cs);
+      const float a0 = q0 * cs - q1 * sn, a1 = q1 * cs + q0 * sn;
+      const float b0 = k0 * cs - k1 * sn, b1 = k1 * cs + k0 * sn;
+      q0 = a0; q1 = a1; k0 = b0; k1 = b1;
+    }
+    *reinterpret_cast<__nv_bfloat162*>(q + dst) = __floats2bfloat162_rn(q0, q1);
+    *reinterpret_cast<__nv_bfloat162*>(k + dst) = __floats2bfloat162_rn(k0, k1);
+    *reinterpret_cast<__nv_bfloat162*>(v + dst) =
+        *reinterpret_cast<const __nv_bfloat162*>(qkv + src + 2 * hs);
+  }
+}
+
+// softmax over rows of x + a + b (fp32 in and out; a, b may be null); one warp per row, C <= 4096
+__global__ void __launch_bounds__(256) add2_softmax_rows_kernel(const float* __restrict__ x,
+                                                                const float* __restrict__ a,
+                                                                const float* __restrict__ b,
+                                                                float* __restrict__ out, long long R, int C) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  for (long long r = static_cast<long long>(blockIdx.x) * wpb + (threadIdx.x >> 5); r < R;
+       r += static_cast<long long>(gridDim.x) * wpb) {
+    const long long o = r * C;
+    float mx = -3.0e38f;
+    for (int c = lane; c < C; c += 32) {
+      const float v = x[o + c] + (a ? a[o + c] : 0.f) + (b ? b[o + c] : 0.f);
+      mx = fmaxf(mx, v);
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+    float sum = 0.f;
+    for (int c = lane; c < C; c += 32) {
+      const float v = x[o + c] + (a ? a[o + c] : 0.f) + (b ? b[o + c] : 0.f);
+      sum += __expf(v - mx);
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int c = lane; c < C; c += 32) {
+      const float v = x[o + c] + (a ? a[o + c] : 0.f) + (b ? b[o + c] : 0.f);
+      out[o + c] = __expf(v - mx) * inv;
+    }
+  }
+}
+
+// pool2 over the sequence axis of [B][L][C] bf16: mode 0 = max, 1 = mean, 2 = softmax-weighted with logits
+// w [B][L][C] (attention pooling of width 2).  L even.
+__global__ void __launch_bounds__(256) pool2_kernel(const __nv_bfloat16* __restrict__ x,
+                                                    const __nv_bfloat16* __restrict__ w,
+                                                    __nv_bfloat16* __restrict__ out, int B, int L, int C, int mode) {
+  const int c8 = C / 8;
+  const long long total = static_cast<long long>(B) * (L / 2) * c8;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % c8) * 8;
+    const long long bl = i / c8;
+    const int l2 = static_cast<int>(bl % (L / 2));
+    const int b = static_cast<int>(bl / (L / 2));
+    const long long s0 = (static_cast<long long>(b) * L + 2 * l2) * C + c;
+    float x0[8], x1[8], o[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + s0), x0);
+    unpack8(*reinterpret_cast<const uint4*>(x + s0 + C), x1);
+    if (mode == 2) {
+      float w0[8], w1[8];
+      unpack8(*reinterpret_cast<const uint4*>(w + s0), w0);
+      unpack8(*reinterpret_cast<const uint4*>(w + s0 + C), w1);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float m = fmaxf(w0[e], w1[e]);
+        const float e0 = __expf(w0[e] - m), e1 = __expf(w1[e] - m);
+        o[e] = (x0[e] * e0 + x1[e] * e1) / (e0 + e1);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = mode == 0 ? fmaxf(x0[e], x1[e]) : 0.5f * (x0[e] + x1[e]);
+    }
+    *reinterpret_cast<uint4*>(out + (static_cast<long long>(b) * (L / 2) + l2) * C + c) = pack8(o);
+  }
+}
+
+// residual + LayerNorm: s = x + res (written to sum_out when not null), out = LN(s) * gamma + beta
+template <int CHUNKS>
+__global__ void __launch_bounds__(256) residual_ln_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          const __nv_bfloat16* __restrict__ res,
+                                                          const float* __restrict__ gamma,
+                                                          const float* __restrict__ beta,
+                                                          __nv_bfloat16* __restrict__ sum_out,
+                                                          __nv_bfloat16* __restrict__ out, long long R, int C,
+                                                          float eps) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  for (long long r = static_cast<long long>(blockIdx.x) * wpb + (threadIdx.x >> 5); r < R;
+       r += static_cast<long long>(gridDim.x) * wpb) {
+    float v[CHUNKS][8];
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < C) {
+        float rr[8];
+        unpack8(*reinterpret_cast<const uint4*>(x + r * C + c), v[k]);
+        unpack8(*reinterpret_cast<const uint4*>(res + r * C + c), rr);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          // the sum is rounded to the activation type first, as the unfused residual add does
+          v[k][j] = __bfloat162float(__float2bfloat16(v[k][j] + rr[j]));
+          sum += v[k][j];
+        }
+        if (sum_out != nullptr) *reinterpret_cast<uint4*>(sum_out + r * C + c) = pack8(v[k]);
+      }
+    }
+    sum = warp_sum(sum);
+    const float mu = sum / C;
+    float var = 0.f;
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < C) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) var += (v[k][j] - mu) * (v[k][j] - mu);
+      }
+    }
+    var = warp_sum(var);
+    const float rstd = rsqrtf(var / C + eps);
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < C) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (v[k][j] - mu) * rstd * gamma[c + j] + (beta ? beta[c + j] : 0.f);
+        *reinterpret_cast<uint4*>(out + r * C + c) = pack8(o);
+      }
+    }
+  }
+}
+
+}  // namespace ubm
+
+using namespace ubm;
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+extern "C" int ubm_rmsnorm_rows(const void* x, const void* scale, void* out, long long R, int C, float eps,
+                                void* stream) {
+  if (R <= 0 || C <= 0 || (C & 7) || !aligned16(x) || !aligned16(out) || !aligned16(scale))
+    return UBM_ERR_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = seq_grid(R, 8);
+  const __nv_bfloat16* xx = static_cast<const __nv_bfloat16*>(x);
+  const float* sc = static_cast<const float*>(scale);
+  __nv_bfloat16* oo = static_cast<__nv_bfloat16*>(out);
+  if (C <= 1024) rmsnorm_rows_kernel<4><<<grid, 256, 0, st>>>(xx, sc, oo, R, C, eps);
+  else if (C <= 2048) rmsnorm_rows_kernel<8><<<grid, 256, 0, st>>>(xx, sc, oo, R, C, eps);
+  else if (C <= 4096) rmsnorm_rows_kernel<16><<<grid, 256, 0, st>>>(xx, sc, oo, R, C, eps);
+  else rmsnorm_rows_wide_kernel<<<grid, 256, 0, st>>>(xx, sc, oo, R, C, eps);
+  UBM_CHECK_LAUNCH("rmsnorm_rows_kernel");
+  return UBM_OK;
+}
+
+// z: bf16 [B][L][3d]; ht: fp32 [K][3d] (tap-major); tail: bf16 [B][K-1][3d] or null; u, x2: bf16 [B][L][d].
+extern "C" int ubm_fir_gate3(const void* z, const void* ht, const void* tail, void* u, void* x2, int B, int L, int d,
+                             int K, void* stream) {
+  // three filter windows live in registers at once: up to four taps (the input stage of Hyena uses three)
+  if (B <= 0 || L <= 0 || d <= 0 || (d & 7) || K < 1 || K > 4) return UBM_ERR_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long total = static_cast<long long>(B) * ((L + kFirTL - 1) / kFirTL) * (d / 8);
+  const int grid = seq_grid(total, 128);
+#define UBM_FG3(KK)                                                                                            \
+  fir_gate3_kernel<KK><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(z), static_cast<const float*>(ht), \
+                                             static_cast<const __nv_bfloat16*>(tail),                           \
+                                             static_cast<__nv_bfloat16*>(u), static_cast<__nv_bfloat16*>(x2), B, L, d)
+  switch (K) {
+    case 1: UBM_FG3(1); break;
+    case 2: UBM_FG3(2); break;
+    case 3: UBM_FG3(3); break;
+    default: UBM_FG3(4); break;
+  }
+#undef UBM_FG3
+  UBM_CHECK_LAUNCH("fir_gate3_kernel");
+  return UBM_OK;
+}
+
+// u: bf16 [B][L][d]; ht: fp32 [K][d]; D: fp32 [d]; x2: bf16 [B][L][d] or null; tail: bf16 [B][K-1][d] or null.
+extern "C" int ubm_fir_inner_gate(const void* u, const void* ht, const void* D, const void* x2, const void* tail,
+                                  void* out, int B, int L, int d, int K, void* stream) {
+  if (B <= 0 || L <= 0 || d <= 0 || (d & 7) || K < 1) return UBM_ERR_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* uu = static_cast<const __nv_bfloat16*>(u);
+  const float* hh = static_cast<const float*>(ht);
+  const float* dd = static_cast<const float*>(D);
+  const __nv_bfloat16* xx = static_cast<const __nv_bfloat16*>(x2);
+  const __nv_bfloat16* tt = static_cast<const __nv_bfloat16*>(tail);
+  __nv_bfloat16* oo = static_cast<__nv_bfloat16*>(out);
+  if (K <= 8) {
+    const long long total = static_cast<long long>(B) * ((L + kFirTL - 1) / kFirTL) * (d / 8);
+    const int grid = seq_grid(total, 128);
+#define UBM_FIG(KK) fir_inner_gate_kernel<KK><<<grid, 128, 0, st>>>(uu, hh, dd, xx, tt, oo, B, L, d)
+    switch (K) {
+      case 1: UBM_FIG(1); break;
+      case 2: UBM_FIG(2); break;
+      case 3: UBM_FIG(3); break;
+      case 4: UBM_FIG(4); break;
+      case 5: UBM_FIG(5); break;
+      case 6: UBM_FIG(6); break;
+      case 7: UBM_FIG(7); break;
+      default: UBM_FIG(8); break;
+    }
+#undef UBM_FIG
+  } else {
+    const long long total = static_cast<long long>(B) * L * (d / 8);
+    fir_inner_gate_long_kernel<<<seq_grid(total, 128), 128, 0, st>>>(uu, hh, K, dd, xx, tt, oo, B, L, d);
+  }
+  UBM_CHECK_LAUNCH("fir_inner_gate_kernel");
+  return UBM_OK;
+}
+
+extern "C" int ubm_fftconv_epilogue(const void* y, int n, const void* u, const void* D, const void* x2, void* out,
+                                    int B, int L, int d, void* stream) {
+  if (B <= 0 || L <= 0 || d <= 0 || n < L) return UBM_ERR_ARGUMENT;
+  const long long tiles = static_cast<long long>(B) * ((L + 31) / 32) * ((d + 31) / 32);
+  fftconv_epilogue_kernel<<<seq_grid(tiles, 1), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(y), n, static_cast<const __nv_bfloat16*>(u), static_cast<const float*>(D),
+      static_cast<const __nv_bfloat16*>(x2), static_cast<__nv_bfloat16*>(out), B, L, d);
+  UBM_CHECK_LAUNCH("fftconv_epilogue_kernel");
+  return UBM_OK;
+}
+
+extern "C" int ubm_pole_step(void* state, const void* lam, const void* res, const void* u, const void* D,
+                             const void* x2, void* out, int B, int d, int S, void* stream) {
+  if (B <= 0 || d <= 0 || S <= 0) return UBM_ERR_ARGUMENT;
+  pole_step_kernel<<<seq_grid(static_cast<long long>(B) * d, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<float*>(state), static_cast<const float*>(lam), static_cast<const float*>(res),
+      static_cast<const __nv_bfloat16*>(u), static_cast<const float*>(D), static_cast<const __nv_bfloat16*>(x2),
+      static_cast<__nv_bfloat16*>(out), B, d, S);
+  UBM_CHECK_LAUNCH("pole_step_kernel");
+  return UBM_OK;
+}
+
+// op: 0 gelu_new, 1 add2, 2 bias_residual, 3 scale_shift_gelu, 4 silu_mul (see ew_kernel)
+extern "C" int ubm_elementwise(int op, const void* x, const void* a, const void* b, const void* v0, const void* v1,
+                               void* out, long long R, int C, void* stream) {
+  if (R <= 0 || C <= 0 || (C & 7) || !aligned16(x) || !aligned16(out) || !aligned16(a) || !aligned16(b))
+    return UBM_ERR_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = seq_grid(R * (C / 8), 256);
+  const __nv_bfloat16* xx = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* aa = static_cast<const __nv_bfloat16*>(a);
+  const __nv_bfloat16* bb = static_cast<const __nv_bfloat16*>(b);
+  const float* p0 = static_cast<const float*>(v0);
+  const float* p1 = static_cast<const float*>(v1);
+  __nv_bfloat16* oo = static_cast<__nv_bfloat16*>(out);
+  switch (op) {
+    case EW_GELU_NEW: ew_kernel<EW_GELU_NEW><<<grid, 256, 0, st>>>(xx, aa, bb, p0, p1, oo, R, C); break;
+    case EW_ADD2: ew_kernel<EW_ADD2><<<grid, 256, 0, st>>>(xx, aa, bb, p0, p1, oo, R, C); break;
+    case EW_BIAS_RESIDUAL:
+      if (v0 == nullptr) return UBM_ERR_ARGUMENT;
+      ew_kernel<EW_BIAS_RESIDUAL><<<grid, 256, 0, st>>>(xx, aa, bb, p0, p1, oo, R, C);
+      break;
+    case EW_SCALE_SHIFT_GELU:
+      if (v0 == nullptr || v1 == nullptr) return UBM_ERR_ARGUMENT;
+      ew_kernel<EW_SCALE_SHIFT_GELU><<<grid, 256, 0, st>>>(xx, aa, bb, p0, p1, oo, R, C);
+      break;
+    case EW_SILU_MUL:
+      if (a == nullptr) return UBM_ERR_ARGUMENT;
+      ew_kernel<EW_SILU_MUL><<<grid, 256, 0, st>>>(xx, aa, bb, p0, p1, oo, R, C);
+      break;
+    default: return UBM_ERR_ARGUMENT;
+  }
+  UBM_CHECK_LAUNCH("ew_kernel");
+  return UBM_OK;
+}
+
+extern "C" int ubm_rotary_split_qkv(const void* qkv, const void* pos, void* q, void* k, void* v, long long T, int H,
+                                    int Dh, int rot, float base, void* stream) {
+  if (T <= 0 || H <= 0 || Dh <= 0 || (Dh & 1) || rot < 0 || rot > Dh || (rot & 1)) return UBM_ERR_ARGUMENT;
+  rotary_split_qkv_kernel<<<seq_grid(T * H * (Dh / 2), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(qkv), static_cast<const int*>(pos), static_cast<__nv_bfloat16*>(q),
+      static_cast<__nv_bfloat16*>(k), static_cast<__nv_bfloat16*>(v), T, H, Dh, rot, base);
+  UBM_CHECK_LAUNCH("rotary_split_qkv_kernel");
+  return UBM_OK;
+}
+
+extern "C" int ubm_add2_softmax_rows(const void* x, const void* a, const void* b, void* out, long long R, int C,
+                                     void* stream) {
+  if (R <= 0 || C <= 0) return UBM_ERR_ARGUMENT;
+  add2_softmax_rows_kernel<<<seq_grid(R, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(x), static_cast<const float*>(a), static_cast<const float*>(b),
+      static_cast<float*>(out), R, C);
+  UBM_CHECK_LAUNCH("add2_softmax_rows_kernel");
+  return UBM_OK;
+}
+
+extern "C" int ubm_pool2(const void* x, const void* w, void* out, int B, int L, int C, int mode, void* stream) {
+  if (B <= 0 || L <= 0 || (L & 1) || C <= 0 || (C & 7) || mode < 0 || mode > 2 || (mode == 2 && w == nullptr))
+    return UBM_ERR_ARGUMENT;
+  pool2_kernel<<<seq_grid(static_cast<long long>(B) * (L / 2) * (C / 8), 256), 256, 0,
+                 static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x),
+                                                      static_cast<const __nv_bfloat16*>(w),
+                                                      static_cast<__nv_bfloat16*>(out), B, L, C, mode);
+  UBM_CHECK_LAUNCH("pool2_kernel");
+  return UBM_OK;
+}
+
+extern "C" int ubm_residual_ln(const void* x, const void* res, const void* gamma, const void* beta, void* sum_out,
+                               void* out, long long R, int C, float eps, void* stream) {
+  if (R <= 0 || C <= 0 || (C & 7) || C > 4096 || res == nullptr || gamma == nullptr) return UBM_ERR_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = seq_grid(R, 8);
+  const __nv_bfloat16* xx = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* rr = static_cast<const __nv_bfloat16*>(res);
+  const float* g = static_cast<const float*>(gamma);
+  const float* bt = static_cast<const float*>(beta);
+  __nv_bfloat16* so = static_cast<__nv_bfloat16*>(sum_out);
+  __nv_bfloat16* oo = static_cast<__nv_bfloat16*>(out);
+  if (C <= 1024) residual_ln_kernel<4><<<grid, 256, 0, st>>>(xx, rr, g, bt, so, oo, R, C, eps);
+  else if (C <= 2048) residual_ln_kernel<8><<<grid, 256, 0, st>>>(xx, rr, g, bt, so, oo, R, C, eps);
+  else residual_ln_kernel<16><<<grid, 256, 0, st>>>(xx, rr, g, bt, so, oo, R, C, eps);
+  UBM_CHECK_LAUNCH("residual_ln_kernel");
+  return UBM_OK;
+}

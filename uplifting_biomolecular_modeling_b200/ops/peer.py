@@ -71,3 +71,50 @@ def attention_peer_bias(q, k, v, bias_ptrs: Sequence[int], peer_rows: Sequence[i
                                                   native.current_stream(q.device))
     native.check(rc, "ubm_attention_d32_peer_bias")
     return out
+
+
+native.declare("ubm_gemm_bf16_scatter_rows",
+               [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_float,
+                c_void_p, c_void_p])
+native.declare("ubm_sum_slots", [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p])
+
+
+class ReduceScatterState:
+    """Slot buffers of the GEMM -> reduce-scatter: on every GPU two symmetric buffers [P][rows_per_rank][N] bf16
+    (alternating between calls, so a sender never overwrites slots their owner is still adding)."""
+
+    def __init__(self, heap, rows_per_rank: int, n: int):
+        self.heap, self.rows, self.n = heap, rows_per_rank, n
+        self.bufs = [heap.alloc((heap.world, rows_per_rank, n), torch.bfloat16) for _ in range(2)]
+        self.calls = 0
+
+
+def gemm_reduce_scatter(x: torch.Tensor, w: torch.Tensor, state: ReduceScatterState, bias=None, residual=None,
+                        alpha: float = 1.0) -> torch.Tensor:
+    """Row-parallel linear of a tensor-parallel layer.  x: bf16 [M, K_local]; w: bf16 [N, K_local] (this rank's
+    slice of the contraction dimension).  Every rank's GEMM epilogue stores its partial product straight into
+    the slot it owns in the memory of the GPU that owns those output rows (rows m of GPU m // rows_per_rank);
+    after a barrier that orders the stores each GPU adds its P slots in rank order (deterministic) with bias and
+    residual.  Returns this rank's rows [rows_per_rank, N] of sum_over_ranks(x @ w.T)."""
+    heap = state.heap
+    P, r = heap.world, heap.rank
+    M, K = x.shape
+    N = w.shape[0]
+    if M > P * state.rows or N != state.n:
+        raise ValueError("shape does not fit the slot buffers")
+    buf = state.bufs[state.calls & 1]
+    state.calls += 1
+    slot_bytes = state.rows * N * 2
+    ptrs = _ptrs([buf.ptr(q, r * slot_bytes) for q in range(P)])
+    st = native.status_tensor(x.device)
+    rc = native.lib().ubm_gemm_bf16_scatter_rows(native.ptr(x), native.ptr(w), ptrs, P, state.rows, M, N, K,
+                                                 x.stride(0), w.stride(0), N, 0, float(alpha), native.ptr(st),
+                                                 native.current_stream(x.device))
+    native.check(rc, "ubm_gemm_bf16_scatter_rows")
+    heap.barrier()
+    out = torch.empty((state.rows, N), dtype=torch.bfloat16, device=x.device)
+    b32 = None if bias is None else bias.float().contiguous()
+    rc = native.lib().ubm_sum_slots(native.ptr(buf.local), state.rows * N, P, native.ptr(b32), native.ptr(residual),
+                                    native.ptr(out), state.rows, N, native.current_stream(x.device))
+    native.check(rc, "ubm_sum_slots")
+    return out

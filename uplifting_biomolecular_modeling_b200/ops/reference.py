@@ -164,3 +164,81 @@ def window_attention(q, k, v, bias, wq: int = 32, wk: int = 128):
     p = torch.softmax(s, dim=-1)
     o = torch.einsum("bhwqk,bhwkd->bhwqd", p, vw.float())
     return o.reshape(B, H, A, D).to(q.dtype)
+
+
+# ------------------------------------------------------------------------------------------
+# Plain statements of the row / sequence kernels in ops.seq (fp32 arithmetic on the given values).
+def rmsnorm_rows(x, scale, eps: float = 1e-6):
+    x32 = x.float()
+    return x32 * torch.rsqrt(x32.pow(2).mean(-1, keepdim=True) + eps) * scale.float()
+
+
+def causal_fir(x, h, tail=None):
+    """x: [B, L, C]; h: [C, K] (h[:, 0] multiplies the current sample); tail: [B, K-1, C] or None."""
+    B, L, C = x.shape
+    K = h.shape[1]
+    pad = x.new_zeros((B, K - 1, C)) if tail is None else tail.to(x.dtype)
+    xp = torch.cat([pad, x], 1).float()
+    y = torch.zeros((B, L, C), dtype=torch.float32, device=x.device)
+    for k in range(K):
+        y = y + h[:, k].float() * xp[:, K - 1 - k:K - 1 - k + L]
+    return y
+
+
+def fir_gate3(z, h, tail=None):
+    zf = causal_fir(z, h, tail)
+    x1, x2, v = zf.chunk(3, -1)
+    return x1 * v, x2
+
+
+def fir_inner_gate(u, h, D, x2, tail=None):
+    y = causal_fir(u, h, tail) + u.float() * D.float()
+    return y if x2 is None else x2.float() * y
+
+
+def fftconv_epilogue(y, u, D, x2):
+    L = u.shape[1]
+    out = y[..., :L].transpose(1, 2).float() + u.float() * D.float()
+    return out if x2 is None else x2.float() * out
+
+
+def pole_step(state, lam, res, u, D, x2):
+    s = state * lam.float().unsqueeze(0) + u.float().unsqueeze(-1)
+    y = (s * res.float().unsqueeze(0)).sum(-1) + u.float() * D.float()
+    return (y if x2 is None else x2.float() * y), s
+
+
+def gelu_new(x):
+    x = x.float()
+    return 0.5 * x * (1.0 + torch.tanh(0.7978845608028654 * (x + 0.044715 * x ** 3)))
+
+
+def rotary_split_qkv(qkv, pos, heads: int, rot: int, base: float = 10000.0):
+    T = qkv.shape[0]
+    Dh = qkv.shape[1] // (3 * heads)
+    q, k, v = qkv.float().view(T, 3, heads, Dh).unbind(1)
+    inv = base ** (-torch.arange(0, rot, 2, device=qkv.device, dtype=torch.float32) / rot)
+    ang = pos.float()[:, None] * inv[None, :]
+    sn, cs = torch.sin(ang)[:, None, :], torch.cos(ang)[:, None, :]
+
+    def rotate(t):
+        t = t.clone()
+        a, b = t[..., 0:rot:2], t[..., 1:rot:2]
+        t[..., 0:rot:2], t[..., 1:rot:2] = a * cs - b * sn, b * cs + a * sn
+        return t
+    return rotate(q), rotate(k), v
+
+
+def pool2(x, mode: str = "max", w=None):
+    B, L, C = x.shape
+    xp = x.float().view(B, L // 2, 2, C)
+    if mode == "max":
+        return xp.max(2).values
+    if mode == "mean":
+        return xp.mean(2)
+    return (xp * torch.softmax(w.float().view(B, L // 2, 2, C), 2)).sum(2)
+
+
+def residual_ln(x, res, gamma, beta, eps: float = 1e-5):
+    s = (x.float() + res.float()).to(x.dtype).float()
+    return torch.nn.functional.layer_norm(s, (s.shape[-1],), gamma.float(), None if beta is None else beta.float(), eps)

@@ -17,6 +17,8 @@ native.declare("ubm_adaln_rows", [c_void_p] * 4 + [c_ll, c_int, c_ll, c_ll, c_fl
 native.declare("ubm_gate_residual", [c_void_p] * 4 + [c_ll, c_int, c_ll, c_ll, c_void_p])
 native.declare("ubm_swiglu_rows", [c_void_p] * 2 + [c_ll, c_int, c_void_p])
 native.declare("ubm_swiglu3_rows", [c_void_p] * 2 + [c_ll, c_int, c_void_p])
+native.declare("ubm_segment_mean", [c_void_p] * 3 + [c_int] * 5 + [c_void_p])
+native.declare("ubm_gather_rows_add", [c_void_p] * 4 + [c_int] * 4 + [c_void_p])
 
 _DT = {torch.bfloat16: 0, torch.float32: 1}
 
@@ -123,4 +125,28 @@ def swiglu_rows(ab: torch.Tensor) -> torch.Tensor:
     out = torch.empty(ab.shape[:-1] + (Hd,), dtype=ab.dtype, device=ab.device)
     rc = native.lib().ubm_swiglu_rows(native.ptr(ab), native.ptr(out), R, Hd, native.current_stream(ab.device))
     native.check(rc, "ubm_swiglu_rows")
+    return out
+
+
+def segment_mean(t: torch.Tensor, table: torch.Tensor, n_tokens: int) -> torch.Tensor:
+    """Mean of atom rows per token.  t: bf16 [B, A, C]; table: int32 [N, M] atom indices (-1 = none)."""
+    t = t.contiguous()
+    B, A, C = t.shape
+    out = torch.empty((B, n_tokens, C), dtype=t.dtype, device=t.device)
+    rc = native.lib().ubm_segment_mean(native.ptr(t), native.ptr(table), native.ptr(out), B, A, n_tokens,
+                                       table.shape[1], C, native.current_stream(t.device))
+    native.check(rc, "ubm_segment_mean")
+    return out
+
+
+def gather_rows_add(q: Optional[torch.Tensor], a: torch.Tensor, a2t: torch.Tensor) -> torch.Tensor:
+    """q + a[:, a2t] (token rows broadcast to their atoms).  q: bf16 [B, A, C] or None; a: [B, N, C]; a2t: int32 [A]."""
+    a = a.contiguous()
+    B, N, C = a.shape
+    A = a2t.shape[0]
+    out = torch.empty((B, A, C), dtype=a.dtype, device=a.device)
+    qq = None if q is None else q.contiguous()
+    rc = native.lib().ubm_gather_rows_add(native.ptr(qq), native.ptr(a), native.ptr(a2t), native.ptr(out), B, A, N, C,
+                                          native.current_stream(a.device))
+    native.check(rc, "ubm_gather_rows_add")
     return out

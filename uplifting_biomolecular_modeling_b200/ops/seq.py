@@ -1,0 +1,198 @@
+"""Python face of the row / sequence kernels for the language-model and genomics families
+(``csrc/seq_sm100.cu``): RMSNorm, the causal FIR stages of the Hyena operators with their gates folded in, the
+FFT-convolution epilogue, the decode step of the pole-residue filter, and the exact elementwise sets (gelu_new,
+residual adds, bias + residual, folded batch-norm + GELU, rotary split of a fused q|k|v row, softmax of a
+three-term sum, width-2 pooling, residual + LayerNorm).  Every wrapper has a plain statement of the same name in
+:mod:`ops.reference`.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import native
+from .native import c_float, c_int, c_ll, c_void_p
+
+native.declare("ubm_rmsnorm_rows", [c_void_p] * 3 + [c_ll, c_int, c_float, c_void_p])
+native.declare("ubm_fir_gate3", [c_void_p] * 5 + [c_int] * 4 + [c_void_p])
+native.declare("ubm_fir_inner_gate", [c_void_p] * 6 + [c_int] * 4 + [c_void_p])
+native.declare("ubm_fftconv_epilogue", [c_void_p, c_int] + [c_void_p] * 4 + [c_int] * 3 + [c_void_p])
+native.declare("ubm_pole_step", [c_void_p] * 7 + [c_int] * 3 + [c_void_p])
+native.declare("ubm_elementwise", [c_int] + [c_void_p] * 6 + [c_ll, c_int, c_void_p])
+native.declare("ubm_rotary_split_qkv", [c_void_p] * 5 + [c_ll, c_int, c_int, c_int, c_float, c_void_p])
+native.declare("ubm_add2_softmax_rows", [c_void_p] * 4 + [c_ll, c_int, c_void_p])
+native.declare("ubm_pool2", [c_void_p] * 3 + [c_int] * 4 + [c_void_p])
+native.declare("ubm_residual_ln", [c_void_p] * 6 + [c_ll, c_int, c_float, c_void_p])
+
+EW = {"gelu_new": 0, "add2": 1, "bias_residual": 2, "scale_shift_gelu": 3, "silu_mul": 4}
+
+
+def _bf16c(t: torch.Tensor) -> torch.Tensor:
+    if t.dtype != torch.bfloat16:
+        raise TypeError("bf16 activation expected")
+    return t.contiguous()
+
+
+def _f32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    return None if t is None else t.detach().float().contiguous()
+
+
+def _stream(t: torch.Tensor):
+    return native.current_stream(t.device)
+
+
+def rmsnorm_rows(x: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    x = _bf16c(x)
+    C = x.shape[-1]
+    out = torch.empty_like(x)
+    rc = native.lib().ubm_rmsnorm_rows(native.ptr(x), native.ptr(_f32(scale)), native.ptr(out), x.numel() // C, C,
+                                       float(eps), _stream(x))
+    native.check(rc, "ubm_rmsnorm_rows")
+    return out
+
+
+def taps_major(h: torch.Tensor) -> torch.Tensor:
+    """[C, K] filter -> fp32 [K, C] (tap-major, the layout the FIR kernels read)."""
+    return h.detach().float().t().contiguous()
+
+
+def fir_gate3(z: torch.Tensor, ht: torch.Tensor, tail: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """z: [B, L, 3d]; ht: fp32 [K, 3d] from :func:`taps_major`; tail: [B, K-1, 3d].  Returns (u, x2), each [B, L, d]."""
+    z = _bf16c(z)
+    B, L, C = z.shape
+    d = C // 3
+    u = torch.empty((B, L, d), dtype=torch.bfloat16, device=z.device)
+    x2 = torch.empty_like(u)
+    t = None if tail is None else _bf16c(tail)
+    rc = native.lib().ubm_fir_gate3(native.ptr(z), native.ptr(ht), native.ptr(t), native.ptr(u), native.ptr(x2),
+                                    B, L, d, ht.shape[0], _stream(z))
+    native.check(rc, "ubm_fir_gate3")
+    return u, x2
+
+
+def fir_inner_gate(u: torch.Tensor, ht: torch.Tensor, D: torch.Tensor, x2: Optional[torch.Tensor],
+                   tail: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x2 * (causal_fir(u, h) + D * u); u, x2: [B, L, d]; ht: fp32 [K, d]; tail: [B, K-1, d]."""
+    u = _bf16c(u)
+    B, L, d = u.shape
+    out = torch.empty_like(u)
+    x2c = None if x2 is None else _bf16c(x2)
+    t = None if tail is None else _bf16c(tail)
+    rc = native.lib().ubm_fir_inner_gate(native.ptr(u), native.ptr(ht), native.ptr(_f32(D)), native.ptr(x2c),
+                                         native.ptr(t), native.ptr(out), B, L, d, ht.shape[0], _stream(u))
+    native.check(rc, "ubm_fir_inner_gate")
+    return out
+
+
+def fftconv_epilogue(y: torch.Tensor, u: torch.Tensor, D: torch.Tensor, x2: Optional[torch.Tensor]) -> torch.Tensor:
+    """y: fp32 [B, d, n] (inverse FFT output, first L samples used); u, x2: [B, L, d] -> x2 * (y^T + D * u)."""
+    u = _bf16c(u)
+    B, L, d = u.shape
+    y = y.contiguous()
+    if y.dtype != torch.float32 or y.shape[0] != B or y.shape[1] != d or y.shape[2] < L:
+        raise ValueError("y must be fp32 [B, d, n >= L]")
+    out = torch.empty_like(u)
+    x2c = None if x2 is None else _bf16c(x2)
+    rc = native.lib().ubm_fftconv_epilogue(native.ptr(y), y.shape[2], native.ptr(u), native.ptr(_f32(D)),
+                                           native.ptr(x2c), native.ptr(out), B, L, d, _stream(u))
+    native.check(rc, "ubm_fftconv_epilogue")
+    return out
+
+
+def pole_step(state: torch.Tensor, lam: torch.Tensor, res: torch.Tensor, u: torch.Tensor, D: torch.Tensor,
+              x2: Optional[torch.Tensor]) -> torch.Tensor:
+    """state: fp32 [B, d, S], updated in place; u, x2: [B, d] -> x2 * (sum_s state * res + D * u)."""
+    if state.dtype != torch.float32 or not state.is_contiguous():
+        raise ValueError("state must be contiguous fp32")
+    u = _bf16c(u)
+    B, d, S = state.shape
+    out = torch.empty_like(u)
+    x2c = None if x2 is None else _bf16c(x2)
+    rc = native.lib().ubm_pole_step(native.ptr(state), native.ptr(_f32(lam)), native.ptr(_f32(res)), native.ptr(u),
+                                    native.ptr(_f32(D)), native.ptr(x2c), native.ptr(out), B, d, S, _stream(u))
+    native.check(rc, "ubm_pole_step")
+    return out
+
+
+def elementwise(op: str, x: torch.Tensor, a: Optional[torch.Tensor] = None, b: Optional[torch.Tensor] = None,
+                v0: Optional[torch.Tensor] = None, v1: Optional[torch.Tensor] = None) -> torch.Tensor:
+    x = _bf16c(x)
+    C = x.shape[-1]
+    out = torch.empty_like(x)
+    aa = None if a is None else _bf16c(a)
+    bb = None if b is None else _bf16c(b)
+    rc = native.lib().ubm_elementwise(EW[op], native.ptr(x), native.ptr(aa), native.ptr(bb), native.ptr(_f32(v0)),
+                                      native.ptr(_f32(v1)), native.ptr(out), x.numel() // C, C, _stream(x))
+    native.check(rc, "ubm_elementwise")
+    return out
+
+
+def gelu_new(x):
+    return elementwise("gelu_new", x)
+
+
+def residual_add2(x, a, b=None):
+    return elementwise("add2", x, a, b)
+
+
+def bias_residual(x, bias, res=None):
+    return elementwise("bias_residual", x, res, None, bias)
+
+
+def scale_shift_gelu(x, scale, shift):
+    return elementwise("scale_shift_gelu", x, None, None, scale, shift)
+
+
+def silu_mul(x, a):
+    return elementwise("silu_mul", x, a)
+
+
+def rotary_split_qkv(qkv: torch.Tensor, pos: torch.Tensor, heads: int, rot: int, base: float = 10000.0):
+    """qkv: [T, 3 * heads * Dh] -> (q, k, v) each [T, heads, Dh]; interleaved-pair rotary on the first ``rot`` dims."""
+    qkv = _bf16c(qkv)
+    T = qkv.shape[0]
+    Dh = qkv.shape[1] // (3 * heads)
+    q = torch.empty((T, heads, Dh), dtype=torch.bfloat16, device=qkv.device)
+    k, v = torch.empty_like(q), torch.empty_like(q)
+    p = pos.to(torch.int32).contiguous()
+    rc = native.lib().ubm_rotary_split_qkv(native.ptr(qkv), native.ptr(p), native.ptr(q), native.ptr(k), native.ptr(v),
+                                           T, heads, Dh, rot, float(base), _stream(qkv))
+    native.check(rc, "ubm_rotary_split_qkv")
+    return q, k, v
+
+
+def add2_softmax_rows(x: torch.Tensor, a: Optional[torch.Tensor] = None, b: Optional[torch.Tensor] = None):
+    x = x.float().contiguous()
+    C = x.shape[-1]
+    out = torch.empty_like(x)
+    aa = None if a is None else a.float().contiguous()
+    bb = None if b is None else b.float().contiguous()
+    rc = native.lib().ubm_add2_softmax_rows(native.ptr(x), native.ptr(aa), native.ptr(bb), native.ptr(out),
+                                            x.numel() // C, C, _stream(x))
+    native.check(rc, "ubm_add2_softmax_rows")
+    return out
+
+
+def pool2(x: torch.Tensor, mode: str = "max", w: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Width-2 pooling along dim 1 of [B, L, C]: ``max``, ``mean`` or ``softmax`` (weights from logits ``w``)."""
+    x = _bf16c(x)
+    B, L, C = x.shape
+    out = torch.empty((B, L // 2, C), dtype=torch.bfloat16, device=x.device)
+    ww = None if w is None else _bf16c(w)
+    rc = native.lib().ubm_pool2(native.ptr(x), native.ptr(ww), native.ptr(out), B, L, C,
+                                {"max": 0, "mean": 1, "softmax": 2}[mode], _stream(x))
+    native.check(rc, "ubm_pool2")
+    return out
+
+
+def residual_ln(x: torch.Tensor, res: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor],
+                eps: float = 1e-5, return_sum: bool = False):
+    x, res = _bf16c(x), _bf16c(res)
+    C = x.shape[-1]
+    out = torch.empty_like(x)
+    s = torch.empty_like(x) if return_sum else None
+    rc = native.lib().ubm_residual_ln(native.ptr(x), native.ptr(res), native.ptr(_f32(gamma)), native.ptr(_f32(beta)),
+                                      native.ptr(s), native.ptr(out), x.numel() // C, C, float(eps), _stream(x))
+    native.check(rc, "ubm_residual_ln")
+    return (out, s) if return_sum else out
