@@ -1,0 +1,91 @@
+"""Evo2-shaped generation: one long prefill and a run of single-token decode steps, optionally tensor parallel.
+
+    python benchmarks/evo2_generate.py --config evo2_7b --prefill 32768 --new 256                      # one GPU
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node P --master-addr 127.0.0.1 --master-port 29561 \
+        benchmarks/evo2_generate.py --config evo2_7b --prefill 32768 --new 256                         # TP = P
+
+bf16, random-init weights of the named configuration, a random byte prompt.  The kernel path is on
+(``set_impl("fused")``: RMSNorm, FIR / gate stages, convolution epilogues, decode state step, tcgen05 GEMMs; under
+tensor parallelism the row-parallel projections use the GEMM whose epilogue does the reduce-scatter over peer
+memory).  Times are CUDA-event times, max over ranks; rank 0 prints one JSON line.
+"""
+import argparse
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import torch
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="evo2_7b")
+    ap.add_argument("--prefill", type=int, default=32768)
+    ap.add_argument("--new", type=int, default=256)
+    ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = the configuration's)")
+    ap.add_argument("--impl", default="fused", choices=["fused", "torch"])
+    ap.add_argument("--warmup", type=int, default=1)
+    a = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    from uplifting_biomolecular_modeling_b200.models import evo2
+    from uplifting_biomolecular_modeling_b200.ops import native
+    over = {"n_layers": a.layers, "attn_layers": tuple(i for i in evo2.CONFIGS[a.config].attn_layers if i < a.layers)} \
+        if a.layers else {}
+    model = evo2.build(a.config, device=dev, dtype=torch.bfloat16, seed=0, **over)
+    par = None
+    if a.impl == "fused":
+        model.set_impl("fused")
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        from uplifting_biomolecular_modeling_b200.parallel import comm, symm, tp
+        par = tp.TensorParallel(comm.GroupComm(), symm.SymmHeap())
+        par.shard_evo2(model)
+    g = torch.Generator(device=dev).manual_seed(1)
+    tokens = torch.randint(0, model.cfg.vocab, (1, a.prefill), device=dev, generator=g)
+
+    def run():
+        states = [dict() for _ in model.blocks]
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        logits = model(tokens, states)
+        nxt = logits[:, -1:].argmax(-1)
+        e[1].record()
+        for _ in range(a.new - 1):
+            nxt = model.step(nxt, states)[:, -1:].argmax(-1)
+        e[2].record()
+        torch.cuda.synchronize(dev)
+        return e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2]), int(nxt.item())
+
+    for _ in range(a.warmup):
+        run()
+    if world > 1:
+        torch.distributed.barrier()
+    pre, dec, last = run()
+    native.raise_on_status(dev, "evo2 generate")
+    t = torch.tensor([pre, dec], device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    if rank == 0:
+        pre, dec = t.tolist()
+        print(json.dumps({
+            "bench": "evo2_generate", "config": a.config, "layers": model.cfg.n_layers, "tp": world, "impl": a.impl,
+            "prefill_tokens": a.prefill, "new_tokens": a.new, "prefill_ms": round(pre, 2),
+            "prefill_tokens_per_s": round(a.prefill / pre * 1e3, 1), "decode_ms_per_token": round(dec / max(a.new - 1, 1), 3),
+            "decode_tokens_per_s": round((a.new - 1) / dec * 1e3, 1), "last_token": last,
+            "fused_reduce_scatter_calls": 0 if par is None else par.fused_calls,
+            "peak_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2)}), flush=True)
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

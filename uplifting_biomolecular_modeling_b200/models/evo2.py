@@ -11,8 +11,9 @@ kernels for the same pieces: evo2/opt/evo2_opt/kit/base.py:55 ``_fir3_kernel``, 
 
 Prefill runs the medium / long operators as FFT convolutions; decoding keeps per-layer state (FIR
 tails, pole states, attention KV cache) and advances one token per step.  Tensor parallelism shards
-the channel dimension of every operator: column-parallel input projections, row-parallel output
-projections, with the two collectives fused into the GEMMs (``parallel.tp``).
+the channel dimension of every operator (``parallel.tp``): column-parallel input projections, row-parallel
+output projections whose reduce-scatter is done by the GEMM epilogue over peer memory.  The causal attention
+of the five attention layers is a library call (scaled_dot_product_attention).
 """
 from __future__ import annotations
 
@@ -247,9 +248,12 @@ class AttentionOperator(nn.Module):
         self.out_proj = nn.Linear(d, d, bias=True)
 
     def _qkv(self, x, pos, lin):
+        """q, k, v as [B, L, heads held here, head_dim]; under tensor parallelism the projection returns only
+        this rank's heads."""
         B, L, d = x.shape
-        H = self.cfg.n_heads
-        q, k, v = lin(self.qkv, x).view(B, L, 3, H, d // H).unbind(2)
+        hd = self.cfg.d_model // self.cfg.n_heads
+        qkv = lin(self.qkv, x)
+        q, k, v = qkv.view(B, L, 3, qkv.shape[-1] // (3 * hd), hd).unbind(2)
         return rope(q, pos, self.cfg.rope_base), rope(k, pos, self.cfg.rope_base), v
 
     def forward(self, x, state: Optional[dict] = None, linear=None):
@@ -260,7 +264,7 @@ class AttentionOperator(nn.Module):
         o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
         if state is not None:
             state["k"], state["v"] = k, v
-        return lin(self.out_proj, o.transpose(1, 2).reshape(B, L, d))
+        return lin(self.out_proj, o.transpose(1, 2).reshape(B, L, -1))
 
     def step(self, x, state: dict, linear=None):
         lin = linear or (lambda m, t: m(t))
@@ -270,7 +274,7 @@ class AttentionOperator(nn.Module):
         state["k"] = torch.cat([state["k"], k], 1)
         state["v"] = torch.cat([state["v"], v], 1)
         o = F.scaled_dot_product_attention(q.transpose(1, 2), state["k"].transpose(1, 2), state["v"].transpose(1, 2))
-        return lin(self.out_proj, o.transpose(1, 2).reshape(B, 1, d))
+        return lin(self.out_proj, o.transpose(1, 2).reshape(B, 1, -1))
 
 
 class SwiGLU(nn.Module):
