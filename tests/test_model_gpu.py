@@ -78,3 +78,27 @@ def test_outer_product_mean_fused_vs_reference(full):
     native.raise_on_status("cuda", "outer product mean")
     err = ((out.float() - ref).abs().mean() / ref.abs().mean()).item()
     assert err < 3e-2, err
+
+
+def test_template_embedder_fused_vs_reference():
+    from uplifting_biomolecular_modeling_b200.models import template
+    from uplifting_biomolecular_modeling_b200.ops import native
+    torch.manual_seed(2)
+    N, T = 72, 3
+    asym = torch.tensor([0] * 40 + [1] * 32)
+    m = template.TemplateEmbedder(c_z=128, n_blocks=1).cuda().eval()
+    f = {k: v.cuda() for k, v in template.synthetic_template_features(N, T, asym).items()}
+    z = torch.randn(1, N, N, 128, device="cuda")
+    with torch.no_grad():
+        ref = m(z, f)
+        zp = m.linear_z(m.z_norm(z[0]))
+        v_ref = m.embed_reference(zp, f)
+        v_fused = m._embed_fused(zp, f)
+        mb = m.to(torch.bfloat16)
+        mb.impl = "fused"
+        out = mb(z.bfloat16(), f)
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "template")
+    assert (v_fused - v_ref).abs().max().item() < 3e-2 * v_ref.abs().max().item()
+    err = ((out.float() - ref).abs().mean() / ref.abs().mean()).item()
+    assert err < 5e-2, err

@@ -47,6 +47,7 @@ class CofoldConfig:
     msa_feat: int = 34
     atom_feat: int = 24
     relpos_bins: int = 139
+    template_blocks: int = 0          # > 0 adds the template embedder (2 in the AF3 family); features optional
 
 
 CONFIGS: Dict[str, CofoldConfig] = {
@@ -188,6 +189,9 @@ class CofoldModel(nn.Module):
         self.s_recycle = nn.Linear(cfg.c_s, cfg.c_s, bias=False)
         self.z_recycle = nn.Linear(cfg.c_z, cfg.c_z, bias=False)
         self.msa_module = MSAModule(cfg.c_m, cfg.c_z, cfg.c_s, cfg.msa_blocks, cfg.msa_feat)
+        if cfg.template_blocks > 0:
+            from .template import TemplateEmbedder
+            self.template_embedder = TemplateEmbedder(cfg.c_z, n_blocks=cfg.template_blocks)
         self.pairformer_module = PairformerModule(cfg.c_s, cfg.c_z, cfg.pairformer_blocks)
         self.distogram_module = DistogramModule(cfg.c_z, cfg.distogram_bins)
         score = DiffusionModule(cfg.c_s, cfg.c_z, cfg.c_atom, cfg.c_atompair, cfg.token_depth, cfg.token_heads,
@@ -234,6 +238,11 @@ class CofoldModel(nn.Module):
         for _ in range(n + 1):
             s = s_init + self.s_recycle(self.s_norm(s))
             z = z_init + self.z_recycle(self.z_norm(z))
+            if self.cfg.template_blocks > 0 and "template_distogram" in feats:
+                tf = {k: (v[0] if k.startswith("template_") else v) for k, v in feats.items()
+                      if k.startswith("template_")}
+                tf["asym_id"] = feats["chain_id"][0]
+                z = z + self.template_embedder(z, tf).to(z.dtype)
             z = self.msa_module(z, s_inputs, feats["msa_feat"], feats["msa_mask"], tmask, None)
             s, z = self.pairformer_module(s, z, smask, None)
         return s, z

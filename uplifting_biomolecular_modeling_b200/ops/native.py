@@ -36,6 +36,8 @@ _SIGNATURES = {
     "ubm_gemm_bf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                       c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_int, c_int, c_int, c_float,
                       c_void_p, c_void_p],
+    "ubm_template_embed": [c_void_p] * 11 + [c_int, c_int, c_void_p],
+    "ubm_template_tail": [c_void_p, c_void_p, c_int, c_ll, c_int, c_void_p],
     "ubm_gemm_bf16_ex": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                          c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_int, c_int, c_int, c_float,
                          c_ll, c_ll, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p],
