@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = the configuration's)")
     ap.add_argument("--impl", default="fused", choices=["fused", "torch"])
     ap.add_argument("--warmup", type=int, default=1)
+    ap.add_argument("--graph", type=int, default=1, help="1: decode step captured in a CUDA graph and replayed")
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -58,8 +59,12 @@ def main():
         logits = model(tokens, states)
         nxt = logits[:, -1:].argmax(-1)
         e[1].record()
-        for _ in range(a.new - 1):
-            nxt = model.step(nxt, states)[:, -1:].argmax(-1)
+        if a.graph:
+            # capture (one eager step + one captured step) is inside the timed decode region
+            nxt = model._generate_graph(tokens, states, nxt, a.new)[:, -1:]
+        else:
+            for _ in range(a.new - 1):
+                nxt = model.step(nxt, states)[:, -1:].argmax(-1)
         e[2].record()
         torch.cuda.synchronize(dev)
         return e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2]), int(nxt.item())
@@ -76,7 +81,7 @@ def main():
     if rank == 0:
         pre, dec = t.tolist()
         print(json.dumps({
-            "bench": "evo2_generate", "config": a.config, "layers": model.cfg.n_layers, "tp": world, "impl": a.impl,
+            "bench": "evo2_generate", "config": a.config, "layers": model.cfg.n_layers, "tp": world, "impl": a.impl, "decode_graph": bool(a.graph),
             "prefill_tokens": a.prefill, "new_tokens": a.new, "prefill_ms": round(pre, 2),
             "prefill_tokens_per_s": round(a.prefill / pre * 1e3, 1), "decode_ms_per_token": round(dec / max(a.new - 1, 1), 3),
             "decode_tokens_per_s": round((a.new - 1) / dec * 1e3, 1), "last_token": last,

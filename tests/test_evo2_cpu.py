@@ -31,3 +31,21 @@ def test_decode_steps_match_prefill():
     out = m.generate(toks[:, :8], 5)
     assert out.shape == (1, 5)
     assert torch.isfinite(m.score(toks)).all()
+
+
+def test_static_state_decode_equals_plain_decode():
+    """Fixed-address states (what a captured decode graph uses) give the same tokens as the growing ones."""
+    import torch
+    from uplifting_biomolecular_modeling_b200.models import evo2
+    m = evo2.build("evo2_tiny", device="cpu", dtype=torch.float32, seed=2)
+    tok = torch.randint(0, m.cfg.vocab, (1, 30), generator=torch.Generator().manual_seed(3))
+    ref = m.generate(tok, 8)
+    states = [dict() for _ in m.blocks]
+    nxt = m(tok, states)[:, -1:].argmax(-1)
+    pos = m.make_static_states(states, 30 + 8)
+    outs = [nxt]
+    for _ in range(7):
+        nxt = m.step(nxt, states)[:, -1:].argmax(-1)
+        pos.add_(1)
+        outs.append(nxt)
+    assert torch.equal(torch.cat(outs, 1), ref)

@@ -122,3 +122,14 @@ def test_evo2_fused_matches_plain_statements():
     scale = ref.abs().max().item()
     assert (out - ref).abs().max().item() < 6e-2 * scale
     assert (out_step - ref_step).abs().max().item() < 6e-2 * scale
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+def test_gemv_rows(M):
+    from uplifting_biomolecular_modeling_b200.ops import seq
+    g = torch.Generator(device="cuda").manual_seed(6)
+    K, N = 4096, 1000
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * K ** -0.5).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g)
+    _close(seq.gemv_rows(x, w, b), x.float() @ w.float().t() + b)

@@ -194,29 +194,45 @@ class HyenaOperator(nn.Module):
         if _fusable(self, z) and self.cfg.fir_len <= 4:
             from ..ops import seq
             u, x2 = seq.fir_gate3(z, self._kernel_taps()[0], state["fir_tail"])
-            state["fir_tail"] = torch.cat([state["fir_tail"], z], 1)[:, 1:]
+            _push(state, "fir_tail", z)
             if self.kind in ("hcs", "hcm"):
                 gated = seq.fir_inner_gate(u, self._kernel_taps()[1], self.D, x2, state["inner_tail"])
-                state["inner_tail"] = torch.cat([state["inner_tail"], u], 1)[:, 1:]
+                _push(state, "inner_tail", u)
             else:
-                st = state["poles"].float().contiguous()
+                st = state["poles"]
+                if st.dtype != torch.float32 or not st.is_contiguous():
+                    st = st.float().contiguous()
+                    state["poles"] = st
                 gated = seq.pole_step(st, torch.exp(self.log_poles.float()), self.residues, u[:, 0], self.D,
-                                      x2[:, 0]).unsqueeze(1)
-                state["poles"] = st
+                                      x2[:, 0]).unsqueeze(1)          # updates st in place
             return lin(self.out_proj, gated)
         zf = causal_fir(z, self.fir, state["fir_tail"])
-        state["fir_tail"] = torch.cat([state["fir_tail"], z], 1)[:, 1:]
+        _push(state, "fir_tail", z)
         x1, x2, v = zf.chunk(3, dim=-1)
         u = x1 * v
         if self.kind in ("hcs", "hcm"):
             y = causal_fir(u, self.h, state["inner_tail"]) + u * self.D.to(u.dtype)
-            state["inner_tail"] = torch.cat([state["inner_tail"], u], 1)[:, 1:]
+            _push(state, "inner_tail", u)
         else:
             lam = torch.exp(self.log_poles.float())
             s = state["poles"] * lam.unsqueeze(0) + u[:, 0].float().unsqueeze(-1)     # [B, d, S]
-            state["poles"] = s
+            if state.get("static"):
+                state["poles"].copy_(s)
+                s = state["poles"]
+            else:
+                state["poles"] = s
             y = (s * self.residues.float().unsqueeze(0)).sum(-1).unsqueeze(1).to(u.dtype) + u * self.D.to(u.dtype)
         return lin(self.out_proj, x2 * y)
+
+
+def _push(state: dict, key: str, new: torch.Tensor) -> None:
+    """Shift a [B, K-1, C] tail by one position and append ``new`` ([B, 1, C]).  A static state (one that a
+    captured decode graph reads and writes at fixed addresses) is rewritten in place."""
+    nxt = torch.cat([state[key], new.to(state[key].dtype)], 1)[:, 1:]
+    if state.get("static"):
+        state[key].copy_(nxt)
+    else:
+        state[key] = nxt
 
 
 def _last(t: torch.Tensor, n: int) -> torch.Tensor:
@@ -269,6 +285,19 @@ class AttentionOperator(nn.Module):
     def step(self, x, state: dict, linear=None):
         lin = linear or (lambda m, t: m(t))
         B, _, d = x.shape
+        if state.get("static"):
+            # fixed-size cache, the position is a device tensor: no host value enters the step, so it can be
+            # captured in a CUDA graph.  Keys past the position are masked.
+            pos = state["pos"]                                              # int64 [1]
+            q, k, v = self._qkv(x, pos, lin)
+            state["k"].index_copy_(1, pos, k.to(state["k"].dtype))
+            state["v"].index_copy_(1, pos, v.to(state["v"].dtype))
+            kc, vc = state["k"], state["v"]                                 # [B, Lmax, H, hd]
+            sc = torch.einsum("bqhd,bkhd->bhqk", q, kc).float() * (q.shape[-1] ** -0.5)
+            dead = torch.arange(kc.shape[1], device=x.device) > pos
+            sc = sc.masked_fill(dead[None, None, None, :], float("-inf"))
+            o = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(sc, -1).to(vc.dtype), vc)
+            return lin(self.out_proj, o.reshape(B, 1, -1))
         pos = torch.tensor([state["k"].shape[1]], device=x.device)
         q, k, v = self._qkv(x, pos, lin)
         state["k"] = torch.cat([state["k"], k], 1)
@@ -351,18 +380,76 @@ class StripedHyena2(nn.Module):
             x = blk.step(x, states[i], self.linear)
         return self.logits(x)
 
+    def make_static_states(self, states: List[dict], max_len: int) -> torch.Tensor:
+        """Turn the states a prefill produced into fixed-address buffers (attention caches of ``max_len``
+        positions, tails and pole states updated in place) and return the shared position tensor."""
+        dev = self.embedding.weight.device
+        pos = None
+        for blk, st in zip(self.blocks, states):
+            st["static"] = True
+            if blk.kind == "attn":
+                k, v = st["k"], st["v"]
+                B, L = k.shape[:2]
+                if pos is None:
+                    pos = torch.full((1,), L, dtype=torch.long, device=dev)
+                for name, t in (("k", k), ("v", v)):
+                    buf = t.new_zeros((B, max_len) + tuple(t.shape[2:]))
+                    buf[:, :L] = t
+                    st[name] = buf
+                st["pos"] = pos
+            else:
+                for name in ("fir_tail", "inner_tail"):
+                    if name in st:
+                        st[name] = st[name].contiguous().clone()
+                if "poles" in st:
+                    st["poles"] = st["poles"].float().contiguous().clone()
+        if pos is None:
+            pos = torch.zeros((1,), dtype=torch.long, device=dev)
+        return pos
+
     @torch.no_grad()
-    def generate(self, tokens: torch.Tensor, max_new_tokens: int) -> torch.Tensor:
-        """Greedy decoding: prefill, then ``max_new_tokens`` single-token steps."""
+    def generate(self, tokens: torch.Tensor, max_new_tokens: int, graph: bool = False) -> torch.Tensor:
+        """Greedy decoding: prefill, then ``max_new_tokens`` single-token steps.  ``graph=True`` (GPU): the decode
+        step is captured once in a CUDA graph over fixed-address states and replayed per token."""
         states = [dict() for _ in self.blocks]
         logits = self.forward(tokens, states)
         nxt = logits[:, -1:].argmax(-1)
+        if graph and tokens.is_cuda and max_new_tokens > 2:
+            return self._generate_graph(tokens, states, nxt, max_new_tokens)
         out = [nxt]
         for _ in range(max_new_tokens - 1):
             logits = self.step(nxt, states)
             nxt = logits[:, -1:].argmax(-1)
             out.append(nxt)
         return torch.cat(out, 1)
+
+    def _generate_graph(self, tokens, states, first, max_new_tokens):
+        dev = tokens.device
+        B, L = tokens.shape
+        pos = self.make_static_states(states, L + max_new_tokens)
+        tok = first.clone()                                               # static input / feedback buffer
+        out = torch.zeros((B, max_new_tokens), dtype=first.dtype, device=dev)
+        out[:, 0:1] = first
+        cnt = torch.ones((1,), dtype=torch.long, device=dev)
+
+        def one_step():
+            nxt = self.step(tok, states)[:, -1:].argmax(-1)
+            out.index_copy_(1, cnt, nxt)
+            tok.copy_(nxt)
+            pos.add_(1)
+            cnt.add_(1)
+
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            one_step()                                                    # eager step: warms every kernel up
+        torch.cuda.current_stream(dev).wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            one_step()
+        for _ in range(max_new_tokens - 2):
+            g.replay()
+        return out
 
     @torch.no_grad()
     def score(self, tokens: torch.Tensor) -> torch.Tensor:
@@ -393,6 +480,9 @@ def fused_linear(module: nn.Linear, x: torch.Tensor) -> torch.Tensor:
     x2 = x.reshape(-1, x.shape[-1])
     if not x2.is_contiguous():
         x2 = x2.contiguous()
+    if x2.shape[0] <= 8:                      # decode rows: stream the weights once (memory bound)
+        from ..ops import seq
+        return seq.gemv_rows(x2, ent[2], ent[3]).view(*x.shape[:-1], ent[2].shape[0])
     return gemm.gemm(x2, ent[2], bias=ent[3]).view(*x.shape[:-1], ent[2].shape[0])
 
 

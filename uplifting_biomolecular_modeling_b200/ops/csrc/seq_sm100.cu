@@ -775,3 +775,61 @@ extern "C" int ubm_residual_ln(const void* x, const void* res, const void* gamma
   UBM_CHECK_LAUNCH("residual_ln_kernel");
   return UBM_OK;
 }
+
+// ------------------------------------------------------------------------------------------ decode GEMV
+// y[b][n] = sum_k W[n][k] x[b][k] (+ bias[n]) for a handful of rows b (single-token decode): the weight matrix is
+// streamed once at memory speed, one warp per output row n, 16-byte loads, fp32 accumulation; the activations
+// (at most 8 rows) are re-read from L1/L2.  A 128-row MMA tile would use one row of it and, with N / 256 tiles,
+// a fraction of the SMs.
+namespace ubm {
+template <int MB>
+__global__ void __launch_bounds__(256) gemv_rows_kernel(const __nv_bfloat16* __restrict__ x,
+                                                        const __nv_bfloat16* __restrict__ w,
+                                                        const float* __restrict__ bias,
+                                                        __nv_bfloat16* __restrict__ out, int M, int N, int K) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  for (int n = blockIdx.x * wpb + (threadIdx.x >> 5); n < N; n += gridDim.x * wpb) {
+    float acc[MB];
+#pragma unroll
+    for (int b = 0; b < MB; ++b) acc[b] = 0.f;
+    const __nv_bfloat16* wr = w + static_cast<long long>(n) * K;
+    for (int k = lane * 8; k < K; k += 256) {
+      float wv[8];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(wr + k)), wv);
+#pragma unroll
+      for (int b = 0; b < MB; ++b) {
+        if (b < M) {
+          float xv[8];
+          unpack8(*reinterpret_cast<const uint4*>(x + static_cast<long long>(b) * K + k), xv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[b] = fmaf(wv[e], xv[e], acc[b]);
+        }
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < MB; ++b) {
+      const float s = warp_sum(acc[b]);
+      if (lane == 0 && b < M) out[static_cast<long long>(b) * N + n] = __float2bfloat16(s + (bias ? bias[n] : 0.f));
+    }
+  }
+}
+}  // namespace ubm
+
+// x: bf16 [M][K] (M <= 8), w: bf16 [N][K] (rows contiguous, K a multiple of 8), bias: fp32 [N] or null, out: bf16 [M][N]
+extern "C" int ubm_gemv_rows(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
+                             void* stream) {
+  if (M < 1 || M > 8 || N < 1 || K < 8 || (K & 7) || !aligned16(x) || !aligned16(w)) return UBM_ERR_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = seq_grid(N, 8);
+  const __nv_bfloat16* xx = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* ww = static_cast<const __nv_bfloat16*>(w);
+  const float* bb = static_cast<const float*>(bias);
+  __nv_bfloat16* oo = static_cast<__nv_bfloat16*>(out);
+  if (M == 1) gemv_rows_kernel<1><<<grid, 256, 0, st>>>(xx, ww, bb, oo, M, N, K);
+  else if (M <= 2) gemv_rows_kernel<2><<<grid, 256, 0, st>>>(xx, ww, bb, oo, M, N, K);
+  else if (M <= 4) gemv_rows_kernel<4><<<grid, 256, 0, st>>>(xx, ww, bb, oo, M, N, K);
+  else gemv_rows_kernel<8><<<grid, 256, 0, st>>>(xx, ww, bb, oo, M, N, K);
+  UBM_CHECK_LAUNCH("gemv_rows_kernel");
+  return UBM_OK;
+}

@@ -25,6 +25,8 @@ native.declare("ubm_add2_softmax_rows", [c_void_p] * 4 + [c_ll, c_int, c_void_p]
 native.declare("ubm_pool2", [c_void_p] * 3 + [c_int] * 4 + [c_void_p])
 native.declare("ubm_residual_ln", [c_void_p] * 6 + [c_ll, c_int, c_float, c_void_p])
 
+native.declare("ubm_gemv_rows", [c_void_p] * 4 + [c_int] * 3 + [c_void_p])
+
 EW = {"gelu_new": 0, "add2": 1, "bias_residual": 2, "scale_shift_gelu": 3, "silu_mul": 4}
 
 
@@ -196,3 +198,15 @@ def residual_ln(x: torch.Tensor, res: torch.Tensor, gamma: torch.Tensor, beta: O
                                       native.ptr(s), native.ptr(out), x.numel() // C, C, float(eps), _stream(x))
     native.check(rc, "ubm_residual_ln")
     return (out, s) if return_sum else out
+
+
+def gemv_rows(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x: bf16 [M, K] with M <= 8 (decode rows); w: bf16 [N, K] contiguous; returns bf16 [M, N] = x @ w.T (+ bias)."""
+    x = _bf16c(x)
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    rc = native.lib().ubm_gemv_rows(native.ptr(x), native.ptr(w), native.ptr(bias), native.ptr(out), M, N, K,
+                                    _stream(x))
+    native.check(rc, "ubm_gemv_rows")
+    return out

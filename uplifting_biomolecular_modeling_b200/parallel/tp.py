@@ -121,7 +121,11 @@ class TensorParallel:
             w = module.weight.detach()
             if w.dtype != torch.bfloat16 or not w.is_contiguous():
                 w = w.to(torch.bfloat16).contiguous()
-            part = gemm.gemm(x2.contiguous(), w)
+            if M <= 8:
+                from ..ops import seq
+                part = seq.gemv_rows(x2.contiguous(), w)
+            else:
+                part = gemm.gemm(x2.contiguous(), w)
         else:
             part = torch.nn.functional.linear(x2, module.weight)
         y = self._sum(part)
