@@ -53,8 +53,11 @@ class SymmHeap:
         self.group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
         self.device = device or torch.device("cuda", torch.cuda.current_device())
+        import warnings
         try:
-            sm.enable_symm_mem_for_group(self.group.group_name)
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")
+                sm.enable_symm_mem_for_group(self.group.group_name)
         except Exception:  # noqa: BLE001  (already enabled, or not needed by this torch)
             pass
         self._flags = self.alloc((64,), torch.int32)
