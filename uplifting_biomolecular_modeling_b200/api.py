@@ -91,6 +91,7 @@ class Predictor:
             out[k] = d.to(self.dtype) if d.is_floating_point() else d
         out["no_padding"] = no_padding
         out["msa_full"] = msa_full      # host-side facts about the masks: they select mask-free kernels
+        out["_on_device"] = True
         return out
 
     # ------------------------------------------------------------------ sampler step graph
@@ -144,7 +145,7 @@ class Predictor:
     @torch.no_grad()
     def predict(self, feats_host: Dict[str, torch.Tensor], recycles: Optional[int] = None,
                 samples: Optional[int] = None, steps: Optional[int] = None, confidence: bool = True,
-                seed: Optional[int] = None) -> Dict[str, torch.Tensor]:
+                seed: Optional[int] = None, to_host: bool = True) -> Dict[str, torch.Tensor]:
         m = self.model
         dev = self.device
         if dev.type == "cuda":
@@ -161,7 +162,9 @@ class Predictor:
                 marks.append((name, time.perf_counter()))
 
         mark("start")
-        feats = self.to_device(feats_host)
+        # features already on the device (a dict produced by to_device) skip the host copy; with
+        # to_host=False the result stays on the device as well: the device-only form of the same call
+        feats = feats_host if feats_host.get("_on_device") is True else self.to_device(feats_host)
         s_inputs, s_init, z_init, atom_c, atom_p = m.embed(feats)
         mark("embed")
         s, z = m.trunk(feats, s_inputs, s_init, z_init, recycles)
@@ -187,14 +190,14 @@ class Predictor:
             out["plddt"] = (p * (torch.arange(50, device=p.device) + 0.5) / 50).sum(-1)
             pae = torch.softmax(conf["pae_logits"].float(), -1)
             out["pae_mean"] = (pae * (torch.arange(64, device=p.device) + 0.5) * 0.5).sum(-1).mean()
-        host = {k: v.float().cpu() for k, v in out.items()}
+        host = {k: v.float().cpu() for k, v in out.items()} if to_host else {k: v.float() for k, v in out.items()}
         mark("confidence_and_copy")
         if timing:
             self.last_timing = {marks[i][0]: round((marks[i][1] - marks[i - 1][1]) * 1e3, 2)
                                 for i in range(1, len(marks))}
             import sys
             print(f"[ubm] STAGES ms {self.last_timing}", file=sys.stderr, flush=True)
-        self.d2h_bytes = sum(v.numel() * 4 for v in host.values())
+        self.d2h_bytes = sum(v.numel() * 4 for v in host.values()) if to_host else 0
         if dev.type == "cuda" and m.fused:
             from .ops import native
             native.raise_on_status(dev, "predict")
