@@ -55,7 +55,7 @@ def main():
     ap.add_argument("--n", type=int, default=768)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--attn-variant", type=int, default=0, help="0 = by shape, 1 = two rows per CTA")
+    ap.add_argument("--attn-variant", type=int, default=0, help="attention: 0 = default (four rows per CTA from 4 rows on), 5 = two rows per CTA, 1 = P and bias through shared memory; window_attention: 1 = CUDA-core kernel")
     ap.add_argument("--m", type=int, default=7680, help="rows of the gemm_rows case / atoms of window_attention")
     ap.add_argument("--k", type=int, default=768)
     ap.add_argument("--nn", type=int, default=3072)

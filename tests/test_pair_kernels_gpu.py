@@ -57,10 +57,14 @@ def test_trimul(N, outgoing):
     assert _rel_err(out, ref) < 6e-2
 
 
+@pytest.mark.parametrize("variant", [0, 5])
 @pytest.mark.parametrize("rows,N,H", [(2, 128, 4), (5, 200, 4), (8, 384, 2)])
-def test_attention_core(rows, N, H):
-    """The attention kernel alone: base-2 softmax with shared bias, gate and tail masking."""
+def test_attention_core(rows, N, H, variant, request):
+    """The attention kernel alone: base-2 softmax with shared bias, gate and tail masking.  Variant 0 takes the
+    four-rows-per-CTA form for rows >= 4, variant 5 always the two-row form."""
     from uplifting_biomolecular_modeling_b200.ops import native, pair, reference
+    pair.set_attention_variant(variant)
+    request.addfinalizer(lambda: pair.set_attention_variant(0))
     g = torch.Generator(device="cuda").manual_seed(5)
     D = 32
     q = _rand((rows, N, H * D), g).bfloat16()

@@ -50,13 +50,18 @@ struct AttnCfg {
   // As many stages as fit: the loop is bound by the latency of the tile loads unless they are issued
   // several tiles ahead (with two stages every tile waited a full TMA round trip).
   static constexpr int kPSmem = TP ? 0 : R2 * kPBytes;
-  static constexpr int kStages = (224 * 1024 - R2 * kQBytes - kPSmem) / kStageBytes;
-  static_assert(kStages >= 2 && kStages <= 8, "stage count");
-  static constexpr int kSmemBytes = R2 * kQBytes + kStages * kStageBytes + kPSmem + 512 + 1024;
   // tensor memory map (512 columns): S[r] at r*TK, O[r] at 256 + r*D, then (TP) P[r] and the identity
   static constexpr int kTmemP = 256 + R2 * D;             // P[r] at kTmemP + r * TK / 2 (two bf16 per column)
   static constexpr int kTmemI = kTmemP + R2 * TK / 2;     // identity: 64 columns (128 x 128 bf16)
-  static_assert(!TP || (R2 * TK <= 256 && kTmemI + 64 <= 512), "tensor memory budget");
+  // With four rows per CTA the identity operand of the bias MMA does not fit in tensor memory any more
+  // (S 256 + O 128 + P 128 columns): it lives in shared memory (32 KB, K-major, 128-byte swizzle) and the bias
+  // MMA is the shared-memory form.
+  static constexpr bool kIdentSmem = TP && (kTmemI + 64 > 512);
+  static constexpr int kIdentBytes = kIdentSmem ? kATile * kATile * 2 : 0;
+  static constexpr int kStages = (224 * 1024 - R2 * kQBytes - kPSmem - kIdentBytes) / kStageBytes;
+  static_assert(kStages >= 2 && kStages <= 8, "stage count");
+  static constexpr int kSmemBytes = R2 * kQBytes + kStages * kStageBytes + kPSmem + kIdentBytes + 512 + 1024;
+  static_assert(!TP || (R2 * TK <= 256 && (kIdentSmem ? kTmemI : kTmemI + 64) <= 512), "tensor memory budget");
   static constexpr int kThreads = 128 + R2 * 128;
   // setmaxnreg moves registers inside the pool the CTA was launched with (threads x compiled registers):
   //   R2 = 2: 384 x 168 = 64512 = 128 x 56 + 256 x 224;   R2 = 4: 640 x 96 = 61440 >= 128 x 56 + 512 x 104.
@@ -71,7 +76,8 @@ struct AttnCfg {
 
 struct AttnParams {
   int rows, Nq, Nk, H;
-  const __nv_bfloat16* gate;  // [rows][Nq][H*32] or null
+  const __nv_bfloat16* gate;  // [rows][Nq] rows of H*D gate values (row stride ld_gate) or null
+  long long ld_gate;
   __nv_bfloat16* out;         // [rows][Nq][H*32], or transposed [Nq][rows][H*32]
   int transpose_out;
   int has_bias;
@@ -139,7 +145,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sQ = smem;                              // R2 x Q tile
   uint8_t* sSt = sQ + R2 * kAQBytes;               // stages
   uint8_t* sP = sSt + kAStages * kAStageBytes;     // R2 x P tile
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + (TP ? 0 : R2 * kAPBytes));   // no P tiles in smem when TP
+  uint8_t* sIdent = sP + (TP ? 0 : R2 * kAPBytes);                               // no P tiles in smem when TP
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sIdent + Cfg::kIdentBytes);
   uint64_t* q_full = bars;             // [1]
   uint64_t* q_empty = q_full + 1;      // [1] commit
   uint64_t* kv_full = q_empty + 1;     // [stages]
@@ -188,7 +195,24 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tP = tmem_base + Cfg::kTmemP;
   const uint32_t tI = tmem_base + Cfg::kTmemI;
   const int T = p.n_kt;
-  if (TP) {
+  if (TP && Cfg::kIdentSmem) {
+    // identity A operand in shared memory: two k-blocks of [128 rows][64 k], row q has a one at k = q
+    for (int i = threadIdx.x; i < kATile * 16; i += blockDim.x) {
+      const int row = i >> 4, c16 = i & 15;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if ((row >> 3) == c16) {
+        const uint32_t one = (row & 1) ? 0x3F800000u : 0x00003F80u;
+        const int w = (row & 7) >> 1;
+        v.x = w == 0 ? one : 0u;
+        v.y = w == 1 ? one : 0u;
+        v.z = w == 2 ? one : 0u;
+        v.w = w == 3 ? one : 0u;
+      }
+      *reinterpret_cast<uint4*>(sIdent + (c16 >> 3) * 16384 + swz128_offset(row, c16 & 7)) = v;
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+  } else if (TP) {
     // identity A operand: lane q holds 128 bf16, element q is 1.0 (two bf16 per 32-bit column)
     if (warp >= 4 && warp < 8) {
       const int qrow0 = (warp & 3) * 32 + lane;
@@ -274,13 +298,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint64_t bd0 = umma_smem_desc(st + 2 * R2 * kAKVBytes, 16384, 1024, kSwizzle128);
         const uint64_t ad0 = umma_smem_desc(qa, 16, Cfg::kSbo, Cfg::kSwz);
         const uint64_t kd0 = umma_smem_desc(ka, 16, Cfg::kSbo, Cfg::kSwz);
+        const uint64_t id0 = umma_smem_desc(smem_u32(sIdent), 16, 1024, kSwizzle128);
         if (leader) {
           if (with_bias) {
             // S = I . bias^T: the 128 x TK bias tile sits in shared memory as TK/64 boxes of [128 q][64 k]
 #pragma unroll
-            for (int k = 0; k < kATile / 16; ++k)
-              umma_ts(tS + r * TK, tI + k * 8, bd0 + static_cast<uint64_t>(k * (2048 >> 4)), idesc_bias,
-                      k != 0 ? 1u : 0u);
+            for (int k = 0; k < kATile / 16; ++k) {
+              if (Cfg::kIdentSmem) {
+                umma_ss(tS + r * TK, id0 + static_cast<uint64_t>((k >> 2) * (16384 >> 4) + (k & 3) * 2),
+                        bd0 + static_cast<uint64_t>(k * (2048 >> 4)), idesc_bias, k != 0 ? 1u : 0u);
+              } else {
+                umma_ts(tS + r * TK, tI + k * 8, bd0 + static_cast<uint64_t>(k * (2048 >> 4)), idesc_bias,
+                        k != 0 ? 1u : 0u);
+              }
+            }
           }
 #pragma unroll
           for (int k = 0; k < kAD / 16; ++k)
@@ -513,7 +544,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
             for (int d = 0; d < 32; ++d) f[d] = __uint_as_float(ov[d]) * inv;
             if (p.gate != nullptr) {
-              const __nv_bfloat16* gp = p.gate + in_row * (p.H * kAD) + h * kAD + dc * 32;
+              const __nv_bfloat16* gp = p.gate + in_row * p.ld_gate + h * kAD + dc * 32;
 #pragma unroll
               for (int c = 0; c < 2; ++c) {
                 float e[16];
@@ -543,7 +574,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
 template <int D, int TK, int R2, bool TP = false>
 static int launch_attention(const void* q, const void* k, const void* v, const void* bias, const void* gate, void* out,
-                            int rows, int Nq, int Nk, int H, long long ldb, long long ld_in, int transpose_out,
+                            int rows, int Nq, int Nk, int H, long long ldb, long long ld_in, long long ld_gate,
+                            int transpose_out,
                             void* status, void* stream, int npeers = 0, const void* const* bias_ptrs = nullptr,
                             const int* peer_rows = nullptr, long long peer_head_stride = 0) {
   using Cfg = AttnCfg<D, TK, R2, TP>;
@@ -583,6 +615,7 @@ static int launch_attention(const void* q, const void* k, const void* v, const v
   p.Nk = Nk;
   p.H = H;
   p.gate = static_cast<const __nv_bfloat16*>(gate);
+  p.ld_gate = ld_gate > 0 ? ld_gate : static_cast<long long>(H) * D;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.transpose_out = transpose_out;
   p.has_bias = bias != nullptr ? 1 : 0;
@@ -654,41 +687,51 @@ extern "C" int ubm_attention_read_timeline(long long* host_out) {
 
 extern "C" int ubm_attention_set_variant(int v) {
   g_attn_variant = v & 0xff;  // 0 = P and bias through tensor memory; 1 = P and bias through shared memory;
-                              // 2 = four rows per CTA; 3 = 64-key steps
+                              // 2 = four rows per CTA; 3 = 64-key steps; 4 = four rows per CTA with P in
+                              // tensor memory (one bias tile per four rows: less L2 traffic per row; the
+                              // default for rows >= 4); 5 = two rows per CTA with P in tensor memory
   return 0;
 }
 
 // q, k, v, gate, out: bf16 [rows][N*][H*D] (innermost contiguous).  bias: bf16 [H][Nq][ldb] (ldb multiple
 // of 8) or null.  q must carry the factor log2(e)/sqrt(d) and bias the factor log2(e).  transpose_out
 // writes out[q][r] instead of out[r][q].  ld_in: row stride of q / k / v in elements (0 = H*D), so the
-// three may be column slices of one projection output.  D = 32 (ubm_attention_d32) or 64 (ubm_attention_d64).
+// three may be column slices of one projection output; ld_gate: row stride of the gate (0 = H*D; a multiple of
+// 16 elements), so the gate may be a column slice of the same output.  D = 32 (ubm_attention_d32) or 64
+// (ubm_attention_d64).
 extern "C" int ubm_attention_d32(const void* q, const void* k, const void* v, const void* bias, const void* gate,
                                  void* out, int rows, int Nq, int Nk, int H, long long ldb, long long ld_in,
-                                 int transpose_out, void* status, void* stream) {
-  if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0) return ubm::UBM_ERR_ARGUMENT;
+                                 long long ld_gate, int transpose_out, void* status, void* stream) {
+  if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0 || (ld_gate & 15)) return ubm::UBM_ERR_ARGUMENT;
   if (bias != nullptr && (ldb < Nk || (ldb & 7))) return ubm::UBM_ERR_ARGUMENT;
+  // default (variant 0): four rows per CTA once there are enough rows to fill the groups - one bias tile per four
+  // rows instead of two cuts the L2 traffic per row by a quarter (measured 5.31 -> 4.98 ms at N = 1536);
+  // variant 5 forces the two-row form
+  if ((g_attn_variant == 0 || g_attn_variant == 4) && rows >= 4)
+    return ubm::launch_attention<32, 64, 4, true>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, ld_gate,
+                                                  transpose_out, status, stream);
   if (g_attn_variant == 2 && rows >= 3)
-    return ubm::launch_attention<32, 64, 4>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
+    return ubm::launch_attention<32, 64, 4>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, ld_gate, transpose_out,
                                             status, stream);
   if (g_attn_variant == 3)
-    return ubm::launch_attention<32, 64, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
+    return ubm::launch_attention<32, 64, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, ld_gate, transpose_out,
                                             status, stream);
   if (g_attn_variant == 1)
-    return ubm::launch_attention<32, 128, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
+    return ubm::launch_attention<32, 128, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, ld_gate, transpose_out,
                                              status, stream);
-  return ubm::launch_attention<32, 128, 2, true>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in,
+  return ubm::launch_attention<32, 128, 2, true>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, ld_gate,
                                                  transpose_out, status, stream);
 }
 
 extern "C" int ubm_attention_d64(const void* q, const void* k, const void* v, const void* bias, const void* gate,
                                  void* out, int rows, int Nq, int Nk, int H, long long ldb, long long ld_in,
-                                 int transpose_out, void* status, void* stream) {
-  if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0) return ubm::UBM_ERR_ARGUMENT;
+                                 long long ld_gate, int transpose_out, void* status, void* stream) {
+  if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0 || (ld_gate & 15)) return ubm::UBM_ERR_ARGUMENT;
   if (bias != nullptr && (ldb < Nk || (ldb & 7))) return ubm::UBM_ERR_ARGUMENT;
   if (g_attn_variant == 1)
-    return ubm::launch_attention<64, 64, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
+    return ubm::launch_attention<64, 64, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, ld_gate, transpose_out,
                                             status, stream);
-  return ubm::launch_attention<64, 64, 2, true>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, transpose_out,
+  return ubm::launch_attention<64, 64, 2, true>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, ld_gate, transpose_out,
                                                 status, stream);
 }
 
@@ -703,6 +746,6 @@ extern "C" int ubm_attention_d32_peer_bias(const void* q, const void* k, const v
                                            long long ld_in, void* status, void* stream) {
   if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0 || npeers <= 0) return ubm::UBM_ERR_ARGUMENT;
   if (ldb < Nk || (ldb & 7) || (peer_head_stride & 7)) return ubm::UBM_ERR_ARGUMENT;
-  return ubm::launch_attention<32, 128, 2>(q, k, v, nullptr, gate, out, rows, Nq, Nk, H, ldb, ld_in, 0, status,
+  return ubm::launch_attention<32, 128, 2>(q, k, v, nullptr, gate, out, rows, Nq, Nk, H, ldb, ld_in, 0, 0, status,
                                            stream, npeers, bias_ptrs, peer_rows, peer_head_stride);
 }

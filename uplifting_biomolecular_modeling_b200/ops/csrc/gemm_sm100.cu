@@ -30,6 +30,7 @@ struct GemmParams {
   float alpha;
   int out_fp32;
   int act;  // 0 none, 1 silu, 2 sigmoid, 3 gelu (erf), 4 relu
+  int act_col0;  // the activation applies to output columns >= act_col0 (a multiple of 32; 0 = all columns)
   int res_tma;  // residual tiles arrive by TMA (tensor map in the auxiliary map slot 0)
   // blocked output (cblk_col != 0): element (m, n) goes to (m / 32) * cblk_hi + (m % 32) * cblk_lo +
   // (n / 32) * cblk_col + n % 32.  With m = (i, c) and n = (j, d), c, d < 32, this writes the outer-product
@@ -422,7 +423,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (n0 + j < n_limit) f[j] += __ldg(p.bias + n0 + j);
             }
           }
-          if (p.act != 0) {
+          if (p.act != 0 && n0 >= p.act_col0) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] = apply_act(f[j], p.act);
           }
@@ -637,16 +638,18 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
 // status: device pointer to a ubm::KernelStatus (16 bytes) or null.
 // cblk_*: blocked output addressing (see GemmParams); all zero for the plain [M][N] layout.  The blocked form
 // needs N to be a multiple of 32.  gate: optional bf16 [gate_rows][ld_gate] multiplied in before the residual
-// (C = act(alpha A.B^T + bias) * gate[m % gate_rows] + residual).
+// (C = act(alpha A.B^T + bias) * gate[m % gate_rows] + residual).  act_col0: the activation applies to columns
+// >= act_col0 only (several projections with different activations in one GEMM).
 extern "C" int ubm_gemm_bf16_ex(const void* A, const void* B, void* C, const void* bias, const void* residual, int M,
                                 int N, int K, int batch, long long lda, long long ldb, long long ldc, long long ldr,
                                 long long strideA, long long strideB, long long strideC, long long strideR,
                                 int mn_major, int out_fp32, int act, float alpha, long long cblk_hi,
                                 long long cblk_lo, long long cblk_col, const void* gate, long long ld_gate,
-                                int gate_rows, void* status, void* stream) {
+                                int gate_rows, int act_col0, void* status, void* stream) {
   using namespace ubm;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return UBM_ERR_ARGUMENT;
   if (cblk_col != 0 && ((N & 31) || residual != nullptr)) return UBM_ERR_ARGUMENT;
+  if (act_col0 < 0 || (act_col0 & 31)) return UBM_ERR_ARGUMENT;
   if ((lda & 7) || (ldb & 7) || (batch > 1 && ((strideA & 7) || (strideB & 7)))) {
     fprintf(stderr, "[ubm] gemm: leading dimensions / batch strides must be multiples of 8 elements\n");
     return UBM_ERR_ARGUMENT;
@@ -666,6 +669,7 @@ extern "C" int ubm_gemm_bf16_ex(const void* A, const void* B, void* C, const voi
   p.alpha = alpha;
   p.out_fp32 = out_fp32;
   p.act = act;
+  p.act_col0 = act_col0;
   p.cblk_hi = cblk_hi;
   p.cblk_lo = cblk_lo;
   p.cblk_col = cblk_col;
@@ -703,7 +707,7 @@ extern "C" int ubm_gemm_bf16(const void* A, const void* B, void* C, const void* 
                              long long strideA, long long strideB, long long strideC, long long strideR, int mn_major,
                              int out_fp32, int act, float alpha, void* status, void* stream) {
   return ubm_gemm_bf16_ex(A, B, C, bias, residual, M, N, K, batch, lda, ldb, ldc, ldr, strideA, strideB, strideC,
-                          strideR, mn_major, out_fp32, act, alpha, 0, 0, 0, nullptr, 0, 0, status, stream);
+                          strideR, mn_major, out_fp32, act, alpha, 0, 0, 0, nullptr, 0, 0, 0, status, stream);
 }
 
 // GEMM whose epilogue scatters output rows to their owners: the transfer half of a reduce-scatter fused into the

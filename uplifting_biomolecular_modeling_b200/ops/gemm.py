@@ -23,9 +23,10 @@ def _as3(t: torch.Tensor) -> torch.Tensor:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, mn_major: bool = False, bias: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, act: Optional[str] = None, alpha: float = 1.0,
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
-         c_blocked: Optional[tuple] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+         c_blocked: Optional[tuple] = None, gate: Optional[torch.Tensor] = None, act_from: int = 0) -> torch.Tensor:
     """C = act(alpha * A.B^T + bias) * gate + residual.
 
+    ``act_from``: the activation applies to output columns >= act_from (a multiple of 32) only.
     ``gate`` (bf16 [rows, N], rows dividing M, row stride free): row m is multiplied by gate row m % rows -
     a conditioning gate shared by the samples stacked along M.
 
@@ -88,7 +89,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, mn_major: bool = False, bias: Opti
         0 if res3 is None or batch == 1 else res3.stride(0),
         1 if mn_major else 0, 1 if out3.dtype == torch.float32 else 0, ACT[act], float(alpha),
         int(cb[0]), int(cb[1]), int(cb[2]), native.ptr(gate), 0 if gate is None else gate.stride(0),
-        0 if gate is None else gate.shape[0], native.ptr(st), native.current_stream(a.device))
+        0 if gate is None else gate.shape[0], int(act_from), native.ptr(st), native.current_stream(a.device))
     native.check(rc, "ubm_gemm_bf16_ex")
     if c_blocked is not None:
         return out

@@ -40,7 +40,7 @@ _SIGNATURES = {
     "ubm_template_tail": [c_void_p, c_void_p, c_int, c_ll, c_int, c_void_p],
     "ubm_gemm_bf16_ex": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                          c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_int, c_int, c_int, c_float,
-                         c_ll, c_ll, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p],
+                         c_ll, c_ll, c_ll, c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p],
 }
 
 ERROR_NAMES = {0: "ok", -1: "bad argument", -2: "driver entry point / tensor map", -3: "launch failed",

@@ -147,8 +147,8 @@ def trimul_fused(z: torch.Tensor, mask: Optional[torch.Tensor], w: TrimulPacked,
 
 
 # ------------------------------------------------------------------------------------------
-native.declare("ubm_attention_d32", [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_ll, c_ll, c_int, c_void_p, c_void_p])
-native.declare("ubm_attention_d64", [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_ll, c_ll, c_int, c_void_p, c_void_p])
+native.declare("ubm_attention_d32", [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_void_p, c_void_p])
+native.declare("ubm_attention_d64", [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_void_p, c_void_p])
 
 native.declare("ubm_attention_set_variant", [c_int])
 
@@ -198,15 +198,17 @@ class TriattPacked:
 
 
 def attention(q, k, v, bias, gate, out, rows: int, Nq: int, Nk: int, H: int, D: int = 32, ldb: int = 0,
-              ld_in: int = 0, transpose_out: bool = False):
+              ld_in: int = 0, transpose_out: bool = False, ld_gate: int = 0):
     """Raw launch of the tcgen05 attention kernel (see csrc/attention_sm100.cu for the layout).
-    D is the (padded) head dimension, 32 or 64; ld_in the row stride of q / k / v in elements."""
+    D is the (padded) head dimension, 32 or 64; ld_in the row stride of q / k / v in elements, ld_gate that of
+    the gate (0 = H * D)."""
     st = native.status_tensor(q.device)
     fn = native.lib().ubm_attention_d32 if D == 32 else native.lib().ubm_attention_d64
     if D not in (32, 64):
         raise ValueError("attention kernel supports head dimensions 32 and 64 (pad smaller heads)")
     rc = fn(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(bias), native.ptr(gate), native.ptr(out), rows,
-            Nq, Nk, H, ldb, ld_in, 1 if transpose_out else 0, native.ptr(st), native.current_stream(q.device))
+            Nq, Nk, H, ldb, ld_in, ld_gate, 1 if transpose_out else 0, native.ptr(st),
+            native.current_stream(q.device))
     native.check(rc, f"ubm_attention_d{D}")
     return out
 
@@ -222,6 +224,8 @@ class ApbPacked:
     wqkv: torch.Tensor      # bf16 [3*H*Dp, c]
     bqkv: torch.Tensor      # fp32 [3*H*Dp]
     wg: torch.Tensor        # bf16 [H*Dp, c]
+    wqkvg: torch.Tensor     # bf16 [4*H*Dp, c]: q|k|v|gate in one projection (sigmoid on the last quarter)
+    bqkvg: torch.Tensor     # fp32 [4*H*Dp]
     wo: torch.Tensor        # bf16 [c, H*Dp]
     H: int
     Dp: int
@@ -248,7 +252,10 @@ class ApbPacked:
         wg = pad_rows(w_g).to(torch.bfloat16).contiguous()
         wo = torch.zeros((w_o.shape[0], heads, Dp), dtype=torch.float32, device=w_o.device)
         wo[:, :, :D] = w_o.detach().float().view(w_o.shape[0], heads, D)
-        return cls(wqkv, bqkv, wg, wo.view(w_o.shape[0], heads * Dp).to(torch.bfloat16).contiguous(), heads, Dp)
+        wqkvg = torch.cat([wqkv, wg], 0).contiguous()
+        bqkvg = torch.cat([bqkv, torch.zeros(heads * Dp, device=w_q.device)]).contiguous()
+        return cls(wqkv, bqkv, wg, wqkvg, bqkvg,
+                   wo.view(w_o.shape[0], heads * Dp).to(torch.bfloat16).contiguous(), heads, Dp)
 
 
 def apb_fused(x: torch.Tensor, w: ApbPacked, bias_planes: torch.Tensor, ldb: int,
@@ -260,11 +267,12 @@ def apb_fused(x: torch.Tensor, w: ApbPacked, bias_planes: torch.Tensor, ldb: int
     B, N, c = x.shape
     HD = w.H * w.Dp
     x2 = x.reshape(B * N, c)
-    qkv = _gemm.gemm(x2, w.wqkv, bias=w.bqkv)
-    g = _gemm.gemm(x2, w.wg, act="sigmoid")
+    # q | k | v | gate from one GEMM (sigmoid on the gate columns); the attention kernel reads all four as column
+    # slices of its output
+    qkvg = _gemm.gemm(x2, w.wqkvg, bias=w.bqkvg, act="sigmoid", act_from=3 * HD)
     o = torch.empty((B * N, HD), dtype=torch.bfloat16, device=x.device)
-    attention(qkv[:, :HD], qkv[:, HD:2 * HD], qkv[:, 2 * HD:], bias_planes, g, o, rows=B, Nq=N, Nk=N, H=w.H,
-              D=w.Dp, ldb=ldb, ld_in=3 * HD)
+    attention(qkvg[:, :HD], qkvg[:, HD:2 * HD], qkvg[:, 2 * HD:3 * HD], bias_planes, qkvg[:, 3 * HD:], o, rows=B,
+              Nq=N, Nk=N, H=w.H, D=w.Dp, ldb=ldb, ld_in=4 * HD, ld_gate=4 * HD)
     return _gemm.gemm(o, w.wo, gate=out_gate, residual=out_residual).view(B, N, -1)
 
 
