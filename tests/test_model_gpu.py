@@ -102,3 +102,33 @@ def test_template_embedder_fused_vs_reference():
     assert (v_fused - v_ref).abs().max().item() < 3e-2 * v_ref.abs().max().item()
     err = ((out.float() - ref).abs().mean() / ref.abs().mean()).item()
     assert err < 5e-2, err
+
+
+@pytest.mark.parametrize("dim", [64, 256])
+def test_transition_other_widths_fused_vs_reference(dim):
+    from uplifting_biomolecular_modeling_b200.models import pairformer
+    from uplifting_biomolecular_modeling_b200.ops import native
+    torch.manual_seed(3)
+    t = pairformer.Transition(dim).cuda().eval()
+    x = torch.randn(3, 700, dim, device="cuda")
+    with torch.no_grad():
+        ref = t(x, residual=True)
+        tb = t.to(torch.bfloat16)
+        tb.impl = "fused"
+        out = tb(x.bfloat16(), residual=True)
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "transition")
+    err = ((out.float() - ref).abs().mean() / (ref - x).abs().mean()).item()
+    assert err < 5e-2, err
+
+
+def test_layernorm_rows_narrow():
+    from uplifting_biomolecular_modeling_b200.ops import rows
+    g = torch.Generator(device="cuda").manual_seed(4)
+    for C in (64, 128, 256, 384):
+        x = (torch.randn(1001, C, device="cuda", generator=g) * 2 + 0.5).bfloat16()
+        w = 1 + 0.1 * torch.randn(C, device="cuda", generator=g)
+        b = 0.1 * torch.randn(C, device="cuda", generator=g)
+        ref = torch.nn.functional.layer_norm(x.float(), (C,), w, b)
+        out = rows.layernorm_rows(x, w, b)
+        assert torch.allclose(out.float(), ref, atol=3e-2, rtol=2e-2), C

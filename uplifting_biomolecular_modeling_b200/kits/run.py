@@ -104,7 +104,7 @@ def _run_lm(spec, act, args, allow_partial, family) -> int:
         return report.EXIT_NOT_ACTIVE
     act.register_exit()
     model = lm.build(family, spec.config if args.model_config is None else args.model_config, device=device,
-                     mode=act.mode, seed=args.seed)
+                     mode=act.mode, seed=args.seed, kit=spec.name)
     prompt = args.prompt or "ACGT" * 16
     t0 = time.time()
     res = model.run(args.verb, prompt, max_new_tokens=args.max_new_tokens)

@@ -1,12 +1,13 @@
 """Sequence-model families behind the language-model and genomic-track kits (``score`` / ``generate`` /
-``predict`` verbs).  ``evo2`` is the StripedHyena-2 decoder of :mod:`models.evo2`; the protein language
-models and the genomic track models are served by small generic stand-ins of the right operator mix
-until their own modules are written."""
+``predict`` verbs): ``evo2`` is the StripedHyena-2 decoder of :mod:`models.evo2`, the protein / DNA language
+models (ESM-C, E1, ProGen2, GPN-Star) live in :mod:`models.plm`, the genomic track models (Enformer, Borzoi,
+Flashzoi, ChromBPNet) in :mod:`models.genomics`.  ``build`` returns a runner with one ``run(verb, prompt)``
+method so the kit command line does not depend on the family."""
 from __future__ import annotations
 
 import torch
 
-from . import evo2
+from . import evo2, genomics, plm
 
 
 class _Runner:
@@ -24,8 +25,56 @@ class _Runner:
         raise ValueError(f"unknown verb {verb!r}")
 
 
-def build(family: str, config: str, device="cpu", mode: str = "exact", seed: int = 0) -> _Runner:
-    cfg = config if config in evo2.CONFIGS else "evo2_tiny"
+class _PLMRunner(_Runner):
+    def run(self, verb: str, prompt: str, max_new_tokens: int = 32) -> dict:
+        cfg = self.model.cfg
+        toks = plm.tokenize(prompt, cfg, self.device)
+        kw = {}
+        if cfg.family == "gpnstar":
+            align, index = plm.synthetic_alignment(cfg, toks)
+            kw = {"alignment": align, "clade_index": index}
+        if verb == "generate":
+            out = self.model.generate(toks, max_new_tokens)
+            letters = plm.AMINO
+            return {"new_tokens": int(out.shape[1] - toks.shape[1]),
+                    "text": "".join(letters[int(t) - 4] if 4 <= int(t) < 4 + len(letters) else "X"
+                                    for t in out[0].tolist())}
+        if verb in ("score", "predict", "embedding", "logits", "vep"):
+            res = {"score": float(self.model.score(toks, **kw)[0]), "tokens": int(toks.shape[1])}
+            if verb == "vep" and cfg.family == "gpnstar":
+                res["vep_min"] = float(self.model.variant_effect(toks, **kw).min())
+            return res
+        raise ValueError(f"unknown verb {verb!r}")
+
+
+class _TrackRunner(_Runner):
+    def run(self, verb: str, prompt: str, max_new_tokens: int = 32) -> dict:
+        if verb not in ("predict", "score"):
+            raise ValueError(f"unknown verb {verb!r}")
+        cfg = self.model.cfg
+        need = genomics.input_length(cfg)
+        text = (prompt * (need // max(1, len(prompt)) + 1))[:need]
+        x = genomics.one_hot_dna(text, self.device, next(self.model.parameters()).dtype)
+        with torch.no_grad():
+            out = self.model(x)
+        if cfg.family == "chrombpnet":
+            prof, counts = out
+            return {"score": float(counts[0]), "bins": int(prof.shape[1]), "tokens": need}
+        return {"score": float(out.mean()), "bins": int(out.shape[1]), "tracks": int(out.shape[2]), "tokens": need}
+
+
+def build(family: str, config: str, device="cpu", mode: str = "exact", seed: int = 0, kit: str = "") -> _Runner:
+    """``family`` is the kit's model family (evo2 | protein_lm | genomic_track), ``kit`` its name (which model of the
+    family), ``config`` a configuration key of that model (unknown keys fall back to the model's small default)."""
     dtype = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
+    if family == "protein_lm" or kit in plm.DEFAULT:
+        name = config if config in plm.CONFIGS else plm.DEFAULT.get(kit, "esmc_tiny")
+        impl = "reference" if mode == "off" else None
+        return _PLMRunner(plm.build(name, device=device, dtype=dtype, seed=seed, impl=impl), device, mode)
+    if family == "genomic_track" or kit in genomics.DEFAULT:
+        name = config if config in genomics.CONFIGS else genomics.DEFAULT.get(kit, "enformer_tiny")
+        impl = "reference" if mode == "off" else None
+        return _TrackRunner(genomics.build(name, device=device, dtype=dtype, seed=seed, impl=impl), device, mode)
+    cfg = config if config in evo2.CONFIGS else "evo2_tiny"
     m = evo2.build(cfg, device=device, dtype=dtype, seed=seed)
     return _Runner(m, device, mode)

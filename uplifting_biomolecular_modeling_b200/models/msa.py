@@ -36,18 +36,15 @@ class OuterProductMean(_Switchable):
         if not (self.impl == "fused" and m.is_cuda and m.dtype == torch.bfloat16 and m.shape[0] == 1):
             return R.outer_product_mean(m, mask, self.norm.weight, self.norm.bias, self.proj_a.weight,
                                         self.proj_b.weight, self.proj_o.weight, self.proj_o.bias)
-        from ..ops import gemm
+        from ..ops import gemm, rows
         B, S, N, _ = m.shape
         c = self.c_hidden
-        n = self.norm(m)
+        n = rows.layernorm_rows(m.contiguous(), self.norm.weight, self.norm.bias, self.norm.eps)
         mk = mask.unsqueeze(-1).to(n.dtype)
-        a = (self.proj_a(n) * mk)[0]                      # [S, N, c]
-        b = (self.proj_b(n) * mk)[0]
-        Sp = (S + 7) // 8 * 8
-        at = torch.zeros((N * c, Sp), dtype=torch.bfloat16, device=m.device)
-        bt = torch.zeros((N * c, Sp), dtype=torch.bfloat16, device=m.device)
-        at[:, :S] = a.permute(1, 2, 0).reshape(N * c, S)
-        bt[:, :S] = b.permute(1, 2, 0).reshape(N * c, S)
+        # [S, N, c] seen as [S, N*c]: sequences (the contraction) along rows, (token, channel) contiguous - the
+        # operand form of the MN-major GEMM, so no [N*c, S] transposed copies are made
+        a2 = (self.proj_a(n) * mk)[0].reshape(S, N * c)
+        b2 = (self.proj_b(n) * mk)[0].reshape(S, N * c)
         wo = self.proj_o.weight.to(torch.bfloat16).contiguous()
         bo = self.proj_o.bias.float()
         out = torch.empty((N, N, wo.shape[0]), dtype=torch.bfloat16, device=m.device)
@@ -66,10 +63,11 @@ class OuterProductMean(_Switchable):
             nr = (i1 - i0) * N
             if blocked:
                 # product [(i, c), (j, d)] stored straight into [(i, j), (c, d)] by the kernel's epilogue
-                gemm.gemm(at[i0 * c:i1 * c], bt, alpha=1.0 / S, out=t2, c_blocked=(N * c * c, c, c * c))
+                gemm.gemm(a2[:, i0 * c:i1 * c], b2, mn_major=True, alpha=1.0 / S, out=t2,
+                          c_blocked=(N * c * c, c, c * c))
                 t = t2[:nr]
             else:
-                t = gemm.gemm(at[i0 * c:i1 * c], bt, alpha=1.0 / S)
+                t = gemm.gemm(a2[:, i0 * c:i1 * c], b2, mn_major=True, alpha=1.0 / S)
                 t = t.view(i1 - i0, c, N, c).permute(0, 2, 1, 3).reshape(nr, c * c)
             if scale is None:
                 gemm.gemm(t, wo, bias=bo, out=out[i0:i1].view(nr, -1))
@@ -98,7 +96,7 @@ class PairWeightedAveraging(_Switchable):
         from ..ops import gemm, rows
         B, S, N, _ = m.shape
         H, c = self.heads, self.c_h
-        mn = self.norm_m(m)
+        mn = rows.layernorm_rows(m.contiguous(), self.norm_m.weight, self.norm_m.bias, self.norm_m.eps)
         b = rows.pair_head_bias(z[0].contiguous(), self.norm_z.weight, self.norm_z.bias, self.proj_z.weight).float()
         b = b + ((1.0 - mask[0].float()) * -1e6)[None]
         Np = (N + 7) // 8 * 8

@@ -64,6 +64,20 @@ class Transition(_Switchable):
                 self._packed = pair.TransitionPacked.pack(self.norm.weight, self.norm.bias, self.fc1.weight,
                                                           self.fc2.weight, self.fc3.weight)
             return pair.transition_fused(x.contiguous(), self._packed, residual=residual)
+        if self.impl == "fused" and x.is_cuda and x.dtype == torch.bfloat16 and self.dim % 8 == 0 \
+                and self.dim <= 1024 and self.hidden % 8 == 0 and self.out_dim % 8 == 0:
+            # other widths (the MSA track at 64, the template stack): LayerNorm rows -> one GEMM for both hidden
+            # projections -> SwiGLU rows -> output GEMM with the residual in its epilogue
+            from ..ops import gemm, rows
+            if self._packed is None:
+                self._packed = (torch.cat([self.fc1.weight, self.fc2.weight], 0).detach().to(torch.bfloat16).contiguous(),
+                                self.fc3.weight.detach().to(torch.bfloat16).contiguous())
+            w12, w3 = self._packed
+            x2 = x.reshape(-1, self.dim).contiguous()
+            n = rows.layernorm_rows(x2, self.norm.weight, self.norm.bias, self.norm.eps)
+            h = rows.swiglu_rows(gemm.gemm(n, w12))
+            y = gemm.gemm(h, w3, residual=x2 if residual and self.out_dim == self.dim else None)
+            return y.view(*x.shape[:-1], self.out_dim)
         return R.transition(x, self.norm.weight, self.norm.bias, self.fc1.weight, self.fc2.weight, self.fc3.weight,
                             residual=residual)
 

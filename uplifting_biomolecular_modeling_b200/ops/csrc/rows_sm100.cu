@@ -72,6 +72,66 @@ __global__ void __launch_bounds__(256) layernorm_rows_kernel(const TI* __restric
   }
 }
 
+// LayerNorm of narrow bf16 rows with 16-byte accesses: C = 8 * LPR channels, LPR lanes per row (8, 16 or 32),
+// 32 / LPR rows per warp instruction; statistics by xor-shuffles inside the LPR lanes of a row.  The MSA track
+// (C = 64, 1.5 M rows per call) spends its LayerNorms here.
+template <int LPR>
+__global__ void __launch_bounds__(256) layernorm_rows_narrow_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                    const float* __restrict__ gamma,
+                                                                    const float* __restrict__ beta,
+                                                                    __nv_bfloat16* __restrict__ out, long long R,
+                                                                    float eps) {
+  constexpr int C = 8 * LPR;
+  constexpr int RPW = 32 / LPR;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / LPR, li = lane % LPR;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  float g[8], b[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    g[j] = gamma != nullptr ? gamma[li * 8 + j] : 1.f;
+    b[j] = beta != nullptr ? beta[li * 8 + j] : 0.f;
+  }
+  for (long long r0 = wid * RPW; r0 < R; r0 += warps * RPW) {
+    const long long r = r0 + sub;
+    const bool ok = r < R;
+    float v[8];
+    float sum = 0.f;
+    if (ok) {
+      const uint4 u = *reinterpret_cast<const uint4*>(x + r * C + li * 8);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[2 * j] = bf16_lo(w[j]);
+        v[2 * j + 1] = bf16_hi(w[j]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sum += v[j];
+#pragma unroll
+    for (int s = LPR / 2; s > 0; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
+    const float mu = sum * (1.0f / C);
+    float sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sq += (v[j] - mu) * (v[j] - mu);
+#pragma unroll
+    for (int s = LPR / 2; s > 0; s >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, s);
+    const float rstd = rsqrtf(sq * (1.0f / C) + eps);
+    if (ok) {
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        o[j] = pack_bf16x2((v[2 * j] - mu) * rstd * g[2 * j] + b[2 * j],
+                           (v[2 * j + 1] - mu) * rstd * g[2 * j + 1] + b[2 * j + 1]);
+      *reinterpret_cast<uint4*>(out + r * C + li * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
 // z rows [R][128] bf16 -> planes out[h][i][j] (bf16, leading dimension Np), LN folded:
 //   out = scale_out * (rstd * (w[h] . x - mu * colsum[h]) + colbias[h])
 // One thread per row; weights in shared memory (broadcast reads).
@@ -300,6 +360,20 @@ extern "C" int ubm_layernorm_rows(const void* x, const void* gamma, const void* 
   using namespace ubm;
   if (R <= 0 || C <= 0 || C > 1024) return UBM_ERR_ARGUMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (in_dtype == 0 && out_dtype == 0 && (C == 64 || C == 128 || C == 256) &&
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+    const __nv_bfloat16* xx = static_cast<const __nv_bfloat16*>(x);
+    __nv_bfloat16* oo = static_cast<__nv_bfloat16*>(out);
+    const float* gg = static_cast<const float*>(gamma);
+    const float* bb = static_cast<const float*>(beta);
+    const int rows_per_block = 8 * (256 / C);
+    const int grid2 = grid_for(R, rows_per_block);
+    if (C == 64) layernorm_rows_narrow_kernel<8><<<grid2, 256, 0, st>>>(xx, gg, bb, oo, R, eps);
+    else if (C == 128) layernorm_rows_narrow_kernel<16><<<grid2, 256, 0, st>>>(xx, gg, bb, oo, R, eps);
+    else layernorm_rows_narrow_kernel<32><<<grid2, 256, 0, st>>>(xx, gg, bb, oo, R, eps);
+    UBM_CHECK_LAUNCH("layernorm_rows_narrow_kernel");
+    return UBM_OK;
+  }
   const int grid = grid_for(R, 8);
   const float* g = static_cast<const float*>(gamma);
   const float* b = static_cast<const float*>(beta);

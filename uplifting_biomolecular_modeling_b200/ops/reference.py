@@ -242,3 +242,26 @@ def pool2(x, mode: str = "max", w=None):
 def residual_ln(x, res, gamma, beta, eps: float = 1e-5):
     s = (x.float() + res.float()).to(x.dtype).float()
     return torch.nn.functional.layer_norm(s, (s.shape[-1],), gamma.float(), None if beta is None else beta.float(), eps)
+
+
+def column_attention(q, k, v, index, bias=None, scale=None):
+    """q: [T, H, D]; k, v: [R, T, H, D]; index: [C] clade -> row; bias: [H, C] or None."""
+    D = q.shape[-1]
+    sc = float(D) ** -0.5 if scale is None else float(scale)
+    kc, vc = k.float()[index.long()], v.float()[index.long()]          # [C, T, H, D]
+    s = torch.einsum("thd,cthd->thc", q.float(), kc) * sc
+    if bias is not None:
+        s = s + bias.float().unsqueeze(0)
+    return torch.einsum("thc,cthd->thd", torch.softmax(s, -1), vc)
+
+
+def relative_shift(pos):
+    """pos: [..., L, >= 2L - 1] -> [..., L, L] with out[i, j] = pos[i, j - i + L - 1]."""
+    L = pos.shape[-2]
+    j = torch.arange(L, device=pos.device)
+    gather = (j[None, :] - j[:, None] + L - 1).expand(pos.shape[:-2] + (L, L))
+    return torch.gather(pos, -1, gather)
+
+
+def relshift_softmax(content, pos):
+    return torch.softmax(content.float() + relative_shift(pos.float()), -1)

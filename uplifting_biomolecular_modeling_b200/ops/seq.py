@@ -26,6 +26,8 @@ native.declare("ubm_pool2", [c_void_p] * 3 + [c_int] * 4 + [c_void_p])
 native.declare("ubm_residual_ln", [c_void_p] * 6 + [c_ll, c_int, c_float, c_void_p])
 
 native.declare("ubm_gemv_rows", [c_void_p] * 4 + [c_int] * 3 + [c_void_p])
+native.declare("ubm_column_attention", [c_void_p] * 6 + [c_ll, c_int, c_int, c_int, c_float, c_void_p])
+native.declare("ubm_relshift_softmax", [c_void_p] * 3 + [c_ll, c_int, c_int, c_void_p])
 
 EW = {"gelu_new": 0, "add2": 1, "bias_residual": 2, "scale_shift_gelu": 3, "silu_mul": 4}
 
@@ -209,4 +211,43 @@ def gemv_rows(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
     rc = native.lib().ubm_gemv_rows(native.ptr(x), native.ptr(w), native.ptr(bias), native.ptr(out), M, N, K,
                                     _stream(x))
     native.check(rc, "ubm_gemv_rows")
+    return out
+
+
+def column_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, index: torch.Tensor,
+                     bias: Optional[torch.Tensor] = None, scale: Optional[float] = None) -> torch.Tensor:
+    """Per-column attention over clade rows (``csrc/lmops_sm100.cu``).  q: bf16 [T, H, D]; k, v: bf16 [R, T, H, D]
+    (one row per distinct alignment row); index: int [C] clade -> row; bias: fp32 [H, C] or None.  D is 32 or 64,
+    C <= 256.  Returns bf16 [T, H, D]."""
+    q, k, v = _bf16c(q), _bf16c(k), _bf16c(v)
+    T, H, D = q.shape
+    C = index.shape[0]
+    idx = index.to(torch.int32).contiguous()
+    out = torch.empty_like(q)
+    sc = float(D) ** -0.5 if scale is None else float(scale)
+    rc = native.lib().ubm_column_attention(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(idx),
+                                           native.ptr(_f32(bias)), native.ptr(out), T, H, D, C, sc, _stream(q))
+    native.check(rc, "ubm_column_attention")
+    return out
+
+
+def relshift_softmax(content: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+    """softmax_j(content[..., i, j] + pos[..., i, j - i + L - 1]) for content fp32 [..., L, L] and relative-position
+    logits pos fp32 [..., L, P] with P >= 2L - 1 (columns past 2L - 2 are padding; the row stride of ``pos`` may
+    exceed P): the shift is an index, no shifted copy is made."""
+    content = content.float().contiguous()
+    L = content.shape[-1]
+    if pos.dtype != torch.float32 or pos.stride(-1) != 1:
+        pos = pos.float().contiguous()
+    ldp = pos.stride(-2)
+    flat = pos.dim() == 2 or all(pos.stride(i) == pos.stride(i + 1) * pos.shape[i + 1] for i in range(pos.dim() - 2))
+    if not flat:
+        pos = pos.contiguous()
+        ldp = pos.stride(-2)
+    if content.shape[-2] != L or pos.shape[-1] < 2 * L - 1 or pos.shape[:-1] != content.shape[:-1]:
+        raise ValueError("relshift_softmax expects content [..., L, L] and pos [..., L, >= 2L - 1]")
+    out = torch.empty_like(content)
+    rc = native.lib().ubm_relshift_softmax(native.ptr(content), native.ptr(pos), native.ptr(out),
+                                           content.numel() // L, L, ldp, _stream(content))
+    native.check(rc, "ubm_relshift_softmax")
     return out
