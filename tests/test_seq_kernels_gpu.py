@@ -133,3 +133,16 @@ def test_gemv_rows(M):
     w = (torch.randn(N, K, device="cuda", generator=g) * K ** -0.5).bfloat16()
     b = torch.randn(N, device="cuda", generator=g)
     _close(seq.gemv_rows(x, w, b), x.float() @ w.float().t() + b)
+
+
+def test_per_channel_vectors_given_in_bf16():
+    """Per-channel vectors that need a conversion are converted into tensors that outlive the launch."""
+    from uplifting_biomolecular_modeling_b200.ops import reference as R, seq
+    g = torch.Generator(device="cuda").manual_seed(11)
+    x = torch.randn(3, 50, 64, device="cuda", generator=g).bfloat16()
+    sc = (1 + 0.1 * torch.randn(64, device="cuda", generator=g)).bfloat16()
+    sh = (0.5 * torch.randn(64, device="cuda", generator=g)).bfloat16()
+    want = torch.nn.functional.gelu(x.float() * sc.float() + sh.float())
+    _close(seq.scale_shift_gelu(x, sc, sh), want)
+    res = torch.randn(3, 50, 64, device="cuda", generator=g).bfloat16()
+    _close(seq.residual_ln(x, res, sc, sh), R.residual_ln(x, res, sc, sh))

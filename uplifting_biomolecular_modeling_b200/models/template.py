@@ -71,9 +71,10 @@ class TemplateEmbedder(_Switchable):
         pbm = f["template_pb_mask"].float().contiguous()
         bbm = f["template_bb_mask"].float().contiguous()
         asym = f["asym_id"].to(torch.int32).contiguous()
+        zpc = zp.to(bf).contiguous()
         rc = native.lib().ubm_template_embed(native.ptr(dg), native.ptr(uv), native.ptr(pbm), native.ptr(bbm),
                                              native.ptr(asym), native.ptr(ri), native.ptr(rj),
-                                             native.ptr(zp.to(bf).contiguous()), native.ptr(w_dgram),
+                                             native.ptr(zpc), native.ptr(w_dgram),
                                              native.ptr(w_vec), native.ptr(out), T, N, native.current_stream(dev))
         native.check(rc, "ubm_template_embed")
         return out.to(zp.dtype)
@@ -97,7 +98,8 @@ class TemplateEmbedder(_Switchable):
             from ..ops import gemm, native
             N = s.shape[1]
             u = torch.empty((N * N, self.c_t), dtype=torch.bfloat16, device=s.device)
-            rc = native.lib().ubm_template_tail(native.ptr(s.contiguous()), native.ptr(u), T, N * N, self.c_t,
+            sc = s.contiguous()
+            rc = native.lib().ubm_template_tail(native.ptr(sc), native.ptr(u), T, N * N, self.c_t,
                                                 native.current_stream(s.device))
             native.check(rc, "ubm_template_tail")
             out = gemm.gemm(u, self.linear_t.weight.detach().to(torch.bfloat16).contiguous()).view(N, N, -1)

@@ -50,7 +50,8 @@ def rmsnorm_rows(x: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6) -> tor
     x = _bf16c(x)
     C = x.shape[-1]
     out = torch.empty_like(x)
-    rc = native.lib().ubm_rmsnorm_rows(native.ptr(x), native.ptr(_f32(scale)), native.ptr(out), x.numel() // C, C,
+    sc = _f32(scale)        # held in a variable: a temporary would be freed (and its block reused) before the launch
+    rc = native.lib().ubm_rmsnorm_rows(native.ptr(x), native.ptr(sc), native.ptr(out), x.numel() // C, C,
                                        float(eps), _stream(x))
     native.check(rc, "ubm_rmsnorm_rows")
     return out
@@ -83,7 +84,8 @@ def fir_inner_gate(u: torch.Tensor, ht: torch.Tensor, D: torch.Tensor, x2: Optio
     out = torch.empty_like(u)
     x2c = None if x2 is None else _bf16c(x2)
     t = None if tail is None else _bf16c(tail)
-    rc = native.lib().ubm_fir_inner_gate(native.ptr(u), native.ptr(ht), native.ptr(_f32(D)), native.ptr(x2c),
+    Df = _f32(D)
+    rc = native.lib().ubm_fir_inner_gate(native.ptr(u), native.ptr(ht), native.ptr(Df), native.ptr(x2c),
                                          native.ptr(t), native.ptr(out), B, L, d, ht.shape[0], _stream(u))
     native.check(rc, "ubm_fir_inner_gate")
     return out
@@ -98,7 +100,8 @@ def fftconv_epilogue(y: torch.Tensor, u: torch.Tensor, D: torch.Tensor, x2: Opti
         raise ValueError("y must be fp32 [B, d, n >= L]")
     out = torch.empty_like(u)
     x2c = None if x2 is None else _bf16c(x2)
-    rc = native.lib().ubm_fftconv_epilogue(native.ptr(y), y.shape[2], native.ptr(u), native.ptr(_f32(D)),
+    Df = _f32(D)
+    rc = native.lib().ubm_fftconv_epilogue(native.ptr(y), y.shape[2], native.ptr(u), native.ptr(Df),
                                            native.ptr(x2c), native.ptr(out), B, L, d, _stream(u))
     native.check(rc, "ubm_fftconv_epilogue")
     return out
@@ -113,8 +116,9 @@ def pole_step(state: torch.Tensor, lam: torch.Tensor, res: torch.Tensor, u: torc
     B, d, S = state.shape
     out = torch.empty_like(u)
     x2c = None if x2 is None else _bf16c(x2)
-    rc = native.lib().ubm_pole_step(native.ptr(state), native.ptr(_f32(lam)), native.ptr(_f32(res)), native.ptr(u),
-                                    native.ptr(_f32(D)), native.ptr(x2c), native.ptr(out), B, d, S, _stream(u))
+    lamf, resf, Df = _f32(lam), _f32(res), _f32(D)
+    rc = native.lib().ubm_pole_step(native.ptr(state), native.ptr(lamf), native.ptr(resf), native.ptr(u),
+                                    native.ptr(Df), native.ptr(x2c), native.ptr(out), B, d, S, _stream(u))
     native.check(rc, "ubm_pole_step")
     return out
 
@@ -126,8 +130,11 @@ def elementwise(op: str, x: torch.Tensor, a: Optional[torch.Tensor] = None, b: O
     out = torch.empty_like(x)
     aa = None if a is None else _bf16c(a)
     bb = None if b is None else _bf16c(b)
-    rc = native.lib().ubm_elementwise(EW[op], native.ptr(x), native.ptr(aa), native.ptr(bb), native.ptr(_f32(v0)),
-                                      native.ptr(_f32(v1)), native.ptr(out), x.numel() // C, C, _stream(x))
+    # the converted vectors live in variables until the launch is queued: two temporaries in one argument list
+    # would share one freed block
+    v0f, v1f = _f32(v0), _f32(v1)
+    rc = native.lib().ubm_elementwise(EW[op], native.ptr(x), native.ptr(aa), native.ptr(bb), native.ptr(v0f),
+                                      native.ptr(v1f), native.ptr(out), x.numel() // C, C, _stream(x))
     native.check(rc, "ubm_elementwise")
     return out
 
@@ -196,7 +203,8 @@ def residual_ln(x: torch.Tensor, res: torch.Tensor, gamma: torch.Tensor, beta: O
     C = x.shape[-1]
     out = torch.empty_like(x)
     s = torch.empty_like(x) if return_sum else None
-    rc = native.lib().ubm_residual_ln(native.ptr(x), native.ptr(res), native.ptr(_f32(gamma)), native.ptr(_f32(beta)),
+    gf, bf = _f32(gamma), _f32(beta)
+    rc = native.lib().ubm_residual_ln(native.ptr(x), native.ptr(res), native.ptr(gf), native.ptr(bf),
                                       native.ptr(s), native.ptr(out), x.numel() // C, C, float(eps), _stream(x))
     native.check(rc, "ubm_residual_ln")
     return (out, s) if return_sum else out
@@ -225,8 +233,9 @@ def column_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, index: t
     idx = index.to(torch.int32).contiguous()
     out = torch.empty_like(q)
     sc = float(D) ** -0.5 if scale is None else float(scale)
+    bf = _f32(bias)
     rc = native.lib().ubm_column_attention(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(idx),
-                                           native.ptr(_f32(bias)), native.ptr(out), T, H, D, C, sc, _stream(q))
+                                           native.ptr(bf), native.ptr(out), T, H, D, C, sc, _stream(q))
     native.check(rc, "ubm_column_attention")
     return out
 
