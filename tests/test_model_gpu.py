@@ -125,7 +125,7 @@ def test_transition_other_widths_fused_vs_reference(dim):
 def test_layernorm_rows_narrow():
     from uplifting_biomolecular_modeling_b200.ops import rows
     g = torch.Generator(device="cuda").manual_seed(4)
-    for C in (64, 128, 256, 384):
+    for C in (64, 128, 256, 384, 768, 960, 1152, 1536, 2048):
         x = (torch.randn(1001, C, device="cuda", generator=g) * 2 + 0.5).bfloat16()
         w = 1 + 0.1 * torch.randn(C, device="cuda", generator=g)
         b = 0.1 * torch.randn(C, device="cuda", generator=g)

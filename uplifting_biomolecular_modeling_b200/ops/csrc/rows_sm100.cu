@@ -72,6 +72,62 @@ __global__ void __launch_bounds__(256) layernorm_rows_kernel(const TI* __restric
   }
 }
 
+// LayerNorm of wide bf16 rows (256 < C <= 2048, C a multiple of 8): one warp per row, 16-byte accesses, the row kept
+// in registers (CHUNKS x 8 values per lane).  The single / token tracks and the LM and genomics trunks land here.
+template <int CHUNKS>
+__global__ void __launch_bounds__(256) layernorm_rows_wide_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                  const float* __restrict__ gamma,
+                                                                  const float* __restrict__ beta,
+                                                                  __nv_bfloat16* __restrict__ out, long long R, int C,
+                                                                  float eps) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  for (long long r = static_cast<long long>(blockIdx.x) * wpb + (threadIdx.x >> 5); r < R;
+       r += static_cast<long long>(gridDim.x) * wpb) {
+    float v[CHUNKS][8];
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < C) {
+        const uint4 u = *reinterpret_cast<const uint4*>(x + r * C + c);
+        v[k][0] = bf16_lo(u.x); v[k][1] = bf16_hi(u.x); v[k][2] = bf16_lo(u.y); v[k][3] = bf16_hi(u.y);
+        v[k][4] = bf16_lo(u.z); v[k][5] = bf16_hi(u.z); v[k][6] = bf16_lo(u.w); v[k][7] = bf16_hi(u.w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sum += v[k][j];
+      }
+    }
+    const float mu = warp_sum(sum) / C;
+    float sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+      if (k * 256 + lane * 8 < C) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = v[k][j] - mu;
+          sq += d * d;
+        }
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(sq) / C + eps);
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < C) {
+        float y[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          y[j] = (v[k][j] - mu) * rstd;
+          if (gamma != nullptr) y[j] *= gamma[c + j];
+          if (beta != nullptr) y[j] += beta[c + j];
+        }
+        *reinterpret_cast<uint4*>(out + r * C + c) = make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]),
+                                                                pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7]));
+      }
+    }
+  }
+}
+
 // LayerNorm of narrow bf16 rows with 16-byte accesses: C = 8 * LPR channels, LPR lanes per row (8, 16 or 32),
 // 32 / LPR rows per warp instruction; statistics by xor-shuffles inside the LPR lanes of a row.  The MSA track
 // (C = 64, 1.5 M rows per call) spends its LayerNorms here.
@@ -358,8 +414,22 @@ static inline int grid_for(long long work, int per_block) {
 extern "C" int ubm_layernorm_rows(const void* x, const void* gamma, const void* beta, void* out, long long R, int C,
                                   float eps, int in_dtype, int out_dtype, void* stream) {
   using namespace ubm;
-  if (R <= 0 || C <= 0 || C > 1024) return UBM_ERR_ARGUMENT;
+  if (R <= 0 || C <= 0) return UBM_ERR_ARGUMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (in_dtype == 0 && out_dtype == 0 && C > 256 && C <= 2048 && (C & 7) == 0 &&
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+    const __nv_bfloat16* xx = static_cast<const __nv_bfloat16*>(x);
+    __nv_bfloat16* oo = static_cast<__nv_bfloat16*>(out);
+    const float* gg = static_cast<const float*>(gamma);
+    const float* bb = static_cast<const float*>(beta);
+    const int gridw = grid_for(R, 8);
+    if (C <= 512) layernorm_rows_wide_kernel<2><<<gridw, 256, 0, st>>>(xx, gg, bb, oo, R, C, eps);
+    else if (C <= 1024) layernorm_rows_wide_kernel<4><<<gridw, 256, 0, st>>>(xx, gg, bb, oo, R, C, eps);
+    else layernorm_rows_wide_kernel<8><<<gridw, 256, 0, st>>>(xx, gg, bb, oo, R, C, eps);
+    UBM_CHECK_LAUNCH("layernorm_rows_wide_kernel");
+    return UBM_OK;
+  }
+  if (C > 1024) return UBM_ERR_ARGUMENT;
   if (in_dtype == 0 && out_dtype == 0 && (C == 64 || C == 128 || C == 256) &&
       ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
     const __nv_bfloat16* xx = static_cast<const __nv_bfloat16*>(x);
