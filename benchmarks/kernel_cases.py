@@ -107,6 +107,12 @@ def main():
         else:
             fn = lambda: (f1(), f2(), f3())  # noqa: E731
             byts, flops = 9 * zb, 2.0 * 128 * N ** 3 + 2.0 * N * N * 128 * 768
+    elif a.case == "head_bias":
+        from uplifting_biomolecular_modeling_b200.ops import rows as rows_ops
+        wb = r(16, c)
+        hb = torch.empty((16, N, Np), dtype=torch.bfloat16, device=dev)
+        fn = lambda: rows_ops.pair_head_bias(z, ones, zeros, wb, out=hb)  # noqa: E731
+        byts, flops = z.numel() * 2 + hb.numel() * 2, 2.0 * N * N * 128 * 16
     elif a.case in ("triatt_proj", "triatt"):
         w = pair.TriattPacked.pack(ones, zeros, r(4, c), r(c, c), r(c, c), r(c, c), r(c, c), r(c), r(c, c), r(c), 4)
         ws = {}

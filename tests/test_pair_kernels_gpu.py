@@ -197,3 +197,21 @@ def test_segment_mean_and_gather_rows():
     got = rows.gather_rows_add(q, a, a2t.to(torch.int32))
     assert torch.equal(got, q + a[:, a2t])
     assert torch.equal(rows.gather_rows_add(None, a, a2t.to(torch.int32)), a[:, a2t])
+
+
+@pytest.mark.parametrize("N", [37, 136, 200])
+@pytest.mark.parametrize("H", [4, 16, 32])
+@pytest.mark.parametrize("transpose", [False, True])
+def test_pair_head_bias_planes(N, H, transpose):
+    """LN(z) -> H head-bias planes, several pair rows per thread (vector stores when 4 rows share a plane row)."""
+    from uplifting_biomolecular_modeling_b200.ops import rows
+    g = torch.Generator(device="cuda").manual_seed(N + H)
+    z = (torch.randn(N, N, 128, device="cuda", generator=g) * 1.5 + 0.3).bfloat16()
+    lw = 1 + 0.1 * torch.randn(128, device="cuda", generator=g)
+    lb = 0.1 * torch.randn(128, device="cuda", generator=g)
+    w = torch.randn(H, 128, device="cuda", generator=g) / 128 ** 0.5
+    out = rows.pair_head_bias(z, lw, lb, w, scale=1.3, transpose=transpose)
+    ref = 1.3 * torch.nn.functional.layer_norm(z.float(), (128,), lw, lb) @ w.t()          # [N, N, H]
+    ref = ref.permute(2, 1, 0) if transpose else ref.permute(2, 0, 1)
+    assert out.shape == (H, N, N)
+    assert (out.float() - ref).abs().max().item() < 4e-2

@@ -191,56 +191,97 @@ __global__ void __launch_bounds__(256) layernorm_rows_narrow_kernel(const __nv_b
 // z rows [R][128] bf16 -> planes out[h][i][j] (bf16, leading dimension Np), LN folded:
 //   out = scale_out * (rstd * (w[h] . x - mu * colsum[h]) + colbias[h])
 // One thread per row; weights in shared memory (broadcast reads).
-template <int H>
+template <int H, int RPT>
 __global__ void __launch_bounds__(128) pair_head_bias_kernel(const __nv_bfloat16* __restrict__ z,
                                                              const float* __restrict__ w,
                                                              const float* __restrict__ colsum,
                                                              const float* __restrict__ colbias,
                                                              __nv_bfloat16* __restrict__ out, int N, int Np,
                                                              int transpose_out) {
+  // Each thread owns RPT consecutive pair rows: a weight vector fetched from shared memory (a broadcast 16-byte
+  // load costs four wavefronts) serves RPT rows, which moves the kernel off the shared-memory limit, and the RPT
+  // results of a head are consecutive plane elements (one 8-byte store for RPT = 4).
   __shared__ float sw[H * 128];
   for (int i = threadIdx.x; i < H * 128; i += blockDim.x) sw[i] = w[i];
   __syncthreads();
   const long long R = static_cast<long long>(N) * N;
-  for (long long r = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; r < R;
-       r += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const uint4* xr = reinterpret_cast<const uint4*>(z + r * 128);
-    float acc[H];
+  const long long groups = (R + RPT - 1) / RPT;
+  for (long long gq = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; gq < groups;
+       gq += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r0 = gq * RPT;
+    float acc[RPT][H];
+    float sum[RPT], sumsq[RPT];
 #pragma unroll
-    for (int h = 0; h < H; ++h) acc[h] = 0.f;
-    float sum = 0.f, sumsq = 0.f;
-#pragma unroll 4
+    for (int q = 0; q < RPT; ++q) {
+      sum[q] = 0.f;
+      sumsq[q] = 0.f;
+#pragma unroll
+      for (int h = 0; h < H; ++h) acc[q][h] = 0.f;
+    }
+#pragma unroll 2
     for (int c16 = 0; c16 < 16; ++c16) {
-      const uint4 u = __ldg(xr + c16);
-      const uint32_t ww[4] = {u.x, u.y, u.z, u.w};
-      float e[8];
+      float e[RPT][8];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        e[2 * j] = bf16_lo(ww[j]);
-        e[2 * j + 1] = bf16_hi(ww[j]);
-      }
+      for (int q = 0; q < RPT; ++q) {
+        const long long r = r0 + q < R ? r0 + q : R - 1;
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(z + r * 128) + c16);
+        e[q][0] = bf16_lo(u.x); e[q][1] = bf16_hi(u.x); e[q][2] = bf16_lo(u.y); e[q][3] = bf16_hi(u.y);
+        e[q][4] = bf16_lo(u.z); e[q][5] = bf16_hi(u.z); e[q][6] = bf16_lo(u.w); e[q][7] = bf16_hi(u.w);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        sum += e[j];
-        sumsq += e[j] * e[j];
+        for (int j = 0; j < 8; ++j) {
+          sum[q] += e[q][j];
+          sumsq[q] = fmaf(e[q][j], e[q][j], sumsq[q]);
+        }
       }
 #pragma unroll
       for (int h = 0; h < H; ++h) {
         const float4 w0 = *reinterpret_cast<const float4*>(&sw[h * 128 + c16 * 8]);
         const float4 w1 = *reinterpret_cast<const float4*>(&sw[h * 128 + c16 * 8 + 4]);
-        acc[h] += e[0] * w0.x + e[1] * w0.y + e[2] * w0.z + e[3] * w0.w + e[4] * w1.x + e[5] * w1.y +
-                  e[6] * w1.z + e[7] * w1.w;
+#pragma unroll
+        for (int q = 0; q < RPT; ++q) {
+          float a = acc[q][h];
+          a = fmaf(e[q][0], w0.x, a); a = fmaf(e[q][1], w0.y, a); a = fmaf(e[q][2], w0.z, a);
+          a = fmaf(e[q][3], w0.w, a); a = fmaf(e[q][4], w1.x, a); a = fmaf(e[q][5], w1.y, a);
+          a = fmaf(e[q][6], w1.z, a); a = fmaf(e[q][7], w1.w, a);
+          acc[q][h] = a;
+        }
       }
     }
-    const float mu = sum * (1.f / 128.f);
-    const float rstd = rsqrtf(fmaxf(sumsq * (1.f / 128.f) - mu * mu, 0.f) + 1e-5f);
-    const int i = static_cast<int>(r / N);
-    const int j = static_cast<int>(r - static_cast<long long>(i) * N);
-    const long long off = transpose_out ? (static_cast<long long>(j) * Np + i) : (static_cast<long long>(i) * Np + j);
+    float mu[RPT], rstd[RPT];
 #pragma unroll
-    for (int h = 0; h < H; ++h) {
-      const float val = rstd * (acc[h] - mu * colsum[h]) + colbias[h];
-      out[static_cast<long long>(h) * N * Np + off] = __float2bfloat16(val);
+    for (int q = 0; q < RPT; ++q) {
+      mu[q] = sum[q] * (1.f / 128.f);
+      rstd[q] = rsqrtf(fmaxf(sumsq[q] * (1.f / 128.f) - mu[q] * mu[q], 0.f) + 1e-5f);
+    }
+    const int i0 = static_cast<int>(r0 / N);
+    const int j0 = static_cast<int>(r0 - static_cast<long long>(i0) * N);
+    const bool vec = RPT == 4 && !transpose_out && j0 + RPT <= N && ((Np | j0) & 3) == 0;
+    if (vec) {
+      const long long off = static_cast<long long>(i0) * Np + j0;
+#pragma unroll
+      for (int h = 0; h < H; ++h) {
+        const float cs = colsum[h], cb = colbias[h];
+        float v[RPT];
+#pragma unroll
+        for (int q = 0; q < RPT; ++q) v[q] = fmaf(rstd[q], acc[q][h] - mu[q] * cs, cb);
+        *reinterpret_cast<uint2*>(out + static_cast<long long>(h) * N * Np + off) =
+            make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[RPT - 2], v[RPT - 1]));
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < RPT; ++q) {
+        const long long r = r0 + q;
+        if (r < R) {
+          const int i = static_cast<int>(r / N);
+          const int j = static_cast<int>(r - static_cast<long long>(i) * N);
+          const long long off =
+              transpose_out ? (static_cast<long long>(j) * Np + i) : (static_cast<long long>(i) * Np + j);
+#pragma unroll
+          for (int h = 0; h < H; ++h)
+            out[static_cast<long long>(h) * N * Np + off] =
+                __float2bfloat16(fmaf(rstd[q], acc[q][h] - mu[q] * colsum[h], colbias[h]));
+        }
+      }
     }
   }
 }
@@ -477,17 +518,17 @@ extern "C" int ubm_pair_head_bias(const void* z, const void* w, const void* cols
   using namespace ubm;
   if (N <= 0 || Np < N) return UBM_ERR_ARGUMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int grid = grid_for(static_cast<long long>(N) * N, 128);
+  const int grid = grid_for((static_cast<long long>(N) * N + 1) / 2, 128);     // 2 or 4 rows per thread
   const __nv_bfloat16* zz = static_cast<const __nv_bfloat16*>(z);
   const float* ww = static_cast<const float*>(w);
   const float* cs = static_cast<const float*>(colsum);
   const float* cb = static_cast<const float*>(colbias);
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
   switch (H) {
-    case 4: pair_head_bias_kernel<4><<<grid, 128, 0, st>>>(zz, ww, cs, cb, o, N, Np, transpose_out); break;
-    case 8: pair_head_bias_kernel<8><<<grid, 128, 0, st>>>(zz, ww, cs, cb, o, N, Np, transpose_out); break;
-    case 16: pair_head_bias_kernel<16><<<grid, 128, 0, st>>>(zz, ww, cs, cb, o, N, Np, transpose_out); break;
-    case 32: pair_head_bias_kernel<32><<<grid, 128, 0, st>>>(zz, ww, cs, cb, o, N, Np, transpose_out); break;
+    case 4: pair_head_bias_kernel<4, 4><<<grid, 128, 0, st>>>(zz, ww, cs, cb, o, N, Np, transpose_out); break;
+    case 8: pair_head_bias_kernel<8, 4><<<grid, 128, 0, st>>>(zz, ww, cs, cb, o, N, Np, transpose_out); break;
+    case 16: pair_head_bias_kernel<16, 4><<<grid, 128, 0, st>>>(zz, ww, cs, cb, o, N, Np, transpose_out); break;
+    case 32: pair_head_bias_kernel<32, 2><<<grid, 128, 0, st>>>(zz, ww, cs, cb, o, N, Np, transpose_out); break;
     default: return UBM_ERR_ARGUMENT;
   }
   UBM_CHECK_LAUNCH("pair_head_bias_kernel");
