@@ -90,6 +90,11 @@ __device__ __forceinline__ void decode_ntile(const GemmParams& p, int nb, int& q
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
+// warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..9 = two epilogue groups of four warps: each group covers the
+// four TMEM lane quadrants and takes half of the tile's 32-column chunks.  With one group the epilogue of a
+// 128 x 256 tile (about 10 us) outlasted its main loop whenever K was below about 1400.
+constexpr int kGemmThreads = 320;
+constexpr int kEpiGroups = 2;
 
 template <int BN>
 struct GemmCfg {
@@ -142,7 +147,7 @@ __device__ __forceinline__ void decode_ntile_rot(const GemmParams& p, int nb_rot
 }
 
 template <int BN, bool MN_MAJOR, bool PEER>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ PeerMaps peers, const __grid_constant__ PeerMaps gathered, GemmParams p) {
   using Cfg = GemmCfg<BN>;
@@ -171,9 +176,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);
+      mbar_init(&tempty_bar[a], 4 * kEpiGroups);
       mbar_init(&rfull_bar[a], 1);
-      mbar_init(&rempty_bar[a], 4);
+      mbar_init(&rempty_bar[a], 4 * kEpiGroups);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -371,8 +376,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    const int grp = (warp - 2) >> 2;                       // which half of the tile's column chunks
+    constexpr int kChunksPerGroup = (BN / 32) / kEpiGroups;
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool vec_ok = p.out_fp32 ? ((p.ldc & 3) == 0 && (p.strideC & 3) == 0 &&
@@ -538,15 +545,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       };
       uint32_t va[32], vb[32];
-      if (nchunks > 0) tmem_ld32(tmem_addr(tmem_base, q, acc * BN), va);
+      const int c_begin = grp * kChunksPerGroup;
+      const int c_end = min(nchunks, c_begin + kChunksPerGroup);
+      if (c_begin < c_end) tmem_ld32(tmem_addr(tmem_base, q, acc * BN + c_begin * 32), va);
 #pragma unroll 1
-      for (int c = 0; c < nchunks; c += 2) {
+      for (int c = c_begin; c < c_end; c += 2) {
         tmem_ld_wait();
-        if (c + 1 < nchunks) tmem_ld32(tmem_addr(tmem_base, q, acc * BN + (c + 1) * 32), vb);
+        if (c + 1 < c_end) tmem_ld32(tmem_addr(tmem_base, q, acc * BN + (c + 1) * 32), vb);
         process(va, c);
-        if (c + 1 < nchunks) {
+        if (c + 1 < c_end) {
           tmem_ld_wait();
-          if (c + 2 < nchunks) tmem_ld32(tmem_addr(tmem_base, q, acc * BN + (c + 2) * 32), va);
+          if (c + 2 < c_end) tmem_ld32(tmem_addr(tmem_base, q, acc * BN + (c + 2) * 32), va);
           process(vb, c + 1);
         }
       }
@@ -625,7 +634,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
     if (rc) return rc;
     p.res_tma = 1;
   }
-  kern<<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, none, aux, p);
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, none, aux, p);
   UBM_CHECK_LAUNCH("gemm_bf16_kernel");
   return UBM_OK;
 }
@@ -839,7 +848,7 @@ extern "C" int ubm_gemm_bf16_allgather_b(const void* A, const void* const* B_ptr
     const int compute = sm_count() - p.copy_ctas;
     grid = (p.num_tiles < compute ? p.num_tiles : compute) + p.copy_ctas;
   }
-  kern<<<grid, 192, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmA, tmA, maps, gmaps, p);
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmA, tmA, maps, gmaps, p);
   UBM_CHECK_LAUNCH("gemm_bf16_kernel<peer>");
   return UBM_OK;
 }
