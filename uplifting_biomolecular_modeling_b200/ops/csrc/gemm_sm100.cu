@@ -192,6 +192,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch: the set-up above (barriers, tensor memory, descriptor prefetch) touched nothing
+  // that an earlier kernel writes, so it may run while the previous kernel of the stream drains; from here on the
+  // kernel reads its operands.  Both instructions are no-ops for a launch without the attribute.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const int num_kb = (p.K + kBK - 1) / kBK;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
@@ -634,7 +639,26 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
     if (rc) return rc;
     p.res_tma = 1;
   }
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, none, aux, p);
+  // launched so that its set-up may overlap the tail of the previous kernel in the stream (see the kernel)
+  static const bool pdl = [] {
+    const char* e = getenv("UBM_PDL");
+    return e == nullptr || e[0] != '0';
+  }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, none, aux, p);
+  if (le != cudaSuccess) {
+    fprintf(stderr, "[ubm] gemm_bf16_kernel: launch failed: %s\n", cudaGetErrorString(le));
+    return UBM_ERR_LAUNCH;
+  }
   UBM_CHECK_LAUNCH("gemm_bf16_kernel");
   return UBM_OK;
 }
