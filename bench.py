@@ -139,12 +139,17 @@ def main():
     value_e2e = world * 3600.0 * 1000.0 / ms_e2e
     finite = bool(torch.isfinite(out["coords"]).all())
     if rank == 0:
-        line = {"metric": "predictions/hour at N=1536 (AF3-shaped cofold, fast mode)", "value": round(value, 3),
+        c = pred.cfg
+        shape = "AF3-shaped" if args.config == "af3" else f"{args.config}-shaped"
+        model = (f"{shape} cofold ({c.pairformer_blocks} Pairformer blocks, {c.msa_blocks} MSA blocks, "
+                 f"{c.token_depth}-block DiT, {c.samples}x{args.sampling_steps or c.sampling_steps} sampling)")
+        line = {"metric": f"predictions/hour at N={args.tokens} ({shape} cofold, {args.mode} mode)",
+                "value": round(value, 3),
                 "unit": "predictions/hour", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": round(ms, 3), "sec_per_prediction": round(ms / 1000.0, 4),
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
                 "data": "synthetic features, random-init weights", "impl": "ours",
-                "config": dict(CONFIG, tokens=args.tokens, msa_depth=args.msa_depth, mode=args.mode,
+                "config": dict(CONFIG, model=model, tokens=args.tokens, msa_depth=args.msa_depth, mode=args.mode,
                                global_batch=world, seq_len=args.tokens, parallelism=f"dp{world}",
                                sampling_steps=args.sampling_steps or pred.cfg.sampling_steps,
                                samples=pred.cfg.samples, trunk_passes=(pred.cfg.recycles if args.recycles is None
