@@ -3,6 +3,7 @@ the all-gather -> triangle contraction GEMM and the attention kernel with its pa
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Sequence
 
 import torch
@@ -87,6 +88,12 @@ class ReduceScatterState:
         self.heap, self.rows, self.n = heap, rows_per_rank, n
         self.bufs = [heap.alloc((heap.world, rows_per_rank, n), torch.bfloat16) for _ in range(2)]
         self.calls = 0
+        if os.environ.get("UBM_P2P_CHECK", "0") == "1":
+            # every rank's puts of one call against the slot buffer sizes, before any kernel stores to a peer
+            from ..parallel import plan_check
+            P, row_bytes = heap.world, n * 2
+            plan = plan_check.reduce_scatter_plan(P, [rows_per_rank] * P, row_bytes)
+            plan_check.check_exchange_plan(plan, {(q, "slots"): P * rows_per_rank * row_bytes for q in range(P)})
 
 
 def gemm_reduce_scatter(x: torch.Tensor, w: torch.Tensor, state: ReduceScatterState, bias=None, residual=None,
