@@ -105,7 +105,8 @@ def _run_lm(spec, act, args, allow_partial, family) -> int:
     act.register_exit()
     model = lm.build(family, spec.config if args.model_config is None else args.model_config, device=device,
                      mode=act.mode, seed=args.seed, kit=spec.name)
-    prompt = args.prompt or "ACGT" * 16
+    protein = family == "protein_lm" and spec.name != "gpnstar"
+    prompt = args.prompt or ("MKTAYIAKQRQISFVKSHFSRQLEERLGLIEVQ" * 2 if protein else "ACGT" * 16)
     t0 = time.time()
     res = model.run(args.verb, prompt, max_new_tokens=args.max_new_tokens)
     report.emit(report.line(spec.tag, "DONE", ("seconds", round(time.time() - t0, 3)), ("verb", args.verb),
