@@ -29,6 +29,8 @@ def main():
     ap.add_argument("--impl", default="fused", choices=["fused", "torch"])
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--graph", type=int, default=1, help="1: decode step captured in a CUDA graph and replayed")
+    ap.add_argument("--specdec", type=int, default=0, help="k > 0: also time speculative decoding with k proposals per round")
+    ap.add_argument("--draft", default="evo2_1b", help="configuration of the draft model for --specdec")
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -78,6 +80,35 @@ def main():
     t = torch.tensor([pre, dec], device=dev)
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    spec = None
+    if a.specdec > 0 and world == 1:
+        # Random-init weights make the acceptance rate meaningless (target and draft agree by chance); what the
+        # run measures is the cost of a round: k draft steps + one target pass over k + 1 tokens, against the
+        # target's single-token step (both eager).
+        draft = evo2.build(a.draft, device=dev, dtype=torch.bfloat16, seed=1)
+        if a.impl == "fused":
+            draft.set_impl("fused")
+        short = tokens[:, :min(a.prefill, 4096)]
+        model.generate_speculative(draft, short, 2 * (a.specdec + 1), k=a.specdec)          # warm-up
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        states = [dict() for _ in model.blocks]
+        nxt = model(short, states)[:, -1:].argmax(-1)
+        ev[0].record()
+        for _ in range(16):
+            nxt = model.step(nxt, states)[:, -1:].argmax(-1)
+        ev[1].record()
+        seq = torch.randint(0, model.cfg.vocab, (1, a.specdec + 1), device=dev, generator=g)
+        for _ in range(16):
+            model.extend(seq, states)
+            model.commit(states, 1)
+        ev[2].record()
+        _, stats = model.generate_speculative(draft, short, 16 * (a.specdec + 1), k=a.specdec)
+        ev[3].record()
+        torch.cuda.synchronize(dev)
+        spec = {"k": a.specdec, "draft": a.draft, "target_step_ms_eager": round(ev[0].elapsed_time(ev[1]) / 16, 3),
+                "target_pass_over_k_plus_1_ms": round(ev[1].elapsed_time(ev[2]) / 16, 3),
+                "rounds": stats["rounds"], "accepted": stats["accepted"], "proposed": stats["proposed"],
+                "ms_per_round_incl_prefill": round(ev[2].elapsed_time(ev[3]) / max(stats["rounds"], 1), 3)}
     if rank == 0:
         pre, dec = t.tolist()
         print(json.dumps({
@@ -86,7 +117,7 @@ def main():
             "prefill_tokens_per_s": round(a.prefill / pre * 1e3, 1), "decode_ms_per_token": round(dec / max(a.new - 1, 1), 3),
             "decode_tokens_per_s": round((a.new - 1) / dec * 1e3, 1), "last_token": last,
             "fused_reduce_scatter_calls": 0 if par is None else par.fused_calls,
-            "peak_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2)}), flush=True)
+            "peak_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2), "specdec": spec}), flush=True)
     if world > 1:
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()

@@ -49,3 +49,37 @@ def test_static_state_decode_equals_plain_decode():
         pos.add_(1)
         outs.append(nxt)
     assert torch.equal(torch.cat(outs, 1), ref)
+
+
+def test_multi_token_continuation_equals_single_steps():
+    """extend(k tokens) + commit(j) leaves the states where j single-token steps would, and gives their logits."""
+    from uplifting_biomolecular_modeling_b200.models import evo2
+    m = evo2.build("evo2_tiny", seed=3)
+    toks = torch.randint(0, 4, (1, 37), generator=torch.Generator().manual_seed(0))
+    nxt = torch.randint(0, 4, (1, 5), generator=torch.Generator().manual_seed(1))
+    a = [dict() for _ in m.blocks]
+    b = [dict() for _ in m.blocks]
+    m.forward(toks, a)
+    m.forward(toks, b)
+    step_logits = torch.cat([m.step(nxt[:, i:i + 1], a) for i in range(3)], 1)
+    ext = m.extend(nxt, b)
+    torch.testing.assert_close(ext[:, :3], step_logits, atol=2e-4, rtol=2e-4)
+    m.commit(b, 3)
+    # both state sets now continue identically
+    torch.testing.assert_close(m.step(nxt[:, 3:4], a), m.step(nxt[:, 3:4], b), atol=2e-4, rtol=2e-4)
+
+
+def test_speculative_decoding_reproduces_greedy_decoding():
+    from uplifting_biomolecular_modeling_b200.models import evo2
+    target = evo2.build("evo2_tiny", seed=3)
+    toks = torch.randint(0, 4, (1, 29), generator=torch.Generator().manual_seed(2))
+    want = target.generate(toks, 20)
+    # a draft with other weights: proposals are mostly rejected, the output must not change
+    other = evo2.build("evo2_tiny", seed=11)
+    got, stats = target.generate_speculative(other, toks, 20, k=4)
+    assert torch.equal(got, want), (got, want)
+    assert stats["proposed"] == 4 * stats["rounds"]
+    # the target as its own draft: every proposal is accepted, k + 1 tokens per round
+    got2, stats2 = target.generate_speculative(target, toks, 20, k=4)
+    assert torch.equal(got2, want)
+    assert stats2["accepted"] == stats2["proposed"] and stats2["rounds"] == 4

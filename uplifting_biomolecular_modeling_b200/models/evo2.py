@@ -224,6 +224,46 @@ class HyenaOperator(nn.Module):
             y = (s * self.residues.float().unsqueeze(0)).sum(-1).unsqueeze(1).to(u.dtype) + u * self.D.to(u.dtype)
         return lin(self.out_proj, x2 * y)
 
+    # ---- multi-token continuation (speculative decoding): k tokens after an existing state, then keep j of them
+    def extend(self, x: torch.Tensor, state: dict, linear=None) -> torch.Tensor:
+        """x: [B, k, d] continuing ``state`` (not a static one).  The state itself is left as it was; what a later
+        :meth:`commit` needs (projected inputs, gated inputs, the pole state after every token) is parked under
+        ``state["pending"]``."""
+        lin = linear or (lambda m, t: m(t))
+        z = lin(self.in_proj, x)
+        zf = causal_fir(z, self.fir, state["fir_tail"])
+        x1, x2, v = zf.chunk(3, dim=-1)
+        u = x1 * v
+        pend = {"z": z, "u": u}
+        if self.kind in ("hcs", "hcm"):
+            y = causal_fir(u, self.h, state["inner_tail"]) + u * self.D.to(u.dtype)
+        else:
+            lam = torch.exp(self.log_poles.float()).unsqueeze(0)
+            res = self.residues.float().unsqueeze(0)
+            s = state["poles"].float()
+            ys, ss = [], []
+            for t in range(u.shape[1]):
+                s = s * lam + u[:, t].float().unsqueeze(-1)
+                ss.append(s)
+                ys.append((s * res).sum(-1))
+            pend["poles"] = ss
+            y = torch.stack(ys, 1).to(u.dtype) + u * self.D.to(u.dtype)
+        state["pending"] = pend
+        return lin(self.out_proj, x2 * y)
+
+    def commit(self, state: dict, j: int) -> None:
+        """Make the first ``j`` tokens of the last :meth:`extend` part of the state; drop the rest."""
+        pend = state.pop("pending")
+        if j <= 0:
+            return
+        K = self.cfg.fir_len
+        state["fir_tail"] = _last(torch.cat([state["fir_tail"], pend["z"][:, :j].to(state["fir_tail"].dtype)], 1), K - 1)
+        if self.kind in ("hcs", "hcm"):
+            state["inner_tail"] = _last(torch.cat([state["inner_tail"], pend["u"][:, :j].to(state["inner_tail"].dtype)], 1),
+                                        self.h.shape[1] - 1)
+        else:
+            state["poles"] = pend["poles"][j - 1]
+
 
 def _push(state: dict, key: str, new: torch.Tensor) -> None:
     """Shift a [B, K-1, C] tail by one position and append ``new`` ([B, 1, C]).  A static state (one that a
@@ -305,6 +345,26 @@ class AttentionOperator(nn.Module):
         o = F.scaled_dot_product_attention(q.transpose(1, 2), state["k"].transpose(1, 2), state["v"].transpose(1, 2))
         return lin(self.out_proj, o.transpose(1, 2).reshape(B, 1, -1))
 
+    def extend(self, x, state: dict, linear=None):
+        """k tokens after the cached ones (dynamic cache): the new keys are appended, each new query sees the cache
+        and the new keys up to itself.  :meth:`commit` keeps the first j of them."""
+        lin = linear or (lambda m, t: m(t))
+        B, k, d = x.shape
+        L0 = state["k"].shape[1]
+        pos = torch.arange(L0, L0 + k, device=x.device)
+        q, kk, vv = self._qkv(x, pos, lin)
+        state["pending"] = {"len0": L0}
+        state["k"] = torch.cat([state["k"], kk], 1)
+        state["v"] = torch.cat([state["v"], vv], 1)
+        mask = torch.arange(L0 + k, device=x.device)[None, :] <= pos[:, None]
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), state["k"].transpose(1, 2), state["v"].transpose(1, 2),
+                                           attn_mask=mask)
+        return lin(self.out_proj, o.transpose(1, 2).reshape(B, k, -1))
+
+    def commit(self, state: dict, j: int) -> None:
+        keep = state.pop("pending")["len0"] + max(j, 0)
+        state["k"], state["v"] = state["k"][:, :keep], state["v"][:, :keep]
+
 
 class SwiGLU(nn.Module):
     def __init__(self, d: int, ffn: int):
@@ -338,6 +398,10 @@ class Block(nn.Module):
 
     def step(self, x, state, linear=None):
         x = x + self.mixer.step(self.pre_norm(x), state, linear)
+        return x + self.mlp(self.post_norm(x), linear)
+
+    def extend(self, x, state, linear=None):
+        x = x + self.mixer.extend(self.pre_norm(x), state, linear)
         return x + self.mlp(self.post_norm(x), linear)
 
 
@@ -379,6 +443,19 @@ class StripedHyena2(nn.Module):
         for i, blk in enumerate(self.blocks):
             x = blk.step(x, states[i], self.linear)
         return self.logits(x)
+
+    @torch.no_grad()
+    def extend(self, tokens: torch.Tensor, states: List[dict]) -> torch.Tensor:
+        """tokens: [B, k] continuing ``states`` -> logits [B, k, vocab]; one pass over the weights for k tokens.
+        The states change only at :meth:`commit`."""
+        x = self.embedding(tokens)
+        for i, blk in enumerate(self.blocks):
+            x = blk.extend(x, states[i], self.linear)
+        return self.logits(x)
+
+    def commit(self, states: List[dict], j: int) -> None:
+        for blk, st in zip(self.blocks, states):
+            blk.mixer.commit(st, j)
 
     def make_static_states(self, states: List[dict], max_len: int) -> torch.Tensor:
         """Turn the states a prefill produced into fixed-address buffers (attention caches of ``max_len``
@@ -422,6 +499,57 @@ class StripedHyena2(nn.Module):
             nxt = logits[:, -1:].argmax(-1)
             out.append(nxt)
         return torch.cat(out, 1)
+
+    @torch.no_grad()
+    def generate_speculative(self, draft: "StripedHyena2", tokens: torch.Tensor, max_new_tokens: int, k: int = 6):
+        """Greedy decoding of this model with ``draft`` proposing ``k`` tokens per round (batch 1).  Each round
+        costs k single-token passes of the draft and ONE pass of this model over k + 1 tokens; the proposals are
+        kept up to the first one this model would not have chosen, and this model's own choice follows them, so
+        the output is the plain greedy sequence.  Returns (new tokens [1, max_new_tokens], statistics)."""
+        if tokens.shape[0] != 1:
+            raise ValueError("speculative decoding runs one sequence at a time")
+        t_states = [dict() for _ in self.blocks]
+        d_states = [dict() for _ in draft.blocks]
+        cur = self.forward(tokens, t_states)[:, -1:].argmax(-1)
+        draft.forward(tokens, d_states)
+        out = [cur]
+        n_out = 1
+        stats = {"rounds": 0, "proposed": 0, "accepted": 0}
+        while n_out < max_new_tokens:
+            # the draft consumes cur, p1 .. p(k-1) and proposes p1 .. pk.  Continuation never writes a state tensor
+            # in place (tails, pole states and caches are replaced by new tensors), so a shallow copy of the
+            # dicts is a snapshot.
+            snap = [dict(st) for st in d_states]
+            consumed, props, tok = [], [], cur
+            for _ in range(k):
+                lg = draft.extend(tok, d_states)
+                draft.commit(d_states, 1)
+                consumed.append(tok)
+                tok = lg[:, -1:].argmax(-1)
+                props.append(tok)
+            seq = torch.cat([cur] + props, 1)                               # [1, k + 1]
+            choice = self.extend(seq, t_states).argmax(-1)                  # this model's token after each prefix
+            agree = (choice[:, :k] == seq[:, 1:]).long()[0]
+            j = int(agree.cumprod(0).sum())                                 # accepted proposals
+            self.commit(t_states, j + 1)                                    # cur, p1 .. pj are now consumed
+            new = [seq[:, i:i + 1] for i in range(1, j + 1)] + [choice[:, j:j + 1]]
+            out.extend(new)
+            n_out += len(new)
+            stats["rounds"] += 1
+            stats["proposed"] += k
+            stats["accepted"] += j
+            cur = new[-1]
+            # the draft must have consumed exactly cur_old, p1 .. pj: it has consumed k tokens
+            if j == k:
+                draft.extend(props[-1], d_states)
+                draft.commit(d_states, 1)
+            elif j < k - 1:
+                for st, old in zip(d_states, snap):
+                    st.clear()
+                    st.update(old)
+                draft.extend(torch.cat(consumed[:j + 1], 1), d_states)
+                draft.commit(d_states, j + 1)
+        return torch.cat(out, 1)[:, :max_new_tokens], stats
 
     def _generate_graph(self, tokens, states, first, max_new_tokens):
         dev = tokens.device
