@@ -224,7 +224,10 @@ class ParallelDecoderBlock(nn.Module):
         qh = q.view(B, L, H, D).transpose(1, 2)
         kh, vh = K[:, :end].transpose(1, 2), V[:, :end].transpose(1, 2)
         if L == 1:
-            o = F.scaled_dot_product_attention(qh, kh, vh)
+            # written out: the library's fused attention re-plans whenever the key length changes, which with a
+            # growing prefix is every decode step (milliseconds of host time per call)
+            sc = torch.matmul(qh.float(), kh.float().transpose(-1, -2)) * (D ** -0.5)
+            o = torch.matmul(torch.softmax(sc, -1).to(vh.dtype), vh)
         else:
             i = torch.arange(L, device=q.device)[:, None] + start
             j = torch.arange(end, device=q.device)[None, :]
