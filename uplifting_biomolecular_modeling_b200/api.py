@@ -71,6 +71,39 @@ class Predictor:
         self._pinned: Dict[str, torch.Tensor] = {}
         self.last_timing: Dict[str, float] = {}
 
+    # ------------------------------------------------------------------ provider decisions
+    def provider_plan(self, n_tokens: int, n_atoms: Optional[int] = None) -> Dict[str, object]:
+        """The row of every op family that serves this model's call classes at ``n_tokens`` under the current mode,
+        looked up in the measured table and recorded in the cell census (once per call class).  ``off`` has no
+        providers."""
+        if self.mode == "off":
+            return {}
+        from .core import arch
+        from .ops import provider
+        sm = (arch.device_sm(self.device.index or 0) if self.device.type == "cuda" else None) or "cpu"
+        c = self.cfg
+        dt = "bf16" if self.dtype == torch.bfloat16 else str(self.dtype).replace("torch.", "")
+        tri_heads, d_tri = 4, 32                                   # triangle attention: 4 heads of 32 channels
+        d_tok = 64                                                  # token attention: 768 / 16 = 48, padded to 64
+        calls = [
+            ("triattn", f"D{d_tri}H{tri_heads}", n_tokens, {"head_dim": d_tri, "dtype": dt}),
+            ("trimul", f"C{c.c_z}H{c.c_z}", n_tokens, {"c_z": c.c_z, "c_hidden": c.c_z, "dtype": dt}),
+            ("transition", f"C{c.c_z}X4", n_tokens, {"c": c.c_z, "expansion": 4, "dtype": dt}),
+            ("transition", f"C{c.c_s}X4", n_tokens, {"c": c.c_s, "expansion": 4, "dtype": dt}),
+            ("transition", f"C{c.c_m}X4", n_tokens, {"c": c.c_m, "expansion": 4, "dtype": dt}),
+            ("apb", f"D{d_tok}H{c.token_heads}S{c.samples}", n_tokens, {"head_dim": d_tok, "dtype": dt}),
+            ("ln", f"C{c.c_z}", n_tokens, {"c": c.c_z, "dtype": dt}),
+            ("ln", f"C{c.c_m}", n_tokens, {"c": c.c_m, "dtype": dt}),
+        ]
+        if n_atoms:
+            calls.append(("apb", "WIN32x128", n_atoms, {"head_dim": c.c_atom // c.atom_heads, "window": (32, 128),
+                                                        "dtype": dt}))
+        plan = {}
+        for fam, klass, n, call in calls:
+            plan[f"{fam}|{klass}"] = provider.select(fam, sm, klass, n, self.mode, call)
+        self.last_plan = plan
+        return plan
+
     # ------------------------------------------------------------------ host <-> device
     def to_device(self, feats: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
         out = {}
@@ -171,6 +204,9 @@ class Predictor:
         mark("trunk")
         N = s.shape[1]
         nsamp = samples or self.cfg.samples
+        if getattr(self, "_plan_key", None) != N:
+            self._plan_key = N
+            self.provider_plan(N, feats["ref_pos"].shape[1] if "ref_pos" in feats else None)
         sm = m.structure_module
         prep = sm.score_model.prepare(s, s_inputs, m.z_cond_norm(z), atom_c, atom_c, atom_p, m.fused)
         step_fn = self._step_fn(prep, feats, N, nsamp)
