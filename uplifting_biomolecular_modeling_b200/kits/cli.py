@@ -41,6 +41,8 @@ def _parser(kit: str) -> argparse.ArgumentParser:
     ap.add_argument("--model_config", default=None, help="override the kit's model configuration key")
     ap.add_argument("--prompt", default=None)
     ap.add_argument("--max_new_tokens", type=int, default=32)
+    ap.add_argument("--upstream-fix", dest="upstream_fix", default=None,
+                    help="comma-separated corrections to the stock model that change outputs on purpose")
     return ap
 
 
@@ -72,6 +74,13 @@ def main(argv: Optional[List[str]] = None) -> int:
     if undeclared:
         report.emit(report.not_active_line(spec.tag, f"undeclared variable(s) {','.join(undeclared)}"))
         return report.EXIT_NOT_ACTIVE
+    if args.upstream_fix:
+        from ..core import upstream_fix
+        try:
+            upstream_fix.resolve(upstream_fix.parse(args.upstream_fix), kit)
+        except upstream_fix.UnknownFix as e:
+            print(f"{kit}: {e}", file=sys.stderr)
+            return report.EXIT_USAGE
     if args.verb == "install":
         return _install(spec, args)
     try:

@@ -65,6 +65,10 @@ def _run_cofold(spec, act, args, allow_partial) -> int:
         if args.checkpoint:
             from ..models import weights
             weights.load_checkpoint(pred.model, args.checkpoint)
+        if getattr(args, "upstream_fix", None):
+            from ..core import upstream_fix
+            act.words = list(getattr(act, "words", [])) + upstream_fix.apply_all(
+                pred.model, upstream_fix.parse(args.upstream_fix), spec.tag, spec.name)
         act.apply(pred)
     except base.ActivationError:
         return report.EXIT_NOT_ACTIVE
