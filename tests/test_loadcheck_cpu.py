@@ -1,0 +1,20 @@
+"""Verdict logic of the kernel self-verification (the probes themselves need a GPU)."""
+import pytest
+
+from uplifting_biomolecular_modeling_b200.ops import loadcheck
+
+
+def test_verdict_line_and_refusal(capsys):
+    good = loadcheck.run_all("cpu", probes={"a": lambda d: (1e-3, 2e-2), "b": lambda d: (0.0, 1e-2)})
+    assert good.ok and "KERNELS-VERIFIED families=2 failed=none" in good.line("boltz2-opt")
+
+    def boom(dev):
+        raise RuntimeError("launch failed")
+    bad = loadcheck.run_all("cpu", probes={"a": lambda d: (1e-3, 2e-2), "b": lambda d: (0.5, 2e-2),
+                                           "c": lambda d: (float("nan"), 1.0), "d": boom})
+    assert not bad.ok and [p.family for p in bad.failed] == ["b", "c", "d"]
+    assert "KERNELS-REFUSED" in bad.line() and "failed=b,c,d" in bad.line()
+    assert "RuntimeError" in bad.failed[2].detail
+    with pytest.raises(loadcheck.KernelsRefused, match="b\\("):
+        raise loadcheck.KernelsRefused(bad.failed)
+
