@@ -18,3 +18,4 @@ def test_verdict_line_and_refusal(capsys):
     with pytest.raises(loadcheck.KernelsRefused, match="b\\("):
         raise loadcheck.KernelsRefused(bad.failed)
 
+

@@ -15,6 +15,7 @@ Mode vocabulary and the no-silent-fallback rule are those of the reference kits 
 """
 from __future__ import annotations
 
+import os
 import time
 from typing import Dict, Optional
 
@@ -63,6 +64,13 @@ class Predictor:
                 native.lib()
             except native.NativeUnavailable as e:
                 raise NotActive(f"mode {mode}: {e}") from e
+            if os.environ.get("UBM_LOADCHECK", "0") == "1":
+                # every kernel family reproduces its fp32 statement on this GPU before it serves (once per process)
+                from .ops import loadcheck
+                try:
+                    loadcheck.require(self.device, tag="ubm")
+                except loadcheck.KernelsRefused as e:
+                    raise NotActive(f"mode {mode}: {e}") from e
             n = self.model.set_impl("fused")
             self.levers.append(f"fused_kernels:{n}")
         self.use_graphs = (mode != "off" and self.device.type == "cuda") if use_graphs is None else use_graphs

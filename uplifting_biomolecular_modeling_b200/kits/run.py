@@ -70,6 +70,12 @@ def _run_cofold(spec, act, args, allow_partial) -> int:
             act.words = list(getattr(act, "words", [])) + upstream_fix.apply_all(
                 pred.model, upstream_fix.parse(args.upstream_fix), spec.tag, spec.name)
         act.apply(pred)
+        if act.mode in ("fast", "big") and device != "cpu" and os.environ.get("UBM_LOADCHECK", "0") == "1":
+            from ..ops import loadcheck
+            try:
+                loadcheck.require(device, tag=spec.tag)
+            except loadcheck.KernelsRefused:
+                return report.EXIT_KERNELS_REFUSED
     except base.ActivationError:
         return report.EXIT_NOT_ACTIVE
     except api.NotActive as e:
