@@ -9,8 +9,6 @@ from __future__ import annotations
 import hashlib
 from typing import Mapping, Optional
 
-import torch
-
 
 class DigestMismatch(RuntimeError):
     pass
@@ -27,7 +25,8 @@ def file_digest(path: str, chunk: int = 1 << 22) -> str:
     return h.hexdigest()
 
 
-def weight_digest(state: Mapping[str, torch.Tensor]) -> str:
+def weight_digest(state: Mapping[str, "torch.Tensor"]) -> str:
+    import torch  # noqa: PLC0415 - the contract runtime stays importable without the tensor library
     h = hashlib.sha256()
     for name in sorted(state):
         t = state[name].detach().cpu().contiguous()
