@@ -19,3 +19,11 @@ def test_verdict_line_and_refusal(capsys):
         raise loadcheck.KernelsRefused(bad.failed)
 
 
+
+
+@pytest.mark.gpu
+def test_every_family_verifies_on_the_gpu():
+    lc = loadcheck.run_all("cuda:0", use_cache=False)
+    assert lc.ok, lc.line()
+    # the probes sit well inside their tolerances (a false refusal would take a working GPU out of service)
+    assert all(p.error <= 0.5 * p.tolerance for p in lc.probes), [(p.family, p.error) for p in lc.probes]

@@ -64,7 +64,7 @@ class Predictor:
                 native.lib()
             except native.NativeUnavailable as e:
                 raise NotActive(f"mode {mode}: {e}") from e
-            if os.environ.get("UBM_LOADCHECK", "0") == "1":
+            if os.environ.get("UBM_LOADCHECK", "1") != "0":
                 # every kernel family reproduces its fp32 statement on this GPU before it serves (once per process)
                 from .ops import loadcheck
                 try:

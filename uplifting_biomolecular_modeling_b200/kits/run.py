@@ -70,7 +70,7 @@ def _run_cofold(spec, act, args, allow_partial) -> int:
             act.words = list(getattr(act, "words", [])) + upstream_fix.apply_all(
                 pred.model, upstream_fix.parse(args.upstream_fix), spec.tag, spec.name)
         act.apply(pred)
-        if act.mode in ("fast", "big") and device != "cpu" and os.environ.get("UBM_LOADCHECK", "0") == "1":
+        if act.mode in ("fast", "big") and device != "cpu" and os.environ.get("UBM_LOADCHECK", "1") != "0":
             from ..ops import loadcheck
             try:
                 loadcheck.require(device, tag=spec.tag)
