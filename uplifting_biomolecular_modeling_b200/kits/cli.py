@@ -41,6 +41,8 @@ def _parser(kit: str) -> argparse.ArgumentParser:
     ap.add_argument("--model_config", default=None, help="override the kit's model configuration key")
     ap.add_argument("--prompt", default=None)
     ap.add_argument("--max_new_tokens", type=int, default=32)
+    ap.add_argument("--specdec", type=int, default=0,
+                    help="evo2 generate: k > 0 decodes speculatively with k proposals per round from a draft model")
     ap.add_argument("--upstream-fix", dest="upstream_fix", default=None,
                     help="comma-separated corrections to the stock model that change outputs on purpose")
     return ap

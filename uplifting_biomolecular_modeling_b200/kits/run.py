@@ -114,7 +114,7 @@ def _run_lm(spec, act, args, allow_partial, family) -> int:
         return report.EXIT_NOT_ACTIVE
     act.register_exit()
     model = lm.build(family, spec.config if args.model_config is None else args.model_config, device=device,
-                     mode=act.mode, seed=args.seed, kit=spec.name)
+                     mode=act.mode, seed=args.seed, kit=spec.name, specdec=getattr(args, "specdec", 0))
     protein = family == "protein_lm" and spec.name != "gpnstar"
     prompt = args.prompt or ("MKTAYIAKQRQISFVKSHFSRQLEERLGLIEVQ" * 2 if protein else "ACGT" * 16)
     t0 = time.time()

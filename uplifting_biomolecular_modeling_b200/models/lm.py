@@ -13,13 +13,21 @@ from . import evo2, genomics, plm
 class _Runner:
     def __init__(self, model, device, mode):
         self.model, self.device, self.mode = model, device, mode
+        self.draft = None                 # a smaller model of the family: generate() then decodes speculatively
+        self.specdec_k = 0
 
     def run(self, verb: str, prompt: str, max_new_tokens: int = 32) -> dict:
         toks = evo2.tokenize(prompt, self.device)
         if verb == "generate":
-            out = self.model.generate(toks, max_new_tokens)
+            extra = {}
+            if self.draft is not None and self.specdec_k > 0:
+                out, stats = self.model.generate_speculative(self.draft, toks, max_new_tokens, k=self.specdec_k)
+                extra = {"specdec_rounds": stats["rounds"], "specdec_accepted": stats["accepted"],
+                         "specdec_proposed": stats["proposed"]}
+            else:
+                out = self.model.generate(toks, max_new_tokens)
             return {"new_tokens": int(out.shape[1]), "text": "".join(chr(int(t)) if 32 <= int(t) < 127 else "?"
-                                                                      for t in out[0].tolist())}
+                                                                      for t in out[0].tolist()), **extra}
         if verb in ("score", "predict"):
             return {"score": float(self.model.score(toks)[0]), "tokens": int(toks.shape[1])}
         raise ValueError(f"unknown verb {verb!r}")
@@ -63,7 +71,11 @@ class _TrackRunner(_Runner):
         return {"score": float(out.mean()), "bins": int(out.shape[1]), "tracks": int(out.shape[2]), "tokens": need}
 
 
-def build(family: str, config: str, device="cpu", mode: str = "exact", seed: int = 0, kit: str = "") -> _Runner:
+DRAFT_OF = {"evo2_7b": "evo2_1b", "evo2_1b": "evo2_tiny", "evo2_tiny": "evo2_tiny"}
+
+
+def build(family: str, config: str, device="cpu", mode: str = "exact", seed: int = 0, kit: str = "",
+          specdec: int = 0) -> _Runner:
     """``family`` is the kit's model family (evo2 | protein_lm | genomic_track), ``kit`` its name (which model of the
     family), ``config`` a configuration key of that model (unknown keys fall back to the model's small default)."""
     dtype = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
@@ -77,4 +89,10 @@ def build(family: str, config: str, device="cpu", mode: str = "exact", seed: int
         return _TrackRunner(genomics.build(name, device=device, dtype=dtype, seed=seed, impl=impl), device, mode)
     cfg = config if config in evo2.CONFIGS else "evo2_tiny"
     m = evo2.build(cfg, device=device, dtype=dtype, seed=seed)
-    return _Runner(m, device, mode)
+    r = _Runner(m, device, mode)
+    if specdec > 0:
+        # ``specdec`` k > 0: the family's next smaller configuration proposes k tokens per round (greedy output is
+        # unchanged; see StripedHyena2.generate_speculative)
+        r.draft = evo2.build(DRAFT_OF.get(cfg, "evo2_tiny"), device=device, dtype=dtype, seed=seed + 1)
+        r.specdec_k = specdec
+    return r
