@@ -83,3 +83,24 @@ def test_speculative_decoding_reproduces_greedy_decoding():
     got2, stats2 = target.generate_speculative(target, toks, 20, k=4)
     assert torch.equal(got2, want)
     assert stats2["accepted"] == stats2["proposed"] and stats2["rounds"] == 4
+
+
+def test_filter_spectra_are_cached_per_length_and_follow_the_weights():
+    from uplifting_biomolecular_modeling_b200.models import evo2
+    m = evo2.build("evo2_tiny", seed=5)
+    toks = torch.randint(0, 4, (1, 96), generator=torch.Generator().manual_seed(0))
+    a = m(toks)
+    ops = [b.mixer for b in m.blocks if getattr(b.mixer, "kind", None) in ("hcm", "hcl")]
+    assert ops and all(len(o.__dict__.get("_spectra", {})) == 1 for o in ops)
+    first = [next(iter(o._spectra.values()))[1] for o in ops]
+    b = m(toks)
+    assert torch.equal(a, b)
+    assert all(next(iter(o._spectra.values()))[1] is f for o, f in zip(ops, first))       # reused, not recomputed
+    m(toks[:, :80])
+    m(toks[:, :72])
+    assert all(len(o._spectra) == 2 for o in ops)                                          # bounded
+    hcl = next(o for o in ops if o.kind == "hcl")
+    with torch.no_grad():
+        hcl.residues.mul_(1.5)                                                             # bumps the version
+    c = m(toks)
+    assert not torch.equal(a, c)

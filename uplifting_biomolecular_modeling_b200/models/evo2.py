@@ -90,13 +90,20 @@ def causal_fir(x: torch.Tensor, h: torch.Tensor, tail: Optional[torch.Tensor] = 
     return F.conv1d(xp, w, groups=C).transpose(1, 2)
 
 
-def fft_causal_conv(x: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
-    """Depthwise causal convolution with a filter as long as the sequence.  x: [B, L, C]; h: [C, Lh]."""
+def fft_size(L: int, Lh: int) -> int:
+    return 1 << (L + Lh - 1).bit_length()
+
+
+def fft_causal_conv(x: torch.Tensor, h: Optional[torch.Tensor], spectrum: Optional[torch.Tensor] = None,
+                    n: Optional[int] = None) -> torch.Tensor:
+    """Depthwise causal convolution with a filter as long as the sequence.  x: [B, L, C]; h: [C, Lh], or its
+    spectrum ``rfft(h, n)`` ([C, n/2 + 1]) with the transform size ``n``."""
     B, L, C = x.shape
-    n = 1 << (L + h.shape[1] - 1).bit_length()
+    if spectrum is None:
+        n = fft_size(L, h.shape[1])
+        spectrum = torch.fft.rfft(h.float(), n=n)
     X = torch.fft.rfft(x.float().transpose(1, 2), n=n)
-    Hf = torch.fft.rfft(h.float(), n=n)
-    y = torch.fft.irfft(X * Hf.unsqueeze(0), n=n)[..., :L]
+    y = torch.fft.irfft(X * spectrum.unsqueeze(0), n=n)[..., :L]
     return y.transpose(1, 2).to(x.dtype)
 
 
@@ -122,6 +129,27 @@ class HyenaOperator(nn.Module):
         self._taps = None           # tap-major fp32 copies of the filters for the kernels
 
     # ---- filters
+    def filter_spectrum(self, L: int):
+        """(rfft of this operator's long / medium filter at the transform size for length L, that size).  The
+        weights are constants at inference, so the spectrum is computed once per sequence length and kept (two
+        lengths per operator; each entry is d x (n/2 + 1) complex64); a changed parameter version drops it."""
+        h_len = L if self.kind == "hcl" else self.h.shape[1]
+        n = fft_size(L, h_len)
+        # version counter, shape and storage address: a sharded copy (tensor parallelism swaps ``.data``) or an
+        # in-place update both drop the entry
+        ver = tuple((p._version, tuple(p.shape), p.data_ptr())
+                    for p in ((self.log_poles, self.residues) if self.kind == "hcl" else (self.h,)))
+        cache = self.__dict__.setdefault("_spectra", {})
+        ent = cache.get((L, n))
+        dev = self.D.device
+        if ent is None or ent[0] != ver or ent[1].device != dev:
+            h = self.long_filter(L) if self.kind == "hcl" else self.h
+            if len(cache) >= 2:
+                cache.pop(next(iter(cache)))
+            ent = (ver, torch.fft.rfft(h.float(), n=n))
+            cache[(L, n)] = ent
+        return ent[1], n
+
     def long_filter(self, L: int) -> torch.Tensor:
         t = torch.arange(L, device=self.residues.device, dtype=torch.float32)
         lam = torch.exp(self.log_poles.float())                                   # in (0, 1)
@@ -132,11 +160,11 @@ class HyenaOperator(nn.Module):
         if self.kind in ("hcs", "hcm"):
             tail = None if state is None else state.get("inner_tail")
             if self.kind == "hcm" and u.shape[1] > 4 * self.h.shape[1] and tail is None:
-                y = fft_causal_conv(u, self.h)
+                y = fft_causal_conv(u, None, *self.filter_spectrum(u.shape[1]))
             else:
                 y = causal_fir(u, self.h, tail)
         else:
-            y = fft_causal_conv(u, self.long_filter(u.shape[1]))
+            y = fft_causal_conv(u, None, *self.filter_spectrum(u.shape[1]))
         return y + u * self.D.to(u.dtype)
 
     def _kernel_taps(self):
@@ -149,16 +177,11 @@ class HyenaOperator(nn.Module):
         """x2 * (conv(u) + D u) with the gate folded into the convolution's epilogue."""
         from ..ops import seq
         if self.kind in ("hcs", "hcm"):
-            if self.kind == "hcm" and u.shape[1] > 4 * self.h.shape[1] and tail is None:
-                h = self.h
-            else:
+            if not (self.kind == "hcm" and u.shape[1] > 4 * self.h.shape[1] and tail is None):
                 return seq.fir_inner_gate(u, self._kernel_taps()[1], self.D, x2, tail)
-        else:
-            h = self.long_filter(u.shape[1])
-        L = u.shape[1]
-        n = 1 << (L + h.shape[1] - 1).bit_length()
+        Hf, n = self.filter_spectrum(u.shape[1])
         X = torch.fft.rfft(u.float().transpose(1, 2), n=n)
-        y = torch.fft.irfft(X * torch.fft.rfft(h.float(), n=n).unsqueeze(0), n=n)        # [B, d, n] fp32
+        y = torch.fft.irfft(X * Hf.unsqueeze(0), n=n)                                     # [B, d, n] fp32
         return seq.fftconv_epilogue(y, u, self.D, x2)
 
     def forward(self, x: torch.Tensor, state: Optional[dict] = None, linear=None) -> torch.Tensor:
