@@ -6,7 +6,9 @@ not reproduce its statement on this driver / GPU.
 
 The probes are deterministic (fixed generator seeds), take well under a second together, and need no files: the
 reference side is computed on the spot in fp32, so there are no recorded vectors to go stale.  ``run_all`` caches
-its verdict per device for the life of the process.
+its verdict per device for the life of the process.  The pair-layer probes seed the global generators
+(``torch.manual_seed(3)``) to build their weights: code that depends on the global random state seeds it after
+the first kernel-mode ``Predictor`` has been constructed (``Predictor.predict`` seeds every call itself).
 
 Reference: recorded test vectors + byte gates of the native kernels (triattn_native testvectors/cases.py,
 apb/fpf_apb/loadcheck.py), warm probes against fp64 (fpf_trimul_v4/DESIGN.md:39-45).
