@@ -1,4 +1,5 @@
-"""Generate the per-kit entry points: ``kits/<kit>/run.sh``, ``configs/b200.env`` and the ``.pth`` hook
+"""Generate the per-kit entry points: ``kits/<kit>/run.sh``, ``configs/b200.env``, ``CHANGES.md`` (what each mode
+changes, lever by lever) and the ``.pth`` hook
 package for library-style activation.  Run once after editing the registry:
 ``python -m uplifting_biomolecular_modeling_b200.kits.scaffold``.  The generated ``run.sh`` keeps the
 reference's surface: ``run.sh install | check | <command> --config <card> --mode off|exact|fast|big
@@ -38,6 +39,66 @@ NCCL_NVLS_ENABLE=${{NCCL_NVLS_ENABLE:-1}}
 """
 
 
+FAMILY_MODULE = {
+    "cofold": "models/cofold.py (Pairformer trunk, MSA module, template embedder, diffusion sampler, confidence head)",
+    "design": "models/cofold.py structure trunk with the design conditioning levers",
+    "evo2": "models/evo2.py (StripedHyena-2; tensor parallel through parallel/tp.py)",
+    "protein_lm": "models/plm.py (ESM-C / E1 / ProGen2 / GPN-Star block forms)",
+    "genomic_track": "models/genomics.py (Enformer / Borzoi / Flashzoi / ChromBPNet)",
+}
+
+CHANGES = """# {name} - what each mode changes
+
+Upstream: {upstream}.  Served by `{module}`.
+Entry point: `kits/{name}/run.sh` (verbs: {verbs}); library use: `{env}=<mode>` or
+`uplifting_biomolecular_modeling_b200.kits.base.enable("{name}", mode)`.{library}
+
+| mode | meaning |
+|---|---|
+| `off` | the plain PyTorch statements, nothing engaged; the process is proven clean of kit state (`STOCK clean=True`) |
+{mode_rows}
+
+GPUs per run: {ngpu}.{ceiling}
+
+## Levers by mode
+
+{lever_tables}
+
+Every lever prints one `[{tag}] LEVER name=... state=engaged|skipped reason=...` line and is counted in the run's
+ledger; `MODEL_OPT_LEVERS_OFF=<lever,...>` removes levers from a mode (the run then reports a partial activation
+and exits 3 unless `--allow-partial`).  A mode that cannot engage prints `[{tag}] NOT ACTIVE: <reason>` and exits 3;
+kernels that fail their load-time check against the fp32 statements exit 5 (`KERNELS-REFUSED`).
+"""
+
+MODE_MEANING = {
+    "exact": "| `exact` | the same statements with step-invariant work hoisted and the sampler / forward step replayed as a CUDA graph; outputs bitwise equal to `off` |",
+    "fast": "| `fast` | the sm_100a kernel path in bf16 (tcgen05 kernels, fused row kernels, CUDA graphs); outputs within the documented tolerance of `off` |",
+    "big": "| `big` | `fast` plus the memory levers (row chunking, released intermediates) and, with `--n_gpu P`, the row-sharded pair tensor over peer memory |",
+}
+
+
+def changes_text(spec) -> str:
+    from .levers import LEVERS
+    tables = []
+    for mode in spec.modes:
+        names = spec.levers.get(mode, ())
+        if not names:
+            continue
+        rows = "\n".join(f"| `{n}` | {LEVERS[n].strategy} | `{LEVERS[n].impl}` | {'yes' if LEVERS[n].needs_gpu else 'no'} |"
+                         for n in names if n in LEVERS)
+        tables.append(f"### `{mode}`\n\n| lever | strategy | implemented by | needs a GPU |\n|---|---|---|---|\n{rows}")
+    return CHANGES.format(
+        name=spec.name, upstream=spec.upstream, module=FAMILY_MODULE.get(spec.family, spec.family),
+        verbs=", ".join(spec.commands), env=spec.env, tag=spec.tag,
+        library=("  Library-style kit: no mode is on by default; name one." if spec.library_style else
+                 f"  Default mode: `{spec.default}`."),
+        mode_rows="\n".join(MODE_MEANING[m] for m in spec.modes if m in MODE_MEANING),
+        ngpu=", ".join(str(n) for n in spec.n_gpu),
+        ceiling=("" if not spec.big_token_ceiling else
+                 f"  The reference states a single-GPU `big` ceiling of {spec.big_token_ceiling} tokens on an 80 GB card."),
+        lever_tables="\n\n".join(tables) or "(no levers beyond the mode's definition)")
+
+
 def generate(root: str = None) -> int:
     root = root or home.kits_root()
     n = 0
@@ -54,6 +115,8 @@ def generate(root: str = None) -> int:
         os.chmod(p, os.stat(p).st_mode | stat.S_IXUSR | stat.S_IXGRP | stat.S_IXOTH)
         with open(os.path.join(d, "configs", "b200.env"), "w") as f:
             f.write(ENV.format(name=name))
+        with open(os.path.join(d, "CHANGES.md"), "w") as f:
+            f.write(changes_text(spec))
         n += 1
     return n
 
