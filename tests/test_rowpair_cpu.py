@@ -85,3 +85,32 @@ def test_host_wait_times_out_by_name():
         return True
 
     assert all(run_ranks(2, fn, hub=hub))
+
+
+@pytest.mark.parametrize("P,N", [(2, 10), (3, 11)])
+def test_heads_gather_and_feature_broadcast(P, N):
+    from uplifting_biomolecular_modeling_b200.core.testing import run_ranks
+    from uplifting_biomolecular_modeling_b200.parallel import rowpair
+    from uplifting_biomolecular_modeling_b200.parallel.layout import Layout
+    torch.manual_seed(0)
+    z = torch.randn(N, N, 8)
+    lin = torch.nn.Linear(8, 5)
+    want = lin(z + z.transpose(0, 1))
+    feats0 = {"a": torch.arange(7.0), "b": torch.randint(0, 9, (3, 4)), "big": torch.randn(50, 33), "flag": True}
+    layout = Layout(N, P)
+
+    def body(comm):
+        z_loc = rowpair.shard_rows(z, layout, comm.rank)
+        logits = rowpair.sym_logit_rows(z_loc, lin, layout, comm)
+        whole = rowpair.gather_rows_to_rank0_host(logits, comm, block_cols=3)
+        feats = rowpair.broadcast_features(feats0 if comm.rank == 0 else None, comm, chunk_bytes=256)
+        return whole, feats
+
+    for r, (whole, feats) in enumerate(run_ranks(P, body)):
+        if r == 0:
+            torch.testing.assert_close(whole, want, atol=1e-5, rtol=1e-5)
+        else:
+            assert whole is None
+        assert feats["flag"] is True and set(feats) == set(feats0)
+        for k in ("a", "b", "big"):
+            assert feats[k].dtype == feats0[k].dtype and torch.equal(feats[k], feats0[k])

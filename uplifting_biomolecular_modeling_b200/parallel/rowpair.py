@@ -196,3 +196,86 @@ def shard_bytes(n: int, c: int, elt: int, world: int) -> int:
     """u = N^2 * C * elt / P, the unit of the per-rank peak model peak = a(N) + b(N) / P
     (common/opt_core/opt_core/mem/rowpair/API.md:174)."""
     return n * n * c * elt // world
+
+
+# ------------------------------------------------------------------------------------------ heads, gathers, features
+def sym_logit_rows(z_loc: torch.Tensor, linear, layout: Layout, comm: Comm) -> torch.Tensor:
+    """Rows of ``linear(z + z^T)`` (distogram / contact heads) from a row shard: the transposed shard arrives by the
+    same distributed transpose the ending-node attention uses; the sum and the projection are local.
+    Reference: heads.sym_logit_rows (mem/rowpair/heads.py:150)."""
+    zt = transpose_shard(z_loc, layout, comm)
+    return linear(z_loc + zt)
+
+
+def gather_rows_to_rank0_host(x_loc: torch.Tensor, comm: Comm, block_cols: Optional[int] = None,
+                              max_block_bytes: int = 64 << 20) -> Optional[torch.Tensor]:
+    """Row shards ``[rows_r, N, ...]`` -> the whole tensor in host memory on rank 0 (None elsewhere), gathered in
+    column blocks of at most ``max_block_bytes`` per rank so that no rank ever stages the whole tensor on its
+    device.  Reference: dist.gather_rows_to_rank0_host (mem/rowpair/dist.py:1686)."""
+    rows = [int(t.item()) for t in comm.all_gather(torch.tensor([x_loc.shape[0]], dtype=torch.long, device=x_loc.device))]
+    N = x_loc.shape[1]
+    tail = tuple(x_loc.shape[2:])
+    per_col = max(1, x_loc.shape[0]) * x_loc.element_size()
+    for d in tail:
+        per_col *= int(d)
+    if block_cols is None:
+        block_cols = max(1, min(N, max_block_bytes // max(1, per_col)))
+    out = None
+    if comm.rank == 0:
+        pin = torch.cuda.is_available() and x_loc.is_cuda
+        out = torch.empty((sum(rows), N) + tail, dtype=x_loc.dtype, pin_memory=pin)
+    starts = [sum(rows[:r]) for r in range(comm.world)]
+    for c0 in range(0, N, block_cols):
+        c1 = min(N, c0 + block_cols)
+        parts = comm.all_gather(x_loc[:, c0:c1].contiguous())
+        if comm.rank == 0:
+            for r, p in enumerate(parts):
+                out[starts[r]:starts[r] + rows[r], c0:c1].copy_(p, non_blocking=True)
+    if comm.rank == 0 and x_loc.is_cuda:
+        torch.cuda.current_stream(x_loc.device).synchronize()
+    return out
+
+
+def broadcast_features(feats, comm: Comm, src: int = 0, chunk_bytes: int = 64 << 20, device=None):
+    """Rank ``src`` featurises, every rank receives: the key / shape / dtype table travels through the host store,
+    the tensors as coalesced byte chunks of at most ``chunk_bytes`` (small tensors share a chunk, large ones are
+    split).  Returns the feature dict on every rank.  Reference: bcast.broadcast_tensordict
+    (mem/rowpair/bcast.py:118)."""
+    import json
+    if comm.world == 1:
+        return feats
+    key = "ubm_features_table"
+    if comm.rank == src:
+        table = [(k, list(v.shape), str(v.dtype).replace("torch.", "")) for k, v in feats.items()
+                 if isinstance(v, torch.Tensor)]
+        extras = {k: v for k, v in feats.items() if not isinstance(v, torch.Tensor)}
+        comm.host_signal(key, json.dumps({"table": table, "extras": extras}))
+    meta = json.loads(comm.host_wait(key))
+    table = meta["table"]
+    dev = device if device is not None else (next(iter(feats.values())).device if comm.rank == src and feats else "cpu")
+    sizes = []
+    for k, shape, dt in table:
+        n = 1
+        for s in shape:
+            n *= s
+        sizes.append(n * torch.empty((), dtype=getattr(torch, dt)).element_size())
+    # every tensor starts on a 16-byte boundary of the wire buffer (views of wider element types need it)
+    offsets, total = [], 0
+    for nbytes in sizes:
+        offsets.append(total)
+        total += (nbytes + 15) // 16 * 16
+    flat = torch.zeros(total, dtype=torch.uint8, device=dev)
+    if comm.rank == src:
+        for (k, _, _), o, nbytes in zip(table, offsets, sizes):
+            if nbytes:
+                flat[o:o + nbytes].copy_(feats[k].contiguous().view(-1).view(torch.uint8))
+    for o in range(0, total, chunk_bytes):
+        piece = flat[o:o + chunk_bytes]
+        got = comm.broadcast(piece.contiguous(), src)
+        if comm.rank != src:
+            piece.copy_(got)
+    out = dict(meta["extras"])
+    for (k, shape, dt), o, nbytes in zip(table, offsets, sizes):
+        out[k] = flat[o:o + nbytes].view(getattr(torch, dt)).view(*shape) if nbytes else \
+            torch.empty(shape, dtype=getattr(torch, dt), device=dev)
+    return out
