@@ -114,3 +114,27 @@ def test_heads_gather_and_feature_broadcast(P, N):
         assert feats["flag"] is True and set(feats) == set(feats0)
         for k in ("a", "b", "big"):
             assert feats[k].dtype == feats0[k].dtype and torch.equal(feats[k], feats0[k])
+
+
+@pytest.mark.parametrize("P,N", [(2, 12), (3, 10)])
+def test_token_transformer_on_row_shards_equals_dense(P, N):
+    from uplifting_biomolecular_modeling_b200.core.testing import run_ranks
+    from uplifting_biomolecular_modeling_b200.models import diffusion
+    from uplifting_biomolecular_modeling_b200.parallel import rowpair
+    from uplifting_biomolecular_modeling_b200.parallel.layout import Layout
+    torch.manual_seed(1)
+    tr = diffusion.DiffusionTransformer(depth=2, dim=32, dim_s=24, heads=4).eval()
+    a = torch.randn(2, N, 32)
+    s = torch.randn(1, N, 24)
+    bias = torch.randn(1, 4, N, N)
+    with torch.no_grad():
+        want = tr(a, s, [bias, bias])
+    layout = Layout(N, P)
+
+    def body(comm):
+        r0, r1 = layout.rows(comm.rank)
+        with torch.no_grad():
+            return rowpair.dit_rows(tr, a[:, r0:r1], s[:, r0:r1], bias[:, :, r0:r1], comm)
+
+    got = torch.cat(run_ranks(P, body), 1)
+    torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)

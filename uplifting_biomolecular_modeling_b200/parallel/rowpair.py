@@ -279,3 +279,26 @@ def broadcast_features(feats, comm: Comm, src: int = 0, chunk_bytes: int = 64 <<
         out[k] = flat[o:o + nbytes].view(getattr(torch, dt)).view(*shape) if nbytes else \
             torch.empty(shape, dtype=getattr(torch, dt), device=dev)
     return out
+
+
+# ------------------------------------------------------------------------------------------ token transformer (DiT)
+def dit_layer_rows(layer, a_loc: torch.Tensor, s_loc: torch.Tensor, bias_loc: torch.Tensor, comm: Comm):
+    """One diffusion-transformer token layer on a token-row shard.  a_loc: [B, R, c] activations of the local
+    token rows, s_loc: [B or 1, R, c_s] their conditioning, bias_loc: [1, H, R, N] the bias rows of the local
+    queries.  Per layer one all-gather of the AdaLN-normalised rows (keys / values of every token); queries, the
+    gate, the conditioned transition and both residuals are local to the shard.
+    Reference: diffusion.dit_block_sharded (mem/rowpair/diffusion.py:545)."""
+    h = layer.hoist(s_loc)
+    b_loc = layer.adaln(a_loc, None, h["adaln"], False)
+    parts = comm.all_gather(b_loc.transpose(0, 1).contiguous())                # token rows lead for the gather
+    b_all = torch.cat(parts, 0).transpose(0, 1)                                 # [B, N, c]
+    o_loc = layer.pair_bias_attn(b_loc, None, None, bias=bias_loc, k_in=b_all)
+    a_loc = a_loc + torch.sigmoid(h["gate"]) * o_loc
+    return a_loc + layer.transition(a_loc, None, h["t_adaln"], h["t_gate"], False)
+
+
+def dit_rows(transformer, a_loc, s_loc, bias_loc, comm: Comm):
+    """All token layers on a token-row shard (see :func:`dit_layer_rows`)."""
+    for layer in transformer.layers:
+        a_loc = dit_layer_rows(layer, a_loc, s_loc, bias_loc, comm)
+    return a_loc
