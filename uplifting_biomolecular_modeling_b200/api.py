@@ -193,7 +193,6 @@ class Predictor:
             torch.cuda.manual_seed(self.seed if seed is None else seed)
         else:
             torch.manual_seed(self.seed if seed is None else seed)
-        import os
         timing = os.environ.get("UBM_STAGE_TIMES") == "1" and dev.type == "cuda"
         marks = []
 
