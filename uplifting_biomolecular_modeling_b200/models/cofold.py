@@ -48,6 +48,7 @@ class CofoldConfig:
     atom_feat: int = 24
     relpos_bins: int = 139
     template_blocks: int = 0          # > 0 adds the template embedder (2 in the AF3 family); features optional
+    align_reverse_diff: bool = False  # Boltz-2 sampler: rigid alignment of noisy onto denoised coordinates per step
 
 
 CONFIGS: Dict[str, CofoldConfig] = {
@@ -197,6 +198,7 @@ class CofoldModel(nn.Module):
         score = DiffusionModule(cfg.c_s, cfg.c_z, cfg.c_atom, cfg.c_atompair, cfg.token_depth, cfg.token_heads,
                                 cfg.atom_depth, cfg.atom_heads, cfg.window_q, cfg.window_k)
         self.structure_module = AtomDiffusion(score, cfg.sampling_steps)
+        self.structure_module.align_reverse_diff = cfg.align_reverse_diff
         self.z_cond_norm = nn.LayerNorm(cfg.c_z)
         self.confidence_module = ConfidenceModule(cfg)
         self.fused = False

@@ -493,6 +493,10 @@ class AtomDiffusion(nn.Module):
         self.num_steps, self.gamma_0, self.gamma_min = num_steps, gamma_0, gamma_min
         self.noise_scale, self.step_scale = noise_scale, step_scale
         self.sigma_data = score_model.sigma_data
+        # Boltz-2's sampler aligns the noisy coordinates onto the denoised ones before the update
+        # ("alignment_reverse_diff"); off unless a configuration asks for it.  The alignment is graph-safe
+        # (models/align.py: fixed-sweep Jacobi SVD, no solver call between replays).
+        self.align_reverse_diff = False
 
     def denoise(self, x_noisy, sigma, prep, atom_to_token, n_tokens):
         """Preconditioned network output D(x; sigma).  sigma: [B]."""
@@ -516,6 +520,9 @@ class AtomDiffusion(nn.Module):
             torch.randn(x.shape, device=x.device, generator=generator)
         x_noisy = x + eps
         den = self.denoise(x_noisy, t_hat.expand(B), prep, atom_to_token, n_tokens)
+        if self.align_reverse_diff:
+            from .align import weighted_rigid_align
+            x_noisy = weighted_rigid_align(x_noisy, den)
         d = (x_noisy - den) / t_hat
         return x_noisy + self.step_scale * (sigma_t - t_hat) * d
 
