@@ -27,6 +27,8 @@ def _load_features(args, cfg, config_name):
 
 
 def run(spec, act: "base.Activation", args, allow_partial: bool) -> int:
+    if spec.name in ("proteinmpnn", "esm_if1", "ef2inv"):
+        return _run_design(spec, act, args, allow_partial)
     if spec.family in ("cofold", "design"):
         return _run_cofold(spec, act, args, allow_partial)
     if spec.family == "evo2":
@@ -102,6 +104,44 @@ def _run_cofold(spec, act, args, allow_partial) -> int:
     report.emit(report.line(spec.tag, "DONE", ("seconds", round(dt, 3)), ("tokens", feats["token_feat"].shape[1]),
                             ("samples", out["coords"].shape[0])))
     return act.finish(0, allow_partial, args.out_dir, incomplete)
+
+
+def _run_design(spec, act, args, allow_partial) -> int:
+    """``design`` verb of the sequence-design kits: inverse folding of a synthetic backbone (proteinmpnn, esm_if1) or
+    sequence inversion through the structure trunk (ef2inv)."""
+    import torch
+    from ..models import cofold, design
+    try:
+        act.apply(None)
+    except base.ActivationError:
+        return report.EXIT_NOT_ACTIVE
+    act.register_exit()
+    n = args.tokens or 32
+    t0 = time.time()
+    if spec.name == "ef2inv":
+        model = cofold.build_model("tiny", device="cpu", dtype=torch.float32, seed=args.seed)
+        feats = cofold.synthetic_features(n, 4, model.cfg, seed=args.seed)
+        g = torch.Generator().manual_seed(args.seed)
+        target = torch.randint(0, model.cfg.distogram_bins, (1, n, n), generator=g)
+        inv = design.SequenceInversion(model, feats, target, seed=args.seed)
+        losses = [inv.step() for _ in range(4)]
+        res = {"loss_first": round(losses[0], 4), "loss_last": round(losses[-1], 4), "tokens": n}
+        seqs = inv.sequence()
+    else:
+        dec = design.build_decoder(seed=args.seed)
+        x = torch.randn(1, n, 3, generator=torch.Generator().manual_seed(args.seed)) * 6.0
+        k = args.diffusion_samples or 2
+        seqs = dec.sample(x, seeds=[args.seed + i for i in range(k)])
+        res = {"sequences": k, "tokens": n}
+    letters = "ACDEFGHIKLMNPQRSTVWY"
+    text = ["".join(letters[int(t)] for t in row.tolist()) for row in seqs]
+    report.emit(report.line(spec.tag, "DONE", ("seconds", round(time.time() - t0, 3)), ("verb", args.verb),
+                            *res.items(), ("first", text[0][:40])))
+    if args.out_dir:
+        os.makedirs(args.out_dir, exist_ok=True)
+        with open(os.path.join(args.out_dir, "design.json"), "w") as f:
+            json.dump(dict(res, sequences_text=text), f)
+    return act.finish(0, allow_partial, args.out_dir)
 
 
 def _run_lm(spec, act, args, allow_partial, family) -> int:
