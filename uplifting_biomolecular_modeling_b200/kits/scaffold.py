@@ -41,7 +41,7 @@ NCCL_NVLS_ENABLE=${{NCCL_NVLS_ENABLE:-1}}
 
 FAMILY_MODULE = {
     "cofold": "models/cofold.py (Pairformer trunk, MSA module, template embedder, diffusion sampler, confidence head)",
-    "design": "models/cofold.py structure trunk with the design conditioning levers",
+    "design": "models/cofold.py structure trunk with the design conditioning levers; models/design.py (sequence inversion, inverse-folding decoder) for ef2inv / proteinmpnn / esm_if1",
     "evo2": "models/evo2.py (StripedHyena-2; tensor parallel through parallel/tp.py)",
     "protein_lm": "models/plm.py (ESM-C / E1 / ProGen2 / GPN-Star block forms)",
     "genomic_track": "models/genomics.py (Enformer / Borzoi / Flashzoi / ChromBPNet)",
