@@ -62,3 +62,18 @@ def test_every_wait_in_the_tensor_core_kernels_is_bounded():
             f"{f}: raw barrier wait outside the bounded helper"
     helper = open(os.path.join(csrc, "sm100.cuh")).read()
     assert "globaltimer" in helper and "try_wait" in helper
+
+
+def test_pair_index_products_are_64_bit():
+    """N * N * 128 passes 2^31 at N = 4096: every product of two token extents in kernel code is widened first."""
+    csrc = os.path.join(PKG, "ops", "csrc")
+    rx = re.compile(r"\bN\s*\*\s*(N|Np)\b|\bNp\s*\*\s*N\b")
+    bad = []
+    for f in sorted(os.listdir(csrc)):
+        if not f.endswith((".cu", ".cuh")):
+            continue
+        for n, line in enumerate(open(os.path.join(csrc, f)), 1):
+            code = line.split("//")[0]
+            if rx.search(code) and not re.search(r"long long|size_t|int64_t|uint64_t", code):
+                bad.append(f"{f}:{n}: {code.strip()}")
+    assert not bad, bad
