@@ -59,6 +59,7 @@ def main():
     ap.add_argument("--m", type=int, default=7680, help="rows of the gemm_rows case / atoms of window_attention")
     ap.add_argument("--k", type=int, default=768)
     ap.add_argument("--nn", type=int, default=3072)
+    ap.add_argument("--incoming", type=int, default=0, help="trimul / trimul_gemm: 1 = the incoming update (MN-major contraction)")
     a = ap.parse_args()
     N, c = a.n, 128
     pair.set_attention_variant(a.attn_variant)
@@ -92,7 +93,8 @@ def main():
         f1 = lambda: lib.ubm_trimul_proj(native.ptr(z), native.ptr(w.w_in), native.ptr(w.in_colsum),  # noqa: E731
                                          native.ptr(w.in_colbias), 0, native.ptr(planes), 0, N, Np, native.ptr(st),
                                          stream)
-        f2 = lambda: gemm.gemm(planes[0][:, :, :N], planes[1][:, :, :N], out=x[:, :, :N])  # noqa: E731
+        f2 = lambda: gemm.gemm(planes[0][:, :, :N], planes[1][:, :, :N], mn_major=bool(a.incoming),  # noqa: E731
+                               out=x[:, :, :N])
         f3 = lambda: lib.ubm_trimul_out(native.ptr(x), native.ptr(z), native.ptr(w.wo), native.ptr(w.wg),  # noqa: E731
                                         native.ptr(w.o_colsum), native.ptr(w.o_colbias), native.ptr(w.g_colsum),
                                         native.ptr(w.g_colbias), native.ptr(out), N, Np, 1, native.ptr(st), stream)
