@@ -104,3 +104,16 @@ def test_filter_spectra_are_cached_per_length_and_follow_the_weights():
         hcl.residues.mul_(1.5)                                                             # bumps the version
     c = m(toks)
     assert not torch.equal(a, c)
+
+
+def test_oversized_filter_spectra_are_not_kept(monkeypatch):
+    from uplifting_biomolecular_modeling_b200.models import evo2
+    m = evo2.build("evo2_tiny", seed=5)
+    toks = torch.randint(0, 4, (1, 96), generator=torch.Generator().manual_seed(0))
+    want = m(toks)
+    for b in m.blocks:
+        b.mixer.__dict__.pop("_spectra", None)
+    monkeypatch.setattr(evo2, "SPECTRUM_CACHE_MAX_BYTES", 16)
+    got = m(toks)
+    assert torch.equal(got, want)
+    assert all(not b.mixer.__dict__.get("_spectra") for b in m.blocks)

@@ -90,6 +90,9 @@ def causal_fir(x: torch.Tensor, h: torch.Tensor, tail: Optional[torch.Tensor] = 
     return F.conv1d(xp, w, groups=C).transpose(1, 2)
 
 
+SPECTRUM_CACHE_MAX_BYTES = 2 << 30
+
+
 def fft_size(L: int, Lh: int) -> int:
     return 1 << (L + Lh - 1).bit_length()
 
@@ -144,9 +147,14 @@ class HyenaOperator(nn.Module):
         dev = self.D.device
         if ent is None or ent[0] != ver or ent[1].device != dev:
             h = self.long_filter(L) if self.kind == "hcl" else self.h
+            spec = torch.fft.rfft(h.float(), n=n)
+            # an entry is d x (n/2 + 1) complex64: kept only below a size limit (million-token contexts would pin tens
+            # of GB per operator); above it the spectrum is rebuilt per call as before
+            if spec.numel() * 8 > SPECTRUM_CACHE_MAX_BYTES:
+                return spec, n
             if len(cache) >= 2:
                 cache.pop(next(iter(cache)))
-            ent = (ver, torch.fft.rfft(h.float(), n=n))
+            ent = (ver, spec)
             cache[(L, n)] = ent
         return ent[1], n
 
