@@ -183,3 +183,23 @@ def test_sample_loop_chunks():
     out = sample_loop.run(sample, lambda x: {"plddt": x.mean((1, 2))}, n_samples=5, chunk=2)
     assert seen == [(0, 2), (2, 4), (4, 5)]
     assert out["coords"].shape == (5, 3, 3) and out["plddt"].tolist() == [0.0, 1.0, 2.0, 3.0, 4.0]
+
+
+def test_track_writer_and_one_hot_lookup(tmp_path):
+    import numpy as np
+    import torch
+    from uplifting_biomolecular_modeling_b200.host import tracks
+    from uplifting_biomolecular_modeling_b200.models import genomics
+    x = genomics.one_hot_dna("ACGTNacgt-")
+    assert x.shape == (1, 10, 8) and x[0, :, 4:].sum() == 0
+    assert x[0, :4, :4].equal(torch.eye(4)) and x[0, 5:9, :4].equal(torch.eye(4))
+    assert x[0, 4].sum() == 0 and x[0, 9].sum() == 0
+    lines = tracks.bedgraph_lines("chr1", 1000, 128, [0.5, 0.5, 0.25, 0.25, 0.25, 1.0])
+    assert lines == ["chr1\t1000\t1256\t0.5", "chr1\t1256\t1640\t0.25", "chr1\t1640\t1768\t1"]
+    w = tracks.TrackWriter(str(tmp_path), bin_size=128, columns=(0, 2), save_arrays=True)
+    w.submit("chr1", 0, torch.tensor([[1.0, 9, 3], [1.0, 9, 4]]))
+    w.submit("chr1", 256, np.array([[2.0, 9, 4], [2.0, 9, 4]]))
+    assert w.close() == 5
+    t0 = open(tmp_path / "track_0.bedGraph").read().splitlines()
+    assert t0[0].startswith("track type=bedGraph") and t0[1:] == ["chr1\t0\t256\t1", "chr1\t256\t512\t2"]
+    assert np.load(tmp_path / "chr1_256.npy").shape == (2, 3)

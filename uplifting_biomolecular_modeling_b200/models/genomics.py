@@ -37,14 +37,23 @@ def _bf16(w: torch.Tensor) -> torch.Tensor:
     return w.detach().to(torch.bfloat16).contiguous()
 
 
+_ONE_HOT_LUT = None
+
+
 def one_hot_dna(text: str, device="cpu", dtype=torch.float32, channels: int = 8) -> torch.Tensor:
-    """ACGT -> one-hot [1, L, channels] (channels >= 4; the extra channels stay zero so rows are 16 bytes)."""
-    lut = {"A": 0, "C": 1, "G": 2, "T": 3}
-    x = torch.zeros((1, len(text), channels), dtype=dtype, device=device)
-    for i, ch in enumerate(text.upper()):
-        if ch in lut:
-            x[0, i, lut[ch]] = 1
-    return x
+    """ACGT -> one-hot [1, L, channels] (channels >= 4; the extra channels stay zero so rows are 16 bytes; any other
+    letter is an all-zero row).  One table lookup over the raw bytes: no per-character loop."""
+    global _ONE_HOT_LUT
+    if _ONE_HOT_LUT is None:
+        lut = torch.zeros((256, 4))
+        for i, ch in enumerate("ACGT"):
+            lut[ord(ch), i] = 1
+            lut[ord(ch.lower()), i] = 1
+        _ONE_HOT_LUT = lut
+    raw = torch.frombuffer(bytearray(text.encode("latin-1", "replace")), dtype=torch.uint8).long()
+    x = torch.zeros((1, raw.numel(), channels), dtype=dtype)
+    x[0, :, :4] = _ONE_HOT_LUT[raw].to(dtype)
+    return x.to(device)
 
 
 # ------------------------------------------------------------------------------------------ convolution as a GEMM
