@@ -311,7 +311,10 @@ class ProteinLM(nn.Module):
         if cfg.family == "gpnstar":
             if alignment is None:
                 raise ValueError("gpnstar needs the alignment rows [B, R, L] and the clade -> row index")
-            align = self.row_embed(alignment)                                # [B, R, L, d]
+            # only the alignment rows that some clade refers to are embedded and projected (per layer the K | V
+            # projection of the rows is the largest GEMM of this family): clade -> row becomes clade -> kept row
+            uniq, clade_index = torch.unique(clade_index, return_inverse=True)
+            align = self.row_embed(alignment[:, uniq])                       # [B, R', L, d], R' <= clades
         for blk in self.blocks:
             if cfg.family == "progen2":
                 x = blk(x, pos)
