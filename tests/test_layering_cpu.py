@@ -38,19 +38,6 @@ def test_nothing_committed_depends_on_scratch_or_compat_layers():
     assert not bad, bad
 
 
-def test_kernel_sources_name_no_closed_call_and_no_multicast_load():
-    closed = re.compile(r"cu(da)?Memcpy(3D)?BatchAsync")
-    multicast = re.compile(r"cp\.async\.bulk[^;\"]*multicast::cluster")
-    bad = []
-    for path in _sources((".cu", ".cuh", ".h", ".py", ".sh")):
-        if os.path.basename(path) == "test_layering_cpu.py":
-            continue
-        text = open(path, errors="replace").read()
-        if closed.search(text) or multicast.search(text):
-            bad.append(path)
-    assert not bad, bad
-
-
 def test_every_wait_in_the_tensor_core_kernels_is_bounded():
     """Spin loops on barriers go through the bounded helpers of sm100.cuh (time limit + status word)."""
     csrc = os.path.join(PKG, "ops", "csrc")
