@@ -55,10 +55,11 @@ def main():
     ap.add_argument("--n", type=int, default=768)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--attn-variant", type=int, default=0, help="attention: 0 = default (four rows per CTA from 4 rows on), 5 = two rows per CTA, 1 = P and bias through shared memory; window_attention: 1 = CUDA-core kernel")
+    ap.add_argument("--attn-variant", type=int, default=0, help="attention: 0 = default (four rows per CTA from 4 rows on), 5 = two rows per CTA, 1 = P and bias through shared memory, +16 = no polynomial exponentials; window_attention: 1 = CUDA-core kernel")
     ap.add_argument("--m", type=int, default=7680, help="rows of the gemm_rows case / atoms of window_attention")
     ap.add_argument("--k", type=int, default=768)
     ap.add_argument("--nn", type=int, default=3072)
+    ap.add_argument("--masked", type=int, default=0, help="attention: 1 = key mask with a padded tail of a tenth of the keys")
     ap.add_argument("--incoming", type=int, default=0, help="trimul / trimul_gemm: 1 = the incoming update (MN-major contraction)")
     a = ap.parse_args()
     N, c = a.n, 128
@@ -82,7 +83,12 @@ def main():
         k, v, g = torch.randn_like(q), torch.randn_like(q), torch.rand_like(q)
         bias = torch.randn(H, N, Np, device=dev).bfloat16()
         out = torch.empty_like(q)
-        fn = lambda: pair.attention(q, k, v, bias, g, out, rows, N, N, H, D, ldb=Np)  # noqa: E731
+        km = None
+        if a.masked:
+            keep = torch.ones(rows, N, device=dev)
+            keep[:, N - N // 10:] = 0
+            km = pair.KeyMask.pack(keep)
+        fn = lambda: pair.attention(q, k, v, bias, g, out, rows, N, N, H, D, ldb=Np, mask=km)  # noqa: E731
         byts = 5 * q.numel() * 2 + bias.numel() * 2
         flops = 4.0 * rows * H * N * N * D
     elif a.case in ("trimul_proj", "trimul_gemm", "trimul_out", "trimul"):

@@ -48,14 +48,18 @@ def swiglu_rows(ab):
     return (F.silu(a) * b).to(ab.dtype)
 
 
-def attention(q, k, v, bias, gate, out, rows, Nq, Nk, H, D=32, ldb=0, ld_in=0, transpose_out=False, ld_gate=0):
+def attention(q, k, v, bias, gate, out, rows, Nq, Nk, H, D=32, ldb=0, ld_in=0, transpose_out=False, ld_gate=0,
+              mask=None):
     """q arrives multiplied by log2(e) / sqrt(D): probabilities are 2^(q.k)."""
     if bias is not None or gate is not None or transpose_out:
         raise NotImplementedError
     qh = q.reshape(rows, Nq, H, D).transpose(1, 2).float()
     kh = k.reshape(rows, Nk, H, D).transpose(1, 2).float()
     vh = v.reshape(rows, Nk, H, D).transpose(1, 2).float()
-    p = torch.softmax(torch.matmul(qh, kh.transpose(-1, -2)) / LOG2E, -1)
+    sc = torch.matmul(qh, kh.transpose(-1, -2))
+    if mask is not None:
+        sc = sc + mask.add[:, None, None, :Nk].float()
+    p = torch.softmax(sc / LOG2E, -1)
     out.copy_(torch.matmul(p, vh).transpose(1, 2).reshape(rows * Nq, H * D).to(out.dtype))
     return out
 

@@ -57,7 +57,78 @@ def test_trimul(N, outgoing):
     assert _rel_err(out, ref) < 6e-2
 
 
-@pytest.mark.parametrize("variant", [0, 5])
+def _attention_case(rows, N, H, D, g, masked):
+    """Inputs, the kernel's scaled operands and the fp32 statement of one attention call."""
+    from uplifting_biomolecular_modeling_b200.ops import pair, reference
+    q = _rand((rows, N, H * D), g).bfloat16()
+    k = _rand((rows, N, H * D), g).bfloat16()
+    v = _rand((rows, N, H * D), g).bfloat16()
+    gate = torch.rand((rows, N, H * D), device="cuda", generator=g).bfloat16()
+    Np = (N + 7) // 8 * 8
+    bias = torch.zeros((H, N, Np), device="cuda", dtype=torch.bfloat16)
+    bias[:, :, :N] = _rand((H, N, N), g).bfloat16()
+    qs = (q.float() * (pair.LOG2E / D ** 0.5)).bfloat16()
+    bs = (bias.float() * pair.LOG2E).bfloat16()
+    keep = None
+    if masked:
+        # some rows unmasked, some with scattered masked keys, some with a masked tail (padding)
+        keep = torch.ones((rows, N), device="cuda")
+        keep[1::3] = (torch.rand((len(range(1, rows, 3)), N), device="cuda", generator=g) > 0.3).float()
+        keep[2::3, N - N // 5:] = 0
+        keep[0, N - 3:] = 0
+        keep[:, 0] = 1
+    refs = []
+    for r0 in range(0, rows, 64):     # the fp32 statement in row chunks (its score tensor is rows x H x N x N)
+        sl = slice(r0, min(rows, r0 + 64))
+        qh = qs[sl].float().view(-1, N, H, D).transpose(1, 2) / pair.LOG2E
+        kh = k[sl].float().view(-1, N, H, D).transpose(1, 2)
+        vh = v[sl].float().view(-1, N, H, D).transpose(1, 2)
+        b = bs.float()[None, :, :, :N] / pair.LOG2E
+        if keep is not None:
+            b = b + ((1.0 - keep[sl]) * -1e9)[:, None, None, :]
+        o = reference.attention_with_bias(qh, kh, vh, b, scale=1.0)
+        refs.append(o.transpose(1, 2).reshape(-1, N, H * D) * gate[sl].float())
+    return qs, k, v, bs, gate, Np, keep, torch.cat(refs, 0)
+
+
+@pytest.mark.parametrize("variant", [0, 0x10])
+@pytest.mark.parametrize("rows,N,H,D", [(7, 200, 4, 32), (9, 384, 2, 32), (1, 136, 4, 32), (5, 200, 4, 64)])
+def test_attention_masked(rows, N, H, D, variant, request):
+    """Key masks per row (scattered keys, padded tails, unmasked rows) in every tile shape and with the polynomial
+    exponentials, against the fp32 statement with the same mask."""
+    from uplifting_biomolecular_modeling_b200.ops import native, pair
+    pair.set_attention_variant(variant)
+    request.addfinalizer(lambda: pair.set_attention_variant(0))
+    g = torch.Generator(device="cuda").manual_seed(15)
+    qs, k, v, bs, gate, Np, keep, ref = _attention_case(rows, N, H, D, g, masked=True)
+    km = pair.KeyMask.pack(keep)
+    assert km is not None and int(km.flags.sum()) < km.flags.numel()      # some steps take the mask-free loop
+    out = torch.empty_like(qs)
+    pair.attention(qs, k, v, bs, gate, out, rows, N, N, H, D, ldb=Np, mask=km)
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "attention")
+    err = (out.float() - ref).abs().max().item()
+    assert err < 3e-2, err
+    assert pair.KeyMask.pack(torch.ones((rows, N), device="cuda")) is None
+
+
+@pytest.mark.parametrize("masked", [False, True])
+def test_attention_core_n1536(masked):
+    """The benchmark size (1536 rows x 1536 keys, 4 heads x 32): every row against fp32 computed in row chunks."""
+    from uplifting_biomolecular_modeling_b200.ops import native, pair
+    g = torch.Generator(device="cuda").manual_seed(16)
+    rows = N = 1536
+    qs, k, v, bs, gate, Np, keep, ref = _attention_case(rows, N, 4, 32, g, masked)
+    out = torch.empty_like(qs)
+    pair.attention(qs, k, v, bs, gate, out, rows, N, N, 4, 32, ldb=Np,
+                   mask=None if keep is None else pair.KeyMask.pack(keep))
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "attention")
+    err = (out.float() - ref).abs().max().item()
+    assert err < 3e-2, err
+
+
+@pytest.mark.parametrize("variant", [0, 1, 5, 0x10])
 @pytest.mark.parametrize("rows,N,H", [(2, 128, 4), (5, 200, 4), (8, 384, 2)])
 def test_attention_core(rows, N, H, variant, request):
     """The attention kernel alone: base-2 softmax with shared bias, gate and tail masking.  Variant 0 takes the
@@ -110,6 +181,20 @@ def test_triangle_attention(N, starting):
     err = (out.float() - ref).abs().mean() / ref.abs().mean()
     assert err.item() < 3e-2, err.item()
     assert _rel_err(out, ref) < 6e-2
+    # with a pair mask (padding tail + scattered pairs): the ending node attends over the transposed mask
+    tok = torch.ones(N, device="cuda")
+    tok[N - N // 6:] = 0
+    pm = tok[:, None] * tok[None, :] * (torch.rand((N, N), device="cuda", generator=g) > 0.05).float()
+    pm[:, 0] = 1
+    pm[0, :] = 1
+    km = pair.KeyMask.pack(pm if starting else pm.t())
+    out = pair.triangle_attention_fused(z, w, starting=starting, residual=False, mask=km)
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "triangle attention (masked)")
+    ref = reference.triangle_attention(z.float(), pm, ln_w, ln_b, w_bias, w_q, w_k, w_v, w_g, b_g, w_o, b_o, H,
+                                       starting=starting)
+    err = (out.float() - ref).abs().mean() / ref.abs().mean()
+    assert err.item() < 3e-2, err.item()
 
 
 @pytest.mark.parametrize("B,N,H,D,c", [(3, 200, 16, 48, 768), (1, 136, 16, 24, 384)])

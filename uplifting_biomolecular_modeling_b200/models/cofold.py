@@ -235,6 +235,9 @@ class CofoldModel(nn.Module):
         tmask = feats["token_mask"]
         # without padding tokens the single-track attention needs no key mask (and may run fused)
         smask = None if feats.get("no_padding") is True else tmask
+        # pair mask of the triangle updates, as upstream builds it (boltz2/stock/src/boltz/model/models/boltz2.py:
+        # mask[:, :, None] * mask[:, None, :]); None only when the features say that no token is padding
+        pmask = None if smask is None else tmask[:, :, None] * tmask[:, None, :]
         for layer in self.msa_module.layers:
             layer.outer_product_mean.full_mask = feats.get("msa_full") is True
         for _ in range(n + 1):
@@ -245,8 +248,8 @@ class CofoldModel(nn.Module):
                       if k.startswith("template_")}
                 tf["asym_id"] = feats["chain_id"][0]
                 z = z + self.template_embedder(z, tf).to(z.dtype)
-            z = self.msa_module(z, s_inputs, feats["msa_feat"], feats["msa_mask"], tmask, None)
-            s, z = self.pairformer_module(s, z, smask, None)
+            z = self.msa_module(z, s_inputs, feats["msa_feat"], feats["msa_mask"], tmask, pmask)
+            s, z = self.pairformer_module(s, z, smask, pmask)
         return s, z
 
     def structure(self, feats, s, z, s_inputs, atom_c, atom_p, samples=None, steps=None, generator=None,

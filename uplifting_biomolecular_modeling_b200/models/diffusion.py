@@ -114,7 +114,9 @@ class DiffusionTransformerLayer(_Switchable):
                         self.transition.output_projection.bias.detach().float()], 0)
         return w1, b1, w2, b2
 
-    def _fused_token_layer(self, a, h, bias):
+    lever = "fused_dit"
+
+    def _fused_token_layer(self, a, h, bias, mask=None):
         """Token-transformer layer on the fused path: AdaLN rows -> q|k|v and gate projections (tcgen05
         GEMM) -> attention with the hoisted pair-bias planes shared by all samples -> output projection whose
         epilogue applies the conditioning gate and the residual; then the conditioned SwiGLU transition the same
@@ -135,7 +137,7 @@ class DiffusionTransformerLayer(_Switchable):
                                                    attn.heads)
             a = pair.window_attention_fused(b, attn._packed, bias.data, out_gate=gate, out_residual=a2)
         else:
-            a = attn._fused_forward(b, bias, out_gate=gate, out_residual=a2)
+            a = attn._fused_forward(b, bias, out_gate=gate, out_residual=a2, mask=mask)
         a2 = a.view(B * N, C)
         tr = self.transition
         if self._packed is None:
@@ -151,10 +153,17 @@ class DiffusionTransformerLayer(_Switchable):
         fused = self.impl == "fused"
         h = hoisted if hoisted is not None else self.hoist(s)
         from .pairformer import BiasPlanes
-        if fused and mask is None and a.is_cuda and a.dtype == torch.bfloat16 and \
-                ((window is None and isinstance(bias, BiasPlanes)) or
-                 (window == (32, 128) and isinstance(bias, WindowBias) and self.pair_bias_attn.head_dim == 32)):
-            return self._fused_token_layer(a, h, bias)
+        if fused:
+            token = window is None and isinstance(bias, BiasPlanes)
+            atoms = window == (32, 128) and isinstance(bias, WindowBias) and self.pair_bias_attn.head_dim == 32
+            why = self._tensor_reason(a) or (None if (token or atoms) else "bias_layout") \
+                or ("window_mask" if (atoms and mask is not None) else None)
+            klass = f"WIN{window[0]}x{window[1]}" if window is not None else \
+                f"D{64 if self.pair_bias_attn.head_dim > 32 else 32}H{self.pair_bias_attn.heads}S{a.shape[0]}"
+            if self._decide(why, klass, a.shape[1], {"head_dim": self.pair_bias_attn.head_dim, "dtype": "bf16",
+                                                     **({"window": tuple(window)} if window is not None else {})},
+                            "tcgen05_window" if atoms else "tcgen05_2row"):
+                return self._fused_token_layer(a, h, bias, mask)
         if isinstance(bias, WindowBias):
             bias = bias.dense()
         if isinstance(bias, BiasPlanes):

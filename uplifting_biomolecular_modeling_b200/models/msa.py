@@ -32,8 +32,11 @@ class OuterProductMean(_Switchable):
         self.row_block = 128
         self.full_mask = False      # set by the caller when the MSA mask is known (on the host) to be all ones
 
+    lever = "fused_opm"
+
     def forward(self, m: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
-        if not (self.impl == "fused" and m.is_cuda and m.dtype == torch.bfloat16 and m.shape[0] == 1):
+        why = self._tensor_reason(m) or (f"batch_{m.shape[0]}" if m.shape[0] != 1 else None)
+        if not self._decide(why, f"C{m.shape[-1]}H{self.c_hidden}S{m.shape[1]}", m.shape[2]):
             return R.outer_product_mean(m, mask, self.norm.weight, self.norm.bias, self.proj_a.weight,
                                         self.proj_b.weight, self.proj_o.weight, self.proj_o.bias)
         from ..ops import gemm, rows
@@ -88,8 +91,11 @@ class PairWeightedAveraging(_Switchable):
         self.proj_z = nn.Linear(c_z, heads, bias=False)
         self.proj_o = nn.Linear(c_h * heads, c_m, bias=False)
 
+    lever = "fused_pwa"
+
     def forward(self, m: torch.Tensor, z: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
-        if not (self.impl == "fused" and m.is_cuda and m.dtype == torch.bfloat16 and m.shape[0] == 1):
+        why = self._tensor_reason(m) or (f"batch_{m.shape[0]}" if m.shape[0] != 1 else None)
+        if not self._decide(why, f"C{m.shape[-1]}H{self.heads}x{self.c_h}S{m.shape[1]}", m.shape[2]):
             return R.pair_weighted_averaging(m, z, mask, self.norm_m.weight, self.norm_m.bias, self.norm_z.weight,
                                              self.norm_z.bias, self.proj_m.weight, self.proj_g.weight,
                                              self.proj_z.weight, self.proj_o.weight, self.heads)

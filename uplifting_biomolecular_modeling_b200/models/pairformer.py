@@ -25,12 +25,31 @@ class _Switchable(nn.Module):
     """A module with a per-instance implementation word and a lazily packed weight cache."""
 
     impl: str = "reference"
+    lever: str = ""          # the lever whose ledger counts this module's calls (ops.dispatch.LEVERS)
 
     def __init__(self):
         super().__init__()
         self.impl = "reference"
         self._packed = None
         self._workspace: Optional[dict] = None
+
+    def _decide(self, reason: Optional[str], klass: Optional[str] = None, tokens: Optional[int] = None,
+                call: Optional[dict] = None, row: Optional[str] = None) -> bool:
+        """Under the kernel implementation every call is decided and counted before it runs: ``reason`` None =
+        the kernel serves, otherwise the plain statement runs as ``fallback:<reason>`` in the lever's ledger (an
+        undeclared reason ends the run PARTIAL).  With the plain implementation there is nothing to count."""
+        if self.impl != "fused":
+            return False
+        from ..ops import dispatch
+        return dispatch.decide(self.lever, reason, klass, tokens, call, row)
+
+    @staticmethod
+    def _tensor_reason(x: torch.Tensor) -> Optional[str]:
+        if not x.is_cuda:
+            return "not_cuda"
+        if x.dtype != torch.bfloat16:
+            return f"dtype_{str(x.dtype).replace('torch.', '')}"
+        return None
 
     def set_impl(self, impl: str, workspace: Optional[dict] = None):
         if impl not in IMPLS:
@@ -56,16 +75,23 @@ class Transition(_Switchable):
         self.fc3 = nn.Linear(hidden, out_dim, bias=False)
         self.dim, self.hidden, self.out_dim = dim, hidden, out_dim
 
+    lever = "fused_transition"
+
     def forward(self, x: torch.Tensor, residual: bool = False) -> torch.Tensor:
-        if self._fusable(x) and self.dim == 128 and self.out_dim == 128 and self.hidden % 64 == 0 \
-                and self.hidden <= 1024:
+        one_kernel = self.dim == 128 and self.out_dim == 128 and self.hidden % 64 == 0 and self.hidden <= 1024
+        rows_ok = self.dim % 8 == 0 and self.dim <= 1024 and self.hidden % 8 == 0 and self.out_dim % 8 == 0
+        why = self._tensor_reason(x) or (None if (one_kernel or rows_ok) else f"width_{self.dim}x{self.hidden}")
+        tokens = x.shape[-2]
+        served = self._decide(why, f"C{self.dim}X{max(1, self.hidden // max(1, self.dim))}", tokens,
+                              {"c": self.dim, "expansion": self.hidden // max(1, self.dim), "dtype": "bf16"},
+                              "tcgen05_fused" if one_kernel else "rows_gemm")
+        if served and one_kernel:
             from ..ops import pair
             if self._packed is None:
                 self._packed = pair.TransitionPacked.pack(self.norm.weight, self.norm.bias, self.fc1.weight,
                                                           self.fc2.weight, self.fc3.weight)
             return pair.transition_fused(x.contiguous(), self._packed, residual=residual)
-        if self.impl == "fused" and x.is_cuda and x.dtype == torch.bfloat16 and self.dim % 8 == 0 \
-                and self.dim <= 1024 and self.hidden % 8 == 0 and self.out_dim % 8 == 0:
+        if served:
             # other widths (the MSA track at 64, the template stack): LayerNorm rows -> one GEMM for both hidden
             # projections -> SwiGLU rows -> output GEMM with the residual in its epilogue
             from ..ops import gemm, rows
@@ -93,8 +119,14 @@ class TriangleMultiplication(_Switchable):
         self.p_out = nn.Linear(dim, dim, bias=False)
         self.g_out = nn.Linear(dim, dim, bias=False)
 
+    lever = "fused_trimul"
+
     def forward(self, z: torch.Tensor, mask: Optional[torch.Tensor], residual: bool = False) -> torch.Tensor:
-        if self._fusable(z) and z.shape[0] == 1:
+        c = z.shape[-1]
+        why = self._tensor_reason(z) or (f"width_{c}" if c != 128 or self.p_in.weight.shape[0] != 256 else None) \
+            or (f"batch_{z.shape[0]}" if z.shape[0] != 1 else None)
+        if self._decide(why, f"C{c}H{self.p_in.weight.shape[0] // 2}", z.shape[1],
+                        {"c_z": c, "c_hidden": self.p_in.weight.shape[0] // 2, "dtype": "bf16"}):
             from ..ops import pair
             if self._packed is None:
                 self._packed = pair.TrimulPacked.pack(self.norm_in.weight, self.norm_in.bias, self.p_in.weight,
@@ -140,17 +172,26 @@ class TriangleAttention(_Switchable):
         self.linear = nn.Linear(c_in, heads, bias=False)
         self.mha = _MHA(c_in, c_hidden, heads)
 
+    lever = "fused_triatt"
+
     def forward(self, z: torch.Tensor, mask: Optional[torch.Tensor] = None, residual: bool = False) -> torch.Tensor:
         m = self.mha
-        if self._fusable(z) and z.shape[0] == 1 and mask is None and self.heads == 4 and self.c_hidden == 32:
+        why = self._tensor_reason(z) or (f"width_{z.shape[-1]}" if z.shape[-1] != 128 else None) \
+            or (f"heads_{self.heads}x{self.c_hidden}" if (self.heads, self.c_hidden) != (4, 32) else None) \
+            or (f"batch_{z.shape[0]}" if z.shape[0] != 1 else None)
+        if self._decide(why, f"D{self.c_hidden}H{self.heads}", z.shape[1],
+                        {"head_dim": self.c_hidden, "dtype": "bf16"}):
             from ..ops import pair
+            km = None
+            if mask is not None:
+                km = _cached_key_mask(self._workspace, mask[0], transposed=not self.starting)
             if self._packed is None:
                 self._packed = pair.TriattPacked.pack(self.layer_norm.weight, self.layer_norm.bias,
                                                       self.linear.weight, m.linear_q.weight, m.linear_k.weight,
                                                       m.linear_v.weight, m.linear_g.weight, m.linear_g.bias,
                                                       m.linear_o.weight, m.linear_o.bias, self.heads)
             out = pair.triangle_attention_fused(z[0].contiguous(), self._packed, self.starting, residual=residual,
-                                                workspace=self._workspace)
+                                                workspace=self._workspace, mask=km)
             return out.unsqueeze(0)
         outs = [R.triangle_attention(z[b], None if mask is None else mask[b], self.layer_norm.weight,
                                      self.layer_norm.bias, self.linear.weight, m.linear_q.weight, m.linear_k.weight,
@@ -158,6 +199,20 @@ class TriangleAttention(_Switchable):
                                      m.linear_o.bias, self.heads, starting=self.starting, residual=residual)
                 for b in range(z.shape[0])]
         return torch.stack(outs, 0)
+
+
+def _cached_key_mask(workspace: Optional[dict], mask: torch.Tensor, transposed: bool = False):
+    """Key mask of the attention kernel for a [rows, keys] keep-mask, packed once per mask tensor: the same pair
+    mask reaches every triangle attention of a stack, so the packed form is kept in the stack's workspace under the
+    tensor's identity and version."""
+    from ..ops import pair
+    ws = workspace if workspace is not None else {}
+    key = ("keymask", mask.data_ptr(), mask._version, tuple(mask.shape), transposed)
+    if key not in ws:
+        for k in [k for k in ws if isinstance(k, tuple) and k and k[0] == "keymask" and k[1] != mask.data_ptr()]:
+            del ws[k]
+        ws[key] = pair.KeyMask.pack(mask.t() if transposed else mask)
+    return ws[key]
 
 
 class TriangleAttentionStartingNode(TriangleAttention):
@@ -200,6 +255,8 @@ class AttentionPairBias(_Switchable):
             self.proj_z = nn.Sequential(nn.LayerNorm(c_z), nn.Linear(c_z, heads, bias=False))
         self.proj_o = nn.Linear(c_s, c_s, bias=False)
 
+    lever = "fused_apb"
+
     def pair_bias(self, z: torch.Tensor):
         """[B, H, N, N] bias from the pair tensor (a :class:`BiasPlanes` on the fused path)."""
         if self._fusable(z) and z.shape[0] == 1:
@@ -208,14 +265,20 @@ class AttentionPairBias(_Switchable):
                                                   self.proj_z[1].weight, scale=BiasPlanes.LOG2E))
         return self.proj_z[1](self.proj_z[0](z)).permute(0, 3, 1, 2)
 
-    def _fused_forward(self, s: torch.Tensor, planes: "BiasPlanes", out_gate=None, out_residual=None) -> torch.Tensor:
+    def _fused_forward(self, s: torch.Tensor, planes: "BiasPlanes", out_gate=None, out_residual=None,
+                       mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         from ..ops import pair
+        km = None
+        if mask is not None:
+            km = _cached_key_mask(self._workspace, mask if mask.shape[0] == s.shape[0] else
+                                  mask.expand(s.shape[0], -1) if mask.shape[0] == 1 else
+                                  mask.repeat_interleave(s.shape[0] // mask.shape[0], 0))
         if self._packed is None:
             self._packed = pair.ApbPacked.pack(self.proj_q.weight, self.proj_q.bias, self.proj_k.weight,
                                                self.proj_v.weight, self.proj_g.weight, self.proj_o.weight,
                                                self.heads)
         return pair.apb_fused(s.to(torch.bfloat16).contiguous(), self._packed, planes.view, planes.ld,
-                              out_gate=out_gate, out_residual=out_residual)
+                              out_gate=out_gate, out_residual=out_residual, mask=km)
 
     def forward(self, s: torch.Tensor, z: Optional[torch.Tensor], mask: Optional[torch.Tensor],
                 bias: Optional[torch.Tensor] = None, k_in: Optional[torch.Tensor] = None,
@@ -225,9 +288,14 @@ class AttentionPairBias(_Switchable):
         kin = s if k_in is None else k_in
         if bias is None:
             bias = self.pair_bias(z)
+        if self.impl == "fused":
+            why = ("not_cuda" if not s.is_cuda else None) or ("cross_keys" if k_in is not None else None) \
+                or (None if isinstance(bias, BiasPlanes) else "dense_bias") \
+                or (f"head_dim_{self.head_dim}" if self.head_dim > 64 else None)
+            Dp = 32 if self.head_dim <= 32 else 64
+            if self._decide(why, f"D{Dp}H{self.heads}S{B}", N, {"head_dim": Dp, "dtype": "bf16"}):
+                return self._fused_forward(s, bias, mask=mask).to(s.dtype)
         if isinstance(bias, BiasPlanes):
-            if self.impl == "fused" and mask is None and k_in is None and s.is_cuda:
-                return self._fused_forward(s, bias).to(s.dtype)
             bias = bias.dense()
         H, D = self.heads, self.head_dim
         q = self.proj_q(s).view(B, N, H, D).transpose(1, 2)

@@ -28,18 +28,20 @@ namespace ubm {
 
 constexpr int kATile = 128;  // queries per CTA
 constexpr float kNegBig = -1.0e30f;
-#ifndef UBM_ATTN_POLY_EXP
-#define UBM_ATTN_POLY_EXP 1
-#endif
-constexpr bool kPolyExp = UBM_ATTN_POLY_EXP != 0;   // a quarter of the softmax exponentials as a polynomial
 
 // D = head dimension (32 or 64), TK = keys per step (128 for D = 32, 64 for D = 64 so that two rows,
 // two stages and the P tiles still fit in shared memory).
 // R2 = rows per CTA (softmax warpgroups sharing each bias tile): 2, or 4 with TK = 64 - four warps per
 // scheduler hide the TMEM-load -> bias -> max -> exp latency chain that two cannot.
 // TP = the probability tile stays in tensor memory (the P.V product takes its A operand from TMEM) and the pair
-// bias is added by the tensor cores (S = I . bias^T + Q K^T with an identity A operand in TMEM): the softmax
+// bias is added by the tensor cores: S = bias . I + Q K^T, where the bias tile [128 q][TK keys] is the K-major A
+// operand as TMA delivered it and I is a TK x TK identity in shared memory.  The contraction runs over the TK keys
+// of the step, so a 64-key step costs four MMAs (an identity on the query side would cost eight).  The softmax
 // threads then neither read the bias from shared memory nor write P to it.
+// POLY = how many of every four exponentials run as a polynomial on the FMA pipe instead of the special-function
+// unit (0 or 1).  Measured and dropped at 1536 tokens, four heads of 32: two of four with packed two-wide fp32
+// instructions (5.31 ms against 4.84), exponentials on fp16 or bf16 pairs with two per special-function
+// instruction (5.9 ms), three rows per CTA (5.13 ms).
 template <int D, int TK, int R2, bool TP = false>
 struct AttnCfg {
   static constexpr int kQBytes = kATile * D * 2;
@@ -52,22 +54,20 @@ struct AttnCfg {
   static constexpr int kPSmem = TP ? 0 : R2 * kPBytes;
   // tensor memory map (512 columns): S[r] at r*TK, O[r] at 256 + r*D, then (TP) P[r] and the identity
   static constexpr int kTmemP = 256 + R2 * D;             // P[r] at kTmemP + r * TK / 2 (two bf16 per column)
-  static constexpr int kTmemI = kTmemP + R2 * TK / 2;     // identity: 64 columns (128 x 128 bf16)
-  // With four rows per CTA the identity operand of the bias MMA does not fit in tensor memory any more
-  // (S 256 + O 128 + P 128 columns): it lives in shared memory (32 KB, K-major, 128-byte swizzle) and the bias
-  // MMA is the shared-memory form.
-  static constexpr bool kIdentSmem = TP && (kTmemI + 64 > 512);
-  static constexpr int kIdentBytes = kIdentSmem ? kATile * kATile * 2 : 0;
+  // identity B operand of the bias MMA: TK/64 k-blocks of [TK rows][64 k] bf16, K-major, 128-byte swizzle
+  static constexpr int kIdentBlock = TK * 128;
+  static constexpr int kIdentBytes = TP ? TK * TK * 2 : 0;
   static constexpr int kStages = (224 * 1024 - R2 * kQBytes - kPSmem - kIdentBytes) / kStageBytes;
   static_assert(kStages >= 2 && kStages <= 8, "stage count");
   static constexpr int kSmemBytes = R2 * kQBytes + kStages * kStageBytes + kPSmem + kIdentBytes + 512 + 1024;
-  static_assert(!TP || (R2 * TK <= 256 && (kIdentSmem ? kTmemI : kTmemI + 64) <= 512), "tensor memory budget");
+  static_assert(!TP || (R2 * TK <= 256 && kTmemP + R2 * TK / 2 <= 512), "tensor memory budget");
   static constexpr int kThreads = 128 + R2 * 128;
   // setmaxnreg moves registers inside the pool the CTA was launched with (threads x compiled registers):
-  //   R2 = 2: 384 x 168 = 64512 = 128 x 56 + 256 x 224;   R2 = 4: 640 x 96 = 61440 >= 128 x 56 + 512 x 104.
+  //   R2 = 2: 384 x 168 = 64512 = 128 x 56 + 256 x 224;   R2 = 3: 512 x 128 = 65536 = 128 x 56 + 384 x 152;
+  //   R2 = 4: 640 x 96 = 61440 >= 128 x 56 + 512 x 104.
   // An increase that does not fit that pool would wait forever, so these pairs are checked below.
-  static constexpr int kLaunchRegs = (R2 == 2) ? 168 : 96;
-  static constexpr int kSoftmaxRegs = (R2 == 2) ? 224 : 104;
+  static constexpr int kLaunchRegs = (R2 == 2) ? 168 : (R2 == 3) ? 128 : 96;
+  static constexpr int kSoftmaxRegs = (R2 == 2) ? 224 : (R2 == 3) ? 152 : 104;
   static_assert(128 * 56 + R2 * 128 * kSoftmaxRegs <= kThreads * kLaunchRegs, "setmaxnreg budget");
   static constexpr uint64_t kSwz = (D == 32) ? kSwizzle64 : kSwizzle128;  // operand rows are D * 2 bytes
   static constexpr uint32_t kSbo = (D == 32) ? 512 : 1024;               // 8 rows of D * 2 bytes
@@ -81,6 +81,11 @@ struct AttnParams {
   __nv_bfloat16* out;         // [rows][Nq][H*32], or transposed [Nq][rows][H*32]
   int transpose_out;
   int has_bias;
+  // key mask: additive bf16 rows [rows][ld_mask] (0 = keep, -1e30 = masked) and one flag byte per (row, key step)
+  // that is non-zero when the step holds a masked key; steps with a zero flag run the mask-free loop
+  const __nv_bfloat16* kmask;
+  const uint8_t* kflags;
+  long long ld_mask;
   KernelStatus* status;
   int n_qt, n_kt, n_rp, num_items;
   // peer mode: the bias rows (queries) are row shards owned by several GPUs; query tiles are enumerated
@@ -128,7 +133,7 @@ __device__ long long g_attn_timeline[3 * kTlTiles * 8];
 #define ATT_STAMP(role, tile, ev) do { } while (0)
 #endif
 
-template <int D, int TK, int R2, bool PEER, bool TP>
+template <int D, int TK, int R2, bool PEER, bool TP, int POLY>
 __global__ void __launch_bounds__(128 + R2 * 128, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmB,
@@ -193,14 +198,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tS = tmem_base;         // S[r] at r * TK
   const uint32_t tO = tmem_base + 256;   // O[r] at r * D
   const uint32_t tP = tmem_base + Cfg::kTmemP;
-  const uint32_t tI = tmem_base + Cfg::kTmemI;
   const int T = p.n_kt;
-  if (TP && Cfg::kIdentSmem) {
-    // identity A operand in shared memory: two k-blocks of [128 rows][64 k], row q has a one at k = q
-    for (int i = threadIdx.x; i < kATile * 16; i += blockDim.x) {
-      const int row = i >> 4, c16 = i & 15;
+  if (TP) {
+    // identity B operand in shared memory: TK/64 k-blocks of [TK rows][64 k], row n has a one at k = n
+    constexpr int kChunks = TK / 8;   // 16-byte chunks per row
+    for (int i = threadIdx.x; i < TK * kChunks; i += blockDim.x) {
+      const int row = i / kChunks, cc = i % kChunks;
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if ((row >> 3) == c16) {
+      if ((row >> 3) == cc) {
         const uint32_t one = (row & 1) ? 0x3F800000u : 0x00003F80u;
         const int w = (row & 7) >> 1;
         v.x = w == 0 ? one : 0u;
@@ -208,29 +213,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         v.z = w == 2 ? one : 0u;
         v.w = w == 3 ? one : 0u;
       }
-      *reinterpret_cast<uint4*>(sIdent + (c16 >> 3) * 16384 + swz128_offset(row, c16 & 7)) = v;
+      *reinterpret_cast<uint4*>(sIdent + (cc >> 3) * Cfg::kIdentBlock + swz128_offset(row, cc & 7)) = v;
     }
     fence_proxy_async_smem();
     __syncthreads();
-  } else if (TP) {
-    // identity A operand: lane q holds 128 bf16, element q is 1.0 (two bf16 per 32-bit column)
-    if (warp >= 4 && warp < 8) {
-      const int qrow0 = (warp & 3) * 32 + lane;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t iv[32];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int col = half * 32 + c;
-          iv[c] = (col == (qrow0 >> 1)) ? ((qrow0 & 1) ? 0x3F800000u : 0x00003F80u) : 0u;
-        }
-        tmem_st32(tmem_addr(tI, warp & 3, half * 32), iv);
-      }
-      tmem_st_wait();
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
   }
 
   // Register split: warps 0-3 (producer, MMA issuer, two idle warps) give registers up, the softmax
@@ -286,8 +272,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // The whole warp runs the loop with warp-uniform operands; one elected lane issues the tcgen05 instructions.
     const bool leader = elect_one();
     if (warp <= 2) {
-      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, TK, 0, 0);
-      constexpr uint32_t idesc_bias = umma_idesc_bf16(128, TK, 0, 1);  // B = bias tile, keys contiguous (MN-major)
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, TK, 0, 0);   // also the bias MMA: A = bias tile, B = identity
       const int r_first = warp - 1;
       uint32_t item_cnt = 0, gk = 0;
       auto issue_qk = [&](int r, uint32_t g) {
@@ -295,23 +280,19 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t qa = smem_u32(sQ + r * kAQBytes);
         const uint32_t ka = st + r * 2 * kAKVBytes;
         const bool with_bias = TP && p.has_bias;
-        const uint64_t bd0 = umma_smem_desc(st + 2 * R2 * kAKVBytes, 16384, 1024, kSwizzle128);
+        const uint64_t bd0 = umma_smem_desc(st + 2 * R2 * kAKVBytes, 16, 1024, kSwizzle128);
         const uint64_t ad0 = umma_smem_desc(qa, 16, Cfg::kSbo, Cfg::kSwz);
         const uint64_t kd0 = umma_smem_desc(ka, 16, Cfg::kSbo, Cfg::kSwz);
         const uint64_t id0 = umma_smem_desc(smem_u32(sIdent), 16, 1024, kSwizzle128);
         if (leader) {
           if (with_bias) {
-            // S = I . bias^T: the 128 x TK bias tile sits in shared memory as TK/64 boxes of [128 q][64 k]
+            // S = bias . I: the 128 x TK bias tile sits in shared memory as TK/64 boxes of [128 q][64 k] (K-major A),
+            // the identity as TK/64 blocks of [TK n][64 k] (K-major B); 16 keys per MMA
 #pragma unroll
-            for (int k = 0; k < kATile / 16; ++k) {
-              if (Cfg::kIdentSmem) {
-                umma_ss(tS + r * TK, id0 + static_cast<uint64_t>((k >> 2) * (16384 >> 4) + (k & 3) * 2),
-                        bd0 + static_cast<uint64_t>(k * (2048 >> 4)), idesc_bias, k != 0 ? 1u : 0u);
-              } else {
-                umma_ts(tS + r * TK, tI + k * 8, bd0 + static_cast<uint64_t>(k * (2048 >> 4)), idesc_bias,
-                        k != 0 ? 1u : 0u);
-              }
-            }
+            for (int k = 0; k < TK / 16; ++k)
+              umma_ss(tS + r * TK, bd0 + static_cast<uint64_t>((k >> 2) * (16384 >> 4) + (k & 3) * 2),
+                      id0 + static_cast<uint64_t>((k >> 2) * (Cfg::kIdentBlock >> 4) + (k & 3) * 2), idesc_qk,
+                      k != 0 ? 1u : 0u);
           }
 #pragma unroll
           for (int k = 0; k < kAD / 16; ++k)
@@ -389,6 +370,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   } else {
     if (R2 == 2) {
       asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    } else if (R2 == 3) {
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
     } else {
       asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     }
@@ -409,6 +392,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       float m = kNegBig, l = 0.f;
       for (int j = 0; j < T; ++j) {
         const uint32_t g = gk + j;
+        // flag of this (row, key step), fetched ahead of the wait for the score tile
+        const uint32_t mflag = (p.kflags != nullptr && r < p.rows) ? p.kflags[static_cast<long long>(r) * T + j] : 0u;
         mbar_wait(&s_full[r_in], g & 1u, ws, 59, r_in);
         if (quad == 0 && lane == 0) ATT_STAMP(1 + r_in, g, 0);
         tc_fence_after_sync();
@@ -444,6 +429,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           __syncwarp();
           if (lane == 0) mbar_arrive(&kv_empty[g % kAStages]);
         }
+        if (mflag != 0u) {
+          // masked keys in this step: every thread adds the same TK mask values (one broadcast 16-byte load per 8 keys)
+          const uint4* mp = reinterpret_cast<const uint4*>(p.kmask + static_cast<long long>(r) * p.ld_mask + j * TK);
+#pragma unroll
+          for (int c16 = 0; c16 < TK / 8; ++c16) {
+            const uint4 u = __ldg(mp + c16);
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              t[c16 * 8 + 2 * e] += bf16_lo(w[e]);
+              t[c16 * 8 + 2 * e + 1] += bf16_hi(w[e]);
+            }
+          }
+        }
         if (j == T - 1) {
           const int valid = p.Nk - j * TK;
           if (valid < TK) {
@@ -478,7 +477,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           e01.x = fast_exp2(d01.x);
           e01.y = fast_exp2(d01.y);
           e23.x = fast_exp2(d23.x);
-          e23.y = (kPolyExp && D == 64) ? poly_exp2(d23.y) : fast_exp2(d23.y);
+          e23.y = (POLY == 1) ? poly_exp2(d23.y) : fast_exp2(d23.y);
           ps01 = __fadd2_rn(ps01, e01);
           ps23 = __fadd2_rn(ps23, e23);
           pk[k >> 1] = pack_bf16x2(e01.x, e01.y);
@@ -572,16 +571,23 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-template <int D, int TK, int R2, bool TP = false>
+struct AttnMask {
+  const void* kmask = nullptr;   // bf16 [rows][ld_mask], additive (0 / -1e30)
+  const void* kflags = nullptr;  // uint8 [rows][ceil(Nk / TK)]
+  long long ld_mask = 0;
+};
+
+template <int D, int TK, int R2, bool TP, int POLY, bool PEER>
 static int launch_attention(const void* q, const void* k, const void* v, const void* bias, const void* gate, void* out,
                             int rows, int Nq, int Nk, int H, long long ldb, long long ld_in, long long ld_gate,
-                            int transpose_out,
+                            int transpose_out, AttnMask mask,
                             void* status, void* stream, int npeers = 0, const void* const* bias_ptrs = nullptr,
                             const int* peer_rows = nullptr, long long peer_head_stride = 0) {
   using Cfg = AttnCfg<D, TK, R2, TP>;
   const uint64_t hd = (uint64_t)H * D;
   const uint64_t ldi = ld_in > 0 ? (uint64_t)ld_in : hd;  // row stride of q / k / v in elements
   if (ldi < hd || (ldi & 7)) return UBM_ERR_ARGUMENT;
+  if (PEER != (npeers > 0)) return UBM_ERR_ARGUMENT;
   const CUtensorMapSwizzle swz = (D == 32) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
   CUtensorMap tmQ, tmK, tmV, tmB;
   {
@@ -623,9 +629,18 @@ static int launch_attention(const void* q, const void* k, const void* v, const v
   p.n_qt = (Nq + kATile - 1) / kATile;
   p.n_kt = (Nk + TK - 1) / TK;
   p.n_rp = (rows + R2 - 1) / R2;
+  if (mask.kmask != nullptr) {
+    // the mask rows are read in whole key steps with 16-byte loads
+    if (mask.kflags == nullptr || mask.ld_mask < (long long)p.n_kt * TK || (mask.ld_mask & 7) ||
+        (reinterpret_cast<uintptr_t>(mask.kmask) & 15))
+      return UBM_ERR_ARGUMENT;
+    p.kmask = static_cast<const __nv_bfloat16*>(mask.kmask);
+    p.kflags = static_cast<const uint8_t*>(mask.kflags);
+    p.ld_mask = mask.ld_mask;
+  }
   BiasPeerMaps maps;
   for (int i = 0; i < kAMaxPeers; ++i) maps.m[i] = tmQ;
-  if (npeers > 0) {
+  if (PEER) {
     if (npeers > kAMaxPeers || bias_ptrs == nullptr || peer_rows == nullptr) return UBM_ERR_ARGUMENT;
     p.npeers = npeers;
     p.has_bias = 1;
@@ -651,27 +666,19 @@ static int launch_attention(const void* q, const void* k, const void* v, const v
   }
   p.num_items = p.n_qt * p.n_rp * H;
   const int grid = p.num_items < sm_count() ? p.num_items : sm_count();
+  auto kern = attention_kernel<D, TK, R2, PEER, TP, POLY>;
   {
     // the in-kernel register re-split must fit the pool this build was compiled with, or it would never return
     cudaFuncAttributes fa;
-    cudaError_t e = npeers > 0 ? cudaFuncGetAttributes(&fa, attention_kernel<D, TK, R2, true, TP>)
-                               : cudaFuncGetAttributes(&fa, attention_kernel<D, TK, R2, false, TP>);
+    cudaError_t e = cudaFuncGetAttributes(&fa, kern);
     if (e != cudaSuccess || 128 * 56 + R2 * 128 * Cfg::kSoftmaxRegs > Cfg::kThreads * fa.numRegs) {
       fprintf(stderr, "[ubm] attention: register budget check failed (numRegs=%d)\n", e == cudaSuccess ? fa.numRegs : -1);
       return UBM_ERR_LAUNCH;
     }
   }
-  if (npeers > 0) {
-    auto kern = attention_kernel<D, TK, R2, true, TP>;
-    int rc = set_smem(kern, Cfg::kSmemBytes);
-    if (rc) return rc;
-    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmB, maps, p);
-  } else {
-    auto kern = attention_kernel<D, TK, R2, false, TP>;
-    int rc = set_smem(kern, Cfg::kSmemBytes);
-    if (rc) return rc;
-    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmB, maps, p);
-  }
+  int rc = set_smem(kern, Cfg::kSmemBytes);
+  if (rc) return rc;
+  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, tmB, maps, p);
   UBM_CHECK_LAUNCH("attention_kernel");
   return UBM_OK;
 }
@@ -685,54 +692,65 @@ extern "C" int ubm_attention_read_timeline(long long* host_out) {
 }
 #endif
 
+// Low nibble: tile shape for head dimension 32 - 0 = by row count (four rows per CTA with 64-key steps from four
+// rows on, else two rows with 64-key steps), 5 = two rows per CTA with 128-key steps, 1 = two rows, 128-key steps,
+// P and bias through shared memory.  Bits 4-5: 0 = one exponential in four runs as a polynomial on the FMA pipe
+// (four-row form and head dimension 64), 1 = none does.
 extern "C" int ubm_attention_set_variant(int v) {
-  g_attn_variant = v & 0xff;  // 0 = P and bias through tensor memory; 1 = P and bias through shared memory;
-                              // 2 = four rows per CTA; 3 = 64-key steps; 4 = four rows per CTA with P in
-                              // tensor memory (one bias tile per four rows: less L2 traffic per row; the
-                              // default for rows >= 4); 5 = two rows per CTA with P in tensor memory
+  g_attn_variant = v & 0xff;
   return 0;
 }
+
+#define UBM_ATTN_ARGS q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, ld_gate, transpose_out, m, status, stream
 
 // q, k, v, gate, out: bf16 [rows][N*][H*D] (innermost contiguous).  bias: bf16 [H][Nq][ldb] (ldb multiple
 // of 8) or null.  q must carry the factor log2(e)/sqrt(d) and bias the factor log2(e).  transpose_out
 // writes out[q][r] instead of out[r][q].  ld_in: row stride of q / k / v in elements (0 = H*D), so the
 // three may be column slices of one projection output; ld_gate: row stride of the gate (0 = H*D; a multiple of
-// 16 elements), so the gate may be a column slice of the same output.  D = 32 (ubm_attention_d32) or 64
+// 16 elements), so the gate may be a column slice of the same output.  kmask / kflags / ld_mask: optional key
+// mask per row (see AttnParams; flags are per 64-key step); null = no mask.  D = 32 (ubm_attention_d32) or 64
 // (ubm_attention_d64).
 extern "C" int ubm_attention_d32(const void* q, const void* k, const void* v, const void* bias, const void* gate,
-                                 void* out, int rows, int Nq, int Nk, int H, long long ldb, long long ld_in,
-                                 long long ld_gate, int transpose_out, void* status, void* stream) {
+                                 void* out, const void* kmask, const void* kflags, int rows, int Nq, int Nk, int H,
+                                 long long ldb, long long ld_in, long long ld_gate, long long ld_mask,
+                                 int transpose_out, void* status, void* stream) {
   if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0 || (ld_gate & 15)) return ubm::UBM_ERR_ARGUMENT;
   if (bias != nullptr && (ldb < Nk || (ldb & 7))) return ubm::UBM_ERR_ARGUMENT;
-  // default (variant 0): four rows per CTA once there are enough rows to fill the groups - one bias tile per four
-  // rows instead of two cuts the L2 traffic per row by a quarter (measured 5.31 -> 4.98 ms at N = 1536);
-  // variant 5 forces the two-row form
-  if ((g_attn_variant == 0 || g_attn_variant == 4) && rows >= 4)
-    return ubm::launch_attention<32, 64, 4, true>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, ld_gate,
-                                                  transpose_out, status, stream);
-  if (g_attn_variant == 2 && rows >= 3)
-    return ubm::launch_attention<32, 64, 4>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, ld_gate, transpose_out,
-                                            status, stream);
-  if (g_attn_variant == 3)
-    return ubm::launch_attention<32, 64, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, ld_gate, transpose_out,
-                                            status, stream);
-  if (g_attn_variant == 1)
-    return ubm::launch_attention<32, 128, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, ld_gate, transpose_out,
-                                             status, stream);
-  return ubm::launch_attention<32, 128, 2, true>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, ld_gate,
-                                                 transpose_out, status, stream);
+  ubm::AttnMask m;
+  m.kmask = kmask;
+  m.kflags = kflags;
+  m.ld_mask = ld_mask;
+  const int shape = g_attn_variant & 15, poly = (g_attn_variant >> 4) & 3;
+  if (shape == 1) {
+    if (kmask != nullptr) return ubm::UBM_ERR_ARGUMENT;   // flags are per 64-key step
+    return ubm::launch_attention<32, 128, 2, false, 0, false>(UBM_ATTN_ARGS);
+  }
+  if (shape == 5) {
+    if (kmask != nullptr) return ubm::UBM_ERR_ARGUMENT;
+    return ubm::launch_attention<32, 128, 2, true, 0, false>(UBM_ATTN_ARGS);
+  }
+  if (rows >= 4) {
+    // four rows per CTA: one bias tile per four rows keeps the L2 traffic per row low; one exponential in four as a
+    // polynomial (4.84 against 5.00 ms at 1536 tokens; two in four cost more issue slots than they free: 5.31 ms)
+    if (poly == 1) return ubm::launch_attention<32, 64, 4, true, 0, false>(UBM_ATTN_ARGS);
+    return ubm::launch_attention<32, 64, 4, true, 1, false>(UBM_ATTN_ARGS);
+  }
+  return ubm::launch_attention<32, 64, 2, true, 0, false>(UBM_ATTN_ARGS);
 }
 
 extern "C" int ubm_attention_d64(const void* q, const void* k, const void* v, const void* bias, const void* gate,
-                                 void* out, int rows, int Nq, int Nk, int H, long long ldb, long long ld_in,
-                                 long long ld_gate, int transpose_out, void* status, void* stream) {
+                                 void* out, const void* kmask, const void* kflags, int rows, int Nq, int Nk, int H,
+                                 long long ldb, long long ld_in, long long ld_gate, long long ld_mask,
+                                 int transpose_out, void* status, void* stream) {
   if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0 || (ld_gate & 15)) return ubm::UBM_ERR_ARGUMENT;
   if (bias != nullptr && (ldb < Nk || (ldb & 7))) return ubm::UBM_ERR_ARGUMENT;
-  if (g_attn_variant == 1)
-    return ubm::launch_attention<64, 64, 2>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, ld_gate, transpose_out,
-                                            status, stream);
-  return ubm::launch_attention<64, 64, 2, true>(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb, ld_in, ld_gate, transpose_out,
-                                                status, stream);
+  ubm::AttnMask m;
+  m.kmask = kmask;
+  m.kflags = kflags;
+  m.ld_mask = ld_mask;
+  const int poly = (g_attn_variant >> 4) & 3;
+  if (poly == 1) return ubm::launch_attention<64, 64, 2, true, 0, false>(UBM_ATTN_ARGS);
+  return ubm::launch_attention<64, 64, 2, true, 1, false>(UBM_ATTN_ARGS);
 }
 
 // Pair-bias all-gather fused into the attention kernel (head dimension 32): the bias planes are row
@@ -746,6 +764,7 @@ extern "C" int ubm_attention_d32_peer_bias(const void* q, const void* k, const v
                                            long long ld_in, void* status, void* stream) {
   if (rows <= 0 || Nq <= 0 || Nk <= 0 || H <= 0 || npeers <= 0) return ubm::UBM_ERR_ARGUMENT;
   if (ldb < Nk || (ldb & 7) || (peer_head_stride & 7)) return ubm::UBM_ERR_ARGUMENT;
-  return ubm::launch_attention<32, 128, 2>(q, k, v, nullptr, gate, out, rows, Nq, Nk, H, ldb, ld_in, 0, 0, status,
-                                           stream, npeers, bias_ptrs, peer_rows, peer_head_stride);
+  return ubm::launch_attention<32, 128, 2, false, 0, true>(q, k, v, nullptr, gate, out, rows, Nq, Nk, H, ldb, ld_in, 0, 0,
+                                                           ubm::AttnMask{}, status, stream, npeers, bias_ptrs, peer_rows,
+                                                           peer_head_stride);
 }

@@ -147,8 +147,9 @@ def trimul_fused(z: torch.Tensor, mask: Optional[torch.Tensor], w: TrimulPacked,
 
 
 # ------------------------------------------------------------------------------------------
-native.declare("ubm_attention_d32", [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_void_p, c_void_p])
-native.declare("ubm_attention_d64", [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_void_p, c_void_p])
+_ATTN_SIG = [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_int, c_void_p, c_void_p]
+native.declare("ubm_attention_d32", _ATTN_SIG)
+native.declare("ubm_attention_d64", _ATTN_SIG)
 
 native.declare("ubm_attention_set_variant", [c_int])
 
@@ -156,9 +157,37 @@ LOG2E = 1.4426950408889634
 
 
 def set_attention_variant(v: int) -> None:
-    """0 = choose by shape (four rows per CTA with 64-key steps when there are at least three rows),
-    1 = always two rows per CTA with 128-key steps."""
+    """Low nibble, head dimension 32: 0 = choose by row count (four rows per CTA from four rows on), 5 = two rows
+    with 128-key steps, 1 = two rows, P and bias through shared memory.  Bits 4-5: 0 = one exponential in four as a
+    polynomial on the FMA pipe, 1 = all on the special-function unit."""
     native.lib().ubm_attention_set_variant(int(v))
+
+
+MASK_STEP = 64          # the kernel's flags are per 64-key step
+MASK_NEG = -1.0e30
+
+
+@dataclass
+class KeyMask:
+    """A key mask laid out for the attention kernel: additive bf16 rows (0 keeps, -1e30 masks) padded to whole
+    64-key steps, and one flag byte per (row, step) that is set when the step holds a masked key, so that rows and
+    steps without masked keys run the mask-free loop (the reference skips the mask the same way for unmasked row
+    groups: common/opt_core/opt_core/kernels/flash_triattn.py:35-37)."""
+    add: torch.Tensor        # bf16 [rows, ld]
+    flags: torch.Tensor      # uint8 [rows, ld / 64]
+
+    @classmethod
+    def pack(cls, keep: torch.Tensor) -> Optional["KeyMask"]:
+        """keep: [rows, Nk], non-zero = attend.  Returns None when nothing is masked (one host read)."""
+        keep = keep != 0
+        if bool(keep.all()):
+            return None
+        rows, nk = keep.shape
+        ld = ceil_to(nk, MASK_STEP)
+        add = torch.zeros((rows, ld), dtype=torch.bfloat16, device=keep.device)
+        add[:, :nk].masked_fill_(~keep, MASK_NEG)
+        flags = (add.view(rows, ld // MASK_STEP, MASK_STEP) != 0).any(-1).to(torch.uint8).contiguous()
+        return cls(add, flags)
 
 
 @dataclass
@@ -198,23 +227,27 @@ class TriattPacked:
 
 
 def attention(q, k, v, bias, gate, out, rows: int, Nq: int, Nk: int, H: int, D: int = 32, ldb: int = 0,
-              ld_in: int = 0, transpose_out: bool = False, ld_gate: int = 0):
+              ld_in: int = 0, transpose_out: bool = False, ld_gate: int = 0, mask: Optional[KeyMask] = None):
     """Raw launch of the tcgen05 attention kernel (see csrc/attention_sm100.cu for the layout).
     D is the (padded) head dimension, 32 or 64; ld_in the row stride of q / k / v in elements, ld_gate that of
-    the gate (0 = H * D)."""
+    the gate (0 = H * D); mask a :class:`KeyMask` over [rows, Nk] or None."""
     st = native.status_tensor(q.device)
     fn = native.lib().ubm_attention_d32 if D == 32 else native.lib().ubm_attention_d64
     if D not in (32, 64):
         raise ValueError("attention kernel supports head dimensions 32 and 64 (pad smaller heads)")
-    rc = fn(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(bias), native.ptr(gate), native.ptr(out), rows,
-            Nq, Nk, H, ldb, ld_in, ld_gate, 1 if transpose_out else 0, native.ptr(st),
-            native.current_stream(q.device))
+    if mask is not None and (mask.add.shape[0] != rows or mask.add.shape[1] < Nk):
+        raise ValueError(f"key mask of shape {tuple(mask.add.shape)} does not cover [{rows}, {Nk}]")
+    rc = fn(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(bias), native.ptr(gate), native.ptr(out),
+            native.ptr(None if mask is None else mask.add), native.ptr(None if mask is None else mask.flags), rows,
+            Nq, Nk, H, ldb, ld_in, ld_gate, 0 if mask is None else mask.add.stride(0), 1 if transpose_out else 0,
+            native.ptr(st), native.current_stream(q.device))
     native.check(rc, f"ubm_attention_d{D}")
     return out
 
 
-def attention_d32(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb: int = 0, transpose_out: bool = False):
-    return attention(q, k, v, bias, gate, out, rows, Nq, Nk, H, 32, ldb, 0, transpose_out)
+def attention_d32(q, k, v, bias, gate, out, rows, Nq, Nk, H, ldb: int = 0, transpose_out: bool = False,
+                  mask: Optional[KeyMask] = None):
+    return attention(q, k, v, bias, gate, out, rows, Nq, Nk, H, 32, ldb, 0, transpose_out, mask=mask)
 
 
 @dataclass
@@ -259,9 +292,11 @@ class ApbPacked:
 
 
 def apb_fused(x: torch.Tensor, w: ApbPacked, bias_planes: torch.Tensor, ldb: int,
-              out_gate: Optional[torch.Tensor] = None, out_residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+              out_gate: Optional[torch.Tensor] = None, out_residual: Optional[torch.Tensor] = None,
+              mask: Optional[KeyMask] = None) -> torch.Tensor:
     """Gated attention with pair bias on rows x: bf16 [B, N, c]; bias_planes: bf16 [H, N, ldb] holding
-    log2(e) * bias (shared by the B rows).  Returns proj_o(sigmoid(proj_g x) * attention) as [B, N, c];
+    log2(e) * bias (shared by the B rows); mask: key mask over [B, N] or None.
+    Returns proj_o(sigmoid(proj_g x) * attention) as [B, N, c];
     with ``out_gate`` ([N, c], shared by the B rows) and ``out_residual`` ([B*N, c]) the output projection's
     epilogue returns residual + gate * projection."""
     B, N, c = x.shape
@@ -272,15 +307,17 @@ def apb_fused(x: torch.Tensor, w: ApbPacked, bias_planes: torch.Tensor, ldb: int
     qkvg = _gemm.gemm(x2, w.wqkvg, bias=w.bqkvg, act="sigmoid", act_from=3 * HD)
     o = torch.empty((B * N, HD), dtype=torch.bfloat16, device=x.device)
     attention(qkvg[:, :HD], qkvg[:, HD:2 * HD], qkvg[:, 2 * HD:3 * HD], bias_planes, qkvg[:, 3 * HD:], o, rows=B,
-              Nq=N, Nk=N, H=w.H, D=w.Dp, ldb=ldb, ld_in=4 * HD, ld_gate=4 * HD)
+              Nq=N, Nk=N, H=w.H, D=w.Dp, ldb=ldb, ld_in=4 * HD, ld_gate=4 * HD, mask=mask)
     return _gemm.gemm(o, w.wo, gate=out_gate, residual=out_residual).view(B, N, -1)
 
 
 def triangle_attention_fused(z: torch.Tensor, w: TriattPacked, starting: bool, residual: bool = True,
-                             out: Optional[torch.Tensor] = None, workspace: Optional[dict] = None) -> torch.Tensor:
-    """z: bf16 [N, N, 128] contiguous (no padding mask).  Three launches: projection (LN folded,
-    q|k|v|gate rows + head bias planes, written at the transposed pair index for the ending
-    node) -> attention -> output projection with residual."""
+                             out: Optional[torch.Tensor] = None, workspace: Optional[dict] = None,
+                             mask: Optional[KeyMask] = None) -> torch.Tensor:
+    """z: bf16 [N, N, 128] contiguous; mask: key mask over [attention row, key] (for the ending node the
+    attention rows are the columns of z, so the caller packs the transposed pair mask).  Three launches:
+    projection (LN folded, q|k|v|gate rows + head bias planes, written at the transposed pair index for the
+    ending node) -> attention -> output projection with residual."""
     if z.dtype != torch.bfloat16 or z.dim() != 3 or z.shape[-1] != 128 or not z.is_contiguous():
         raise ValueError("triangle_attention_fused expects a contiguous bf16 [N, N, 128] tensor")
     N = z.shape[0]
@@ -300,7 +337,7 @@ def triangle_attention_fused(z: torch.Tensor, w: TriattPacked, starting: bool, r
                                       native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(g), native.ptr(hb), 0,
                                       N, Np, w.heads, 0 if starting else 1, native.ptr(st), stream)
     native.check(rc, "ubm_triatt_proj")
-    attention_d32(q, k, v, hb, g, og, rows=N, Nq=N, Nk=N, H=w.heads, ldb=Np, transpose_out=not starting)
+    attention_d32(q, k, v, hb, g, og, rows=N, Nq=N, Nk=N, H=w.heads, ldb=Np, transpose_out=not starting, mask=mask)
     z2 = z.view(N * N, 128)
     out = torch.empty_like(z) if out is None else out
     _gemm.gemm(og, w.wo, bias=w.bo, residual=z2 if residual else None, out=out.view(N * N, 128))
