@@ -34,7 +34,7 @@ def test_registry_covers_the_reference_kits():
 def test_dry_run_lines_with_fake_gpu(capsys):
     act = base.Activation(registry.get("boltz2"), "fast", "cli", 1, probe=_b200(), environ={})
     act.apply(None, dry_run=True)
-    assert act.lines[0].startswith("[boltz2-opt] DRY-RUN mode=fast levers=hoist_pair_bias,")
+    assert act.lines[0].startswith("[boltz2-opt] DRY-RUN mode=fast levers=sampler_graph,graph_verify,fused_transition,")
     lever_lines = [l for l in act.lines if " LEVER " in l]
     assert any("name=fused_triatt state=on impl=pair_proj+attention_sm100@1 origin=core "
                "strategy=F1.kernel_fusion" in l for l in lever_lines)
@@ -98,3 +98,61 @@ def test_pred_off_on_cpu_writes_outputs_and_manifest(tmp_path):
     m = json.load(open(out / "opt_manifest.json"))
     assert m["mode"] == "off" and m["verdict"]["exit_code"] == 0
     assert (out / "prediction.pt").exists()
+
+
+def test_no_lever_is_a_no_op():
+    """Every lever of the table has an ``apply`` that changes the object it is given (or raises): a table of names
+    that do nothing cannot come back."""
+    import types
+    from uplifting_biomolecular_modeling_b200.kits import levers
+    used = {n for spec in registry.REGISTRY.values() for names in spec.levers.values() for n in names}
+    assert used <= set(levers.LEVERS), used - set(levers.LEVERS)
+    for name, lv in levers.LEVERS.items():
+        assert lv.apply is not None and lv.apply.__name__ != "_noop", name
+        if lv.needs_gpu or name == "expandable_segments":
+            continue                                  # these need a device (or the live allocator) to act on
+        obj = types.SimpleNamespace(model=types.SimpleNamespace(workspace={}), n_gpu=1)
+        before = dict(vars(obj))
+        ev = lv.apply(obj)
+        assert ev and (vars(obj) != before or obj.model.workspace), name
+
+
+def test_pred_refuses_unreadable_input_and_unknown_config(tmp_path):
+    r = _run(["kits/boltz2/run.sh", "pred", "--mode", "off", "--model_config", "tiny", "--input",
+              str(tmp_path / "missing.pt")])
+    assert r.returncode == 2 and "error=input" in r.stderr and "no_such_file" in r.stderr.replace(" ", "_")
+    r = _run(["kits/boltz2/run.sh", "pred", "--mode", "off", "--model_config", "nonesuch", "--tokens", "16"])
+    assert r.returncode == 2 and "unknown_model_config" in r.stderr
+    spec = tmp_path / "complex.json"
+    spec.write_text(json.dumps({"chains": [[12, "protein"], [8, "protein"]], "msa_depth": 2}))
+    out = tmp_path / "o"
+    r = _run(["kits/boltz2/run.sh", "pred", "--mode", "off", "--model_config", "tiny", "--input", str(spec),
+              "--out_dir", str(out)])
+    assert r.returncode == 0 and "tokens=20" in r.stderr, r.stderr[-1500:]
+
+
+def test_partial_checkpoint_is_not_active(tmp_path):
+    import torch
+    from uplifting_biomolecular_modeling_b200.models import cofold
+    m = cofold.build_model("tiny", seed=1)
+    sd = m.state_dict()
+    k0 = next(iter(sd))
+    torch.save({"state_dict": {k0: sd[k0]}}, tmp_path / "one.ckpt")
+    args = ["kits/boltz2/run.sh", "pred", "--mode", "off", "--model_config", "tiny", "--tokens", "16", "--msa_depth",
+            "2", "--checkpoint", str(tmp_path / "one.ckpt")]
+    r = _run(args)
+    assert r.returncode == 3 and "NOT ACTIVE" in r.stderr and "missing" in r.stderr
+    r = _run(args + ["--allow-partial", "--out_dir", str(tmp_path / "o")])
+    assert r.returncode == 0 and "[boltz2-opt] WEIGHTS" in r.stderr and "matched=1" in r.stderr
+    man = json.load(open(tmp_path / "o" / "opt_manifest.json"))
+    assert man["checkpoint"]["matched"] == 1 and man["checkpoint"]["missing"]
+
+
+def test_design_verb_runs_the_design_pipeline(tmp_path):
+    out = tmp_path / "d"
+    r = _run(["kits/boltzgen/run.sh", "design", "--mode", "off", "--model_config", "tiny", "--tokens", "24",
+              "--diffusion_samples", "2", "--out_dir", str(out)])
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "designs=2" in r.stderr and "verb=design" in r.stderr
+    d = json.load(open(out / "design.json"))
+    assert len(d["sequences_text"]) == 2 and len(d["sequences_text"][0]) == 24

@@ -6,8 +6,10 @@ One object owns a model on one GPU under one mode word:
 * ``exact`` - the same statements, with what is step-invariant hoisted and the sampler step replayed
               from a CUDA graph: bitwise identical to ``off`` by construction (same kernels, same order).
 * ``fast``  - the fused sm_100a kernels in the pair stack / MSA module / diffusion transformer, plus graphs.
-* ``big``   - ``fast`` plus the memory levers (row-chunked pair ops, released intermediates); with
-              ``n_gpu > 1`` the pair tensor is row-sharded over the ranks (``parallel.rowpair``).
+* ``big``   - ``fast`` plus the memory levers: triangle attention and the triangle-multiplication contraction run
+              per block of ``row_block`` rows (q|k|v|gate and the contracted planes exist for one block), the trunk's
+              scratch is released before the sampler; with ``n_gpu > 1`` the pair tensor is row-sharded over the
+              ranks (``parallel.rowpair``).
 
 ``predict`` takes a feature dict on the host (pinned memory is used for the copy), runs embed ->
 trunk -> sampler -> confidence, and returns host tensors.  It is the call the benchmarks time end to end.
@@ -74,10 +76,30 @@ class Predictor:
             n = self.model.set_impl("fused")
             self.levers.append(f"fused_kernels:{n}")
         self.use_graphs = (mode != "off" and self.device.type == "cuda") if use_graphs is None else use_graphs
+        self.verify_graphs = 1 if mode != "off" else 0      # first replay of a captured graph checked against eager
+        self.row_block = 0          # ``big``: pair operations of the kernel path in blocks of this many rows
+        self.release = False        # ``big``: trunk scratch returned to the allocator before the sampler
+        if mode == "big":
+            self.row_block = int(os.environ.get("UBM_BIG_ROW_BLOCK", "512"))
+            self.model.workspace["row_block"] = self.row_block
+            self.release = True
+        if mode in ("fast", "big"):
+            from .ops import dispatch
+            dispatch.set_tier(mode)
         self._graph = None
         self._graph_key = None
         self._pinned: Dict[str, torch.Tensor] = {}
         self.last_timing: Dict[str, float] = {}
+
+    def set_mode(self, mode: str) -> None:
+        """Change the mode word of a predictor built under ``off`` (the kit runner builds the plain model first and
+        lets the activation's levers switch implementations on one by one)."""
+        if mode not in MODES:
+            raise ValueError(f"mode {mode!r} not in {MODES}")
+        self.mode = mode
+        if mode in ("fast", "big"):
+            from .ops import dispatch
+            dispatch.set_tier(mode)
 
     # ------------------------------------------------------------------ provider decisions
     def provider_plan(self, n_tokens: int, n_atoms: Optional[int] = None) -> Dict[str, object]:
@@ -178,6 +200,21 @@ class Predictor:
                 native.add_launches(per_replay)
             return static_out
 
+        if self.verify_graphs:
+            # replay against the eager step on the same inputs and random state: bit for bit, or the graph is not used
+            # (reference: common/opt_core/opt_core/capture/graphs.py:569, ``verify >= 1``)
+            gen = torch.Generator(device=self.device).manual_seed(97)
+            x0 = torch.randn((samples, A, 3), device=self.device, generator=gen)
+            args = (x0, torch.tensor(1.5, device=self.device), torch.tensor(0.75, device=self.device),
+                    torch.tensor(0.0, device=self.device))
+            torch.cuda.manual_seed(4242)
+            got = fn(*args).clone()
+            torch.cuda.manual_seed(4242)
+            want = sm.step(*args, prep, a2t, n_tokens)
+            if not torch.equal(got, want):
+                worst = float((got - want).abs().max())
+                raise NotActive(f"sampler graph replay differs from the eager step (max abs {worst:.3e})")
+            self.graph_verified = getattr(self, "graph_verified", 0) + 1
         self._graph = {"graph": graph, "prep": prep, "a2t": a2t, "fn": fn}
         self._graph_key = key
         return fn
@@ -215,6 +252,13 @@ class Predictor:
             self._plan_key = N
             self.provider_plan(N, feats["ref_pos"].shape[1] if "ref_pos" in feats else None)
         sm = m.structure_module
+        if self.release:
+            # ``big``: the pair stack's scratch (projection planes, q|k|v|gate rows) goes back to the allocator
+            keep = {k: v for k, v in m.workspace.items() if k == "row_block"}
+            m.workspace.clear()
+            m.workspace.update(keep)
+            if dev.type == "cuda":
+                torch.cuda.empty_cache()
         prep = sm.score_model.prepare(s, s_inputs, m.z_cond_norm(z), atom_c, atom_c, atom_p, m.fused)
         step_fn = self._step_fn(prep, feats, N, nsamp)
         # the sampler's random stream starts here in every mode (graph warm-up / capture draw numbers too)

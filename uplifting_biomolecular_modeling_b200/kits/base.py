@@ -38,6 +38,8 @@ class Activation:
         self.levers_on: List[str] = []
         self.levers_off: Dict[str, str] = {}
         self.levers_skipped: Dict[str, str] = {}
+        self.levers_dropped: Dict[str, str] = {}     # droppable levers that declined: reported, never PARTIAL
+        self.evidence: Dict[str, dict] = {}
         self.words: List[str] = []
         self.gates: List[gates.Gate] = []
         self.probe = probe or gates.probe_gpus
@@ -95,12 +97,18 @@ class Activation:
                 self.levers_on.append(n)
                 continue
             try:
-                lv.apply(predictor)
+                if hasattr(predictor, "__dict__") and not hasattr(predictor, "n_gpu"):
+                    predictor.n_gpu = self.n_gpu
+                self.evidence[n] = lv.apply(predictor) or {}
                 self.levers_on.append(n)
             except BaseException as e:  # noqa: BLE001
-                if gates.is_cannot_run(e):
+                why = f"{type(e).__name__}:{report.token(str(e))[:80]}"
+                if lv.droppable:
+                    self.levers_dropped[n] = why
+                elif gates.is_cannot_run(e):
                     raise self.refuse(f"lever {n} cannot run: {e}")
-                self.levers_skipped[n] = f"{type(e).__name__}:{report.token(str(e))[:80]}"
+                else:
+                    self.levers_skipped[n] = why
         verb = "DRY-RUN" if dry_run else "ACTIVE"
         self._emit(report.with_words(report.line(self.spec.tag, verb, ("mode", self.mode),
                                                  ("levers", self.levers_on or None), ("source", self.source),
@@ -115,8 +123,9 @@ class Activation:
             elif n in self.levers_off:
                 self._emit(report.lever_line(self.spec.tag, n, "off", reason=self.levers_off[n], impl=impl,
                                              origin=origin, strategy=strat))
-            elif n in self.levers_skipped:
-                self._emit(report.lever_line(self.spec.tag, n, "skipped", reason=self.levers_skipped[n], impl=impl,
+            elif n in self.levers_skipped or n in self.levers_dropped:
+                why = self.levers_skipped.get(n) or self.levers_dropped.get(n)
+                self._emit(report.lever_line(self.spec.tag, n, "skipped", reason=why, impl=impl,
                                              origin=origin, strategy=strat))
         return self
 
@@ -138,7 +147,10 @@ class Activation:
                                                    self.levers_skipped, self.words, v,
                                                    gpu=self.gates[0].detail if self.gates else None,
                                                    ledgers=counters.BOOK.stats(),
-                                                   extra={"n_gpu": self.n_gpu, "levers_off": self.levers_off}))
+                                                   extra={"n_gpu": self.n_gpu, "levers_off": self.levers_off,
+                                                          "levers_dropped": self.levers_dropped,
+                                                          "lever_evidence": self.evidence,
+                                                          **getattr(self, "manifest_extra", {})}))
         return v["exit_code"]
 
     def register_exit(self, rc_getter=lambda: 0) -> None:

@@ -22,6 +22,7 @@ class Lever:
     origin: str = "core"
     needs_gpu: bool = False
     apply: Optional[Callable] = None          # (predictor) -> dict of evidence
+    droppable: bool = False                   # a refusal of this lever leaves the mode whole (reported, not PARTIAL)
 
 
 def _fused(kinds_fn, lever_name):
@@ -82,8 +83,81 @@ def _flag(attr, value=True):
     return apply
 
 
-def _noop(pred):
-    return {}
+def _expandable(pred):
+    """Allocator policy of ``big``: expandable segments requested and read back (a process whose allocator already
+    runs without them reports ``skipped`` with the reason; the lever is droppable)."""
+    from ..mem import allocator
+    ok = allocator.want_expandable()
+    live = allocator.verify_expandable()
+    if live is False:
+        raise RuntimeError("allocator_already_initialised_without_expandable_segments")
+    return {"requested": ok, "verified": live}
+
+
+def _chunk_pair_ops(pred):
+    """Pair operations of the kernel path run in row blocks: the triangle-attention q|k|v|gate rows, the
+    triangle-multiplication output stage and the transition exist for one block of rows at a time."""
+    rows = int(getattr(pred, "row_block", 0) or 512)
+    pred.row_block = rows
+    pred.model.workspace["row_block"] = rows
+    return {"row_block": rows}
+
+
+def _release(pred):
+    """The trunk's scratch buffers are returned to the allocator before the sampler starts."""
+    pred.release = True
+    return {"release": True}
+
+
+def _rowpair(pred):
+    """Row-sharded prediction over the ranks of ``--n_gpu P`` (the activation hands the run to the launcher)."""
+    import torch
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    want = int(getattr(pred, "n_gpu", 1) or 1)
+    if want > 1 and n < want:
+        raise gates.CannotRun(f"rowpair_tp: {want} GPUs requested, {n} visible")
+    pred.sharding = "rowpair"
+    return {"visible_gpus": n, "n_gpu": want}
+
+
+def _graph_verify(pred):
+    """The first replay of every captured graph is compared bit for bit with the eager step on the same inputs."""
+    pred.verify_graphs = 1
+    return {"verify": 1}
+
+
+def _cond_dedup(pred):
+    """Design batches share one trunk pass and one set of step-invariant sampler tensors."""
+    pred.cond_dedup = True
+    return {"cond_dedup": True}
+
+
+def _kernel_path(pred):
+    """Sequence models: row kernels, tcgen05 GEMMs and the convolution kernels replace the plain statements."""
+    import torch
+    model = getattr(pred, "model", None)
+    if model is None or not hasattr(model, "set_impl"):
+        raise gates.CannotRun("kernel_path: no switchable model")
+    if not torch.cuda.is_available():
+        raise gates.CannotRun("kernel_path: needs a CUDA device")
+    model.set_impl("fused")
+    return {"impl": "fused"}
+
+
+def _decode_graph(pred):
+    """Generation: the decode step is captured once and replayed per token."""
+    pred.decode_graph = True
+    return {"decode_graph": True}
+
+
+def _tp_fused(pred):
+    """Tensor parallelism of the sequence models with the collectives fused into the GEMM kernels."""
+    import torch
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    if n < 2:
+        raise RuntimeError("single_gpu")
+    pred.tp = "fused"
+    return {"visible_gpus": n}
 
 
 LEVERS: Dict[str, Lever] = {l.name: l for l in [
@@ -98,22 +172,14 @@ LEVERS: Dict[str, Lever] = {l.name: l for l in [
     Lever("fused_pwa", "F1.kernel_fusion", "gemm_sm100@1", needs_gpu=True, apply=_fused(_kinds_pwa, "fused_pwa")),
     Lever("fused_dit", "F1.kernel_fusion", "attention_d64+rows_sm100@1", needs_gpu=True,
           apply=_fused(_kinds_dit, "fused_dit")),
-    Lever("bf16_pair_stack", "F4.precision", "models.cofold", apply=_noop),
-    Lever("hoist_pair_bias", "F3.hoisting", "models.diffusion.prepare", apply=_noop),
-    Lever("hoist_conditioning", "F3.hoisting", "models.diffusion.hoist", apply=_noop),
     Lever("sampler_graph", "F2.graph_capture", "api.Predictor._step_fn", needs_gpu=True, apply=_flag("use_graphs")),
-    Lever("segment_mean_det", "F1.kernel_fusion", "models.diffusion.segment_mean", apply=_noop),
-    Lever("chunk_pair_ops", "F5.memory", "mem.chunk", apply=_flag("chunk_rows", 256)),
-    Lever("release_intermediates", "F5.memory", "mem.release", apply=_flag("release", True)),
-    Lever("expandable_segments", "F5.memory", "mem.allocator", apply=_noop),
-    Lever("rowpair_tp", "F7.tensor_parallel", "parallel.rowpair", needs_gpu=True, apply=_noop),
-    Lever("cond_dedup", "F3.hoisting", "models.design", apply=_noop),
-    Lever("attn_bf16", "F4.precision", "attention_sm100@1", needs_gpu=True, apply=_noop),
-    Lever("graph_rng", "F2.graph_capture", "capture.rng", apply=_noop),
-    Lever("resident_weights", "F6.host_overlap", "models.lm", apply=_noop),
-    Lever("forward_graph", "F2.graph_capture", "capture.graphs", needs_gpu=True, apply=_noop),
-    Lever("fused_rows", "F1.kernel_fusion", "rows_sm100@1", needs_gpu=True, apply=_noop),
-    Lever("tc_gemm", "F1.kernel_fusion", "gemm_sm100@1", needs_gpu=True, apply=_noop),
-    Lever("fused_conv", "F1.kernel_fusion", "hyena_sm100@1", needs_gpu=True, apply=_noop),
-    Lever("tp_fused", "F7.tensor_parallel", "parallel.tp", needs_gpu=True, apply=_noop),
+    Lever("graph_verify", "F2.graph_capture", "capture.graphs.verify", needs_gpu=True, apply=_graph_verify),
+    Lever("chunk_pair_ops", "F5.memory", "models.pairformer row blocks", apply=_chunk_pair_ops),
+    Lever("release_intermediates", "F5.memory", "api.Predictor.release", apply=_release),
+    Lever("expandable_segments", "F5.memory", "mem.allocator", apply=_expandable, droppable=True),
+    Lever("rowpair_tp", "F7.tensor_parallel", "parallel.rowpair", needs_gpu=True, apply=_rowpair),
+    Lever("cond_dedup", "F3.hoisting", "models.design.DesignPipeline", apply=_cond_dedup),
+    Lever("kernel_path", "F1.kernel_fusion", "rows+gemm+seq_sm100@1", needs_gpu=True, apply=_kernel_path),
+    Lever("decode_graph", "F2.graph_capture", "models.evo2.generate", needs_gpu=True, apply=_decode_graph),
+    Lever("tp_fused", "F7.tensor_parallel", "parallel.tp", needs_gpu=True, apply=_tp_fused, droppable=True),
 ]}

@@ -11,12 +11,14 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Optional, Tuple
 
-COFOLD_LEVERS_EXACT = ("hoist_pair_bias", "hoist_conditioning", "sampler_graph", "segment_mean_det")
+# Every name below is a lever of kits/levers.py whose ``apply`` changes what runs; work that every mode does
+# (step-invariant hoists in the sampler, bf16 storage of the pair stack) is not a lever and is not listed.
+COFOLD_LEVERS_EXACT = ("sampler_graph", "graph_verify")
 COFOLD_LEVERS_FAST = ("fused_transition", "fused_trimul", "fused_triatt", "fused_apb", "fused_opm", "fused_pwa",
-                      "fused_dit", "bf16_pair_stack")
+                      "fused_dit")
 COFOLD_LEVERS_BIG = ("chunk_pair_ops", "release_intermediates", "expandable_segments", "rowpair_tp")
-LM_LEVERS_EXACT = ("resident_weights", "forward_graph", "fused_rows")
-LM_LEVERS_FAST = ("tc_gemm", "fused_conv", "tp_fused")
+LM_LEVERS_EXACT = ("kernel_path", "decode_graph")
+LM_LEVERS_FAST = ("tp_fused",)
 
 
 @dataclass(frozen=True)
@@ -49,8 +51,8 @@ def _cofold(name, upstream, config="af3", n_gpu=(1, 2, 4, 8), ceiling=None, defa
 
 
 def _design(name, upstream, modes=("off", "exact", "fast"), default="fast", commands=("design",)):
-    lv = {"off": (), "exact": ("sampler_graph", "hoist_conditioning", "cond_dedup"),
-          "fast": ("fused_transition", "fused_trimul", "fused_triatt", "fused_apb", "attn_bf16"),
+    lv = {"off": (), "exact": ("sampler_graph", "cond_dedup"),
+          "fast": ("fused_transition", "fused_trimul", "fused_triatt", "fused_apb", "fused_dit"),
           "big": ("chunk_pair_ops",)}
     return KitSpec(name, upstream, "design", modes, default, ("install", "check") + tuple(commands), "design", (1,),
                    False, None, {m: lv[m] for m in modes})
@@ -87,7 +89,7 @@ REGISTRY: Dict[str, KitSpec] = {k.name: k for k in [
     _design("caliby", "Caliby"), _design("esm_if1", "ESM-IF1", ("off", "exact"), "exact"),
     _design("ef2inv", "ESMFold2 inversion"),
     KitSpec("proteinmpnn", "ProteinMPNN", "design", ("off", "exact", "fast"), None, ("install", "check", "design"),
-            "design", (1,), False, None, {"off": (), "exact": ("sampler_graph", "graph_rng"), "fast": ("attn_bf16",)}),
+            "design", (1,), False, None, {"off": (), "exact": ("cond_dedup",), "fast": ()}),
     # genomic / protein language models
     _lm("evo2", "Evo 2 7b/40b (StripedHyena-2)", "evo2", ("off", "exact", "fast"), "exact", ("score", "generate"),
         config="evo2_7b", n_gpu=(1, 2, 4, 8)),

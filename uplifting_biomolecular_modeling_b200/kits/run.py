@@ -16,11 +16,41 @@ from ..core import counters, report, stock_proof
 from . import base
 
 
+class InputError(ValueError):
+    """``--input`` / ``--model_config`` / ``--checkpoint`` cannot be honoured as given (exit 2, never a substitute)."""
+
+
+REQUIRED_FEATURES = ("token_feat", "token_mask", "residue_index", "chain_id", "token_bonds", "msa_feat", "msa_mask",
+                     "ref_pos", "atom_to_token", "token_rep_atom")
+
+
 def _load_features(args, cfg, config_name):
+    """Features of one prediction: a ``.pt`` feature dict or a ``.json`` description of a synthetic complex
+    (``{"tokens": N, "msa_depth": S, "chains": [[length, kind], ...], "seed": k}``); without ``--input`` a synthetic
+    complex of ``--tokens`` / ``--msa_depth``.  A path that cannot be read, or a file of another kind, is an error:
+    nothing is substituted for a named input."""
     import torch
     from ..models import cofold
-    if args.input and args.input.endswith(".pt") and os.path.exists(args.input):
-        return torch.load(args.input, map_location="cpu")
+    if args.input:
+        if not os.path.exists(args.input):
+            raise InputError(f"--input {args.input}: no such file")
+        if args.input.endswith(".pt"):
+            feats = torch.load(args.input, map_location="cpu", weights_only=True)
+            missing = [k for k in REQUIRED_FEATURES if k not in feats]
+            if missing:
+                raise InputError(f"--input {args.input}: feature(s) {','.join(missing)} missing")
+            return feats
+        if args.input.endswith(".json"):
+            with open(args.input) as f:
+                spec = json.load(f)
+            n = int(spec.get("tokens") or sum(int(c[0]) for c in spec.get("chains", [])) or 0)
+            if n <= 0:
+                raise InputError(f"--input {args.input}: gives neither tokens nor chains")
+            chains = [(int(c[0]), str(c[1])) for c in spec["chains"]] if "chains" in spec else \
+                cofold.chains_for(config_name, n)
+            return cofold.synthetic_features(n, int(spec.get("msa_depth", args.msa_depth or 16)), cfg,
+                                             seed=int(spec.get("seed", args.seed)), chains=chains)
+        raise InputError(f"--input {args.input}: expected a .pt feature file or a .json complex description")
     n = args.tokens or 128
     return cofold.synthetic_features(n, args.msa_depth or 16, cfg, seed=args.seed,
                                      chains=cofold.chains_for(config_name, n))
@@ -29,7 +59,9 @@ def _load_features(args, cfg, config_name):
 def run(spec, act: "base.Activation", args, allow_partial: bool) -> int:
     if spec.name in ("proteinmpnn", "esm_if1", "ef2inv"):
         return _run_design(spec, act, args, allow_partial)
-    if spec.family in ("cofold", "design"):
+    if spec.family == "design":
+        return _run_diffusion_design(spec, act, args, allow_partial)
+    if spec.family == "cofold":
         return _run_cofold(spec, act, args, allow_partial)
     if spec.family == "evo2":
         return _run_lm(spec, act, args, allow_partial, "evo2")
@@ -39,9 +71,14 @@ def run(spec, act: "base.Activation", args, allow_partial: bool) -> int:
 def _run_cofold(spec, act, args, allow_partial) -> int:
     import torch
     from .. import api
-    config = args.model_config or (spec.config if spec.family == "cofold" else "tiny")
-    if config not in __import__("uplifting_biomolecular_modeling_b200.models.cofold", fromlist=["CONFIGS"]).CONFIGS:
-        config = "af3"
+    from ..models import cofold as _cofold
+    config = args.model_config or spec.config
+    if config not in _cofold.CONFIGS:
+        if args.model_config:
+            report.emit(report.line(spec.tag, "USAGE", ("error", "unknown_model_config"), ("given", config),
+                                    ("known", ",".join(sorted(_cofold.CONFIGS)))))
+            return report.EXIT_USAGE
+        config = "af3"          # kits of the AF3 family without a configuration of their own share this one
     if act.mode == "off":
         proof = stock_proof.env_proof([spec.env], [], {k: v for k, v in os.environ.items() if k != spec.env}, {}, [])
         report.emit(stock_proof.proof_line(spec.tag, proof))
@@ -63,10 +100,21 @@ def _run_cofold(spec, act, args, allow_partial) -> int:
         overrides["samples"] = args.diffusion_samples
     try:
         pred = api.Predictor(config, mode="off", device=device, dtype=dtype, seed=args.seed, **overrides)
-        pred.mode = act.mode
-        if args.checkpoint:
+        pred.set_mode(act.mode)
+        ckpt = args.checkpoint or _weights_file(args.weights)
+        if ckpt:
             from ..models import weights
-            weights.load_checkpoint(pred.model, args.checkpoint)
+            try:
+                rep = weights.load_checkpoint(pred.model, ckpt, strict=not allow_partial)
+            except (ValueError, OSError) as e:
+                act.refuse(f"checkpoint {ckpt}: {e}")
+                return report.EXIT_NOT_ACTIVE
+            act.manifest_extra = {"checkpoint": {"path": ckpt, "matched": rep.matched, "missing": rep.missing[:50],
+                                                 "unexpected": rep.unexpected[:50],
+                                                 "shape_mismatch": rep.shape_mismatch[:50]}}
+            report.emit(report.line(spec.tag, "WEIGHTS", ("path", ckpt), ("matched", rep.matched),
+                                    ("missing", len(rep.missing)), ("unexpected", len(rep.unexpected)),
+                                    ("shape_mismatch", len(rep.shape_mismatch))))
         if getattr(args, "upstream_fix", None):
             from ..core import upstream_fix
             act.words = list(getattr(act, "words", [])) + upstream_fix.apply_all(
@@ -84,7 +132,11 @@ def _run_cofold(spec, act, args, allow_partial) -> int:
         act.refuse(str(e))
         return report.EXIT_NOT_ACTIVE
     act.register_exit()
-    feats = _load_features(args, pred.cfg, config)
+    try:
+        feats = _load_features(args, pred.cfg, config)
+    except InputError as e:
+        report.emit(report.line(spec.tag, "USAGE", ("error", "input"), ("detail", report.token(str(e))[:200])))
+        return act.finish(report.EXIT_USAGE, allow_partial, None)
     t0 = time.time()
     try:
         out = pred.predict(feats)
@@ -104,6 +156,70 @@ def _run_cofold(spec, act, args, allow_partial) -> int:
     report.emit(report.line(spec.tag, "DONE", ("seconds", round(dt, 3)), ("tokens", feats["token_feat"].shape[1]),
                             ("samples", out["coords"].shape[0])))
     return act.finish(0, allow_partial, args.out_dir, incomplete)
+
+
+def _weights_file(weights_dir):
+    """``--weights D``: the one checkpoint file in D (``*.ckpt`` / ``*.pt`` / ``*.safetensors``); None without D.
+    Several candidates are an error of the call, reported by the loader as an unreadable path."""
+    if not weights_dir:
+        return None
+    if os.path.isfile(weights_dir):
+        return weights_dir
+    if not os.path.isdir(weights_dir):
+        return weights_dir                      # the loader reports the missing path
+    c = sorted(f for f in os.listdir(weights_dir) if f.endswith((".ckpt", ".pt", ".safetensors")))
+    if len(c) == 1:
+        return os.path.join(weights_dir, c[0])
+    return None if not c else os.path.join(weights_dir, "<ambiguous:" + ",".join(c[:4]) + ">")
+
+
+def _run_diffusion_design(spec, act, args, allow_partial) -> int:
+    """``design`` verb of the diffusion design kits (BoltzGen, Complexa, PXDesign, Genie 3, RFdiffusion 1 / 3,
+    Caliby, ColabDesign, mosaic): backbones of ``--diffusion_samples`` designs are sampled by the structure module
+    on a target whose designed positions carry the unknown-residue token, then each backbone is given a sequence
+    by the inverse-folding decoder.  One trunk pass and one set of step-invariant sampler tensors serve the whole
+    design batch (``cond_dedup``); the sampler step replays from a CUDA graph under ``exact`` and above.
+    Reference: the resident sampler-graph drivers of those kits (e.g. rfdiffusion1/opt/forward/se3fast_addon)."""
+    import torch
+    from .. import api
+    from ..models import cofold, design
+    device = "cuda:0" if torch.cuda.is_available() else "cpu"
+    dtype = torch.bfloat16 if device != "cpu" else torch.float32
+    config = args.model_config or spec.config
+    if config not in cofold.CONFIGS:
+        report.emit(report.line(spec.tag, "USAGE", ("error", "unknown_model_config"), ("given", config)))
+        return report.EXIT_USAGE
+    over = {}
+    if args.sampling_steps is not None:
+        over["sampling_steps"] = args.sampling_steps
+    over["samples"] = args.diffusion_samples or 2
+    try:
+        pred = api.Predictor(config, mode="off", device=device, dtype=dtype, seed=args.seed, **over)
+        pred.set_mode(act.mode)
+        act.apply(pred)
+    except base.ActivationError:
+        return report.EXIT_NOT_ACTIVE
+    except api.NotActive as e:
+        act.refuse(str(e))
+        return report.EXIT_NOT_ACTIVE
+    act.register_exit()
+    n = args.tokens or 48
+    t0 = time.time()
+    pipe = design.DesignPipeline(pred, seed=args.seed, dedup=bool(getattr(pred, "cond_dedup", False)))
+    try:
+        res = pipe.run(n_tokens=n, designs=over["samples"], designed_fraction=0.5)
+    except Exception as e:  # noqa: BLE001
+        report.emit(report.line(spec.tag, "FAILED", ("error", type(e).__name__), ("detail", report.token(str(e))[:200])))
+        return act.finish(report.EXIT_FAIL, allow_partial, args.out_dir)
+    report.emit(report.line(spec.tag, "DONE", ("seconds", round(time.time() - t0, 3)), ("verb", args.verb),
+                            ("designs", len(res["sequences"])), ("tokens", n), ("trunk_passes", res["trunk_passes"]),
+                            ("first", res["sequences"][0][:40])))
+    if args.out_dir:
+        os.makedirs(args.out_dir, exist_ok=True)
+        torch.save({"coords": res["coords"]}, os.path.join(args.out_dir, "designs.pt"))
+        with open(os.path.join(args.out_dir, "design.json"), "w") as f:
+            json.dump({"sequences_text": res["sequences"], "tokens": n, "trunk_passes": res["trunk_passes"]}, f)
+    return act.finish(0, allow_partial, args.out_dir)
 
 
 def _run_design(spec, act, args, allow_partial) -> int:
@@ -148,13 +264,16 @@ def _run_lm(spec, act, args, allow_partial, family) -> int:
     import torch
     from ..models import lm
     device = "cuda:0" if torch.cuda.is_available() else "cpu"
+    # the model is built on its plain statements; the mode's levers then switch the kernel path, the decode graph
+    # and the tensor-parallel form on, each reporting what it did
+    model = lm.build(family, spec.config if args.model_config is None else args.model_config, device=device,
+                     mode="off", seed=args.seed, kit=spec.name, specdec=getattr(args, "specdec", 0))
+    model.mode = act.mode
     try:
-        act.apply(None)
+        act.apply(model)
     except base.ActivationError:
         return report.EXIT_NOT_ACTIVE
     act.register_exit()
-    model = lm.build(family, spec.config if args.model_config is None else args.model_config, device=device,
-                     mode=act.mode, seed=args.seed, kit=spec.name, specdec=getattr(args, "specdec", 0))
     protein = family == "protein_lm" and spec.name != "gpnstar"
     prompt = args.prompt or ("MKTAYIAKQRQISFVKSHFSRQLEERLGLIEVQ" * 2 if protein else "ACGT" * 16)
     t0 = time.time()

@@ -35,7 +35,7 @@ ENV = """# {name}: deployment parameters for an 8 x B200 (sm_100a, 180 GB HBM3e)
 MODEL_OPT_TARGET_GPU=b200
 MODEL_OPT_STACK_KEY=${{MODEL_OPT_STACK_KEY:-torch2.11-cu128-sm100a}}
 MODEL_OPT_JIT_ROOT=${{MODEL_OPT_JIT_ROOT:-/tmp/model_opt_jit}}
-NCCL_NVLS_ENABLE=${{NCCL_NVLS_ENABLE:-1}}
+NCCL_NVLS_ENABLE=${{NCCL_NVLS_ENABLE:-0}}
 """
 
 

@@ -58,6 +58,9 @@ CONFIGS: Dict[str, CofoldConfig] = {
     "af3": CofoldConfig(name="af3", pairformer_blocks=48, recycles=3, samples=5),
     # BASELINE config 4: big mode, 1 recycle, single-sequence MSA
     "big4096": CofoldConfig(name="big4096", pairformer_blocks=48, recycles=0, samples=1),
+    # diffusion design kits: a structure-module-heavy model (short trunk, no recycling, many samples per target)
+    "design": CofoldConfig(name="design", pairformer_blocks=12, msa_blocks=1, recycles=0, samples=8,
+                           sampling_steps=100, confidence_blocks=1),
     "tiny": CofoldConfig(name="tiny", pairformer_blocks=2, msa_blocks=1, recycles=1, token_depth=2,
                          atom_depth=1, sampling_steps=4, samples=2, confidence_blocks=1),
 }

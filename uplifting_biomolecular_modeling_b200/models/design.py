@@ -181,3 +181,52 @@ def build_decoder(seed: int = 0, **kw) -> InverseFoldingDecoder:
             if p.dim() >= 2:
                 p.copy_(torch.randn(p.shape, generator=g) / math.sqrt(p.shape[-1]))
     return m.eval()
+
+
+LETTERS = "ACDEFGHIKLMNPQRSTVWY"
+
+
+class DesignPipeline:
+    """Backbone diffusion followed by inverse folding: the ``design`` verb of the diffusion design kits.
+
+    A target of ``n_tokens`` residues is built with a fraction of its positions marked "to be designed" (their
+    residue type is the unknown token, so the trunk conditions on the rest only); the structure module samples one
+    backbone per design; the inverse-folding decoder gives each backbone a sequence from its own random stream.
+    With ``dedup`` the designs are the samples of ONE prediction (one trunk pass, one set of step-invariant sampler
+    tensors, every step batched over the designs); without it each design is a prediction of its own.  The
+    reference's design kits get the same saving from their ``cond_dedup`` / ``sdedup`` levers and resident sampler
+    graphs (boltzgen, rfdiffusion1 ``se3fast_addon``, pxdesign CHANGES.md)."""
+
+    def __init__(self, predictor, seed: int = 0, dedup: bool = True, decoder: Optional[InverseFoldingDecoder] = None):
+        self.pred, self.seed, self.dedup = predictor, seed, dedup
+        self.decoder = decoder or build_decoder(seed=seed)
+
+    def features(self, n_tokens: int, designed_fraction: float = 0.5):
+        from . import cofold
+        cfg = self.pred.cfg
+        feats = cofold.synthetic_features(n_tokens, 1, cfg, seed=self.seed)
+        g = torch.Generator().manual_seed(self.seed + 17)
+        designed = torch.rand(n_tokens, generator=g) < designed_fraction
+        tf = feats["token_feat"].clone()
+        tf[:, designed, :] = 0
+        tf[:, designed, min(20, tf.shape[-1] - 1)] = 1          # unknown-residue slot
+        feats["token_feat"] = tf
+        return feats, designed
+
+    @torch.no_grad()
+    def run(self, n_tokens: int, designs: int = 2, designed_fraction: float = 0.5) -> dict:
+        feats, designed = self.features(n_tokens, designed_fraction)
+        rep = feats["token_rep_atom"][0]
+        if self.dedup:
+            out = self.pred.predict(feats, samples=designs, confidence=False)
+            coords = out["coords"]
+            passes = 1
+        else:
+            coords = torch.cat([self.pred.predict(feats, samples=1, confidence=False, seed=self.seed + i)["coords"]
+                                for i in range(designs)], 0)
+            passes = designs
+        backbones = coords[:, rep].float().cpu()                  # one representative atom per token
+        dec = self.decoder
+        seqs = torch.cat([dec.sample(backbones[i:i + 1], seeds=[self.seed + 1000 + i]) for i in range(designs)], 0)
+        text = ["".join(LETTERS[int(t) % len(LETTERS)] for t in row.tolist()) for row in seqs]
+        return {"coords": coords.cpu(), "sequences": text, "designed": designed, "trunk_passes": passes}

@@ -15,6 +15,7 @@ class _Runner:
         self.model, self.device, self.mode = model, device, mode
         self.draft = None                 # a smaller model of the family: generate() then decodes speculatively
         self.specdec_k = 0
+        self.decode_graph = False         # the ``decode_graph`` lever: replay the decode step from a CUDA graph
 
     def run(self, verb: str, prompt: str, max_new_tokens: int = 32) -> dict:
         toks = evo2.tokenize(prompt, self.device)
@@ -25,7 +26,7 @@ class _Runner:
                 extra = {"specdec_rounds": stats["rounds"], "specdec_accepted": stats["accepted"],
                          "specdec_proposed": stats["proposed"]}
             else:
-                out = self.model.generate(toks, max_new_tokens)
+                out = self.model.generate(toks, max_new_tokens, graph=self.decode_graph)
             return {"new_tokens": int(out.shape[1]), "text": "".join(chr(int(t)) if 32 <= int(t) < 127 else "?"
                                                                       for t in out[0].tolist()), **extra}
         if verb in ("score", "predict"):

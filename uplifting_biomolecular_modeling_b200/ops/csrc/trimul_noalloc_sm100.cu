@@ -32,8 +32,13 @@ void* g_scratch_ptr[kMaxDevices] = {nullptr};
 int scratch_for_current_device(void** out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+  if (e != cudaSuccess) {
     fprintf(stderr, "[ubm] trimul_noalloc: cudaGetDevice failed: %s\n", cudaGetErrorString(e));
+    return ubm::UBM_ERR_DRIVER;
+  }
+  if (dev < 0 || dev >= kMaxDevices) {
+    fprintf(stderr, "[ubm] trimul_noalloc: device ordinal %d is outside the %d devices this entry point tracks\n", dev,
+            kMaxDevices);
     return ubm::UBM_ERR_DRIVER;
   }
   if (g_scratch_ptr[dev] == nullptr) {

@@ -301,8 +301,8 @@ constexpr int kTOSmemBytes = 2 * kTOTileBytes + kTOStages * kTOStageBytes + (512
 }  // namespace ubm
 
 // x: bf16 planes [128][N][Np]; z: bf16 [N*N][128]; wo, wg: bf16 [128][128] (gamma folded);
-// *_colsum / *_colbias: fp32 [128]; out: bf16 [N*N][128] (may alias z only when add_residual == 0
-// is not required: each row is read from shared memory before it is written).
+// *_colsum / *_colbias: fp32 [128]; out: bf16 [N*N][128].  out may alias z, with or without the residual: a tile's
+// rows of z are copied to shared memory before the same CTA writes those rows, and no other tile touches them.
 extern "C" int ubm_trimul_out_rows(const void* x, const void* z, const void* wo, const void* wg, const void* o_colsum,
                                    const void* o_colbias, const void* g_colsum, const void* g_colbias, void* out,
                                    int rows, int N, int Np, int add_residual, void* status, void* stream) {

@@ -25,6 +25,10 @@ native.declare("ubm_trimul_proj", [c_void_p] * 7 + [c_int, c_int, c_void_p, c_vo
 native.declare("ubm_triatt_proj", [c_void_p] * 13 + [c_int, c_int, c_int, c_int, c_void_p, c_void_p])
 native.declare("ubm_trimul_out", [c_void_p] * 9 + [c_int, c_int, c_int, c_void_p, c_void_p])
 native.declare("ubm_transition", [c_void_p] * 8 + [c_ll, c_int, c_int, c_void_p, c_void_p])
+# row-block forms (also the per-rank forms of the row-sharded pair stack)
+native.declare("ubm_trimul_proj_rows", [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+native.declare("ubm_triatt_proj_rows", [c_void_p] * 13 + [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+native.declare("ubm_trimul_out_rows", [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_void_p, c_void_p])
 
 
 def ceil_to(n: int, m: int) -> int:
@@ -111,17 +115,56 @@ class TrimulPacked:
         return cls(w_in, s_in, b_in, wo, so, bo, wg, sg, bg)
 
 
+def _trimul_blocked(z, m, w: TrimulPacked, outgoing: bool, residual: bool, out, ws: dict, rb: int):
+    """Row-blocked triangle multiplication: the projected operand planes a, b exist whole (the contraction of a
+    row block needs every row of the other operand), the contracted planes x only for ``rb`` rows of the update
+    at a time - contraction and output stage alternate per block.  Same kernels, same sums as the whole form."""
+    N = z.shape[0]
+    Np = ceil_to(N, 8)
+    dev = z.device
+    key = ("trimul_blocked", N, rb, dev)
+    if key not in ws:
+        ws[key] = (torch.empty((2, 128, N, Np), dtype=torch.bfloat16, device=dev),
+                   torch.empty((128, rb, Np), dtype=torch.bfloat16, device=dev))
+    planes, xb = ws[key]
+    st = native.status_tensor(dev)
+    stream = native.current_stream(dev)
+    lib = native.lib()
+    rc = lib.ubm_trimul_proj(native.ptr(z), native.ptr(w.w_in), native.ptr(w.in_colsum), native.ptr(w.in_colbias),
+                             native.ptr(m), native.ptr(planes), 0, N, Np, native.ptr(st), stream)
+    native.check(rc, "ubm_trimul_proj")
+    out = torch.empty_like(z) if out is None else out
+    for r0 in range(0, N, rb):
+        r1 = min(N, r0 + rb)
+        xv = xb.view(-1)[: 128 * (r1 - r0) * Np].view(128, r1 - r0, Np)
+        if outgoing:      # x[c, i, j] = sum_k a[c, i, k] b[c, j, k]: rows i of a against all of b
+            _gemm.gemm(planes[0][:, r0:r1, :N], planes[1][:, :, :N], out=xv[:, :, :N])
+        else:             # x[c, i, j] = sum_k a[c, k, i] b[c, k, j]: columns i of a (MN-major operands)
+            _gemm.gemm(planes[0][:, :, r0:r1], planes[1][:, :, :N], mn_major=True, out=xv[:, :, :N])
+        rc = lib.ubm_trimul_out_rows(native.ptr(xv), native.ptr(z[r0:r1]), native.ptr(w.wo), native.ptr(w.wg),
+                                     native.ptr(w.o_colsum), native.ptr(w.o_colbias), native.ptr(w.g_colsum),
+                                     native.ptr(w.g_colbias), native.ptr(out[r0:r1]), r1 - r0, N, Np,
+                                     1 if residual else 0, native.ptr(st), stream)
+        native.check(rc, "ubm_trimul_out_rows")
+    return out
+
+
 def trimul_fused(z: torch.Tensor, mask: Optional[torch.Tensor], w: TrimulPacked, outgoing: bool,
                  residual: bool = True, out: Optional[torch.Tensor] = None,
                  workspace: Optional[dict] = None) -> torch.Tensor:
     """z: bf16 [N, N, 128] contiguous; mask: [N, N] or None.  Three launches: projection ->
-    batched tcgen05 contraction -> output stage."""
+    batched tcgen05 contraction -> output stage.  With ``workspace["row_block"]`` set (the ``chunk_pair_ops`` lever)
+    and smaller than N, contraction and output stage run per block of rows (see :func:`_trimul_blocked`)."""
     if z.dtype != torch.bfloat16 or z.dim() != 3 or z.shape[-1] != 128 or not z.is_contiguous():
         raise ValueError("trimul_fused expects a contiguous bf16 [N, N, 128] tensor")
     N = z.shape[0]
     Np = ceil_to(N, 8)
     dev = z.device
     ws = workspace if workspace is not None else {}
+    rb = int(ws.get("row_block", 0) or 0)
+    if 0 < rb < N:
+        m = None if mask is None else mask.to(torch.float32).contiguous()
+        return _trimul_blocked(z, m, w, outgoing, residual, out, ws, rb // 8 * 8 or 8)
     key = ("trimul", N, dev)
     if key not in ws:
         ws[key] = (torch.empty((2, 128, N, Np), dtype=torch.bfloat16, device=dev),
@@ -201,6 +244,7 @@ class TriattPacked:
     wo: torch.Tensor         # bf16 [128, 128]
     bo: Optional[torch.Tensor]
     heads: int
+    raw_bias: tuple = ()     # (ln_w, ln_b, w_bias) as given: the row-blocked form computes the bias planes first
 
     @classmethod
     def pack(cls, ln_w, ln_b, w_bias, w_q, w_k, w_v, w_g, b_g, w_o, b_o, heads: int) -> "TriattPacked":
@@ -223,7 +267,7 @@ class TriattPacked:
             wb_colbias = (w_bias.detach().float() @ ln_b.detach().float()) * LOG2E
         return cls(w, colsum, colbias, wb, wb_colsum, wb_colbias.contiguous(),
                    w_o.detach().to(torch.bfloat16).contiguous(),
-                   None if b_o is None else b_o.detach().float().contiguous(), heads)
+                   None if b_o is None else b_o.detach().float().contiguous(), heads, (ln_w, ln_b, w_bias))
 
 
 def attention(q, k, v, bias, gate, out, rows: int, Nq: int, Nk: int, H: int, D: int = 32, ldb: int = 0,
@@ -311,6 +355,49 @@ def apb_fused(x: torch.Tensor, w: ApbPacked, bias_planes: torch.Tensor, ldb: int
     return _gemm.gemm(o, w.wo, gate=out_gate, residual=out_residual).view(B, N, -1)
 
 
+def _triatt_blocked(z, w: TriattPacked, starting: bool, residual: bool, out, ws: dict, mask, rb: int):
+    """Row-blocked triangle attention: the per-head bias planes of the whole pair tensor first (one pass of a row
+    kernel; transposed for the ending node), then projection -> attention -> output projection for ``rb``
+    attention rows at a time, so q | k | v | gate | o exist for one block only.  For the ending node an attention
+    row is a column of z: the block's columns are gathered to rows before the projection and the update is
+    added back to those columns."""
+    from . import rows as _rows
+    N = z.shape[0]
+    Np = ceil_to(N, 8)
+    dev = z.device
+    key = ("triatt_blocked", N, rb, dev)
+    if key not in ws:
+        ws[key] = (torch.empty((5, rb * N, 128), dtype=torch.bfloat16, device=dev),
+                   torch.zeros((w.heads, N, Np), dtype=torch.bfloat16, device=dev),
+                   torch.zeros((w.heads, rb, Np), dtype=torch.bfloat16, device=dev))
+    qkvgo, hb, hb_scratch = ws[key]
+    ln_w, ln_b, w_bias = w.raw_bias
+    _rows.pair_head_bias(z, ln_w, ln_b, w_bias, scale=LOG2E, transpose=not starting, out=hb)
+    st = native.status_tensor(dev)
+    stream = native.current_stream(dev)
+    lib = native.lib()
+    out = torch.empty_like(z) if out is None else out
+    for r0 in range(0, N, rb):
+        r1 = min(N, r0 + rb)
+        R = r1 - r0
+        src = z[r0:r1] if starting else z[:, r0:r1].transpose(0, 1).contiguous()
+        q, k, v, g, og = (qkvgo[i][: R * N] for i in range(5))
+        rc = lib.ubm_triatt_proj_rows(native.ptr(src), native.ptr(w.w), native.ptr(w.colsum), native.ptr(w.colbias),
+                                      native.ptr(w.wb), native.ptr(w.wb_colsum), native.ptr(w.wb_colbias),
+                                      native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(g),
+                                      native.ptr(hb_scratch), 0, R, rb, N, Np, w.heads, 0, native.ptr(st), stream)
+        native.check(rc, "ubm_triatt_proj_rows")
+        km = None if mask is None else KeyMask(mask.add[r0:r1], mask.flags[r0:r1])
+        attention_d32(q, k, v, hb, g, og, rows=R, Nq=N, Nk=N, H=w.heads, ldb=Np, mask=km)
+        if starting:
+            _gemm.gemm(og, w.wo, bias=w.bo, residual=z[r0:r1].view(R * N, 128) if residual else None,
+                       out=out[r0:r1].view(R * N, 128))
+        else:
+            upd = _gemm.gemm(og, w.wo, bias=w.bo).view(R, N, 128).transpose(0, 1)
+            out[:, r0:r1] = (z[:, r0:r1] + upd) if residual else upd
+    return out
+
+
 def triangle_attention_fused(z: torch.Tensor, w: TriattPacked, starting: bool, residual: bool = True,
                              out: Optional[torch.Tensor] = None, workspace: Optional[dict] = None,
                              mask: Optional[KeyMask] = None) -> torch.Tensor:
@@ -324,6 +411,9 @@ def triangle_attention_fused(z: torch.Tensor, w: TriattPacked, starting: bool, r
     Np = ceil_to(N, 8)
     dev = z.device
     ws = workspace if workspace is not None else {}
+    rb = int(ws.get("row_block", 0) or 0)
+    if 0 < rb < N:
+        return _triatt_blocked(z, w, starting, residual, out, ws, mask, rb)
     key = ("triatt", N, dev)
     if key not in ws:
         ws[key] = (torch.empty((5, N * N, 128), dtype=torch.bfloat16, device=dev),

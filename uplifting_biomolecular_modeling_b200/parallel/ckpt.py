@@ -68,21 +68,33 @@ class TrunkCheckpointer:
         name = f"z_rank{self.rank}.pt"
         _atomic_save({"z": z_loc.detach().cpu(), "rows": tuple(rows), "features": feats_digest,
                       "dtype": str(z_loc.dtype)}, os.path.join(sd, name))
+        # every rank hashes its own shard (rank 0 hashing all of them would leave the others seconds ahead, into
+        # device-side waits on a rank that is still on the host)
+        with open(os.path.join(sd, name + ".sha256"), "w") as f:
+            f.write(sha256_file(os.path.join(sd, name)))
         if self.rank == 0:
+            import random
+            rng = {"cpu": torch.get_rng_state(), "python": random.getstate()}
+            if torch.cuda.is_available():
+                rng["cuda"] = torch.cuda.get_rng_state_all()
             _atomic_save({"replicated": {k: v.detach().cpu() for k, v in (replicated or {}).items()},
-                          "rng": torch.get_rng_state(), "signature": self.signature},
-                         os.path.join(sd, "replicated.pt"))
+                          "rng": rng, "signature": self.signature}, os.path.join(sd, "replicated.pt"))
         if barrier is not None:
             barrier()
         if self.rank == 0:
-            files = sorted(f for f in os.listdir(sd) if f.endswith(".pt"))
+            files = {}
+            for f in sorted(x for x in os.listdir(sd) if x.endswith(".pt")):
+                side = os.path.join(sd, f + ".sha256")
+                files[f] = open(side).read().strip() if os.path.exists(side) else sha256_file(os.path.join(sd, f))
             man = {"step": step, "world": self.world, "signature": self.signature, "features": feats_digest,
-                   "files": {f: sha256_file(os.path.join(sd, f)) for f in files}}
+                   "files": files}
             fd, tmp = tempfile.mkstemp(prefix=".manifest.", dir=sd)
             with os.fdopen(fd, "w") as f:
                 json.dump(man, f, indent=1, sort_keys=True)
             os.replace(tmp, os.path.join(sd, "manifest.json"))
             self._prune()
+        if barrier is not None:
+            barrier()          # nobody goes back to the device before the manifest exists and old steps are pruned
         return sd
 
     def _prune(self) -> None:
@@ -122,3 +134,16 @@ class TrunkCheckpointer:
             raise ResumeRefused(f"resume refused: dtype {mine['dtype']} != {dtype}")
         rep = torch.load(os.path.join(sd, "replicated.pt"), map_location="cpu")
         return mine["z"].to(device), {k: v.to(device) for k, v in rep["replicated"].items()}, rep["rng"]
+
+    @staticmethod
+    def restore_rng(rng) -> None:
+        """Put the python / CPU / CUDA random states of a checkpoint back (older checkpoints hold the CPU state only)."""
+        if isinstance(rng, torch.Tensor):
+            torch.set_rng_state(rng)
+            return
+        import random
+        torch.set_rng_state(rng["cpu"])
+        if "python" in rng:
+            random.setstate(rng["python"])
+        if "cuda" in rng and torch.cuda.is_available() and len(rng["cuda"]) == torch.cuda.device_count():
+            torch.cuda.set_rng_state_all(rng["cuda"])

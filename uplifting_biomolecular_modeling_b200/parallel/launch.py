@@ -51,6 +51,12 @@ def rank_env(rank: int, world: int, port: int, base: Optional[Mapping[str, str]]
                 "PYTHONHASHSEED": env.get("PYTHONHASHSEED", "0")})
     if cpu:
         env["ROWPAIR_BACKEND"] = "gloo"
+    else:
+        # A rank that leaves (or is stopped by the fail-fast teardown) must hold no NVLink multicast binding: the
+        # package's kernels use plain peer loads and stores, so nothing is lost by keeping multicast off in NCCL and
+        # in torch's symmetric memory for rank processes.  A caller that wants NVLS sets the variables itself.
+        env.setdefault("NCCL_NVLS_ENABLE", "0")
+        env.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     if extra:
         env.update({k: str(v) for k, v in extra.items()})
     return env
@@ -200,11 +206,17 @@ def run_prediction_sharded(spec, act, args, config: str, allow_partial: bool) ->
                                               ("source", act.source), ("n_gpu", act.n_gpu),
                                               ("sharding", "rowpair")), act.words))
     wargs = ["--config", config, "--tokens", str(args.tokens or 256), "--msa_depth", str(args.msa_depth or 1),
-             "--seed", str(args.seed)]
+             "--seed", str(args.seed), "--structure", "1"]
     if args.out_dir:
         wargs += ["--out_dir", args.out_dir]
     if args.recycling_steps is not None:
         wargs += ["--recycles", str(args.recycling_steps)]
+    for flag, val in (("--input", args.input), ("--checkpoint", args.checkpoint or args.weights),
+                      ("--sampling_steps", args.sampling_steps), ("--diffusion_samples", args.diffusion_samples)):
+        if val is not None:
+            wargs += [flag, str(val)]
+    if allow_partial:
+        wargs += ["--allow-partial"]
     try:
         run_sharded(act.n_gpu, "uplifting_biomolecular_modeling_b200.parallel.worker", wargs)
     except RankFailed as e:

@@ -10,6 +10,7 @@ ordinary TMA / ld.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional, Sequence
 
 import torch
@@ -66,6 +67,10 @@ class SymmHeap:
         dist.barrier(self.group)
         self._flag_ptrs = ptr_array(self._flags.ptrs)
         self._epoch = 0
+        # Limit of the device-side wait in a stream barrier.  The kernel default (4 s) suits kernels that follow one
+        # another on the device; ranks that do host work between steps (checkpoint writes, feature loading) skew by
+        # more, so a long-running worker raises it through ROWPAIR_BARRIER_LIMIT_MS (default 60 s).
+        self.limit_ms = int(os.environ.get("ROWPAIR_BARRIER_LIMIT_MS", "60000"))
 
     def alloc(self, shape, dtype) -> SymmTensor:
         t = self.sm.empty(*shape, dtype=dtype, device=self.device)
@@ -76,6 +81,7 @@ class SymmHeap:
         """Stream-ordered barrier among the ranks (bounded wait; failure shows in the status word)."""
         self._epoch += 1
         st = native.status_tensor(self.device)
-        rc = native.lib().ubm_peer_barrier(self._flag_ptrs, self.rank, self.world, self._epoch, int(limit_ms),
+        rc = native.lib().ubm_peer_barrier(self._flag_ptrs, self.rank, self.world, self._epoch,
+                                           int(limit_ms) or self.limit_ms,
                                            native.ptr(st), native.current_stream(self.device))
         native.check(rc, "ubm_peer_barrier")
