@@ -51,14 +51,124 @@ def summarize_clocks(samples):
 
 
 def reference_arm(args):
-    """The unmodified reference cannot produce this metric here: its kits patch upstream model packages
-    (protenix / boltz / openfold3 / chai_lab) that are not installable offline; only its core
-    (opt_core) installs."""
-    why = ("reference kits need their upstream model packages (boltz/protenix/openfold3/chai_lab with "
-           "pytorch_lightning, rdkit, cuequivariance, ...) which are not in the offline wheelhouse; only "
-           "common/opt_core installs (baseline/_ref)")
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    """The reference's own public path for this metric is a kit's ``pred`` verb (``boltz predict`` patched in
+    memory by ``boltz2_opt``).  It is tried as it stands: the stock package ships in the reference as a pure-Python
+    wheel and is installed without dependencies under ``baseline/_ref``; whatever import stops it is named in the
+    ``unavailable`` line.  Nothing of this repository's models, kernels or engine is put in its place.  As context
+    (never as the headline), the stock trunk modules that do import - ``PairformerModule`` and ``MSAModule``, the
+    Pairformer part of the same N = 1536 workload - are timed unmodified and reported under ``stock_trunk``."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    line = {"impl": "reference"}
+    if not os.path.isdir(os.path.join(ref, "boltz")):
+        line["unavailable"] = ("baseline/_ref holds no stock model package: install the wheel the reference ships "
+                               "(boltz2/stock/boltz-2.2.1-py3-none-any.whl) with pip --no-deps --target baseline/_ref")
+        print(json.dumps(line))
+        return 0
+    sys.path.insert(0, ref)
+    failing = []
+    for mod in ("boltz.main", "boltz.model.models.boltz2", "boltz.model.modules.diffusionv2"):
+        try:
+            __import__(mod)
+        except Exception as e:  # noqa: BLE001 - the reason is the answer
+            failing.append(f"{mod}: {type(e).__name__}: {e}")
+    if not failing:
+        failing.append("imports succeed but `boltz predict` needs its checkpoint and CCD downloads (no network)")
+    line["unavailable"] = ("the stock prediction path does not import here: " + "; ".join(failing) +
+                           " (none of pytorch_lightning, einx, rdkit, cuequivariance is in the offline wheelhouse)")
+    try:
+        import torch
+        if torch.cuda.is_available() and os.environ.get("UBM_BENCH_STOCK_TRUNK", "1") != "0":
+            sys.path.insert(0, os.path.join(ROOT, "benchmarks"))
+            import trunk_vs_reference as tvr
+            ok, why = tvr.stock_available()
+            if ok:
+                blocks = 48
+                res = tvr.measure(args.tokens, blocks, 4, args.msa_depth, rounds=1, ours=False,
+                                  log=lambda *_: None)
+                passes = (3 if args.recycles is None else args.recycles) + 1
+                line["stock_trunk"] = {
+                    "what": "unmodified stock boltz-2.2.1 PairformerModule(v2, 48 blocks) and MSAModule(4 blocks), "
+                            "eval, bf16 autocast, use_kernels=False, random-init, one pass each; not the headline metric",
+                    "tokens": args.tokens, "msa_depth": args.msa_depth,
+                    "pairformer_ms_per_pass": res["pairformer"]["stock_ms"],
+                    "msa_module_ms_per_pass": res["msa_module"]["stock_ms"],
+                    "trunk_ms_for_passes": round(passes * (res["pairformer"]["stock_ms"] + res["msa_module"]["stock_ms"]), 1),
+                    "trunk_passes": passes}
+            else:
+                line["stock_trunk"] = {"unavailable": why}
+    except Exception as e:  # noqa: BLE001 - context only; the unavailable line stands
+        line["stock_trunk"] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+    print(json.dumps(line))
     return 0
+
+
+def big_mode(args, world, rank, dev):
+    """BASELINE's second metric: one N = 4096 prediction trunk (48 Pairformer blocks, single-sequence MSA, one pass)
+    with the pair tensor held by the run's P GPUs - latency (device-timed, max over ranks, second run) and peak GB
+    per GPU.  P = 1: the single-GPU ``big`` mode (row-blocked kernel path).  P > 1: row-sharded over the ranks, once
+    with the gathers fused into the kernels (``peer``) and once with NCCL gathers (``nccl``)."""
+    import torch
+    import torch.distributed as dist
+    from uplifting_biomolecular_modeling_b200.models import cofold
+    N = int(os.environ.get("UBM_BENCH_BIG_TOKENS", "4096"))
+    out = {"tokens": N, "config": "big4096: 8 chains x 512 residues, single-sequence MSA, 48 Pairformer blocks, 1 pass",
+           "n_gpus": world}
+    torch.cuda.empty_cache()
+    if world == 1:
+        from uplifting_biomolecular_modeling_b200 import api
+        pred = api.Predictor("big4096", mode="big", device=str(dev), dtype=torch.bfloat16, seed=0)
+        feats = pred.to_device(cofold.synthetic_features(N, 1, pred.cfg, seed=0, chains=cofold.chains_for("big4096", N)))
+        ms = None
+        for rep in range(2):
+            torch.cuda.reset_peak_memory_stats(dev)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            with torch.no_grad():
+                s_inputs, s_init, z_init, _, _ = pred.model.embed(feats)
+                s, z = pred.model.trunk(feats, s_inputs, s_init, z_init, 0)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            del s, z, z_init
+        out["single_gpu_big"] = {"latency_ms": round(ms, 1), "row_block": pred.row_block,
+                                 "peak_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2)}
+        return out
+    from uplifting_biomolecular_modeling_b200.parallel import comm as C
+    from uplifting_biomolecular_modeling_b200.parallel import worker
+    from uplifting_biomolecular_modeling_b200.parallel.layout import Layout
+    from uplifting_biomolecular_modeling_b200.parallel.rowpair_fused import FusedRowPair
+    from uplifting_biomolecular_modeling_b200.parallel.symm import SymmHeap
+    from uplifting_biomolecular_modeling_b200.models import pairformer as pf
+    from uplifting_biomolecular_modeling_b200.ops import native
+    comm = C.GroupComm()
+    model = cofold.build_model("big4096", device=dev, dtype=torch.bfloat16, seed=0)
+    pf.set_impl(model, "fused", kinds=(pf.Transition,), workspace=model.workspace)
+    feats = cofold.synthetic_features(N, 1, model.cfg, device=dev, dtype=torch.bfloat16, seed=0,
+                                      chains=cofold.chains_for("big4096", N))
+    lay = Layout(N, world, align=128)
+    heap = SymmHeap(device=dev)
+    for gather in ("peer", "nccl"):
+        fused = FusedRowPair(lay, comm, heap, gather=gather)
+        ms = None
+        for rep in range(2):
+            torch.cuda.reset_peak_memory_stats(dev)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0.record()
+            worker.sharded_trunk(model, feats, comm, lay, fused, 0, torch.bfloat16, checkpoint=False)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+        native.raise_on_status(dev, "big mode")
+        t = torch.tensor([ms, torch.cuda.max_memory_allocated(dev) / 2 ** 30], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[f"rowpair_{gather}"] = {"latency_ms_max_over_ranks": round(float(t[0]), 1),
+                                    "peak_gb_per_gpu_max": round(float(t[1]), 2)}
+        del fused
+        torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -89,7 +199,10 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")      # the package's kernels use plain peer loads and stores
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=600))
 
     pred = api.Predictor(args.config, mode=args.mode, device=str(dev), dtype=torch.bfloat16, seed=rank)
     chains = cofold.chains_for(args.config, args.tokens)
@@ -138,8 +251,26 @@ def main():
     value = world * 3600.0 * 1000.0 / ms
     value_e2e = world * 3600.0 * 1000.0 / ms_e2e
     finite = bool(torch.isfinite(out["coords"]).all())
+    ledgers = {}
+    try:
+        from uplifting_biomolecular_modeling_b200.core import counters
+        ledgers = {k: {"served": v["served"], "fallback": v["fallback"], **({"fallback_by": v["fallback_by"]}
+                                                                                if v["fallback"] else {})}
+                   for k, v in counters.BOOK.stats().items()}
+    except Exception:  # noqa: BLE001
+        pass
+    cfg, h2d_bytes, d2h_bytes = pred.cfg, pred.h2d_bytes, pred.d2h_bytes
+    big = None
+    if os.environ.get("UBM_BENCH_BIG", "1") != "0" and args.tokens == 1536:
+        # the second metric of the baseline (big-mode latency and peak memory at this run's P); measured after the
+        # headline regions, never inside them
+        del pred, feats_dev, out
+        try:
+            big = big_mode(args, world, rank, dev)
+        except Exception as e:  # noqa: BLE001 - the headline line must still be printed
+            big = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
     if rank == 0:
-        c = pred.cfg
+        c = cfg
         shape = "AF3-shaped" if args.config == "af3" else f"{args.config}-shaped"
         model = (f"{shape} cofold ({c.pairformer_blocks} Pairformer blocks, {c.msa_blocks} MSA blocks, "
                  f"{c.token_depth}-block DiT, {c.samples}x{args.sampling_steps or c.sampling_steps} sampling)")
@@ -151,16 +282,16 @@ def main():
                 "data": "synthetic features, random-init weights", "impl": "ours",
                 "config": dict(CONFIG, model=model, tokens=args.tokens, msa_depth=args.msa_depth, mode=args.mode,
                                global_batch=world, seq_len=args.tokens, parallelism=f"dp{world}",
-                               sampling_steps=args.sampling_steps or pred.cfg.sampling_steps,
-                               samples=pred.cfg.samples, trunk_passes=(pred.cfg.recycles if args.recycles is None
+                               sampling_steps=args.sampling_steps or cfg.sampling_steps,
+                               samples=cfg.samples, trunk_passes=(cfg.recycles if args.recycles is None
                                                                        else args.recycles) + 1),
                 "clocks": summarize_clocks(samples),
                 "e2e": {"value": round(value_e2e, 3), "unit": "predictions/hour", "ms_per_step": round(ms_e2e, 3),
-                        "h2d_bytes_per_step": pred.h2d_bytes, "d2h_bytes_per_step": pred.d2h_bytes,
+                        "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                         "note": "Predictor.predict(host features): pinned-host feature copy in, coordinates / "
                                 "confidence copy out, every step; `value` is the same call on device-resident "
                                 "features with the result left on the device"},
-                "gpu_launches": launches, "finite_output": finite}
+                "gpu_launches": launches, "finite_output": finite, "kernel_ledgers": ledgers, "big_mode": big}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

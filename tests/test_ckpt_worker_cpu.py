@@ -49,7 +49,7 @@ def test_weights_load_by_upstream_names(tmp_path):
 
 
 def test_sharded_worker_on_gloo_matches_single_rank(tmp_path):
-    common = ["--config", "tiny", "--tokens", "24", "--msa_depth", "2", "--recycles", "0"]
+    common = ["--config", "tiny", "--tokens", "24", "--msa_depth", "2", "--recycles", "0", "--structure", "1"]
     outs = []
     for world in (1, 2):
         out = tmp_path / f"w{world}"
@@ -61,5 +61,11 @@ def test_sharded_worker_on_gloo_matches_single_rank(tmp_path):
         outs.append(torch.load(out / "trunk.pt"))
     assert torch.allclose(outs[0]["s"], outs[1]["s"], atol=1e-4, rtol=1e-4)
     assert abs(outs[0]["distogram_logits_mean"] - outs[1]["distogram_logits_mean"]) < 1e-4
+    # the sharded run returns a structure: rank 0 received the row shards and ran sampler + confidence head
+    preds = [torch.load(tmp_path / f"w{w}" / "prediction.pt") for w in (1, 2)]
+    assert preds[1]["coords"].shape == preds[0]["coords"].shape and preds[1]["coords"].dim() == 3
+    assert torch.isfinite(preds[1]["coords"]).all() and "plddt" in preds[1]
+    assert torch.allclose(preds[0]["coords"], preds[1]["coords"], atol=5e-2, rtol=1e-2)
+    assert "[rowpair] STRUCTURE rank=0" in (tmp_path / "log2" / "rank0.log").read_text()
     log = (tmp_path / "log2" / "rank1.log").read_text()
     assert "[rowpair] SCHEDULE rank=1" in log and "[rowpair] MEMSTATS rank=1" in log

@@ -51,11 +51,14 @@ def _tree_copy(dst, src) -> None:
 class Predictor:
     def __init__(self, config: str = "af3", mode: str = "fast", device: str = "cuda:0",
                  dtype: torch.dtype = torch.bfloat16, seed: int = 0, use_graphs: Optional[bool] = None,
-                 **overrides):
+                 model=None, **overrides):
+        """``model``: an already built model of ``config`` (the row-sharded worker hands its replica over for the
+        structure and confidence stages); otherwise the model is built here."""
         if mode not in MODES:
             raise ValueError(f"mode {mode!r} not in {MODES}")
         self.mode, self.device, self.dtype, self.seed = mode, torch.device(device), dtype, seed
-        self.model = cofold.build_model(config, device=self.device, dtype=dtype, seed=seed, **overrides)
+        self.model = model if model is not None else \
+            cofold.build_model(config, device=self.device, dtype=dtype, seed=seed, **overrides)
         self.cfg = self.model.cfg
         self.levers = []
         if mode in ("fast", "big"):
@@ -246,6 +249,29 @@ class Predictor:
         mark("embed")
         s, z = m.trunk(feats, s_inputs, s_init, z_init, recycles)
         mark("trunk")
+        out = self.structure_and_confidence(feats, s, z, s_inputs, atom_c, atom_p, samples, steps, confidence, seed,
+                                            mark)
+        host = {k: v.float().cpu() for k, v in out.items()} if to_host else {k: v.float() for k, v in out.items()}
+        mark("confidence_and_copy")
+        if timing:
+            self.last_timing = {marks[i][0]: round((marks[i][1] - marks[i - 1][1]) * 1e3, 2)
+                                for i in range(1, len(marks))}
+            import sys
+            print(f"[ubm] STAGES ms {self.last_timing}", file=sys.stderr, flush=True)
+        self.d2h_bytes = sum(v.numel() * 4 for v in host.values()) if to_host else 0
+        if dev.type == "cuda" and m.fused:
+            from .ops import native
+            native.raise_on_status(dev, "predict")
+        return host
+
+    @torch.no_grad()
+    def structure_and_confidence(self, feats, s, z, s_inputs, atom_c, atom_p, samples=None, steps=None,
+                                 confidence: bool = True, seed: Optional[int] = None, mark=lambda name: None):
+        """Sampler and confidence head on a finished trunk (s [1, N, c_s], z [1, N, N, c_z] on this device); returns
+        device tensors.  ``predict`` calls it after its own trunk; the row-sharded worker calls it on rank 0 with the
+        gathered pair tensor."""
+        m = self.model
+        dev = self.device
         N = s.shape[1]
         nsamp = samples or self.cfg.samples
         if getattr(self, "_plan_key", None) != N:
@@ -277,15 +303,4 @@ class Predictor:
             out["plddt"] = (p * (torch.arange(50, device=p.device) + 0.5) / 50).sum(-1)
             pae = torch.softmax(conf["pae_logits"].float(), -1)
             out["pae_mean"] = (pae * (torch.arange(64, device=p.device) + 0.5) * 0.5).sum(-1).mean()
-        host = {k: v.float().cpu() for k, v in out.items()} if to_host else {k: v.float() for k, v in out.items()}
-        mark("confidence_and_copy")
-        if timing:
-            self.last_timing = {marks[i][0]: round((marks[i][1] - marks[i - 1][1]) * 1e3, 2)
-                                for i in range(1, len(marks))}
-            import sys
-            print(f"[ubm] STAGES ms {self.last_timing}", file=sys.stderr, flush=True)
-        self.d2h_bytes = sum(v.numel() * 4 for v in host.values()) if to_host else 0
-        if dev.type == "cuda" and m.fused:
-            from .ops import native
-            native.raise_on_status(dev, "predict")
-        return host
+        return out

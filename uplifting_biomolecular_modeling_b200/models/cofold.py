@@ -134,6 +134,10 @@ class InputEmbedder(nn.Module):
     def forward(self, feats):
         c, p = self.atom_tensors(feats)
         biases = [m(p).permute(0, 4, 1, 2, 3) for m in self.atom_pair_bias]
+        layers = self.atom_attention_encoder.atom_transformer.layers
+        if layers and layers[0].impl == "fused" and p.is_cuda and (self.cfg.window_q, self.cfg.window_k) == (32, 128):
+            from .diffusion import WindowBias
+            biases = [WindowBias(b) for b in biases]         # the window-attention kernel's bias layout
         n_tokens = feats["token_feat"].shape[1]
         a, _ = self.atom_attention_encoder(c, c, biases, torch.zeros_like(feats["ref_pos"]),
                                            feats["atom_to_token"][0], n_tokens)

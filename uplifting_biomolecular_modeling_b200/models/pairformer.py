@@ -153,15 +153,17 @@ class TriangleMultiplicationIncoming(TriangleMultiplication):
 
 
 class _MHA(nn.Module):
-    """Parameter holder with the OpenFold attention names used by Boltz-2's triangle attention."""
+    """Parameter holder with the OpenFold attention names used by Boltz-2's triangle attention.  Boltz-2 keeps no
+    bias on the gate and output projections (boltz2/stock/src/boltz/model/layers/triangular_attention/
+    primitives.py:259-267); ``bias=True`` gives the OpenFold / AF3-family form that has them."""
 
-    def __init__(self, c_in: int, c_hidden: int, heads: int):
+    def __init__(self, c_in: int, c_hidden: int, heads: int, bias: bool = False):
         super().__init__()
         self.linear_q = nn.Linear(c_in, c_hidden * heads, bias=False)
         self.linear_k = nn.Linear(c_in, c_hidden * heads, bias=False)
         self.linear_v = nn.Linear(c_in, c_hidden * heads, bias=False)
-        self.linear_o = nn.Linear(c_hidden * heads, c_in)
-        self.linear_g = nn.Linear(c_in, c_hidden * heads)
+        self.linear_o = nn.Linear(c_hidden * heads, c_in, bias=bias)
+        self.linear_g = nn.Linear(c_in, c_hidden * heads, bias=bias)
 
 
 class TriangleAttention(_Switchable):

@@ -88,6 +88,18 @@ struct AttnParams {
   long long ld_mask;
   KernelStatus* status;
   int n_qt, n_kt, n_rp, num_items;
+  // Pair-bias all-gather inside this launch: the bias planes [H][Nq][ldb] that the tiles read are a buffer of THIS
+  // GPU whose rows [g_row0[q], g_row0[q] + g_rows[q]) belong to GPU q.  Before the tile loop every CTA copies its
+  // share of the peers' rows from their buffers (g_src[q], same layout, plain peer loads) into the local one, then
+  // adds one to g_done; the TMA producers start on bias tiles once g_done has reached g_target (all CTAs of this
+  // launch).  The wait is bounded.  g_n == 0: no gather.
+  int g_n, g_me;
+  const __nv_bfloat16* g_src[8];
+  int g_row0[8], g_rows[8];
+  __nv_bfloat16* g_dst;
+  long long g_ld, g_plane;          // elements per bias row / per head plane
+  uint32_t* g_done;
+  uint32_t g_target;
   // peer mode: the bias rows (queries) are row shards owned by several GPUs; query tiles are enumerated
   // shard by shard and each tile's bias comes through that GPU's tensor map
   int npeers;
@@ -199,6 +211,33 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tO = tmem_base + 256;   // O[r] at r * D
   const uint32_t tP = tmem_base + Cfg::kTmemP;
   const int T = p.n_kt;
+  if (p.g_n > 1) {
+    // ---- gather prologue: 16-byte units of the peers' bias rows, round-robin over the CTAs of the launch
+    for (int q = 0; q < p.g_n; ++q) {
+      if (q == p.g_me || p.g_rows[q] <= 0) continue;
+      const long long units_per_plane = static_cast<long long>(p.g_rows[q]) * p.g_ld / 8;     // 8 bf16 = 16 bytes
+      const long long off0 = static_cast<long long>(p.g_row0[q]) * p.g_ld;
+      for (int h = 0; h < p.H; ++h) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.g_src[q] + h * p.g_plane + off0);
+        uint4* dst = reinterpret_cast<uint4*>(p.g_dst + h * p.g_plane + off0);
+        for (long long u = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; u < units_per_plane;
+             u += static_cast<long long>(gridDim.x) * blockDim.x) {
+          uint4 v;
+          asm volatile("ld.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                       : "l"(src + u));
+          dst[u] = v;
+        }
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();                   // cumulative: what the CTA's threads wrote is visible before the count
+      fence_proxy_async_all();           // the copies are generic-proxy writes that TMA loads will read
+      atomicAdd(p.g_done, 1u);
+    }
+  }
   if (TP) {
     // identity B operand in shared memory: TK/64 k-blocks of [TK rows][64 k], row n has a one at k = n
     constexpr int kChunks = TK / 8;   // 16-byte chunks per row
@@ -227,6 +266,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t item_cnt = 0, gk = 0;
+      if (p.g_n > 1) {
+        // every CTA of the launch has finished its share of the gather (bounded wait, as for a peer flag)
+        wait_flag_ge(p.g_done, p.g_target, ws, 63, 0);
+        fence_proxy_async_all();
+      }
       for (int item = blockIdx.x; item < p.num_items; item += gridDim.x, ++item_cnt) {
         const int qt = item % p.n_qt;
         const int tmp = item / p.n_qt;
@@ -571,6 +615,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
+struct AttnGather {
+  int n = 0, me = 0;
+  const void* const* src = nullptr;   // n device pointers: every GPU's bias buffer [H][Nq][ldb]
+  const int* rows = nullptr;          // rows owned by each GPU (sum = Nq)
+  void* done = nullptr;               // uint32 counter in this GPU's memory
+  unsigned int epoch = 0;             // launches so far with this counter, this one included
+};
+
 struct AttnMask {
   const void* kmask = nullptr;   // bf16 [rows][ld_mask], additive (0 / -1e30)
   const void* kflags = nullptr;  // uint8 [rows][ceil(Nk / TK)]
@@ -582,7 +634,7 @@ static int launch_attention(const void* q, const void* k, const void* v, const v
                             int rows, int Nq, int Nk, int H, long long ldb, long long ld_in, long long ld_gate,
                             int transpose_out, AttnMask mask,
                             void* status, void* stream, int npeers = 0, const void* const* bias_ptrs = nullptr,
-                            const int* peer_rows = nullptr, long long peer_head_stride = 0) {
+                            const int* peer_rows = nullptr, long long peer_head_stride = 0, AttnGather gather = {}) {
   using Cfg = AttnCfg<D, TK, R2, TP>;
   const uint64_t hd = (uint64_t)H * D;
   const uint64_t ldi = ld_in > 0 ? (uint64_t)ld_in : hd;  // row stride of q / k / v in elements
@@ -666,6 +718,26 @@ static int launch_attention(const void* q, const void* k, const void* v, const v
   }
   p.num_items = p.n_qt * p.n_rp * H;
   const int grid = p.num_items < sm_count() ? p.num_items : sm_count();
+  if (gather.n > 1) {
+    if (PEER || gather.n > 8 || bias == nullptr || gather.src == nullptr || gather.rows == nullptr ||
+        gather.done == nullptr || (ldb & 7))
+      return UBM_ERR_ARGUMENT;
+    p.g_n = gather.n;
+    p.g_me = gather.me;
+    int row = 0;
+    for (int i = 0; i < gather.n; ++i) {
+      p.g_src[i] = static_cast<const __nv_bfloat16*>(gather.src[i]);
+      p.g_row0[i] = row;
+      p.g_rows[i] = gather.rows[i];
+      row += gather.rows[i];
+    }
+    if (row != Nq) return UBM_ERR_ARGUMENT;
+    p.g_dst = static_cast<__nv_bfloat16*>(const_cast<void*>(bias));
+    p.g_ld = ldb;
+    p.g_plane = static_cast<long long>(ldb) * Nq;
+    p.g_done = static_cast<uint32_t*>(gather.done);
+    p.g_target = gather.epoch * static_cast<uint32_t>(grid);   // the grid size is the same for every launch on a counter
+  }
   auto kern = attention_kernel<D, TK, R2, PEER, TP, POLY>;
   {
     // the in-kernel register re-split must fit the pool this build was compiled with, or it would never return
@@ -751,6 +823,39 @@ extern "C" int ubm_attention_d64(const void* q, const void* k, const void* v, co
   const int poly = (g_attn_variant >> 4) & 3;
   if (poly == 1) return ubm::launch_attention<64, 64, 2, true, 0, false>(UBM_ATTN_ARGS);
   return ubm::launch_attention<64, 64, 2, true, 1, false>(UBM_ATTN_ARGS);
+}
+
+// Pair-bias all-gather inside the attention launch (head dimension 32, four-row form).  Every GPU holds a bias
+// buffer bf16 [H][Nq][ldb] in memory its peers have mapped and has written the rows it owns (rows[i] rows for GPU
+// i, in rank order); bias_bufs[i] is GPU i's buffer, bias_bufs[me] this GPU's.  The kernel first copies the
+// peers' rows into this GPU's buffer - every CTA a share, plain peer loads, no multicast - and then runs the
+// attention on the completed planes with the same tile code as ubm_attention_d32; `done` is a uint32 counter on
+// this GPU (zero before the first launch) and `epoch` the number of launches that have used it, this one
+// included.  All launches that share a counter must have the same rows, Nq and H (same grid).  The caller
+// orders the ranks around the launch: a barrier after the owners wrote their rows, one after the launch.
+extern "C" int ubm_attention_d32_gather_bias(const void* q, const void* k, const void* v,
+                                             const void* const* bias_bufs, const int* rows_per_gpu, int ngpus,
+                                             int me, void* done, unsigned int epoch, const void* gate, void* out,
+                                             const void* kmask, const void* kflags, int rows, int Nq, int Nk, int H,
+                                             long long ldb, long long ld_in, long long ld_gate, long long ld_mask,
+                                             int transpose_out, void* status, void* stream) {
+  if (rows < 4 || Nq <= 0 || Nk <= 0 || H <= 0 || ngpus < 1 || ngpus > 8 || me < 0 || me >= ngpus ||
+      bias_bufs == nullptr || (ld_gate & 15) || ldb < Nk || (ldb & 7))
+    return ubm::UBM_ERR_ARGUMENT;
+  ubm::AttnMask m;
+  m.kmask = kmask;
+  m.kflags = kflags;
+  m.ld_mask = ld_mask;
+  ubm::AttnGather g;
+  g.n = ngpus;
+  g.me = me;
+  g.src = bias_bufs;
+  g.rows = rows_per_gpu;
+  g.done = done;
+  g.epoch = epoch;
+  return ubm::launch_attention<32, 64, 4, true, 1, false>(q, k, v, bias_bufs[me], gate, out, rows, Nq, Nk, H, ldb,
+                                                          ld_in, ld_gate, transpose_out, m, status, stream, 0, nullptr,
+                                                          nullptr, 0, g);
 }
 
 // Pair-bias all-gather fused into the attention kernel (head dimension 32): the bias planes are row

@@ -121,7 +121,6 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   }
 }
 
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // Order of n-tiles in gather-once mode: shards are visited starting with this rank's own (no copy
 // needed), then rank+1, rank+2, ... so that the ranks pull from different owners at the same time.

@@ -63,6 +63,38 @@ def gemm_allgather_b(a: torch.Tensor, b_ptrs: Sequence[int], rows: Sequence[int]
     return out
 
 
+native.declare("ubm_attention_d32_gather_bias",
+               [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, ctypes.c_uint, c_void_p,
+                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_int, c_void_p,
+                c_void_p])
+
+
+class BiasGatherState:
+    """Counter and launch count of the in-kernel pair-bias gather (one per symmetric bias buffer)."""
+
+    def __init__(self, device):
+        self.done = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = 0
+
+
+def attention_gather_bias(q, k, v, bias_bufs: Sequence[int], rows_per_gpu: Sequence[int], me: int,
+                          state: BiasGatherState, gate, out, rows: int, N: int, H: int, ldb: int,
+                          transpose_out: bool = False, mask=None):
+    """Triangle-attention core whose launch also performs the all-gather of the pair-bias planes: ``bias_bufs[i]`` is
+    GPU i's [H, N, ldb] buffer (symmetric memory) holding the rows it owns; the kernel completes this GPU's buffer
+    from the peers' and attends on it.  Needs at least four rows."""
+    st = native.status_tensor(q.device)
+    state.epoch += 1
+    rc = native.lib().ubm_attention_d32_gather_bias(
+        native.ptr(q), native.ptr(k), native.ptr(v), _ptrs(bias_bufs), _ints(rows_per_gpu), len(rows_per_gpu), me,
+        native.ptr(state.done), state.epoch, native.ptr(gate), native.ptr(out),
+        native.ptr(None if mask is None else mask.add), native.ptr(None if mask is None else mask.flags), rows, N, N, H,
+        ldb, 0, 0, 0 if mask is None else mask.add.stride(0), 1 if transpose_out else 0, native.ptr(st),
+        native.current_stream(q.device))
+    native.check(rc, "ubm_attention_d32_gather_bias")
+    return out
+
+
 def attention_peer_bias(q, k, v, bias_ptrs: Sequence[int], peer_rows: Sequence[int], head_stride: int, gate, out,
                         rows: int, N: int, H: int, ldb: int):
     st = native.status_tensor(q.device)

@@ -7,8 +7,9 @@ the projected triangle-multiplication operands (``planes``) and the per-head tri
   trimul outgoing : projection (local rows) -> barrier -> contraction GEMM whose B tiles are TMA-loaded from
                     the owners' planes (all-gather fused into the GEMM) -> barrier -> output stage (local)
   trimul incoming : z^T rows by all-to-all, then the same three kernels on z^T, output stage on z
-  triatt starting : projection (q|k|v|gate rows + bias planes) -> barrier -> attention whose bias tiles
-                    are TMA-loaded from the owners' planes (bias all-gather fused) -> barrier -> output GEMM
+  triatt starting : projection (q|k|v|gate rows + this rank's rows of the bias planes) -> barrier -> attention
+                    launch whose prologue copies the peers' bias rows into the local planes with plain peer loads
+                    (the all-gather is part of the kernel; the tiles then read local memory) -> barrier -> output GEMM
   triatt ending   : the starting-node schedule on z^T rows, update transposed back by all-to-all
   transition      : local
 
@@ -52,6 +53,14 @@ class FusedRowPair:
         self.headbias = heap.alloc((heads, self.Rmax, self.Np), torch.bfloat16)
         self.planes.local.zero_()
         self.headbias.local.zero_()
+        # whole bias planes [H, N, Np] in symmetric memory: every rank writes the rows it owns into its own copy and
+        # the attention launch completes the copy from the peers' ("peer" mode: the all-gather is the kernel's prologue)
+        self.row0 = layout.rows(self.rank)[0]
+        self.hb_full = None
+        if gather == "peer" and self.world > 1 and min(self.counts) >= 0:
+            self.hb_full = heap.alloc((heads, self.N, self.Np), torch.bfloat16)
+            self.hb_full.local.zero_()
+            self._hb_state = peer.BiasGatherState(dev)
         self.x = torch.empty((128, self.Rmax, self.Np), dtype=torch.bfloat16, device=dev)
         self.qkvgo = torch.empty((5, self.Rmax * self.N, 128), dtype=torch.bfloat16, device=dev)
         self.dev = dev
@@ -108,16 +117,25 @@ class FusedRowPair:
         src = z_loc if starting else transpose_shard(z_loc, self.layout, self.comm)
         q, k, v, g, og = (self.qkvgo[i][: R * N] for i in range(5))
         lib = native.lib()
+        fused_gather = self.hb_full is not None and min(self.counts) >= 4
         if R > 0:
+            # in the fused-gather mode the projection writes this rank's bias rows straight into its rows of the
+            # whole planes (plane stride N rows); otherwise into the [H, Rmax, Np] shard buffer
+            hb_ptr = (self.hb_full.ptr(self.rank, self.row0 * Np * 2), N) if fused_gather else \
+                (native.ptr(self.headbias.local), Rmax)
             rc = lib.ubm_triatt_proj_rows(native.ptr(src), native.ptr(w.w), native.ptr(w.colsum), native.ptr(w.colbias),
                                           native.ptr(w.wb), native.ptr(w.wb_colsum), native.ptr(w.wb_colbias),
                                           native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(g),
-                                          native.ptr(self.headbias.local), 0, R, Rmax, N, Np, H, 0, native.ptr(st),
-                                          stream)
+                                          hb_ptr[0], 0, R, hb_ptr[1], N, Np, H, 0, native.ptr(st), stream)
             native.check(rc, "ubm_triatt_proj_rows")
         # the bias tiles are reused by every row pair: reading them in-kernel from the owner crosses NVLink once
         # per reuse, so only the "peer_direct" mode does that; otherwise the planes are gathered once
-        if self.gather == "peer_direct":
+        if fused_gather:
+            self.heap.barrier()                  # every owner's bias rows are written and visible
+            peer.attention_gather_bias(q, k, v, [self.hb_full.ptr(p) for p in range(self.world)], self.counts,
+                                       self.rank, self._hb_state, g, og, rows=R, N=N, H=H, ldb=Np)
+            self.heap.barrier()                  # nobody still reads my rows when the next projection overwrites them
+        elif self.gather == "peer_direct":
             self.heap.barrier()
             if R > 0:
                 peer.attention_peer_bias(q, k, v, [self.headbias.ptr(p) for p in range(self.world)], self.counts,
