@@ -43,6 +43,13 @@ def test_row_sharded_pair_block_on_four_gpus_with_ragged_rows(tmp_path):
 
 
 @pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("masked", [0, 1])
+def test_outer_product_mean_over_sequence_shards_reduce_scatter(tmp_path, masked):
+    log = _run("tests/multigpu/opm_seqshard_check.py", [256, 96, masked], 2, tmp_path)
+    assert f"OPM-SEQSHARD ok world=2 N=256 S=96 masked={masked}" in log, log[-2000:]
+
+
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
 def test_tensor_parallel_gemm_reduce_scatter_matches_nccl(tmp_path):
     log = _run("tests/multigpu/tp_gemm_check.py", [], 2, tmp_path)
     m = re.search(r"TP_GEMM_RS world=2 .* err_fused=([0-9.e+-]+) err_nccl=([0-9.e+-]+)", log)

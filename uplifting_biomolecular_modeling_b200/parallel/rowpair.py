@@ -187,6 +187,87 @@ def msa_layer_rows(layer, z_loc, m, msa_mask, layout: Layout, comm: Comm, rank: 
     return z_loc, m
 
 
+# ------------------------------------------------------------------------------- MSA sharded over sequences
+def seq_bounds(n_seq: int, world: int) -> List[Tuple[int, int]]:
+    """Contiguous sequence ranges of the ranks (the first ``n_seq % world`` ranks hold one more)."""
+    base, extra = divmod(n_seq, world)
+    out, a = [], 0
+    for r in range(world):
+        b = a + base + (1 if r < extra else 0)
+        out.append((a, b))
+        a = b
+    return out
+
+
+def opm_seqshard(m_loc, mask_loc, mod, layout: Layout, comm: Comm, n_seq: int, row_block: int = 64):
+    """Outer product mean with the MSA sharded over SEQUENCES: every rank contracts its own sequences for every
+    pair (i, j), projects the partial sum (the projection is linear) and the partial updates are reduce-scattered
+    onto the row owners - rank q receives the sum over ranks of rows [r0_q, r1_q).  This is the plain statement of
+    the schedule (partials exchanged with the comm surface's all-to-all and added in rank order); the GPU form puts
+    the scatter into the projection GEMM's epilogue (``FusedRowPair.opm_seqshard_``).  The reference keeps m
+    replicated or token-sharded and has no reduce-scatter (common/opt_core/opt_core/mem/rowpair/msa.py:157); a deep
+    MSA then costs every rank the whole [S, N, c_m] tensor, which this schedule divides by P.
+
+    m_loc: [1, S_loc, N, c_m]; mask_loc: [1, S_loc, N].  Returns the update of the local pair rows [R, N, c_z].
+    The mean divides by the per-pair count of unmasked sequences over ALL ranks."""
+    n = R.layer_norm(m_loc, mod.norm.weight, mod.norm.bias)
+    mk = mask_loc.unsqueeze(-1).to(n.dtype)
+    a = (F.linear(n, mod.proj_a.weight) * mk)[0]                     # [S_loc, N, c]
+    b = (F.linear(n, mod.proj_b.weight) * mk)[0]
+    N = a.shape[1]
+    cnt_part = torch.einsum("si,sj->ij", mask_loc[0].float(), mask_loc[0].float())      # [N, N] partial counts
+    parts_out, parts_cnt = [], []
+    for (q0, q1) in layout.bounds():
+        rows = []
+        for i0 in range(q0, q1, max(1, row_block)):
+            i1 = min(q1, i0 + max(1, row_block))
+            num = torch.einsum("sic,sjd->ijcd", a[:, i0:i1].float(), b.float()).reshape(i1 - i0, N, -1)
+            rows.append(F.linear(num.to(mod.proj_o.weight.dtype), mod.proj_o.weight))     # partial, no bias
+        parts_out.append(torch.cat(rows, 0) if rows else a.new_zeros((0, N, mod.proj_o.weight.shape[0])))
+        parts_cnt.append(cnt_part[q0:q1].contiguous())
+    got = comm.all_to_all([p.float().contiguous() for p in parts_out])        # from rank q: its partial of MY rows
+    gotc = comm.all_to_all(parts_cnt)
+    tot = got[0]
+    cnt = gotc[0]
+    for q in range(1, comm.world):                                             # rank order: deterministic
+        tot = tot + got[q]
+        cnt = cnt + gotc[q]
+    out = tot / cnt.clamp(min=1.0).unsqueeze(-1) + mod.proj_o.bias.float()
+    return out.to(m_loc.dtype)
+
+
+def pwa_seqshard(m_loc, z_loc, mod, layout: Layout, comm: Comm):
+    """Pair-weighted averaging with the MSA sharded over sequences: the softmax weights of the local pair rows are
+    all-gathered (every rank needs the weights of every query token), the average itself is local to the rank's
+    sequences - the MSA rows never travel."""
+    mn = R.layer_norm(m_loc, mod.norm_m.weight, mod.norm_m.bias)
+    zn = R.layer_norm(z_loc, mod.norm_z.weight, mod.norm_z.bias)
+    B, S, N, _ = mn.shape
+    H, c = mod.heads, mod.c_h
+    w_loc = torch.softmax(F.linear(zn, mod.proj_z.weight).float(), dim=1)                 # [R, N, H] over j
+    w = comm.all_gather_rows(w_loc.contiguous()).permute(2, 0, 1)                          # [H, N, N]
+    v = F.linear(mn, mod.proj_m.weight).view(B, S, N, H, c)[0]                             # [S_loc, N, H, c]
+    o = torch.einsum("hij,sjhd->sihd", w, v.float()).to(m_loc.dtype)
+    g = torch.sigmoid(F.linear(mn[0], mod.proj_g.weight))
+    return F.linear(g * o.reshape(S, N, H * c), mod.proj_o.weight).unsqueeze(0)
+
+
+def msa_layer_seqshard(layer, z_loc, m_loc, msa_mask_loc, layout: Layout, comm: Comm, rank: int, n_seq: int,
+                       pair_block=None, opm=None):
+    """One MSA block with the MSA sharded over sequences and the pair tensor over rows.  ``opm(m_loc, mask_loc,
+    module)`` may replace :func:`opm_seqshard` (the fused GEMM -> reduce-scatter form)."""
+    m_loc = m_loc + pwa_seqshard(m_loc, z_loc, layer.pair_weighted_averaging, layout, comm)
+    m_loc = m_loc + layer.msa_transition(m_loc)
+    upd = opm(m_loc, msa_mask_loc, layer.outer_product_mean) if opm is not None else \
+        opm_seqshard(m_loc, msa_mask_loc, layer.outer_product_mean, layout, comm, n_seq)
+    z_loc = z_loc + upd.to(z_loc.dtype)
+    if pair_block is not None:
+        z_loc = pair_block(layer.pairformer_layer, z_loc.contiguous())
+    else:
+        _, z_loc = pairformer_layer_rows(layer.pairformer_layer, None, z_loc, layout, comm, rank)
+    return z_loc, m_loc
+
+
 def gather_pair(z_loc, comm: Comm) -> torch.Tensor:
     return comm.all_gather_rows(z_loc)
 

@@ -161,6 +161,72 @@ class FusedRowPair:
         upd = transpose_shard(upd_t, self.layout, self.comm)
         return z_loc + upd
 
+    # ------------------------------------------------------------------ outer product mean, MSA sharded over sequences
+    def opm_seqshard_(self, m_loc: torch.Tensor, mask_loc: torch.Tensor, mod, n_seq: int,
+                      row_block: int = 128) -> torch.Tensor:
+        """Outer product mean of an MSA sharded over sequences, GEMM -> reduce-scatter in one kernel: per block of
+        pair rows every rank contracts its own sequences (MN-major tcgen05 GEMM with the blocked epilogue), then the
+        projection GEMM's epilogue stores the rank's partial update straight into the slot it owns in the memory of
+        the GPU that owns those rows (plain peer stores); a stream barrier orders the stores and the owner adds the P
+        slots in rank order.  m_loc: bf16 [1, S_loc, N, c_m]; mask_loc: [1, S_loc, N].  Returns the update of the
+        local rows, bf16 [R, N, c_z].  Plain statement: ``rowpair.opm_seqshard``."""
+        from ..ops import rows as _rows
+        from . import symm as _symm
+        P, me, N, dev = self.world, self.rank, self.N, self.dev
+        S_loc = m_loc.shape[1]
+        c = mod.c_hidden
+        cz = mod.proj_o.weight.shape[0]
+        if c != 32 or S_loc == 0 or (N * c) % 32:
+            raise ValueError("fused sequence-sharded outer product mean needs c_hidden = 32 and sequences on every rank")
+        rb = max(8, min(row_block, self.Rmax))
+        if not hasattr(self, "_opm_slots"):
+            self._opm_slots = [self.heap.alloc((P, rb * N, cz), torch.bfloat16) for _ in range(2)]
+            self._opm_t = torch.empty((rb * N, c * c), dtype=torch.bfloat16, device=dev)
+            self._opm_calls = 0
+        n = _rows.layernorm_rows(m_loc.contiguous(), mod.norm.weight, mod.norm.bias, mod.norm.eps)
+        mk = mask_loc.unsqueeze(-1).to(n.dtype)
+        a2 = (mod.proj_a(n) * mk)[0].reshape(S_loc, N * c)
+        b2 = (mod.proj_b(n) * mk)[0].reshape(S_loc, N * c)
+        wo = mod.proj_o.weight.detach().to(torch.bfloat16).contiguous()
+        full = bool(getattr(mod, "full_mask", False))
+        bias = mod.proj_o.bias.float().contiguous()
+        cnt_rows = None
+        if not full:
+            # pairs with masked sequences: per-pair counts over all ranks (the mean's denominator); the first GEMM
+            # carries 1 / S and the summed update is rescaled by S / count on c_z channels
+            import torch.distributed as dist
+            cnt = torch.einsum("si,sj->ij", mask_loc[0].float(), mask_loc[0].float())
+            dist.all_reduce(cnt)
+            r0, r1 = self.layout.rows(me)
+            cnt_rows = (float(n_seq) / cnt[r0:r1].clamp(min=1.0)).unsqueeze(-1)
+        out = torch.empty((max(self.rows, 0), N, cz), dtype=torch.bfloat16, device=dev)
+        st = native.status_tensor(dev)
+        stream = native.current_stream(dev)
+        lib = native.lib()
+        slot_elems = rb * N * cz
+        for q in range(P):
+            q0, q1 = self.layout.rows(q)
+            for i0 in range(q0, q1, rb):
+                i1 = min(q1, i0 + rb)
+                nr = (i1 - i0) * N
+                buf = self._opm_slots[self._opm_calls & 1]
+                self._opm_calls += 1
+                _gemm.gemm(a2[:, i0 * c:i1 * c], b2, mn_major=True, alpha=1.0 / n_seq, out=self._opm_t,
+                           c_blocked=(N * c * c, c, c * c))
+                dst = _symm.ptr_array([buf.ptr(q, me * slot_elems * 2)])
+                rc = lib.ubm_gemm_bf16_scatter_rows(native.ptr(self._opm_t), native.ptr(wo), dst, 1, nr, nr, cz, c * c,
+                                                    c * c, c * c, cz, 0, 1.0, native.ptr(st), stream)
+                native.check(rc, "ubm_gemm_bf16_scatter_rows")
+                self.heap.barrier()              # every rank's partial of this block is in the owner's slots
+                if q == me:
+                    o = out[i0 - q0:i1 - q0].view(nr, cz)
+                    rc = lib.ubm_sum_slots(native.ptr(buf.local), slot_elems, P, native.ptr(bias) if full else 0, 0,
+                                           native.ptr(o), nr, cz, stream)
+                    native.check(rc, "ubm_sum_slots")
+        if cnt_rows is not None and self.rows > 0:
+            out = (out.float() * cnt_rows + bias).to(torch.bfloat16)
+        return out
+
     # ------------------------------------------------------------------ one Pairformer block (pair part)
     def pair_block_(self, layer, z_loc: torch.Tensor) -> torch.Tensor:
         def packed(mod, maker):
