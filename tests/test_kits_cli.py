@@ -34,7 +34,7 @@ def test_registry_covers_the_reference_kits():
 def test_dry_run_lines_with_fake_gpu(capsys):
     act = base.Activation(registry.get("boltz2"), "fast", "cli", 1, probe=_b200(), environ={})
     act.apply(None, dry_run=True)
-    assert act.lines[0].startswith("[boltz2-opt] DRY-RUN mode=fast levers=sampler_graph,graph_verify,fused_transition,")
+    assert act.lines[0].startswith("[boltz2-opt] DRY-RUN mode=fast levers=sampler_graph,graph_verify,trunk_graph,fused_transition,")
     lever_lines = [l for l in act.lines if " LEVER " in l]
     assert any("name=fused_triatt state=on impl=pair_proj+attention_sm100@1 origin=core "
                "strategy=F1.kernel_fusion" in l for l in lever_lines)
@@ -156,3 +156,20 @@ def test_design_verb_runs_the_design_pipeline(tmp_path):
     assert "designs=2" in r.stderr and "verb=design" in r.stderr
     d = json.load(open(out / "design.json"))
     assert len(d["sequences_text"]) == 2 and len(d["sequences_text"][0]) == 24
+
+
+def test_resident_loop_over_a_directory_of_inputs(tmp_path):
+    """Several inputs through one activation: featurised ahead, predicted in order, written behind; a bad item is
+    reported and the others still run."""
+    inp = tmp_path / "in"
+    inp.mkdir()
+    for i, n in enumerate((12, 16)):
+        (inp / f"c{i}.json").write_text(json.dumps({"tokens": n, "msa_depth": 2}))
+    (inp / "broken.json").write_text(json.dumps({"msa_depth": 2}))
+    out = tmp_path / "o"
+    r = _run(["kits/boltz2/run.sh", "pred", "--mode", "off", "--model_config", "tiny", "--input", str(inp),
+              "--out_dir", str(out)])
+    assert r.returncode == 2, r.stderr[-1500:]                       # the broken item makes the run a usage error ...
+    assert "item=broken error=input" in r.stderr
+    assert (out / "c0" / "prediction.pt").exists() and (out / "c1" / "prediction.pt").exists()   # ... the rest ran
+    assert "RESIDENT items=2 failed=1" in r.stderr

@@ -89,6 +89,12 @@ class Predictor:
         if mode in ("fast", "big"):
             from .ops import dispatch
             dispatch.set_tier(mode)
+        if self.use_graphs and self.device.type == "cuda":
+            from .capture import graphs
+            self.model.trunk_graphs = graphs.GraphCache(policy=graphs.FixedK(1), verify=self.verify_graphs,
+                                                        budget=graphs.GraphByteBudget(4 << 30))
+        self.sample_chunk = int(os.environ.get("UBM_BIG_SAMPLE_CHUNK", "0")) if mode == "big" else 0
+        self.stage_peaks: Dict[str, Dict[str, int]] = {}
         self._graph = None
         self._graph_key = None
         self._pinned: Dict[str, torch.Tensor] = {}
@@ -236,10 +242,19 @@ class Predictor:
         timing = os.environ.get("UBM_STAGE_TIMES") == "1" and dev.type == "cuda"
         marks = []
 
+        census = self.mode == "big" and dev.type == "cuda"
+        if census:
+            from .mem import peak as _peak
+            _peak.reset(dev)
+
         def mark(name):
             if timing:
                 torch.cuda.synchronize(dev)
                 marks.append((name, time.perf_counter()))
+            if census and name != "start":
+                # per-stage peak of the allocator (``big`` only): what the memory levers are judged by
+                self.stage_peaks[name] = _peak.allocator_peak(dev)
+                _peak.reset(dev)
 
         mark("start")
         # features already on the device (a dict produced by to_device) skip the host copy; with
@@ -293,7 +308,18 @@ class Predictor:
         else:
             torch.manual_seed(self.seed if seed is None else seed)
         mark("sampler_setup")
-        x, _ = m.structure(feats, s, z, s_inputs, atom_c, atom_p, nsamp, steps, None, step_fn, prep)
+        if self.sample_chunk and nsamp > self.sample_chunk:
+            # ``big``: the samples are rolled out a chunk at a time (peak of the structure stage = one chunk); every
+            # chunk continues the same random stream, so the samples differ from an unchunked run's
+            from .mem import sample_loop
+            chunk_fn = self._step_fn(prep, feats, N, self.sample_chunk) if self.use_graphs else None
+
+            def roll(k0, k1):
+                fn = chunk_fn if (k1 - k0) == self.sample_chunk else None
+                return m.structure(feats, s, z, s_inputs, atom_c, atom_p, k1 - k0, steps, None, fn, prep)[0]
+            x = sample_loop.run(roll, None, nsamp, self.sample_chunk)["coords"].to(dev)
+        else:
+            x, _ = m.structure(feats, s, z, s_inputs, atom_c, atom_p, nsamp, steps, None, step_fn, prep)
         mark("sampler")
         out = {"coords": x}
         if confidence:

@@ -126,6 +126,15 @@ def _graph_verify(pred):
     return {"verify": 1}
 
 
+def _trunk_graph(pred):
+    """Pairformer stack passes of small inputs replay from a CUDA graph (capture once per shape, first replay
+    verified against eager, byte budget on the static buffers)."""
+    from ..capture import graphs
+    pred.model.trunk_graphs = graphs.GraphCache(policy=graphs.FixedK(1), verify=1,
+                                                budget=graphs.GraphByteBudget(4 << 30))
+    return {"max_tokens": pred.model.trunk_graph_max_tokens}
+
+
 def _cond_dedup(pred):
     """Design batches share one trunk pass and one set of step-invariant sampler tensors."""
     pred.cond_dedup = True
@@ -174,6 +183,7 @@ LEVERS: Dict[str, Lever] = {l.name: l for l in [
           apply=_fused(_kinds_dit, "fused_dit")),
     Lever("sampler_graph", "F2.graph_capture", "api.Predictor._step_fn", needs_gpu=True, apply=_flag("use_graphs")),
     Lever("graph_verify", "F2.graph_capture", "capture.graphs.verify", needs_gpu=True, apply=_graph_verify),
+    Lever("trunk_graph", "F2.graph_capture", "capture.graphs.GraphCache", needs_gpu=True, apply=_trunk_graph),
     Lever("chunk_pair_ops", "F5.memory", "models.pairformer row blocks", apply=_chunk_pair_ops),
     Lever("release_intermediates", "F5.memory", "api.Predictor.release", apply=_release),
     Lever("expandable_segments", "F5.memory", "mem.allocator", apply=_expandable, droppable=True),

@@ -13,7 +13,7 @@ from typing import Dict, Optional, Tuple
 
 # Every name below is a lever of kits/levers.py whose ``apply`` changes what runs; work that every mode does
 # (step-invariant hoists in the sampler, bf16 storage of the pair stack) is not a lever and is not listed.
-COFOLD_LEVERS_EXACT = ("sampler_graph", "graph_verify")
+COFOLD_LEVERS_EXACT = ("sampler_graph", "graph_verify", "trunk_graph")
 COFOLD_LEVERS_FAST = ("fused_transition", "fused_trimul", "fused_triatt", "fused_apb", "fused_opm", "fused_pwa",
                       "fused_dit")
 COFOLD_LEVERS_BIG = ("chunk_pair_ops", "release_intermediates", "expandable_segments", "rowpair_tp")

@@ -132,30 +132,86 @@ def _run_cofold(spec, act, args, allow_partial) -> int:
         act.refuse(str(e))
         return report.EXIT_NOT_ACTIVE
     act.register_exit()
+    # Resident loop: the model is built and activated once; inputs (one file, a comma list, or every .pt / .json of
+    # a directory) are featurised ahead on a helper thread, predicted on this thread, written behind on a writer
+    # thread (reference: <kit>_opt/worker.py + prefetch.py + writer.py of the cofolding kits).
+    from ..host import resident
     try:
-        feats = _load_features(args, pred.cfg, config)
+        items = _input_items(args)
     except InputError as e:
         report.emit(report.line(spec.tag, "USAGE", ("error", "input"), ("detail", report.token(str(e))[:200])))
         return act.finish(report.EXIT_USAGE, allow_partial, None)
-    t0 = time.time()
-    try:
+    multi = len(items) > 1
+    done, errors = [], []
+
+    def prepare(item):
+        ns = type(args)(**dict(vars(args), input=item[1]))
+        return item, _load_features(ns, pred.cfg, config)
+
+    def forward(prepared):
+        item, feats = prepared
+        t0 = time.time()
         out = pred.predict(feats)
-    except Exception as e:  # noqa: BLE001
-        report.emit(report.line(spec.tag, "FAILED", ("error", type(e).__name__), ("detail", report.token(str(e))[:200])))
-        return act.finish(report.EXIT_FAIL, allow_partial, args.out_dir)
-    dt = time.time() - t0
+        return {"out": out, "tokens": int(feats["token_feat"].shape[1]), "seconds": time.time() - t0}
+
+    def write(pair):
+        item, res = pair
+        out = res["out"]
+        if args.out_dir:
+            d = os.path.join(args.out_dir, item[0]) if multi else args.out_dir
+            os.makedirs(d, exist_ok=True)
+            torch.save({k: v for k, v in out.items()}, os.path.join(d, "prediction.pt"))
+            with open(os.path.join(d, "confidence.json"), "w") as f:
+                json.dump({"plddt_mean": float(out["plddt"].mean()) if "plddt" in out else None,
+                           "pae_mean": float(out["pae_mean"]) if "pae_mean" in out else None}, f)
+            if getattr(pred, "stage_peaks", None):
+                from ..mem import peak as _peak
+                _peak.write(d, pred.stage_peaks)
+        done.append(item[0])
+        report.emit(report.line(spec.tag, "DONE", ("item", item[0]), ("seconds", round(res["seconds"], 3)),
+                                ("tokens", res["tokens"]), ("samples", out["coords"].shape[0])))
+
+    def on_error(item, e):
+        errors.append((item[0], e))
+        kind = "input" if isinstance(e, InputError) else type(e).__name__
+        report.emit(report.line(spec.tag, "USAGE" if isinstance(e, InputError) else "FAILED", ("item", item[0]),
+                                ("error", kind), ("detail", report.token(str(e))[:200])))
+
+    stats = resident.run_resident(items, prepare, forward, write, workers=1, depth=2, on_error=on_error)
+    if multi:
+        report.emit(report.line(spec.tag, "RESIDENT", *stats.words().items()))
+    if errors:
+        bad_input = all(isinstance(e, InputError) for _, e in errors)
+        return act.finish(report.EXIT_USAGE if bad_input else report.EXIT_FAIL, allow_partial, args.out_dir)
     incomplete = None
     if args.out_dir:
-        os.makedirs(args.out_dir, exist_ok=True)
-        torch.save({k: v for k, v in out.items()}, os.path.join(args.out_dir, "prediction.pt"))
-        with open(os.path.join(args.out_dir, "confidence.json"), "w") as f:
-            json.dump({"plddt_mean": float(out["plddt"].mean()) if "plddt" in out else None,
-                       "pae_mean": float(out["pae_mean"]) if "pae_mean" in out else None}, f)
-        if not os.path.exists(os.path.join(args.out_dir, "prediction.pt")):
+        first = os.path.join(args.out_dir, items[0][0]) if multi else args.out_dir
+        if not os.path.exists(os.path.join(first, "prediction.pt")):
             incomplete = "prediction.pt missing"
-    report.emit(report.line(spec.tag, "DONE", ("seconds", round(dt, 3)), ("tokens", feats["token_feat"].shape[1]),
-                            ("samples", out["coords"].shape[0])))
     return act.finish(0, allow_partial, args.out_dir, incomplete)
+
+
+def _input_items(args):
+    """(name, path) pairs of a run: ``--input`` may name one file, several separated by commas, or a directory whose
+    ``.pt`` / ``.json`` files are taken in sorted order; without ``--input`` one synthetic item."""
+    if not args.input:
+        return [("synthetic", None)]
+    paths = []
+    for part in str(args.input).split(","):
+        part = part.strip()
+        if os.path.isdir(part):
+            found = sorted(f for f in os.listdir(part) if f.endswith((".pt", ".json")))
+            if not found:
+                raise InputError(f"--input {part}: directory holds no .pt / .json input")
+            paths += [os.path.join(part, f) for f in found]
+        elif part:
+            paths.append(part)
+    names, seen = [], {}
+    for pth in paths:
+        base = os.path.splitext(os.path.basename(pth))[0] or "input"
+        seen[base] = seen.get(base, 0) + 1
+        names.append(base if seen[base] == 1 else f"{base}_{seen[base]}")
+    return list(zip(names, paths))
 
 
 def _weights_file(weights_dir):

@@ -210,6 +210,10 @@ class CofoldModel(nn.Module):
         self.confidence_module = ConfidenceModule(cfg)
         self.fused = False
         self.workspace: dict = {}
+        # the ``trunk_graph`` lever: Pairformer stack passes replayed from a CUDA graph below this token count (the
+        # stack is launch-bound there: ~40 launches per block); None = eager
+        self.trunk_graphs = None
+        self.trunk_graph_max_tokens = 512
 
     # ------------------------------------------------------------------ implementation switch
     def set_impl(self, impl: str, kinds=None) -> int:
@@ -256,8 +260,16 @@ class CofoldModel(nn.Module):
                 tf["asym_id"] = feats["chain_id"][0]
                 z = z + self.template_embedder(z, tf).to(z.dtype)
             z = self.msa_module(z, s_inputs, feats["msa_feat"], feats["msa_mask"], tmask, pmask)
-            s, z = self.pairformer_module(s, z, smask, pmask)
+            if self.trunk_graphs is not None and smask is None and z.is_cuda and \
+                    z.shape[1] <= self.trunk_graph_max_tokens:
+                # capture-once, replay-many, first replay checked bit for bit against eager (capture.graphs)
+                s, z = self.trunk_graphs.run(self._stack_unmasked, s, z)
+            else:
+                s, z = self.pairformer_module(s, z, smask, pmask)
         return s, z
+
+    def _stack_unmasked(self, s, z):
+        return self.pairformer_module(s, z, None, None)
 
     def structure(self, feats, s, z, s_inputs, atom_c, atom_p, samples=None, steps=None, generator=None,
                   step_fn=None, prep=None):
