@@ -173,3 +173,26 @@ def test_resident_loop_over_a_directory_of_inputs(tmp_path):
     assert "item=broken error=input" in r.stderr
     assert (out / "c0" / "prediction.pt").exists() and (out / "c1" / "prediction.pt").exists()   # ... the rest ran
     assert "RESIDENT items=2 failed=1" in r.stderr
+
+
+def test_install_places_the_pth_hook_and_the_variable_activates_in_process(tmp_path):
+    site_dir = tmp_path / "site"
+    r = _run(["kits/boltz2/run.sh", "install", "--pth-dir", str(site_dir)])
+    assert r.returncode == 0 and "pth=" in r.stderr, r.stderr[-1500:]
+    pth = site_dir / "boltz2_opt_autoload.pth"
+    assert pth.exists() and "BOLTZ2_OPT" in pth.read_text()
+    code = (f"import site, sys; site.addsitedir({str(site_dir)!r}); "
+            "import uplifting_biomolecular_modeling_b200.models.cofold as c; "
+            "print('loaded', 'uplifting_biomolecular_modeling_b200.kits.base' in sys.modules)")
+    env = {k: v for k, v in os.environ.items() if not k.startswith("BOLTZ2_OPT")}
+    # variable unset: the hook imports nothing of the kit layer
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd=str(tmp_path))
+    assert r.returncode == 0 and "loaded False" in r.stdout, r.stderr[-1500:]
+    # an unknown mode is refused before anything runs
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True,
+                       env=dict(env, BOLTZ2_OPT="turbo"), cwd=str(tmp_path))
+    assert r.returncode == 3 and "NOT ACTIVE" in r.stderr
+    # a mode whose gates fail on this machine (no B200 here) is NOT ACTIVE with exit 3 at the trigger import
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True,
+                       env=dict(env, BOLTZ2_OPT="fast", CUDA_VISIBLE_DEVICES=""), cwd=str(tmp_path))
+    assert r.returncode == 3 and "[boltz2-opt] NOT ACTIVE" in r.stderr, (r.returncode, r.stderr[-1500:])

@@ -183,6 +183,25 @@ def enable(kit: str, mode: Optional[str] = None, strict: bool = True, trigger: O
     return act
 
 
+def predictor(kit: str, config: Optional[str] = None, device: Optional[str] = None, **kw):
+    """A :class:`~..api.Predictor` for a cofolding kit under the kit's active mode (``enable`` or ``<KIT>_OPT``): the
+    model is built on its plain statements and the mode's levers are applied to it one by one.  Without an active
+    mode the predictor runs ``off``."""
+    import torch
+    from .. import api
+    spec = get(kit)
+    act = _ACTIVE.get(kit)
+    dev = device or ("cuda:0" if torch.cuda.is_available() else "cpu")
+    pred = api.Predictor(config or spec.config, mode="off", device=dev,
+                         dtype=torch.bfloat16 if dev != "cpu" else torch.float32, **kw)
+    if act is not None and act.mode != "off":
+        pred.set_mode(act.mode)
+        applied = Activation(spec, act.mode, act.source, 1, act.strict, act.environ, act.probe)
+        applied.apply(pred)
+        _ACTIVE[kit] = applied
+    return pred
+
+
 def status(kit: str) -> dict:
     act = _ACTIVE.get(kit)
     if act is None:

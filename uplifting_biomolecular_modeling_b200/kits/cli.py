@@ -43,6 +43,9 @@ def _parser(kit: str) -> argparse.ArgumentParser:
     ap.add_argument("--max_new_tokens", type=int, default=32)
     ap.add_argument("--specdec", type=int, default=0,
                     help="evo2 generate: k > 0 decodes speculatively with k proposals per round from a draft model")
+    ap.add_argument("--pth-dir", dest="pth_dir", default=None,
+                    help="install: site directory that receives <kit>_opt_autoload.pth (in-process activation by "
+                         "<KIT>_OPT=<mode>)")
     ap.add_argument("--upstream-fix", dest="upstream_fix", default=None,
                     help="comma-separated corrections to the stock model that change outputs on purpose")
     return ap
@@ -111,7 +114,16 @@ def _install(spec, args) -> int:
     except Exception as e:  # noqa: BLE001
         report.emit(report.line(spec.tag, "INSTALL", ("state", "failed"), ("reason", report.token(str(e))[:160])))
         return report.EXIT_FAIL
-    report.emit(report.line(spec.tag, "INSTALL", ("state", "ok"), ("library", path), ("weights", args.weights)))
+    pth = None
+    if args.pth_dir:
+        from . import autoload_hook
+        try:
+            pth = autoload_hook.place_pth(spec.name, args.pth_dir)
+        except OSError as e:
+            report.emit(report.line(spec.tag, "INSTALL", ("state", "failed"), ("reason", report.token(str(e))[:160])))
+            return report.EXIT_FAIL
+    report.emit(report.line(spec.tag, "INSTALL", ("state", "ok"), ("library", path), ("weights", args.weights),
+                            ("pth", pth)))
     if args.weights:
         os.makedirs(args.weights, exist_ok=True)
     return report.EXIT_OK

@@ -119,6 +119,9 @@ def main(argv=None) -> int:
         peak = 0
     report.emit(report.line(TAG, "MEMSTATS", ("rank", comm.rank), ("peak_bytes", peak),
                             ("seconds", round(time.time() - t0, 3))))
+    # one census point of the per-rank model peak = a(N) + b(N) / P (fitted over runs at several P by mem.peak.fit_a_b)
+    from ..mem import peak as _peak
+    sys.stderr.write(_peak.census_line(TAG, "trunk", comm.rank, int(peak), N, comm.world) + "\n")
     peaks = comm.all_gather(torch.tensor([float(peak)], device=dev))
     if a.json and comm.rank == 0:
         print("BIGMODE " + json.dumps({"n_gpus": comm.world, "tokens": N, "blocks": len(model.pairformer_module.layers),
