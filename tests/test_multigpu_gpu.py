@@ -37,6 +37,13 @@ def test_row_sharded_pair_block_matches_single_gpu(tmp_path, gather):
 
 
 @pytest.mark.skipif(_gpus() < 4, reason="needs four GPUs")
+def test_row_sharded_pair_block_on_four_gpus_even_rows(tmp_path):
+    """128 rows per rank: the transposed projections read z columns from the owners inside the kernel."""
+    log = _run("tests/multigpu/rowpair_fused_check.py", [512, 0, "peer"], 4, tmp_path)
+    assert "ROWPAIR-FUSED ok world=4 N=512" in log, log[-2000:]
+
+
+@pytest.mark.skipif(_gpus() < 4, reason="needs four GPUs")
 def test_row_sharded_pair_block_on_four_gpus_with_ragged_rows(tmp_path):
     log = _run("tests/multigpu/rowpair_fused_check.py", [328, 0, "peer"], 4, tmp_path)
     assert "ROWPAIR-FUSED ok world=4 N=328" in log, log[-2000:]

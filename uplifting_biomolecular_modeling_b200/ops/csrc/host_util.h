@@ -110,4 +110,44 @@ inline int set_smem(K kernel, int bytes) {
   return UBM_OK;
 }
 
+
+// Transposed peer source of the projection kernels (row-sharded pair tensor): the rows this GPU projects are
+// COLUMNS of z, z^T[i][k] = z[k][i], and z[k] lives on the GPU that owns row k.  m[q] is a 3-d tensor map over GPU
+// q's shard bf16 [rows_q][N][128] (box 64 channels x 1 column x 128 rows); a 128-entry tile (fixed column, 128
+// consecutive k) is fetched from its owner with a plain TMA load - shard boundaries are multiples of 128, so a tile
+// has one owner.  row0[q] = first row of shard q (row0[n] = N); col0 = first column this GPU projects.
+constexpr int kMaxSrcPeers = 8;
+struct PeerSrcMaps {
+  CUtensorMap m[kMaxSrcPeers];
+};
+struct PeerSrc {
+  int n;                        // 0 = local row-major source
+  int row0[kMaxSrcPeers + 1];
+  int col0;
+};
+
+inline int make_peer_src(PeerSrcMaps* maps, PeerSrc* src, const void* const* z_ptrs, const int* rows, int npeers,
+                         int me, int N, const CUtensorMap& filler) {
+  if (npeers < 1 || npeers > kMaxSrcPeers || me < 0 || me >= npeers || (N & 127)) return UBM_ERR_ARGUMENT;
+  src->n = npeers;
+  int row = 0;
+  for (int q = 0; q < kMaxSrcPeers; ++q) maps->m[q] = filler;
+  for (int q = 0; q < npeers; ++q) {
+    src->row0[q] = row;
+    if (q == me) src->col0 = row;
+    if (rows[q] < 0 || (rows[q] & 127 && q + 1 < npeers)) return UBM_ERR_ARGUMENT;
+    if (rows[q] > 0) {
+      uint64_t d[3] = {128, (uint64_t)N, (uint64_t)rows[q]};
+      uint64_t st[2] = {128 * 2, (uint64_t)N * 128 * 2};
+      uint32_t b[3] = {64, 1, 128};
+      int rc = make_tmap(&maps->m[q], z_ptrs[q], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d, st, b,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc) return rc;
+    }
+    row += rows[q];
+  }
+  for (int q = npeers; q <= kMaxSrcPeers; ++q) src->row0[q] = row;
+  return row == N ? UBM_OK : UBM_ERR_ARGUMENT;
+}
+
 }  // namespace ubm

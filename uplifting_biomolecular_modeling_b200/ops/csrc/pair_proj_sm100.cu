@@ -51,6 +51,7 @@ struct PairProjParams {
   float* stats_out;  // optional [R][2] (mu, rstd) of the input rows, or null
   KernelStatus* status;
   int num_tiles;
+  PeerSrc src;       // src.n > 0: the input rows are columns of z fetched from their owners (see host_util.h)
 };
 
 // Optional timeline (build with -DUBM_PP_TIMELINE): CTA 0 stamps clock64 at fixed points of its first tiles
@@ -68,7 +69,8 @@ __device__ long long g_pp_timeline[4 * kPPTlTiles * 8];
 
 template <int MODE>
 __global__ void __launch_bounds__(320, 1)
-pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, PairProjParams p) {
+pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
+                 const __grid_constant__ PeerSrcMaps peers, PairProjParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sW = smem;                               // 128 KB
@@ -139,8 +141,21 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         if (*abort_flag) break;
         uint8_t* dst = sX + stage * kPPXBytes;
         mbar_expect_tx(&x_full[stage], kPPXBytes);
-        tma_load_2d(dst, &tmX, &x_full[stage], 0, t * kPPRows);
-        tma_load_2d(dst + 16384, &tmX, &x_full[stage], 64, t * kPPRows);
+        if (p.src.n > 0) {
+          // transposed source: tile = (column col0 + i of z, rows k0 .. k0 + 127), fetched from the owner of k0
+          const int tiles_per_row = p.N / kPPRows;
+          const int i = t / tiles_per_row;
+          const int k0 = (t - i * tiles_per_row) * kPPRows;
+          int q = 0;
+#pragma unroll
+          for (int j = 1; j < kMaxSrcPeers; ++j)
+            if (j < p.src.n && k0 >= p.src.row0[j]) q = j;
+          tma_load_3d(dst, &peers.m[q], &x_full[stage], 0, p.src.col0 + i, k0 - p.src.row0[q]);
+          tma_load_3d(dst + 16384, &peers.m[q], &x_full[stage], 64, p.src.col0 + i, k0 - p.src.row0[q]);
+        } else {
+          tma_load_2d(dst, &tmX, &x_full[stage], 0, t * kPPRows);
+          tma_load_2d(dst + 16384, &tmX, &x_full[stage], 64, t * kPPRows);
+        }
         if (++stage == kPPStages) {
           stage = 0;
           phase ^= 1u;
@@ -337,13 +352,21 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 constexpr int kPPSmemBytes = kPPWBytes + kPPStages * kPPXBytes + (512 + 512 + kPPMaxHeads * 128) * 4 + 256 + 1024;
 
 template <int MODE>
-static int launch_pair_proj(const void* x, const void* w, PairProjParams p, cudaStream_t stream) {
+static int launch_pair_proj(const void* x, const void* w, PairProjParams p, cudaStream_t stream,
+                            const void* const* z_ptrs = nullptr, const int* peer_rows = nullptr, int npeers = 0,
+                            int me = 0) {
   CUtensorMap tmX, tmW;
   uint64_t dX[2] = {(uint64_t)kPPC, (uint64_t)p.R};
   uint64_t sX[1] = {(uint64_t)kPPC * 2};
   uint32_t bX[2] = {64, kPPRows};
   int rc = make_tmap(&tmX, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dX, sX, bX, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
+  PeerSrcMaps maps;
+  for (int q = 0; q < kMaxSrcPeers; ++q) maps.m[q] = tmX;
+  if (npeers > 0) {
+    rc = make_peer_src(&maps, &p.src, z_ptrs, peer_rows, npeers, me, p.N, tmX);
+    if (rc) return rc;
+  }
   uint64_t dW[2] = {(uint64_t)kPPC, 512};
   uint64_t sW[1] = {(uint64_t)kPPC * 2};
   uint32_t bW[2] = {64, 256};
@@ -354,7 +377,7 @@ static int launch_pair_proj(const void* x, const void* w, PairProjParams p, cuda
   rc = set_smem(kern, kPPSmemBytes);
   if (rc) return rc;
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  kern<<<grid, 320, kPPSmemBytes, stream>>>(tmX, tmW, p);
+  kern<<<grid, 320, kPPSmemBytes, stream>>>(tmX, tmW, maps, p);
   UBM_CHECK_LAUNCH("pair_proj_kernel");
   return UBM_OK;
 }
@@ -364,10 +387,11 @@ static int launch_pair_proj(const void* x, const void* w, PairProjParams p, cuda
 // w: [512][128] bf16 = rows [q; k; v; g] (gamma folded, q pre-scaled by 1/sqrt(d)).
 // wb: fp32 [H][128] head-bias weights (gamma folded); wb_colsum/wb_colbias fp32 [H].
 // q,k,v,g: bf16 [N*N][128]; headbias: bf16 [H][N][Np].
-extern "C" int ubm_triatt_proj_rows(const void* z, const void* w, const void* colsum, const void* colbias,
+static int triatt_proj_impl(const void* z, const void* w, const void* colsum, const void* colbias,
                                     const void* wb, const void* wb_colsum, const void* wb_colbias, void* q, void* k,
                                     void* v, void* g, void* headbias, void* stats_out, int rows, int plane_rows, int N,
-                                    int Np, int H, int transpose_out, void* status, void* stream) {
+                                    int Np, int H, int transpose_out, void* status, void* stream,
+                                    const void* const* z_ptrs, const int* peer_rows, int npeers, int me) {
   using namespace ubm;
   if (N <= 0 || rows <= 0 || plane_rows < rows || Np < N || (Np & 7) || H <= 0 || H > kPPMaxHeads)
     return UBM_ERR_ARGUMENT;
@@ -392,7 +416,31 @@ extern "C" int ubm_triatt_proj_rows(const void* z, const void* w, const void* co
   p.transpose_out = transpose_out;
   p.stats_out = static_cast<float*>(stats_out);
   p.status = static_cast<KernelStatus*>(status);
-  return launch_pair_proj<MODE_TRIATT>(z, w, p, static_cast<cudaStream_t>(stream));
+  return launch_pair_proj<MODE_TRIATT>(z, w, p, static_cast<cudaStream_t>(stream), z_ptrs, peer_rows, npeers, me);
+}
+
+extern "C" int ubm_triatt_proj_rows(const void* z, const void* w, const void* colsum, const void* colbias,
+                                    const void* wb, const void* wb_colsum, const void* wb_colbias, void* q, void* k,
+                                    void* v, void* g, void* headbias, void* stats_out, int rows, int plane_rows, int N,
+                                    int Np, int H, int transpose_out, void* status, void* stream) {
+  return triatt_proj_impl(z, w, colsum, colbias, wb, wb_colsum, wb_colbias, q, k, v, g, headbias, stats_out, rows,
+                          plane_rows, N, Np, H, transpose_out, status, stream, nullptr, nullptr, 0, 0);
+}
+
+// The ending-node form on a row-sharded pair tensor: this GPU projects COLUMNS [col0, col0 + rows) of z, where
+// col0 is the first row it owns.  z_ptrs[q] = GPU q's shard bf16 [peer_rows[q]][N][128] (symmetric memory, written
+// and made visible before this launch); the kernel fetches every 128-entry tile from its owner with a plain TMA
+// load (no multicast), so the distributed transpose and the LayerNorm + q|k|v|gate + head-bias projection are one
+// kernel.  N and the shard boundaries must be multiples of 128.  Outputs as ubm_triatt_proj_rows.
+extern "C" int ubm_triatt_proj_rows_peer(const void* const* z_ptrs, const int* peer_rows, int npeers, int me,
+                                         const void* w, const void* colsum, const void* colbias, const void* wb,
+                                         const void* wb_colsum, const void* wb_colbias, void* q, void* k, void* v,
+                                         void* g, void* headbias, int rows, int plane_rows, int N, int Np, int H,
+                                         void* status, void* stream) {
+  if (z_ptrs == nullptr || peer_rows == nullptr || npeers < 1 || me < 0 || me >= npeers || rows != peer_rows[me])
+    return ubm::UBM_ERR_ARGUMENT;
+  return triatt_proj_impl(z_ptrs[me], w, colsum, colbias, wb, wb_colsum, wb_colbias, q, k, v, g, headbias, nullptr,
+                          rows, plane_rows, N, Np, H, 0, status, stream, z_ptrs, peer_rows, npeers, me);
 }
 
 #ifdef UBM_PP_TIMELINE

@@ -41,11 +41,12 @@ struct TrimulProjParams {
   __nv_bfloat16* planes;  // [2][128][plane_rows][Np]
   float* stats_out;       // optional [R][2]
   KernelStatus* status;
+  PeerSrc src;            // src.n > 0: the input rows are columns of z fetched from their owners (see host_util.h)
 };
 
 __global__ void __launch_bounds__(320, 1)
 trimul_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
-                   TrimulProjParams p) {
+                   const __grid_constant__ PeerSrcMaps peers, TrimulProjParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sW = smem;                               // 128 KB
@@ -105,8 +106,18 @@ trimul_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         if (*abort_flag) break;
         uint8_t* dst = sX + stage * kTPXBytes;
         mbar_expect_tx(&x_full[stage], kTPXBytes);
-        tma_load_2d(dst, &tmX, &x_full[stage], 0, flat);
-        tma_load_2d(dst + 16384, &tmX, &x_full[stage], 64, flat);
+        if (p.src.n > 0) {
+          // transposed source: tile = (column col0 + i of z, rows s0 .. s0 + 127), fetched from the owner of s0
+          int q = 0;
+#pragma unroll
+          for (int j = 1; j < kMaxSrcPeers; ++j)
+            if (j < p.src.n && s0 >= p.src.row0[j]) q = j;
+          tma_load_3d(dst, &peers.m[q], &x_full[stage], 0, p.src.col0 + i, s0 - p.src.row0[q]);
+          tma_load_3d(dst + 16384, &peers.m[q], &x_full[stage], 64, p.src.col0 + i, s0 - p.src.row0[q]);
+        } else {
+          tma_load_2d(dst, &tmX, &x_full[stage], 0, flat);
+          tma_load_2d(dst + 16384, &tmX, &x_full[stage], 64, flat);
+        }
         if (++stage == kTPStages) {
           stage = 0;
           phase ^= 1u;
@@ -295,9 +306,10 @@ constexpr int kTPSmemBytes = kTPWBytes + kTPStages * kTPXBytes + 2 * 2 * 3 * 128
 // the LayerNorm gamma.  colsum/colbias: fp32 [512].  mask: fp32 [rows*N] or null.
 // planes: bf16 [2][128][plane_rows][Np] (Np multiple of 8, >= N); entries N..Np-1 of a row are written as zeros
 // up to the end of the last 128-wide tile.
-extern "C" int ubm_trimul_proj_rows(const void* z, const void* w, const void* colsum, const void* colbias,
+static int trimul_proj_impl(const void* z, const void* w, const void* colsum, const void* colbias,
                                     const void* mask, void* planes, void* stats_out, int rows, int plane_rows, int N,
-                                    int Np, void* status, void* stream) {
+                                    int Np, void* status, void* stream, const void* const* z_ptrs,
+                                    const int* peer_rows, int npeers, int me) {
   using namespace ubm;
   if (N <= 0 || rows <= 0 || plane_rows < rows || Np < N || (Np & 7)) return UBM_ERR_ARGUMENT;
   TrimulProjParams p = {};
@@ -326,12 +338,40 @@ extern "C" int ubm_trimul_proj_rows(const void* z, const void* w, const void* co
   uint32_t bW[2] = {64, 256};
   rc = make_tmap(&tmW, w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dW, sW, bW, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
+  PeerSrcMaps maps;
+  for (int q = 0; q < kMaxSrcPeers; ++q) maps.m[q] = tmX;
+  if (npeers > 0) {
+    rc = make_peer_src(&maps, &p.src, z_ptrs, peer_rows, npeers, me, N, tmX);
+    if (rc) return rc;
+  }
   rc = set_smem(trimul_proj_kernel, kTPSmemBytes);
   if (rc) return rc;
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  trimul_proj_kernel<<<grid, 320, kTPSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmX, tmW, p);
+  trimul_proj_kernel<<<grid, 320, kTPSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmX, tmW, maps, p);
   UBM_CHECK_LAUNCH("trimul_proj_kernel");
   return UBM_OK;
+}
+
+extern "C" int ubm_trimul_proj_rows(const void* z, const void* w, const void* colsum, const void* colbias,
+                                    const void* mask, void* planes, void* stats_out, int rows, int plane_rows, int N,
+                                    int Np, void* status, void* stream) {
+  return trimul_proj_impl(z, w, colsum, colbias, mask, planes, stats_out, rows, plane_rows, N, Np, status, stream,
+                          nullptr, nullptr, 0, 0);
+}
+
+// The incoming-edge form on a row-sharded pair tensor: this GPU projects COLUMNS [col0, col0 + rows) of z (col0 =
+// first row it owns), reading every 128-entry tile of a column from the GPU that owns those rows with a plain TMA
+// load (no multicast): the distributed transpose and the LayerNorm + gated a / b projections are one kernel.
+// z_ptrs[q] = GPU q's shard bf16 [peer_rows[q]][N][128] in symmetric memory; N and shard boundaries multiples of
+// 128.  mask, if given, is this GPU's fp32 [rows][N] mask of the TRANSPOSED rows.  Outputs as ubm_trimul_proj_rows.
+extern "C" int ubm_trimul_proj_rows_peer(const void* const* z_ptrs, const int* peer_rows, int npeers, int me,
+                                         const void* w, const void* colsum, const void* colbias, const void* mask,
+                                         void* planes, int rows, int plane_rows, int N, int Np, void* status,
+                                         void* stream) {
+  if (z_ptrs == nullptr || peer_rows == nullptr || npeers < 1 || me < 0 || me >= npeers || rows != peer_rows[me])
+    return ubm::UBM_ERR_ARGUMENT;
+  return trimul_proj_impl(z_ptrs[me], w, colsum, colbias, mask, planes, nullptr, rows, plane_rows, N, Np, status,
+                          stream, z_ptrs, peer_rows, npeers, me);
 }
 
 extern "C" int ubm_trimul_proj(const void* z, const void* w, const void* colsum, const void* colbias, const void* mask,

@@ -69,6 +69,12 @@ native.declare("ubm_attention_d32_gather_bias",
                 c_void_p])
 
 
+native.declare("ubm_triatt_proj_rows_peer",
+               [c_void_p, c_void_p, c_int, c_int] + [c_void_p] * 11 + [c_int] * 5 + [c_void_p, c_void_p])
+native.declare("ubm_trimul_proj_rows_peer",
+               [c_void_p, c_void_p, c_int, c_int] + [c_void_p] * 5 + [c_int] * 4 + [c_void_p, c_void_p])
+
+
 class BiasGatherState:
     """Counter and launch count of the in-kernel pair-bias gather (one per symmetric bias buffer)."""
 

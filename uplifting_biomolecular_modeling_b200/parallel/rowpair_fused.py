@@ -6,11 +6,14 @@ the projected triangle-multiplication operands (``planes``) and the per-head tri
 
   trimul outgoing : projection (local rows) -> barrier -> contraction GEMM whose B tiles are TMA-loaded from
                     the owners' planes (all-gather fused into the GEMM) -> barrier -> output stage (local)
-  trimul incoming : z^T rows by all-to-all, then the same three kernels on z^T, output stage on z
+  trimul incoming : the projection kernel fetches its input tiles - columns of z - from the owners' shards
+                    (distributed transpose + LayerNorm + gated projections in one kernel), then the outgoing
+                    schedule; all-to-all + local projection when N or a shard is not a multiple of 128
   triatt starting : projection (q|k|v|gate rows + this rank's rows of the bias planes) -> barrier -> attention
                     launch whose prologue copies the peers' bias rows into the local planes with plain peer loads
                     (the all-gather is part of the kernel; the tiles then read local memory) -> barrier -> output GEMM
-  triatt ending   : the starting-node schedule on z^T rows, update transposed back by all-to-all
+  triatt ending   : projection fetching columns of z from the owners (as above), attention, output GEMM, the
+                    update transposed back by all-to-all
   transition      : local
 
 The barriers are stream-ordered kernels with bounded waits (``parallel.symm``).  The two transposes use
@@ -61,6 +64,12 @@ class FusedRowPair:
             self.hb_full = heap.alloc((heads, self.N, self.Np), torch.bfloat16)
             self.hb_full.local.zero_()
             self._hb_state = peer.BiasGatherState(dev)
+        # "peer" mode, N and every shard a multiple of 128: the projections of the transposed forms (incoming
+        # triangle multiplication, ending-node attention) fetch their input tiles - columns of z - from the owners'
+        # shards themselves, so z shards are staged in symmetric memory and no all-to-all precedes the projection
+        self.zsym = None
+        if gather == "peer" and self.world > 1 and self.N % 128 == 0 and all(c % 128 == 0 and c > 0 for c in self.counts):
+            self.zsym = heap.alloc((self.Rmax, self.N, 128), torch.bfloat16)
         self.x = torch.empty((128, self.Rmax, self.Np), dtype=torch.bfloat16, device=dev)
         self.qkvgo = torch.empty((5, self.Rmax * self.N, 128), dtype=torch.bfloat16, device=dev)
         self.dev = dev
@@ -71,13 +80,21 @@ class FusedRowPair:
         R, N, Np, Rmax = self.rows, self.N, self.Np, self.Rmax
         st = native.status_tensor(self.dev)
         stream = native.current_stream(self.dev)
-        src = z_loc if outgoing else transpose_shard(z_loc, self.layout, self.comm)
         lib = native.lib()
-        if R > 0:
-            rc = lib.ubm_trimul_proj_rows(native.ptr(src), native.ptr(w.w_in), native.ptr(w.in_colsum),
-                                          native.ptr(w.in_colbias), 0, native.ptr(self.planes.local), 0, R, Rmax, N, Np,
-                                          native.ptr(st), stream)
-            native.check(rc, "ubm_trimul_proj_rows")
+        if not outgoing and self.zsym is not None:
+            # transpose + LayerNorm + gated projections in one kernel: tiles of z^T come from the owners' shards
+            self._stage_z(z_loc)
+            rc = lib.ubm_trimul_proj_rows_peer(self._z_ptrs(), self._counts_arr(), self.world, self.rank,
+                                               native.ptr(w.w_in), native.ptr(w.in_colsum), native.ptr(w.in_colbias),
+                                               0, native.ptr(self.planes.local), R, Rmax, N, Np, native.ptr(st), stream)
+            native.check(rc, "ubm_trimul_proj_rows_peer")
+        else:
+            src = z_loc if outgoing else transpose_shard(z_loc, self.layout, self.comm)
+            if R > 0:
+                rc = lib.ubm_trimul_proj_rows(native.ptr(src), native.ptr(w.w_in), native.ptr(w.in_colsum),
+                                              native.ptr(w.in_colbias), 0, native.ptr(self.planes.local), 0, R, Rmax, N,
+                                              Np, native.ptr(st), stream)
+                native.check(rc, "ubm_trimul_proj_rows")
         xv = self.x.view(-1)[: 128 * max(R, 1) * Np].view(128, max(R, 1), Np)   # [128][rows][Np] for the output stage
         a_loc = self.planes.local[0][:, :R, :N]
         if self.gather in ("peer", "peer_direct"):
@@ -109,16 +126,46 @@ class FusedRowPair:
             return out
         return z_loc
 
+    # ------------------------------------------------------------------ z shards readable by the peers
+    def _stage_z(self, z_loc: torch.Tensor) -> None:
+        """Copy this rank's rows of z into its symmetric staging buffer and order the ranks: after the barrier
+        every shard is written and visible, and (the barrier being the first since the previous reader's last
+        barrier) nobody still reads the old contents."""
+        self.zsym.local[: self.rows].copy_(z_loc)
+        self.heap.barrier()
+
+    def _z_ptrs(self):
+        from . import symm as _symm
+        return _symm.ptr_array([self.zsym.ptr(q) for q in range(self.world)])
+
+    def _counts_arr(self):
+        from . import symm as _symm
+        return _symm.int_array(self.counts)
+
     # ------------------------------------------------------------------ triangle attention
     def triatt_(self, z_loc: torch.Tensor, w: pair.TriattPacked, starting: bool) -> torch.Tensor:
         R, N, Np, Rmax, H = self.rows, self.N, self.Np, self.Rmax, self.H
         st = native.status_tensor(self.dev)
         stream = native.current_stream(self.dev)
-        src = z_loc if starting else transpose_shard(z_loc, self.layout, self.comm)
         q, k, v, g, og = (self.qkvgo[i][: R * N] for i in range(5))
         lib = native.lib()
         fused_gather = self.hb_full is not None and min(self.counts) >= 4
-        if R > 0:
+        peer_src = (not starting) and self.zsym is not None
+        src = None
+        if peer_src:
+            # ending node: transpose + LayerNorm + q|k|v|gate + head-bias projection in one kernel
+            self._stage_z(z_loc)
+            hb_ptr = (self.hb_full.ptr(self.rank, self.row0 * Np * 2), N) if fused_gather else \
+                (native.ptr(self.headbias.local), Rmax)
+            rc = lib.ubm_triatt_proj_rows_peer(self._z_ptrs(), self._counts_arr(), self.world, self.rank,
+                                               native.ptr(w.w), native.ptr(w.colsum), native.ptr(w.colbias),
+                                               native.ptr(w.wb), native.ptr(w.wb_colsum), native.ptr(w.wb_colbias),
+                                               native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(g), hb_ptr[0],
+                                               R, hb_ptr[1], N, Np, H, native.ptr(st), stream)
+            native.check(rc, "ubm_triatt_proj_rows_peer")
+        else:
+            src = z_loc if starting else transpose_shard(z_loc, self.layout, self.comm)
+        if R > 0 and not peer_src:
             # in the fused-gather mode the projection writes this rank's bias rows straight into its rows of the
             # whole planes (plane stride N rows); otherwise into the [H, Rmax, Np] shard buffer
             hb_ptr = (self.hb_full.ptr(self.rank, self.row0 * Np * 2), N) if fused_gather else \
@@ -149,13 +196,12 @@ class FusedRowPair:
             if R > 0:
                 hb_full = torch.cat([self._hb_all[p][:, :self.counts[p]] for p in range(self.world)], dim=1).contiguous()
                 pair.attention(q, k, v, hb_full, g, og, rows=R, Nq=N, Nk=N, H=H, D=32, ldb=Np)
-        src2 = src.view(R * N, 128)
         if starting:
             out = torch.empty_like(z_loc)
             if R > 0:
                 _gemm.gemm(og, w.wo, bias=w.bo, residual=z_loc.view(R * N, 128), out=out.view(R * N, 128))
             return out
-        upd_t = torch.empty_like(src)
+        upd_t = torch.empty_like(z_loc)
         if R > 0:
             _gemm.gemm(og, w.wo, bias=w.bo, out=upd_t.view(R * N, 128))
         upd = transpose_shard(upd_t, self.layout, self.comm)
