@@ -68,3 +68,28 @@ def test_worker_packing_reports_oom_as_rc_6(tmp_path):
     bad = [py, "-c", "import sys; sys.exit(4)"]
     assert packing.run_workers([bad], str(tmp_path / "c")).exit_code == 1
     assert packing.mps_available({}) is False
+
+
+def test_roomy_call_runs_from_a_frame_larger_than_a_stack_chunk():
+    import sys
+    from uplifting_biomolecular_modeling_b200.core import pystack, warm
+
+    def depth():
+        f, n = sys._getframe(), 0
+        while f is not None:
+            n += 1
+            f = f.f_back
+        return n
+
+    assert pystack.roomy_call(lambda a, b=1: a + b, 2, b=3) == 5
+    assert pystack.frame_slots() * 8 > 16 * 1024                      # bigger than one 16 KiB chunk
+    assert pystack.roomy_call(depth) == depth() + 2                  # the large frame and the callee sit above the caller
+    try:
+        pystack.roomy_call(lambda: 1 / 0)
+        raise AssertionError("exception swallowed")
+    except ZeroDivisionError:
+        pass
+    assert pystack.call_cost_us(200) < 1000.0
+    w = warm.warm(["json", "no_such_module_xyz"])
+    w.join(10)
+    assert "json" in w.seconds and "no_such_module_xyz" in w.errors

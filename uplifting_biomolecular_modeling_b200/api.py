@@ -61,6 +61,12 @@ class Predictor:
             cofold.build_model(config, device=self.device, dtype=dtype, seed=seed, **overrides)
         self.cfg = self.model.cfg
         self.levers = []
+        # numerics of every mode: no TF32 in the fp32 parts, highest matmul precision; applied around each prediction
+        # and restored afterwards (core.det.NumericsGuard), recorded in manifests and trunk checkpoints
+        from .core import det
+        self.policy = det.Policy(compute_dtype="bf16" if dtype == torch.bfloat16 else str(dtype).replace("torch.", ""),
+                                 allow_tf32=False, autocast=False, matmul_precision="highest")
+        self.numerics = det.numerics_signature(self.policy)
         if mode in ("fast", "big"):
             if self.device.type != "cuda":
                 raise NotActive(f"mode {mode} needs a CUDA device (sm_100a); got {self.device}")
@@ -233,6 +239,11 @@ class Predictor:
     def predict(self, feats_host: Dict[str, torch.Tensor], recycles: Optional[int] = None,
                 samples: Optional[int] = None, steps: Optional[int] = None, confidence: bool = True,
                 seed: Optional[int] = None, to_host: bool = True) -> Dict[str, torch.Tensor]:
+        from .core import det
+        with det.NumericsGuard(self.policy):
+            return self._predict(feats_host, recycles, samples, steps, confidence, seed, to_host)
+
+    def _predict(self, feats_host, recycles, samples, steps, confidence, seed, to_host):
         m = self.model
         dev = self.device
         if dev.type == "cuda":

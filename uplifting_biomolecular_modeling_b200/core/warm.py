@@ -5,6 +5,8 @@ from __future__ import annotations
 
 import importlib
 import threading
+
+from . import pystack
 import time
 from typing import Dict, Optional, Sequence
 
@@ -20,7 +22,9 @@ class Warm:
         for m in self.modules:
             t0 = time.perf_counter()
             try:
-                importlib.import_module(m)
+                # imports run from a frame larger than a stack chunk (see core.pystack): their cost must not
+                # depend on the depth this thread happens to be at
+                pystack.roomy_call(importlib.import_module, m)
             except Exception as e:                      # a failed warm-up is not an error: the real import reports it
                 self.errors[m] = f"{type(e).__name__}: {e}"
             self.seconds[m] = time.perf_counter() - t0

@@ -99,8 +99,12 @@ def _run_cofold(spec, act, args, allow_partial) -> int:
     if args.diffusion_samples is not None:
         overrides["samples"] = args.diffusion_samples
     try:
+        if getattr(args, "det", 0):
+            from ..core import det
+            det.apply_switches(det.Recipe(seed=args.seed))       # seeds, deterministic algorithms, no TF32
         pred = api.Predictor(config, mode="off", device=device, dtype=dtype, seed=args.seed, **overrides)
         pred.set_mode(act.mode)
+        act.manifest_extra = {"numerics": pred.numerics, "det": int(getattr(args, "det", 0))}
         ckpt = args.checkpoint or _weights_file(args.weights)
         if ckpt:
             from ..models import weights
@@ -109,9 +113,10 @@ def _run_cofold(spec, act, args, allow_partial) -> int:
             except (ValueError, OSError) as e:
                 act.refuse(f"checkpoint {ckpt}: {e}")
                 return report.EXIT_NOT_ACTIVE
-            act.manifest_extra = {"checkpoint": {"path": ckpt, "matched": rep.matched, "missing": rep.missing[:50],
+            act.manifest_extra = dict(getattr(act, "manifest_extra", {}))
+            act.manifest_extra["checkpoint"] = {"path": ckpt, "matched": rep.matched, "missing": rep.missing[:50],
                                                  "unexpected": rep.unexpected[:50],
-                                                 "shape_mismatch": rep.shape_mismatch[:50]}}
+                                                 "shape_mismatch": rep.shape_mismatch[:50]}
             report.emit(report.line(spec.tag, "WEIGHTS", ("path", ckpt), ("matched", rep.matched),
                                     ("missing", len(rep.missing)), ("unexpected", len(rep.unexpected)),
                                     ("shape_mismatch", len(rep.shape_mismatch))))
