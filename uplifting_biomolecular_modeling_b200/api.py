@@ -92,6 +92,7 @@ class Predictor:
             self.row_block = int(os.environ.get("UBM_BIG_ROW_BLOCK", "512"))
             self.model.workspace["row_block"] = self.row_block
             self.release = True
+            self.model.park_z_init = True
         if mode in ("fast", "big"):
             from .ops import dispatch
             dispatch.set_tier(mode)

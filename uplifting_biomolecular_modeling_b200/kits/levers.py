@@ -109,6 +109,12 @@ def _release(pred):
     return {"release": True}
 
 
+def _park_pair_init(pred):
+    """The initial pair tensor waits in pinned host memory between recycling passes (one fetch per pass)."""
+    pred.model.park_z_init = True
+    return {"park_z_init": True}
+
+
 def _rowpair(pred):
     """Row-sharded prediction over the ranks of ``--n_gpu P`` (the activation hands the run to the launcher)."""
     import torch
@@ -186,6 +192,7 @@ LEVERS: Dict[str, Lever] = {l.name: l for l in [
     Lever("trunk_graph", "F2.graph_capture", "capture.graphs.GraphCache", needs_gpu=True, apply=_trunk_graph),
     Lever("chunk_pair_ops", "F5.memory", "models.pairformer row blocks", apply=_chunk_pair_ops),
     Lever("release_intermediates", "F5.memory", "api.Predictor.release", apply=_release),
+    Lever("park_pair_init", "F5.memory", "mem.offload.HostPark", apply=_park_pair_init),
     Lever("expandable_segments", "F5.memory", "mem.allocator", apply=_expandable, droppable=True),
     Lever("rowpair_tp", "F7.tensor_parallel", "parallel.rowpair", needs_gpu=True, apply=_rowpair),
     Lever("cond_dedup", "F3.hoisting", "models.design.DesignPipeline", apply=_cond_dedup),

@@ -214,6 +214,9 @@ class CofoldModel(nn.Module):
         # stack is launch-bound there: ~40 launches per block); None = eager
         self.trunk_graphs = None
         self.trunk_graph_max_tokens = 512
+        # the ``park_pair_init`` lever (big): the initial pair tensor, which every recycling pass reads once, waits in
+        # pinned host memory between passes instead of holding N x N x c_z on the device for the whole trunk
+        self.park_z_init = False
 
     # ------------------------------------------------------------------ implementation switch
     def set_impl(self, impl: str, kinds=None) -> int:
@@ -251,9 +254,21 @@ class CofoldModel(nn.Module):
         pmask = None if smask is None else tmask[:, :, None] * tmask[:, None, :]
         for layer in self.msa_module.layers:
             layer.outer_product_mean.full_mask = feats.get("msa_full") is True
+        park = None
+        if self.park_z_init and n > 0 and z_init.is_cuda:
+            from ..mem.offload import HostPark
+            park = HostPark(z_init)
+            z_shape = z_init.shape
+            del z_init
         for _ in range(n + 1):
             s = s_init + self.s_recycle(self.s_norm(s))
-            z = z_init + self.z_recycle(self.z_norm(z))
+            zr = self.z_recycle(self.z_norm(z))
+            if park is not None:
+                z = park.fetch(zr.device)            # one pair tensor in from the host per pass
+                z += zr
+            else:
+                z = z_init + zr
+            del zr
             if self.cfg.template_blocks > 0 and "template_distogram" in feats:
                 tf = {k: (v[0] if k.startswith("template_") else v) for k, v in feats.items()
                       if k.startswith("template_")}
@@ -266,6 +281,8 @@ class CofoldModel(nn.Module):
                 s, z = self.trunk_graphs.run(self._stack_unmasked, s, z)
             else:
                 s, z = self.pairformer_module(s, z, smask, pmask)
+        if park is not None:
+            park.release()
         return s, z
 
     def _stack_unmasked(self, s, z):
