@@ -121,12 +121,51 @@ class TriangleMultiplication(_Switchable):
 
     lever = "fused_trimul"
 
+    def _rows_gemm_forward(self, z: torch.Tensor, mask: Optional[torch.Tensor], residual: bool) -> torch.Tensor:
+        """Widths other than 128 (the template stack at 64, the ESM family at 256): LayerNorm rows -> one tcgen05
+        GEMM for [p_in; g_in] with the sigmoid on the gate half in its epilogue -> channel-major operand planes ->
+        the batched contraction GEMM (K-major for outgoing, MN-major for incoming) -> LayerNorm rows -> output GEMM
+        whose epilogue applies the output gate and the residual.  Gating products and the two layout changes are
+        plain tensor statements."""
+        from ..ops import gemm, rows
+        N, c = z.shape[1], z.shape[-1]
+        h = self.p_in.weight.shape[0] // 2
+        if self._packed is None:
+            bf = lambda t: t.detach().to(torch.bfloat16).contiguous()  # noqa: E731
+            self._packed = (bf(torch.cat([self.p_in.weight, self.g_in.weight], 0)), bf(self.g_out.weight),
+                            bf(self.p_out.weight))
+        w_in, w_go, w_po = self._packed
+        x = z[0].reshape(N * N, c).contiguous()
+        n = rows.layernorm_rows(x, self.norm_in.weight, self.norm_in.bias, self.norm_in.eps)
+        pg = gemm.gemm(n, w_in, act="sigmoid", act_from=2 * h)                      # [N^2, 4h] = p | sigmoid(g)
+        ab = pg[:, :2 * h] * pg[:, 2 * h:]
+        if mask is not None:
+            ab = ab * mask[0].reshape(N * N, 1).to(ab.dtype)
+        Np = (N + 7) // 8 * 8
+        planes = torch.zeros((2, h, N, Np), dtype=torch.bfloat16, device=z.device)
+        planes[0, :, :, :N] = ab[:, :h].reshape(N, N, h).permute(2, 0, 1)
+        planes[1, :, :, :N] = ab[:, h:].reshape(N, N, h).permute(2, 0, 1)
+        xc = torch.zeros((h, N, Np), dtype=torch.bfloat16, device=z.device)
+        gemm.gemm(planes[0][:, :, :N], planes[1][:, :, :N], mn_major=not self.outgoing, out=xc[:, :, :N])
+        xr = xc[:, :, :N].permute(1, 2, 0).reshape(N * N, h).contiguous()
+        xn = rows.layernorm_rows(xr, self.norm_out.weight, self.norm_out.bias, self.norm_out.eps)
+        go = gemm.gemm(n, w_go, act="sigmoid")
+        out = gemm.gemm(xn, w_po, gate=go, residual=x if residual else None)
+        return out.view(1, N, N, c)
+
     def forward(self, z: torch.Tensor, mask: Optional[torch.Tensor], residual: bool = False) -> torch.Tensor:
         c = z.shape[-1]
-        why = self._tensor_reason(z) or (f"width_{c}" if c != 128 or self.p_in.weight.shape[0] != 256 else None) \
+        h2 = self.p_in.weight.shape[0]
+        one_kernel_set = c == 128 and h2 == 256
+        rows_ok = c % 32 == 0 and h2 % 64 == 0 and c <= 1024
+        why = self._tensor_reason(z) or (None if (one_kernel_set or rows_ok) else f"width_{c}x{h2 // 2}") \
             or (f"batch_{z.shape[0]}" if z.shape[0] != 1 else None)
-        if self._decide(why, f"C{c}H{self.p_in.weight.shape[0] // 2}", z.shape[1],
-                        {"c_z": c, "c_hidden": self.p_in.weight.shape[0] // 2, "dtype": "bf16"}):
+        served = self._decide(why, f"C{c}H{h2 // 2}", z.shape[1],
+                              {"c_z": c, "c_hidden": h2 // 2, "dtype": "bf16"},
+                              "tcgen05_3stage" if one_kernel_set else "rows_gemm")
+        if served and not one_kernel_set:
+            return self._rows_gemm_forward(z, mask, residual)
+        if served:
             from ..ops import pair
             if self._packed is None:
                 self._packed = pair.TrimulPacked.pack(self.norm_in.weight, self.norm_in.bias, self.p_in.weight,
@@ -176,13 +215,58 @@ class TriangleAttention(_Switchable):
 
     lever = "fused_triatt"
 
+    def _rows_gemm_forward(self, z: torch.Tensor, mask: Optional[torch.Tensor], residual: bool) -> torch.Tensor:
+        """Widths / head shapes other than 128 channels with 4 x 32: LayerNorm rows -> one tcgen05 GEMM for
+        q | k | v | gate (heads padded to the kernel's head dimension 32 or 64, sigmoid on the gate columns) -> the
+        attention kernel on column slices of that output with the head-bias planes and the key mask -> output GEMM
+        with bias and residual.  The ending node runs on the transposed pair tensor (a tensor statement)."""
+        from ..ops import gemm, pair, rows
+        m = self.mha
+        N, c = z.shape[1], z.shape[-1]
+        H, D = self.heads, self.c_hidden
+        if self._packed is None:
+            w = pair.ApbPacked.pack(m.linear_q.weight, None, m.linear_k.weight, m.linear_v.weight, m.linear_g.weight,
+                                    m.linear_o.weight, H)
+            if m.linear_g.bias is not None:
+                bg = torch.zeros((H, w.Dp), device=z.device)
+                bg[:, :D] = m.linear_g.bias.detach().float().view(H, D)
+                w.bqkvg[3 * H * w.Dp:] = bg.view(-1)
+            self._packed = w
+        w = self._packed
+        HD = H * w.Dp
+        src = z[0] if self.starting else z[0].transpose(0, 1)
+        x = src.reshape(N * N, c).contiguous()
+        n = rows.layernorm_rows(x, self.layer_norm.weight, self.layer_norm.bias, self.layer_norm.eps)
+        qkvg = gemm.gemm(n, w.wqkvg, bias=w.bqkvg, act="sigmoid", act_from=3 * HD)
+        Np = (N + 7) // 8 * 8
+        hb = torch.zeros((H, N, Np), dtype=torch.bfloat16, device=z.device)
+        hb[:, :, :N] = (F.linear(n, self.linear.weight.to(n.dtype)).float() * pair.LOG2E).view(N, N, H).permute(2, 0, 1)
+        km = None
+        if mask is not None:
+            km = _cached_key_mask(self._workspace, mask[0], transposed=not self.starting)
+        o = torch.empty((N * N, HD), dtype=torch.bfloat16, device=z.device)
+        pair.attention(qkvg[:, :HD], qkvg[:, HD:2 * HD], qkvg[:, 2 * HD:3 * HD], hb, qkvg[:, 3 * HD:], o, rows=N, Nq=N,
+                       Nk=N, H=H, D=w.Dp, ldb=Np, ld_in=4 * HD, ld_gate=4 * HD, mask=km)
+        bo = None if m.linear_o.bias is None else m.linear_o.bias.float()
+        upd = gemm.gemm(o, w.wo, bias=bo, residual=x if residual else None).view(N, N, c)
+        if not self.starting:
+            upd = upd.transpose(0, 1)
+        return upd.unsqueeze(0)
+
     def forward(self, z: torch.Tensor, mask: Optional[torch.Tensor] = None, residual: bool = False) -> torch.Tensor:
         m = self.mha
-        why = self._tensor_reason(z) or (f"width_{z.shape[-1]}" if z.shape[-1] != 128 else None) \
-            or (f"heads_{self.heads}x{self.c_hidden}" if (self.heads, self.c_hidden) != (4, 32) else None) \
+        c = z.shape[-1]
+        one_kernel_set = c == 128 and (self.heads, self.c_hidden) == (4, 32)
+        rows_ok = c % 32 == 0 and c <= 1024 and self.c_hidden <= 64 and (self.heads * (32 if self.c_hidden <= 32 else 64)) % 32 == 0
+        why = self._tensor_reason(z) or (None if (one_kernel_set or rows_ok) else
+                                         f"shape_{c}_{self.heads}x{self.c_hidden}") \
             or (f"batch_{z.shape[0]}" if z.shape[0] != 1 else None)
-        if self._decide(why, f"D{self.c_hidden}H{self.heads}", z.shape[1],
-                        {"head_dim": self.c_hidden, "dtype": "bf16"}):
+        served = self._decide(why, f"D{self.c_hidden}H{self.heads}", z.shape[1],
+                              {"head_dim": 32 if self.c_hidden <= 32 else 64, "dtype": "bf16"},
+                              "tcgen05_4row" if one_kernel_set else "rows_gemm")
+        if served and not one_kernel_set:
+            return self._rows_gemm_forward(z, mask, residual)
+        if served:
             from ..ops import pair
             km = None
             if mask is not None:
