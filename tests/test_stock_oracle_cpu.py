@@ -101,3 +101,25 @@ def test_msa_module_matches_stock(stock):
         z1 = ref(z, emb, feats)
         z2 = own(z, emb, msa_feat, msa_mask, mask, pm)
     assert torch.allclose(z1, z2, atol=2e-4, rtol=1e-4), (z1 - z2).abs().max()
+
+
+def test_diffusion_transformer_matches_stock(stock):
+    """Token transformer of the diffusion module: stock ``DiffusionTransformer`` (AdaLN, pair-bias attention shared
+    over the samples, conditioned SwiGLU transition) against this package's, same weights by strict load - the
+    parameter names (``output_projection.0``, ``swish_gate.0``) and which SwiGLU half is the gate are upstream's."""
+    from boltz.model.modules import transformersv2 as st
+    from uplifting_biomolecular_modeling_b200.models import diffusion
+    torch.manual_seed(4)
+    depth, heads, dim, N, mult = 2, 16, 768, 10, 3
+    ref = _randomize(st.DiffusionTransformer(depth=depth, heads=heads, dim=dim, dim_single_cond=dim)).eval()
+    own = diffusion.DiffusionTransformer(depth, dim, dim, heads).eval()
+    own.load_state_dict(ref.state_dict(), strict=True)
+    a, s = torch.randn(mult, N, dim), torch.randn(mult, N, dim)
+    bias = torch.randn(1, N, N, depth * heads)
+    mask = torch.ones(mult, N)
+    with torch.no_grad():
+        out_ref = ref(a, s, bias=bias, mask=mask, multiplicity=mult)
+        b5 = bias.view(1, N, N, depth, heads)
+        biases = [b5[:, :, :, i].permute(0, 3, 1, 2) for i in range(depth)]          # [1, H, N, N] per layer
+        out_own = own(a, s, biases, mask[:1], multiplicity=mult)        # this package repeats the mask over samples itself
+    assert torch.allclose(out_ref, out_own, atol=3e-4, rtol=1e-4), (out_ref - out_own).abs().max()

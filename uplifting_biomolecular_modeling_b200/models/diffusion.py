@@ -51,18 +51,20 @@ class ConditionedTransitionBlock(nn.Module):
         super().__init__()
         self.adaln = AdaLN(dim, dim_s)
         hidden = dim * expansion
-        self.swish_gated = nn.Linear(dim, 2 * hidden, bias=False)
+        # parameter names and the SwiGLU halves as upstream (boltz2/stock/src/boltz/model/modules/transformersv2.py:
+        # 34-65, utils.py:29-35): ``swish_gate.0`` projects to [values | gates] and the GATES half goes through silu;
+        # ``output_projection.0`` is the conditioning gate's Linear (the Sequential's sigmoid is applied in forward)
+        self.swish_gate = nn.Sequential(nn.Linear(dim, 2 * hidden, bias=False))
         self.a_to_b = nn.Linear(dim, hidden, bias=False)
         self.b_to_a = nn.Linear(hidden, dim, bias=False)
-        self.output_projection = nn.Linear(dim_s, dim)
-        nn.init.constant_(self.output_projection.bias, -2.0)
+        self.output_projection = nn.Sequential(nn.Linear(dim_s, dim), nn.Sigmoid())
+        nn.init.constant_(self.output_projection[0].bias, -2.0)
 
     def forward(self, a, s=None, cond=None, gate=None, fused: bool = False):
         x = self.adaln(a, s, cond, fused)
-        sg = self.swish_gated(x)
-        u, g = sg.chunk(2, dim=-1)
-        b = F.silu(u) * g * self.a_to_b(x)
-        gate = self.output_projection(s) if gate is None else gate
+        vals, gates = self.swish_gate[0](x).chunk(2, dim=-1)
+        b = F.silu(gates) * vals * self.a_to_b(x)
+        gate = self.output_projection[0](s) if gate is None else gate
         return torch.sigmoid(gate) * self.b_to_a(b)
 
 
@@ -86,12 +88,15 @@ class DiffusionTransformerLayer(_Switchable):
         self.pair_bias_attn = AttentionPairBias(dim, 128, heads, compute_pair_bias=False)
         self.output_projection_linear = nn.Linear(dim_s, dim)
         nn.init.constant_(self.output_projection_linear.bias, -2.0)
+        # upstream registers the same Linear a second time inside a Sequential (transformersv2.py:159-165): its
+        # checkpoints carry both names, so the alias is kept for strict loading
+        self.output_projection = nn.Sequential(self.output_projection_linear, nn.Sigmoid())
         self.transition = ConditionedTransitionBlock(dim, dim_s)
         self.dim, self.heads = dim, heads
 
     def hoist(self, s):
         """Everything that depends only on the conditioning s (same for every layer call of a step)."""
-        gate, t_gate = self.output_projection_linear(s), self.transition.output_projection(s)
+        gate, t_gate = self.output_projection_linear(s), self.transition.output_projection[0](s)
         return {"adaln": self.adaln.cond(s), "gate": gate, "t_adaln": self.transition.adaln.cond(s),
                 "t_gate": t_gate, "gate_sig": torch.sigmoid(gate), "t_gate_sig": torch.sigmoid(t_gate)}
 
@@ -109,9 +114,9 @@ class DiffusionTransformerLayer(_Switchable):
         w1 = torch.cat([ws, wb, tws, twb], 0)
         b1 = torch.cat([bs, zc, tbs, zc], 0)
         w2 = torch.cat([self.output_projection_linear.weight.detach().float(),
-                        self.transition.output_projection.weight.detach().float()], 0)
+                        self.transition.output_projection[0].weight.detach().float()], 0)
         b2 = torch.cat([self.output_projection_linear.bias.detach().float(),
-                        self.transition.output_projection.bias.detach().float()], 0)
+                        self.transition.output_projection[0].bias.detach().float()], 0)
         return w1, b1, w2, b2
 
     lever = "fused_dit"
@@ -141,7 +146,10 @@ class DiffusionTransformerLayer(_Switchable):
         a2 = a.view(B * N, C)
         tr = self.transition
         if self._packed is None:
-            self._packed = (torch.cat([tr.swish_gated.weight, tr.a_to_b.weight], 0).to(torch.bfloat16).contiguous(),
+            # the row kernel computes silu(first) * second * third: gates half first, then values, then a_to_b
+            wsg = tr.swish_gate[0].weight
+            hid = wsg.shape[0] // 2
+            self._packed = (torch.cat([wsg[hid:], wsg[:hid], tr.a_to_b.weight], 0).to(torch.bfloat16).contiguous(),
                             tr.b_to_a.weight.to(torch.bfloat16).contiguous())
         w_in, w_ba = self._packed
         x = rows.adaln_rows(a, h["t_adaln"][0], h["t_adaln"][1]).view(B * N, C)
@@ -354,11 +362,30 @@ def segment_mean(t: torch.Tensor, atom_to_token: torch.Tensor, n_tokens: int, fu
     return (g.float().sum(2) / counts[None, :, None].float()).to(t.dtype)
 
 
+class AtomTransformer(nn.Module):
+    """Holder with upstream's nesting: the windowed atom transformer's layers live under ``diffusion_transformer``
+    (boltz2/stock/src/boltz/model/modules/transformersv2.py:211-262), so that checkpoints name them
+    ``atom_encoder.diffusion_transformer.layers.N...`` / ``atom_decoder.diffusion_transformer.layers.N...``."""
+
+    def __init__(self, depth: int, c_atom: int, heads: int):
+        super().__init__()
+        self.diffusion_transformer = DiffusionTransformer(depth, c_atom, c_atom, heads)
+
+    def forward(self, *a, **kw):
+        return self.diffusion_transformer(*a, **kw)
+
+
 class AtomEncoderDecoderBase(nn.Module):
+    _holder = "atom_encoder"
+
     def __init__(self, c_atom: int, c_token: int, depth: int, heads: int):
         super().__init__()
         self.c_atom = c_atom
-        self.atom_transformer = DiffusionTransformer(depth, c_atom, c_atom, heads)
+        setattr(self, self._holder, AtomTransformer(depth, c_atom, heads))
+
+    @property
+    def atom_transformer(self) -> "DiffusionTransformer":
+        return getattr(self, self._holder).diffusion_transformer
 
 
 class AtomAttentionEncoder(AtomEncoderDecoderBase):
@@ -388,6 +415,8 @@ class AtomAttentionEncoder(AtomEncoderDecoderBase):
 
 
 class AtomAttentionDecoder(AtomEncoderDecoderBase):
+    _holder = "atom_decoder"
+
     def __init__(self, c_atom: int = 128, c_token: int = 768, depth: int = 3, heads: int = 4):
         super().__init__(c_atom, c_token, depth, heads)
         self.a_to_q_trans = nn.Linear(c_token, c_atom, bias=False)
