@@ -174,3 +174,61 @@ def test_pair_block_at_other_widths_runs_on_the_kernel_path(c, heads, N):
         assert lg.served >= 1 and not lg.fallbacks, (lever, lg.stats())
     counters.BOOK._ledgers.clear()
     dispatch.reset()
+
+
+def test_exact_is_bitwise_off_on_the_af3_shape():
+    """The flagship model's shapes (48-block configuration cut to 4 blocks and 6 sampler steps to keep the test
+    short): 256 tokens, no padding, so the Pairformer stack passes replay from the verified graph cache and the
+    sampler step from its verified graph; coordinates and confidence equal `off` bit for bit."""
+    from uplifting_biomolecular_modeling_b200 import api
+    from uplifting_biomolecular_modeling_b200.models import cofold
+    kw = dict(pairformer_blocks=4, msa_blocks=1, sampling_steps=6, samples=2, recycles=2, confidence_blocks=1,
+              token_depth=4)
+    off = api.Predictor("af3", mode="off", device="cuda:0", seed=0, **kw)
+    exact = api.Predictor("af3", mode="exact", device="cuda:0", seed=0, **kw)
+    feats = cofold.synthetic_features(256, 8, off.cfg, seed=2)
+    a = off.predict(feats)
+    b = exact.predict(feats)
+    b2 = exact.predict(feats)                    # second call: every stack pass and sampler step is a replay
+    assert torch.equal(a["coords"], b["coords"]) and torch.equal(a["coords"], b2["coords"])
+    assert torch.equal(a["plddt"], b["plddt"])
+    g = exact.model.trunk_graphs
+    assert g is not None and g.stats["captured"] >= 1 and g.stats["retired"] == 0 and g.stats["replayed"] >= 3
+    assert exact.graph_verified >= 1
+
+
+def test_big_mode_matches_fast_and_lowers_the_peak():
+    """`big` on one GPU: row-blocked pair operations give the numbers of `fast` (same kernels, same sums per output)
+    with a lower allocator peak; a padded input exercises the key masks of the blocked attention."""
+    from uplifting_biomolecular_modeling_b200.models import pairformer
+    from uplifting_biomolecular_modeling_b200.ops import native
+    torch.manual_seed(1)
+    N = 320
+    layer = pairformer.PairformerLayer(no_seq=True).cuda().to(torch.bfloat16).eval()
+    with torch.no_grad():
+        for p in layer.parameters():
+            p.normal_(0, 0.5 * p.shape[-1] ** -0.5 if p.dim() > 1 else 0.1)
+        for mod in layer.modules():
+            if isinstance(mod, torch.nn.LayerNorm):
+                mod.weight.add_(1.0)
+    z = torch.randn(1, N, N, 128, device="cuda").bfloat16()
+    tok = torch.ones(N, device="cuda")
+    tok[N - 30:] = 0
+    pm = (tok[:, None] * tok[None, :]).unsqueeze(0)
+    peaks, outs = [], []
+    for rb in (0, 64):
+        ws = {"row_block": rb} if rb else {}
+        pairformer.set_impl(layer, "fused", workspace=ws)
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        base = torch.cuda.memory_allocated()
+        with torch.no_grad():
+            outs.append(layer.pair_update(z, pm))
+        torch.cuda.synchronize()
+        peaks.append(torch.cuda.max_memory_allocated() - base)
+        ws.clear()
+    native.raise_on_status("cuda", "big mode block")
+    v = tok.bool()
+    a, b = outs[0][0][v][:, v].float(), outs[1][0][v][:, v].float()
+    assert ((a - b).abs().mean() / a.abs().mean()).item() < 5e-3
+    assert peaks[1] < 0.7 * peaks[0], peaks

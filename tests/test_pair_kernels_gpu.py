@@ -300,3 +300,66 @@ def test_pair_head_bias_planes(N, H, transpose):
     ref = ref.permute(2, 1, 0) if transpose else ref.permute(2, 0, 1)
     assert out.shape == (H, N, N)
     assert (out.float() - ref).abs().max().item() < 4e-2
+
+
+@pytest.mark.parametrize("N,outgoing", [(1536, True), (1536, False), (4096, True)])
+def test_trimul_large_sampled_rows(N, outgoing):
+    """Benchmark sizes: the fused triangle multiplication at 1536 and 4096 tokens (pair planes pass 2^31 elements at
+    4096: the 64-bit index paths run here) against fp32 computed for a sample of output rows."""
+    from uplifting_biomolecular_modeling_b200.ops import native, pair, reference
+    g = torch.Generator(device="cuda").manual_seed(21)
+    c = 128
+    z = (_rand((N, N, c), g) + 0.2).bfloat16()
+    niw, nib = 1.0 + 0.1 * _rand((c,), g), 0.1 * _rand((c,), g)
+    now, nob = 1.0 + 0.1 * _rand((c,), g), 0.1 * _rand((c,), g)
+    p_in, g_in = _rand((2 * c, c), g, c ** -0.5), _rand((2 * c, c), g, c ** -0.5)
+    p_out, g_out = _rand((c, c), g, c ** -0.5), _rand((c, c), g, c ** -0.5)
+    w = pair.TrimulPacked.pack(niw, nib, p_in, g_in, now, nob, p_out, g_out)
+    out = pair.trimul_fused(z, None, w, outgoing=outgoing, residual=False, workspace={})
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "trimul")
+    # fp32 statement for a few output rows i: projections of the operand rows that those outputs read
+    rows = [0, N // 3, N - 1]
+    F = torch.nn.functional
+
+    def proj(x):                                     # x: [..., c] fp32 rows of z -> gated a | b
+        n = F.layer_norm(x, (c,), niw, nib)
+        return F.linear(n, p_in) * torch.sigmoid(F.linear(n, g_in))
+    errs = []
+    for i in rows:
+        if outgoing:          # x[i, j] = sum_k a[i, k] b[j, k]
+            a_i = proj(z[i].float())[:, :c]                                   # [N(k), c]
+            xi = torch.empty((N, c), device="cuda")
+            for j0 in range(0, N, 256):
+                b_j = proj(z[j0:j0 + 256].float())[..., c:]                   # [256, N(k), c]
+                xi[j0:j0 + 256] = torch.einsum("kc,jkc->jc", a_i, b_j)
+        else:                 # x[i, j] = sum_k a[k, i] b[k, j]
+            a_i = proj(z[:, i].float())[:, :c]                                # [N(k), c]
+            xi = torch.zeros((N, c), device="cuda")
+            for k0 in range(0, N, 256):
+                b_k = proj(z[k0:k0 + 256].float())[..., c:]                   # [256(k), N(j), c]
+                xi += torch.einsum("kc,kjc->jc", a_i[k0:k0 + 256], b_k)
+        ni = F.layer_norm(z[i].float(), (c,), niw, nib)
+        ref_i = F.linear(F.layer_norm(xi, (c,), now, nob), p_out) * torch.sigmoid(F.linear(ni, g_out))
+        errs.append(((out[i].float() - ref_i).abs().mean() / ref_i.abs().mean()).item())
+    assert max(errs) < 3e-2, errs
+
+
+def test_transition_n1536():
+    from uplifting_biomolecular_modeling_b200.ops import native, pair, reference
+    g = torch.Generator(device="cuda").manual_seed(22)
+    N, c, hidden = 1536, 128, 512
+    x = (_rand((N, N, c), g) + 0.3).bfloat16()
+    nw, nb = 1.0 + 0.1 * _rand((c,), g), 0.1 * _rand((c,), g)
+    fc1, fc2 = _rand((hidden, c), g, c ** -0.5), _rand((hidden, c), g, c ** -0.5)
+    fc3 = _rand((c, hidden), g, hidden ** -0.5)
+    out = pair.transition_fused(x, pair.TransitionPacked.pack(nw, nb, fc1, fc2, fc3), residual=True)
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "transition")
+    worst = 0.0
+    for r0 in (0, 700, N - 64):                       # row chunks of the fp32 statement
+        ref = reference.transition(x[r0:r0 + 64].float(), nw, nb, fc1, fc2, fc3, residual=True)
+        upd_ref = ref - x[r0:r0 + 64].float()
+        upd = out[r0:r0 + 64].float() - x[r0:r0 + 64].float()
+        worst = max(worst, ((upd - upd_ref).abs().mean() / upd_ref.abs().mean()).item())
+    assert worst < 2e-2, worst

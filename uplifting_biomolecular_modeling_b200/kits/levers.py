@@ -38,6 +38,8 @@ def _fused(kinds_fn, lever_name):
         if n == 0:
             raise gates.CannotRun(f"{lever_name}: the model has no module of this kind")
         return {"modules": n}
+    apply.__doc__ = ("Switches the model's modules of this kind to their sm_100a kernel implementation; every call is "
+                     "then counted served or fallback in the lever's ledger.")
     return apply
 
 
@@ -76,10 +78,11 @@ def _kinds_dit():
     return (diffusion.DiffusionTransformerLayer,)
 
 
-def _flag(attr, value=True):
+def _flag(attr, value=True, doc=""):
     def apply(pred):
         setattr(pred, attr, value)
         return {attr: value}
+    apply.__doc__ = doc
     return apply
 
 
@@ -95,8 +98,8 @@ def _expandable(pred):
 
 
 def _chunk_pair_ops(pred):
-    """Pair operations of the kernel path run in row blocks: the triangle-attention q|k|v|gate rows, the
-    triangle-multiplication output stage and the transition exist for one block of rows at a time."""
+    """Pair operations of the kernel path run in row blocks: the triangle-attention q|k|v|gate|o rows and the
+    contracted planes of the triangle multiplication exist for one block of rows at a time."""
     rows = int(getattr(pred, "row_block", 0) or 512)
     pred.row_block = rows
     pred.model.workspace["row_block"] = rows
@@ -187,7 +190,8 @@ LEVERS: Dict[str, Lever] = {l.name: l for l in [
     Lever("fused_pwa", "F1.kernel_fusion", "gemm_sm100@1", needs_gpu=True, apply=_fused(_kinds_pwa, "fused_pwa")),
     Lever("fused_dit", "F1.kernel_fusion", "attention_d64+rows_sm100@1", needs_gpu=True,
           apply=_fused(_kinds_dit, "fused_dit")),
-    Lever("sampler_graph", "F2.graph_capture", "api.Predictor._step_fn", needs_gpu=True, apply=_flag("use_graphs")),
+    Lever("sampler_graph", "F2.graph_capture", "api.Predictor._step_fn", needs_gpu=True, apply=_flag("use_graphs", True, "The sampler step is captured once per shape in a CUDA graph and replayed for every "
+                                            "step and every later prediction.")),
     Lever("graph_verify", "F2.graph_capture", "capture.graphs.verify", needs_gpu=True, apply=_graph_verify),
     Lever("trunk_graph", "F2.graph_capture", "capture.graphs.GraphCache", needs_gpu=True, apply=_trunk_graph),
     Lever("chunk_pair_ops", "F5.memory", "models.pairformer row blocks", apply=_chunk_pair_ops),

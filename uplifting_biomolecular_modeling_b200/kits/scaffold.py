@@ -71,9 +71,9 @@ kernels that fail their load-time check against the fp32 statements exit 5 (`KER
 """
 
 MODE_MEANING = {
-    "exact": "| `exact` | the same statements with step-invariant work hoisted and the sampler / forward step replayed as a CUDA graph; outputs bitwise equal to `off` |",
-    "fast": "| `fast` | the sm_100a kernel path in bf16 (tcgen05 kernels, fused row kernels, CUDA graphs); outputs within the documented tolerance of `off` |",
-    "big": "| `big` | `fast` plus the memory levers (row chunking, released intermediates) and, with `--n_gpu P`, the row-sharded pair tensor over peer memory |",
+    "exact": "| `exact` | the same statements with the sampler / forward step (and small Pairformer stacks) replayed from CUDA graphs whose first replay is checked bit for bit against eager; outputs bitwise equal to `off` |",
+    "fast": "| `fast` | the sm_100a kernel path in bf16 (tcgen05 kernels, fused row kernels, CUDA graphs); outputs within the documented tolerance of `off`; every module call is counted served / fallback and an undeclared fallback ends the run PARTIAL (exit 3) |",
+    "big": "| `big` | `fast` plus the memory levers (pair operations in row blocks, trunk scratch released before the sampler, initial pair tensor parked in pinned host memory, expandable allocator segments) and, with `--n_gpu P`, the row-sharded pair tensor over peer memory; rank 0 runs sampler and confidence head and writes coordinates |",
 }
 
 
@@ -84,9 +84,13 @@ def changes_text(spec) -> str:
         names = spec.levers.get(mode, ())
         if not names:
             continue
-        rows = "\n".join(f"| `{n}` | {LEVERS[n].strategy} | `{LEVERS[n].impl}` | {'yes' if LEVERS[n].needs_gpu else 'no'} |"
-                         for n in names if n in LEVERS)
-        tables.append(f"### `{mode}`\n\n| lever | strategy | implemented by | needs a GPU |\n|---|---|---|---|\n{rows}")
+        def what(n):
+            doc = (LEVERS[n].apply.__doc__ or "").strip().split("\n\n")[0] if LEVERS[n].apply else ""
+            return " ".join(doc.split()) or "switches the named modules to their kernel implementation"
+        rows = "\n".join(f"| `{n}` | {LEVERS[n].strategy} | `{LEVERS[n].impl}` | {'yes' if LEVERS[n].needs_gpu else 'no'} | "
+                         f"{what(n)} |" for n in names if n in LEVERS)
+        tables.append(f"### `{mode}`\n\n| lever | strategy | implemented by | needs a GPU | what it does |\n"
+                      f"|---|---|---|---|---|\n{rows}")
     return CHANGES.format(
         name=spec.name, upstream=spec.upstream, module=FAMILY_MODULE.get(spec.family, spec.family),
         verbs=", ".join(spec.commands), env=spec.env, tag=spec.tag,
