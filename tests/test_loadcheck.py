@@ -21,9 +21,23 @@ def test_verdict_line_and_refusal(capsys):
 
 
 
+def test_a_family_that_fails_tuned_is_retried_under_its_safe_setting():
+    state = {"safe": False}
+
+    def flaky(dev):
+        return (1e-3, 2e-2) if state["safe"] else (0.9, 2e-2)
+    lc = loadcheck.run_all("cpu", probes={"triattn": flaky, "gemm": lambda d: (0.0, 1e-2)},
+                           safe={"triattn": lambda: state.__setitem__("safe", True)})
+    assert lc.ok and "settings=safe:triattn" in lc.line("x")
+    state["safe"] = False
+    lc = loadcheck.run_all("cpu", probes={"triattn": lambda d: (0.9, 2e-2)}, safe={"triattn": lambda: None})
+    assert not lc.ok and "KERNELS-REFUSED" in lc.line() and "settings=tuned" in lc.line()     # safe form failed too
+
+
 @pytest.mark.gpu
 def test_every_family_verifies_on_the_gpu():
     lc = loadcheck.run_all("cuda:0", use_cache=False)
     assert lc.ok, lc.line()
     # the probes sit well inside their tolerances (a false refusal would take a working GPU out of service)
     assert all(p.error <= 0.5 * p.tolerance for p in lc.probes), [(p.family, p.error) for p in lc.probes]
+    assert "settings=tuned" in lc.line()

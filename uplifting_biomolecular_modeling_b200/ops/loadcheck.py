@@ -56,8 +56,10 @@ class LoadCheck:
     def line(self, tag: str = "opt_core") -> str:
         verb = "KERNELS-VERIFIED" if self.ok else "KERNELS-REFUSED"
         worst = max(self.probes, key=lambda p: p.error / max(p.tolerance, 1e-30)) if self.probes else None
+        safe = [p.family for p in self.probes if p.ok and p.detail == "safe"]
         return report.line(tag, verb, ("families", len(self.probes)), ("failed", ",".join(p.family for p in self.failed) or "none"),
-                           ("worst", f"{worst.family}:{worst.error:.2e}/{worst.tolerance:.0e}" if worst else "none"))
+                           ("worst", f"{worst.family}:{worst.error:.2e}/{worst.tolerance:.0e}" if worst else "none"),
+                           ("settings", "tuned" if not safe else "safe:" + ",".join(safe)))
 
 
 def _rel(out: torch.Tensor, ref: torch.Tensor) -> float:
@@ -146,29 +148,66 @@ def _probe_column_attention(dev) -> Tuple[float, float]:
     return _rel(seq.column_attention(q, k, v, idx), R.column_attention(q, k, v, idx)), 2e-2
 
 
+def _probe_window(dev) -> Tuple[float, float]:
+    """Atom attention in 32 x 128 windows (4 heads of 32) against the windowed fp32 statement."""
+    import copy
+    from ..models import diffusion, pairformer
+    from . import pair
+    torch.manual_seed(7)
+    B, A, c, H = 2, 160, 128, 4
+    attn = pairformer.AttentionPairBias(c, 128, H, compute_pair_bias=False).to(dev).eval()
+    x = torch.randn(B, A, c, device=dev, generator=_gen(dev, 8))
+    bias = torch.randn(1, H, A // 32, 32, 128, device=dev, generator=_gen(dev, 9))
+    with torch.no_grad():
+        ref = diffusion._window_attention(attn, x, bias, (32, 128))
+        ab = copy.deepcopy(attn).to(torch.bfloat16)
+        w = pair.ApbPacked.pack(ab.proj_q.weight, ab.proj_q.bias, ab.proj_k.weight, ab.proj_v.weight,
+                                ab.proj_g.weight, ab.proj_o.weight, H)
+        out = pair.window_attention_fused(x.bfloat16(), w, diffusion.WindowBias(bias).data)
+    return _rel(out, ref), 4e-2
+
+
 PROBES: Dict[str, Callable] = {
     "gemm": _probe_gemm, "ln": _probe_layernorm, "triattn": _probe_triattn, "trimul": _probe_trimul,
-    "transition": _probe_transition, "seq": _probe_seq, "column_attention": _probe_column_attention,
+    "transition": _probe_transition, "window": _probe_window, "seq": _probe_seq,
+    "column_attention": _probe_column_attention,
 }
 
 
-def run_all(device="cuda:0", probes: Optional[Dict[str, Callable]] = None, use_cache: bool = True) -> LoadCheck:
-    """Run every probe on ``device``; a probe that raises counts as failed with the exception's name."""
+def _run_probe(family: str, fn: Callable, device) -> Probe:
+    from . import native
+    try:
+        err, tol = fn(device)
+        if str(device).startswith("cuda"):
+            torch.cuda.synchronize(device)
+            native.raise_on_status(device, f"load check {family}")
+        ok = err == err and err <= tol            # NaN fails
+        return Probe(family, ok, float(err), tol, "" if ok else f"error {err:.3e} > {tol:.0e}")
+    except Exception as e:  # noqa: BLE001 - any failure of a probe is a refusal of that family
+        return Probe(family, False, float("inf"), 0.0, f"{type(e).__name__}: {str(e)[:80]}")
+
+
+def run_all(device="cuda:0", probes: Optional[Dict[str, Callable]] = None, use_cache: bool = True,
+            safe: Optional[Dict[str, Callable]] = None) -> LoadCheck:
+    """Run every probe on ``device``; a probe that raises counts as failed with the exception's name.  A family that
+    fails under the tuned settings and has a safe setting (``ops.safe_settings``) is switched to it and probed once
+    more; passing then, it serves with the safe setting (``detail == "safe"``)."""
     key = str(device)
     if use_cache and probes is None and key in _VERDICT:
         return _VERDICT[key]
-    from . import native
+    from . import safe_settings
     results = []
     for family, fn in (probes or PROBES).items():
-        try:
-            err, tol = fn(device)
-            if str(device).startswith("cuda"):
-                torch.cuda.synchronize(device)
-                native.raise_on_status(device, f"load check {family}")
-            ok = err == err and err <= tol            # NaN fails
-            results.append(Probe(family, ok, float(err), tol, "" if ok else f"error {err:.3e} > {tol:.0e}"))
-        except Exception as e:  # noqa: BLE001 - any failure of a probe is a refusal of that family
-            results.append(Probe(family, False, float("inf"), 0.0, f"{type(e).__name__}: {str(e)[:80]}"))
+        pr = _run_probe(family, fn, device)
+        if not pr.ok:
+            applied = safe[family]() is None if (safe is not None and family in safe) else \
+                (safe is None and safe_settings.apply(family))
+            if applied:
+                again = _run_probe(family, fn, device)
+                if again.ok:
+                    again.detail = "safe"
+                    pr = again
+        results.append(pr)
     lc = LoadCheck(key, results)
     if use_cache and probes is None:
         _VERDICT[key] = lc
