@@ -49,6 +49,43 @@ def test_gemm_epilogue_bias_residual_act():
     assert torch.allclose(out.float(), ref, atol=6e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("act", ["silu", "sigmoid", "gelu", "relu"])
+def test_gemm_activation_from_a_column(act):
+    """Every activation of the epilogue, applied from column 64 on (the q | k | v | gate projection's form)."""
+    from uplifting_biomolecular_modeling_b200.ops import gemm, native
+    g = torch.Generator(device="cuda").manual_seed(5)
+    a = torch.randn(520, 192, device="cuda", generator=g).bfloat16()
+    b = (torch.randn(320, 192, device="cuda", generator=g) * 0.1).bfloat16()
+    bias = torch.randn(320, device="cuda", generator=g) * 0.1
+    out = gemm.gemm(a, b, bias=bias, act=act, act_from=64, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "gemm")
+    y = a.float() @ b.float().T + bias
+    fn = {"silu": torch.nn.functional.silu, "sigmoid": torch.sigmoid, "gelu": torch.nn.functional.gelu,
+          "relu": torch.relu}[act]
+    ref = torch.cat([y[:, :64], fn(y[:, 64:])], 1)
+    assert torch.allclose(out, ref, atol=4e-3, rtol=4e-3), (out - ref).abs().max().item()
+
+
+@pytest.mark.parametrize("M,H,K", [(640, 192, 128), (1000, 96, 256), (7680, 1536, 768), (130, 32, 64)])
+def test_gemm_swiglu3_epilogue(M, H, K):
+    """silu(x Wg^T) * (x Wv^T) * (x Wb^T) formed on the accumulator of one 192-wide-tile product against the three
+    separate fp32 products (H = 96 and 32 leave a tile with one column triple / part of the tile empty)."""
+    from uplifting_biomolecular_modeling_b200.ops import gemm, native
+    g = torch.Generator(device="cuda").manual_seed(6)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    wg, wv, wb = ((torch.randn(H, K, device="cuda", generator=g) * K ** -0.5).bfloat16() for _ in range(3))
+    out = gemm.gemm(x, gemm.pack_swiglu3(wg, wv, wb), act="swiglu3")
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "gemm")
+    assert out.shape == (M, H) and out.dtype == torch.bfloat16
+    xf = x.float()
+    ref = torch.nn.functional.silu(xf @ wg.float().T) * (xf @ wv.float().T) * (xf @ wb.float().T)
+    err = (out.float() - ref).abs().max().item()
+    assert err <= 2e-2 * max(ref.abs().max().item(), 1.0), err
+    assert ((out.float() - ref).abs().mean() / ref.abs().mean()).item() < 8e-3
+
+
 @pytest.mark.parametrize("M,N,K", [(1000, 128, 128), (384, 96, 256), (257, 128, 64)])
 def test_gemm_residual_tiles_by_tma(M, N, K):
     """N <= 128 takes the 128-wide tile whose residual arrives through the shared-memory ring."""

@@ -146,14 +146,18 @@ class DiffusionTransformerLayer(_Switchable):
         a2 = a.view(B * N, C)
         tr = self.transition
         if self._packed is None:
-            # the row kernel computes silu(first) * second * third: gates half first, then values, then a_to_b
-            wsg = tr.swish_gate[0].weight
+            # silu(gates half) * values half * a_to_b: upstream's swish_gate stores the values first
+            wsg = tr.swish_gate[0].weight.detach()
             hid = wsg.shape[0] // 2
-            self._packed = (torch.cat([wsg[hid:], wsg[:hid], tr.a_to_b.weight], 0).to(torch.bfloat16).contiguous(),
-                            tr.b_to_a.weight.to(torch.bfloat16).contiguous())
-        w_in, w_ba = self._packed
+            if hid % 32 == 0:
+                # one projection whose epilogue forms the product on the accumulator (no [M, 3 * hid] intermediate)
+                w_in = gemm.pack_swiglu3(wsg[hid:], wsg[:hid], tr.a_to_b.weight.detach())
+            else:
+                w_in = torch.cat([wsg[hid:], wsg[:hid], tr.a_to_b.weight.detach()], 0).to(torch.bfloat16).contiguous()
+            self._packed = (w_in, tr.b_to_a.weight.detach().to(torch.bfloat16).contiguous(), hid % 32 == 0)
+        w_in, w_ba, in_epilogue = self._packed
         x = rows.adaln_rows(a, h["t_adaln"][0], h["t_adaln"][1]).view(B * N, C)
-        u = rows.swiglu3_rows(gemm.gemm(x, w_in))
+        u = gemm.gemm(x, w_in, act="swiglu3") if in_epilogue else rows.swiglu3_rows(gemm.gemm(x, w_in))
         return gemm.gemm(u, w_ba, gate=t_gate, residual=a2).view(B, N, C)
 
     def forward(self, a, s, bias, mask=None, multiplicity: int = 1, hoisted: Optional[dict] = None,

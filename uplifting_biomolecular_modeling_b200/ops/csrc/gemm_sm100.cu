@@ -29,7 +29,11 @@ struct GemmParams {
   long long ldr, strideR;
   float alpha;
   int out_fp32;
-  int act;  // 0 none, 1 silu, 2 sigmoid, 3 gelu (erf), 4 relu
+  // 0 none, 1 silu, 2 sigmoid, 3 gelu (erf), 4 relu; 5 = three-way SwiGLU over column triples (192-wide tiles
+  // only): the N columns come in groups of 96 = 32 gate | 32 value | 32 second value, and the output, N / 3 columns
+  // wide, is silu(gate) * value * second value - the conditioned transition's swish gate and its a_to_b branch
+  // from one projection with no [M, N] intermediate
+  int act;
   int act_col0;  // the activation applies to output columns >= act_col0 (a multiple of 32; 0 = all columns)
   int res_tma;  // residual tiles arrive by TMA (tensor map in the auxiliary map slot 0)
   // blocked output (cblk_col != 0): element (m, n) goes to (m / 32) * cblk_hi + (m % 32) * cblk_lo +
@@ -108,16 +112,34 @@ struct GemmCfg {
   static constexpr int kResSlotBytes = kBM * 128 * 2;
   static constexpr int kResBytes = kResTma ? 2 * kResSlotBytes : 0;
   static constexpr int kSmemBytes = kStages * kStageBytes + kResBytes + 1024 /*align*/ + 512 /*barriers*/;
-  static constexpr int kTmemCols = (2 * BN <= 32) ? 32 : 2 * BN;  // two accumulator buffers
+  // two accumulator buffers; the allocation is a power of two (384 columns of the 192-wide tile take 512)
+  static constexpr int kTmemCols = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128
+                                   : (2 * BN <= 256) ? 256 : 512;
 };
 
-__device__ __forceinline__ float apply_act(float v, int act) {
+// Activation of one 32-column chunk.  The switch sits outside the element loop: with the (warp-uniform) choice
+// made per element, every element paid an indirect branch and the 32 activations ran one after another - a
+// sigmoid on a quarter of the columns of a 7680 x 768 x 4096 projection cost 33 us on top of 45.
+__device__ __forceinline__ void apply_act32(float (&f)[32], int act) {
   switch (act) {
-    case 1: return siluf_fast(v);
-    case 2: return sigmoidf_fast(v);
-    case 3: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
-    case 4: return fmaxf(v, 0.0f);
-    default: return v;
+    case 1:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = siluf_fast(f[j]);
+      break;
+    case 2:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = sigmoidf_fast(f[j]);
+      break;
+    case 3:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = 0.5f * f[j] * (1.0f + erff(f[j] * 0.70710678118654752f));
+      break;
+    case 4:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = fmaxf(f[j], 0.0f);
+      break;
+    default:
+      break;
   }
 }
 
@@ -455,10 +477,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (n0 + j < n_limit) f[j] += __ldg(p.bias + n0 + j);
             }
           }
-          if (p.act != 0 && n0 >= p.act_col0) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = apply_act(f[j], p.act);
-          }
+          if (p.act != 0 && n0 >= p.act_col0) apply_act32(f, p.act);
           if (p.gate != nullptr) {
             const __nv_bfloat16* gr = p.gate + static_cast<long long>(m % p.gate_rows) * p.ld_gate + n0;
             if (n0 + 32 <= n_limit && (reinterpret_cast<uintptr_t>(gr) & 31) == 0) {
@@ -572,6 +591,47 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t va[32], vb[32];
       const int c_begin = grp * kChunksPerGroup;
       const int c_end = min(nchunks, c_begin + kChunksPerGroup);
+      if constexpr (BN == 192) {
+        if (p.act == 5) {
+          // this warp's three chunks are one column triple: gate | value | second value of 32 output columns
+          if (c_begin + 3 <= c_end) {
+            const uint32_t t0 = tmem_addr(tmem_base, q, acc * BN + c_begin * 32);
+            tmem_ld32(t0, va);
+            tmem_ld_wait();
+            tmem_ld32(t0 + 32, vb);
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = siluf_fast(__uint_as_float(va[j]) * p.alpha);
+            tmem_ld_wait();
+            tmem_ld32(t0 + 64, va);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] *= __uint_as_float(vb[j]) * p.alpha;
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] *= __uint_as_float(va[j]) * p.alpha;
+            if (row_ok) {
+              const int o0 = (n_base + c_begin * 32) / 3;
+              __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.strideC +
+                                  static_cast<long long>(m) * p.ldc + o0;
+              if ((reinterpret_cast<uintptr_t>(cp) & 31) == 0) {
+                st_bf16x16(cp, f);
+                st_bf16x16(cp + 16, f + 16);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) cp[j] = __float2bfloat16(f[j]);
+              }
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+          if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1u;
+          }
+          continue;
+        }
+      }
       if (c_begin < c_end) tmem_ld32(tmem_addr(tmem_base, q, acc * BN + c_begin * 32), va);
 #pragma unroll 1
       for (int c = c_begin; c < c_end; c += 2) {
@@ -746,6 +806,15 @@ extern "C" int ubm_gemm_bf16_ex(const void* A, const void* B, void* C, const voi
     const long long w256 = (tm * ((N + 255) / 256) + sms - 1) / sms;
     const long long w128 = (tm * ((N + 127) / 128) + sms - 1) / sms;
     if (static_cast<double>(w128) * 0.5 * 1.15 < static_cast<double>(w256)) wide = false;
+  }
+  if (act == 5) {
+    if (mn_major || out_fp32 || bias != nullptr || residual != nullptr || gate != nullptr || cblk_col != 0 ||
+        act_col0 != 0 || (N % 96) != 0) {
+      fprintf(stderr, "[ubm] gemm: the three-way SwiGLU epilogue takes a K-major bf16 product of 96-column groups "
+                      "with no bias, gate or residual\n");
+      return UBM_ERR_ARGUMENT;
+    }
+    return launch_gemm<192, false>(A, B, p, lda, ldb, strideA, strideB, st);
   }
   if (mn_major) {
     return wide ? launch_gemm<256, true>(A, B, p, lda, ldb, strideA, strideB, st)
