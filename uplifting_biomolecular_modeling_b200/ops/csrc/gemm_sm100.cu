@@ -36,6 +36,11 @@ struct GemmParams {
   int act;
   int act_col0;  // the activation applies to output columns >= act_col0 (a multiple of 32; 0 = all columns)
   int res_tma;  // residual tiles arrive by TMA (tensor map in the auxiliary map slot 0)
+  // bf16 output leaves through shared memory: every epilogue warp stages its 32 rows x 64 columns (128-byte swizzle;
+  // 32 columns in the 64-byte swizzle for the SwiGLU form) and one lane stores the box with a bulk tensor copy
+  // (tensor map in the auxiliary map slot 1).  A row-per-lane 32-byte global store costs the warp about 375 cycles
+  // (32 requests of one sector each); the staged form writes whole 128-byte lines and does not hold the warp.
+  int c_tma;
   // blocked output (cblk_col != 0): element (m, n) goes to (m / 32) * cblk_hi + (m % 32) * cblk_lo +
   // (n / 32) * cblk_col + n % 32.  With m = (i, c) and n = (j, d), c, d < 32, this writes the outer-product
   // layout [(i, j)][(c, d)] directly, so no permuted copy of the product is made.
@@ -105,13 +110,17 @@ struct GemmCfg {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  // BN = 128 gives up one operand stage for a two-slot ring of residual tiles (128 x 128 bf16 each) that the
-  // producer fills by TMA, so the epilogue never waits on a global load
+  // BN = 128 has room for a two-slot ring of residual tiles (128 x 128 bf16 each) that the producer fills by TMA,
+  // so the epilogue never waits on a global load
   static constexpr bool kResTma = (BN == 128);
-  static constexpr int kStages = (BN == 256) ? 4 : 5;
+  static constexpr int kStages = 4;   // 128 KB (BN = 128) to 192 KB (BN = 256) of operands in flight
   static constexpr int kResSlotBytes = kBM * 128 * 2;
   static constexpr int kResBytes = kResTma ? 2 * kResSlotBytes : 0;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kResBytes + 1024 /*align*/ + 512 /*barriers*/;
+  // output staging of the eight epilogue warps: 32 rows x 128 bytes each
+  static constexpr int kOutWarpBytes = 32 * 128;
+  static constexpr int kOutBytes = 8 * kOutWarpBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kResBytes + kOutBytes + 1024 /*align*/ + 512 /*barriers*/;
+  static_assert(kSmemBytes <= 232448, "shared memory of one CTA");
   // two accumulator buffers; the allocation is a power of two (384 columns of the 192-wide tile take 512)
   static constexpr int kTmemCols = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128
                                    : (2 * BN <= 256) ? 256 : 512;
@@ -196,7 +205,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sRes = smem + Cfg::kStages * Cfg::kStageBytes;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sRes + Cfg::kResBytes);
+  uint8_t* sOut = sRes + Cfg::kResBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sOut + Cfg::kOutBytes);
   uint64_t* empty_bar = full_bar + Cfg::kStages;
   uint64_t* tfull_bar = empty_bar + Cfg::kStages;
   uint64_t* tempty_bar = tfull_bar + 2;
@@ -433,6 +443,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                       (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)
                                    : ((p.ldc & 7) == 0 && (p.strideC & 7) == 0 &&
                                       (reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    const bool c_tma = !PEER && p.c_tma != 0;                 // warp-uniform
+    uint8_t* stage_w = sOut + (warp - 2) * Cfg::kOutWarpBytes;  // this warp's staging rows (1024-byte aligned)
+    const CUtensorMap* tmC = &gathered.m[1];
     uint32_t lt = 0;
     for (int t = cta_id; t < p.num_tiles; t += compute_ctas, ++lt) {
       const int b = t / tiles_per_batch;
@@ -565,6 +578,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int j = 0; j < 32; ++j)
                 if (n0 + j < n_limit) cp[j] = f[j];
             }
+          } else if (c_tma) {
+            // this chunk is one half of the warp's 64-column box: four 16-byte units of staging row `lane`
+#pragma unroll
+            for (int j8 = 0; j8 < 4; ++j8) {
+              uint4 u;
+              u.x = pack_bf16x2(f[j8 * 8], f[j8 * 8 + 1]);
+              u.y = pack_bf16x2(f[j8 * 8 + 2], f[j8 * 8 + 3]);
+              u.z = pack_bf16x2(f[j8 * 8 + 4], f[j8 * 8 + 5]);
+              u.w = pack_bf16x2(f[j8 * 8 + 6], f[j8 * 8 + 7]);
+              *reinterpret_cast<uint4*>(stage_w + swz128_offset(lane, (c & 1) * 4 + j8)) = u;
+            }
           } else {
             __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(c_base) + b * p.strideC + c_off;
             if (n0 + 32 <= n_limit && (reinterpret_cast<uintptr_t>(cp) & 31) == 0) {
@@ -609,8 +633,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j) f[j] *= __uint_as_float(va[j]) * p.alpha;
-            if (row_ok) {
-              const int o0 = (n_base + c_begin * 32) / 3;
+            const int o0 = (n_base + c_begin * 32) / 3;
+            if (c_tma) {
+              if (lane == 0) tma_store_wait_read<0>();   // the previous box of this warp has left the staging rows
+              __syncwarp();
+              if (row_ok) {
+#pragma unroll
+                for (int j8 = 0; j8 < 4; ++j8) {
+                  uint4 u;
+                  u.x = pack_bf16x2(f[j8 * 8], f[j8 * 8 + 1]);
+                  u.y = pack_bf16x2(f[j8 * 8 + 2], f[j8 * 8 + 3]);
+                  u.z = pack_bf16x2(f[j8 * 8 + 4], f[j8 * 8 + 5]);
+                  u.w = pack_bf16x2(f[j8 * 8 + 6], f[j8 * 8 + 7]);
+                  *reinterpret_cast<uint4*>(stage_w + swz64_offset(lane, j8)) = u;
+                }
+              }
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_3d(tmC, stage_w, o0, mb * kBM + q * 32, b);
+                tma_store_commit();
+              }
+            } else if (row_ok) {
               __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.strideC +
                                   static_cast<long long>(m) * p.ldc + o0;
               if ((reinterpret_cast<uintptr_t>(cp) & 31) == 0) {
@@ -637,11 +681,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int c = c_begin; c < c_end; c += 2) {
         tmem_ld_wait();
         if (c + 1 < c_end) tmem_ld32(tmem_addr(tmem_base, q, acc * BN + (c + 1) * 32), vb);
+        if (c_tma) {
+          if (lane == 0) tma_store_wait_read<0>();   // the previous box of this warp has left the staging rows
+          __syncwarp();
+        }
         process(va, c);
         if (c + 1 < c_end) {
           tmem_ld_wait();
           if (c + 2 < c_end) tmem_ld32(tmem_addr(tmem_base, q, acc * BN + (c + 2) * 32), va);
           process(vb, c + 1);
+        }
+        if (c_tma) {
+          // columns past N (an odd last chunk) and rows past M hold stale bytes: the copy clips them
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(tmC, stage_w, n_base + c * 32, mb * kBM + q * 32, b);
+            tma_store_commit();
+          }
         }
       }
       tc_fence_before_sync();
@@ -655,6 +712,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         acc_phase ^= 1u;
       }
     }
+    if (c_tma && lane == 0) tma_store_wait_all<0>();   // the staging rows are read and the boxes written
   }
 
   tc_fence_before_sync();
@@ -718,6 +776,27 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
                    CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     p.res_tma = 1;
+  }
+  p.c_tma = 0;
+  {
+    static const bool c_tma_on = [] {
+      const char* e = getenv("UBM_GEMM_TMA_STORE");
+      return e == nullptr || e[0] != '0';
+    }();
+    const bool swiglu = p.act == 5;
+    const long long n_out = swiglu ? p.N / 3 : p.N;
+    if (c_tma_on && !p.out_fp32 && p.cblk_col == 0 && p.c_peer_rows == 0 && (p.ldc & 7) == 0 &&
+        (p.batch == 1 || (p.strideC & 7) == 0) && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 &&
+        (swiglu || BN != 192)) {
+      const long long sc = p.batch == 1 ? (long long)p.M * p.ldc : p.strideC;
+      uint64_t dC[3] = {(uint64_t)n_out, (uint64_t)p.M, (uint64_t)p.batch};
+      uint64_t sC[2] = {(uint64_t)p.ldc * 2, (uint64_t)sc * 2};
+      uint32_t bC[3] = {swiglu ? 32u : 64u, 32, 1};
+      rc = make_tmap(&aux.m[1], p.C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dC, sC, bC,
+                     swiglu ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc) return rc;
+      p.c_tma = 1;
+    }
   }
   // launched so that its set-up may overlap the tail of the previous kernel in the stream (see the kernel)
   static const bool pdl = [] {
