@@ -52,7 +52,20 @@ struct PairProjParams {
   KernelStatus* status;
   int num_tiles;
   PeerSrc src;       // src.n > 0: the input rows are columns of z fetched from their owners (see host_util.h)
+  // q | k | v | gate leave through shared memory: every epilogue warp stages its 32 rows x 32 columns (64-byte
+  // swizzle) and one lane stores the box with a bulk tensor copy (maps in PairOutMaps).  Off when a warp's 32 rows
+  // could straddle two values of the first pair index under the transposed write (N not a multiple of 32).
+  int out_tma;
 };
+
+// Output maps, one per q / k / v / gate buffer.  Plain write: {128, R, 1} with boxes {32, 32, 1} at (column, row, 0).
+// Transposed write (ending node): {128, N, N} = out[pk][pi][channel] with boxes {32, 1, 32} at (column, pi, pk0):
+// 32 consecutive second indices of one first index land on 32 rows that are N * 128 elements apart.
+struct PairOutMaps {
+  CUtensorMap m[4];
+};
+constexpr int kPPOutWarpBytes = 32 * 64;
+constexpr int kPPOutBytes = 8 * kPPOutWarpBytes;
 
 // Optional timeline (build with -DUBM_PP_TIMELINE): CTA 0 stamps clock64 at fixed points of its first tiles
 // into a global buffer [4 roles][kPPTlTiles][8 events] (roles: producer, MMA issuer, epilogue group 0, 1).
@@ -70,12 +83,14 @@ __device__ long long g_pp_timeline[4 * kPPTlTiles * 8];
 template <int MODE>
 __global__ void __launch_bounds__(320, 1)
 pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
-                 const __grid_constant__ PeerSrcMaps peers, PairProjParams p) {
+                 const __grid_constant__ PeerSrcMaps peers, const __grid_constant__ PairOutMaps outs,
+                 PairProjParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sW = smem;                               // 128 KB
   uint8_t* sX = smem + kPPWBytes;                   // stages * 32 KB
-  float* sColsum = reinterpret_cast<float*>(sX + kPPStages * kPPXBytes);  // 512
+  uint8_t* sOut = sX + kPPStages * kPPXBytes;       // 8 warps x 2 KB of output staging
+  float* sColsum = reinterpret_cast<float*>(sOut + kPPOutBytes);          // 512
   float* sColbias = sColsum + 512;                                         // 512
   float* sWb = sColbias + 512;                                             // kPPMaxHeads * 128
   uint64_t* bars = reinterpret_cast<uint64_t*>(sWb + kPPMaxHeads * 128);
@@ -212,6 +227,8 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const int grp = (warp - 2) >> 2;  // 0 or 1: which 256-column half
     const int q = warp & 3;           // TMEM lane quadrant
     const int row_in_tile = q * 32 + lane;
+    const bool out_tma = p.out_tma != 0;                 // warp-uniform
+    uint8_t* stage_w = sOut + (warp - 2) * kPPOutWarpBytes;
     int stage = 0;
     uint32_t phase = 0;
     uint32_t acc_phase = 0;
@@ -302,20 +319,52 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         const float2 b2 = make_float2(-mu * rstd, -mu * rstd);
         // 32-column chunks, the tensor-memory load of the next chunk in flight while this one is processed;
         // the chunk body exists twice (ping-pong registers), not eight times
+        // first row of this warp's 32 (a multiple of 32): its pair index places the warp's output box
+        const long long r0 = static_cast<long long>(t) * kPPRows + q * 32;
+        const int bi = static_cast<int>(r0 / p.N);
+        const int bk = static_cast<int>(r0 - static_cast<long long>(bi) * p.N);
         auto chunk = [&](const uint32_t (&av)[32], const int c0) {
-          if (!row_ok) return;
-          if (q == 0 && lane == 0 && c0 == 32) PP_STAMP(2 + grp, lt, 5);
-          float f[32];
-          ln_fold32(av, a2, b2, sColsum + grp * 256 + c0, sColbias + grp * 256 + c0, f);
-          if (grp == 1 && c0 >= 128) {      // gate columns (warp-uniform)
-#pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = sigmoidf_fast(f[j]);
+          if (out_tma) {
+            if (lane == 0) tma_store_wait_read<0>();    // the previous box of this warp has left the staging rows
+            __syncwarp();
           }
-          if (q == 0 && lane == 0 && c0 == 32) PP_STAMP(2 + grp, lt, 6);
-          __nv_bfloat16* dst = (c0 < 128 ? o0 + c0 : o1 + (c0 - 128));
-          st_bf16x16(dst, f);
-          st_bf16x16(dst + 16, f + 16);
-          if (q == 0 && lane == 0 && c0 == 32) PP_STAMP(2 + grp, lt, 7);
+          if (row_ok) {
+            if (q == 0 && lane == 0 && c0 == 32) PP_STAMP(2 + grp, lt, 5);
+            float f[32];
+            ln_fold32(av, a2, b2, sColsum + grp * 256 + c0, sColbias + grp * 256 + c0, f);
+            if (grp == 1 && c0 >= 128) {      // gate columns (warp-uniform)
+#pragma unroll
+              for (int j = 0; j < 32; ++j) f[j] = sigmoidf_fast(f[j]);
+            }
+            if (q == 0 && lane == 0 && c0 == 32) PP_STAMP(2 + grp, lt, 6);
+            if (out_tma) {
+#pragma unroll
+              for (int j8 = 0; j8 < 4; ++j8) {
+                uint4 u;
+                u.x = pack_bf16x2(f[j8 * 8], f[j8 * 8 + 1]);
+                u.y = pack_bf16x2(f[j8 * 8 + 2], f[j8 * 8 + 3]);
+                u.z = pack_bf16x2(f[j8 * 8 + 4], f[j8 * 8 + 5]);
+                u.w = pack_bf16x2(f[j8 * 8 + 6], f[j8 * 8 + 7]);
+                *reinterpret_cast<uint4*>(stage_w + swz64_offset(lane, j8)) = u;
+              }
+            } else {
+              __nv_bfloat16* dst = (c0 < 128 ? o0 + c0 : o1 + (c0 - 128));
+              st_bf16x16(dst, f);
+              st_bf16x16(dst + 16, f + 16);
+            }
+            if (q == 0 && lane == 0 && c0 == 32) PP_STAMP(2 + grp, lt, 7);
+          }
+          if (out_tma) {
+            // rows past R hold stale bytes: the copy clips them
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              const CUtensorMap* om = &outs.m[grp * 2 + (c0 >> 7)];
+              if (p.transpose_out) tma_store_3d(om, stage_w, c0 & 127, bi, bk);
+              else tma_store_3d(om, stage_w, c0 & 127, static_cast<int>(r0), 0);
+              tma_store_commit();
+            }
+          }
         };
         uint32_t va[32], vb[32];
         tmem_ld32(tbase, va);
@@ -339,6 +388,7 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       }
       acc_phase ^= 1u;
     }
+    if (out_tma && lane == 0) tma_store_wait_all<0>();   // the staging rows are read and the boxes written
   }
 
   tc_fence_before_sync();
@@ -349,7 +399,9 @@ pair_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   }
 }
 
-constexpr int kPPSmemBytes = kPPWBytes + kPPStages * kPPXBytes + (512 + 512 + kPPMaxHeads * 128) * 4 + 256 + 1024;
+constexpr int kPPSmemBytes =
+    kPPWBytes + kPPStages * kPPXBytes + kPPOutBytes + (512 + 512 + kPPMaxHeads * 128) * 4 + 256 + 1024;
+static_assert(kPPSmemBytes <= 232448, "shared memory of one CTA");
 
 template <int MODE>
 static int launch_pair_proj(const void* x, const void* w, PairProjParams p, cudaStream_t stream,
@@ -373,11 +425,42 @@ static int launch_pair_proj(const void* x, const void* w, PairProjParams p, cuda
   rc = make_tmap(&tmW, w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dW, sW, bW, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
   p.num_tiles = static_cast<int>((p.R + kPPRows - 1) / kPPRows);
+  PairOutMaps outs;
+  for (int i = 0; i < 4; ++i) outs.m[i] = tmX;
+  p.out_tma = 0;
+  {
+    static const bool on = [] {
+      const char* e = getenv("UBM_PROJ_TMA_STORE");
+      return e == nullptr || e[0] != '0';
+    }();
+    void* bufs[4] = {p.q, p.k, p.v, p.g};
+    bool ok = on && MODE == MODE_TRIATT && p.R < (1ll << 31) && (!p.transpose_out || (p.N % 32) == 0);
+    for (int i = 0; i < 4; ++i) ok = ok && bufs[i] != nullptr && (reinterpret_cast<uintptr_t>(bufs[i]) & 15) == 0;
+    if (ok) {
+      for (int i = 0; i < 4; ++i) {
+        if (p.transpose_out) {
+          uint64_t d[3] = {128, (uint64_t)p.N, (uint64_t)p.N};
+          uint64_t st[2] = {128 * 2, (uint64_t)p.N * 128 * 2};
+          uint32_t b[3] = {32, 1, 32};
+          rc = make_tmap(&outs.m[i], bufs[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d, st, b,
+                         CU_TENSOR_MAP_SWIZZLE_64B);
+        } else {
+          uint64_t d[3] = {128, (uint64_t)p.R, 1};
+          uint64_t st[2] = {128 * 2, (uint64_t)p.R * 128 * 2};
+          uint32_t b[3] = {32, 32, 1};
+          rc = make_tmap(&outs.m[i], bufs[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d, st, b,
+                         CU_TENSOR_MAP_SWIZZLE_64B);
+        }
+        if (rc) return rc;
+      }
+      p.out_tma = 1;
+    }
+  }
   auto kern = pair_proj_kernel<MODE>;
   rc = set_smem(kern, kPPSmemBytes);
   if (rc) return rc;
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  kern<<<grid, 320, kPPSmemBytes, stream>>>(tmX, tmW, maps, p);
+  kern<<<grid, 320, kPPSmemBytes, stream>>>(tmX, tmW, maps, outs, p);
   UBM_CHECK_LAUNCH("pair_proj_kernel");
   return UBM_OK;
 }

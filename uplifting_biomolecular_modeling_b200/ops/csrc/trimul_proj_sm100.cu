@@ -42,16 +42,24 @@ struct TrimulProjParams {
   float* stats_out;       // optional [R][2]
   KernelStatus* status;
   PeerSrc src;            // src.n > 0: the input rows are columns of z fetched from their owners (see host_util.h)
+  // the planes leave through shared memory: every epilogue warp stages 32 channels x 32 entries (64-byte swizzle)
+  // and one lane stores the box {32 entries, 1 row, 32 planes} with a bulk tensor copy (map tmP over
+  // {Np, plane_rows, 256})
+  int out_tma;
 };
+constexpr int kTPOutWarpBytes = 32 * 64;
+constexpr int kTPOutBytes = 8 * kTPOutWarpBytes;
 
 __global__ void __launch_bounds__(320, 1)
 trimul_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
-                   const __grid_constant__ PeerSrcMaps peers, TrimulProjParams p) {
+                   const __grid_constant__ PeerSrcMaps peers, const __grid_constant__ CUtensorMap tmP,
+                   TrimulProjParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sW = smem;                               // 128 KB
   uint8_t* sX = smem + kTPWBytes;                   // stages * 32 KB
-  float* sStat = reinterpret_cast<float*>(sX + kTPStages * kTPXBytes);   // [2 groups][2 parities][3][128]
+  uint8_t* sOut = sX + kTPStages * kTPXBytes;       // 8 warps x 2 KB of output staging
+  float* sStat = reinterpret_cast<float*>(sOut + kTPOutBytes);           // [2 groups][2 parities][3][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + 2 * 2 * 3 * 128);
   uint64_t* x_full = bars;                 // [stages]
   uint64_t* x_empty = x_full + kTPStages;  // [stages]
@@ -179,6 +187,8 @@ trimul_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     uint32_t acc_phase = 0;
     uint32_t par = 0;
     const bool wide = (p.Np & 15) == 0;   // plane rows 32-byte aligned: 32-byte stores
+    const bool out_tma = p.out_tma != 0;  // warp-uniform
+    uint8_t* stage_w = sOut + (warp - 2) * kTPOutWarpBytes;
     for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, par ^= 1u) {
       const int i = t / p.tiles_per_row;
       const int s0 = (t - i * p.tiles_per_row) * kTPRows;
@@ -272,7 +282,22 @@ trimul_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           u[j].w = pack_bf16x2(o[j * 8 + 6], o[j * 8 + 7]);
         }
         const int sc = s0 + ci * 16;
-        if (wide && sc + 16 <= p.Np) {
+        if (out_tma) {
+          if ((ci & 1) == 0) {
+            if (lane == 0) tma_store_wait_read<0>();   // the previous box of this warp has left the staging rows
+            __syncwarp();
+          }
+          *reinterpret_cast<uint4*>(stage_w + swz64_offset(lane, (ci & 1) * 2)) = u[0];
+          *reinterpret_cast<uint4*>(stage_w + swz64_offset(lane, (ci & 1) * 2 + 1)) = u[1];
+          if (ci & 1) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&tmP, stage_w, s0 + (ci >> 1) * 32, i, grp * 128 + q * 32);   // entries past Np are clipped
+              tma_store_commit();
+            }
+          }
+        } else if (wide && sc + 16 <= p.Np) {
           st_global_256(dst + ci * 16, u[0], u[1]);   // a whole 32-byte sector per lane
         } else {
           if (sc < p.Np) *reinterpret_cast<uint4*>(dst + ci * 16) = u[0];
@@ -288,6 +313,7 @@ trimul_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       }
       acc_phase ^= 1u;
     }
+    if (out_tma && lane == 0) tma_store_wait_all<0>();   // the staging rows are read and the boxes written
   }
 
   tc_fence_before_sync();
@@ -298,7 +324,8 @@ trimul_proj_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
   }
 }
 
-constexpr int kTPSmemBytes = kTPWBytes + kTPStages * kTPXBytes + 2 * 2 * 3 * 128 * 4 + 256 + 1024;
+constexpr int kTPSmemBytes = kTPWBytes + kTPStages * kTPXBytes + kTPOutBytes + 2 * 2 * 3 * 128 * 4 + 256 + 1024;
+static_assert(kTPSmemBytes <= 232448, "shared memory of one CTA");
 
 }  // namespace ubm
 
@@ -344,10 +371,26 @@ static int trimul_proj_impl(const void* z, const void* w, const void* colsum, co
     rc = make_peer_src(&maps, &p.src, z_ptrs, peer_rows, npeers, me, N, tmX);
     if (rc) return rc;
   }
+  CUtensorMap tmP = tmX;
+  p.out_tma = 0;
+  {
+    static const bool on = [] {
+      const char* e = getenv("UBM_PROJ_TMA_STORE");
+      return e == nullptr || e[0] != '0';
+    }();
+    if (on && (reinterpret_cast<uintptr_t>(planes) & 15) == 0) {
+      uint64_t dP[3] = {(uint64_t)Np, (uint64_t)plane_rows, 256};
+      uint64_t sP[2] = {(uint64_t)Np * 2, (uint64_t)plane_rows * Np * 2};
+      uint32_t bP[3] = {32, 1, 32};
+      rc = make_tmap(&tmP, planes, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dP, sP, bP, CU_TENSOR_MAP_SWIZZLE_64B);
+      if (rc) return rc;
+      p.out_tma = 1;
+    }
+  }
   rc = set_smem(trimul_proj_kernel, kTPSmemBytes);
   if (rc) return rc;
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  trimul_proj_kernel<<<grid, 320, kTPSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmX, tmW, maps, p);
+  trimul_proj_kernel<<<grid, 320, kTPSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmX, tmW, maps, tmP, p);
   UBM_CHECK_LAUNCH("trimul_proj_kernel");
   return UBM_OK;
 }
