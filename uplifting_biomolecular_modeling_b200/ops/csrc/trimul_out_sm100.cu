@@ -33,18 +33,25 @@ struct TrimulOutParams {
   int add_residual;
   KernelStatus* status;
   int tiles_per_i, num_tiles;
+  // the output rows leave through shared memory: every epilogue warp stages 32 rows x 32 channels (64-byte swizzle)
+  // and one lane stores the box with a bulk tensor copy (map tmO over {128, N, rows}; second indices past N are
+  // clipped)
+  int out_tma;
 };
+constexpr int kTOOutWarpBytes = 32 * 64;
+constexpr int kTOOutBytes = 8 * kTOOutWarpBytes;
 
 __global__ void __launch_bounds__(320, 1)
 trimul_out_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmZ,
                   const __grid_constant__ CUtensorMap tmWo, const __grid_constant__ CUtensorMap tmWg,
-                  TrimulOutParams p) {
+                  const __grid_constant__ CUtensorMap tmO, TrimulOutParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sWo = smem;                    // 32 KB: two k-blocks [128][64]
   uint8_t* sWg = smem + kTOTileBytes;     // 32 KB
   uint8_t* sSt = smem + 2 * kTOTileBytes; // stages: {x tile 32 KB, z tile 32 KB}
-  float* sConst = reinterpret_cast<float*>(sSt + kTOStages * kTOStageBytes);  // 4 x 128
+  uint8_t* sOut = sSt + kTOStages * kTOStageBytes;   // 8 warps x 2 KB of output staging
+  float* sConst = reinterpret_cast<float*>(sOut + kTOOutBytes);               // 4 x 128
   float* sStats = sConst + 512;                                               // [2 tiles][128 rows][4]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sStats + 2 * 128 * 4);
   uint64_t* full = bars;                 // [stages]
@@ -176,6 +183,8 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     const int grp = (warp - 2) >> 2;
     const int q = warp & 3;
     const int row = q * 32 + lane;
+    const bool out_tma = p.out_tma != 0;   // warp-uniform
+    uint8_t* stage_w = sOut + (warp - 2) * kTOOutWarpBytes;
     int stage = 0;
     uint32_t phase = 0;
     int acc = 0;
@@ -238,6 +247,10 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         tmem_ld32(tO + c0, ov);
         tmem_ld32(tG + c0, gv);
         tmem_ld_wait();
+        if (out_tma) {
+          if (lane == 0) tma_store_wait_read<0>();   // the previous box of this warp has left the staging rows
+          __syncwarp();
+        }
         if (row_ok) {
           float f[32], fg[32];
           const int cb0 = grp * 64 + c0;
@@ -266,9 +279,29 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
               }
             }
           }
-          __nv_bfloat16* dst = p.out + r * 128 + grp * 64 + c0;
-          st_bf16x16(dst, f);
-          st_bf16x16(dst + 16, f + 16);
+          if (out_tma) {
+#pragma unroll
+            for (int j8 = 0; j8 < 4; ++j8) {
+              uint4 u;
+              u.x = pack_bf16x2(f[j8 * 8], f[j8 * 8 + 1]);
+              u.y = pack_bf16x2(f[j8 * 8 + 2], f[j8 * 8 + 3]);
+              u.z = pack_bf16x2(f[j8 * 8 + 4], f[j8 * 8 + 5]);
+              u.w = pack_bf16x2(f[j8 * 8 + 6], f[j8 * 8 + 7]);
+              *reinterpret_cast<uint4*>(stage_w + swz64_offset(lane, j8)) = u;
+            }
+          } else {
+            __nv_bfloat16* dst = p.out + r * 128 + grp * 64 + c0;
+            st_bf16x16(dst, f);
+            st_bf16x16(dst + 16, f + 16);
+          }
+        }
+        if (out_tma) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&tmO, stage_w, grp * 64 + c0, j0 + q * 32, i);
+            tma_store_commit();
+          }
         }
       }
       tc_fence_before_sync();
@@ -286,6 +319,7 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         acc_phase ^= 1u;
       }
     }
+    if (out_tma && lane == 0) tma_store_wait_all<0>();   // the staging rows are read and the boxes written
   }
 
   tc_fence_before_sync();
@@ -296,7 +330,9 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   }
 }
 
-constexpr int kTOSmemBytes = 2 * kTOTileBytes + kTOStages * kTOStageBytes + (512 + 2 * 128 * 4) * 4 + 256 + 1024;
+constexpr int kTOSmemBytes =
+    2 * kTOTileBytes + kTOStages * kTOStageBytes + kTOOutBytes + (512 + 2 * 128 * 4) * 4 + 256 + 1024;
+static_assert(kTOSmemBytes <= 232448, "shared memory of one CTA");
 
 }  // namespace ubm
 
@@ -346,10 +382,26 @@ extern "C" int ubm_trimul_out_rows(const void* x, const void* z, const void* wo,
   p.status = static_cast<KernelStatus*>(status);
   p.tiles_per_i = (N + 127) / 128;
   p.num_tiles = p.tiles_per_i * rows;
+  CUtensorMap tmO = tmZ;
+  p.out_tma = 0;
+  {
+    static const bool on = [] {
+      const char* e = getenv("UBM_PROJ_TMA_STORE");
+      return e == nullptr || e[0] != '0';
+    }();
+    if (on && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+      uint64_t d[3] = {128, (uint64_t)N, (uint64_t)rows};
+      uint64_t st[2] = {256, (uint64_t)N * 256};
+      uint32_t b[3] = {32, 32, 1};
+      int rc2 = make_tmap(&tmO, out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d, st, b, CU_TENSOR_MAP_SWIZZLE_64B);
+      if (rc2) return rc2;
+      p.out_tma = 1;
+    }
+  }
   int rc = set_smem(trimul_out_kernel, kTOSmemBytes);
   if (rc) return rc;
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  trimul_out_kernel<<<grid, 320, kTOSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmX, tmZ, tmWo, tmWg, p);
+  trimul_out_kernel<<<grid, 320, kTOSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmX, tmZ, tmWo, tmWg, tmO, p);
   UBM_CHECK_LAUNCH("trimul_out_kernel");
   return UBM_OK;
 }
