@@ -154,15 +154,21 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     const bool leader = elect_one();
     {
       constexpr uint32_t idesc = umma_idesc_bf16(128, 128);
-      uint32_t g = 0;   // chunks whose GEMM1 has been issued
-      uint32_t g2 = 0;  // chunks whose GEMM2 has been issued
-      uint32_t xt = 0;
-      uint32_t tile_cnt = 0;
-      auto gemm2 = [&](uint32_t c, bool first_of_tile) {
+      // One flat loop over this CTA's chunks (global index G = local tile * nch + chunk).  Step G issues the first
+      // GEMM of chunk G and then the second GEMM of chunk G - 2: the accumulator buffer of chunk G is released halfway
+      // through the SwiGLU pass of chunk G - 2, so the first GEMM of G runs under the rest of that pass and under
+      // the pass of chunk G - 1 on the other group.  (Issuing the second GEMM of G - 1 here instead made every
+      // first GEMM wait for the END of a SwiGLU pass, and the group that had just finished idled for its duration.)
+      const uint32_t my_tiles =
+          static_cast<uint32_t>(p.num_tiles) > blockIdx.x ? (p.num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+      const uint32_t total = my_tiles * static_cast<uint32_t>(nch);
+      auto gemm2 = [&](uint32_t c) {
+        const uint32_t tl = c / nch, hh = c - tl * nch;
+        const bool first_of_tile = hh == 0;
         const int b = c & 1;
         mbar_wait(&wo_full[b], (c >> 1) & 1u, ws, 43, b);
         mbar_wait(&h_full[b], (c >> 1) & 1u, ws, 33, b);
-        if (first_of_tile) mbar_wait(y_empty, (tile_cnt & 1u) ^ 1u, ws, 34);
+        if (first_of_tile) mbar_wait(y_empty, (tl & 1u) ^ 1u, ws, 34);
         tc_fence_after_sync();
         const uint32_t ha = smem_u32(sH + b * kTRHBytes);
         const uint32_t wo = smem_u32(sW + b * kTRWStage + kTRWabBytes);
@@ -175,43 +181,38 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     (first_of_tile && k == 0) ? 0u : 1u);
           umma_commit(&h_empty[b]);
           umma_commit(&wo_empty[b]);
+          if (hh == static_cast<uint32_t>(nch) - 1) umma_commit(y_full);
         }
         __syncwarp();
       };
-      for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++xt, ++tile_cnt) {
-        const int xs = xt & 1;
-        mbar_wait(&x_full[xs], (xt >> 1) & 1u, ws, 35, xs);
+      for (uint32_t G = 0; G < total; ++G) {
+        const uint32_t tl = G / nch, hh = G - tl * nch;
+        const int xs = tl & 1;
+        if (hh == 0) mbar_wait(&x_full[xs], (tl >> 1) & 1u, ws, 35, xs);
         const uint32_t xa = smem_u32(sX + xs * kTRXBytes);
-        for (int h = 0; h < nch; ++h, ++g) {
-          const int b = g & 1;
-          mbar_wait(&w_full[b], (g >> 1) & 1u, ws, 36, b);
-          mbar_wait(&ab_empty[b], ((g >> 1) & 1u) ^ 1u, ws, 37, b);
-          tc_fence_after_sync();
-          const uint32_t wa = smem_u32(sW + b * kTRWStage);
-          const uint64_t ad0 = umma_smem_desc(xa, 16, 1024, kSwizzle128);
-          const uint64_t bd0 = umma_smem_desc(wa, 16, 1024, kSwizzle128);
-          if (leader) {
+        const int b = G & 1;
+        mbar_wait(&w_full[b], (G >> 1) & 1u, ws, 36, b);
+        mbar_wait(&ab_empty[b], ((G >> 1) & 1u) ^ 1u, ws, 37, b);
+        tc_fence_after_sync();
+        const uint32_t wa = smem_u32(sW + b * kTRWStage);
+        const uint64_t ad0 = umma_smem_desc(xa, 16, 1024, kSwizzle128);
+        const uint64_t bd0 = umma_smem_desc(wa, 16, 1024, kSwizzle128);
+        if (leader) {
 #pragma unroll
-            for (int kb = 0; kb < 2; ++kb) {
+          for (int kb = 0; kb < 2; ++kb) {
 #pragma unroll
-              for (int k = 0; k < 4; ++k)
-                umma_ss(tAB + b * 128, ad0 + static_cast<uint64_t>(kb * (16384 >> 4) + k * 2),
-                        bd0 + static_cast<uint64_t>(kb * (16384 >> 4) + k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
-            }
-            umma_commit(&w_empty[b]);
-            umma_commit(&ab_full[b]);
+            for (int k = 0; k < 4; ++k)
+              umma_ss(tAB + b * 128, ad0 + static_cast<uint64_t>(kb * (16384 >> 4) + k * 2),
+                      bd0 + static_cast<uint64_t>(kb * (16384 >> 4) + k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          __syncwarp();
-          if (h >= 1) {
-            gemm2(g2, h == 1);
-            ++g2;
-          }
+          umma_commit(&w_empty[b]);
+          umma_commit(&ab_full[b]);
         }
-        gemm2(g2, nch == 1);
-        ++g2;
-        if (leader) umma_commit(y_full);
         __syncwarp();
+        if (G >= 2) gemm2(G - 2);
       }
+      if (total >= 2) gemm2(total - 2);
+      if (total >= 1) gemm2(total - 1);
     }
   } else {
     // ------------------------------------------------------------------ SwiGLU / epilogue groups
