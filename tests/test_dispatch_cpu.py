@@ -61,3 +61,23 @@ def test_checkpoint_key_collisions_and_shape_mismatches_are_named(tmp_path):
         weights.load_checkpoint(lin, str(tmp_path / "c.pt"))
     rep = weights.load_checkpoint(lin, str(tmp_path / "c.pt"), strict=False)
     assert rep.matched == 1 and rep.shape_mismatch and rep.shape_mismatch[0].startswith("weight:")
+
+
+def test_token_window_of_a_lever_is_a_declared_counted_fallback(monkeypatch):
+    """The ``below_min`` rung: a call outside a lever's token window runs the plain statement, is counted under its
+    own reason and leaves the ledger closed (the window is a setting, not a degradation)."""
+    monkeypatch.setenv("UBM_MIN_TOKENS_FUSED_TRIMUL", "128")
+    monkeypatch.setenv("UBM_MAX_TOKENS", "4096")
+    _fresh()
+    assert dispatch.decide("fused_trimul", None, "c128", 64) is False
+    assert dispatch.decide("fused_trimul", None, "c128", 256) is True
+    assert dispatch.decide("fused_trimul", None, "c128", 8192) is False
+    assert dispatch.decide("fused_transition", None, "c128", 64) is True       # the general window has no minimum
+    lg = counters.BOOK.get("fused_trimul")
+    assert lg.served == 1 and lg.fallbacks == {"below_min_tokens": 1, "above_max_tokens": 1}
+    assert lg.gate() is None
+    gate = dispatch.size_gate("fused_trimul")
+    assert gate.total == 3 and "below_min_tokens:128=1" in gate.words()
+    reasons = {r["reason"] for r in cell_census.records() if r["family"] == "trimul" and r["outcome"] == "named_fallback"}
+    assert reasons == {"below_min_tokens", "above_max_tokens"}
+    _fresh()

@@ -232,3 +232,28 @@ def test_big_mode_matches_fast_and_lowers_the_peak():
     a, b = outs[0][0][v][:, v].float(), outs[1][0][v][:, v].float()
     assert ((a - b).abs().mean() / a.abs().mean()).item() < 5e-3
     assert peaks[1] < 0.7 * peaks[0], peaks
+
+
+def test_rigid_alignment_runs_inside_the_sampler_graph():
+    """The sampler's alignment of the noisy coordinates onto the denoised ones (fixed-sweep fp64 Jacobi SVD, no solver
+    call) on the GPU: same rotation as on the CPU, and a captured sampler step with the alignment switched on replays
+    bit for bit (the predictor compares the first replay with the eager step and refuses the graph otherwise)."""
+    from uplifting_biomolecular_modeling_b200 import api
+    from uplifting_biomolecular_modeling_b200.models import align, cofold
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(4, 200, 3, generator=g)
+    y = torch.randn(4, 200, 3, generator=g)
+    w = torch.rand(4, 200, generator=g)
+    ref = align.weighted_rigid_align(x, y, w)
+    got = align.weighted_rigid_align(x.cuda(), y.cuda(), w.cuda())
+    assert (got.cpu() - ref).abs().max() < 1e-4
+    pred = api.Predictor("tiny", mode="exact", device="cuda:0", seed=0)
+    pred.model.structure_module.align_reverse_diff = True
+    feats = cofold.synthetic_features(96, 8, pred.cfg, seed=1)
+    out = pred.predict(feats, steps=6)
+    assert torch.isfinite(out["coords"]).all()
+    assert getattr(pred, "graph_verified", 0) >= 1
+    off = api.Predictor("tiny", mode="off", device="cuda:0", seed=0)
+    off.model.structure_module.align_reverse_diff = True
+    want = off.predict(feats, steps=6)
+    assert torch.equal(out["coords"], want["coords"])

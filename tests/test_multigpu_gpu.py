@@ -77,3 +77,26 @@ def test_big_mode_worker_returns_a_structure(tmp_path):
                               extra_env={"PYTHONPATH": ROOT, "NCCL_NVLS_ENABLE": "0"}, echo_rank0=False)
     pred = torch.load(out / "prediction.pt")
     assert pred["coords"].dim() == 3 and torch.isfinite(pred["coords"]).all() and "plddt" in pred
+
+
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_layer_pipeline_over_two_gpus_matches_one():
+    """The layer split of the deep sequence models on two GPUs of one process: blocks placed by cost, two micro-batches
+    in flight on per-device streams, activations crossing by asynchronous peer copies ordered by events."""
+    from uplifting_biomolecular_modeling_b200.parallel import pipeline
+    torch.manual_seed(0)
+    blocks = [torch.nn.Sequential(torch.nn.Linear(256, 256), torch.nn.GELU()).eval() for _ in range(7)]
+    x = torch.randn(6, 128, 256)
+    with torch.no_grad():
+        ref = x.cuda(0)
+        for b in blocks:
+            ref = b.cuda(0)(ref)
+        ref = ref.cpu()
+    pp = pipeline.LayerPipeline(blocks, ["cuda:0", "cuda:1"], weights=[1, 1, 1, 3, 1, 1, 1])
+    assert [len(r) for r in pp.ranges] == [4, 3] or sum(len(r) for r in pp.ranges) == 7
+    for window in (1, 2, 3):
+        out = pp.forward(x.cuda(0), window=window)
+        torch.cuda.synchronize(0)
+        torch.cuda.synchronize(1)
+        assert out.device.index == 1
+        assert torch.allclose(out.cpu(), ref, atol=1e-5, rtol=1e-5), window

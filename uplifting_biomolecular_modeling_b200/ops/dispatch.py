@@ -32,6 +32,24 @@ LEVERS: Dict[str, Tuple[str, str, Tuple[str, ...]]] = {
 _SEEN: set = set()
 _SM: Optional[str] = None
 TIER = "fast"
+# lever -> token-count gate in front of the kernel (the ``below_min`` rung of the reference's ladder).  The kernels
+# here serve every size, so the default admits everything; ``UBM_MIN_TOKENS`` / ``UBM_MAX_TOKENS`` (all levers) and
+# ``UBM_MIN_TOKENS_<LEVER>`` / ``UBM_MAX_TOKENS_<LEVER>`` set a window, outside of which a call is a DECLARED
+# fallback (``below_min_tokens`` / ``above_max_tokens``: counted, named on the lever's line, not PARTIAL).
+_GATES: Dict[str, "object"] = {}
+SIZE_REASONS = ("below_min_tokens", "above_max_tokens")
+
+
+def size_gate(lever: str):
+    import os
+    from . import provider
+    g = _GATES.get(lever)
+    if g is None:
+        def env(word):
+            v = os.environ.get(f"UBM_{word}_TOKENS_{lever.upper()}") or os.environ.get(f"UBM_{word}_TOKENS")
+            return int(v) if v else None
+        g = _GATES[lever] = provider.SizeGate(lever, min_tokens=env("MIN") or 0, max_tokens=env("MAX"))
+    return g
 
 
 def set_tier(word: str) -> None:
@@ -54,7 +72,8 @@ def _sm() -> str:
 
 def ledger(lever: str) -> counters.Ledger:
     impl, _, declared = LEVERS.get(lever, ("unknown", lever, ()))
-    return counters.BOOK.get(lever, impl, declared_fallbacks=declared, strategy="F1.kernel_fusion")
+    return counters.BOOK.get(lever, impl, declared_fallbacks=tuple(declared) + SIZE_REASONS,
+                             strategy="F1.kernel_fusion")
 
 
 def decide(lever: str, reason: Optional[str], klass: Optional[str] = None, tokens: Optional[int] = None,
@@ -62,6 +81,8 @@ def decide(lever: str, reason: Optional[str], klass: Optional[str] = None, token
     """Record one call.  ``reason`` None = the kernel serves; otherwise the plain statement runs and the call is
     counted as ``fallback:<reason>``.  Returns True when the kernel serves."""
     lg = ledger(lever)
+    if reason is None and tokens is not None and not size_gate(lever).admit(int(tokens)):
+        reason = "below_min_tokens" if tokens < size_gate(lever).min_tokens else "above_max_tokens"
     if reason is None:
         lg.serve(klass)
     else:
@@ -94,5 +115,6 @@ def _census(lever, klass, tokens, reason, call, row) -> None:
 
 
 def reset() -> None:
-    """Forget which call classes were recorded (tests)."""
+    """Forget which call classes were recorded and re-read the size windows (tests)."""
     _SEEN.clear()
+    _GATES.clear()
