@@ -5,7 +5,8 @@
 Cases: ``attention`` (triangle-attention core, H=4 x D=32, rows = N), ``attention_d64`` (token attention,
 16 heads x 64, 5 samples), ``trimul_proj``, ``trimul_gemm``, ``trimul_out``, ``triatt_proj``, ``transition``,
 ``out_gemm`` (the [N*N,128] x [128,128] output projection with residual), ``trimul`` (three launches),
-``triatt`` (three launches), ``gemm_rows`` (--m --k --nn: a row GEMM with bias), ``window_attention`` (--m atoms,
+``triatt`` (three launches), ``causal_attention`` (--n tokens, --heads, head dimension 128; --lib 1 = the
+library call), ``gemm_rows`` (--m --k --nn: a row GEMM with bias), ``window_attention`` (--m atoms,
 5 samples, 4 heads x 32).  Inputs are larger than L2 for N >= 768.  Prints one line per case with the
 mean time, the algorithmic bytes and FLOPs, and the fractions of the measured peaks in MEASURED_PEAKS.json
 (fallback 6.65 TB/s, 1.59 PFLOP/s when the file is absent).
@@ -59,6 +60,8 @@ def main():
     ap.add_argument("--m", type=int, default=7680, help="rows of the gemm_rows case / atoms of window_attention")
     ap.add_argument("--k", type=int, default=768)
     ap.add_argument("--nn", type=int, default=3072)
+    ap.add_argument("--heads", type=int, default=32, help="causal_attention: heads")
+    ap.add_argument("--lib", type=int, default=0, help="causal_attention: 1 = time the library attention instead")
     ap.add_argument("--masked", type=int, default=0, help="attention: 1 = key mask with a padded tail of a tenth of the keys")
     ap.add_argument("--incoming", type=int, default=0, help="trimul / trimul_gemm: 1 = the incoming update (MN-major contraction)")
     a = ap.parse_args()
@@ -68,7 +71,7 @@ def main():
     torch.manual_seed(0)
     r = lambda *s: torch.randn(*s, device=dev) * 0.08  # noqa: E731
     ones, zeros = torch.ones(c, device=dev), torch.zeros(c, device=dev)
-    z = torch.randn(N, N, c, device=dev).bfloat16()
+    z = torch.randn(N, N, c, device=dev).bfloat16() if a.case not in ("causal_attention", "gemm_rows") else None
     Np = pair.ceil_to(N, 8)
     st = native.status_tensor(dev)
     stream = native.current_stream(dev)
@@ -157,6 +160,20 @@ def main():
         out = torch.empty((M, NN), dtype=torch.bfloat16, device=dev)
         fn = lambda: gemm.gemm(x, wt, bias=bvec, out=out)  # noqa: E731
         byts, flops = (x.numel() + wt.numel() + out.numel()) * 2, 2.0 * M * K * NN
+    elif a.case == "causal_attention":
+        # causal self-attention at head dimension 128: --n tokens, --heads heads, batch 1; --lib 1 times the library call
+        import torch.nn.functional as F
+        from uplifting_biomolecular_modeling_b200.ops import causal
+        T, Hh = N, a.heads
+        qkv = torch.randn(1, T, 3, Hh, 128, device=dev).bfloat16()
+        q, k, v = qkv.unbind(2)
+        out = torch.empty(1, T, Hh, 128, device=dev, dtype=torch.bfloat16)
+        if a.lib:
+            qh, kh, vh = (t.transpose(1, 2) for t in (q, k, v))
+            fn = lambda: F.scaled_dot_product_attention(qh, kh, vh, is_causal=True)  # noqa: E731
+        else:
+            fn = lambda: causal.causal_attention(q, k, v, out=out)  # noqa: E731
+        byts, flops = 4 * T * Hh * 128 * 2, 4.0 * T * T * 128 * Hh / 2
     elif a.case == "window_attention":
         B, A, H = 5, a.m // 32 * 32, 4
         xw = torch.randn(B * A, 3 * H * 32, device=dev).bfloat16()

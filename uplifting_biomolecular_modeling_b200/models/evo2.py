@@ -13,7 +13,8 @@ Prefill runs the medium / long operators as FFT convolutions; decoding keeps per
 tails, pole states, attention KV cache) and advances one token per step.  Tensor parallelism shards
 the channel dimension of every operator (``parallel.tp``): column-parallel input projections, row-parallel
 output projections whose reduce-scatter is done by the GEMM epilogue over peer memory.  The causal attention
-of the five attention layers is a library call (scaled_dot_product_attention).
+of the five attention layers is the library's fused attention; the package's own tcgen05 causal kernel
+(``ops/causal.py``, head dimension 128) is measured slower than it and is taken only on request.
 """
 from __future__ import annotations
 
@@ -344,6 +345,18 @@ class AttentionOperator(nn.Module):
         d = cfg.d_model
         self.qkv = nn.Linear(d, 3 * d, bias=False)
         self.out_proj = nn.Linear(d, d, bias=True)
+        self.impl = "torch"
+
+    def _causal(self, q, k, v):
+        """q, k, v: [B, L, H, hd] -> [B, L, H, hd].  The library's fused attention by default (it is the faster of
+        the two on B200: 1.51 against 1.05 PFLOP/s at 32768 tokens); with ``ops.causal.ENABLED`` the kernel path
+        takes the package's tcgen05 causal kernel at head dimension 128."""
+        if self.impl == "fused":
+            from ..ops import causal
+            if causal.ENABLED and causal.supported(q, k, v) is None:
+                return causal.causal_attention(q, k, v)
+        return F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                              is_causal=True).transpose(1, 2)
 
     def _qkv(self, x, pos, lin):
         """q, k, v as [B, L, heads held here, head_dim]; under tensor parallelism the projection returns only
@@ -359,10 +372,10 @@ class AttentionOperator(nn.Module):
         B, L, d = x.shape
         pos = torch.arange(L, device=x.device)
         q, k, v = self._qkv(x, pos, lin)
-        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
+        o = self._causal(q, k, v)
         if state is not None:
             state["k"], state["v"] = k, v
-        return lin(self.out_proj, o.transpose(1, 2).reshape(B, L, -1))
+        return lin(self.out_proj, o.reshape(B, L, -1))
 
     def step(self, x, state: dict, linear=None):
         lin = linear or (lambda m, t: m(t))
