@@ -260,39 +260,59 @@ def main():
     except Exception:  # noqa: BLE001
         pass
     cfg, h2d_bytes, d2h_bytes = pred.cfg, pred.h2d_bytes, pred.d2h_bytes
+    c = cfg
+    shape = "AF3-shaped" if args.config == "af3" else f"{args.config}-shaped"
+    model = (f"{shape} cofold ({c.pairformer_blocks} Pairformer blocks, {c.msa_blocks} MSA blocks, "
+             f"{c.token_depth}-block DiT, {c.samples}x{args.sampling_steps or c.sampling_steps} sampling)")
+    line = {"metric": f"predictions/hour at N={args.tokens} ({shape} cofold, {args.mode} mode)",
+            "value": round(value, 3),
+            "unit": "predictions/hour", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms, 3), "sec_per_prediction": round(ms / 1000.0, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic features, random-init weights", "impl": "ours",
+            "config": dict(CONFIG, model=model, tokens=args.tokens, msa_depth=args.msa_depth, mode=args.mode,
+                           global_batch=world, seq_len=args.tokens, parallelism=f"dp{world}",
+                           sampling_steps=args.sampling_steps or cfg.sampling_steps,
+                           samples=cfg.samples, trunk_passes=(cfg.recycles if args.recycles is None
+                                                                   else args.recycles) + 1),
+            "clocks": summarize_clocks(samples),
+            "e2e": {"value": round(value_e2e, 3), "unit": "predictions/hour", "ms_per_step": round(ms_e2e, 3),
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+                    "note": "Predictor.predict(host features): pinned-host feature copy in, coordinates / "
+                            "confidence copy out, every step; `value` is the same call on device-resident "
+                            "features with the result left on the device"},
+            "gpu_launches": launches, "finite_output": finite, "kernel_ledgers": ledgers, "big_mode": None}
+    emitted = threading.Lock()
+
+    def emit(big) -> None:
+        """The one JSON line (rank 0), exactly once."""
+        if not emitted.acquire(blocking=False):
+            return
+        if rank == 0:
+            line["big_mode"] = big
+            print(json.dumps(line), flush=True)
+
     big = None
     if os.environ.get("UBM_BENCH_BIG", "1") != "0" and args.tokens == 1536:
         # the second metric of the baseline (big-mode latency and peak memory at this run's P); measured after the
-        # headline regions, never inside them
+        # headline regions, never inside them.  It may not cost the headline line: an exception is recorded in its
+        # place, and a rank that is still inside it after the limit (a peer that never arrives) prints the line
+        # with the time-out recorded and leaves.
         del pred, feats_dev, out
+        limit = float(os.environ.get("UBM_BENCH_BIG_LIMIT_S", "420"))
+
+        def give_up():
+            emit({"error": f"big-mode measurement still running after {limit:.0f} s; abandoned"})
+            os._exit(0)
+        timer = threading.Timer(limit, give_up)
+        timer.daemon = True
+        timer.start()
         try:
             big = big_mode(args, world, rank, dev)
         except Exception as e:  # noqa: BLE001 - the headline line must still be printed
             big = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
-    if rank == 0:
-        c = cfg
-        shape = "AF3-shaped" if args.config == "af3" else f"{args.config}-shaped"
-        model = (f"{shape} cofold ({c.pairformer_blocks} Pairformer blocks, {c.msa_blocks} MSA blocks, "
-                 f"{c.token_depth}-block DiT, {c.samples}x{args.sampling_steps or c.sampling_steps} sampling)")
-        line = {"metric": f"predictions/hour at N={args.tokens} ({shape} cofold, {args.mode} mode)",
-                "value": round(value, 3),
-                "unit": "predictions/hour", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": round(ms, 3), "sec_per_prediction": round(ms / 1000.0, 4),
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-                "data": "synthetic features, random-init weights", "impl": "ours",
-                "config": dict(CONFIG, model=model, tokens=args.tokens, msa_depth=args.msa_depth, mode=args.mode,
-                               global_batch=world, seq_len=args.tokens, parallelism=f"dp{world}",
-                               sampling_steps=args.sampling_steps or cfg.sampling_steps,
-                               samples=cfg.samples, trunk_passes=(cfg.recycles if args.recycles is None
-                                                                       else args.recycles) + 1),
-                "clocks": summarize_clocks(samples),
-                "e2e": {"value": round(value_e2e, 3), "unit": "predictions/hour", "ms_per_step": round(ms_e2e, 3),
-                        "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
-                        "note": "Predictor.predict(host features): pinned-host feature copy in, coordinates / "
-                                "confidence copy out, every step; `value` is the same call on device-resident "
-                                "features with the result left on the device"},
-                "gpu_launches": launches, "finite_output": finite, "kernel_ledgers": ledgers, "big_mode": big}
-        print(json.dumps(line))
+        timer.cancel()
+    emit(big)
     if world > 1:
         dist.destroy_process_group()
     return 0

@@ -235,6 +235,12 @@ def test_row_kernels():
     sc, sh = _rand((64, 768), g).bfloat16(), _rand((64, 768), g).bfloat16()
     ref = torch.sigmoid(sc.float()) * torch.nn.functional.layer_norm(a.float(), (768,)) + sh.float()
     assert torch.allclose(rows.adaln_rows(a, sc, sh).float(), ref, atol=5e-2, rtol=3e-2)
+    # 128 channels (atom track): half a warp per row; odd row count, conditioning rows shared by three samples
+    a1 = _rand((3 * 333, 128), g).bfloat16()
+    sc1, sh1 = _rand((333, 128), g).bfloat16(), _rand((333, 128), g).bfloat16()
+    ref = (torch.sigmoid(sc1.float()) * torch.nn.functional.layer_norm(a1.float(), (128,)).view(3, 333, 128)
+           + sh1.float()).view(-1, 128)
+    assert torch.allclose(rows.adaln_rows(a1, sc1, sh1).float(), ref, atol=5e-2, rtol=3e-2)
     ab = _rand((64, 512), g).bfloat16()
     ref = torch.nn.functional.silu(ab[:, :256].float()) * ab[:, 256:].float()
     assert torch.allclose(rows.swiglu_rows(ab).float(), ref, atol=3e-2, rtol=3e-2)

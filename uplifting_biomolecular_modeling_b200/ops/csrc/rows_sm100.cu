@@ -377,6 +377,58 @@ __global__ void __launch_bounds__(256) adaln_rows_vec_kernel(const __nv_bfloat16
   }
 }
 
+// Rows of 128 channels (the atom track): half a warp per row, so every lane carries 16 bytes; with a whole warp per
+// row half of the lanes sat idle (20.5 us for 63840 rows, 1.6 TB/s).
+__global__ void __launch_bounds__(256) adaln_rows_c128_kernel(const __nv_bfloat16* __restrict__ a,
+                                                              const __nv_bfloat16* __restrict__ scale,
+                                                              const __nv_bfloat16* __restrict__ shift,
+                                                              __nv_bfloat16* __restrict__ out, long long R,
+                                                              long long cond_rows, long long ld_cond, float eps) {
+  constexpr int C = 128;
+  const int halves_per_block = blockDim.x >> 4;
+  const int l16 = threadIdx.x & 15;
+  const int c = l16 * 8;
+  for (long long r = static_cast<long long>(blockIdx.x) * halves_per_block + (threadIdx.x >> 4);
+       r < ((R + 1) & ~1ll); r += static_cast<long long>(gridDim.x) * halves_per_block) {
+    // both halves of a warp run the same number of iterations (R rounded up to even) so the shuffles stay whole
+    const bool ok = r < R;
+    float x[8];
+    float sum = 0.f, sumsq = 0.f;
+    if (ok) {
+      const uint4 u = *reinterpret_cast<const uint4*>(a + r * C + c);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        x[2 * j] = bf16_lo(w[j]);
+        x[2 * j + 1] = bf16_hi(w[j]);
+        sum += x[2 * j] + x[2 * j + 1];
+        sumsq += x[2 * j] * x[2 * j] + x[2 * j + 1] * x[2 * j + 1];
+      }
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) {
+      sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      sumsq += __shfl_xor_sync(0xffffffffu, sumsq, o);
+    }
+    if (!ok) continue;
+    const float mu = sum * (1.0f / C);
+    const float rstd = rsqrtf(fmaxf(sumsq * (1.0f / C) - mu * mu, 0.f) + eps);
+    const long long rc = r % cond_rows;
+    const uint4 us = __ldg(reinterpret_cast<const uint4*>(scale + rc * ld_cond + c));
+    const uint4 uh = __ldg(reinterpret_cast<const uint4*>(shift + rc * ld_cond + c));
+    const uint32_t ws[4] = {us.x, us.y, us.z, us.w};
+    const uint32_t wh[4] = {uh.x, uh.y, uh.z, uh.w};
+    uint32_t o4[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float y0 = sigmoidf_fast(bf16_lo(ws[j])) * ((x[2 * j] - mu) * rstd) + bf16_lo(wh[j]);
+      const float y1 = sigmoidf_fast(bf16_hi(ws[j])) * ((x[2 * j + 1] - mu) * rstd) + bf16_hi(wh[j]);
+      o4[j] = pack_bf16x2(y0, y1);
+    }
+    *reinterpret_cast<uint4*>(out + r * C + c) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+  }
+}
+
 // out = res + sigmoid(gate[r % cond_rows]) * x   (res may be null)
 __global__ void __launch_bounds__(256) gate_residual_kernel(const __nv_bfloat16* __restrict__ x,
                                                             const __nv_bfloat16* __restrict__ gate,
@@ -549,7 +601,9 @@ extern "C" int ubm_adaln_rows(const void* a, const void* scale, const void* shif
                    ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(scale) |
                      reinterpret_cast<uintptr_t>(shift) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
   const int grid = grid_for(R, 8);
-  if (vec && C <= 256) {
+  if (vec && C == 128) {
+    adaln_rows_c128_kernel<<<grid_for((R + 1) / 2 * 2, 16), 256, 0, st>>>(aa, sc, sh, oo, R, cond_rows, ld_cond, eps);
+  } else if (vec && C <= 256) {
     adaln_rows_vec_kernel<1><<<grid, 256, 0, st>>>(aa, sc, sh, oo, R, C, cond_rows, ld_cond, eps);
   } else if (vec && C <= 512) {
     adaln_rows_vec_kernel<2><<<grid, 256, 0, st>>>(aa, sc, sh, oo, R, C, cond_rows, ld_cond, eps);
