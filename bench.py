@@ -171,6 +171,41 @@ def big_mode(args, world, rank, dev):
     return out
 
 
+def second_metric_then_line(line: dict, measure, rank: int, limit_s: float, key: str = "big_mode",
+                            leave=os._exit):
+    """Run the optional second measurement and print the benchmark's one JSON line (rank 0) exactly once.
+
+    The second measurement may not cost the line: an exception is recorded in its place, and a rank that is still
+    inside it after ``limit_s`` (a peer that never arrives at a collective) prints the line with the time-out
+    recorded and leaves the process through ``leave(0)``.  Returns what was recorded under ``key``."""
+    once = threading.Lock()
+
+    def emit(value) -> None:
+        if not once.acquire(blocking=False):
+            return
+        if rank == 0:
+            line[key] = value
+            print(json.dumps(line), flush=True)
+
+    if measure is None:
+        emit(None)
+        return None
+
+    def give_up():
+        emit({"error": f"the measurement was still running after {limit_s:.0f} s; abandoned"})
+        leave(0)
+    timer = threading.Timer(limit_s, give_up)
+    timer.daemon = True
+    timer.start()
+    try:
+        value = measure()
+    except Exception as e:  # noqa: BLE001 - the headline line must still be printed
+        value = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
+    timer.cancel()
+    emit(value)
+    return value
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -282,37 +317,15 @@ def main():
                             "confidence copy out, every step; `value` is the same call on device-resident "
                             "features with the result left on the device"},
             "gpu_launches": launches, "finite_output": finite, "kernel_ledgers": ledgers, "big_mode": None}
-    emitted = threading.Lock()
-
-    def emit(big) -> None:
-        """The one JSON line (rank 0), exactly once."""
-        if not emitted.acquire(blocking=False):
-            return
-        if rank == 0:
-            line["big_mode"] = big
-            print(json.dumps(line), flush=True)
-
     big = None
     if os.environ.get("UBM_BENCH_BIG", "1") != "0" and args.tokens == 1536:
         # the second metric of the baseline (big-mode latency and peak memory at this run's P); measured after the
-        # headline regions, never inside them.  It may not cost the headline line: an exception is recorded in its
-        # place, and a rank that is still inside it after the limit (a peer that never arrives) prints the line
-        # with the time-out recorded and leaves.
+        # headline regions, never inside them
         del pred, feats_dev, out
-        limit = float(os.environ.get("UBM_BENCH_BIG_LIMIT_S", "420"))
-
-        def give_up():
-            emit({"error": f"big-mode measurement still running after {limit:.0f} s; abandoned"})
-            os._exit(0)
-        timer = threading.Timer(limit, give_up)
-        timer.daemon = True
-        timer.start()
-        try:
-            big = big_mode(args, world, rank, dev)
-        except Exception as e:  # noqa: BLE001 - the headline line must still be printed
-            big = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
-        timer.cancel()
-    emit(big)
+        big = second_metric_then_line(line, lambda: big_mode(args, world, rank, dev), rank,
+                                      float(os.environ.get("UBM_BENCH_BIG_LIMIT_S", "420")))
+    else:
+        second_metric_then_line(line, None, rank, 0.0)
     if world > 1:
         dist.destroy_process_group()
     return 0
