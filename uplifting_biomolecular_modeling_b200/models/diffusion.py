@@ -433,8 +433,12 @@ class AtomAttentionDecoder(AtomEncoderDecoderBase):
             aq = gemm.gemm(a.reshape(B * N, -1), _bf16_weight(self.a_to_q_trans)).view(B, N, -1)
             a2t32 = _segment_tables(q, atom_to_token, N)[4]
             q = rows.gather_rows_add(q, aq, a2t32)
-        else:
-            q = q + self.a_to_q_trans(a)[:, atom_to_token]
+            q = self.atom_transformer(q, c, biases, hoisted=hoisted, window=window)
+            # LayerNorm over the atom rows on the row kernel (the library's took 85 us for 63840 x 128), then the
+            # 128 -> 3 projection
+            ln, lin = self.atom_feat_to_atom_pos_update
+            return F.linear(rows.layernorm_rows(q.contiguous(), ln.weight, ln.bias, ln.eps), lin.weight)
+        q = q + self.a_to_q_trans(a)[:, atom_to_token]
         q = self.atom_transformer(q, c, biases, hoisted=hoisted, window=window)
         return self.atom_feat_to_atom_pos_update(q)
 
