@@ -23,6 +23,25 @@ native.declare("ubm_gather_rows_add", [c_void_p] * 4 + [c_int] * 4 + [c_void_p])
 _DT = {torch.bfloat16: 0, torch.float32: 1}
 
 
+_F32_CACHE: dict = {}
+
+
+def _f32_param(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """Contiguous fp32 copy of an affine parameter, kept until the parameter is written again (the conversion was two
+    small launches per LayerNorm call)."""
+    if t is None:
+        return None
+    if t.dtype == torch.float32 and t.is_contiguous():
+        return t.detach()
+    ent = _F32_CACHE.get(id(t))
+    if ent is None or ent[0] is not t or ent[1] != t._version or ent[2].device != t.device:
+        if len(_F32_CACHE) > 4096:
+            _F32_CACHE.clear()
+        ent = (t, t._version, t.detach().float().contiguous())
+        _F32_CACHE[id(t)] = ent
+    return ent[2]
+
+
 def layernorm_rows(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor],
                    eps: float = 1e-5, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     if x.dtype not in _DT or not x.is_contiguous():
@@ -31,8 +50,7 @@ def layernorm_rows(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Option
     R = x.numel() // C
     out_dtype = out_dtype or x.dtype
     out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
-    w = None if weight is None else weight.detach().float().contiguous()
-    b = None if bias is None else bias.detach().float().contiguous()
+    w, b = _f32_param(weight), _f32_param(bias)
     rc = native.lib().ubm_layernorm_rows(native.ptr(x), native.ptr(w), native.ptr(b), native.ptr(out), R, C,
                                          float(eps), _DT[x.dtype], _DT[out_dtype], native.current_stream(x.device))
     native.check(rc, "ubm_layernorm_rows")
