@@ -100,3 +100,11 @@ def test_layer_pipeline_over_two_gpus_matches_one():
         torch.cuda.synchronize(1)
         assert out.device.index == 1
         assert torch.allclose(out.cpu(), ref, atol=1e-5, rtol=1e-5), window
+
+
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_token_transformer_on_row_shards_over_nccl(tmp_path):
+    """The sampler's token transformer with the token rows split over two GPUs (one all-gather of the normalised rows
+    per layer) against the dense transformer."""
+    log = _run("tests/multigpu/dit_rows_check.py", [200, 3], 2, tmp_path)
+    assert "DIT-ROWS ok world=2 N=200 depth=3" in log, log[-2000:]
