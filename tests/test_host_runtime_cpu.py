@@ -86,6 +86,21 @@ def test_coldstart_forms(tmp_path):
         coldstart.load_total(m, part)
 
 
+def test_graph_pool_site_handle_counts_calls():
+    """The object a model calls (``run`` / ``stats`` / ``words``) is a site of the pool: counted in its census; on a
+    machine without CUDA every call runs eagerly."""
+    import torch
+    from uplifting_biomolecular_modeling_b200.capture import pool
+    gp = pool.GraphPool(budget_bytes=1 << 20, default_policy=pool.FixedK(2))
+    gp.site("stack", verify=1)
+    h = gp.handle("stack")
+    x = torch.ones(3)
+    for _ in range(3):
+        assert torch.equal(h.run(lambda t: t * 2, x), x * 2)
+    assert gp.census() == {"stack": {"calls": 3, "replays": 0}}
+    assert h.stats["eager"] == 3 and h.words()[0].startswith("graphs=")
+
+
 def test_capture_policies():
     from uplifting_biomolecular_modeling_b200.capture import pool
     assert pool.break_even_k(3.0, 0.5) == 6 and pool.break_even_k(1.0, 0.0) is None

@@ -150,6 +150,25 @@ def test_partial_checkpoint_is_not_active(tmp_path):
     assert man["checkpoint"]["matched"] == 1 and man["checkpoint"]["missing"]
 
 
+def test_full_checkpoint_loads_cold_and_reproduces_the_weights(tmp_path):
+    """With a checkpoint that carries every parameter the model is built without its random initialisation (the fillers
+    are skipped and counted) and the prediction equals the one of the model that wrote the checkpoint."""
+    import torch
+    from uplifting_biomolecular_modeling_b200.models import cofold
+    m = cofold.build_model("tiny", seed=5)
+    torch.save({"state_dict": m.state_dict()}, tmp_path / "full.ckpt")
+    base_args = ["kits/boltz2/run.sh", "pred", "--mode", "off", "--model_config", "tiny", "--tokens", "16",
+                 "--msa_depth", "2", "--seed", "5"]
+    a = _run(base_args + ["--out_dir", str(tmp_path / "a")])
+    b = _run(base_args + ["--checkpoint", str(tmp_path / "full.ckpt"), "--out_dir", str(tmp_path / "b")])
+    assert a.returncode == 0 and b.returncode == 0, b.stderr[-1500:]
+    word = [w for w in b.stderr.split() if w.startswith("init_skipped=")]
+    assert word and int(word[0].split("=")[1]) > 0
+    pa = torch.load(tmp_path / "a" / "prediction.pt", weights_only=True)
+    pb = torch.load(tmp_path / "b" / "prediction.pt", weights_only=True)
+    assert torch.equal(pa["coords"], pb["coords"])
+
+
 def test_design_verb_runs_the_design_pipeline(tmp_path):
     out = tmp_path / "d"
     r = _run(["kits/boltzgen/run.sh", "design", "--mode", "off", "--model_config", "tiny", "--tokens", "24",
@@ -175,6 +194,38 @@ def test_resident_loop_over_a_directory_of_inputs(tmp_path):
     assert "item=broken error=input" in r.stderr
     assert (out / "c0" / "prediction.pt").exists() and (out / "c1" / "prediction.pt").exists()   # ... the rest ran
     assert "RESIDENT items=2 failed=1" in r.stderr
+
+
+def test_resident_loop_featurises_equal_inputs_once(tmp_path):
+    """Two items with the same bytes under different names are featurised once (keyed by the file's digest) and both
+    predicted."""
+    inp = tmp_path / "in"
+    inp.mkdir()
+    spec = json.dumps({"tokens": 12, "msa_depth": 2})
+    (inp / "a.json").write_text(spec)
+    (inp / "b.json").write_text(spec)
+    (inp / "c.json").write_text(json.dumps({"tokens": 16, "msa_depth": 2}))
+    out = tmp_path / "o"
+    r = _run(["kits/boltz2/run.sh", "pred", "--mode", "off", "--model_config", "tiny", "--input", str(inp),
+              "--out_dir", str(out)])
+    assert r.returncode == 0, r.stderr[-1500:]
+    assert "features_built=2 features_reused=1" in r.stderr
+    for name in "abc":
+        assert (out / name / "prediction.pt").exists()
+
+
+def test_genomic_track_kit_writes_a_bedgraph(tmp_path):
+    """``predict`` of a genomic-track kit leaves the first predicted track as a bedGraph beside its JSON."""
+    out = tmp_path / "t"
+    r = _run(["kits/flashzoi/run.sh", "predict", "--mode", "off", "--out_dir", str(out)])
+    assert r.returncode == 0, r.stderr[-2000:]
+    res = json.load(open(out / "predict.json"))
+    lines = [ln for ln in (out / "track_0.bedGraph").read_text().splitlines() if not ln.startswith("track")]
+    assert 1 <= res["bedgraph_records"] == len(lines) <= res["bins"]          # equal neighbours are merged into one record
+    rows = [ln.split("\t") for ln in lines]
+    assert all(r[0] == "synthetic_window" for r in rows)
+    assert int(rows[0][1]) == 0 and all(int(a[2]) == int(b[1]) for a, b in zip(rows, rows[1:]))   # contiguous
+    assert int(rows[-1][2]) % res["bins"] == 0 and int(rows[-1][2]) > 0                            # bins x bin size
 
 
 def test_install_places_the_pth_hook_and_the_variable_activates_in_process(tmp_path):

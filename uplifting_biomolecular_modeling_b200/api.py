@@ -18,6 +18,7 @@ Mode vocabulary and the no-silent-fallback rule are those of the reference kits 
 from __future__ import annotations
 
 import os
+import sys
 import time
 from typing import Dict, Optional
 
@@ -96,10 +97,14 @@ class Predictor:
         if mode in ("fast", "big"):
             from .ops import dispatch
             dispatch.set_tier(mode)
+        self.graph_pool = None
         if self.use_graphs and self.device.type == "cuda":
-            from .capture import graphs
-            self.model.trunk_graphs = graphs.GraphCache(policy=graphs.FixedK(1), verify=self.verify_graphs,
-                                                        budget=graphs.GraphByteBudget(4 << 30))
+            # capture sites of this predictor under one byte budget and one census (capture.pool); the Pairformer
+            # stack is the first site: captured at the second sighting of a shape, first replay verified
+            from .capture import pool as _pool
+            self.graph_pool = _pool.GraphPool(budget_bytes=4 << 30, default_policy=_pool.FixedK(2))
+            self.graph_pool.site("pairformer_stack", verify=self.verify_graphs)
+            self.model.trunk_graphs = self.graph_pool.handle("pairformer_stack")
         self.sample_chunk = int(os.environ.get("UBM_BIG_SAMPLE_CHUNK", "0")) if mode == "big" else 0
         self.stage_peaks: Dict[str, Dict[str, int]] = {}
         self._graph = None
@@ -193,6 +198,23 @@ class Predictor:
         a2t = feats["atom_to_token"][0].clone()
         static_x = torch.zeros((samples, A, 3), device=self.device)
         static_s = torch.zeros(3, device=self.device)
+        # RNG discipline of the captured step (diffusion_loop.rng): the step draws from the device's default
+        # generator, which the graph registers, so replays advance it (contract ``registered``); a module left in
+        # training mode under another contract, or an undeclared contract, refuses the capture
+        from .diffusion_loop import rng as _rng
+        gate = _rng.capture_contract_gate(_rng.RNG_REGISTERED, [sm])
+        if not gate.ok:
+            raise NotActive(f"sampler graph refused: {gate.detail}")
+        if os.environ.get("UBM_GRAPH_AUDIT") == "1":
+            # opt-in audit before the capture (capture.audit): host synchronisations, allocator growth between warm
+            # runs; draws are allowed under the registered contract
+            from .capture import audit as _audit
+            rep = _audit.audit_capture_safety(
+                lambda: sm.step(static_x, static_s[0] + 1.0, static_s[1] + 0.5, static_s[2], prep, a2t, n_tokens),
+                allow_rng=True, check_determinism=False)
+            print(rep.line("sampler_step"), file=sys.stderr, flush=True)
+            if not rep.safe:
+                raise NotActive("sampler graph refused by the capture audit: " + "; ".join(rep.findings))
         side = torch.cuda.Stream(self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):

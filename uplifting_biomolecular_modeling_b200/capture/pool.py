@@ -126,6 +126,11 @@ class GraphPool:
         s.replays += s.cache.stats["replayed"] - before
         return out
 
+    def handle(self, name: str) -> "SiteHandle":
+        """The site as the object a model calls (``run(fn, *tensors)``, ``stats``, ``words()``): the interface of a
+        single :class:`capture.graphs.GraphCache`, counted in this pool's census and held to its byte budget."""
+        return SiteHandle(self, name)
+
     def new_item(self) -> None:
         self.items += 1
         for s in self.sites.values():
@@ -134,3 +139,18 @@ class GraphPool:
 
     def census(self) -> Dict[str, Dict[str, int]]:
         return {n: {"calls": s.calls, "replays": s.replays} for n, s in self.sites.items()}
+
+
+class SiteHandle:
+    def __init__(self, pool: GraphPool, name: str):
+        self.pool, self.name = pool, name
+
+    def run(self, fn, *tensors):
+        return self.pool.call(self.name, fn, *tensors)
+
+    @property
+    def stats(self) -> Dict[str, int]:
+        return self.pool.sites[self.name].cache.stats
+
+    def words(self):
+        return self.pool.sites[self.name].cache.words()

@@ -138,10 +138,13 @@ def _graph_verify(pred):
 def _trunk_graph(pred):
     """Pairformer stack passes of small inputs replay from a CUDA graph (capture once per shape, first replay
     verified against eager, byte budget on the static buffers)."""
-    from ..capture import graphs
-    pred.model.trunk_graphs = graphs.GraphCache(policy=graphs.FixedK(1), verify=1,
-                                                budget=graphs.GraphByteBudget(4 << 30))
-    return {"max_tokens": pred.model.trunk_graph_max_tokens}
+    from ..capture import pool
+    gp = getattr(pred, "graph_pool", None)
+    if gp is None:
+        gp = pred.graph_pool = pool.GraphPool(budget_bytes=4 << 30, default_policy=pool.FixedK(2))
+    gp.site("pairformer_stack", verify=1)
+    pred.model.trunk_graphs = gp.handle("pairformer_stack")
+    return {"max_tokens": pred.model.trunk_graph_max_tokens, "site": "pairformer_stack"}
 
 
 def _cond_dedup(pred):

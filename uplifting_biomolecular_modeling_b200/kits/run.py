@@ -102,10 +102,20 @@ def _run_cofold(spec, act, args, allow_partial) -> int:
         if getattr(args, "det", 0):
             from ..core import det
             det.apply_switches(det.Recipe(seed=args.seed))       # seeds, deterministic algorithms, no TF32
-        pred = api.Predictor(config, mode="off", device=device, dtype=dtype, seed=args.seed, **overrides)
+        ckpt = args.checkpoint or _weights_file(args.weights)
+        init_skipped = 0
+        if ckpt and not allow_partial:
+            # cold start (host.coldstart): a strict load overwrites every parameter, so the random initialisation is
+            # skipped while the model is built; a checkpoint that misses a parameter is refused below by name, so
+            # no unfilled tensor survives
+            from ..host import coldstart
+            with coldstart.no_init() as skipped:
+                pred = api.Predictor(config, mode="off", device=device, dtype=dtype, seed=args.seed, **overrides)
+            init_skipped = skipped.n
+        else:
+            pred = api.Predictor(config, mode="off", device=device, dtype=dtype, seed=args.seed, **overrides)
         pred.set_mode(act.mode)
         act.manifest_extra = {"numerics": pred.numerics, "det": int(getattr(args, "det", 0))}
-        ckpt = args.checkpoint or _weights_file(args.weights)
         if ckpt:
             from ..models import weights
             try:
@@ -119,7 +129,7 @@ def _run_cofold(spec, act, args, allow_partial) -> int:
                                                  "shape_mismatch": rep.shape_mismatch[:50]}
             report.emit(report.line(spec.tag, "WEIGHTS", ("path", ckpt), ("matched", rep.matched),
                                     ("missing", len(rep.missing)), ("unexpected", len(rep.unexpected)),
-                                    ("shape_mismatch", len(rep.shape_mismatch))))
+                                    ("shape_mismatch", len(rep.shape_mismatch)), ("init_skipped", init_skipped)))
         if getattr(args, "upstream_fix", None):
             from ..core import upstream_fix
             act.words = list(getattr(act, "words", [])) + upstream_fix.apply_all(
@@ -149,9 +159,18 @@ def _run_cofold(spec, act, args, allow_partial) -> int:
     multi = len(items) > 1
     done, errors = [], []
 
+    # items that name the same input bytes (a complex listed twice, or under two names) are featurised once: keyed by
+    # the file's sha256, never by its path or time stamp (host.memo)
+    from ..host import memo as _memo
+    feature_memo = _memo.Memo("features", max_items=8)
+
     def prepare(item):
         ns = type(args)(**dict(vars(args), input=item[1]))
-        return item, _load_features(ns, pred.cfg, config)
+        if item[1] is None or not os.path.isfile(item[1]):
+            return item, _load_features(ns, pred.cfg, config)          # synthetic, or the error path names the input
+        parts = {"file": _memo.file_digest(item[1]), "kind": os.path.splitext(item[1])[1], "config": config,
+                 "msa_depth": args.msa_depth, "seed": args.seed}
+        return item, dict(feature_memo.get_or_build(parts, lambda: _load_features(ns, pred.cfg, config)))
 
     def forward(prepared):
         item, feats = prepared
@@ -184,7 +203,9 @@ def _run_cofold(spec, act, args, allow_partial) -> int:
 
     stats = resident.run_resident(items, prepare, forward, write, workers=1, depth=2, on_error=on_error)
     if multi:
-        report.emit(report.line(spec.tag, "RESIDENT", *stats.words().items()))
+        report.emit(report.line(spec.tag, "RESIDENT", *stats.words().items(),
+                                ("features_built", feature_memo.stats["build"]),
+                                ("features_reused", feature_memo.stats["hit"])))
     if errors:
         bad_input = all(isinstance(e, InputError) for _, e in errors)
         return act.finish(report.EXIT_USAGE if bad_input else report.EXIT_FAIL, allow_partial, args.out_dir)
@@ -343,6 +364,14 @@ def _run_lm(spec, act, args, allow_partial, family) -> int:
                             *[(k, v) for k, v in res.items() if isinstance(v, (int, float, str))]))
     if args.out_dir:
         os.makedirs(args.out_dir, exist_ok=True)
+        tracks = getattr(model, "last_tracks", None)
+        if tracks is not None:
+            # genomic-track kits: the first predicted track of the window as a bedGraph, written on the writer
+            # thread (host.tracks); the window of a synthetic prompt is named for what it is
+            from ..host import tracks as _tracks
+            tw = _tracks.TrackWriter(args.out_dir, bin_size=int(model.last_bin_size), columns=(0,))
+            tw.submit("synthetic_window", 0, tracks)
+            res["bedgraph_records"] = tw.close()
         with open(os.path.join(args.out_dir, f"{args.verb}.json"), "w") as f:
             json.dump({k: (v if isinstance(v, (int, float, str, list)) else str(v)) for k, v in res.items()}, f)
     return act.finish(0, allow_partial, args.out_dir)

@@ -68,7 +68,11 @@ class _TrackRunner(_Runner):
             out = self.model(x)
         if cfg.family == "chrombpnet":
             prof, counts = out
+            # kept for the kit's track writer: base-pair profile of the window, one column
+            self.last_tracks, self.last_bin_size = prof[0].reshape(-1, 1), 1
             return {"score": float(counts[0]), "bins": int(prof.shape[1]), "tokens": need}
+        self.last_tracks = out[0]                                              # [bins, tracks]
+        self.last_bin_size = 2 ** (cfg.tower + 1)                              # base pairs per output bin
         return {"score": float(out.mean()), "bins": int(out.shape[1]), "tracks": int(out.shape[2]), "tokens": need}
 
 
