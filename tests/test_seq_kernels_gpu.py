@@ -135,6 +135,118 @@ def test_gemv_rows(M):
     _close(seq.gemv_rows(x, w, b), x.float() @ w.float().t() + b)
 
 
+@pytest.mark.parametrize("M,K", [(1, 4096), (2, 1024), (5, 11008)])
+def test_gemv_rows_folded_forms_return_the_bits_of_the_separate_kernels(M, K):
+    """SwiGLU over two weight matrices and the residual behind return the bits of the chain of separate kernels;
+    RMSNorm in front agrees to the last place of its scale."""
+    from uplifting_biomolecular_modeling_b200.ops import seq
+    g = torch.Generator(device="cuda").manual_seed(16)
+    N = 776
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * K ** -0.5).bfloat16()
+    w2 = (torch.randn(N, K, device="cuda", generator=g) * K ** -0.5).bfloat16()
+    gamma = 1 + 0.1 * torch.randn(K, device="cuda", generator=g)
+    res = torch.randn(M, N, device="cuda", generator=g).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g)
+    xn = seq.rmsnorm_rows(x, gamma, 1e-6)
+    # the sum of squares is taken in another order than the row kernel's: a last-place difference of the scale
+    _close(seq.gemv_rows(x, w, b, gamma=gamma, eps=1e-6), seq.gemv_rows(xn, w, b), 4e-3)
+    assert torch.equal(seq.gemv_rows(x, w, b, res=res), seq.gemv_rows(x, w, b) + res)
+    sep = seq.silu_mul(seq.gemv_rows(xn, w), seq.gemv_rows(xn, w2))
+    _close(seq.gemv_rows(x, w, gamma=gamma, eps=1e-6, w2=w2), sep, 4e-3)
+    assert torch.equal(seq.gemv_rows(xn, w, w2=w2), sep)
+    _close(seq.gemv_rows(x, w, b, gamma=gamma, res=res), xn.float() @ w.float().t() + b + res.float())
+
+
+@pytest.mark.parametrize("K", [3, 4])
+def test_fir_gate3_moves_the_tail_on_in_place(K):
+    from uplifting_biomolecular_modeling_b200.ops import seq
+    g = torch.Generator(device="cuda").manual_seed(17)
+    B, d = 2, 64
+    h = seq.taps_major(torch.randn(3 * d, K, device="cuda", generator=g) * 0.4)
+    tail = torch.randn(B, K - 1, 3 * d, device="cuda", generator=g).bfloat16()
+    for _ in range(3):
+        z = torch.randn(B, 1, 3 * d, device="cuda", generator=g).bfloat16()
+        u0, x0 = seq.fir_gate3(z, h, tail)
+        want = torch.cat([tail, z], 1)[:, 1:].contiguous()
+        u1, x1 = seq.fir_gate3(z, h, tail, push=True)
+        assert torch.equal(u0, u1) and torch.equal(x0, x1) and torch.equal(tail, want)
+
+
+@pytest.mark.parametrize("K,d", [(7, 64), (128, 4096), (40, 200)])
+def test_fir_step_equals_the_inner_stage_and_moves_the_tail_on(K, d):
+    from uplifting_biomolecular_modeling_b200.ops import reference as R, seq
+    g = torch.Generator(device="cuda").manual_seed(18)
+    B = 2
+    hraw = torch.randn(d, K, device="cuda", generator=g) * K ** -0.5
+    h = seq.taps_major(hraw)
+    D = torch.randn(d, device="cuda", generator=g)
+    tail = torch.randn(B, K - 1, d, device="cuda", generator=g).bfloat16()
+    for _ in range(3):
+        u = torch.randn(B, 1, d, device="cuda", generator=g).bfloat16()
+        x2 = torch.randn(B, 1, d, device="cuda", generator=g).bfloat16()
+        ref = R.fir_inner_gate(u, hraw, D, x2, tail)
+        want = torch.cat([tail, u], 1)[:, 1:].contiguous()
+        out = seq.fir_step(u, h, D, x2, tail)
+        _close(out, ref)
+        assert torch.equal(tail, want)
+
+
+@pytest.mark.parametrize("heads", [4, 1])          # head dimension 32 (plain attention step) and 128 (decode kernels)
+def test_evo2_graph_decode_on_the_folded_block_emits_the_tokens_of_the_separate_kernels(monkeypatch, heads):
+    from uplifting_biomolecular_modeling_b200.models import evo2
+    from uplifting_biomolecular_modeling_b200.ops import native
+    m = evo2.build("evo2_tiny", device="cuda", dtype=torch.bfloat16, seed=4, n_heads=heads)
+    m.set_impl("fused")
+    tok = torch.randint(0, m.cfg.vocab, (1, 64), device="cuda")
+    monkeypatch.setenv("UBM_EVO2_FOLDED_DECODE", "0")
+    want = m.generate(tok, 12, graph=True)
+    plain = m.generate(tok, 12, graph=False)
+    monkeypatch.setenv("UBM_EVO2_FOLDED_DECODE", "1")
+    got = m.generate(tok, 12, graph=True)
+    got_eager = m.generate(tok, 12, graph=False)
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "evo2 decode")
+    assert torch.equal(plain, want)
+    assert torch.equal(got, want) and torch.equal(got_eager, want)
+
+
+@pytest.mark.parametrize("B,H,Lmax,pos", [(1, 4, 300, 0), (2, 3, 5000, 4097), (1, 32, 2048, 2047)])
+def test_decode_attention_against_the_masked_softmax(B, H, Lmax, pos):
+    from uplifting_biomolecular_modeling_b200.models import evo2
+    from uplifting_biomolecular_modeling_b200.ops import native, seq
+    g = torch.Generator(device="cuda").manual_seed(19)
+    hd = 128
+    kc = torch.randn(B, Lmax, H, hd, device="cuda", generator=g).bfloat16()
+    vc = torch.randn(B, Lmax, H, hd, device="cuda", generator=g).bfloat16()
+    qkv = torch.randn(B, 3 * H * hd, device="cuda", generator=g).bfloat16()
+    p = torch.full((1,), pos, dtype=torch.long, device="cuda")
+    q, k, v = qkv.view(B, 1, 3, H, hd).unbind(2)
+    qr, kr = evo2.rope(q, p, 10000.0), evo2.rope(k, p, 10000.0)
+    kref, vref = kc.clone(), vc.clone()
+    kref[:, pos] = kr[:, 0]
+    vref[:, pos] = v[:, 0]
+    sc = torch.einsum("bqhd,bkhd->bhqk", qr.float(), kref[:, :pos + 1].float()) * hd ** -0.5
+    ref = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(sc, -1), vref[:, :pos + 1].float()).reshape(B, H * hd)
+    out = seq.decode_attention(qkv, p, kc, vc, 10000.0)
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "decode attention")
+    _close(out, ref)
+    _close(kc[:, pos], kref[:, pos], 1e-2)
+    assert torch.equal(vc, vref) and torch.equal(kc[:, :pos], kref[:, :pos]) and torch.equal(kc[:, pos + 1:], kref[:, pos + 1:])
+
+
+def test_decode_attention_reports_a_full_cache_in_the_status_word():
+    from uplifting_biomolecular_modeling_b200.ops import native, seq
+    kc = torch.zeros(1, 16, 2, 128, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    qkv = torch.ones(1, 3 * 2 * 128, device="cuda", dtype=torch.bfloat16)
+    seq.decode_attention(qkv, torch.full((1,), 16, dtype=torch.long, device="cuda"), kc, vc, 10000.0)
+    code, where, _, aux = native.read_status("cuda")
+    assert (code, where, aux) == (3, 120, 16)
+    assert not kc.any() and not vc.any()
+
+
 def test_per_channel_vectors_given_in_bf16():
     """Per-channel vectors that need a conversion are converted into tensors that outlive the launch."""
     from uplifting_biomolecular_modeling_b200.ops import reference as R, seq

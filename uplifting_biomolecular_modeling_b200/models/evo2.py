@@ -19,6 +19,7 @@ of the five attention layers is the library's fused attention; the package's own
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, replace
 from typing import Dict, List, Optional, Tuple
 
@@ -131,6 +132,7 @@ class HyenaOperator(nn.Module):
         self.out_proj = nn.Linear(d, d, bias=True)
         self.impl = "torch"
         self._taps = None           # tap-major fp32 copies of the filters for the kernels
+        self._lam_cache = None
 
     # ---- filters
     def filter_spectrum(self, L: int):
@@ -175,6 +177,14 @@ class HyenaOperator(nn.Module):
         else:
             y = fft_causal_conv(u, None, *self.filter_spectrum(u.shape[1]))
         return y + u * self.D.to(u.dtype)
+
+    def _lam(self) -> torch.Tensor:
+        """exp(log_poles) in fp32, kept until the parameter is written again (three launches per decode step)."""
+        ent = self._lam_cache
+        if ent is None or ent[0] != self.log_poles._version or ent[1].device != self.log_poles.device:
+            ent = (self.log_poles._version, torch.exp(self.log_poles.detach().float()).contiguous())
+            self._lam_cache = ent
+        return ent[1]
 
     def _kernel_taps(self):
         if self._taps is None:
@@ -225,17 +235,25 @@ class HyenaOperator(nn.Module):
         z = lin(self.in_proj, x)
         if _fusable(self, z) and self.cfg.fir_len <= 4:
             from ..ops import seq
-            u, x2 = seq.fir_gate3(z, self._kernel_taps()[0], state["fir_tail"])
-            _push(state, "fir_tail", z)
+            # a static state (fixed-address buffers that only this decode loop holds) is moved on inside the
+            # kernels; any other state may be shared with a snapshot and is replaced, not written
+            inplace = bool(state.get("static")) and z.shape[1] == 1 and _kernel_tail(state["fir_tail"])
+            u, x2 = seq.fir_gate3(z, self._kernel_taps()[0], state["fir_tail"], push=inplace)
+            if not inplace:
+                _push(state, "fir_tail", z)
             if self.kind in ("hcs", "hcm"):
-                gated = seq.fir_inner_gate(u, self._kernel_taps()[1], self.D, x2, state["inner_tail"])
-                _push(state, "inner_tail", u)
+                taps = self._kernel_taps()[1]
+                if inplace and 2 <= taps.shape[0] <= 256 and _kernel_tail(state["inner_tail"]):
+                    gated = seq.fir_step(u, taps, self.D, x2, state["inner_tail"])
+                else:
+                    gated = seq.fir_inner_gate(u, taps, self.D, x2, state["inner_tail"])
+                    _push(state, "inner_tail", u)
             else:
                 st = state["poles"]
                 if st.dtype != torch.float32 or not st.is_contiguous():
                     st = st.float().contiguous()
                     state["poles"] = st
-                gated = seq.pole_step(st, torch.exp(self.log_poles.float()), self.residues, u[:, 0], self.D,
+                gated = seq.pole_step(st, self._lam(), self.residues, u[:, 0], self.D,
                                       x2[:, 0]).unsqueeze(1)          # updates st in place
             return lin(self.out_proj, gated)
         zf = causal_fir(z, self.fir, state["fir_tail"])
@@ -295,6 +313,10 @@ class HyenaOperator(nn.Module):
                                         self.h.shape[1] - 1)
         else:
             state["poles"] = pend["poles"][j - 1]
+
+
+def _kernel_tail(t: torch.Tensor) -> bool:
+    return t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and t.shape[1] >= 1
 
 
 def _push(state: dict, key: str, new: torch.Tensor) -> None:
@@ -384,6 +406,14 @@ class AttentionOperator(nn.Module):
             # fixed-size cache, the position is a device tensor: no host value enters the step, so it can be
             # captured in a CUDA graph.  Keys past the position are masked.
             pos = state["pos"]                                              # int64 [1]
+            hd = self.cfg.d_model // self.cfg.n_heads
+            if _fusable(self, x) and x.shape[1] == 1 and hd == 128 and state["k"].dtype == torch.bfloat16 and \
+                    state["k"].is_contiguous() and state["v"].is_contiguous():
+                # rotary embedding, cache write and the masked attention as three launches of the kernel path
+                from ..ops import seq
+                o = seq.decode_attention(lin(self.qkv, x).view(B, -1), pos, state["k"], state["v"],
+                                         self.cfg.rope_base)
+                return lin(self.out_proj, o.view(B, 1, -1))
             q, k, v = self._qkv(x, pos, lin)
             state["k"].index_copy_(1, pos, k.to(state["k"].dtype))
             state["v"].index_copy_(1, pos, v.to(state["v"].dtype))
@@ -450,13 +480,43 @@ class Block(nn.Module):
         x = x + self.mixer(self.pre_norm(x), state, linear)
         return x + self.mlp(self.post_norm(x), linear)
 
-    def step(self, x, state, linear=None):
+    def step(self, x, state, linear=None, folded=None):
+        if folded is not None and _decode_rows(self, x):
+            return self._folded(x, state, self.mixer.step, folded)
         x = x + self.mixer.step(self.pre_norm(x), state, linear)
         return x + self.mlp(self.post_norm(x), linear)
 
-    def extend(self, x, state, linear=None):
+    def extend(self, x, state, linear=None, folded=None):
+        if folded is not None and _decode_rows(self, x):
+            return self._folded(x, state, self.mixer.extend, folded)
         x = x + self.mixer.extend(self.pre_norm(x), state, linear)
         return x + self.mlp(self.post_norm(x), linear)
+
+    def _folded(self, x, state, mixer_fn, folded):
+        """The block on at most 8 rows with four weight-streaming launches instead of eleven: both RMSNorms run in
+        front of the projection that reads them, both residual additions behind the projection that feeds them and
+        the two halves of SwiGLU in one pass over their weights.  ``folded(module, rows, gamma=, eps=, res=,
+        second=)`` is the model's hook for such a projection (:func:`folded_linear`, or the tensor-parallel form);
+        on one GPU every intermediate is rounded where the separate kernels round it, so the tokens are the same."""
+        B, L, d = x.shape
+        rows = x.reshape(B * L, d)
+        first = self.mixer.qkv if self.kind == "attn" else self.mixer.in_proj
+        last = self.mixer.out_proj
+
+        def lin(mod, t):
+            t2 = t.reshape(-1, t.shape[-1])
+            if mod is first:
+                y = folded(mod, t2, gamma=self.pre_norm.scale, eps=self.pre_norm.eps)
+            elif mod is last:
+                y = folded(mod, t2, res=rows)
+            else:
+                y = folded(mod, t2)
+            return y.view(*t.shape[:-1], y.shape[-1])
+
+        x1 = mixer_fn(x, state, lin)                                     # x + mixer(norm(x))
+        r1 = x1.reshape(B * L, d)
+        h = folded(self.mlp.l1, r1, gamma=self.post_norm.scale, eps=self.post_norm.eps, second=self.mlp.l2)
+        return folded(self.mlp.l3, h, res=r1).view(B, L, d)
 
 
 class StripedHyena2(nn.Module):
@@ -467,6 +527,7 @@ class StripedHyena2(nn.Module):
         self.blocks = nn.ModuleList([Block(cfg, cfg.layer_kind(i)) for i in range(cfg.n_layers)])
         self.norm = RMSNorm(cfg.d_model, cfg.eps)
         self.linear = None          # optional callable (module, x) -> y replacing nn.Linear calls (fused / TP GEMMs)
+        self.folded = None          # optional hook of the folded decode block (see Block._folded)
 
     def set_impl(self, impl: str) -> int:
         """``fused``: RMSNorm, the FIR / gate stages, the convolution epilogues, the decode state step and SwiGLU
@@ -478,6 +539,7 @@ class StripedHyena2(nn.Module):
                 m.impl = impl
                 n += 1
         self.linear = fused_linear if impl == "fused" else None
+        self.folded = folded_linear if impl == "fused" else None
         return n
 
     def logits(self, x):
@@ -495,7 +557,7 @@ class StripedHyena2(nn.Module):
     def step(self, token: torch.Tensor, states: List[dict]) -> torch.Tensor:
         x = self.embedding(token)
         for i, blk in enumerate(self.blocks):
-            x = blk.step(x, states[i], self.linear)
+            x = blk.step(x, states[i], self.linear, self.folded)
         return self.logits(x)
 
     @torch.no_grad()
@@ -504,7 +566,7 @@ class StripedHyena2(nn.Module):
         The states change only at :meth:`commit`."""
         x = self.embedding(tokens)
         for i, blk in enumerate(self.blocks):
-            x = blk.extend(x, states[i], self.linear)
+            x = blk.extend(x, states[i], self.linear, self.folded)
         return self.logits(x)
 
     def commit(self, states: List[dict], j: int) -> None:
@@ -647,18 +709,46 @@ BYTE_LUT = {c: i for i, c in enumerate("ACGTN")}
 _W_CACHE: dict = {}
 
 
-def fused_linear(module: nn.Linear, x: torch.Tensor) -> torch.Tensor:
-    """nn.Linear on the tcgen05 GEMM for bf16 GPU activations (weights cached as contiguous bf16); anything
-    else takes the module's own forward."""
-    if not (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0):
-        return module(x)
-    from ..ops import gemm
+def _bf16_weight(module: nn.Linear):
+    """(contiguous bf16 weight, fp32 bias or None) of a linear layer, kept until the weight is written again."""
     key = id(module)
     ent = _W_CACHE.get(key)
     if ent is None or ent[0] is not module.weight or ent[1] != module.weight._version:
         ent = (module.weight, module.weight._version, module.weight.detach().to(torch.bfloat16).contiguous(),
                None if module.bias is None else module.bias.detach().float().contiguous())
         _W_CACHE[key] = ent
+    return ent[2], ent[3]
+
+
+def _decode_rows(block: "Block", x: torch.Tensor) -> bool:
+    """At most 8 bf16 rows on the GPU with the kernel path on, and the widest projection input of the block
+    staged in one CTA's shared memory: the folded decode block serves them."""
+    if not (_fusable(block.pre_norm, x) and x.dim() == 3 and x.shape[0] * x.shape[1] <= 8):
+        return False
+    rows = x.shape[0] * x.shape[1]
+    mb = 1 if rows == 1 else 2 if rows <= 2 else 4 if rows <= 4 else 8
+    widest = max(x.shape[-1], block.mlp.l3.in_features)
+    return widest % 8 == 0 and mb * widest * 2 <= 200 * 1024 and os.environ.get("UBM_EVO2_FOLDED_DECODE", "1") != "0"
+
+
+def folded_linear(module: nn.Linear, rows: torch.Tensor, gamma=None, eps: float = 1e-6, res=None,
+                  second: Optional[nn.Linear] = None) -> torch.Tensor:
+    """A projection of the folded decode block on one GPU: rows [M <= 8, K] -> [M, N] on the weight-streaming
+    kernel with RMSNorm (``gamma``) in front, the residual (``res``) behind and, with ``second``, the SwiGLU of
+    two projections."""
+    from ..ops import seq
+    w, b = _bf16_weight(module)
+    w2 = None if second is None else _bf16_weight(second)[0]
+    return seq.gemv_rows(rows, w, b, gamma=gamma, eps=eps, w2=w2, res=res)
+
+
+def fused_linear(module: nn.Linear, x: torch.Tensor) -> torch.Tensor:
+    """nn.Linear on the tcgen05 GEMM for bf16 GPU activations (weights cached as contiguous bf16); anything
+    else takes the module's own forward."""
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0):
+        return module(x)
+    from ..ops import gemm
+    ent = (None, None) + _bf16_weight(module)
     x2 = x.reshape(-1, x.shape[-1])
     if not x2.is_contiguous():
         x2 = x2.contiguous()

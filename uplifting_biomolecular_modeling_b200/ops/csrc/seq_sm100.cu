@@ -161,9 +161,9 @@ constexpr int kFirTL = 32;   // positions per thread run
 template <int K>
 __global__ void __launch_bounds__(128) fir_gate3_kernel(const __nv_bfloat16* __restrict__ z,
                                                         const float* __restrict__ ht,     // [K][3d]
-                                                        const __nv_bfloat16* __restrict__ tail,  // [B][K-1][3d] or null
+                                                        __nv_bfloat16* tail,  // [B][K-1][3d] or null
                                                         __nv_bfloat16* __restrict__ u, __nv_bfloat16* __restrict__ x2,
-                                                        int B, int L, int d) {
+                                                        int B, int L, int d, int push) {
   const int c8 = d / 8;
   const int runs = (L + kFirTL - 1) / kFirTL;
   const long long total = static_cast<long long>(B) * runs * c8;
@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(128) fir_gate3_kernel(const __nv_bfloat16* __r
     const int run = static_cast<int>(br % runs);
     const int b = static_cast<int>(br / runs);
     const __nv_bfloat16* zb = z + static_cast<long long>(b) * L * C;
-    const __nv_bfloat16* tb = tail == nullptr ? nullptr : tail + static_cast<long long>(b) * (K - 1) * C;
+    __nv_bfloat16* tb = tail == nullptr ? nullptr : tail + static_cast<long long>(b) * (K - 1) * C;
     FirWindow<K> f1, f2, f3;
     f1.load_taps(ht, C, cc);
     f2.load_taps(ht, C, d + cc);
@@ -204,6 +204,100 @@ __global__ void __launch_bounds__(128) fir_gate3_kernel(const __nv_bfloat16* __r
       const long long o = (static_cast<long long>(b) * L + l) * d + cc;
       *reinterpret_cast<uint4*>(u + o) = pack8(uo);
       *reinterpret_cast<uint4*>(x2 + o) = pack8(xo);
+    }
+    // decode (one run per row of the batch): the tail is moved on in place - after the last step w[j] is the
+    // sample j + 1 positions behind the next one, i.e. row K - 2 - j of the new tail.  This thread is the only
+    // one that touches these channels of the tail.
+    if (push && K > 1) {
+#pragma unroll
+      for (int j = 0; j < K - 1; ++j) {
+        __nv_bfloat16* row = tb + static_cast<long long>(K - 2 - j) * C;
+        *reinterpret_cast<uint4*>(row + cc) = pack8(f1.w[j]);
+        *reinterpret_cast<uint4*>(row + d + cc) = pack8(f2.w[j]);
+        *reinterpret_cast<uint4*>(row + 2 * d + cc) = pack8(f3.w[j]);
+      }
+    }
+  }
+}
+
+// Inner operator of hcs / hcm for ONE new position per row of the batch (decode), with the tail moved on in
+// place: out = x2 * (sum_k h[k] s[-k] + D u), s[0] = u, s[-k] = tail[K - 1 - k]; then tail <- (tail[1:], u).
+// A CTA owns 64 channels (one 128-byte line of every row); 32 thread rows split the taps, partial sums meet in
+// shared memory; every tail row is read into registers before the barrier and written one row up after it.
+constexpr int kFirStepMaxTapsPerThread = 8;   // K <= 256
+
+__global__ void __launch_bounds__(256) fir_step_kernel(const __nv_bfloat16* __restrict__ u,     // [B][d]
+                                                       const float* __restrict__ ht, int K,     // [K][d]
+                                                       const float* __restrict__ D,
+                                                       const __nv_bfloat16* __restrict__ x2,    // [B][d] or null
+                                                       __nv_bfloat16* tail,                     // [B][K-1][d]
+                                                       __nv_bfloat16* __restrict__ out, int d) {
+  __shared__ float part[32][8][8];
+  const int cg = threadIdx.x & 7;
+  const int rg = threadIdx.x >> 3;
+  const int b = blockIdx.y;
+  const int cc = (blockIdx.x * 8 + cg) * 8;
+  const bool live = cc < d;
+  __nv_bfloat16* tb = tail + static_cast<long long>(b) * (K - 1) * d;
+  uint4 held[kFirStepMaxTapsPerThread];
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (live) {
+#pragma unroll
+    for (int t = 0; t < kFirStepMaxTapsPerThread; ++t) {
+      const int k = rg + 32 * t;
+      if (k < K)
+        held[t] = k == 0 ? *reinterpret_cast<const uint4*>(u + static_cast<long long>(b) * d + cc)
+                         : *reinterpret_cast<const uint4*>(tb + static_cast<long long>(K - 1 - k) * d + cc);
+    }
+#pragma unroll
+    for (int t = 0; t < kFirStepMaxTapsPerThread; ++t) {
+      const int k = rg + 32 * t;
+      if (k < K) {
+        float xv[8];
+        unpack8(held[t], xv);
+        const float4 h0 = __ldg(reinterpret_cast<const float4*>(ht + static_cast<long long>(k) * d + cc));
+        const float4 h1 = __ldg(reinterpret_cast<const float4*>(ht + static_cast<long long>(k) * d + cc + 4));
+        const float hv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(hv[e], xv[e], acc[e]);
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) part[rg][cg][e] = acc[e];
+  __syncthreads();                                       // every tail row of these channels is in registers
+  if (live) {
+#pragma unroll
+    for (int t = 0; t < kFirStepMaxTapsPerThread; ++t) {
+      const int k = rg + 32 * t;                         // the sample k behind becomes the sample k + 1 behind
+      if (k < K - 1) *reinterpret_cast<uint4*>(tb + static_cast<long long>(K - 2 - k) * d + cc) = held[t];
+    }
+    if (rg == 0) {
+      float cur[8], g[8];
+      unpack8(held[0], cur);
+      float sum[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sum[e] = 0.f;
+      for (int r = 0; r < 32; ++r)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum[e] += part[r][cg][e];
+      const long long o = static_cast<long long>(b) * d + cc;
+      if (x2 != nullptr) {
+        unpack8(*reinterpret_cast<const uint4*>(x2 + o), g);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) g[e] = 1.f;
+      }
+      const float4 d0 = __ldg(reinterpret_cast<const float4*>(D + cc));
+      const float4 d1 = __ldg(reinterpret_cast<const float4*>(D + cc + 4));
+      const float dv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+      float r8[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float conv = __bfloat162float(__float2bfloat16(sum[e]));
+        r8[e] = g[e] * __bfloat162float(__float2bfloat16(conv + cur[e] * dv[e]));
+      }
+      *reinterpret_cast<uint4*>(out + o) = pack8(r8);
     }
   }
 }
@@ -615,17 +709,20 @@ extern "C" int ubm_rmsnorm_rows(const void* x, const void* scale, void* out, lon
 }
 
 // z: bf16 [B][L][3d]; ht: fp32 [K][3d] (tap-major); tail: bf16 [B][K-1][3d] or null; u, x2: bf16 [B][L][d].
-extern "C" int ubm_fir_gate3(const void* z, const void* ht, const void* tail, void* u, void* x2, int B, int L, int d,
-                             int K, void* stream) {
+// push != 0 (decode: L <= 32, tail given): the tail is replaced in place by the last K - 1 samples
+extern "C" int ubm_fir_gate3(const void* z, const void* ht, void* tail, void* u, void* x2, int B, int L, int d,
+                             int K, int push, void* stream) {
   // three filter windows live in registers at once: up to four taps (the input stage of Hyena uses three)
   if (B <= 0 || L <= 0 || d <= 0 || (d & 7) || K < 1 || K > 4) return UBM_ERR_ARGUMENT;
+  if (push && (tail == nullptr || L > kFirTL)) return UBM_ERR_ARGUMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long total = static_cast<long long>(B) * ((L + kFirTL - 1) / kFirTL) * (d / 8);
   const int grid = seq_grid(total, 128);
 #define UBM_FG3(KK)                                                                                            \
   fir_gate3_kernel<KK><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(z), static_cast<const float*>(ht), \
-                                             static_cast<const __nv_bfloat16*>(tail),                           \
-                                             static_cast<__nv_bfloat16*>(u), static_cast<__nv_bfloat16*>(x2), B, L, d)
+                                             static_cast<__nv_bfloat16*>(tail),                                 \
+                                             static_cast<__nv_bfloat16*>(u), static_cast<__nv_bfloat16*>(x2), B, L, d, \
+                                             push)
   switch (K) {
     case 1: UBM_FG3(1); break;
     case 2: UBM_FG3(2); break;
@@ -668,6 +765,19 @@ extern "C" int ubm_fir_inner_gate(const void* u, const void* ht, const void* D, 
     fir_inner_gate_long_kernel<<<seq_grid(total, 128), 128, 0, st>>>(uu, hh, K, dd, xx, tt, oo, B, L, d);
   }
   UBM_CHECK_LAUNCH("fir_inner_gate_kernel");
+  return UBM_OK;
+}
+
+// u, x2, out: bf16 [B][d]; ht: fp32 [K][d]; tail: bf16 [B][K-1][d], moved on in place.  2 <= K <= 256.
+extern "C" int ubm_fir_step(const void* u, const void* ht, const void* D, const void* x2, void* tail, void* out, int B,
+                            int d, int K, void* stream) {
+  if (B <= 0 || B > 65535 || d <= 0 || (d & 7) || K < 2 || K > 32 * kFirStepMaxTapsPerThread || tail == nullptr)
+    return UBM_ERR_ARGUMENT;
+  const dim3 grid((d + 63) / 64, B);
+  fir_step_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(u), static_cast<const float*>(ht), K, static_cast<const float*>(D),
+      static_cast<const __nv_bfloat16*>(x2), static_cast<__nv_bfloat16*>(tail), static_cast<__nv_bfloat16*>(out), d);
+  UBM_CHECK_LAUNCH("fir_step_kernel");
   return UBM_OK;
 }
 
@@ -777,59 +887,208 @@ extern "C" int ubm_residual_ln(const void* x, const void* res, const void* gamma
 }
 
 // ------------------------------------------------------------------------------------------ decode GEMV
-// y[b][n] = sum_k W[n][k] x[b][k] (+ bias[n]) for a handful of rows b (single-token decode): the weight matrix is
-// streamed once at memory speed, one warp per output row n, 16-byte loads, fp32 accumulation; the activations
-// (at most 8 rows) are re-read from L1/L2.  A 128-row MMA tile would use one row of it and, with N / 256 tiles,
-// a fraction of the SMs.
+// y[b][n] = sum_k W[n][k] x^[b][k] (+ bias[n]) for a handful of rows b (single-token decode): the weight matrix is
+// streamed once at memory speed, one warp per output row n, eight independent 16-byte loads per lane in flight,
+// fp32 accumulation.  A 128-row MMA tile would use one row of it and, with N / 256 tiles, a fraction of the SMs.
+// The rows of a decode block are folded into the same launch:
+//   gamma != null : x^ = bf16(x * rsqrt(mean(x^2) + eps) * gamma)   (the block's RMSNorm; else x^ = x)
+//   w2 != null    : out = bf16(silu(g) * u), g = bf16(W x^), u = bf16(W2 x^)   (the two halves of SwiGLU)
+//   res != null   : out = bf16(res + bf16(y))                                   (the residual stream)
+// Every intermediate is rounded to bf16 where the separate kernels round it, so the folded form returns the
+// same bits.  x^ is staged once per CTA in shared memory ([MB][K] bf16).
 namespace ubm {
-template <int MB>
-__global__ void __launch_bounds__(256) gemv_rows_kernel(const __nv_bfloat16* __restrict__ x,
-                                                        const __nv_bfloat16* __restrict__ w,
-                                                        const float* __restrict__ bias,
-                                                        __nv_bfloat16* __restrict__ out, int M, int N, int K) {
+constexpr int kGemvThreads = 512;
+constexpr int kGemvMaxSmem = 200 * 1024;
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16(v)); }
+
+template <int MB, bool DUAL>
+__global__ void __launch_bounds__(kGemvThreads) gemv_rows_kernel(
+    const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, float eps,
+    const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ w2, const float* __restrict__ bias,
+    const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ out, int M, int N, int K) {
+  extern __shared__ __align__(16) unsigned char gemv_smem[];
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(gemv_smem);              // [MB][K]
+  __shared__ float red[MB][kGemvThreads / 32];
   const int lane = threadIdx.x & 31;
-  const int wpb = blockDim.x >> 5;
-  for (int n = blockIdx.x * wpb + (threadIdx.x >> 5); n < N; n += gridDim.x * wpb) {
-    float acc[MB];
+  const int warp = threadIdx.x >> 5;
+  const int wpb = kGemvThreads / 32;
+  const int nv = K >> 3;                                                       // 16-byte vectors per row
+  const int n_first = blockIdx.x * wpb + warp;
+  // the first weight row of this warp starts towards L2 while x^ is staged
+  if (n_first < N) {
+    const char* p0 = reinterpret_cast<const char*>(w + static_cast<long long>(n_first) * K);
+    for (int o = lane * 128; o < K * 2; o += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(p0 + o));
+    if (DUAL) {
+      const char* p1 = reinterpret_cast<const char*>(w2 + static_cast<long long>(n_first) * K);
+      for (int o = lane * 128; o < K * 2; o += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(p1 + o));
+    }
+  }
+  // ---- stage x^
+  if (gamma != nullptr) {
+    float ss[MB];
 #pragma unroll
-    for (int b = 0; b < MB; ++b) acc[b] = 0.f;
-    const __nv_bfloat16* wr = w + static_cast<long long>(n) * K;
-    for (int k = lane * 8; k < K; k += 256) {
-      float wv[8];
-      unpack8(__ldg(reinterpret_cast<const uint4*>(wr + k)), wv);
+    for (int b = 0; b < MB; ++b) ss[b] = 0.f;
+    for (int i = threadIdx.x; i < nv; i += kGemvThreads) {
 #pragma unroll
       for (int b = 0; b < MB; ++b) {
         if (b < M) {
-          float xv[8];
-          unpack8(*reinterpret_cast<const uint4*>(x + static_cast<long long>(b) * K + k), xv);
+          float v[8];
+          unpack8(reinterpret_cast<const uint4*>(x + static_cast<long long>(b) * K)[i], v);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[b] = fmaf(wv[e], xv[e], acc[b]);
+          for (int e = 0; e < 8; ++e) ss[b] += v[e] * v[e];
         }
       }
     }
 #pragma unroll
     for (int b = 0; b < MB; ++b) {
-      const float s = warp_sum(acc[b]);
-      if (lane == 0 && b < M) out[static_cast<long long>(b) * N + n] = __float2bfloat16(s + (bias ? bias[n] : 0.f));
+      const float t = warp_sum(ss[b]);
+      if (lane == 0) red[b][warp] = t;
+    }
+    __syncthreads();
+    float rs[MB];
+#pragma unroll
+    for (int b = 0; b < MB; ++b) {
+      float t = 0.f;
+#pragma unroll
+      for (int q = 0; q < wpb; ++q) t += red[b][q];
+      rs[b] = rsqrtf(t / K + eps);
+    }
+    for (int i = threadIdx.x; i < nv; i += kGemvThreads) {
+      const float4 s0 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * i);
+      const float4 s1 = __ldg(reinterpret_cast<const float4*>(gamma) + 2 * i + 1);
+      const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+      for (int b = 0; b < MB; ++b) {
+        if (b < M) {
+          float v[8], o[8];
+          unpack8(reinterpret_cast<const uint4*>(x + static_cast<long long>(b) * K)[i], v);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = v[e] * rs[b] * sc[e];
+          reinterpret_cast<uint4*>(xs + static_cast<long long>(b) * K)[i] = pack8(o);
+        }
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < nv; i += kGemvThreads) {
+#pragma unroll
+      for (int b = 0; b < MB; ++b)
+        if (b < M)
+          reinterpret_cast<uint4*>(xs + static_cast<long long>(b) * K)[i] =
+              reinterpret_cast<const uint4*>(x + static_cast<long long>(b) * K)[i];
+    }
+  }
+  __syncthreads();
+  // ---- stream the weights
+  for (int n = n_first; n < N; n += gridDim.x * wpb) {
+    float acc[MB], acc2[DUAL ? MB : 1];
+#pragma unroll
+    for (int b = 0; b < MB; ++b) acc[b] = 0.f;
+#pragma unroll
+    for (int b = 0; b < (DUAL ? MB : 1); ++b) acc2[b] = 0.f;
+    const uint4* wr = reinterpret_cast<const uint4*>(w + static_cast<long long>(n) * K);
+    const uint4* wr2 = DUAL ? reinterpret_cast<const uint4*>(w2 + static_cast<long long>(n) * K) : nullptr;
+    // loads in flight per lane: 8 (two matrices x 4, or one matrix x 8 when few rows leave the registers free)
+    constexpr int U = (DUAL || MB > 2) ? 4 : 8;
+    for (int i0 = lane; i0 < nv; i0 += 32 * U) {
+      uint4 wv[U], wv2[DUAL ? U : 1];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + 32 * u;
+        wv[u] = i < nv ? __ldcs(wr + i) : make_uint4(0u, 0u, 0u, 0u);
+        if (DUAL) wv2[u] = i < nv ? __ldcs(wr2 + i) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + 32 * u;
+        if (i < nv) {
+          float wf[8], wf2[8];
+          unpack8(wv[u], wf);
+          if (DUAL) unpack8(wv2[u], wf2);
+#pragma unroll
+          for (int b = 0; b < MB; ++b) {
+            if (b < M) {
+              float xv[8];
+              unpack8(reinterpret_cast<const uint4*>(xs + static_cast<long long>(b) * K)[i], xv);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                acc[b] = fmaf(wf[e], xv[e], acc[b]);
+                if (DUAL) acc2[b] = fmaf(wf2[e], xv[e], acc2[b]);
+              }
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < MB; ++b) {
+      float s = warp_sum(acc[b]);
+      float s2 = DUAL ? warp_sum(acc2[b]) : 0.f;
+      if (lane == 0 && b < M) {
+        const long long o = static_cast<long long>(b) * N + n;
+        if (bias != nullptr) s += bias[n];
+        if (DUAL) {
+          const float g = bf16_round(s), up = bf16_round(s2);
+          s = (g / (1.0f + __expf(-g))) * up;
+        }
+        if (res != nullptr) s = bf16_round(s) + __bfloat162float(res[o]);
+        out[o] = __float2bfloat16(s);
+      }
     }
   }
 }
-}  // namespace ubm
 
-// x: bf16 [M][K] (M <= 8), w: bf16 [N][K] (rows contiguous, K a multiple of 8), bias: fp32 [N] or null, out: bf16 [M][N]
-extern "C" int ubm_gemv_rows(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
-                             void* stream) {
-  if (M < 1 || M > 8 || N < 1 || K < 8 || (K & 7) || !aligned16(x) || !aligned16(w)) return UBM_ERR_ARGUMENT;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int grid = seq_grid(N, 8);
-  const __nv_bfloat16* xx = static_cast<const __nv_bfloat16*>(x);
-  const __nv_bfloat16* ww = static_cast<const __nv_bfloat16*>(w);
-  const float* bb = static_cast<const float*>(bias);
-  __nv_bfloat16* oo = static_cast<__nv_bfloat16*>(out);
-  if (M == 1) gemv_rows_kernel<1><<<grid, 256, 0, st>>>(xx, ww, bb, oo, M, N, K);
-  else if (M <= 2) gemv_rows_kernel<2><<<grid, 256, 0, st>>>(xx, ww, bb, oo, M, N, K);
-  else if (M <= 4) gemv_rows_kernel<4><<<grid, 256, 0, st>>>(xx, ww, bb, oo, M, N, K);
-  else gemv_rows_kernel<8><<<grid, 256, 0, st>>>(xx, ww, bb, oo, M, N, K);
+template <bool DUAL>
+int launch_gemv(const __nv_bfloat16* x, const float* gamma, float eps, const __nv_bfloat16* w, const __nv_bfloat16* w2,
+                const float* bias, const __nv_bfloat16* res, __nv_bfloat16* out, int M, int N, int K,
+                cudaStream_t st) {
+  const int MB = M == 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
+  const size_t smem = static_cast<size_t>(MB) * K * sizeof(__nv_bfloat16);
+  if (smem > static_cast<size_t>(kGemvMaxSmem)) return UBM_ERR_ARGUMENT;
+  const int wpb = kGemvThreads / 32;
+  const int per_sm = smem > 100 * 1024 ? 1 : 2;
+  int grid = (N + wpb - 1) / wpb;
+  if (grid > sm_count() * per_sm) grid = sm_count() * per_sm;
+#define UBM_GEMV(MBV)                                                                                          \
+  do {                                                                                                         \
+    auto kern = gemv_rows_kernel<MBV, DUAL>;                                                                   \
+    if (smem > 48 * 1024 &&                                                                                    \
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvMaxSmem) != cudaSuccess)  \
+      return UBM_ERR_LAUNCH;                                                                                   \
+    kern<<<grid, kGemvThreads, smem, st>>>(x, gamma, eps, w, w2, bias, res, out, M, N, K);                      \
+  } while (0)
+  switch (MB) {
+    case 1: UBM_GEMV(1); break;
+    case 2: UBM_GEMV(2); break;
+    case 4: UBM_GEMV(4); break;
+    default: UBM_GEMV(8); break;
+  }
+#undef UBM_GEMV
   UBM_CHECK_LAUNCH("gemv_rows_kernel");
   return UBM_OK;
+}
+}  // namespace ubm
+
+// x: bf16 [M][K] (M <= 8), w / w2: bf16 [N][K] (rows contiguous, K a multiple of 8; w2 null unless the SwiGLU form
+// is asked for), gamma: fp32 [K] or null, bias: fp32 [N] or null, res: bf16 [M][N] or null, out: bf16 [M][N]
+extern "C" int ubm_gemv_fused(const void* x, const void* gamma, float eps, const void* w, const void* w2,
+                              const void* bias, const void* res, void* out, int M, int N, int K, void* stream) {
+  if (M < 1 || M > 8 || N < 1 || K < 8 || (K & 7) || !aligned16(x) || !aligned16(w) ||
+      (w2 != nullptr && !aligned16(w2)) || (gamma != nullptr && !aligned16(gamma)))
+    return UBM_ERR_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xx = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* ww = static_cast<const __nv_bfloat16*>(w);
+  const __nv_bfloat16* w22 = static_cast<const __nv_bfloat16*>(w2);
+  const __nv_bfloat16* rr = static_cast<const __nv_bfloat16*>(res);
+  __nv_bfloat16* oo = static_cast<__nv_bfloat16*>(out);
+  const float* gg = static_cast<const float*>(gamma);
+  const float* bb = static_cast<const float*>(bias);
+  return w2 != nullptr ? ubm::launch_gemv<true>(xx, gg, eps, ww, w22, bb, rr, oo, M, N, K, st)
+                       : ubm::launch_gemv<false>(xx, gg, eps, ww, w22, bb, rr, oo, M, N, K, st);
+}
+
+extern "C" int ubm_gemv_rows(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
+                             void* stream) {
+  return ubm_gemv_fused(x, nullptr, 0.f, w, nullptr, bias, nullptr, out, M, N, K, stream);
 }

@@ -15,7 +15,8 @@ from . import native
 from .native import c_float, c_int, c_ll, c_void_p
 
 native.declare("ubm_rmsnorm_rows", [c_void_p] * 3 + [c_ll, c_int, c_float, c_void_p])
-native.declare("ubm_fir_gate3", [c_void_p] * 5 + [c_int] * 4 + [c_void_p])
+native.declare("ubm_fir_gate3", [c_void_p] * 5 + [c_int] * 5 + [c_void_p])
+native.declare("ubm_fir_step", [c_void_p] * 6 + [c_int] * 3 + [c_void_p])
 native.declare("ubm_fir_inner_gate", [c_void_p] * 6 + [c_int] * 4 + [c_void_p])
 native.declare("ubm_fftconv_epilogue", [c_void_p, c_int] + [c_void_p] * 4 + [c_int] * 3 + [c_void_p])
 native.declare("ubm_pole_step", [c_void_p] * 7 + [c_int] * 3 + [c_void_p])
@@ -25,7 +26,8 @@ native.declare("ubm_add2_softmax_rows", [c_void_p] * 4 + [c_ll, c_int, c_void_p]
 native.declare("ubm_pool2", [c_void_p] * 3 + [c_int] * 4 + [c_void_p])
 native.declare("ubm_residual_ln", [c_void_p] * 6 + [c_ll, c_int, c_float, c_void_p])
 
-native.declare("ubm_gemv_rows", [c_void_p] * 4 + [c_int] * 3 + [c_void_p])
+native.declare("ubm_gemv_fused", [c_void_p] * 2 + [c_float] + [c_void_p] * 5 + [c_int] * 3 + [c_void_p])
+native.declare("ubm_decode_attention", [c_void_p] * 7 + [c_int] * 4 + [c_float] * 2 + [c_void_p] * 2)
 native.declare("ubm_column_attention", [c_void_p] * 6 + [c_ll, c_int, c_int, c_int, c_float, c_void_p])
 native.declare("ubm_relshift_softmax", [c_void_p] * 3 + [c_ll, c_int, c_int, c_void_p])
 
@@ -38,8 +40,25 @@ def _bf16c(t: torch.Tensor) -> torch.Tensor:
     return t.contiguous()
 
 
+_F32_CACHE: dict = {}
+
+
 def _f32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
-    return None if t is None else t.detach().float().contiguous()
+    """Contiguous fp32 form of a per-channel vector.  Parameters (leaf tensors that outlive the call) are converted
+    once and kept until they are written again: a decode step reads dozens of them."""
+    if t is None:
+        return None
+    if t.dtype == torch.float32 and t.is_contiguous():
+        return t.detach()
+    if not isinstance(t, torch.nn.Parameter):
+        return t.detach().float().contiguous()
+    ent = _F32_CACHE.get(id(t))
+    if ent is None or ent[0] is not t or ent[1] != t._version or ent[2].device != t.device:
+        if len(_F32_CACHE) > 4096:
+            _F32_CACHE.clear()
+        ent = (t, t._version, t.detach().float().contiguous())
+        _F32_CACHE[id(t)] = ent
+    return ent[2]
 
 
 def _stream(t: torch.Tensor):
@@ -62,18 +81,39 @@ def taps_major(h: torch.Tensor) -> torch.Tensor:
     return h.detach().float().t().contiguous()
 
 
-def fir_gate3(z: torch.Tensor, ht: torch.Tensor, tail: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """z: [B, L, 3d]; ht: fp32 [K, 3d] from :func:`taps_major`; tail: [B, K-1, 3d].  Returns (u, x2), each [B, L, d]."""
+def fir_gate3(z: torch.Tensor, ht: torch.Tensor, tail: Optional[torch.Tensor] = None,
+              push: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """z: [B, L, 3d]; ht: fp32 [K, 3d] from :func:`taps_major`; tail: [B, K-1, 3d].  Returns (u, x2), each [B, L, d].
+    ``push`` (decode, L <= 32): ``tail`` (contiguous bf16) is replaced in place by the last K - 1 samples."""
     z = _bf16c(z)
     B, L, C = z.shape
     d = C // 3
     u = torch.empty((B, L, d), dtype=torch.bfloat16, device=z.device)
     x2 = torch.empty_like(u)
+    if push and (tail is None or tail.dtype != torch.bfloat16 or not tail.is_contiguous()):
+        raise ValueError("fir_gate3: push needs a contiguous bf16 tail")
     t = None if tail is None else _bf16c(tail)
     rc = native.lib().ubm_fir_gate3(native.ptr(z), native.ptr(ht), native.ptr(t), native.ptr(u), native.ptr(x2),
-                                    B, L, d, ht.shape[0], _stream(z))
+                                    B, L, d, ht.shape[0], 1 if push else 0, _stream(z))
     native.check(rc, "ubm_fir_gate3")
     return u, x2
+
+
+def fir_step(u: torch.Tensor, ht: torch.Tensor, D: torch.Tensor, x2: Optional[torch.Tensor],
+             tail: torch.Tensor) -> torch.Tensor:
+    """Decode form of :func:`fir_inner_gate` for one new position per batch row.  u, x2: [B, 1, d]; ht: fp32 [K, d]
+    (2 <= K <= 256); tail: contiguous bf16 [B, K-1, d], replaced in place by (tail[:, 1:], u)."""
+    u = _bf16c(u)
+    B, L, d = u.shape
+    if L != 1 or tail.dtype != torch.bfloat16 or not tail.is_contiguous() or tail.shape != (B, ht.shape[0] - 1, d):
+        raise ValueError("fir_step: one position per row and a contiguous bf16 tail [B, K-1, d]")
+    out = torch.empty_like(u)
+    x2c = None if x2 is None else _bf16c(x2)
+    Df = _f32(D)
+    rc = native.lib().ubm_fir_step(native.ptr(u), native.ptr(ht), native.ptr(Df), native.ptr(x2c), native.ptr(tail),
+                                   native.ptr(out), B, d, ht.shape[0], _stream(u))
+    native.check(rc, "ubm_fir_step")
+    return out
 
 
 def fir_inner_gate(u: torch.Tensor, ht: torch.Tensor, D: torch.Tensor, x2: Optional[torch.Tensor],
@@ -210,15 +250,52 @@ def residual_ln(x: torch.Tensor, res: torch.Tensor, gamma: torch.Tensor, beta: O
     return (out, s) if return_sum else out
 
 
-def gemv_rows(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x: bf16 [M, K] with M <= 8 (decode rows); w: bf16 [N, K] contiguous; returns bf16 [M, N] = x @ w.T (+ bias)."""
+def gemv_rows(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *,
+              gamma: Optional[torch.Tensor] = None, eps: float = 1e-6, w2: Optional[torch.Tensor] = None,
+              res: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x: bf16 [M, K] with M <= 8 (decode rows); w: bf16 [N, K] contiguous; returns bf16 [M, N] = x^ @ w.T (+ bias).
+
+    The rows of a decode block fold into the same launch: ``gamma`` (fp32 [K]) puts RMSNorm in front
+    (x^ = rmsnorm(x) * gamma, else x^ = x); ``w2`` makes the SwiGLU form silu(x^ @ w.T) * (x^ @ w2.T); ``res``
+    (bf16 [M, N]) is added behind.  Every intermediate is rounded to bf16 where the separate kernels round it."""
     x = _bf16c(x)
     M, K = x.shape
     N = w.shape[0]
     out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
-    rc = native.lib().ubm_gemv_rows(native.ptr(x), native.ptr(w), native.ptr(bias), native.ptr(out), M, N, K,
-                                    _stream(x))
-    native.check(rc, "ubm_gemv_rows")
+    if w2 is not None and (w2.shape != w.shape or not w2.is_contiguous()):
+        raise ValueError("gemv_rows: w2 must match w")
+    if res is not None:
+        res = _bf16c(res.reshape(M, N))
+    gamma = _f32(gamma)                  # a parameter in another type is converted once, not per decode step
+    rc = native.lib().ubm_gemv_fused(native.ptr(x), native.ptr(gamma), float(eps), native.ptr(w), native.ptr(w2),
+                                     native.ptr(bias), native.ptr(res), native.ptr(out), M, N, K, _stream(x))
+    native.check(rc, "ubm_gemv_fused")
+    return out
+
+
+def decode_attention(qkv: torch.Tensor, pos: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor,
+                     rope_base: float, scale: Optional[float] = None) -> torch.Tensor:
+    """One new token against a fixed-size cache (``csrc/decode_attn_sm100.cu``).  qkv: bf16 [B, 3 * H * 128]
+    (q | k | v); pos: int64 [1] on the device, the cache row the new key / value take (keys 0..pos are attended);
+    kc, vc: contiguous bf16 [B, Lmax, H, 128], written at row pos.  Rotary embedding (interleaved pairs) is applied
+    to q and k.  Returns bf16 [B, H * 128].  No host value enters: the call can be captured in a CUDA graph."""
+    qkv = _bf16c(qkv)
+    B, Lmax, H, hd = kc.shape
+    if hd != 128 or qkv.shape != (B, 3 * H * hd) or vc.shape != kc.shape or kc.dtype != torch.bfloat16 or \
+            vc.dtype != torch.bfloat16 or not kc.is_contiguous() or not vc.is_contiguous():
+        raise ValueError("decode_attention: bf16 caches [B, Lmax, H, 128] and qkv [B, 3*H*128]")
+    if pos.dtype != torch.int64 or pos.numel() != 1 or pos.device != qkv.device:
+        raise ValueError("decode_attention: pos is an int64 device tensor with one element")
+    splits = max(1, min(64, (Lmax + 1023) // 1024))
+    q_rot = torch.empty((B, H, hd), dtype=torch.bfloat16, device=qkv.device)
+    part = torch.empty((B, H, splits, hd + 2), dtype=torch.float32, device=qkv.device)
+    out = torch.empty((B, H * hd), dtype=torch.bfloat16, device=qkv.device)
+    sc = float(hd) ** -0.5 if scale is None else float(scale)
+    rc = native.lib().ubm_decode_attention(native.ptr(qkv), native.ptr(pos), native.ptr(kc), native.ptr(vc),
+                                           native.ptr(q_rot), native.ptr(part), native.ptr(out), B, H, Lmax, splits,
+                                           float(rope_base), sc, native.ptr(native.status_tensor(qkv.device)),
+                                           _stream(qkv))
+    native.check(rc, "ubm_decode_attention")
     return out
 
 

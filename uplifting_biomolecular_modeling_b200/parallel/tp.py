@@ -79,6 +79,7 @@ class TensorParallel:
             blk.mlp.l3._tp_row = True
         evo2._W_CACHE.clear()
         model.linear = self.linear
+        model.folded = self.folded_linear if getattr(model, "folded", None) is not None else None
 
     # ------------------------------------------------------------------ the Linear hook
     def _sum(self, t: torch.Tensor) -> torch.Tensor:
@@ -90,6 +91,22 @@ class TensorParallel:
             return t
         parts = self.comm.all_gather(t.unsqueeze(0))
         return torch.stack([p_[0] for p_ in parts], 0).sum(0)
+
+    def folded_linear(self, module: nn.Linear, rows: torch.Tensor, gamma=None, eps: float = 1e-6, res=None,
+                      second=None) -> torch.Tensor:
+        """The projection hook of the folded decode block (``models.evo2.Block._folded``) under tensor parallelism.
+        Column-parallel projections take the one-GPU form on this rank's slice (their input is replicated, so the
+        RMSNorm in front and the SwiGLU of two slices fold as they do there); a row-parallel projection streams
+        its slice, the partial rows are summed over the ranks and bias and residual are added once behind the sum."""
+        from ..models.evo2 import _bf16_weight, folded_linear
+        if not getattr(module, "_tp_row", False):
+            return folded_linear(module, rows, gamma=gamma, eps=eps, res=res, second=second)
+        from ..ops import seq
+        w, b = _bf16_weight(module)
+        y = self._sum(seq.gemv_rows(rows, w))
+        if b is not None:
+            return seq.elementwise("bias_residual", y, a=res, v0=b)
+        return y if res is None else seq.elementwise("add2", y, a=res)
 
     def linear(self, module: nn.Linear, x: torch.Tensor) -> torch.Tensor:
         """Replacement of ``module(x)`` under tensor parallelism (installed as the model's ``linear`` hook)."""
