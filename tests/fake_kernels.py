@@ -25,6 +25,10 @@ def gemm(a, b, *, mn_major=False, bias=None, residual=None, act=None, alpha=1.0,
         g3 = y.view(*y.shape[:-1], y.shape[-1] // 96, 3, 32)
         y = (F.silu(g3[..., 0, :]) * g3[..., 1, :] * g3[..., 2, :]).reshape(*y.shape[:-1], y.shape[-1] // 3)
         act = None
+    if act == "swiglu":
+        g2 = y.view(*y.shape[:-1], y.shape[-1] // 64, 2, 32)
+        y = (F.silu(g2[..., 0, :]) * g2[..., 1, :]).reshape(*y.shape[:-1], y.shape[-1] // 2)
+        act = None
     fn = {None: None, "none": None, "silu": F.silu, "sigmoid": torch.sigmoid, "gelu": F.gelu, "relu": F.relu}[act]
     if fn is not None:
         y = torch.cat([y[..., :act_from], fn(y[..., act_from:])], -1)

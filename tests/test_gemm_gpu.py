@@ -86,6 +86,25 @@ def test_gemm_swiglu3_epilogue(M, H, K):
     assert ((out.float() - ref).abs().mean() / ref.abs().mean()).item() < 8e-3
 
 
+@pytest.mark.parametrize("M,H,K", [(640, 256, 128), (1000, 96, 256), (4096, 11008, 512), (130, 32, 64)])
+def test_gemm_swiglu_epilogue(M, H, K):
+    """silu(x Wg^T) * (x Wv^T) formed on the accumulator of one 256-wide-tile product against the two separate fp32
+    products (H = 96 and 32 leave the last tile partly empty)."""
+    from uplifting_biomolecular_modeling_b200.ops import gemm, native
+    g = torch.Generator(device="cuda").manual_seed(7)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    wg, wv = ((torch.randn(H, K, device="cuda", generator=g) * K ** -0.5).bfloat16() for _ in range(2))
+    out = gemm.gemm(x, gemm.pack_swiglu(wg, wv), act="swiglu")
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "gemm")
+    assert out.shape == (M, H) and out.dtype == torch.bfloat16
+    xf = x.float()
+    ref = torch.nn.functional.silu(xf @ wg.float().T) * (xf @ wv.float().T)
+    err = (out.float() - ref).abs().max().item()
+    assert err <= 2e-2 * max(ref.abs().max().item(), 1.0), err
+    assert ((out.float() - ref).abs().mean() / ref.abs().mean()).item() < 8e-3
+
+
 @pytest.mark.parametrize("M,N,K", [(1000, 128, 128), (384, 96, 256), (257, 128, 64)])
 def test_gemm_residual_tiles_by_tma(M, N, K):
     """N <= 128 takes the 128-wide tile whose residual arrives through the shared-memory ring."""

@@ -108,3 +108,10 @@ def test_token_transformer_on_row_shards_over_nccl(tmp_path):
     per layer) against the dense transformer."""
     log = _run("tests/multigpu/dit_rows_check.py", [200, 3], 2, tmp_path)
     assert "DIT-ROWS ok world=2 N=200 depth=3" in log, log[-2000:]
+
+
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_evo2_tensor_parallel_prefill_and_folded_decode(tmp_path):
+    """StripedHyena-2 over two GPUs against one: prefill logits and decode steps through the folded decode block."""
+    log = _run("tests/multigpu/evo2_tp_check.py", [192, 4], 2, tmp_path)
+    assert "EVO2-TP ok world=2 tokens=192 steps=4" in log, log[-2000:]

@@ -247,6 +247,33 @@ def test_decode_attention_reports_a_full_cache_in_the_status_word():
     assert not kc.any() and not vc.any()
 
 
+@pytest.mark.parametrize("B,L,d,S", [(1, 3000, 256, 16), (2, 77, 40, 4), (1, 1024, 128, 8)])
+def test_pole_prefill_state_against_the_written_out_powers(B, L, d, S):
+    from uplifting_biomolecular_modeling_b200.ops import seq
+    g = torch.Generator(device="cuda").manual_seed(20)
+    u = torch.randn(B, L, d, device="cuda", generator=g).bfloat16()
+    lam = torch.rand(d, S, device="cuda", generator=g) * 0.5 + 0.45
+    w = lam.double().unsqueeze(0) ** torch.arange(L - 1, -1, -1, device="cuda", dtype=torch.float64).view(L, 1, 1)
+    ref = torch.einsum("bld,lds->bds", u.double(), w)
+    out = seq.pole_prefill_state(u, lam)
+    assert out.dtype == torch.float32 and out.shape == (B, d, S)
+    _close(out, ref, 1e-4)
+
+
+def test_fft_prologue_and_spectrum_product_equal_the_plain_statements():
+    from uplifting_biomolecular_modeling_b200.ops import seq
+    g = torch.Generator(device="cuda").manual_seed(21)
+    B, L, d, n = 2, 300, 72, 640
+    u = torch.randn(B, L, d, device="cuda", generator=g).bfloat16()
+    pad = seq.fft_pad_transpose(u, n)
+    assert torch.equal(pad[..., :L], u.float().transpose(1, 2)) and not pad[..., L:].any()
+    H = torch.fft.rfft(torch.randn(d, 100, device="cuda", generator=g), n=n)
+    X = torch.fft.rfft(pad)
+    want = X * H.unsqueeze(0)
+    got = seq.spectrum_mul_(X.clone(), H.contiguous())
+    assert (got - want).abs().max().item() <= 1e-5 * want.abs().max().item()
+
+
 def test_per_channel_vectors_given_in_bf16():
     """Per-channel vectors that need a conversion are converted into tensors that outlive the launch."""
     from uplifting_biomolecular_modeling_b200.ops import reference as R, seq

@@ -199,8 +199,8 @@ class HyenaOperator(nn.Module):
             if not (self.kind == "hcm" and u.shape[1] > 4 * self.h.shape[1] and tail is None):
                 return seq.fir_inner_gate(u, self._kernel_taps()[1], self.D, x2, tail)
         Hf, n = self.filter_spectrum(u.shape[1])
-        X = torch.fft.rfft(u.float().transpose(1, 2), n=n)
-        y = torch.fft.irfft(X * Hf.unsqueeze(0), n=n)                                     # [B, d, n] fp32
+        X = torch.fft.rfft(seq.fft_pad_transpose(u, n))          # channel-major fp32, zero-padded to the transform size
+        y = torch.fft.irfft(seq.spectrum_mul_(X, Hf.contiguous()), n=n)                   # [B, d, n] fp32
         return seq.fftconv_epilogue(y, u, self.D, x2)
 
     def forward(self, x: torch.Tensor, state: Optional[dict] = None, linear=None) -> torch.Tensor:
@@ -222,6 +222,9 @@ class HyenaOperator(nn.Module):
             state["fir_tail"] = _last(z, K - 1)
             if self.kind in ("hcs", "hcm"):
                 state["inner_tail"] = _last(u, self.h.shape[1] - 1)
+            elif fused and self.log_poles.shape[1] <= 16:
+                from ..ops import seq
+                state["poles"] = seq.pole_prefill_state(u, self._lam())           # sum_t lam^(L-1-t) u_t
             else:
                 lam = torch.exp(self.log_poles.float())                           # [d, S]
                 L = u.shape[1]
@@ -460,11 +463,28 @@ class SwiGLU(nn.Module):
 
     def forward(self, x, linear=None):
         lin = linear or (lambda m, t: m(t))
+        if _fusable(self, x) and linear is not None and x.numel() // x.shape[-1] > 8 and \
+                self.l1.out_features % 32 == 0 and self.l1.bias is None and self.l2.bias is None:
+            # both projections as one product whose epilogue forms silu(gate) * value on the accumulator (the
+            # interleaved weight is a second copy of the two matrices, kept until either is written again)
+            from ..ops import gemm
+            x2 = x.reshape(-1, x.shape[-1])
+            h = gemm.gemm(x2 if x2.is_contiguous() else x2.contiguous(), self._packed(), act="swiglu")
+            return lin(self.l3, h.view(*x.shape[:-1], h.shape[-1]))
         g, up = lin(self.l1, x), lin(self.l2, x)
         if _fusable(self, g):
             from ..ops import seq
             return lin(self.l3, seq.silu_mul(g, up))
         return lin(self.l3, F.silu(g) * up)
+
+    def _packed(self) -> torch.Tensor:
+        ver = tuple((p._version, p.data_ptr(), tuple(p.shape)) for p in (self.l1.weight, self.l2.weight))
+        ent = self.__dict__.get("_packed_w")
+        if ent is None or ent[0] != ver:
+            from ..ops import gemm
+            ent = (ver, gemm.pack_swiglu(self.l1.weight.detach(), self.l2.weight.detach()))
+            self.__dict__["_packed_w"] = ent
+        return ent[1]
 
 
 class Block(nn.Module):

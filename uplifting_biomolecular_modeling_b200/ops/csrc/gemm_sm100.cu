@@ -32,7 +32,8 @@ struct GemmParams {
   // 0 none, 1 silu, 2 sigmoid, 3 gelu (erf), 4 relu; 5 = three-way SwiGLU over column triples (192-wide tiles
   // only): the N columns come in groups of 96 = 32 gate | 32 value | 32 second value, and the output, N / 3 columns
   // wide, is silu(gate) * value * second value - the conditioned transition's swish gate and its a_to_b branch
-  // from one projection with no [M, N] intermediate
+  // from one projection with no [M, N] intermediate; 6 = two-way SwiGLU over column pairs (256-wide tiles): groups
+  // of 64 = 32 gate | 32 value, output N / 2 columns wide
   int act;
   int act_col0;  // the activation applies to output columns >= act_col0 (a multiple of 32; 0 = all columns)
   int res_tma;  // residual tiles arrive by TMA (tensor map in the auxiliary map slot 0)
@@ -676,6 +677,62 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           continue;
         }
       }
+      if constexpr (BN == 256) {
+        if (p.act == 6) {
+          // two-way SwiGLU: every 64 accumulator columns are gate | value of 32 output columns
+#pragma unroll 1
+          for (int c = c_begin; c + 2 <= c_end; c += 2) {
+            const uint32_t t0 = tmem_addr(tmem_base, q, acc * BN + c * 32);
+            tmem_ld32(t0, va);
+            tmem_ld32(t0 + 32, vb);
+            tmem_ld_wait();
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              f[j] = siluf_fast(__uint_as_float(va[j]) * p.alpha) * (__uint_as_float(vb[j]) * p.alpha);
+            const int o0 = (n_base + c * 32) / 2;
+            if (c_tma) {
+              if (lane == 0) tma_store_wait_read<0>();   // the previous box of this warp has left the staging rows
+              __syncwarp();
+              if (row_ok) {
+#pragma unroll
+                for (int j8 = 0; j8 < 4; ++j8) {
+                  uint4 u;
+                  u.x = pack_bf16x2(f[j8 * 8], f[j8 * 8 + 1]);
+                  u.y = pack_bf16x2(f[j8 * 8 + 2], f[j8 * 8 + 3]);
+                  u.z = pack_bf16x2(f[j8 * 8 + 4], f[j8 * 8 + 5]);
+                  u.w = pack_bf16x2(f[j8 * 8 + 6], f[j8 * 8 + 7]);
+                  *reinterpret_cast<uint4*>(stage_w + swz64_offset(lane, j8)) = u;
+                }
+              }
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_3d(tmC, stage_w, o0, mb * kBM + q * 32, b);
+                tma_store_commit();
+              }
+            } else if (row_ok) {
+              __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + b * p.strideC +
+                                  static_cast<long long>(m) * p.ldc + o0;
+              if ((reinterpret_cast<uintptr_t>(cp) & 31) == 0) {
+                st_bf16x16(cp, f);
+                st_bf16x16(cp + 16, f + 16);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) cp[j] = __float2bfloat16(f[j]);
+              }
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+          if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1u;
+          }
+          continue;
+        }
+      }
       if (c_begin < c_end) tmem_ld32(tmem_addr(tmem_base, q, acc * BN + c_begin * 32), va);
 #pragma unroll 1
       for (int c = c_begin; c < c_end; c += 2) {
@@ -783,8 +840,8 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
       const char* e = getenv("UBM_GEMM_TMA_STORE");
       return e == nullptr || e[0] != '0';
     }();
-    const bool swiglu = p.act == 5;
-    const long long n_out = swiglu ? p.N / 3 : p.N;
+    const bool swiglu = p.act == 5 || p.act == 6;
+    const long long n_out = p.act == 5 ? p.N / 3 : p.act == 6 ? p.N / 2 : p.N;
     if (c_tma_on && !p.out_fp32 && p.cblk_col == 0 && p.c_peer_rows == 0 && (p.ldc & 7) == 0 &&
         (p.batch == 1 || (p.strideC & 7) == 0) && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 &&
         (swiglu || BN != 192)) {
@@ -894,6 +951,15 @@ extern "C" int ubm_gemm_bf16_ex(const void* A, const void* B, void* C, const voi
       return UBM_ERR_ARGUMENT;
     }
     return launch_gemm<192, false>(A, B, p, lda, ldb, strideA, strideB, st);
+  }
+  if (act == 6) {
+    if (mn_major || out_fp32 || bias != nullptr || residual != nullptr || gate != nullptr || cblk_col != 0 ||
+        act_col0 != 0 || (N % 64) != 0) {
+      fprintf(stderr, "[ubm] gemm: the two-way SwiGLU epilogue takes a K-major bf16 product of 64-column groups "
+                      "with no bias, gate or residual\n");
+      return UBM_ERR_ARGUMENT;
+    }
+    return launch_gemm<256, false>(A, B, p, lda, ldb, strideA, strideB, st);
   }
   if (mn_major) {
     return wide ? launch_gemm<256, true>(A, B, p, lda, ldb, strideA, strideB, st)

@@ -13,7 +13,7 @@ import torch
 
 from . import native
 
-ACT = {None: 0, "none": 0, "silu": 1, "sigmoid": 2, "gelu": 3, "relu": 4, "swiglu3": 5}
+ACT = {None: 0, "none": 0, "silu": 1, "sigmoid": 2, "gelu": 3, "relu": 4, "swiglu3": 5, "swiglu": 6}
 
 
 def pack_swiglu3(gate_w: torch.Tensor, value_w: torch.Tensor, value2_w: torch.Tensor) -> torch.Tensor:
@@ -24,6 +24,16 @@ def pack_swiglu3(gate_w: torch.Tensor, value_w: torch.Tensor, value2_w: torch.Te
         raise ValueError("pack_swiglu3 expects three [H, K] weights with H a multiple of 32")
     w = torch.stack([gate_w.view(H // 32, 32, K), value_w.view(H // 32, 32, K), value2_w.view(H // 32, 32, K)], 1)
     return w.reshape(3 * H, K).to(torch.bfloat16).contiguous()
+
+
+def pack_swiglu(gate_w: torch.Tensor, value_w: torch.Tensor) -> torch.Tensor:
+    """Rows of two [H, K] projections interleaved in groups of 32 (gate | value) as the ``act="swiglu"`` epilogue
+    reads them; H a multiple of 32.  Returns bf16 [2 * H, K]."""
+    H, K = gate_w.shape
+    if H % 32 or value_w.shape != (H, K):
+        raise ValueError("pack_swiglu expects two [H, K] weights with H a multiple of 32")
+    w = torch.stack([gate_w.view(H // 32, 32, K), value_w.view(H // 32, 32, K)], 1)
+    return w.reshape(2 * H, K).to(torch.bfloat16).contiguous()
 
 
 def _as3(t: torch.Tensor) -> torch.Tensor:
@@ -38,7 +48,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, mn_major: bool = False, bias: Opti
 
     ``act_from``: the activation applies to output columns >= act_from (a multiple of 32) only.
     ``act="swiglu3"`` (b packed by ``pack_swiglu3``, N a multiple of 96, no bias / gate / residual): the result is
-    [.., M, N / 3] = silu(gate) * value * second value, computed in the epilogue on the accumulator.
+    [.., M, N / 3] = silu(gate) * value * second value, computed in the epilogue on the accumulator;
+    ``act="swiglu"`` (``pack_swiglu``, N a multiple of 64): [.., M, N / 2] = silu(gate) * value.
     ``gate`` (bf16 [rows, N], rows dividing M, row stride free): row m is multiplied by gate row m % rows -
     a conditioning gate shared by the samples stacked along M.
 
@@ -75,16 +86,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, mn_major: bool = False, bias: Opti
         out3 = out
     else:
         n_out = N
-        if act == "swiglu3":
-            if N % 96 or mn_major or bias is not None or gate is not None or residual is not None or act_from:
-                raise ValueError("swiglu3 needs a K-major product with N % 96 == 0 and no bias / gate / residual")
-            n_out = N // 3
+        if act in ("swiglu3", "swiglu"):
+            group = 96 if act == "swiglu3" else 64
+            if N % group or mn_major or bias is not None or gate is not None or residual is not None or act_from:
+                raise ValueError(f"{act} needs a K-major product with N % {group} == 0 and no bias / gate / residual")
+            n_out = N // 3 if act == "swiglu3" else N // 2
         if out is None:
-            out = torch.empty((batch, M, n_out), dtype=torch.bfloat16 if act == "swiglu3" else out_dtype,
-                              device=a.device)
+            out = torch.empty((batch, M, n_out), dtype=torch.bfloat16 if n_out != N else out_dtype, device=a.device)
         out3 = _as3(out)
-        if act == "swiglu3" and (out3.shape[-1] != n_out or out3.shape[-2] != M or out3.dtype != torch.bfloat16):
-            raise ValueError(f"swiglu3 output must be bf16 [.., {M}, {n_out}]")
+        if n_out != N and (out3.shape[-1] != n_out or out3.shape[-2] != M or out3.dtype != torch.bfloat16):
+            raise ValueError(f"{act} output must be bf16 [.., {M}, {n_out}]")
         if out3.stride(-1) != 1:
             raise ValueError("output innermost dimension must be contiguous")
     res3 = None

@@ -27,6 +27,9 @@ native.declare("ubm_pool2", [c_void_p] * 3 + [c_int] * 4 + [c_void_p])
 native.declare("ubm_residual_ln", [c_void_p] * 6 + [c_ll, c_int, c_float, c_void_p])
 
 native.declare("ubm_gemv_fused", [c_void_p] * 2 + [c_float] + [c_void_p] * 5 + [c_int] * 3 + [c_void_p])
+native.declare("ubm_pole_prefill_state", [c_void_p] * 4 + [c_int] * 5 + [c_void_p])
+native.declare("ubm_fft_pad_transpose", [c_void_p] * 2 + [c_int] * 4 + [c_void_p])
+native.declare("ubm_spectrum_mul", [c_void_p] * 2 + [c_int, c_ll, c_void_p])
 native.declare("ubm_decode_attention", [c_void_p] * 7 + [c_int] * 4 + [c_float] * 2 + [c_void_p] * 2)
 native.declare("ubm_column_attention", [c_void_p] * 6 + [c_ll, c_int, c_int, c_int, c_float, c_void_p])
 native.declare("ubm_relshift_softmax", [c_void_p] * 3 + [c_ll, c_int, c_int, c_void_p])
@@ -161,6 +164,42 @@ def pole_step(state: torch.Tensor, lam: torch.Tensor, res: torch.Tensor, u: torc
                                     native.ptr(Df), native.ptr(x2c), native.ptr(out), B, d, S, _stream(u))
     native.check(rc, "ubm_pole_step")
     return out
+
+
+def pole_prefill_state(u: torch.Tensor, lam: torch.Tensor) -> torch.Tensor:
+    """The pole state a prefill leaves for decoding: fp32 [B, d, S] with state[b, c, k] = sum_t lam[c, k]^(L-1-t)
+    u[b, t, c].  u: bf16 [B, L, d]; lam: [d, S], S <= 16."""
+    u = _bf16c(u)
+    B, L, d = u.shape
+    lamf = _f32(lam)
+    S = lamf.shape[1]
+    chunks = max(1, min(64, (L + 1023) // 1024))
+    part = torch.empty((B, chunks, d, S), dtype=torch.float32, device=u.device)
+    state = torch.empty((B, d, S), dtype=torch.float32, device=u.device)
+    rc = native.lib().ubm_pole_prefill_state(native.ptr(u), native.ptr(lamf), native.ptr(part), native.ptr(state),
+                                             B, L, d, S, chunks, _stream(u))
+    native.check(rc, "ubm_pole_prefill_state")
+    return state
+
+
+def fft_pad_transpose(u: torch.Tensor, n: int) -> torch.Tensor:
+    """u: bf16 [B, L, d] -> fp32 [B, d, n], zero from position L on (the input layout of the long convolution's FFT)."""
+    u = _bf16c(u)
+    B, L, d = u.shape
+    out = torch.empty((B, d, n), dtype=torch.float32, device=u.device)
+    rc = native.lib().ubm_fft_pad_transpose(native.ptr(u), native.ptr(out), B, L, d, n, _stream(u))
+    native.check(rc, "ubm_fft_pad_transpose")
+    return out
+
+
+def spectrum_mul_(X: torch.Tensor, H: torch.Tensor) -> torch.Tensor:
+    """X: complex64 [B, d, m], multiplied in place by H: complex64 [d, m]."""
+    if X.dtype != torch.complex64 or H.dtype != torch.complex64 or not X.is_contiguous() or not H.is_contiguous() \
+            or X.shape[1:] != H.shape:
+        raise ValueError("spectrum_mul_: contiguous complex64 [B, d, m] and [d, m]")
+    rc = native.lib().ubm_spectrum_mul(native.ptr(X), native.ptr(H), X.shape[0], H.numel(), _stream(X))
+    native.check(rc, "ubm_spectrum_mul")
+    return X
 
 
 def elementwise(op: str, x: torch.Tensor, a: Optional[torch.Tensor] = None, b: Optional[torch.Tensor] = None,
