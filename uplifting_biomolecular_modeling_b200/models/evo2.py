@@ -203,8 +203,10 @@ class HyenaOperator(nn.Module):
         y = torch.fft.irfft(seq.spectrum_mul_(X, Hf.contiguous()), n=n)                   # [B, d, n] fp32
         return seq.fftconv_epilogue(y, u, self.D, x2)
 
-    def forward(self, x: torch.Tensor, state: Optional[dict] = None, linear=None) -> torch.Tensor:
-        """Prefill form.  When ``state`` is a dict it is filled with what decoding needs."""
+    def forward(self, x: torch.Tensor, state: Optional[dict] = None, linear=None,
+                residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Prefill form.  When ``state`` is a dict it is filled with what decoding needs.  ``residual`` (only with a
+        ``linear`` hook that takes one) is added behind the output projection, in its epilogue."""
         lin = linear or (lambda m, t: m(t))
         z = lin(self.in_proj, x)
         fused = _fusable(self, z) and self.cfg.fir_len <= 4
@@ -230,7 +232,7 @@ class HyenaOperator(nn.Module):
                 L = u.shape[1]
                 w = lam.unsqueeze(0) ** torch.arange(L - 1, -1, -1, device=u.device, dtype=torch.float32).view(L, 1, 1)
                 state["poles"] = torch.einsum("bld,lds->bds", u.float(), w)       # sum_t lam^(L-1-t) u_t
-        return lin(self.out_proj, gated)
+        return lin(self.out_proj, gated) if residual is None else lin(self.out_proj, gated, residual)
 
     def step(self, x: torch.Tensor, state: dict, linear=None) -> torch.Tensor:
         """One token.  x: [B, 1, d]."""
@@ -389,10 +391,17 @@ class AttentionOperator(nn.Module):
         B, L, d = x.shape
         hd = self.cfg.d_model // self.cfg.n_heads
         qkv = lin(self.qkv, x)
-        q, k, v = qkv.view(B, L, 3, qkv.shape[-1] // (3 * hd), hd).unbind(2)
+        H = qkv.shape[-1] // (3 * hd)
+        if _fusable(self, qkv) and L > 8 and hd % 2 == 0:
+            # one pass over the projection: rotary embedding of q and k, the three tensors written apart
+            from ..ops import seq
+            q, k, v = seq.rotary_split_qkv(qkv.view(B * L, -1), pos.to(torch.int32).repeat(B), H, hd,
+                                           self.cfg.rope_base)
+            return q.view(B, L, H, hd), k.view(B, L, H, hd), v.view(B, L, H, hd)
+        q, k, v = qkv.view(B, L, 3, H, hd).unbind(2)
         return rope(q, pos, self.cfg.rope_base), rope(k, pos, self.cfg.rope_base), v
 
-    def forward(self, x, state: Optional[dict] = None, linear=None):
+    def forward(self, x, state: Optional[dict] = None, linear=None, residual=None):
         lin = linear or (lambda m, t: m(t))
         B, L, d = x.shape
         pos = torch.arange(L, device=x.device)
@@ -400,7 +409,8 @@ class AttentionOperator(nn.Module):
         o = self._causal(q, k, v)
         if state is not None:
             state["k"], state["v"] = k, v
-        return lin(self.out_proj, o.reshape(B, L, -1))
+        o = o.reshape(B, L, -1)
+        return lin(self.out_proj, o) if residual is None else lin(self.out_proj, o, residual)
 
     def step(self, x, state: dict, linear=None):
         lin = linear or (lambda m, t: m(t))
@@ -461,8 +471,11 @@ class SwiGLU(nn.Module):
         self.l3 = nn.Linear(ffn, d, bias=False)     # down
         self.impl = "torch"
 
-    def forward(self, x, linear=None):
+    def forward(self, x, linear=None, residual=None):
         lin = linear or (lambda m, t: m(t))
+        if residual is not None:
+            inner = lin
+            lin = lambda m, t: inner(m, t, residual) if m is self.l3 else inner(m, t)   # noqa: E731
         if _fusable(self, x) and linear is not None and x.numel() // x.shape[-1] > 8 and \
                 self.l1.out_features % 32 == 0 and self.l1.bias is None and self.l2.bias is None:
             # both projections as one product whose epilogue forms silu(gate) * value on the accumulator (the
@@ -497,6 +510,10 @@ class Block(nn.Module):
         self.mlp = SwiGLU(cfg.d_model, cfg.ffn)
 
     def forward(self, x, state=None, linear=None):
+        if linear is not None and getattr(linear, "takes_residual", False) and _fusable(self.pre_norm, x):
+            # the residual stream is added in the epilogue of the projection that closes each half of the block
+            x = self.mixer(self.pre_norm(x), state, linear, x)
+            return self.mlp(self.post_norm(x), linear, x)
         x = x + self.mixer(self.pre_norm(x), state, linear)
         return x + self.mlp(self.post_norm(x), linear)
 
@@ -762,20 +779,29 @@ def folded_linear(module: nn.Linear, rows: torch.Tensor, gamma=None, eps: float 
     return seq.gemv_rows(rows, w, b, gamma=gamma, eps=eps, w2=w2, res=res)
 
 
-def fused_linear(module: nn.Linear, x: torch.Tensor) -> torch.Tensor:
+def fused_linear(module: nn.Linear, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """nn.Linear on the tcgen05 GEMM for bf16 GPU activations (weights cached as contiguous bf16); anything
-    else takes the module's own forward."""
+    else takes the module's own forward.  ``residual`` (the shape of the result) is added in the epilogue."""
     if not (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0):
-        return module(x)
+        y = module(x)
+        return y if residual is None else y + residual
     from ..ops import gemm
-    ent = (None, None) + _bf16_weight(module)
+    w, b = _bf16_weight(module)
     x2 = x.reshape(-1, x.shape[-1])
     if not x2.is_contiguous():
         x2 = x2.contiguous()
+    r2 = None
+    if residual is not None:
+        r2 = residual.reshape(-1, w.shape[0])
+        if r2.dtype != torch.bfloat16 or not r2.is_contiguous():
+            r2 = r2.to(torch.bfloat16).contiguous()
     if x2.shape[0] <= 8:                      # decode rows: stream the weights once (memory bound)
         from ..ops import seq
-        return seq.gemv_rows(x2, ent[2], ent[3]).view(*x.shape[:-1], ent[2].shape[0])
-    return gemm.gemm(x2, ent[2], bias=ent[3]).view(*x.shape[:-1], ent[2].shape[0])
+        return seq.gemv_rows(x2, w, b, res=r2).view(*x.shape[:-1], w.shape[0])
+    return gemm.gemm(x2, w, bias=b, residual=r2).view(*x.shape[:-1], w.shape[0])
+
+
+fused_linear.takes_residual = True
 
 
 def tokenize(seq: str, device="cpu") -> torch.Tensor:

@@ -108,8 +108,18 @@ class TensorParallel:
             return seq.elementwise("bias_residual", y, a=res, v0=b)
         return y if res is None else seq.elementwise("add2", y, a=res)
 
-    def linear(self, module: nn.Linear, x: torch.Tensor) -> torch.Tensor:
-        """Replacement of ``module(x)`` under tensor parallelism (installed as the model's ``linear`` hook)."""
+    def linear(self, module: nn.Linear, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Replacement of ``module(x)`` under tensor parallelism (installed as the model's ``linear`` hook).
+        ``residual`` (replicated, the shape of the result) is added once, behind the sum over the ranks."""
+        y = self._linear(module, x)
+        if residual is None:
+            return y
+        if y.is_cuda and y.dtype == torch.bfloat16 and residual.dtype == torch.bfloat16 and y.shape[-1] % 8 == 0:
+            from ..ops import seq
+            return seq.elementwise("add2", y.contiguous(), a=residual.contiguous().view(y.shape))
+        return y + residual
+
+    def _linear(self, module: nn.Linear, x: torch.Tensor) -> torch.Tensor:
         from ..models.evo2 import fused_linear
         if not getattr(module, "_tp_row", False):
             return fused_linear(module, x)                       # column-parallel: this rank's output slice
@@ -149,3 +159,6 @@ class TensorParallel:
         if module.bias is not None:
             y = y + module.bias.to(y.dtype)
         return y.view(*x.shape[:-1], N)
+
+
+TensorParallel.linear.takes_residual = True
