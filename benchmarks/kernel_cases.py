@@ -6,7 +6,7 @@ Cases: ``attention`` (triangle-attention core, H=4 x D=32, rows = N), ``attentio
 16 heads x 64, 5 samples), ``trimul_proj``, ``trimul_gemm``, ``trimul_out``, ``triatt_proj``, ``transition``,
 ``out_gemm`` (the [N*N,128] x [128,128] output projection with residual), ``trimul`` (three launches),
 ``triatt`` (three launches), ``causal_attention`` (--n tokens, --heads, head dimension 128; --lib 1 = the
-library call), ``gemm_rows`` (--m --k --nn: a row GEMM with bias), ``window_attention`` (--m atoms,
+library call), ``gemm_rows`` (--m --k --nn: a row GEMM with bias), ``gemv_rows`` (--m <= 8 rows, --k, --nn, --form), ``window_attention`` (--m atoms,
 5 samples, 4 heads x 32).  Inputs are larger than L2 for N >= 768.  Prints one line per case with the
 mean time, the algorithmic bytes and FLOPs, and the fractions of the measured peaks in MEASURED_PEAKS.json
 (fallback 6.65 TB/s, 1.59 PFLOP/s when the file is absent).
@@ -63,6 +63,7 @@ def main():
     ap.add_argument("--heads", type=int, default=32, help="causal_attention: heads")
     ap.add_argument("--lib", type=int, default=0, help="causal_attention: 1 = time the library attention instead")
     ap.add_argument("--masked", type=int, default=0, help="attention: 1 = key mask with a padded tail of a tenth of the keys")
+    ap.add_argument("--form", default="plain", help="gemv_rows: plain | norm (RMSNorm in front) | res (residual behind) | swiglu (RMSNorm + two matrices)")
     ap.add_argument("--incoming", type=int, default=0, help="trimul / trimul_gemm: 1 = the incoming update (MN-major contraction)")
     a = ap.parse_args()
     N, c = a.n, 128
@@ -71,7 +72,7 @@ def main():
     torch.manual_seed(0)
     r = lambda *s: torch.randn(*s, device=dev) * 0.08  # noqa: E731
     ones, zeros = torch.ones(c, device=dev), torch.zeros(c, device=dev)
-    z = torch.randn(N, N, c, device=dev).bfloat16() if a.case not in ("causal_attention", "gemm_rows") else None
+    z = torch.randn(N, N, c, device=dev).bfloat16() if a.case not in ("causal_attention", "gemm_rows", "gemv_rows") else None
     Np = pair.ceil_to(N, 8)
     st = native.status_tensor(dev)
     stream = native.current_stream(dev)
@@ -160,6 +161,17 @@ def main():
         out = torch.empty((M, NN), dtype=torch.bfloat16, device=dev)
         fn = lambda: gemm.gemm(x, wt, bias=bvec, out=out)  # noqa: E731
         byts, flops = (x.numel() + wt.numel() + out.numel()) * 2, 2.0 * M * K * NN
+    elif a.case == "gemv_rows":
+        # decode projection: --m rows (<= 8) x [nn, k] weights streamed once; --form plain | norm | res | swiglu
+        from uplifting_biomolecular_modeling_b200.ops import seq
+        M, K, NN = a.m, a.k, a.nn
+        x = torch.randn(M, K, device=dev).bfloat16()
+        wt, w2 = r(NN, K).bfloat16(), r(NN, K).bfloat16()
+        gamma = torch.ones(K, device=dev)
+        res = torch.randn(M, NN, device=dev).bfloat16()
+        kw = {"plain": {}, "norm": {"gamma": gamma}, "res": {"res": res}, "swiglu": {"gamma": gamma, "w2": w2}}[a.form]
+        fn = lambda: seq.gemv_rows(x, wt, **kw)  # noqa: E731
+        byts, flops = wt.numel() * 2 * (2 if a.form == "swiglu" else 1), 2.0 * M * K * NN
     elif a.case == "causal_attention":
         # causal self-attention at head dimension 128: --n tokens, --heads heads, batch 1; --lib 1 times the library call
         import torch.nn.functional as F
