@@ -117,9 +117,11 @@ def _run_cofold(spec, act, args, allow_partial) -> int:
         pred.set_mode(act.mode)
         act.manifest_extra = {"numerics": pred.numerics, "det": int(getattr(args, "det", 0))}
         if ckpt:
-            from ..models import weights
+            from ..models import mappers, weights
             try:
-                rep = weights.load_checkpoint(pred.model, ckpt, strict=not allow_partial)
+                # kits of another upstream translate its parameter names first (models/mappers.py)
+                rep = weights.load_checkpoint(pred.model, ckpt, strict=not allow_partial,
+                                              mapper=mappers.for_kit(spec.name))
             except (ValueError, OSError) as e:
                 act.refuse(f"checkpoint {ckpt}: {e}")
                 return report.EXIT_NOT_ACTIVE

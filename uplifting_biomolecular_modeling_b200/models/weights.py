@@ -97,11 +97,14 @@ class LoadReport:
 
 
 def load_checkpoint(model: torch.nn.Module, path: str, expected_sha256: Optional[str] = None,
-                    strict: bool = True, ema: Optional[bool] = None) -> LoadReport:
-    """Load by name after prefix stripping.  ``strict`` (the default): every parameter of the model must be in the
+                    strict: bool = True, ema: Optional[bool] = None, mapper=None) -> LoadReport:
+    """Load by name after prefix stripping (and after ``mapper``, a function state -> state that translates an
+    upstream's parameter names into this package's: :mod:`models.mappers`).  ``strict`` (the default): every parameter of the model must be in the
     checkpoint with its shape and the checkpoint may hold nothing else, otherwise ``ValueError`` - a run on partly
     random weights is never silent.  ``strict=False`` loads what matches and reports the rest."""
     state = strip_prefixes(read_state(path, expected_sha256), ema=ema)
+    if mapper is not None:
+        state = mapper(state)
     own = model.state_dict()
     rep = LoadReport()
     matched = {}

@@ -182,6 +182,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(const __nv_bfl
 __global__ void __launch_bounds__(kDecHd) decode_merge_kernel(const float* __restrict__ part,
                                                               __nv_bfloat16* __restrict__ out, int H, int S) {
   const int h = blockIdx.x, b = blockIdx.y;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the projection behind may prefetch its weights
   const float* rec = part + (static_cast<long long>(b) * H + h) * S * kDecRec;
   float M = -INFINITY;
   for (int s = 0; s < S; ++s) M = fmaxf(M, rec[s * kDecRec + kDecHd]);

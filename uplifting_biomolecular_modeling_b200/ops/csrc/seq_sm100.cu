@@ -241,6 +241,7 @@ __global__ void __launch_bounds__(256) fir_step_kernel(const __nv_bfloat16* __re
                                                        __nv_bfloat16* tail,                     // [B][K-1][d]
                                                        __nv_bfloat16* __restrict__ out, int d) {
   __shared__ float part[32][8][8];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the projection behind may prefetch its weights
   const int cg = threadIdx.x & 7;
   const int rg = threadIdx.x >> 3;
   const int b = blockIdx.y;
@@ -468,6 +469,7 @@ __global__ void __launch_bounds__(256) pole_step_kernel(float* __restrict__ stat
                                                         const __nv_bfloat16* __restrict__ x2,
                                                         __nv_bfloat16* __restrict__ out, int B, int d, int S) {
   const long long total = static_cast<long long>(B) * d;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the projection behind may prefetch its weights
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int c = static_cast<int>(i % d);
@@ -1067,6 +1069,12 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_rows_kernel(
       for (int o = lane * 128; o < K * 2; o += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(p1 + o));
     }
   }
+  // Programmatic dependent launch: the prefetch above read only weights, so this CTA may have started while the
+  // previous kernel of the stream drains; x, the residual and the output are touched from here on.  The kernel
+  // behind this one may start its own prefetch as soon as every CTA here has passed this point.  Both
+  // instructions are no-ops for a launch without the attribute.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // ---- stage x^
   if (gamma != nullptr) {
     float ss[MB];
@@ -1192,13 +1200,29 @@ int launch_gemv(const __nv_bfloat16* x, const float* gamma, float eps, const __n
   const int per_sm = smem > 100 * 1024 ? 1 : 2;
   int grid = (N + wpb - 1) / wpb;
   if (grid > sm_count() * per_sm) grid = sm_count() * per_sm;
+  // launched so that its weight prefetch may overlap the tail of the previous kernel in the stream (see the kernel)
+  static const bool pdl = [] {
+    const char* e = getenv("UBM_PDL");
+    return e == nullptr || e[0] != '0';
+  }();
 #define UBM_GEMV(MBV)                                                                                          \
   do {                                                                                                         \
     auto kern = gemv_rows_kernel<MBV, DUAL>;                                                                   \
     if (smem > 48 * 1024 &&                                                                                    \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvMaxSmem) != cudaSuccess)  \
       return UBM_ERR_LAUNCH;                                                                                   \
-    kern<<<grid, kGemvThreads, smem, st>>>(x, gamma, eps, w, w2, bias, res, out, M, N, K);                      \
+    cudaLaunchConfig_t cfg = {};                                                                               \
+    cfg.gridDim = dim3(grid);                                                                                  \
+    cfg.blockDim = dim3(kGemvThreads);                                                                         \
+    cfg.dynamicSmemBytes = smem;                                                                               \
+    cfg.stream = st;                                                                                           \
+    cudaLaunchAttribute attr[1];                                                                               \
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                           \
+    attr[0].val.programmaticStreamSerializationAllowed = 1;                                                    \
+    cfg.attrs = attr;                                                                                          \
+    cfg.numAttrs = pdl ? 1 : 0;                                                                                \
+    if (cudaLaunchKernelEx(&cfg, kern, x, gamma, eps, w, w2, bias, res, out, M, N, K) != cudaSuccess)          \
+      return UBM_ERR_LAUNCH;                                                                                   \
   } while (0)
   switch (MB) {
     case 1: UBM_GEMV(1); break;
