@@ -102,3 +102,24 @@ def test_track_model_fused_vs_reference(name):
         _close(got[1], want[1], 4e-2)
     else:
         _close(got, want, 4e-2)
+
+
+@pytest.mark.parametrize("family,kit", [("evo2", "evo2"), ("protein_lm", "esmc")])
+def test_forward_graph_lever_replays_the_score_of_a_recurring_shape(family, kit):
+    """Second sighting of a shape is captured, the third call replays; every call returns the eager score."""
+    from uplifting_biomolecular_modeling_b200.kits import levers
+    from uplifting_biomolecular_modeling_b200.models import lm
+    from uplifting_biomolecular_modeling_b200.ops import native
+    r = lm.build(family, "lm", device="cuda", kit=kit)
+    if hasattr(r.model, "set_impl"):
+        r.model.set_impl("fused")
+    want = r.run("score", "ACGTMKV" * 9)["score"]
+    ev = levers.LEVERS["forward_graph"].apply(r)
+    assert ev["site"] == "score_forward"
+    got = [r.run("score", "ACGTMKV" * 9)["score"] for _ in range(4)]
+    other = r.run("score", "ACGT" * 5)["score"]                       # another shape: its own entry, eager first
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "forward graph")
+    assert all(abs(g - want) <= 1e-3 * max(1.0, abs(want)) for g in got), (want, got)
+    assert r.graph_pool.census()["score_forward"]["replays"] >= 2
+    assert other == other                                             # a number, not NaN

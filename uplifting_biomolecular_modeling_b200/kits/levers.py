@@ -171,6 +171,18 @@ def _decode_graph(pred):
     return {"decode_graph": True}
 
 
+def _forward_graph(pred):
+    """Scoring: the forward of a recurring input shape (at most ``forward_graph_max_tokens`` tokens) is captured at
+    its second sighting and replayed afterwards; the first replay is compared with the eager result."""
+    from ..capture import pool
+    gp = getattr(pred, "graph_pool", None)
+    if gp is None:
+        gp = pred.graph_pool = pool.GraphPool(budget_bytes=8 << 30, default_policy=pool.FixedK(2))
+    gp.site("score_forward", verify=1)
+    pred.forward_graphs = gp.handle("score_forward")
+    return {"max_tokens": pred.forward_graph_max_tokens, "site": "score_forward"}
+
+
 def _tp_fused(pred):
     """Tensor parallelism of the sequence models with the collectives fused into the GEMM kernels."""
     import torch
@@ -205,5 +217,6 @@ LEVERS: Dict[str, Lever] = {l.name: l for l in [
     Lever("cond_dedup", "F3.hoisting", "models.design.DesignPipeline", apply=_cond_dedup),
     Lever("kernel_path", "F1.kernel_fusion", "rows+gemm+seq_sm100@1", needs_gpu=True, apply=_kernel_path),
     Lever("decode_graph", "F2.graph_capture", "models.evo2.generate", needs_gpu=True, apply=_decode_graph),
+    Lever("forward_graph", "F2.graph_capture", "capture.pool.GraphPool", needs_gpu=True, apply=_forward_graph),
     Lever("tp_fused", "F7.tensor_parallel", "parallel.tp", needs_gpu=True, apply=_tp_fused, droppable=True),
 ]}

@@ -16,6 +16,8 @@ class _Runner:
         self.draft = None                 # a smaller model of the family: generate() then decodes speculatively
         self.specdec_k = 0
         self.decode_graph = False         # the ``decode_graph`` lever: replay the decode step from a CUDA graph
+        self.forward_graphs = None        # the ``forward_graph`` lever: a capture site (``run(fn, *tensors)``)
+        self.forward_graph_max_tokens = 16384
 
     def run(self, verb: str, prompt: str, max_new_tokens: int = 32) -> dict:
         toks = evo2.tokenize(prompt, self.device)
@@ -30,8 +32,14 @@ class _Runner:
             return {"new_tokens": int(out.shape[1]), "text": "".join(chr(int(t)) if 32 <= int(t) < 127 else "?"
                                                                       for t in out[0].tolist()), **extra}
         if verb in ("score", "predict"):
-            return {"score": float(self.model.score(toks)[0]), "tokens": int(toks.shape[1])}
+            return {"score": float(self._score(toks)[0]), "tokens": int(toks.shape[1])}
         raise ValueError(f"unknown verb {verb!r}")
+
+    def _score(self, toks, **kw):
+        """``model.score`` - through the capture site for GPU inputs of a recurring shape that is small enough."""
+        if self.forward_graphs is not None and toks.is_cuda and not kw and toks.shape[1] <= self.forward_graph_max_tokens:
+            return self.forward_graphs.run(lambda t: self.model.score(t), toks)
+        return self.model.score(toks, **kw)
 
 
 class _PLMRunner(_Runner):
@@ -49,7 +57,7 @@ class _PLMRunner(_Runner):
                     "text": "".join(letters[int(t) - 4] if 4 <= int(t) < 4 + len(letters) else "X"
                                     for t in out[0].tolist())}
         if verb in ("score", "predict", "embedding", "logits", "vep"):
-            res = {"score": float(self.model.score(toks, **kw)[0]), "tokens": int(toks.shape[1])}
+            res = {"score": float(self._score(toks, **kw)[0]), "tokens": int(toks.shape[1])}
             if verb == "vep" and cfg.family == "gpnstar":
                 res["vep_min"] = float(self.model.variant_effect(toks, **kw).min())
             return res
