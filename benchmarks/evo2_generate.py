@@ -29,6 +29,7 @@ def main():
     ap.add_argument("--impl", default="fused", choices=["fused", "torch"])
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--graph", type=int, default=1, help="1: decode step captured in a CUDA graph and replayed")
+    ap.add_argument("--fp8", type=int, default=0, help="1: the input projections of the Hyena operators in e4m3 during the prefill")
     ap.add_argument("--specdec", type=int, default=0, help="k > 0: also time speculative decoding with k proposals per round")
     ap.add_argument("--draft", default="evo2_1b", help="configuration of the draft model for --specdec")
     a = ap.parse_args()
@@ -45,6 +46,8 @@ def main():
     par = None
     if a.impl == "fused":
         model.set_impl("fused")
+        if a.fp8:
+            model.set_fp8_input_projections(True)
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
@@ -112,7 +115,7 @@ def main():
     if rank == 0:
         pre, dec = t.tolist()
         print(json.dumps({
-            "bench": "evo2_generate", "config": a.config, "layers": model.cfg.n_layers, "tp": world, "impl": a.impl, "decode_graph": bool(a.graph),
+            "bench": "evo2_generate", "config": a.config, "layers": model.cfg.n_layers, "tp": world, "impl": a.impl, "fp8_input_projections": bool(a.fp8), "decode_graph": bool(a.graph),
             "prefill_tokens": a.prefill, "new_tokens": a.new, "prefill_ms": round(pre, 2),
             "prefill_tokens_per_s": round(a.prefill / pre * 1e3, 1), "decode_ms_per_token": round(dec / max(a.new - 1, 1), 3),
             "decode_tokens_per_s": round((a.new - 1) / dec * 1e3, 1), "last_token": last,

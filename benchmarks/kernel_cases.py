@@ -63,7 +63,7 @@ def main():
     ap.add_argument("--heads", type=int, default=32, help="causal_attention: heads")
     ap.add_argument("--lib", type=int, default=0, help="causal_attention: 1 = time the library attention instead")
     ap.add_argument("--masked", type=int, default=0, help="attention: 1 = key mask with a padded tail of a tenth of the keys")
-    ap.add_argument("--form", default="plain", help="gemv_rows: plain | norm (RMSNorm in front) | res (residual behind) | swiglu (RMSNorm + two matrices)")
+    ap.add_argument("--form", default="plain", help="gemv_rows: plain | norm (RMSNorm in front) | res (residual behind) | swiglu (RMSNorm + two matrices); gemm_rows: fp8 = e4m3 operands")
     ap.add_argument("--incoming", type=int, default=0, help="trimul / trimul_gemm: 1 = the incoming update (MN-major contraction)")
     a = ap.parse_args()
     N, c = a.n, 128
@@ -161,6 +161,11 @@ def main():
         out = torch.empty((M, NN), dtype=torch.bfloat16, device=dev)
         fn = lambda: gemm.gemm(x, wt, bias=bvec, out=out)  # noqa: E731
         byts, flops = (x.numel() + wt.numel() + out.numel()) * 2, 2.0 * M * K * NN
+        if a.form == "fp8":             # the same product with e4m3 operands (kind::f8f6f4)
+            x8, dqx = gemm.quantize_e4m3(x)
+            w8, dqw = gemm.quantize_e4m3(wt)
+            fn = lambda: gemm.gemm_fp8(x8, w8, alpha=dqx * dqw, bias=bvec, out=out)  # noqa: E731
+            byts = x.numel() + wt.numel() + out.numel() * 2
     elif a.case == "gemv_rows":
         # decode projection: --m rows (<= 8) x [nn, k] weights streamed once; --form plain | norm | res | swiglu
         from uplifting_biomolecular_modeling_b200.ops import seq

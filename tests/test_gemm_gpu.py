@@ -105,6 +105,33 @@ def test_gemm_swiglu_epilogue(M, H, K):
     assert ((out.float() - ref).abs().mean() / ref.abs().mean()).item() < 8e-3
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 520, 256), (1024, 1536, 4096), (130, 96, 208), (4096, 12288, 512)])
+def test_gemm_fp8_against_the_product_of_the_dequantised_operands(M, N, K):
+    """e4m3 operands on the kind::f8f6f4 path: the result is the fp32 product of the very same 8-bit values (K = 208
+    leaves a k-block partly empty, N = 96 / 520 a tile), with bias, activation and residual in the epilogue."""
+    from uplifting_biomolecular_modeling_b200.ops import gemm, native
+    g = torch.Generator(device="cuda").manual_seed(8)
+    a = torch.randn(M, K, device="cuda", generator=g)
+    w = torch.randn(N, K, device="cuda", generator=g) * K ** -0.5
+    a8, dqa = gemm.quantize_e4m3(a)
+    w8, dqw = gemm.quantize_e4m3(w)
+    ref = (a8.float() * dqa) @ (w8.float() * dqw).t()
+    out = gemm.gemm_fp8(a8, w8, alpha=dqa * dqw)
+    dev_scale = torch.full((1,), dqa, device="cuda")
+    bias = torch.randn(N, device="cuda", generator=g)
+    res = torch.randn(M, N, device="cuda", generator=g).bfloat16()
+    out2 = gemm.gemm_fp8(a8, w8, alpha=dqw, alpha_dev=dev_scale, bias=bias, residual=res, act="silu")
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "gemm_fp8")
+    scale = max(ref.abs().max().item(), 1.0)
+    assert (out.float() - ref).abs().max().item() <= 1e-2 * scale          # bf16 rounding of the output
+    ref2 = torch.nn.functional.silu(ref + bias) + res.float()
+    assert (out2.float() - ref2).abs().max().item() <= 1.5e-2 * max(ref2.abs().max().item(), 1.0)
+    # and the quantisation itself stays within e4m3's precision of the unquantised product
+    full = a @ w.t()
+    assert ((out.float() - full).abs().mean() / full.abs().mean()).item() < 6e-2
+
+
 @pytest.mark.parametrize("M,N,K", [(1000, 128, 128), (384, 96, 256), (257, 128, 64)])
 def test_gemm_residual_tiles_by_tma(M, N, K):
     """N <= 128 takes the 128-wide tile whose residual arrives through the shared-memory ring."""

@@ -274,6 +274,41 @@ def test_fft_prologue_and_spectrum_product_equal_the_plain_statements():
     assert (got - want).abs().max().item() <= 1e-5 * want.abs().max().item()
 
 
+@pytest.mark.parametrize("R,C", [(37, 256), (300, 4096), (5, 1024)])
+def test_rmsnorm_fp8_rows_and_their_dequantisation_factor(R, C):
+    from uplifting_biomolecular_modeling_b200.ops import reference as Rf, seq
+    g = torch.Generator(device="cuda").manual_seed(22)
+    x = (torch.randn(R, C, device="cuda", generator=g) * 3).bfloat16()
+    sc = 1 + 0.1 * torch.randn(C, device="cuda", generator=g)
+    ref = Rf.rmsnorm_rows(x, sc).float()
+    y8, dq = seq.rmsnorm_fp8(x, sc)
+    torch.cuda.synchronize()
+    assert y8.dtype == torch.float8_e4m3fn and y8.shape == (R, C)
+    amax = ref.abs().max().item()
+    assert abs(dq.item() * 448.0 - amax) <= 1e-2 * amax            # ref is rounded to bf16, the kernel's maximum is not
+    back = y8.float() * dq
+    # three mantissa bits: a relative step of 1/8 at most, half of it as rounding error (plus the subnormal floor)
+    assert ((back - ref).abs() <= 0.0625 * ref.abs() + 2.0 ** -9 * amax + 1e-2 * amax / 448).all()
+
+
+def test_evo2_fp8_input_projections_stay_close_to_the_bf16_prefill():
+    from uplifting_biomolecular_modeling_b200.models import evo2
+    from uplifting_biomolecular_modeling_b200.ops import native
+    m = evo2.build("evo2_tiny", device="cuda", dtype=torch.bfloat16, seed=9, d_model=256, n_heads=2, ffn=512)
+    m.set_impl("fused")
+    tok = torch.randint(0, m.cfg.vocab, (2, 200), device="cuda")
+    want = m(tok).float()
+    assert m.set_fp8_input_projections(True) == 3
+    states = [dict() for _ in m.blocks]
+    got = m(tok, states).float()
+    step = m.step(tok[:, -1:], states)                              # decode keeps the bf16 weights
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "evo2 fp8")
+    assert torch.isfinite(got).all() and torch.isfinite(step.float()).all()
+    rel = ((got - want).abs().mean() / want.abs().mean()).item()
+    assert 0.0 < rel < 8e-2, rel                                    # differs (8-bit operands) but stays close
+
+
 def test_per_channel_vectors_given_in_bf16():
     """Per-channel vectors that need a conversion are converted into tensors that outlive the launch."""
     from uplifting_biomolecular_modeling_b200.ops import reference as R, seq

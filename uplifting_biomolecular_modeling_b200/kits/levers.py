@@ -183,6 +183,18 @@ def _forward_graph(pred):
     return {"max_tokens": pred.forward_graph_max_tokens, "site": "score_forward"}
 
 
+def _fp8_input_proj(pred):
+    """StripedHyena-2 prefill: the input projections of the Hyena operators run in e4m3 (upstream's fp8 input
+    projections): RMSNorm emits 8-bit rows scaled by their maximum, the weights are quantised once."""
+    import torch
+    model = getattr(pred, "model", None)
+    if model is None or not hasattr(model, "set_fp8_input_projections"):
+        raise gates.CannotRun("fp8_input_proj: the model has no Hyena operators")
+    if not torch.cuda.is_available():
+        raise gates.CannotRun("fp8_input_proj: needs a CUDA device")
+    return {"operators": model.set_fp8_input_projections(True)}
+
+
 def _tp_fused(pred):
     """Tensor parallelism of the sequence models with the collectives fused into the GEMM kernels."""
     import torch
@@ -218,5 +230,7 @@ LEVERS: Dict[str, Lever] = {l.name: l for l in [
     Lever("kernel_path", "F1.kernel_fusion", "rows+gemm+seq_sm100@1", needs_gpu=True, apply=_kernel_path),
     Lever("decode_graph", "F2.graph_capture", "models.evo2.generate", needs_gpu=True, apply=_decode_graph),
     Lever("forward_graph", "F2.graph_capture", "capture.pool.GraphPool", needs_gpu=True, apply=_forward_graph),
+    Lever("fp8_input_proj", "F4.precision", "gemm_sm100 kind::f8f6f4 + seq_sm100 rmsnorm_fp8@1", needs_gpu=True,
+          apply=_fp8_input_proj, droppable=True),
     Lever("tp_fused", "F7.tensor_parallel", "parallel.tp", needs_gpu=True, apply=_tp_fused, droppable=True),
 ]}

@@ -18,7 +18,7 @@ COFOLD_LEVERS_FAST = ("fused_transition", "fused_trimul", "fused_triatt", "fused
                       "fused_dit")
 COFOLD_LEVERS_BIG = ("chunk_pair_ops", "release_intermediates", "park_pair_init", "expandable_segments", "rowpair_tp")
 LM_LEVERS_EXACT = ("kernel_path", "decode_graph", "forward_graph")
-LM_LEVERS_FAST = ("tp_fused",)
+LM_LEVERS_FAST = ("tp_fused", "fp8_input_proj")
 
 
 @dataclass(frozen=True)

@@ -133,6 +133,7 @@ class HyenaOperator(nn.Module):
         self.impl = "torch"
         self._taps = None           # tap-major fp32 copies of the filters for the kernels
         self._lam_cache = None
+        self.fp8 = False            # prefill: the input projection in e4m3 (see forward)
 
     # ---- filters
     def filter_spectrum(self, L: int):
@@ -204,11 +205,13 @@ class HyenaOperator(nn.Module):
         return seq.fftconv_epilogue(y, u, self.D, x2)
 
     def forward(self, x: torch.Tensor, state: Optional[dict] = None, linear=None,
-                residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+                residual: Optional[torch.Tensor] = None, pre_norm: Optional["RMSNorm"] = None) -> torch.Tensor:
         """Prefill form.  When ``state`` is a dict it is filled with what decoding needs.  ``residual`` (only with a
-        ``linear`` hook that takes one) is added behind the output projection, in its epilogue."""
+        ``linear`` hook that takes one) is added behind the output projection, in its epilogue.  ``pre_norm``: x is
+        the block's input before its RMSNorm and the input projection runs in fp8 (the norm emits e4m3 rows, the
+        weights are held in e4m3: upstream's fp8 input projections)."""
         lin = linear or (lambda m, t: m(t))
-        z = lin(self.in_proj, x)
+        z = fp8_projection(self.in_proj, x, pre_norm) if pre_norm is not None else lin(self.in_proj, x)
         fused = _fusable(self, z) and self.cfg.fir_len <= 4
         if fused:
             from ..ops import seq
@@ -512,7 +515,10 @@ class Block(nn.Module):
     def forward(self, x, state=None, linear=None):
         if linear is not None and getattr(linear, "takes_residual", False) and _fusable(self.pre_norm, x):
             # the residual stream is added in the epilogue of the projection that closes each half of the block
-            x = self.mixer(self.pre_norm(x), state, linear, x)
+            if getattr(self.mixer, "fp8", False) and x.shape[-1] <= 4096 and x.shape[0] * x.shape[1] > 8:
+                x = self.mixer(x, state, linear, x, self.pre_norm)
+            else:
+                x = self.mixer(self.pre_norm(x), state, linear, x)
             return self.mlp(self.post_norm(x), linear, x)
         x = x + self.mixer(self.pre_norm(x), state, linear)
         return x + self.mlp(self.post_norm(x), linear)
@@ -577,6 +583,16 @@ class StripedHyena2(nn.Module):
                 n += 1
         self.linear = fused_linear if impl == "fused" else None
         self.folded = folded_linear if impl == "fused" else None
+        return n
+
+    def set_fp8_input_projections(self, on: bool = True) -> int:
+        """Prefill: the input projections of the Hyena operators in e4m3 (kernel path, d_model <= 4096).  Returns the
+        number of operators switched."""
+        n = 0
+        for blk in self.blocks:
+            if isinstance(blk.mixer, HyenaOperator):
+                blk.mixer.fp8 = bool(on)
+                n += 1
         return n
 
     def logits(self, x):
@@ -766,6 +782,26 @@ def _decode_rows(block: "Block", x: torch.Tensor) -> bool:
     mb = 1 if rows == 1 else 2 if rows <= 2 else 4 if rows <= 4 else 8
     widest = max(x.shape[-1], block.mlp.l3.in_features)
     return widest % 8 == 0 and mb * widest * 2 <= 200 * 1024 and os.environ.get("UBM_EVO2_FOLDED_DECODE", "1") != "0"
+
+
+_W8_CACHE: dict = {}
+
+
+def fp8_projection(module: nn.Linear, x: torch.Tensor, norm: "RMSNorm") -> torch.Tensor:
+    """module(norm(x)) with both operands in e4m3: the normalised rows are written as 8-bit floats scaled by their
+    own maximum (``ops.seq.rmsnorm_fp8``), the weight is quantised once per version with its maximum, the product
+    accumulates in fp32 and is scaled back in the epilogue.  x: bf16 [B, L, d] on the GPU."""
+    from ..ops import gemm, seq
+    w = module.weight
+    ent = _W8_CACHE.get(id(module))
+    ver = (w._version, w.data_ptr(), tuple(w.shape))
+    if ent is None or ent[0] is not w or ent[1] != ver:
+        q, dq = gemm.quantize_e4m3(w)
+        ent = (w, ver, q, dq, None if module.bias is None else module.bias.detach().float().contiguous())
+        _W8_CACHE[id(module)] = ent
+    x8, dq_x = seq.rmsnorm_fp8(x, norm.scale, norm.eps)
+    y = gemm.gemm_fp8(x8, ent[2], alpha=ent[3], alpha_dev=dq_x, bias=ent[4])
+    return y.view(*x.shape[:-1], y.shape[-1])
 
 
 def folded_linear(module: nn.Linear, rows: torch.Tensor, gamma=None, eps: float = 1e-6, res=None,

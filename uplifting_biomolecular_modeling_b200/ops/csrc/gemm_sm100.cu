@@ -35,6 +35,10 @@ struct GemmParams {
   // from one projection with no [M, N] intermediate; 6 = two-way SwiGLU over column pairs (256-wide tiles): groups
   // of 64 = 32 gate | 32 value, output N / 2 columns wide
   int act;
+  // 1: A and B are e4m3 bytes (K-major, one GPU): 128 elements per k-block instead of 64, tcgen05.mma kind::f8f6f4;
+  // the accumulator is scaled by alpha * *alpha_dev (the product of the two dequantisation factors)
+  int fp8;
+  const float* alpha_dev;  // device scalar multiplied into alpha (written by the kernel that quantised A), or null
   int act_col0;  // the activation applies to output columns >= act_col0 (a multiple of 32; 0 = all columns)
   int res_tma;  // residual tiles arrive by TMA (tensor map in the auxiliary map slot 0)
   // bf16 output leaves through shared memory: every epilogue warp stages its 32 rows x 64 columns (128-byte swizzle;
@@ -251,7 +255,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-  const int num_kb = (p.K + kBK - 1) / kBK;
+  const int kbk = p.fp8 ? 2 * kBK : kBK;        // elements per k-block: a 128-byte row of either type
+  const int num_kb = (p.K + kbk - 1) / kbk;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
   const int compute_ctas = PEER ? static_cast<int>(gridDim.x) - p.copy_ctas : static_cast<int>(gridDim.x);
   const bool gather_once = PEER && p.copy_ctas > 0;
@@ -360,7 +365,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sb = sa + Cfg::kABytes;
           mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
           if (!MN_MAJOR) {
-            tma_load_3d(sa, &tmA, &full_bar[stage], kb * kBK, mb * kBM, b);
+            tma_load_3d(sa, &tmA, &full_bar[stage], kb * kbk, mb * kBM, b);
             if (PEER && gather_once) {
               // own shard straight from the local planes, remote shards from the gathered local copy
               const CUtensorMap* bm = (gq == p.my_rank) ? &peers.m[gq] : &gathered.m[gq];
@@ -371,7 +376,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               decode_ntile<BN>(p, nb, q, n_base, n_limit, lrow);
               tma_load_3d(sb, &peers.m[q], &full_bar[stage], kb * kBK, lrow, b);
             } else {
-              tma_load_3d(sb, &tmB, &full_bar[stage], kb * kBK, nb * BN, b);
+              tma_load_3d(sb, &tmB, &full_bar[stage], kb * kbk, nb * BN, b);
             }
           } else {
 #pragma unroll
@@ -395,6 +400,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool leader = elect_one();
     {
       constexpr uint32_t idesc = umma_idesc_bf16(kBM, BN, MN_MAJOR ? 1 : 0, MN_MAJOR ? 1 : 0);
+      constexpr uint32_t idesc_f8 = umma_idesc_e4m3(kBM, BN);
+      const bool fp8 = !MN_MAJOR && !PEER && p.fp8 != 0;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -414,9 +421,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                         : umma_smem_desc(sb, 16, 1024, kSwizzle128);
           constexpr uint64_t kStep = MN_MAJOR ? (2048 >> 4) : (32 >> 4);
           if (leader) {
+            // four MMAs per 128-byte row: 16 bf16 or 32 e4m3 elements each, 32 bytes apart in both cases
+            if (fp8) {
 #pragma unroll
-            for (int k = 0; k < kBK / 16; ++k)
-              umma_ss(d_tmem, ad0 + k * kStep, bd0 + k * kStep, idesc, (kb | k) != 0 ? 1u : 0u);
+              for (int k = 0; k < kBK / 16; ++k)
+                umma_ss_f8(d_tmem, ad0 + k * kStep, bd0 + k * kStep, idesc_f8, (kb | k) != 0 ? 1u : 0u);
+            } else {
+#pragma unroll
+              for (int k = 0; k < kBK / 16; ++k)
+                umma_ss(d_tmem, ad0 + k * kStep, bd0 + k * kStep, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
             umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
           }
           __syncwarp();
@@ -437,6 +451,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     const int grp = (warp - 2) >> 2;                       // which half of the tile's column chunks
+    const float alpha = p.alpha_dev != nullptr ? p.alpha * __ldg(p.alpha_dev) : p.alpha;
     constexpr int kChunksPerGroup = (BN / 32) / kEpiGroups;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -474,7 +489,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (row_ok) {
           float f[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * alpha;
           if (p.bias != nullptr) {
             if (n0 + 32 <= n_limit && (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) {
 #pragma unroll
@@ -626,14 +641,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tmem_ld32(t0 + 32, vb);
             float f[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = siluf_fast(__uint_as_float(va[j]) * p.alpha);
+            for (int j = 0; j < 32; ++j) f[j] = siluf_fast(__uint_as_float(va[j]) * alpha);
             tmem_ld_wait();
             tmem_ld32(t0 + 64, va);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] *= __uint_as_float(vb[j]) * p.alpha;
+            for (int j = 0; j < 32; ++j) f[j] *= __uint_as_float(vb[j]) * alpha;
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] *= __uint_as_float(va[j]) * p.alpha;
+            for (int j = 0; j < 32; ++j) f[j] *= __uint_as_float(va[j]) * alpha;
             const int o0 = (n_base + c_begin * 32) / 3;
             if (c_tma) {
               if (lane == 0) tma_store_wait_read<0>();   // the previous box of this warp has left the staging rows
@@ -689,7 +704,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             float f[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              f[j] = siluf_fast(__uint_as_float(va[j]) * p.alpha) * (__uint_as_float(vb[j]) * p.alpha);
+              f[j] = siluf_fast(__uint_as_float(va[j]) * alpha) * (__uint_as_float(vb[j]) * alpha);
             const int o0 = (n_base + c * 32) / 2;
             if (c_tma) {
               if (lane == 0) tma_store_wait_read<0>();   // the previous box of this warp has left the staging rows
@@ -792,15 +807,19 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   CUtensorMap tmA, tmB;
   int rc;
   if (!MN_MAJOR) {
+    // operands as rows of 128 bytes: 64 bf16 or (fp8) 128 e4m3 elements per k-block
+    const uint64_t es = p.fp8 ? 1 : 2;
+    const CUtensorMapDataType dt = p.fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const uint32_t bk = p.fp8 ? 2 * kBK : kBK;
     uint64_t dA[3] = {(uint64_t)p.K, (uint64_t)p.M, (uint64_t)p.batch};
-    uint64_t sA[2] = {(uint64_t)lda * 2, (uint64_t)strideA * 2};
-    uint32_t bA[3] = {kBK, kBM, 1};
-    rc = make_tmap(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dA, sA, bA, CU_TENSOR_MAP_SWIZZLE_128B);
+    uint64_t sA[2] = {(uint64_t)lda * es, (uint64_t)strideA * es};
+    uint32_t bA[3] = {bk, kBM, 1};
+    rc = make_tmap(&tmA, A, dt, 3, dA, sA, bA, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     uint64_t dB[3] = {(uint64_t)p.K, (uint64_t)p.N, (uint64_t)p.batch};
-    uint64_t sB[2] = {(uint64_t)ldb * 2, (uint64_t)strideB * 2};
-    uint32_t bB[3] = {kBK, (uint32_t)BN, 1};
-    rc = make_tmap(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dB, sB, bB, CU_TENSOR_MAP_SWIZZLE_128B);
+    uint64_t sB[2] = {(uint64_t)ldb * es, (uint64_t)strideB * es};
+    uint32_t bB[3] = {bk, (uint32_t)BN, 1};
+    rc = make_tmap(&tmB, B, dt, 3, dB, sB, bB, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   } else {
     uint64_t dA[3] = {(uint64_t)p.M, (uint64_t)p.K, (uint64_t)p.batch};
@@ -918,6 +937,8 @@ extern "C" int ubm_gemm_bf16_ex(const void* A, const void* B, void* C, const voi
   p.alpha = alpha;
   p.out_fp32 = out_fp32;
   p.act = act;
+  p.fp8 = 0;
+  p.alpha_dev = nullptr;
   p.act_col0 = act_col0;
   p.cblk_hi = cblk_hi;
   p.cblk_lo = cblk_lo;
@@ -975,6 +996,41 @@ extern "C" int ubm_gemm_bf16(const void* A, const void* B, void* C, const void* 
                              int out_fp32, int act, float alpha, void* status, void* stream) {
   return ubm_gemm_bf16_ex(A, B, C, bias, residual, M, N, K, batch, lda, ldb, ldc, ldr, strideA, strideB, strideC,
                           strideR, mn_major, out_fp32, act, alpha, 0, 0, 0, nullptr, 0, 0, 0, status, stream);
+}
+
+// C[m][n] = act(alpha * *alpha_dev * sum_k A[m][k] B[n][k] + bias[n]) (+ residual) with A [M][K] and B [N][K] in
+// e4m3 (one byte per element, K contiguous; lda / ldb in elements, multiples of 16) and C bf16: tcgen05.mma
+// kind::f8f6f4 with fp32 accumulation.  alpha carries the host-known dequantisation factor (the weights'),
+// alpha_dev (a device float or null) the one a kernel earlier in the stream wrote for the activations.
+extern "C" int ubm_gemm_fp8(const void* A, const void* B, void* C, const void* bias, const void* residual, int M, int N,
+                            int K, long long lda, long long ldb, long long ldc, long long ldr, int act, float alpha,
+                            const void* alpha_dev, void* status, void* stream) {
+  using namespace ubm;
+  if (M <= 0 || N <= 0 || K <= 0 || act < 0 || act > 4) return UBM_ERR_ARGUMENT;
+  if ((lda & 15) || (ldb & 15) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) {
+    fprintf(stderr, "[ubm] gemm_fp8: operands must be 16-byte aligned with leading dimensions in multiples of 16\n");
+    return UBM_ERR_ARGUMENT;
+  }
+  GemmParams p = {};
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.batch = 1;
+  p.C = C;
+  p.ldc = ldc;
+  p.bias = static_cast<const float*>(bias);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.ldr = ldr;
+  p.alpha = alpha;
+  p.act = act;
+  p.fp8 = 1;
+  p.alpha_dev = static_cast<const float*>(alpha_dev);
+  p.gate_rows = 1;
+  p.status = static_cast<KernelStatus*>(status);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long strideA = static_cast<long long>(M) * lda, strideB = static_cast<long long>(N) * ldb;
+  return N > 128 ? launch_gemm<256, false>(A, B, p, lda, ldb, strideA, strideB, st)
+                 : launch_gemm<128, false>(A, B, p, lda, ldb, strideA, strideB, st);
 }
 
 // GEMM whose epilogue scatters output rows to their owners: the transfer half of a reduce-scatter fused into the

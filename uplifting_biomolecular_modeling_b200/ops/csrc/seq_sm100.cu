@@ -14,6 +14,8 @@
 // decode-step state), progen2 kits/v0_ew/kernels.cu:37-209 (gelu_new, rotary_split_qkv, residual_add2),
 // esmc kits/residual_ln/kernels.cu:28-127, enformer kits/v0_2/enformer_xattn.cu:24-99 (add2 softmax) and
 // enformer_fastkit.py:96-157 (bn_gelu, pool, bias_residual).
+#include <cuda_fp8.h>
+
 #include "host_util.h"
 #include "sm100.cuh"
 
@@ -81,6 +83,79 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const __nv_bfloat16* 
         *reinterpret_cast<uint4*>(out + r * C + c) = pack8(o);
       }
     }
+  }
+}
+
+// ------------------------------------------------------------------------------------------ RMSNorm -> e4m3
+// The normalised rows as 8-bit floats for an fp8 projection, scaled by the tensor's own maximum ("current
+// scaling": no state is carried between calls).  Two launches: the first takes max |y| over the tensor
+// (y = x * rsqrt(mean(x^2) + eps) * scale, the bits of a non-negative float order as integers), the second
+// writes e4m3(y * 448 / max) and the dequantisation factor max / 448 for the projection's epilogue.
+template <int CHUNKS, bool EMIT>
+__global__ void __launch_bounds__(256) rmsnorm_fp8_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          const float* __restrict__ scale,
+                                                          unsigned int* __restrict__ amax_bits,
+                                                          uint8_t* __restrict__ out, float* __restrict__ dequant,
+                                                          long long R, int C, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  float q = 0.f;
+  if (EMIT) {
+    const float amax = fmaxf(__uint_as_float(*amax_bits), 1e-12f);
+    q = 448.0f / amax;
+    if (blockIdx.x == 0 && threadIdx.x == 0) *dequant = amax / 448.0f;
+  }
+  float vmax = 0.f;
+  for (long long r = static_cast<long long>(blockIdx.x) * wpb + (threadIdx.x >> 5); r < R;
+       r += static_cast<long long>(gridDim.x) * wpb) {
+    uint4 raw[CHUNKS];
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < C) raw[k] = *reinterpret_cast<const uint4*>(x + r * C + c);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < C) {
+        float v[8];
+        unpack8(raw[k], v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+      }
+    }
+    ss = warp_sum(ss);
+    const float rs = rsqrtf(ss / C + eps);
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < C) {
+        const float4 s0 = __ldg(reinterpret_cast<const float4*>(scale + c));
+        const float4 s1 = __ldg(reinterpret_cast<const float4*>(scale + c + 4));
+        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        float v[8], y[8];
+        unpack8(raw[k], v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) y[j] = v[j] * rs * sc[j];
+        if (EMIT) {
+          uint2 o;
+          o.x = static_cast<unsigned int>(__nv_cvt_float2_to_fp8x2(make_float2(y[0] * q, y[1] * q), __NV_SATFINITE, __NV_E4M3)) |
+                (static_cast<unsigned int>(__nv_cvt_float2_to_fp8x2(make_float2(y[2] * q, y[3] * q), __NV_SATFINITE, __NV_E4M3)) << 16);
+          o.y = static_cast<unsigned int>(__nv_cvt_float2_to_fp8x2(make_float2(y[4] * q, y[5] * q), __NV_SATFINITE, __NV_E4M3)) |
+                (static_cast<unsigned int>(__nv_cvt_float2_to_fp8x2(make_float2(y[6] * q, y[7] * q), __NV_SATFINITE, __NV_E4M3)) << 16);
+          *reinterpret_cast<uint2*>(out + r * C + c) = o;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) vmax = fmaxf(vmax, fabsf(y[j]));
+        }
+      }
+    }
+  }
+  if (!EMIT) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+    if (lane == 0) atomicMax(amax_bits, __float_as_uint(vmax));
   }
 }
 
@@ -813,6 +888,33 @@ extern "C" int ubm_rmsnorm_rows(const void* x, const void* scale, void* out, lon
   else if (C <= 4096) rmsnorm_rows_kernel<16><<<grid, 256, 0, st>>>(xx, sc, oo, R, C, eps);
   else rmsnorm_rows_wide_kernel<<<grid, 256, 0, st>>>(xx, sc, oo, R, C, eps);
   UBM_CHECK_LAUNCH("rmsnorm_rows_kernel");
+  return UBM_OK;
+}
+
+// x: bf16 [R][C] (C a multiple of 8, at most 4096); scale: fp32 [C]; amax: uint32 [1] scratch (the bits of the
+// maximum); out: e4m3 [R][C]; dequant: fp32 [1] = max / 448
+extern "C" int ubm_rmsnorm_fp8(const void* x, const void* scale, void* amax, void* out, void* dequant, long long R,
+                               int C, float eps, void* stream) {
+  if (R <= 0 || C <= 0 || (C & 7) || C > 4096 || !aligned16(x) || !aligned16(scale) || (reinterpret_cast<uintptr_t>(out) & 7))
+    return UBM_ERR_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = seq_grid(R, 8);
+  const __nv_bfloat16* xx = static_cast<const __nv_bfloat16*>(x);
+  const float* sc = static_cast<const float*>(scale);
+  unsigned int* am = static_cast<unsigned int*>(amax);
+  uint8_t* oo = static_cast<uint8_t*>(out);
+  float* dq = static_cast<float*>(dequant);
+  if (cudaMemsetAsync(am, 0, sizeof(unsigned int), st) != cudaSuccess) return UBM_ERR_LAUNCH;
+#define UBM_RF8(CH)                                                                              \
+  do {                                                                                           \
+    rmsnorm_fp8_kernel<CH, false><<<grid, 256, 0, st>>>(xx, sc, am, oo, dq, R, C, eps);          \
+    rmsnorm_fp8_kernel<CH, true><<<grid, 256, 0, st>>>(xx, sc, am, oo, dq, R, C, eps);           \
+  } while (0)
+  if (C <= 1024) UBM_RF8(4);
+  else if (C <= 2048) UBM_RF8(8);
+  else UBM_RF8(16);
+#undef UBM_RF8
+  UBM_CHECK_LAUNCH("rmsnorm_fp8_kernel");
   return UBM_OK;
 }
 

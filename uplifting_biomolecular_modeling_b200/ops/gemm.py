@@ -13,6 +13,9 @@ import torch
 
 from . import native
 
+native.declare("ubm_gemm_fp8", [native.c_void_p] * 5 + [native.c_int] * 3 + [native.c_ll] * 4 +
+               [native.c_int, native.c_float, native.c_void_p, native.c_void_p, native.c_void_p])
+
 ACT = {None: 0, "none": 0, "silu": 1, "sigmoid": 2, "gelu": 3, "relu": 4, "swiglu3": 5, "swiglu": 6}
 
 
@@ -125,6 +128,50 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, mn_major: bool = False, bias: Opti
     if c_blocked is not None:
         return out
     return out3[0] if squeeze and out.dim() == 3 else out
+
+
+_E4M3 = (torch.uint8, torch.float8_e4m3fn)
+
+
+def quantize_e4m3(w: torch.Tensor):
+    """Per-tensor e4m3 form of a matrix: (bytes [rows, cols] as ``torch.float8_e4m3fn``, dequantisation factor
+    max|w| / 448 as a Python float).  One host read of the maximum: meant for weights, once."""
+    amax = float(w.detach().abs().max())
+    amax = max(amax, 1e-12)
+    q = (w.detach().float() * (448.0 / amax)).clamp_(-448.0, 448.0).to(torch.float8_e4m3fn).contiguous()
+    return q, amax / 448.0
+
+
+def gemm_fp8(a8: torch.Tensor, b8: torch.Tensor, alpha: float = 1.0, alpha_dev: Optional[torch.Tensor] = None, *,
+             bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None, act: Optional[str] = None,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 [M, N] = act(alpha * alpha_dev * a8 @ b8^T + bias) (+ residual) with e4m3 operands a8 [M, K], b8 [N, K]
+    (``torch.float8_e4m3fn`` or raw bytes, rows contiguous, K a multiple of 16) on the tcgen05 ``kind::f8f6f4`` path.
+    ``alpha`` is the host-known dequantisation factor, ``alpha_dev`` (fp32 [1] on the device, optional) the one a
+    kernel earlier in the stream wrote (:func:`ops.seq.rmsnorm_fp8`)."""
+    if a8.dtype not in _E4M3 or b8.dtype not in _E4M3 or a8.dim() != 2 or b8.dim() != 2:
+        raise TypeError("gemm_fp8 expects 2-D e4m3 (or uint8) operands")
+    M, K = a8.shape
+    N = b8.shape[0]
+    if b8.shape[1] != K or a8.stride(1) != 1 or b8.stride(1) != 1 or act in ("swiglu", "swiglu3"):
+        raise ValueError("gemm_fp8: K-major operands of equal K; no SwiGLU epilogue")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a8.device)
+    if out.dtype != torch.bfloat16 or out.shape != (M, N) or out.stride(1) != 1:
+        raise ValueError("gemm_fp8 output must be bf16 [M, N] with contiguous rows")
+    if residual is not None and (residual.dtype != torch.bfloat16 or residual.shape != (M, N) or residual.stride(1) != 1):
+        raise ValueError("residual must be bf16 [M, N] with contiguous rows")
+    if bias is not None and bias.dtype != torch.float32:
+        bias = bias.float()
+    if alpha_dev is not None and (alpha_dev.dtype != torch.float32 or alpha_dev.numel() != 1 or alpha_dev.device != a8.device):
+        raise ValueError("alpha_dev is one fp32 value on the operands' device")
+    st = native.status_tensor(a8.device)
+    rc = native.lib().ubm_gemm_fp8(native.ptr(a8), native.ptr(b8), native.ptr(out), native.ptr(bias),
+                                   native.ptr(residual), M, N, K, a8.stride(0), b8.stride(0), out.stride(0),
+                                   0 if residual is None else residual.stride(0), ACT[act], float(alpha),
+                                   native.ptr(alpha_dev), native.ptr(st), native.current_stream(a8.device))
+    native.check(rc, "ubm_gemm_fp8")
+    return out
 
 
 def gemm_tn(a, b, **kw):

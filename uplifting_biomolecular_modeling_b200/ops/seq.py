@@ -27,6 +27,7 @@ native.declare("ubm_pool2", [c_void_p] * 3 + [c_int] * 4 + [c_void_p])
 native.declare("ubm_residual_ln", [c_void_p] * 6 + [c_ll, c_int, c_float, c_void_p])
 
 native.declare("ubm_gemv_fused", [c_void_p] * 2 + [c_float] + [c_void_p] * 5 + [c_int] * 3 + [c_void_p])
+native.declare("ubm_rmsnorm_fp8", [c_void_p] * 5 + [c_ll, c_int, c_float, c_void_p])
 native.declare("ubm_pole_prefill_state", [c_void_p] * 4 + [c_int] * 5 + [c_void_p])
 native.declare("ubm_fft_pad_transpose", [c_void_p] * 2 + [c_int] * 4 + [c_void_p])
 native.declare("ubm_spectrum_mul", [c_void_p] * 2 + [c_int, c_ll, c_void_p])
@@ -77,6 +78,21 @@ def rmsnorm_rows(x: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6) -> tor
                                        float(eps), _stream(x))
     native.check(rc, "ubm_rmsnorm_rows")
     return out
+
+
+def rmsnorm_fp8(x: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6):
+    """RMSNorm rows as e4m3 for an fp8 projection, scaled by the tensor's own maximum.  x: bf16 [.., C], C <= 4096.
+    Returns (``torch.float8_e4m3fn`` [R, C], fp32 [1] dequantisation factor on the device)."""
+    x = _bf16c(x)
+    C = x.shape[-1]
+    R = x.numel() // C
+    out = torch.empty((R, C), dtype=torch.float8_e4m3fn, device=x.device)
+    work = torch.empty(2, dtype=torch.float32, device=x.device)          # [0]: bits of the maximum, [1]: max / 448
+    sc = _f32(scale)
+    rc = native.lib().ubm_rmsnorm_fp8(native.ptr(x), native.ptr(sc), native.ptr(work), native.ptr(out),
+                                      native.ptr(work) + 4, R, C, float(eps), _stream(x))
+    native.check(rc, "ubm_rmsnorm_fp8")
+    return out, work[1:2]
 
 
 def taps_major(h: torch.Tensor) -> torch.Tensor:
