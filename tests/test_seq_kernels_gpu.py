@@ -274,6 +274,22 @@ def test_fft_prologue_and_spectrum_product_equal_the_plain_statements():
     assert (got - want).abs().max().item() <= 1e-5 * want.abs().max().item()
 
 
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 1000), (3, 1040, 77), (8, 256, 300)])
+def test_gemv_rows_with_e4m3_weights(M, K, N):
+    from uplifting_biomolecular_modeling_b200.ops import gemm, seq
+    g = torch.Generator(device="cuda").manual_seed(23)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = torch.randn(N, K, device="cuda", generator=g) * K ** -0.5
+    gamma = 1 + 0.1 * torch.randn(K, device="cuda", generator=g)
+    res = torch.randn(M, N, device="cuda", generator=g).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g)
+    q, dq = gemm.quantize_e4m3(w)
+    _close(seq.gemv_rows(x, q, b, wscale=dq), x.float() @ (q.float() * dq).t() + b, 1e-2)
+    xn = seq.rmsnorm_rows(x, gamma, 1e-6)
+    _close(seq.gemv_rows(x, q, b, gamma=gamma, res=res, wscale=dq),
+           xn.float() @ (q.float() * dq).t() + b + res.float(), 1e-2)
+
+
 @pytest.mark.parametrize("R,C", [(37, 256), (300, 4096), (5, 1024)])
 def test_rmsnorm_fp8_rows_and_their_dequantisation_factor(R, C):
     from uplifting_biomolecular_modeling_b200.ops import reference as Rf, seq
@@ -301,7 +317,7 @@ def test_evo2_fp8_input_projections_stay_close_to_the_bf16_prefill():
     assert m.set_fp8_input_projections(True) == 3
     states = [dict() for _ in m.blocks]
     got = m(tok, states).float()
-    step = m.step(tok[:, -1:], states)                              # decode keeps the bf16 weights
+    step = m.step(tok[:, -1:], states)                              # the folded block reads the e4m3 weights
     torch.cuda.synchronize()
     native.raise_on_status("cuda", "evo2 fp8")
     assert torch.isfinite(got).all() and torch.isfinite(step.float()).all()

@@ -586,12 +586,13 @@ class StripedHyena2(nn.Module):
         return n
 
     def set_fp8_input_projections(self, on: bool = True) -> int:
-        """Prefill: the input projections of the Hyena operators in e4m3 (kernel path, d_model <= 4096).  Returns the
-        number of operators switched."""
+        """The input projections of the Hyena operators in e4m3 (kernel path, d_model <= 4096): both operands in
+        the prefill, the weights in the folded decode block.  Returns the number of operators switched."""
         n = 0
         for blk in self.blocks:
             if isinstance(blk.mixer, HyenaOperator):
                 blk.mixer.fp8 = bool(on)
+                blk.mixer.in_proj.fp8_weights = bool(on)     # read by the folded decode block
                 n += 1
         return n
 
@@ -792,6 +793,15 @@ def fp8_projection(module: nn.Linear, x: torch.Tensor, norm: "RMSNorm") -> torch
     own maximum (``ops.seq.rmsnorm_fp8``), the weight is quantised once per version with its maximum, the product
     accumulates in fp32 and is scaled back in the epilogue.  x: bf16 [B, L, d] on the GPU."""
     from ..ops import gemm, seq
+    q, dq, bias = _e4m3_weight(module)
+    x8, dq_x = seq.rmsnorm_fp8(x, norm.scale, norm.eps)
+    y = gemm.gemm_fp8(x8, q, alpha=dq, alpha_dev=dq_x, bias=bias)
+    return y.view(*x.shape[:-1], y.shape[-1])
+
+
+def _e4m3_weight(module: nn.Linear):
+    """(e4m3 weight, its dequantisation factor, fp32 bias or None), quantised once per weight version."""
+    from ..ops import gemm
     w = module.weight
     ent = _W8_CACHE.get(id(module))
     ver = (w._version, w.data_ptr(), tuple(w.shape))
@@ -799,9 +809,7 @@ def fp8_projection(module: nn.Linear, x: torch.Tensor, norm: "RMSNorm") -> torch
         q, dq = gemm.quantize_e4m3(w)
         ent = (w, ver, q, dq, None if module.bias is None else module.bias.detach().float().contiguous())
         _W8_CACHE[id(module)] = ent
-    x8, dq_x = seq.rmsnorm_fp8(x, norm.scale, norm.eps)
-    y = gemm.gemm_fp8(x8, ent[2], alpha=ent[3], alpha_dev=dq_x, bias=ent[4])
-    return y.view(*x.shape[:-1], y.shape[-1])
+    return ent[2], ent[3], ent[4]
 
 
 def folded_linear(module: nn.Linear, rows: torch.Tensor, gamma=None, eps: float = 1e-6, res=None,
@@ -810,6 +818,9 @@ def folded_linear(module: nn.Linear, rows: torch.Tensor, gamma=None, eps: float 
     kernel with RMSNorm (``gamma``) in front, the residual (``res``) behind and, with ``second``, the SwiGLU of
     two projections."""
     from ..ops import seq
+    if getattr(module, "fp8_weights", False) and second is None and rows.shape[-1] % 16 == 0:
+        q, dq, b8 = _e4m3_weight(module)          # the prefill's e4m3 weights: half the bytes of the step
+        return seq.gemv_rows(rows, q, b8, gamma=gamma, eps=eps, res=res, wscale=dq)
     w, b = _bf16_weight(module)
     w2 = None if second is None else _bf16_weight(second)[0]
     return seq.gemv_rows(rows, w, b, gamma=gamma, eps=eps, w2=w2, res=res)

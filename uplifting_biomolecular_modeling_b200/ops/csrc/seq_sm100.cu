@@ -1149,11 +1149,27 @@ constexpr int kGemvMaxSmem = 200 * 1024;
 
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16(v)); }
 
-template <int MB, bool DUAL>
+__device__ __forceinline__ void unpack16_e4m3(const uint4& u, float (&e)[16]) {
+  const unsigned int w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w[i] & 0xffffu), __NV_E4M3);
+    const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w[i] >> 16), __NV_E4M3);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+    e[4 * i] = a.x; e[4 * i + 1] = a.y; e[4 * i + 2] = b.x; e[4 * i + 3] = b.y;
+  }
+}
+
+// W8: w holds e4m3 bytes ([N][K], K a multiple of 16) and the row sums are multiplied by wscale (the weights'
+// dequantisation factor); the activations stay bf16.  Half the bytes of the bf16 form per output row.
+template <int MB, bool DUAL, bool W8>
 __global__ void __launch_bounds__(kGemvThreads) gemv_rows_kernel(
     const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma, float eps,
     const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ w2, const float* __restrict__ bias,
-    const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ out, int M, int N, int K) {
+    const __nv_bfloat16* __restrict__ res, __nv_bfloat16* __restrict__ out, int M, int N, int K, float wscale) {
+  static_assert(!(DUAL && W8), "the two-matrix form reads bf16 weights");
+  const int wbytes = W8 ? 1 : 2;                                               // bytes per weight element
   extern __shared__ __align__(16) unsigned char gemv_smem[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(gemv_smem);              // [MB][K]
   __shared__ float red[MB][kGemvThreads / 32];
@@ -1164,8 +1180,8 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_rows_kernel(
   const int n_first = blockIdx.x * wpb + warp;
   // the first weight row of this warp starts towards L2 while x^ is staged
   if (n_first < N) {
-    const char* p0 = reinterpret_cast<const char*>(w + static_cast<long long>(n_first) * K);
-    for (int o = lane * 128; o < K * 2; o += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(p0 + o));
+    const char* p0 = reinterpret_cast<const char*>(w) + static_cast<long long>(n_first) * K * wbytes;
+    for (int o = lane * 128; o < K * wbytes; o += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(p0 + o));
     if (DUAL) {
       const char* p1 = reinterpret_cast<const char*>(w2 + static_cast<long long>(n_first) * K);
       for (int o = lane * 128; o < K * 2; o += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(p1 + o));
@@ -1239,11 +1255,46 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_rows_kernel(
     for (int b = 0; b < MB; ++b) acc[b] = 0.f;
 #pragma unroll
     for (int b = 0; b < (DUAL ? MB : 1); ++b) acc2[b] = 0.f;
+    if constexpr (W8) {
+      const uint4* wr8 = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(w) + static_cast<long long>(n) * K);
+      const int nv8 = K >> 4;                                                  // 16 weights per 16-byte vector
+      constexpr int U8 = 4;
+      for (int i0 = lane; i0 < nv8; i0 += 32 * U8) {
+        uint4 wv[U8];
+#pragma unroll
+        for (int u = 0; u < U8; ++u) {
+          const int i = i0 + 32 * u;
+          wv[u] = i < nv8 ? __ldcs(wr8 + i) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < U8; ++u) {
+          const int i = i0 + 32 * u;
+          if (i < nv8) {
+            float wf[16];
+            unpack16_e4m3(wv[u], wf);
+#pragma unroll
+            for (int b = 0; b < MB; ++b) {
+              if (b < M) {
+                float x0[8], x1[8];
+                const uint4* xb = reinterpret_cast<const uint4*>(xs + static_cast<long long>(b) * K);
+                unpack8(xb[2 * i], x0);
+                unpack8(xb[2 * i + 1], x1);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  acc[b] = fmaf(wf[e], x0[e], acc[b]);
+                  acc[b] = fmaf(wf[8 + e], x1[e], acc[b]);
+                }
+              }
+            }
+          }
+        }
+      }
+    }
     const uint4* wr = reinterpret_cast<const uint4*>(w + static_cast<long long>(n) * K);
     const uint4* wr2 = DUAL ? reinterpret_cast<const uint4*>(w2 + static_cast<long long>(n) * K) : nullptr;
     // loads in flight per lane: 8 (two matrices x 4, or one matrix x 8 when few rows leave the registers free)
     constexpr int U = (DUAL || MB > 2) ? 4 : 8;
-    for (int i0 = lane; i0 < nv; i0 += 32 * U) {
+    for (int i0 = lane; i0 < (W8 ? 0 : nv); i0 += 32 * U) {
       uint4 wv[U], wv2[DUAL ? U : 1];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
@@ -1279,6 +1330,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_rows_kernel(
       float s2 = DUAL ? warp_sum(acc2[b]) : 0.f;
       if (lane == 0 && b < M) {
         const long long o = static_cast<long long>(b) * N + n;
+        if (W8) s *= wscale;
         if (bias != nullptr) s += bias[n];
         if (DUAL) {
           const float g = bf16_round(s), up = bf16_round(s2);
@@ -1291,9 +1343,9 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_rows_kernel(
   }
 }
 
-template <bool DUAL>
+template <bool DUAL, bool W8>
 int launch_gemv(const __nv_bfloat16* x, const float* gamma, float eps, const __nv_bfloat16* w, const __nv_bfloat16* w2,
-                const float* bias, const __nv_bfloat16* res, __nv_bfloat16* out, int M, int N, int K,
+                const float* bias, const __nv_bfloat16* res, __nv_bfloat16* out, int M, int N, int K, float wscale,
                 cudaStream_t st) {
   const int MB = M == 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
   const size_t smem = static_cast<size_t>(MB) * K * sizeof(__nv_bfloat16);
@@ -1309,7 +1361,7 @@ int launch_gemv(const __nv_bfloat16* x, const float* gamma, float eps, const __n
   }();
 #define UBM_GEMV(MBV)                                                                                          \
   do {                                                                                                         \
-    auto kern = gemv_rows_kernel<MBV, DUAL>;                                                                   \
+    auto kern = gemv_rows_kernel<MBV, DUAL, W8>;                                                               \
     if (smem > 48 * 1024 &&                                                                                    \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvMaxSmem) != cudaSuccess)  \
       return UBM_ERR_LAUNCH;                                                                                   \
@@ -1323,7 +1375,7 @@ int launch_gemv(const __nv_bfloat16* x, const float* gamma, float eps, const __n
     attr[0].val.programmaticStreamSerializationAllowed = 1;                                                    \
     cfg.attrs = attr;                                                                                          \
     cfg.numAttrs = pdl ? 1 : 0;                                                                                \
-    if (cudaLaunchKernelEx(&cfg, kern, x, gamma, eps, w, w2, bias, res, out, M, N, K) != cudaSuccess)          \
+    if (cudaLaunchKernelEx(&cfg, kern, x, gamma, eps, w, w2, bias, res, out, M, N, K, wscale) != cudaSuccess)  \
       return UBM_ERR_LAUNCH;                                                                                   \
   } while (0)
   switch (MB) {
@@ -1353,8 +1405,20 @@ extern "C" int ubm_gemv_fused(const void* x, const void* gamma, float eps, const
   __nv_bfloat16* oo = static_cast<__nv_bfloat16*>(out);
   const float* gg = static_cast<const float*>(gamma);
   const float* bb = static_cast<const float*>(bias);
-  return w2 != nullptr ? ubm::launch_gemv<true>(xx, gg, eps, ww, w22, bb, rr, oo, M, N, K, st)
-                       : ubm::launch_gemv<false>(xx, gg, eps, ww, w22, bb, rr, oo, M, N, K, st);
+  return w2 != nullptr ? ubm::launch_gemv<true, false>(xx, gg, eps, ww, w22, bb, rr, oo, M, N, K, 1.f, st)
+                       : ubm::launch_gemv<false, false>(xx, gg, eps, ww, w22, bb, rr, oo, M, N, K, 1.f, st);
+}
+
+// The same with the weights in e4m3: w8 [N][K] bytes (K a multiple of 16), wscale their dequantisation factor
+extern "C" int ubm_gemv_fused_w8(const void* x, const void* gamma, float eps, const void* w8, float wscale,
+                                 const void* bias, const void* res, void* out, int M, int N, int K, void* stream) {
+  if (M < 1 || M > 8 || N < 1 || K < 16 || (K & 15) || !aligned16(x) || !aligned16(w8) ||
+      (gamma != nullptr && !aligned16(gamma)))
+    return UBM_ERR_ARGUMENT;
+  return ubm::launch_gemv<false, true>(static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(gamma), eps,
+                                       static_cast<const __nv_bfloat16*>(w8), nullptr, static_cast<const float*>(bias),
+                                       static_cast<const __nv_bfloat16*>(res), static_cast<__nv_bfloat16*>(out), M, N,
+                                       K, wscale, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ubm_gemv_rows(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,

@@ -27,6 +27,7 @@ native.declare("ubm_pool2", [c_void_p] * 3 + [c_int] * 4 + [c_void_p])
 native.declare("ubm_residual_ln", [c_void_p] * 6 + [c_ll, c_int, c_float, c_void_p])
 
 native.declare("ubm_gemv_fused", [c_void_p] * 2 + [c_float] + [c_void_p] * 5 + [c_int] * 3 + [c_void_p])
+native.declare("ubm_gemv_fused_w8", [c_void_p] * 2 + [c_float, c_void_p, c_float] + [c_void_p] * 3 + [c_int] * 3 + [c_void_p])
 native.declare("ubm_rmsnorm_fp8", [c_void_p] * 5 + [c_ll, c_int, c_float, c_void_p])
 native.declare("ubm_pole_prefill_state", [c_void_p] * 4 + [c_int] * 5 + [c_void_p])
 native.declare("ubm_fft_pad_transpose", [c_void_p] * 2 + [c_int] * 4 + [c_void_p])
@@ -307,8 +308,10 @@ def residual_ln(x: torch.Tensor, res: torch.Tensor, gamma: torch.Tensor, beta: O
 
 def gemv_rows(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *,
               gamma: Optional[torch.Tensor] = None, eps: float = 1e-6, w2: Optional[torch.Tensor] = None,
-              res: Optional[torch.Tensor] = None) -> torch.Tensor:
+              res: Optional[torch.Tensor] = None, wscale: Optional[float] = None) -> torch.Tensor:
     """x: bf16 [M, K] with M <= 8 (decode rows); w: bf16 [N, K] contiguous; returns bf16 [M, N] = x^ @ w.T (+ bias).
+    ``w`` may hold e4m3 values (``torch.float8_e4m3fn``, K a multiple of 16) with ``wscale`` their dequantisation
+    factor: half the bytes per output row, activations still bf16 (not with ``w2``).
 
     The rows of a decode block fold into the same launch: ``gamma`` (fp32 [K]) puts RMSNorm in front
     (x^ = rmsnorm(x) * gamma, else x^ = x); ``w2`` makes the SwiGLU form silu(x^ @ w.T) * (x^ @ w2.T); ``res``
@@ -322,6 +325,13 @@ def gemv_rows(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
     if res is not None:
         res = _bf16c(res.reshape(M, N))
     gamma = _f32(gamma)                  # a parameter in another type is converted once, not per decode step
+    if w.dtype in (torch.float8_e4m3fn, torch.uint8):
+        if w2 is not None or wscale is None or not w.is_contiguous():
+            raise ValueError("gemv_rows: e4m3 weights come with wscale, contiguous, and without w2")
+        rc = native.lib().ubm_gemv_fused_w8(native.ptr(x), native.ptr(gamma), float(eps), native.ptr(w), float(wscale),
+                                            native.ptr(bias), native.ptr(res), native.ptr(out), M, N, K, _stream(x))
+        native.check(rc, "ubm_gemv_fused_w8")
+        return out
     rc = native.lib().ubm_gemv_fused(native.ptr(x), native.ptr(gamma), float(eps), native.ptr(w), native.ptr(w2),
                                      native.ptr(bias), native.ptr(res), native.ptr(out), M, N, K, _stream(x))
     native.check(rc, "ubm_gemv_fused")
