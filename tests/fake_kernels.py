@@ -94,6 +94,9 @@ def patched(*model_modules):
         setattr(mod, name, fn)
 
     put(g, "gemm", gemm)
+    # the packing keeps the test's dtype (the library's returns bf16)
+    put(g, "pack_swiglu", lambda a, b: torch.stack([a.view(-1, 32, a.shape[1]), b.view(-1, 32, b.shape[1])], 1)
+        .reshape(2 * a.shape[0], a.shape[1]).contiguous())
     put(rows, "layernorm_rows", layernorm_rows)
     put(rows, "swiglu_rows", swiglu_rows)
     put(pair, "attention", attention)

@@ -95,13 +95,15 @@ class Transition(_Switchable):
             # other widths (the MSA track at 64, the template stack): LayerNorm rows -> one GEMM for both hidden
             # projections -> SwiGLU rows -> output GEMM with the residual in its epilogue
             from ..ops import gemm, rows
+            in_epilogue = self.hidden % 32 == 0     # silu(fc1) * fc2 formed on the accumulator of one product
             if self._packed is None:
-                self._packed = (torch.cat([self.fc1.weight, self.fc2.weight], 0).detach().to(torch.bfloat16).contiguous(),
-                                self.fc3.weight.detach().to(torch.bfloat16).contiguous())
+                w12 = gemm.pack_swiglu(self.fc1.weight.detach(), self.fc2.weight.detach()) if in_epilogue else \
+                    torch.cat([self.fc1.weight, self.fc2.weight], 0).detach().to(torch.bfloat16).contiguous()
+                self._packed = (w12, self.fc3.weight.detach().to(torch.bfloat16).contiguous())
             w12, w3 = self._packed
             x2 = x.reshape(-1, self.dim).contiguous()
             n = rows.layernorm_rows(x2, self.norm.weight, self.norm.bias, self.norm.eps)
-            h = rows.swiglu_rows(gemm.gemm(n, w12))
+            h = gemm.gemm(n, w12, act="swiglu") if in_epilogue else rows.swiglu_rows(gemm.gemm(n, w12))
             y = gemm.gemm(h, w3, residual=x2 if residual and self.out_dim == self.dim else None)
             return y.view(*x.shape[:-1], self.out_dim)
         return R.transition(x, self.norm.weight, self.norm.bias, self.fc1.weight, self.fc2.weight, self.fc3.weight,

@@ -153,6 +153,11 @@ class EncoderBlock(nn.Module):
                  "q_ln": self.q_ln.weight.detach().float(), "q_ln_scaled": self.q_ln.weight.detach().float() * qs}
             if self.cfg.family == "gpnstar":
                 p.update(wq_c=_bf16(self.wq_c.weight), wkv_c=_bf16(self.wkv_c.weight), wo_c=_bf16(self.wo_c.weight))
+            ffn = self.w1.weight.shape[0] // 2
+            if ffn % 32 == 0:
+                # gate | value rows interleaved in groups of 32: silu(a) * b is formed on the GEMM's accumulator
+                from ..ops import gemm
+                p["w1_swiglu"] = gemm.pack_swiglu(self.w1.weight.detach()[:ffn], self.w1.weight.detach()[ffn:])
             self._packed = p
         return self._packed
 
@@ -187,7 +192,10 @@ class EncoderBlock(nn.Module):
             oc = seq.column_attention(qc, kv[:, :, 0], kv[:, :, 1], clade_index, self.clade_bias)
             x2 = gemm.gemm(oc.view(T, d), p["wo_c"], residual=x2)
         n2 = rows.layernorm_rows(x2, self.ln2.weight, self.ln2.bias, cfg.eps)
-        g = rows.swiglu_rows(gemm.gemm(n2, p["w1"]))
+        if "w1_swiglu" in p:
+            g = gemm.gemm(n2, p["w1_swiglu"], act="swiglu")
+        else:
+            g = rows.swiglu_rows(gemm.gemm(n2, p["w1"]))
         return gemm.gemm(g, p["w2"], residual=x2).view(B, L, d)
 
     def forward(self, x, pos, mask=None, align=None, clade_index=None):
