@@ -1177,7 +1177,10 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_rows_kernel(
   const int warp = threadIdx.x >> 5;
   const int wpb = kGemvThreads / 32;
   const int nv = K >> 3;                                                       // 16-byte vectors per row
-  const int n_first = blockIdx.x * wpb + warp;
+  // rows are dealt to the CTAs round-robin (row n belongs to CTA n % grid), so every CTA - and with it every SM -
+  // gets the same number of rows to within one; dealing them warp-major left the CTAs of the last round with a
+  // third more work than the rest (or, for a matrix with fewer rows than warps, some SMs with one CTA of two)
+  const int n_first = warp * gridDim.x + blockIdx.x;
   // the first weight row of this warp starts towards L2 while x^ is staged
   if (n_first < N) {
     const char* p0 = reinterpret_cast<const char*>(w) + static_cast<long long>(n_first) * K * wbytes;
@@ -1352,8 +1355,8 @@ int launch_gemv(const __nv_bfloat16* x, const float* gamma, float eps, const __n
   if (smem > static_cast<size_t>(kGemvMaxSmem)) return UBM_ERR_ARGUMENT;
   const int wpb = kGemvThreads / 32;
   const int per_sm = smem > 100 * 1024 ? 1 : 2;
-  int grid = (N + wpb - 1) / wpb;
-  if (grid > sm_count() * per_sm) grid = sm_count() * per_sm;
+  int grid = sm_count() * per_sm;
+  if (grid > N) grid = N;
   // launched so that its weight prefetch may overlap the tail of the previous kernel in the stream (see the kernel)
   static const bool pdl = [] {
     const char* e = getenv("UBM_PDL");
