@@ -1177,10 +1177,9 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_rows_kernel(
   const int warp = threadIdx.x >> 5;
   const int wpb = kGemvThreads / 32;
   const int nv = K >> 3;                                                       // 16-byte vectors per row
-  // rows are dealt to the CTAs round-robin (row n belongs to CTA n % grid), so every CTA - and with it every SM -
-  // gets the same number of rows to within one; dealing them warp-major left the CTAs of the last round with a
-  // third more work than the rest (or, for a matrix with fewer rows than warps, some SMs with one CTA of two)
-  const int n_first = warp * gridDim.x + blockIdx.x;
+  // rows go to the warps CTA by CTA (dealing them round-robin over the CTAs for an even row count per SM measured
+  // slower: 27.5 against 26.7 us for 4096 -> 12288 and 4.2 against 3.5 ms for the whole decode step)
+  const int n_first = blockIdx.x * wpb + warp;
   // the first weight row of this warp starts towards L2 while x^ is staged
   if (n_first < N) {
     const char* p0 = reinterpret_cast<const char*>(w) + static_cast<long long>(n_first) * K * wbytes;
@@ -1355,8 +1354,8 @@ int launch_gemv(const __nv_bfloat16* x, const float* gamma, float eps, const __n
   if (smem > static_cast<size_t>(kGemvMaxSmem)) return UBM_ERR_ARGUMENT;
   const int wpb = kGemvThreads / 32;
   const int per_sm = smem > 100 * 1024 ? 1 : 2;
-  int grid = sm_count() * per_sm;
-  if (grid > N) grid = N;
+  int grid = (N + wpb - 1) / wpb;
+  if (grid > sm_count() * per_sm) grid = sm_count() * per_sm;
   // launched so that its weight prefetch may overlap the tail of the previous kernel in the stream (see the kernel)
   static const bool pdl = [] {
     const char* e = getenv("UBM_PDL");
