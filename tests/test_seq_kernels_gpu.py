@@ -325,6 +325,24 @@ def test_evo2_fp8_input_projections_stay_close_to_the_bf16_prefill():
     assert 0.0 < rel < 8e-2, rel                                    # differs (8-bit operands) but stays close
 
 
+def test_evo2_speculative_decoding_on_the_kernel_path_returns_the_greedy_tokens():
+    """Multi-token continuation (``extend`` / ``commit`` through the folded block with several rows) and the draft's
+    single-token steps against plain greedy decoding of the target."""
+    from uplifting_biomolecular_modeling_b200.models import evo2
+    from uplifting_biomolecular_modeling_b200.ops import native
+    target = evo2.build("evo2_tiny", device="cuda", dtype=torch.bfloat16, seed=11, n_heads=1)
+    draft = evo2.build("evo2_tiny", device="cuda", dtype=torch.bfloat16, seed=12, n_heads=1, n_layers=2, attn_layers=())
+    target.set_impl("fused")
+    draft.set_impl("fused")
+    tok = torch.randint(0, target.cfg.vocab, (1, 48), device="cuda")
+    want = target.generate(tok, 10, graph=False)
+    got, stats = target.generate_speculative(draft, tok, 10, k=3)
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "evo2 speculative")
+    assert torch.equal(got, want), (got, want)
+    assert stats["proposed"] >= stats["accepted"] >= 0 and stats["rounds"] >= 1
+
+
 def test_per_channel_vectors_given_in_bf16():
     """Per-channel vectors that need a conversion are converted into tensors that outlive the launch."""
     from uplifting_biomolecular_modeling_b200.ops import reference as R, seq
