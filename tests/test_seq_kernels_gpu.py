@@ -34,6 +34,22 @@ def test_fir_gate3(K, tail):
     _close(x2, x2r)
 
 
+@pytest.mark.parametrize("K,L,d", [(128, 1100, 96), (40, 513, 32), (17, 64, 40), (128, 4096, 256)])
+def test_fir_inner_gate_tiled_direct_convolution(K, L, d):
+    """Filters of more than 8 taps over a sequence without a tail take the shared-memory tiled kernel (taps padded to
+    16, ragged channel and position tiles)."""
+    from uplifting_biomolecular_modeling_b200.ops import reference as R, seq
+    g = torch.Generator(device="cuda").manual_seed(24)
+    B = 2
+    u = torch.randn(B, L, d, device="cuda", generator=g).bfloat16()
+    x2 = torch.randn(B, L, d, device="cuda", generator=g).bfloat16()
+    h = torch.randn(d, K, device="cuda", generator=g) * K ** -0.5
+    D = torch.randn(d, device="cuda", generator=g)
+    out = seq.fir_inner_gate(u, seq.taps_major(h), D, x2, None)
+    _close(out, R.fir_inner_gate(u, h, D, x2, None))
+    _close(seq.fir_inner_gate(u, seq.taps_major(h), D, None, None), R.fir_inner_gate(u, h, D, None, None))
+
+
 @pytest.mark.parametrize("K,tail", [(7, False), (7, True), (40, False), (40, True)])
 def test_fir_inner_gate(K, tail):
     from uplifting_biomolecular_modeling_b200.ops import reference as R, seq

@@ -496,6 +496,89 @@ __global__ void __launch_bounds__(128) fir_inner_gate_long_kernel(const __nv_bfl
   }
 }
 
+// The same operator for filters of tens to hundreds of taps over a long sequence (the 128-tap medium filter of a
+// prefill), as a direct convolution on the FMA pipes: 17 G multiply-adds per operator at the 7B shape, against
+// three FFT-sized passes over fp32 copies of the sequence.  A CTA owns 32 channels x 512 positions: the input
+// tile with its halo (bf16) and the taps (fp32, zero-padded to a multiple of 16) sit in shared memory; a thread
+// owns one channel and runs of 16 positions with 16 accumulators, and walks the taps 16 at a time over a
+// 31-value register window (out[p] += h[kb + q] * W[p - q + 15], all indices static), so one shared-memory load
+// feeds eight multiply-adds.  No tail: positions before the sequence are zero.
+constexpr int kFtCh = 32;       // channels per CTA
+constexpr int kFtPos = 512;     // positions per CTA
+constexpr int kFtRun = 16;      // positions per thread run = taps per block
+
+__global__ void __launch_bounds__(128) fir_inner_gate_tiled_kernel(const __nv_bfloat16* __restrict__ u,
+                                                                   const float* __restrict__ ht, int K, int Kpad,
+                                                                   const float* __restrict__ D,
+                                                                   const __nv_bfloat16* __restrict__ x2,
+                                                                   __nv_bfloat16* __restrict__ out, int L, int d) {
+  extern __shared__ __align__(16) unsigned char ft_smem[];
+  float* sh = reinterpret_cast<float*>(ft_smem);                                  // [Kpad][32]
+  __nv_bfloat16* su = reinterpret_cast<__nv_bfloat16*>(sh + Kpad * kFtCh);        // [Kpad + 512][32], row 0 = t0 - Kpad
+  const int c0 = blockIdx.x * kFtCh;
+  const int t0 = blockIdx.y * kFtPos;
+  const int b = blockIdx.z;
+  const __nv_bfloat16* ub = u + static_cast<long long>(b) * L * d;
+  for (int i = threadIdx.x; i < Kpad * kFtCh; i += 128) {
+    const int k = i / kFtCh, c = c0 + (i % kFtCh);
+    sh[i] = (k < K && c < d) ? ht[static_cast<long long>(k) * d + c] : 0.f;
+  }
+  // 16-byte loads of 8 channels: four per row of the tile
+  for (int i = threadIdx.x; i < (Kpad + kFtPos) * (kFtCh / 8); i += 128) {
+    const int row = i / (kFtCh / 8), c8 = (i % (kFtCh / 8)) * 8;
+    const int l = t0 - Kpad + row;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (l >= 0 && l < L && c0 + c8 < d) v = *reinterpret_cast<const uint4*>(ub + static_cast<long long>(l) * d + c0 + c8);
+    *reinterpret_cast<uint4*>(su + row * kFtCh + c8) = v;
+  }
+  __syncthreads();
+  const int c = threadIdx.x % kFtCh;
+  const int grp = threadIdx.x / kFtCh;                                            // 4 groups of position runs
+  if (c0 + c >= d) return;
+  const float dv = D[c0 + c];
+  for (int run = grp; run < kFtPos / kFtRun; run += 4) {
+    const int l0 = t0 + run * kFtRun;
+    if (l0 >= L) break;
+    float acc[kFtRun];
+#pragma unroll
+    for (int p = 0; p < kFtRun; ++p) acc[p] = 0.f;
+    // W[i] = u[l0 - kb - 15 + i], i = 0..30; tile row of position l is l - t0 + Kpad
+    float W[2 * kFtRun - 1];
+    const int base = run * kFtRun + Kpad - (kFtRun - 1);                          // row of W[0] at kb = 0
+#pragma unroll
+    for (int i = 0; i < 2 * kFtRun - 1; ++i) W[i] = __bfloat162float(su[(base + i) * kFtCh + c]);
+    for (int kb = 0; kb < Kpad; kb += kFtRun) {
+      float h[kFtRun];
+#pragma unroll
+      for (int q = 0; q < kFtRun; ++q) h[q] = sh[(kb + q) * kFtCh + c];
+#pragma unroll
+      for (int q = 0; q < kFtRun; ++q)
+#pragma unroll
+        for (int p = 0; p < kFtRun; ++p) acc[p] = fmaf(h[q], W[p - q + kFtRun - 1], acc[p]);
+      if (kb + kFtRun < Kpad) {
+        // the next 16 taps look 16 positions further back: the low half of the window moves up, 16 values come in
+#pragma unroll
+        for (int i = 2 * kFtRun - 2; i >= kFtRun; --i) W[i] = W[i - kFtRun];
+        const int nb = base - (kb + kFtRun);
+#pragma unroll
+        for (int i = 0; i < kFtRun; ++i) W[i] = __bfloat162float(su[(nb + i) * kFtCh + c]);
+      }
+    }
+#pragma unroll
+    for (int p = 0; p < kFtRun; ++p) {
+      const int l = l0 + p;
+      if (l < L) {
+        const long long o = (static_cast<long long>(b) * L + l) * d + c0 + c;
+        const float cur = __bfloat162float(su[(run * kFtRun + p + Kpad) * kFtCh + c]);
+        const float conv = __bfloat162float(__float2bfloat16(acc[p]));
+        const float yy = __bfloat162float(__float2bfloat16(conv + cur * dv));
+        const float g = x2 == nullptr ? 1.f : __bfloat162float(x2[o]);
+        out[o] = __float2bfloat16(g * yy);
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------ FFT-conv epilogue
 // y: fp32 [B][d][n] (channel-major, the inverse FFT's layout; first L of n samples used), u, x2: bf16 [B][L][d].
 // out[b][l][c] = x2 * (bf16(y[b][c][l]) + D[c] * u).  A 32 x 32 tile goes through shared memory so that both the
@@ -970,6 +1053,16 @@ extern "C" int ubm_fir_inner_gate(const void* u, const void* ht, const void* D, 
       default: UBM_FIG(8); break;
     }
 #undef UBM_FIG
+  } else if (tt == nullptr && L >= 64 && K <= 512 && B <= 65535) {
+    const int Kpad = (K + kFtRun - 1) / kFtRun * kFtRun;
+    const size_t smem = static_cast<size_t>(Kpad) * kFtCh * sizeof(float) +
+                        static_cast<size_t>(Kpad + kFtPos) * kFtCh * sizeof(__nv_bfloat16);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(fir_inner_gate_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return UBM_ERR_LAUNCH;
+    const dim3 grid((d + kFtCh - 1) / kFtCh, (L + kFtPos - 1) / kFtPos, B);
+    fir_inner_gate_tiled_kernel<<<grid, 128, smem, st>>>(uu, hh, K, Kpad, dd, xx, oo, L, d);
   } else {
     const long long total = static_cast<long long>(B) * L * (d / 8);
     fir_inner_gate_long_kernel<<<seq_grid(total, 128), 128, 0, st>>>(uu, hh, K, dd, xx, tt, oo, B, L, d);
