@@ -506,8 +506,9 @@ __global__ void __launch_bounds__(128) fir_inner_gate_long_kernel(const __nv_bfl
 constexpr int kFtCh = 32;       // channels per CTA
 constexpr int kFtPos = 512;     // positions per CTA
 constexpr int kFtRun = 16;      // positions per thread run = taps per block
+constexpr int kFtThreads = 256; // eight warps, each a group of position runs
 
-__global__ void __launch_bounds__(128) fir_inner_gate_tiled_kernel(const __nv_bfloat16* __restrict__ u,
+__global__ void __launch_bounds__(kFtThreads, 2) fir_inner_gate_tiled_kernel(const __nv_bfloat16* __restrict__ u,
                                                                    const float* __restrict__ ht, int K, int Kpad,
                                                                    const float* __restrict__ D,
                                                                    const __nv_bfloat16* __restrict__ x2,
@@ -519,12 +520,12 @@ __global__ void __launch_bounds__(128) fir_inner_gate_tiled_kernel(const __nv_bf
   const int t0 = blockIdx.y * kFtPos;
   const int b = blockIdx.z;
   const __nv_bfloat16* ub = u + static_cast<long long>(b) * L * d;
-  for (int i = threadIdx.x; i < Kpad * kFtCh; i += 128) {
+  for (int i = threadIdx.x; i < Kpad * kFtCh; i += kFtThreads) {
     const int k = i / kFtCh, c = c0 + (i % kFtCh);
     sh[i] = (k < K && c < d) ? ht[static_cast<long long>(k) * d + c] : 0.f;
   }
   // 16-byte loads of 8 channels: four per row of the tile
-  for (int i = threadIdx.x; i < (Kpad + kFtPos) * (kFtCh / 8); i += 128) {
+  for (int i = threadIdx.x; i < (Kpad + kFtPos) * (kFtCh / 8); i += kFtThreads) {
     const int row = i / (kFtCh / 8), c8 = (i % (kFtCh / 8)) * 8;
     const int l = t0 - Kpad + row;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -533,15 +534,22 @@ __global__ void __launch_bounds__(128) fir_inner_gate_tiled_kernel(const __nv_bf
   }
   __syncthreads();
   const int c = threadIdx.x % kFtCh;
-  const int grp = threadIdx.x / kFtCh;                                            // 4 groups of position runs
+  const int grp = threadIdx.x / kFtCh;                                            // one warp per group of position runs
   if (c0 + c >= d) return;
   const float dv = D[c0 + c];
-  for (int run = grp; run < kFtPos / kFtRun; run += 4) {
+  for (int run = grp; run < kFtPos / kFtRun; run += kFtThreads / kFtCh) {
     const int l0 = t0 + run * kFtRun;
     if (l0 >= L) break;
     float acc[kFtRun];
 #pragma unroll
     for (int p = 0; p < kFtRun; ++p) acc[p] = 0.f;
+    // the gate values of this run are requested now and used behind the tap loop
+    __nv_bfloat16 gate[kFtRun];
+    if (x2 != nullptr) {
+#pragma unroll
+      for (int p = 0; p < kFtRun; ++p)
+        gate[p] = l0 + p < L ? x2[(static_cast<long long>(b) * L + l0 + p) * d + c0 + c] : __float2bfloat16(0.f);
+    }
     // W[i] = u[l0 - kb - 15 + i], i = 0..30; tile row of position l is l - t0 + Kpad
     float W[2 * kFtRun - 1];
     const int base = run * kFtRun + Kpad - (kFtRun - 1);                          // row of W[0] at kb = 0
@@ -572,7 +580,7 @@ __global__ void __launch_bounds__(128) fir_inner_gate_tiled_kernel(const __nv_bf
         const float cur = __bfloat162float(su[(run * kFtRun + p + Kpad) * kFtCh + c]);
         const float conv = __bfloat162float(__float2bfloat16(acc[p]));
         const float yy = __bfloat162float(__float2bfloat16(conv + cur * dv));
-        const float g = x2 == nullptr ? 1.f : __bfloat162float(x2[o]);
+        const float g = x2 == nullptr ? 1.f : __bfloat162float(gate[p]);
         out[o] = __float2bfloat16(g * yy);
       }
     }
@@ -1062,7 +1070,7 @@ extern "C" int ubm_fir_inner_gate(const void* u, const void* ht, const void* D, 
                              static_cast<int>(smem)) != cudaSuccess)
       return UBM_ERR_LAUNCH;
     const dim3 grid((d + kFtCh - 1) / kFtCh, (L + kFtPos - 1) / kFtPos, B);
-    fir_inner_gate_tiled_kernel<<<grid, 128, smem, st>>>(uu, hh, K, Kpad, dd, xx, oo, L, d);
+    fir_inner_gate_tiled_kernel<<<grid, kFtThreads, smem, st>>>(uu, hh, K, Kpad, dd, xx, oo, L, d);
   } else {
     const long long total = static_cast<long long>(B) * L * (d / 8);
     fir_inner_gate_long_kernel<<<seq_grid(total, 128), 128, 0, st>>>(uu, hh, K, dd, xx, tt, oo, B, L, d);
