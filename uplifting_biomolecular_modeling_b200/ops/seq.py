@@ -351,6 +351,8 @@ def decode_attention(qkv: torch.Tensor, pos: torch.Tensor, kc: torch.Tensor, vc:
         raise ValueError("decode_attention: bf16 caches [B, Lmax, H, 128] and qkv [B, 3*H*128]")
     if pos.dtype != torch.int64 or pos.numel() != 1 or pos.device != qkv.device:
         raise ValueError("decode_attention: pos is an int64 device tensor with one element")
+    # one split per 1024 cache rows (sizing the split count for four full waves of CTAs instead measured slower:
+    # 137 against 130 us at 33000 keys, 58 against 48 us at 8192)
     splits = max(1, min(64, (Lmax + 1023) // 1024))
     q_rot = torch.empty((B, H, hd), dtype=torch.bfloat16, device=qkv.device)
     part = torch.empty((B, H, splits, hd + 2), dtype=torch.float32, device=qkv.device)
