@@ -486,7 +486,7 @@ class SwiGLU(nn.Module):
             # interleaved weight is a second copy of the two matrices, kept until either is written again)
             from ..ops import gemm
             x2 = x.reshape(-1, x.shape[-1])
-            h = gemm.gemm(x2 if x2.is_contiguous() else x2.contiguous(), self._packed(), act="swiglu")
+            h = gemm.gemm(x2 if x2.is_contiguous() else x2.contiguous(), self._swiglu_weight(), act="swiglu")
             return lin(self.l3, h.view(*x.shape[:-1], h.shape[-1]))
         g, up = lin(self.l1, x), lin(self.l2, x)
         if _fusable(self, g):
@@ -494,7 +494,7 @@ class SwiGLU(nn.Module):
             return lin(self.l3, seq.silu_mul(g, up))
         return lin(self.l3, F.silu(g) * up)
 
-    def _packed(self) -> torch.Tensor:
+    def _swiglu_weight(self) -> torch.Tensor:
         ver = tuple((p._version, p.data_ptr(), tuple(p.shape)) for p in (self.l1.weight, self.l2.weight))
         ent = self.__dict__.get("_packed_w")
         if ent is None or ent[0] != ver:
