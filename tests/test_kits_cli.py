@@ -150,6 +150,28 @@ def test_partial_checkpoint_is_not_active(tmp_path):
     assert man["checkpoint"]["matched"] == 1 and man["checkpoint"]["missing"]
 
 
+def test_sequence_kit_checkpoint_is_loaded_strictly(tmp_path):
+    """The language-model kits take --checkpoint too: a full state loads and changes the score, a partial one is
+    NOT ACTIVE with exit 3 unless --allow-partial."""
+    import torch
+    from uplifting_biomolecular_modeling_b200.models import evo2
+    m = evo2.build("evo2_tiny", seed=123)
+    torch.save(m.state_dict(), tmp_path / "full.pt")
+    k0 = next(iter(m.state_dict()))
+    torch.save({k0: m.state_dict()[k0]}, tmp_path / "one.pt")
+    base_args = ["kits/evo2/run.sh", "score", "--mode", "off", "--model_config", "evo2_tiny", "--prompt", "ACGTACGTAC"]
+    r0 = _run(base_args)
+    r1 = _run(base_args + ["--checkpoint", str(tmp_path / "full.pt")])
+    assert r0.returncode == 0 and r1.returncode == 0, r1.stderr[-1500:]
+    assert "[evo2-opt] WEIGHTS" in r1.stderr and "missing=0" in r1.stderr and "unexpected=0" in r1.stderr
+    score = lambda r: [l for l in r.stderr.splitlines() if " DONE " in l][0].split("score=")[1].split()[0]  # noqa: E731
+    assert score(r0) != score(r1)                     # other weights (seed 123 against the kit's seed), other score
+    r2 = _run(base_args + ["--checkpoint", str(tmp_path / "one.pt")])
+    assert r2.returncode == 3 and "NOT ACTIVE" in r2.stderr and "missing" in r2.stderr
+    r3 = _run(base_args + ["--checkpoint", str(tmp_path / "one.pt"), "--allow-partial"])
+    assert r3.returncode == 0 and "matched=1" in r3.stderr
+
+
 def test_full_checkpoint_loads_cold_and_reproduces_the_weights(tmp_path):
     """With a checkpoint that carries every parameter the model is built without its random initialisation (the fillers
     are skipped and counted) and the prediction equals the one of the model that wrote the checkpoint."""

@@ -353,6 +353,23 @@ def _run_lm(spec, act, args, allow_partial, family) -> int:
     model = lm.build(family, spec.config if args.model_config is None else args.model_config, device=device,
                      mode="off", seed=args.seed, kit=spec.name, specdec=getattr(args, "specdec", 0))
     model.mode = act.mode
+    ckpt = getattr(args, "checkpoint", None) or _weights_file(getattr(args, "weights", None))
+    if ckpt:
+        # loaded before the levers run, so that packed / quantised weights are made from the loaded parameters; a
+        # checkpoint that does not fit ends the run by name (no run on partly random weights unless asked for)
+        from ..models import weights
+        try:
+            rep = weights.load_checkpoint(model.model, ckpt, strict=not allow_partial)
+        except (ValueError, OSError) as e:
+            act.refuse(f"checkpoint {ckpt}: {e}")
+            return report.EXIT_NOT_ACTIVE
+        act.manifest_extra = dict(getattr(act, "manifest_extra", {}) or {})
+        act.manifest_extra["checkpoint"] = {"path": ckpt, "matched": rep.matched, "missing": rep.missing[:50],
+                                             "unexpected": rep.unexpected[:50],
+                                             "shape_mismatch": rep.shape_mismatch[:50]}
+        report.emit(report.line(spec.tag, "WEIGHTS", ("path", ckpt), ("matched", rep.matched),
+                                ("missing", len(rep.missing)), ("unexpected", len(rep.unexpected)),
+                                ("shape_mismatch", len(rep.shape_mismatch)), ("init_skipped", 0)))
     try:
         act.apply(model)
     except base.ActivationError:
