@@ -172,6 +172,22 @@ def test_sequence_kit_checkpoint_is_loaded_strictly(tmp_path):
     assert r3.returncode == 0 and "matched=1" in r3.stderr
 
 
+def test_sequence_kit_reads_fasta_input_and_refuses_a_missing_file(tmp_path):
+    fa = tmp_path / "two.fa"
+    fa.write_text(">first some description\nACGTACGT\nACGT\n>second\nTTTTACGTAA\n")
+    out = tmp_path / "o"
+    r = _run(["kits/evo2/run.sh", "score", "--mode", "off", "--model_config", "evo2_tiny", "--input", str(fa),
+              "--out_dir", str(out)])
+    assert r.returncode == 0, r.stderr[-1500:]
+    res = json.load(open(out / "score.json"))
+    assert res["records"] == 2 and [p["id"] for p in res["per_record"]] == ["first", "second"]
+    assert res["per_record"][0]["tokens"] == 12 and res["per_record"][1]["tokens"] == 10
+    assert abs(res["mean_score"] - sum(p["score"] for p in res["per_record"]) / 2) < 1e-9
+    r = _run(["kits/evo2/run.sh", "score", "--mode", "off", "--model_config", "evo2_tiny", "--input",
+              str(tmp_path / "absent.fa")])
+    assert r.returncode == 2 and "USAGE" in r.stderr and "no_such_file" in r.stderr.replace(" ", "_")
+
+
 def test_full_checkpoint_loads_cold_and_reproduces_the_weights(tmp_path):
     """With a checkpoint that carries every parameter the model is built without its random initialisation (the fillers
     are skipped and counted) and the prediction equals the one of the model that wrote the checkpoint."""

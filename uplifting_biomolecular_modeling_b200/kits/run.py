@@ -242,6 +242,36 @@ def _input_items(args):
     return list(zip(names, paths))
 
 
+def _sequence_records(path):
+    """``--input`` of the sequence kits: FASTA records (``>name`` lines) or one sequence per line -> [(name, sequence)];
+    [] without a path.  A missing or empty file is an input error (exit 2), never a silent default prompt."""
+    if not path:
+        return []
+    if not os.path.isfile(path):
+        raise InputError(f"--input {path}: no such file")
+    out, name, buf = [], None, []
+    fasta = False
+    with open(path) as f:
+        for line in f:
+            line = line.strip()
+            if not line:
+                continue
+            if line.startswith(">"):
+                fasta = True
+                if buf:
+                    out.append((name or f"record{len(out)}", "".join(buf)))
+                name, buf = line[1:].split()[0] if len(line) > 1 else None, []
+            elif fasta:
+                buf.append(line)
+            else:
+                out.append((f"line{len(out)}", line))
+    if buf:
+        out.append((name or f"record{len(out)}", "".join(buf)))
+    if not out:
+        raise InputError(f"--input {path}: holds no sequence")
+    return out
+
+
 def _weights_file(weights_dir):
     """``--weights D``: the one checkpoint file in D (``*.ckpt`` / ``*.pt`` / ``*.safetensors``); None without D.
     Several candidates are an error of the call, reported by the loader as an unreadable path."""
@@ -376,9 +406,22 @@ def _run_lm(spec, act, args, allow_partial, family) -> int:
         return report.EXIT_NOT_ACTIVE
     act.register_exit()
     protein = family == "protein_lm" and spec.name != "gpnstar"
+    try:
+        records = _sequence_records(getattr(args, "input", None))
+    except InputError as e:
+        report.emit(report.line(spec.tag, "USAGE", ("error", "input"), ("detail", report.token(str(e))[:200])))
+        return act.finish(report.EXIT_USAGE, allow_partial, None)
     prompt = args.prompt or ("MKTAYIAKQRQISFVKSHFSRQLEERLGLIEVQ" * 2 if protein else "ACGT" * 16)
     t0 = time.time()
-    res = model.run(args.verb, prompt, max_new_tokens=args.max_new_tokens)
+    if records:
+        # --input: a FASTA (or one sequence per line) file; every record is run, the first one's result leads
+        per = [dict(model.run(args.verb, seq, max_new_tokens=args.max_new_tokens), id=name) for name, seq in records]
+        res = dict(per[0], records=len(per))
+        if len(per) > 1 and all("score" in r for r in per):
+            res["mean_score"] = sum(r["score"] for r in per) / len(per)
+        res["per_record"] = [{k: v for k, v in r.items() if isinstance(v, (int, float, str))} for r in per]
+    else:
+        res = model.run(args.verb, prompt, max_new_tokens=args.max_new_tokens)
     report.emit(report.line(spec.tag, "DONE", ("seconds", round(time.time() - t0, 3)), ("verb", args.verb),
                             *[(k, v) for k, v in res.items() if isinstance(v, (int, float, str))]))
     if args.out_dir:
