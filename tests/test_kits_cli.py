@@ -100,6 +100,17 @@ def test_pred_off_on_cpu_writes_outputs_and_manifest(tmp_path):
     assert (out / "prediction.pt").exists()
 
 
+def test_lever_descriptors_can_be_written_on_a_lever_line():
+    """Strategy ids are catalogued and no value that goes on a LEVER line holds a blank (the line grammar refuses it
+    at the moment the lever engages, which is on the GPU for most of them)."""
+    from uplifting_biomolecular_modeling_b200.core import strategies
+    from uplifting_biomolecular_modeling_b200.kits import levers
+    for name, lv in levers.LEVERS.items():
+        assert strategies.is_known(lv.strategy), (name, lv.strategy)
+        for field in (name, lv.strategy, lv.impl):
+            assert field and " " not in str(field), (name, field)
+
+
 def test_no_lever_is_a_no_op():
     """Every lever of the table has an ``apply`` that changes the object it is given (or raises): a table of names
     that do nothing cannot come back."""

@@ -221,7 +221,7 @@ LEVERS: Dict[str, Lever] = {l.name: l for l in [
                                             "step and every later prediction.")),
     Lever("graph_verify", "F2.graph_capture", "capture.graphs.verify", needs_gpu=True, apply=_graph_verify),
     Lever("trunk_graph", "F2.graph_capture", "capture.graphs.GraphCache", needs_gpu=True, apply=_trunk_graph),
-    Lever("chunk_pair_ops", "F5.memory", "models.pairformer row blocks", apply=_chunk_pair_ops),
+    Lever("chunk_pair_ops", "F5.memory", "models.pairformer.row_blocks", apply=_chunk_pair_ops),
     Lever("release_intermediates", "F5.memory", "api.Predictor.release", apply=_release),
     Lever("park_pair_init", "F5.memory", "mem.offload.HostPark", apply=_park_pair_init),
     Lever("expandable_segments", "F5.memory", "mem.allocator", apply=_expandable, droppable=True),
@@ -230,7 +230,7 @@ LEVERS: Dict[str, Lever] = {l.name: l for l in [
     Lever("kernel_path", "F1.kernel_fusion", "rows+gemm+seq_sm100@1", needs_gpu=True, apply=_kernel_path),
     Lever("decode_graph", "F2.graph_capture", "models.evo2.generate", needs_gpu=True, apply=_decode_graph),
     Lever("forward_graph", "F2.graph_capture", "capture.pool.GraphPool", needs_gpu=True, apply=_forward_graph),
-    Lever("fp8_input_proj", "F4.precision", "gemm_sm100 kind::f8f6f4 + seq_sm100 rmsnorm_fp8@1", needs_gpu=True,
+    Lever("fp8_input_proj", "F4.precision", "gemm_sm100.f8f6f4+seq_sm100.rmsnorm_fp8@1", needs_gpu=True,
           apply=_fp8_input_proj, droppable=True),
     Lever("tp_fused", "F7.tensor_parallel", "parallel.tp", needs_gpu=True, apply=_tp_fused, droppable=True),
 ]}
