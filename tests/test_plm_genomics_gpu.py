@@ -104,6 +104,22 @@ def test_track_model_fused_vs_reference(name):
         _close(got, want, 4e-2)
 
 
+@pytest.mark.parametrize("kit", ["enformer", "chrombpnet", "borzoi"])
+def test_forward_graph_lever_replays_the_track_forward(kit):
+    from uplifting_biomolecular_modeling_b200.kits import levers
+    from uplifting_biomolecular_modeling_b200.models import lm
+    from uplifting_biomolecular_modeling_b200.ops import native
+    r = lm.build("genomic_track", "lm", device="cuda", kit=kit)
+    want = r.run("predict", "ACGTTGCA" * 8)
+    levers.LEVERS["forward_graph"].apply(r)
+    got = [r.run("predict", "ACGTTGCA" * 8) for _ in range(4)]
+    torch.cuda.synchronize()
+    native.raise_on_status("cuda", "forward graph")
+    assert all(abs(g["score"] - want["score"]) <= 1e-3 * max(1.0, abs(want["score"])) for g in got), (want, got)
+    assert r.graph_pool.census()["score_forward"]["replays"] >= 2
+    assert r.last_tracks is not None and torch.isfinite(r.last_tracks.float()).all()
+
+
 @pytest.mark.parametrize("family,kit", [("evo2", "evo2"), ("protein_lm", "esmc")])
 def test_forward_graph_lever_replays_the_score_of_a_recurring_shape(family, kit):
     """Second sighting of a shape is captured, the third call replays; every call returns the eager score."""

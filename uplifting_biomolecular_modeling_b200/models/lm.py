@@ -73,7 +73,12 @@ class _TrackRunner(_Runner):
         text = (prompt * (need // max(1, len(prompt)) + 1))[:need]
         x = genomics.one_hot_dna(text, self.device, next(self.model.parameters()).dtype)
         with torch.no_grad():
-            out = self.model(x)
+            if self.forward_graphs is not None and x.is_cuda:
+                # the window length is fixed, so every call after the first has the same shape: captured at the second
+                # sighting, replayed afterwards (the ``forward_graph`` lever)
+                out = self.forward_graphs.run(lambda t: self.model(t), x)
+            else:
+                out = self.model(x)
         if cfg.family == "chrombpnet":
             prof, counts = out
             # kept for the kit's track writer: base-pair profile of the window, one column
