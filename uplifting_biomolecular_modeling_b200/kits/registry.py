@@ -60,7 +60,11 @@ def _design(name, upstream, modes=("off", "exact", "fast"), default="fast", comm
 
 def _lm(name, upstream, family, modes=("off", "exact"), default="exact", commands=("score",), library=False,
         config="lm", n_gpu=(1,)):
-    lv = {"off": (), "exact": LM_LEVERS_EXACT, "fast": LM_LEVERS_FAST}
+    # only levers that change what this family runs: the decode graph, the tensor-parallel form and the e4m3 input
+    # projections belong to StripedHyena-2; the other sequence families take the kernel path and the forward graph
+    evo = family == "evo2"
+    lv = {"off": (), "exact": LM_LEVERS_EXACT if evo else tuple(l for l in LM_LEVERS_EXACT if l != "decode_graph"),
+          "fast": LM_LEVERS_FAST if evo else ()}
     return KitSpec(name, upstream, family, modes, default if not library else None,
                    ("install", "check") + tuple(commands), config, n_gpu, library, None, {m: lv[m] for m in modes})
 
