@@ -301,3 +301,32 @@ def test_install_places_the_pth_hook_and_the_variable_activates_in_process(tmp_p
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True,
                        env=dict(env, BOLTZ2_OPT="fast", CUDA_VISIBLE_DEVICES=""), cwd=str(tmp_path))
     assert r.returncode == 3 and "[boltz2-opt] NOT ACTIVE" in r.stderr, (r.returncode, r.stderr[-1500:])
+
+
+def test_sequence_kit_tensor_parallel_worker_on_two_gloo_ranks(tmp_path):
+    """``--n_gpu P`` of the StripedHyena-2 kit: two ranks of the worker (gloo, plain statements) return the single-
+    process score and tokens; the plan accepts several GPUs in the mode that has the tensor-parallel lever only."""
+    import sys
+    from uplifting_biomolecular_modeling_b200.models import lm
+    from uplifting_biomolecular_modeling_b200.parallel import launch
+    prompt = "ACGTTGCAACGTTTGACCA"
+    one = lm.build("evo2", "evo2_tiny", seed=0, kit="evo2")
+    want_score = one.run("score", prompt)["score"]
+    want_text = one.run("generate", prompt, 6)["text"]
+    for verb in ("score", "generate"):
+        out = tmp_path / f"{verb}.json"
+        launch.run_rank_processes(2, [sys.executable, "-m", "uplifting_biomolecular_modeling_b200.parallel.lm_worker",
+                                      "--config", "evo2_tiny", "--verb", verb, "--prompt", prompt, "--max_new_tokens",
+                                      "6", "--out", str(out)], cpu=True, run_timeout_s=240,
+                                  log_dir=str(tmp_path / f"logs_{verb}"), extra_env={"PYTHONPATH": ROOT},
+                                  echo_rank0=False)
+        res = json.load(open(out))
+        assert res["world"] == 2 and res["reduce_calls"] > 0
+        if verb == "score":
+            assert abs(res["score"] - want_score) <= 1e-4 * max(1.0, abs(want_score))
+        else:
+            assert res["text"] == want_text
+    spec = registry.get("evo2")
+    base.Activation(spec, "fast", "cli", 2, probe=_b200(), environ={}).plan()
+    with pytest.raises(base.ActivationError):
+        base.Activation(spec, "exact", "cli", 2, probe=_b200(), environ={}).plan()

@@ -115,3 +115,24 @@ def test_evo2_tensor_parallel_prefill_and_folded_decode(tmp_path):
     """StripedHyena-2 over two GPUs against one: prefill logits and decode steps through the folded decode block."""
     log = _run("tests/multigpu/evo2_tp_check.py", [192, 4], 2, tmp_path)
     assert "EVO2-TP ok world=2 tokens=192 steps=4" in log, log[-2000:]
+
+
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_evo2_kit_command_line_over_two_gpus(tmp_path):
+    """``run.sh generate --mode fast --n_gpu 2``: two ranks of the tensor-parallel worker behind the kit's surface."""
+    import json
+    import subprocess
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    prompt = "ACGTACGTACGTACGTACGTACGTACGTACGTACGT"
+    r = subprocess.run(["bash", "kits/evo2/run.sh", "generate", "--mode", "fast", "--n_gpu", "2", "--model_config",
+                        "evo2_tiny", "--prompt", prompt, "--max_new_tokens", "8", "--out_dir", str(tmp_path / "o")],
+                       capture_output=True, text=True, cwd=ROOT, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
+    assert "sharding=tensor_parallel" in r.stderr and " DONE " in r.stderr
+    res = json.load(open(tmp_path / "o" / "generate.json"))
+    assert res["world"] == 2 and res["new_tokens"] == 8 and res["reduce_calls"] > 0
+    one = subprocess.run(["bash", "kits/evo2/run.sh", "generate", "--mode", "exact", "--model_config", "evo2_tiny",
+                          "--prompt", prompt, "--max_new_tokens", "8"], capture_output=True, text=True, cwd=ROOT,
+                         env=env, timeout=600)
+    assert one.returncode == 0, one.stderr[-2000:]
+    assert f"text={res['text']}" in one.stderr, (res["text"], one.stderr[-800:])

@@ -62,7 +62,11 @@ class Activation:
         if self.n_gpu not in self.spec.n_gpu:
             raise self.refuse(f"--n_gpu {self.n_gpu} is not offered by this kit (offered: "
                               f"{','.join(map(str, self.spec.n_gpu))})")
-        if self.n_gpu > 1 and self.mode != "big":
+        if self.n_gpu > 1 and self.spec.family == "evo2":
+            # the sequence kit's multi-GPU form is tensor parallelism, a lever of its fast mode
+            if "tp_fused" not in self.table.levers(self.mode):
+                raise self.refuse("--n_gpu > 1 is a fast-mode feature of this kit (tensor parallelism reorders sums)")
+        elif self.n_gpu > 1 and self.mode != "big":
             raise self.refuse("--n_gpu > 1 is a big-mode feature (tile extents reorder sums)")
         names = list(self.table.levers(self.mode))
         if self.n_gpu == 1 and "rowpair_tp" in names:

@@ -196,13 +196,9 @@ def _fp8_input_proj(pred):
 
 
 def _tp_fused(pred):
-    """Tensor parallelism of the sequence models with the collectives fused into the GEMM kernels."""
-    import torch
-    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
-    if n < 2:
-        raise RuntimeError("single_gpu")
-    pred.tp = "fused"
-    return {"visible_gpus": n}
+    """Tensor parallelism of the sequence models with the collectives fused into the GEMM kernels.  It engages in the
+    rank processes that ``--n_gpu P`` starts (``parallel.lm_worker``); a single-process run has nothing to shard."""
+    raise RuntimeError("single_process_run_needs_--n_gpu_above_1")
 
 
 LEVERS: Dict[str, Lever] = {l.name: l for l in [

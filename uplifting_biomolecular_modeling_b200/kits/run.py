@@ -374,9 +374,51 @@ def _run_design(spec, act, args, allow_partial) -> int:
     return act.finish(0, allow_partial, args.out_dir)
 
 
+def _run_lm_sharded(spec, act, args, allow_partial) -> int:
+    """``--n_gpu P`` of the StripedHyena-2 kit: P ranks of ``parallel.lm_worker`` (tensor parallelism); the parent
+    prints ACTIVE, the result of rank 0 and EXIT."""
+    import tempfile
+    from ..parallel import launch
+    try:
+        act.levers_on = act.plan()
+    except base.ActivationError:
+        return report.EXIT_NOT_ACTIVE
+    report.emit(report.with_words(report.line(spec.tag, "ACTIVE", ("mode", act.mode), ("levers", act.levers_on),
+                                              ("source", act.source), ("n_gpu", act.n_gpu),
+                                              ("sharding", "tensor_parallel")), act.words))
+    act.register_exit()
+    out = os.path.join(args.out_dir or tempfile.mkdtemp(prefix="ubm_lm_"), f"{args.verb}.json")
+    os.makedirs(os.path.dirname(out), exist_ok=True)
+    wargs = ["--config", args.model_config or spec.config, "--verb", args.verb, "--seed", str(args.seed),
+             "--max_new_tokens", str(args.max_new_tokens), "--out", out,
+             "--fp8", "1" if "fp8_input_proj" in act.levers_on else "0"]
+    for flag, val in (("--prompt", args.prompt), ("--input", getattr(args, "input", None)),
+                      ("--checkpoint", getattr(args, "checkpoint", None) or _weights_file(getattr(args, "weights", None)))):
+        if val:
+            wargs += [flag, str(val)]
+    if allow_partial:
+        wargs += ["--allow-partial"]
+    import torch
+    t0 = time.time()
+    try:
+        launch.run_sharded(act.n_gpu, "uplifting_biomolecular_modeling_b200.parallel.lm_worker", wargs,
+                           cpu_ok=not torch.cuda.is_available(), backend=None if torch.cuda.is_available() else "gloo",
+                           echo_rank0=False)
+    except launch.RankFailed as e:
+        report.emit(report.line(spec.tag, "FAILED", ("rank", e.rank), ("rc", e.rc)))
+        sys.stderr.write(e.tail)
+        return act.finish(report.EXIT_FAIL, allow_partial, args.out_dir)
+    res = json.load(open(out))
+    report.emit(report.line(spec.tag, "DONE", ("seconds", round(time.time() - t0, 3)), ("verb", args.verb),
+                            *[(k, v) for k, v in res.items() if isinstance(v, (int, float, str))]))
+    return act.finish(0, allow_partial, args.out_dir)
+
+
 def _run_lm(spec, act, args, allow_partial, family) -> int:
     import torch
     from ..models import lm
+    if act.n_gpu > 1:
+        return _run_lm_sharded(spec, act, args, allow_partial)
     device = "cuda:0" if torch.cuda.is_available() else "cpu"
     # the model is built on its plain statements; the mode's levers then switch the kernel path, the decode graph
     # and the tensor-parallel form on, each reporting what it did
