@@ -30,6 +30,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--graph", type=int, default=1, help="1: decode step captured in a CUDA graph and replayed")
     ap.add_argument("--fp8", type=int, default=0, help="1: the input projections of the Hyena operators in e4m3 during the prefill")
+    ap.add_argument("--kernel-table", type=int, default=0, help="1: after two warm prefills, run one prefill under the torch profiler, print its kernel times by name and stop")
     ap.add_argument("--specdec", type=int, default=0, help="k > 0: also time speculative decoding with k proposals per round")
     ap.add_argument("--draft", default="evo2_1b", help="configuration of the draft model for --specdec")
     a = ap.parse_args()
@@ -56,6 +57,30 @@ def main():
         par.shard_evo2(model)
     g = torch.Generator(device=dev).manual_seed(1)
     tokens = torch.randint(0, model.cfg.vocab, (1, a.prefill), device=dev, generator=g)
+
+    if a.kernel_table:
+        # shares of one warm prefill by kernel name (torch profiler: not a timing, the timed numbers come from the
+        # CUDA events of the normal run)
+        import collections
+        import re
+        from torch.profiler import ProfilerActivity, profile
+        for _ in range(2):
+            model(tokens, [dict() for _ in model.blocks])
+        torch.cuda.synchronize(dev)
+        with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+            model(tokens, [dict() for _ in model.blocks])
+            torch.cuda.synchronize(dev)
+        agg = collections.defaultdict(lambda: [0, 0.0])
+        for ev in prof.events():
+            if ev.device_type == torch.autograd.DeviceType.CUDA:
+                k = re.sub(r"\(.*", "", re.sub(r"<.*", "", ev.name))[-70:]
+                agg[k][0] += 1
+                agg[k][1] += ev.device_time_total
+        if rank == 0:
+            print(f"KERNELS total_ms={sum(v[1] for v in agg.values()) / 1e3:.2f} prefill_tokens={a.prefill}")
+            for k, (c, t) in sorted(agg.items(), key=lambda kv: -kv[1][1])[:30]:
+                print(f"KERNELS {t / 1e3:9.2f} ms {c:5d}  {k}")
+        return
 
     def run():
         states = [dict() for _ in model.blocks]

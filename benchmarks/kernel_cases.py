@@ -6,7 +6,7 @@ Cases: ``attention`` (triangle-attention core, H=4 x D=32, rows = N), ``attentio
 16 heads x 64, 5 samples), ``trimul_proj``, ``trimul_gemm``, ``trimul_out``, ``triatt_proj``, ``transition``,
 ``out_gemm`` (the [N*N,128] x [128,128] output projection with residual), ``trimul`` (three launches),
 ``triatt`` (three launches), ``causal_attention`` (--n tokens, --heads, head dimension 128; --lib 1 = the
-library call), ``gemm_rows`` (--m --k --nn: a row GEMM with bias), ``gemv_rows`` (--m <= 8 rows, --k, --nn, --form), ``decode_attention`` (--n cached keys, --heads), ``window_attention`` (--m atoms,
+library call), ``gemm_rows`` (--m --k --nn: a row GEMM with bias), ``gemv_rows`` (--m <= 8 rows, --k, --nn, --form), ``decode_attention`` (--n cached keys, --heads), ``fir_inner_gate`` (--n positions, --k channels, --nn taps), ``window_attention`` (--m atoms,
 5 samples, 4 heads x 32).  Inputs are larger than L2 for N >= 768.  Prints one line per case with the
 mean time, the algorithmic bytes and FLOPs, and the fractions of the measured peaks in MEASURED_PEAKS.json
 (fallback 6.65 TB/s, 1.59 PFLOP/s when the file is absent).
@@ -72,7 +72,7 @@ def main():
     torch.manual_seed(0)
     r = lambda *s: torch.randn(*s, device=dev) * 0.08  # noqa: E731
     ones, zeros = torch.ones(c, device=dev), torch.zeros(c, device=dev)
-    z = torch.randn(N, N, c, device=dev).bfloat16() if a.case not in ("causal_attention", "gemm_rows", "gemv_rows", "decode_attention") else None
+    z = torch.randn(N, N, c, device=dev).bfloat16() if a.case not in ("causal_attention", "gemm_rows", "gemv_rows", "decode_attention", "fir_inner_gate") else None
     Np = pair.ceil_to(N, 8)
     st = native.status_tensor(dev)
     stream = native.current_stream(dev)
@@ -177,6 +177,17 @@ def main():
         kw = {"plain": {}, "norm": {"gamma": gamma}, "res": {"res": res}, "swiglu": {"gamma": gamma, "w2": w2}}[a.form]
         fn = lambda: seq.gemv_rows(x, wt, **kw)  # noqa: E731
         byts, flops = wt.numel() * 2 * (2 if a.form == "swiglu" else 1), 2.0 * M * K * NN
+    elif a.case == "fir_inner_gate":
+        # inner operator of a Hyena layer over --n positions x --k channels with --nn taps (128 = the medium filter:
+        # the tiled direct convolution), gate included
+        from uplifting_biomolecular_modeling_b200.ops import seq
+        Lp, ch, taps = N, a.k, a.nn
+        u = torch.randn(1, Lp, ch, device=dev).bfloat16()
+        x2 = torch.randn(1, Lp, ch, device=dev).bfloat16()
+        ht = seq.taps_major(torch.randn(ch, taps, device=dev) * taps ** -0.5)
+        Dv = torch.randn(ch, device=dev)
+        fn = lambda: seq.fir_inner_gate(u, ht, Dv, x2, None)  # noqa: E731
+        byts, flops = 3 * u.numel() * 2, 2.0 * Lp * ch * taps
     elif a.case == "decode_attention":
         # one new token against a cache of --n keys (--heads heads of 128): rotary + cache write, split-key pass, merge
         from uplifting_biomolecular_modeling_b200.ops import seq
