@@ -1,4 +1,5 @@
 """StripedHyena-2 decoder on CPU: decode steps reproduce the prefill, FFT convolution equals the FIR."""
+import pytest
 import torch
 
 from uplifting_biomolecular_modeling_b200.models import evo2
@@ -117,3 +118,34 @@ def test_oversized_filter_spectra_are_not_kept(monkeypatch):
     got = m(toks)
     assert torch.equal(got, want)
     assert all(not b.mixer.__dict__.get("_spectra") for b in m.blocks)
+
+
+def test_e4m3_weight_quantisation_bounds():
+    """Per-tensor e4m3 form of a weight: the maximum maps to 448, every value is within half a 3-bit mantissa step."""
+    from uplifting_biomolecular_modeling_b200.ops import gemm
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(64, 96, generator=g) * 0.07
+    q, dq = gemm.quantize_e4m3(w)
+    assert q.dtype == torch.float8_e4m3fn and q.shape == w.shape
+    amax = w.abs().max().item()
+    assert abs(dq * 448.0 - amax) < 1e-6 * amax
+    back = q.float() * dq
+    assert back.abs().max().item() == pytest.approx(amax, rel=1e-6)
+    assert ((back - w).abs() <= 0.0625 * w.abs() + 2.0 ** -9 * amax).all()
+
+
+def test_runner_scores_through_the_capture_site_only_when_it_may():
+    """The ``forward_graph`` site is asked for GPU inputs below the token limit; on the CPU the model scores directly."""
+    from uplifting_biomolecular_modeling_b200.models import lm
+
+    class Site:
+        calls = 0
+
+        def run(self, fn, *tensors):
+            Site.calls += 1
+            return fn(*tensors)
+
+    r = lm.build("evo2", "evo2_tiny", seed=0, kit="evo2")
+    want = r.run("score", "ACGTACGTAC")["score"]
+    r.forward_graphs = Site()
+    assert r.run("score", "ACGTACGTAC")["score"] == want and Site.calls == 0        # CPU tensors: never captured
