@@ -149,3 +149,20 @@ def test_runner_scores_through_the_capture_site_only_when_it_may():
     want = r.run("score", "ACGTACGTAC")["score"]
     r.forward_graphs = Site()
     assert r.run("score", "ACGTACGTAC")["score"] == want and Site.calls == 0        # CPU tensors: never captured
+
+
+def test_checkpoint_dry_run_against_a_meta_model(tmp_path):
+    """A launcher's check before rank processes start: names and shapes against a model that holds no memory."""
+    from uplifting_biomolecular_modeling_b200.models import weights
+    m = evo2.build("evo2_tiny", seed=3)
+    torch.save(m.state_dict(), tmp_path / "full.pt")
+    k0 = next(iter(m.state_dict()))
+    torch.save({k0: m.state_dict()[k0]}, tmp_path / "one.pt")
+    with torch.device("meta"):
+        probe = evo2.StripedHyena2(evo2.CONFIGS["evo2_tiny"])
+    rep = weights.load_checkpoint(probe, str(tmp_path / "full.pt"), strict=True, dry_run=True)
+    assert rep.complete and rep.matched == len(m.state_dict())
+    assert all(p.is_meta for p in probe.parameters())                  # nothing was written
+    with pytest.raises(ValueError, match="missing"):
+        weights.load_checkpoint(probe, str(tmp_path / "one.pt"), strict=True, dry_run=True)
+    assert weights.load_checkpoint(probe, str(tmp_path / "one.pt"), strict=False, dry_run=True).matched == 1

@@ -330,3 +330,34 @@ def test_sequence_kit_tensor_parallel_worker_on_two_gloo_ranks(tmp_path):
     base.Activation(spec, "fast", "cli", 2, probe=_b200(), environ={}).plan()
     with pytest.raises(base.ActivationError):
         base.Activation(spec, "exact", "cli", 2, probe=_b200(), environ={}).plan()
+
+
+def test_sequence_kit_sharded_launcher_checks_the_checkpoint_before_it_starts_ranks(tmp_path, capsys):
+    """The parent of ``--n_gpu P``: a fitting checkpoint goes to the ranks (gloo here), one that does not fit is
+    NOT ACTIVE with exit 3 and no rank process is started."""
+    import argparse
+    import torch
+    from uplifting_biomolecular_modeling_b200.core import report
+    from uplifting_biomolecular_modeling_b200.kits import run
+    from uplifting_biomolecular_modeling_b200.models import evo2
+    m = evo2.build("evo2_tiny", seed=5)
+    torch.save(m.state_dict(), tmp_path / "full.pt")
+    k0 = next(iter(m.state_dict()))
+    torch.save({k0: m.state_dict()[k0]}, tmp_path / "one.pt")
+    spec = registry.get("evo2")
+
+    def args(ckpt, out):
+        return argparse.Namespace(verb="score", model_config="evo2_tiny", prompt="ACGTTGCAAC", input=None, seed=0,
+                                  max_new_tokens=4, checkpoint=str(ckpt), weights=None, out_dir=str(out))
+
+    act = base.Activation(spec, "fast", "cli", 2, probe=_b200(), environ={})
+    rc = run._run_lm_sharded(spec, act, args(tmp_path / "one.pt", tmp_path / "o1"), False)
+    assert rc == report.EXIT_NOT_ACTIVE and not os.path.exists(tmp_path / "o1" / "score.json")
+    act = base.Activation(spec, "fast", "cli", 2, probe=_b200(), environ={})
+    rc = run._run_lm_sharded(spec, act, args(tmp_path / "full.pt", tmp_path / "o2"), False)
+    res = json.load(open(tmp_path / "o2" / "score.json"))
+    m.eval()
+    want = float(m.score(evo2.tokenize("ACGTTGCAAC"))[0])
+    assert res["world"] == 2 and abs(res["score"] - want) <= 1e-4 * max(1.0, abs(want))
+    err = capsys.readouterr().err
+    assert "WEIGHTS" in err and "sharding=tensor_parallel" in err and "NOT ACTIVE" in err

@@ -383,6 +383,23 @@ def _run_lm_sharded(spec, act, args, allow_partial) -> int:
         act.levers_on = act.plan()
     except base.ActivationError:
         return report.EXIT_NOT_ACTIVE
+    ckpt = getattr(args, "checkpoint", None) or _weights_file(getattr(args, "weights", None))
+    if ckpt:
+        # held against the model's names and shapes here (meta device, nothing is allocated), so that a checkpoint
+        # that does not fit is NOT ACTIVE with exit 3 before any rank starts
+        import torch
+        from ..models import evo2 as _evo2, weights
+        cfg = args.model_config or spec.config
+        try:
+            with torch.device("meta"):
+                probe = _evo2.StripedHyena2(_evo2.CONFIGS[cfg if cfg in _evo2.CONFIGS else "evo2_tiny"])
+            rep = weights.load_checkpoint(probe, ckpt, strict=not allow_partial, dry_run=True)
+        except (ValueError, OSError) as e:
+            act.refuse(f"checkpoint {ckpt}: {e}")
+            return report.EXIT_NOT_ACTIVE
+        report.emit(report.line(spec.tag, "WEIGHTS", ("path", ckpt), ("matched", rep.matched),
+                                ("missing", len(rep.missing)), ("unexpected", len(rep.unexpected)),
+                                ("shape_mismatch", len(rep.shape_mismatch)), ("init_skipped", 0)))
     report.emit(report.with_words(report.line(spec.tag, "ACTIVE", ("mode", act.mode), ("levers", act.levers_on),
                                               ("source", act.source), ("n_gpu", act.n_gpu),
                                               ("sharding", "tensor_parallel")), act.words))
@@ -392,8 +409,7 @@ def _run_lm_sharded(spec, act, args, allow_partial) -> int:
     wargs = ["--config", args.model_config or spec.config, "--verb", args.verb, "--seed", str(args.seed),
              "--max_new_tokens", str(args.max_new_tokens), "--out", out,
              "--fp8", "1" if "fp8_input_proj" in act.levers_on else "0"]
-    for flag, val in (("--prompt", args.prompt), ("--input", getattr(args, "input", None)),
-                      ("--checkpoint", getattr(args, "checkpoint", None) or _weights_file(getattr(args, "weights", None)))):
+    for flag, val in (("--prompt", args.prompt), ("--input", getattr(args, "input", None)), ("--checkpoint", ckpt)):
         if val:
             wargs += [flag, str(val)]
     if allow_partial:

@@ -97,11 +97,13 @@ class LoadReport:
 
 
 def load_checkpoint(model: torch.nn.Module, path: str, expected_sha256: Optional[str] = None,
-                    strict: bool = True, ema: Optional[bool] = None, mapper=None) -> LoadReport:
+                    strict: bool = True, ema: Optional[bool] = None, mapper=None, dry_run: bool = False) -> LoadReport:
     """Load by name after prefix stripping (and after ``mapper``, a function state -> state that translates an
     upstream's parameter names into this package's: :mod:`models.mappers`).  ``strict`` (the default): every parameter of the model must be in the
     checkpoint with its shape and the checkpoint may hold nothing else, otherwise ``ValueError`` - a run on partly
-    random weights is never silent.  ``strict=False`` loads what matches and reports the rest."""
+    random weights is never silent.  ``strict=False`` loads what matches and reports the rest.  ``dry_run`` checks
+    names and shapes (and raises as above) without writing a parameter - a launcher holds a checkpoint against a
+    model built on the meta device before it starts rank processes."""
     state = strip_prefixes(read_state(path, expected_sha256), ema=ema)
     if mapper is not None:
         state = mapper(state)
@@ -124,6 +126,8 @@ def load_checkpoint(model: torch.nn.Module, path: str, expected_sha256: Optional
         raise ValueError(f"{path}: {len(rep.missing)} missing / {len(rep.unexpected)} unexpected / "
                          f"{len(rep.shape_mismatch)} shape-mismatched parameters (first: "
                          f"{(rep.missing + rep.unexpected + rep.shape_mismatch)[0]})")
+    if dry_run:                                    # names and shapes only: the model may live on the meta device
+        return rep
     model.load_state_dict({k: v.to(own[k].dtype) for k, v in matched.items()}, strict=False)
     for m in model.modules():                      # packed (folded) weights are rebuilt from the new parameters
         if hasattr(m, "_packed"):
