@@ -350,11 +350,14 @@ def test_sequence_kit_sharded_launcher_checks_the_checkpoint_before_it_starts_ra
         return argparse.Namespace(verb="score", model_config="evo2_tiny", prompt="ACGTTGCAAC", input=None, seed=0,
                                   max_new_tokens=4, checkpoint=str(ckpt), weights=None, out_dir=str(out))
 
-    act = base.Activation(spec, "fast", "cli", 2, probe=_b200(), environ={})
-    rc = run._run_lm_sharded(spec, act, args(tmp_path / "one.pt", tmp_path / "o1"), False)
+    def activation():
+        act = base.Activation(spec, "fast", "cli", 2, probe=_b200(), environ={})
+        act.register_exit = lambda: None            # no exit hook in the test process
+        return act
+
+    rc = run._run_lm_sharded(spec, activation(), args(tmp_path / "one.pt", tmp_path / "o1"), False)
     assert rc == report.EXIT_NOT_ACTIVE and not os.path.exists(tmp_path / "o1" / "score.json")
-    act = base.Activation(spec, "fast", "cli", 2, probe=_b200(), environ={})
-    rc = run._run_lm_sharded(spec, act, args(tmp_path / "full.pt", tmp_path / "o2"), False)
+    rc = run._run_lm_sharded(spec, activation(), args(tmp_path / "full.pt", tmp_path / "o2"), False)
     res = json.load(open(tmp_path / "o2" / "score.json"))
     m.eval()
     want = float(m.score(evo2.tokenize("ACGTTGCAAC"))[0])
