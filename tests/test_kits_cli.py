@@ -364,3 +364,29 @@ def test_sequence_kit_sharded_launcher_checks_the_checkpoint_before_it_starts_ra
     assert res["world"] == 2 and abs(res["score"] - want) <= 1e-4 * max(1.0, abs(want))
     err = capsys.readouterr().err
     assert "WEIGHTS" in err and "sharding=tensor_parallel" in err and "NOT ACTIVE" in err
+
+
+def test_sharded_cofold_launcher_refuses_a_checkpoint_that_does_not_fit_before_it_starts_ranks(tmp_path, capsys):
+    import argparse
+    import torch
+    from uplifting_biomolecular_modeling_b200.core import report
+    from uplifting_biomolecular_modeling_b200.models import cofold
+    from uplifting_biomolecular_modeling_b200.parallel import launch
+    m = cofold.build_model("tiny", seed=1)
+    k0 = next(iter(m.state_dict()))
+    torch.save({"state_dict": {k0: m.state_dict()[k0]}}, tmp_path / "one.ckpt")
+    spec = registry.get("boltz2")
+    act = base.Activation(spec, "big", "cli", 2, probe=_b200(), environ={})
+    act.register_exit = lambda: None
+    args = argparse.Namespace(checkpoint=str(tmp_path / "one.ckpt"), weights=None, tokens=32, msa_depth=2, seed=0,
+                              out_dir=None, recycling_steps=None, input=None, sampling_steps=None,
+                              diffusion_samples=None)
+    started = []
+    real = launch.run_sharded
+    launch.run_sharded = lambda *a, **k: started.append(a)
+    try:
+        rc = launch.run_prediction_sharded(spec, act, args, "tiny", False)
+    finally:
+        launch.run_sharded = real
+    assert rc == report.EXIT_NOT_ACTIVE and not started
+    assert "NOT ACTIVE" in capsys.readouterr().err

@@ -202,11 +202,28 @@ def arm_exit_guard(rank: int, grace_s: Optional[float] = None) -> None:
 def run_prediction_sharded(spec, act, args, config: str, allow_partial: bool) -> int:
     """``pred --mode big --n_gpu P``: start P ranks of ``parallel.worker``; the parent prints ACTIVE and EXIT."""
     act.levers_on = act.plan()
+    ckpt = args.checkpoint or args.weights
+    if ckpt:
+        # names and shapes are held against a model on the meta device before any rank starts, so that a checkpoint
+        # that does not fit is NOT ACTIVE with exit 3 instead of a failed rank
+        import torch
+        from ..models import cofold, mappers, weights
+        try:
+            with torch.device("meta"):
+                probe = cofold.CofoldModel(cofold.CONFIGS[config])
+            rep = weights.load_checkpoint(probe, ckpt, strict=not allow_partial, dry_run=True,
+                                          mapper=mappers.for_kit(spec.name))
+        except (ValueError, OSError) as e:
+            act.refuse(f"checkpoint {ckpt}: {e}")
+            return report.EXIT_NOT_ACTIVE
+        report.emit(report.line(spec.tag, "WEIGHTS", ("path", ckpt), ("matched", rep.matched),
+                                ("missing", len(rep.missing)), ("unexpected", len(rep.unexpected)),
+                                ("shape_mismatch", len(rep.shape_mismatch)), ("init_skipped", 0)))
     report.emit(report.with_words(report.line(spec.tag, "ACTIVE", ("mode", act.mode), ("levers", act.levers_on),
                                               ("source", act.source), ("n_gpu", act.n_gpu),
                                               ("sharding", "rowpair")), act.words))
     wargs = ["--config", config, "--tokens", str(args.tokens or 256), "--msa_depth", str(args.msa_depth or 1),
-             "--seed", str(args.seed), "--structure", "1"]
+             "--seed", str(args.seed), "--structure", "1", "--kit", spec.name]
     if args.out_dir:
         wargs += ["--out_dir", args.out_dir]
     if args.recycling_steps is not None:

@@ -44,6 +44,7 @@ def main(argv=None) -> int:
     ap.add_argument("--structure", type=int, default=0, help="1 = sampler and confidence head on rank 0 after the trunk")
     ap.add_argument("--input", default=None, help="feature file (.pt) or complex description (.json), read by rank 0")
     ap.add_argument("--checkpoint", default=None)
+    ap.add_argument("--kit", default="", help="kit name: selects the checkpoint name mapper of its upstream, if any")
     ap.add_argument("--allow-partial", action="store_true")
     ap.add_argument("--sampling_steps", type=int, default=None)
     ap.add_argument("--diffusion_samples", type=int, default=None)
@@ -56,7 +57,8 @@ def main(argv=None) -> int:
     model = cofold.build_model(a.config, device=dev, dtype=dtype, seed=a.seed, **over)
     if a.checkpoint:
         from ..models import weights
-        rep = weights.load_checkpoint(model, a.checkpoint, strict=not a.allow_partial)
+        from ..models import mappers
+        rep = weights.load_checkpoint(model, a.checkpoint, strict=not a.allow_partial, mapper=mappers.for_kit(a.kit))
         report.emit(report.line(TAG, "WEIGHTS", ("rank", comm.rank), ("matched", rep.matched),
                                 ("missing", len(rep.missing)), ("unexpected", len(rep.unexpected))))
     comm.check_replicated(next(model.parameters()).float(), "model weights")
